@@ -1,0 +1,123 @@
+// One-shot all-reduce over peer memory (NVLink 5 / NVSwitch), 2..8 ranks, bf16 payload, fp32 sum in
+// rank order (every rank adds the same values in the same order, so results are bit-identical
+// across ranks).  Block b owns chunk b of the message end to end: push own chunk into every
+// peer's receive slot, release a flag per peer, wait (bounded) for every peer's flag, reduce.
+#include "comm.h"
+#include <string.h>
+
+namespace saber {
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long ar_now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const AllReduceParams p) {
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const uint32_t seq = *p.seq_base + static_cast<uint32_t>(p.site) + 1u;
+  const uint32_t par = seq & 1u;
+  const int nvec = p.n_elems >> 3;
+  const int per = (nvec + kArBlocks - 1) / kArBlocks;
+  const int v0 = b * per, v1 = min(nvec, v0 + per);
+  const uint4* src = reinterpret_cast<const uint4*>(p.in);
+  const size_t slot_vecs = static_cast<size_t>(p.max_elems) >> 3;
+
+  // push
+  for (int peer = 0; peer < p.nranks; ++peer) {
+    if (peer == p.rank) continue;
+    uint4* dst = reinterpret_cast<uint4*>(p.peer_recv[peer]) + (par * p.nranks + p.rank) * slot_vecs;
+    for (int v = v0 + tid; v < v1; v += blockDim.x) dst[v] = src[v];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < p.nranks && tid != p.rank)
+    st_release_sys(p.peer_flags[tid] + (par * p.nranks + p.rank) * kArBlocks + b, seq);
+
+  // wait (bounded): flag of peer `tid` in this rank's own region
+  if (tid < p.nranks && tid != p.rank) {
+    const uint32_t* f = p.peer_flags[p.rank] + (par * p.nranks + tid) * kArBlocks + b;
+    const unsigned long long limit =
+        (p.spin_limit_us ? static_cast<unsigned long long>(p.spin_limit_us) : 1000000ull) * 1000ull;
+    const unsigned long long t0 = ar_now_ns();
+    while (static_cast<int32_t>(ld_acquire_sys(f) - seq) < 0) {
+      if (ar_now_ns() - t0 > limit) {
+        atomicCAS(p.err, 0u, 5u);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+
+  // reduce in rank order
+  const uint4* own_recv = reinterpret_cast<const uint4*>(p.peer_recv[p.rank]);
+  uint4* dst = reinterpret_cast<uint4*>(p.out);
+  for (int v = v0 + tid; v < v1; v += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < p.nranks; ++s) {
+      const uint4 raw = (s == p.rank) ? src[v] : __ldcg(own_recv + (par * p.nranks + s) * slot_vecs + v);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    dst[v] = o;
+  }
+}
+
+__global__ void comm_advance_kernel(uint32_t* seq_base, uint32_t by) { *seq_base += by; }
+
+}  // namespace saber
+
+extern "C" int saber_allreduce_launch(const saber::AllReduceParams* p, cudaStream_t stream) {
+  using namespace saber;
+  if (p->nranks < 1 || p->nranks > kMaxRanks || (p->n_elems & 7) || p->n_elems > p->max_elems)
+    return static_cast<int>(cudaErrorInvalidValue);
+  if (p->nranks == 1) {
+    if (p->out != p->in)
+      return static_cast<int>(cudaMemcpyAsync(p->out, p->in, static_cast<size_t>(p->n_elems) * 2,
+                                              cudaMemcpyDeviceToDevice, stream));
+    return 0;
+  }
+  allreduce_oneshot_kernel<<<kArBlocks, 512, 0, stream>>>(*p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int saber_comm_advance_launch(uint32_t* seq_base, uint32_t by, cudaStream_t stream) {
+  saber::comm_advance_kernel<<<1, 1, 0, stream>>>(seq_base, by);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int saber_ipc_get_handle(void* dev_ptr, void* out_handle_64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, dev_ptr);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  static_assert(sizeof(h) == 64, "IPC handle is 64 bytes");
+  memcpy(out_handle_64, &h, 64);
+  return 0;
+}
+extern "C" int saber_ipc_open_handle(const void* handle_64, void** out_ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle_64, 64);
+  return static_cast<int>(cudaIpcOpenMemHandle(out_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+extern "C" int saber_ipc_close(void* ptr) { return static_cast<int>(cudaIpcCloseMemHandle(ptr)); }
+extern "C" int saber_dev_malloc(void** out, size_t bytes) {
+  return static_cast<int>(cudaMalloc(out, bytes));
+}
+extern "C" int saber_dev_free(void* p) { return static_cast<int>(cudaFree(p)); }

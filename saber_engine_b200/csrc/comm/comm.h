@@ -1,0 +1,43 @@
+// Peer-memory communication: symmetric-heap helpers (CUDA IPC) and the one-shot all-reduce family.
+//
+// Every rank allocates the same regions at the same offsets of its own heap and maps every peer's
+// heap; kernels then store straight into peers over NVLink and signal with system-scope flags.
+// Sequence numbers instead of toggling bits: each collective call site of a program has a static
+// index, the rank keeps one device word `seq_base` that advances by the program's site count at
+// the end of every program run, and a call's sequence is seq_base + site + 1.  Ranks run the same
+// programs in the same order, so sequences agree without any host exchange, receive slots are
+// double-buffered by sequence parity, and every flag wait is bounded (error word, no hang).
+//
+// Parity: the reference's 2-rank one-shot push all-reduce with parity slots and bounded spins
+// (crates/saber-kernels/hip/sar_exact.h:1-10, sar_prims.h:78-120) and its global-parity form
+// (flashnext_ar_gp.hip:1-8), generalised to 8 ranks over NVSwitch.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace saber {
+
+constexpr int kMaxRanks = 8;
+constexpr int kArBlocks = 32;   // fixed grid of the stand-alone all-reduce: flags are per block
+
+struct AllReduceParams {
+  const __nv_bfloat16* in;      // [n_elems] this rank's partial
+  __nv_bfloat16* out;           // [n_elems] reduced result (may alias in)
+  void* peer_recv[kMaxRanks];   // each rank's receive region: [2][nranks][max_elems] bf16
+  uint32_t* peer_flags[kMaxRanks];  // each rank's flag region: [2][nranks][kArBlocks]
+  const uint32_t* seq_base;     // this rank's sequence base (device word)
+  uint32_t* err;
+  int n_elems, max_elems, site, nranks, rank;
+  uint32_t spin_limit_us;       // 0 = default bound
+};
+
+}  // namespace saber
+
+extern "C" int saber_allreduce_launch(const saber::AllReduceParams* p, cudaStream_t stream);
+extern "C" int saber_comm_advance_launch(uint32_t* seq_base, uint32_t by, cudaStream_t stream);
+extern "C" int saber_ipc_get_handle(void* dev_ptr, void* out_handle_64);
+extern "C" int saber_ipc_open_handle(const void* handle_64, void** out_ptr);
+extern "C" int saber_ipc_close(void* ptr);
+extern "C" int saber_dev_malloc(void** out, size_t bytes);
+extern "C" int saber_dev_free(void* p);

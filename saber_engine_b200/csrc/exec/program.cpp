@@ -1,0 +1,215 @@
+// Step program: the native executor of a decode/prefill bucket.
+//
+// A program is an ordered list of kernel launches whose parameter blocks (pointers, shapes,
+// strides) are all fixed when the bucket is built; everything that changes from step to step
+// (positions, block tables, slot ids, accepted-row counts) lives in device index buffers the
+// kernels read.  The same list is therefore (a) walked eagerly, one launch per op, and (b) captured
+// once into a CUDA graph and replayed with a single launch per step.  After capture the graph's
+// kernel-node count must equal the launches the ops declared, so a silent extra or missing launch
+// is a build error, not a performance mystery.
+//
+// Parity: this is the role of the reference's CapturedBucket / Launcher / BlockPlan trio
+// (crates/saber-exec/src/capture.rs:13-30 asserted node counts, src/launch.rs:1-25,
+// src/layer.rs:1-45), re-shaped for CUDA graphs and typed parameter blocks instead of packed
+// kernarg buffers.
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <string>
+#include <variant>
+#include <vector>
+
+#include "../comm/comm.h"
+#include "../kernels/attn.h"
+#include "../kernels/gdn.h"
+#include "../kernels/gemm_i8.h"
+#include "../kernels/rowops.h"
+#include "../kernels/sample.h"
+
+namespace {
+
+struct OpGemm { saber::GemmI8Params p; int stages; };
+struct OpRow { int mode; saber::RowOpParams p; };
+struct OpEmbed { const void* table; const int32_t* ids; void* out; int M, H, vocab_lo, vocab_n; };
+struct OpGdnConv { saber::GdnConvParams p; int nseq; };
+struct OpGdnRec { saber::GdnRecParams p; int nseq, vs; };
+struct OpRope { saber::RopeKvParams p; };
+struct OpAttn { saber::AttnParams p; };
+struct OpArgmax { const void* logits; int rows, ld, V, id_offset; int32_t* idx; float* val; };
+struct OpSeam { const void* logits; int rows, ld, V, id_offset; const float* temps; int32_t* ids; float* vals; float* lse; };
+struct OpVerify { saber::VerifyParams p; };
+struct OpMemset { void* dst; int value; size_t bytes; };
+struct OpCopy { void* dst; const void* src; size_t bytes; };
+struct OpAllReduce { saber::AllReduceParams p; };
+
+using Op = std::variant<OpGemm, OpRow, OpEmbed, OpGdnConv, OpGdnRec, OpRope, OpAttn, OpArgmax,
+                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce>;
+
+struct Entry {
+  Op op;
+  int launches;      // kernel/memset/memcpy nodes this op contributes to a captured graph
+  std::string tag;   // label for explain / tracing
+};
+
+struct Program {
+  std::vector<Entry> ops;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  int captured_nodes = -1;
+  int last_failed_op = -1;
+};
+
+int launch(const Op& op, cudaStream_t s) {
+  return std::visit(
+      [&](auto&& o) -> int {
+        using T = std::decay_t<decltype(o)>;
+        if constexpr (std::is_same_v<T, OpGemm>) return saber_gemm_i8_launch(&o.p, o.stages, s);
+        else if constexpr (std::is_same_v<T, OpRow>) return saber_row_producer_launch(o.mode, &o.p, s);
+        else if constexpr (std::is_same_v<T, OpEmbed>)
+          return saber_embed_gather_launch(o.table, o.ids, o.out, o.M, o.H, o.vocab_lo, o.vocab_n, s);
+        else if constexpr (std::is_same_v<T, OpGdnConv>) return saber_gdn_conv_launch(&o.p, o.nseq, s);
+        else if constexpr (std::is_same_v<T, OpGdnRec>) return saber_gdn_recurrent_launch(&o.p, o.nseq, o.vs, s);
+        else if constexpr (std::is_same_v<T, OpRope>) return saber_rope_kv_launch(&o.p, s);
+        else if constexpr (std::is_same_v<T, OpAttn>) return saber_attn_launch(&o.p, s);
+        else if constexpr (std::is_same_v<T, OpArgmax>)
+          return saber_argmax_launch(o.logits, o.rows, o.ld, o.V, o.id_offset, o.idx, o.val, s);
+        else if constexpr (std::is_same_v<T, OpSeam>)
+          return saber_topk_seam_launch(o.logits, o.rows, o.ld, o.V, o.id_offset, o.temps, o.ids, o.vals, o.lse, s);
+        else if constexpr (std::is_same_v<T, OpVerify>) return saber_verify_launch(&o.p, s);
+        else if constexpr (std::is_same_v<T, OpMemset>)
+          return static_cast<int>(cudaMemsetAsync(o.dst, o.value, o.bytes, s));
+        else if constexpr (std::is_same_v<T, OpCopy>)
+          return static_cast<int>(cudaMemcpyAsync(o.dst, o.src, o.bytes, cudaMemcpyDeviceToDevice, s));
+        else if constexpr (std::is_same_v<T, OpAllReduce>) return saber_allreduce_launch(&o.p, s);
+        else return static_cast<int>(cudaErrorInvalidValue);
+      },
+      op);
+}
+
+int add(void* h, Op op, int launches, const char* tag) {
+  auto* pr = static_cast<Program*>(h);
+  pr->ops.push_back(Entry{std::move(op), launches, tag ? tag : ""});
+  return static_cast<int>(pr->ops.size()) - 1;
+}
+
+}  // namespace
+
+extern "C" {
+
+void* saber_program_create() { return new Program(); }
+
+void saber_program_destroy(void* h) {
+  auto* pr = static_cast<Program*>(h);
+  if (!pr) return;
+  if (pr->exec) cudaGraphExecDestroy(pr->exec);
+  if (pr->graph) cudaGraphDestroy(pr->graph);
+  delete pr;
+}
+
+int saber_program_add_gemm(void* h, const saber::GemmI8Params* p, int stages, const char* tag) {
+  return add(h, OpGemm{*p, stages}, 1, tag);
+}
+int saber_program_add_row(void* h, int mode, const saber::RowOpParams* p, const char* tag) {
+  return add(h, OpRow{mode, *p}, 1, tag);
+}
+int saber_program_add_embed(void* h, const void* table, const int32_t* ids, void* out, int M, int H,
+                            int vocab_lo, int vocab_n, const char* tag) {
+  return add(h, OpEmbed{table, ids, out, M, H, vocab_lo, vocab_n}, 1, tag);
+}
+int saber_program_add_gdn_conv(void* h, const saber::GdnConvParams* p, int nseq, const char* tag) {
+  return add(h, OpGdnConv{*p, nseq}, p->commit ? 2 : 1, tag);
+}
+int saber_program_add_gdn_rec(void* h, const saber::GdnRecParams* p, int nseq, int vs, const char* tag) {
+  return add(h, OpGdnRec{*p, nseq, vs}, 1, tag);
+}
+int saber_program_add_rope(void* h, const saber::RopeKvParams* p, const char* tag) {
+  return add(h, OpRope{*p}, 1, tag);
+}
+int saber_program_add_attn(void* h, const saber::AttnParams* p, const char* tag) {
+  return add(h, OpAttn{*p}, p->splits > 1 ? 2 : 1, tag);
+}
+int saber_program_add_argmax(void* h, const void* logits, int rows, int ld, int V, int id_offset,
+                             int32_t* idx, float* val, const char* tag) {
+  return add(h, OpArgmax{logits, rows, ld, V, id_offset, idx, val}, 1, tag);
+}
+int saber_program_add_seam(void* h, const void* logits, int rows, int ld, int V, int id_offset,
+                           const float* temps, int32_t* ids, float* vals, float* lse, const char* tag) {
+  return add(h, OpSeam{logits, rows, ld, V, id_offset, temps, ids, vals, lse}, 1, tag);
+}
+int saber_program_add_verify(void* h, const saber::VerifyParams* p, const char* tag) {
+  return add(h, OpVerify{*p}, 1, tag);
+}
+int saber_program_add_memset(void* h, void* dst, int value, size_t bytes, const char* tag) {
+  return add(h, OpMemset{dst, value, bytes}, 1, tag);
+}
+int saber_program_add_copy(void* h, void* dst, const void* src, size_t bytes, const char* tag) {
+  return add(h, OpCopy{dst, src, bytes}, 1, tag);
+}
+int saber_program_add_allreduce(void* h, const saber::AllReduceParams* p, const char* tag) {
+  return add(h, OpAllReduce{*p}, 1, tag);
+}
+
+int saber_program_num_ops(void* h) { return static_cast<int>(static_cast<Program*>(h)->ops.size()); }
+
+int saber_program_declared_launches(void* h) {
+  int n = 0;
+  for (auto& e : static_cast<Program*>(h)->ops) n += e.launches;
+  return n;
+}
+
+const char* saber_program_op_tag(void* h, int i) {
+  auto* pr = static_cast<Program*>(h);
+  return (i >= 0 && i < static_cast<int>(pr->ops.size())) ? pr->ops[i].tag.c_str() : "";
+}
+
+int saber_program_last_failed_op(void* h) { return static_cast<Program*>(h)->last_failed_op; }
+
+// Eager walk of ops [first, last). Returns 0 or the CUDA error of the first failing launch.
+int saber_program_run_range(void* h, int first, int last, cudaStream_t stream) {
+  auto* pr = static_cast<Program*>(h);
+  const int n = static_cast<int>(pr->ops.size());
+  if (last < 0 || last > n) last = n;
+  for (int i = first; i < last; ++i) {
+    const int e = launch(pr->ops[i].op, stream);
+    if (e != 0) { pr->last_failed_op = i; return e; }
+  }
+  return 0;
+}
+
+int saber_program_run(void* h, cudaStream_t stream) { return saber_program_run_range(h, 0, -1, stream); }
+
+// Capture the whole program on `stream` (which must not be the legacy default stream) and
+// instantiate it. Returns the number of nodes in the captured graph, or -(cuda error).
+int saber_program_capture(void* h, cudaStream_t stream) {
+  auto* pr = static_cast<Program*>(h);
+  if (pr->exec) { cudaGraphExecDestroy(pr->exec); pr->exec = nullptr; }
+  if (pr->graph) { cudaGraphDestroy(pr->graph); pr->graph = nullptr; }
+  cudaError_t e = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+  if (e != cudaSuccess) return -static_cast<int>(e);
+  const int le = saber_program_run(h, stream);
+  cudaGraph_t g = nullptr;
+  e = cudaStreamEndCapture(stream, &g);
+  if (le != 0) { if (g) cudaGraphDestroy(g); return -le; }
+  if (e != cudaSuccess) return -static_cast<int>(e);
+  size_t nodes = 0;
+  e = cudaGraphGetNodes(g, nullptr, &nodes);
+  if (e != cudaSuccess) { cudaGraphDestroy(g); return -static_cast<int>(e); }
+  cudaGraphExec_t ex = nullptr;
+  e = cudaGraphInstantiate(&ex, g, 0);
+  if (e != cudaSuccess) { cudaGraphDestroy(g); return -static_cast<int>(e); }
+  pr->graph = g;
+  pr->exec = ex;
+  pr->captured_nodes = static_cast<int>(nodes);
+  return pr->captured_nodes;
+}
+
+int saber_program_replay(void* h, cudaStream_t stream) {
+  auto* pr = static_cast<Program*>(h);
+  if (!pr->exec) return static_cast<int>(cudaErrorInvalidValue);
+  return static_cast<int>(cudaGraphLaunch(pr->exec, stream));
+}
+
+int saber_program_captured_nodes(void* h) { return static_cast<Program*>(h)->captured_nodes; }
+
+}  // extern "C"

@@ -1,0 +1,219 @@
+// Gated DeltaNet (linear attention) step kernels for sm_100a.
+//
+// Math (per value head, state S[V=128][K=128], one token):
+//   g = -exp(A_log) * softplus(a + dt_bias);  beta = sigmoid(b)
+//   S <- S * exp(g);  u = (v - S k) * beta;  S <- S + u (x) k;  o = S q
+// with q, k the causal depthwise conv (4 taps) + SiLU outputs, L2-normalised per head, q scaled by
+// 1/sqrt(128).  Parity: crates/saber-kernels/hip/sgdn_rec.h:1-30 (recurrence), sgdn_conv.h:1-10
+// (conv), and the base + stash + replay form of sgdn_replay.h:1-12: the state in memory is always
+// the COMMITTED state; a speculative step's rows run on a register copy and leave only a small
+// stash (k, v, g, beta per row); the next step first replays the `shift` rows that were accepted,
+// stores the new committed state, and then answers its own rows.  No per-row state snapshots.
+//
+// Two launches per layer: conv_update (thread = channel, block = one 128-wide head so the q/k L2
+// norm is a block reduction) and recurrent (CTA = (value head, v-slice, sequence), two threads per
+// state row holding 64 fp32 each).  Prefill chunks use the same kernels with commit=1: rows are
+// consumed for good, the final state is stored and conv_commit rewrites the conv window.
+#include "gdn.h"
+#include <cuda_bf16.h>
+
+namespace saber {
+
+__device__ __forceinline__ float gdn_silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float gdn_softplus(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+
+// ---------------------------------------------------------------------------------- conv update
+// grid (C / 128, nseq), block 128.
+__global__ void __launch_bounds__(128) gdn_conv_update_kernel(const GdnConvParams p) {
+  __shared__ float red[4];
+  const int b = blockIdx.y;
+  const int slot = p.slots[b];
+  if (slot < 0) return;
+  const int ch = blockIdx.x * 128 + threadIdx.x;
+  const int row0 = p.cu_rows[b];
+  const int n = p.cu_rows[b + 1] - row0;
+  if (n <= 0) return;
+  const int shift = p.shift[b];
+  __nv_bfloat16* hp = p.hist + static_cast<size_t>(slot) * p.hist_rows * p.C + ch;
+  // window = the three committed inputs that precede this step's first row
+  float b0 = __bfloat162float(hp[static_cast<size_t>(shift) * p.C]);
+  float b1 = __bfloat162float(hp[static_cast<size_t>(shift + 1) * p.C]);
+  float b2 = __bfloat162float(hp[static_cast<size_t>(shift + 2) * p.C]);
+  if (!p.commit) {
+    hp[0] = __float2bfloat16(b0);
+    hp[p.C] = __float2bfloat16(b1);
+    hp[2 * static_cast<size_t>(p.C)] = __float2bfloat16(b2);
+  }
+  const float w0 = p.conv_w[ch * 4 + 0], w1 = p.conv_w[ch * 4 + 1], w2 = p.conv_w[ch * 4 + 2],
+              w3 = p.conv_w[ch * 4 + 3];
+  const bool is_q = ch < p.n_q, is_k = !is_q && ch < p.n_q + p.n_k;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int r = 0; r < n; ++r) {
+    const __nv_bfloat16 xb = p.x[static_cast<size_t>(row0 + r) * p.ldx + ch];
+    const float x = __bfloat162float(xb);
+    float y = gdn_silu(w0 * b0 + w1 * b1 + w2 * b2 + w3 * x);
+    b0 = b1; b1 = b2; b2 = x;
+    if (!p.commit && r < p.hist_rows - 3) hp[static_cast<size_t>(3 + r) * p.C] = xb;
+    if (is_q || is_k) {  // uniform per block: a block is one head
+      float ss = y * y;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      __syncthreads();
+      if (lane == 0) red[warp] = ss;
+      __syncthreads();
+      ss = red[0] + red[1] + red[2] + red[3];
+      y *= rsqrtf(ss + 1e-6f);
+      if (is_q) y *= p.q_scale;
+    }
+    p.out[static_cast<size_t>(row0 + r) * p.C + ch] = y;
+  }
+}
+
+// After a committing (prefill) step: window = last three inputs of (old window ++ this step's rows).
+__global__ void __launch_bounds__(128) gdn_conv_commit_kernel(const GdnConvParams p) {
+  const int b = blockIdx.y;
+  const int slot = p.slots[b];
+  if (slot < 0) return;
+  const int ch = blockIdx.x * 128 + threadIdx.x;
+  const int row0 = p.cu_rows[b];
+  const int n = p.cu_rows[b + 1] - row0;
+  if (n <= 0) return;
+  const int shift = p.shift[b];
+  __nv_bfloat16* hp = p.hist + static_cast<size_t>(slot) * p.hist_rows * p.C + ch;
+  __nv_bfloat16 win[3];
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    const int j = n + i;  // index into (old window(3) ++ rows(n)), last three are j = n..n+2
+    win[i] = j < 3 ? hp[static_cast<size_t>(shift + j) * p.C]
+                   : p.x[static_cast<size_t>(row0 + j - 3) * p.ldx + ch];
+  }
+#pragma unroll
+  for (int i = 0; i < 3; ++i) hp[static_cast<size_t>(i) * p.C] = win[i];
+}
+
+// ---------------------------------------------------------------------------------- recurrence
+// grid (HV * VS, nseq); block = 2 * (128 / VS) threads; thread = (v row, k half).
+template <int VS>
+__global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecParams p) {
+  constexpr int VR = 128 / VS;         // v rows per CTA
+  constexpr int NT = 2 * VR;           // threads
+  constexpr int KP = 64 + 4;           // padded half stride in shared memory (bank spread)
+  __shared__ __align__(16) float ks[2][2 * KP];
+  __shared__ __align__(16) float qs[2][2 * KP];
+  const int b = blockIdx.y;
+  const int slot = p.slots[b];
+  if (slot < 0) return;
+  const int h = blockIdx.x / VS, vs = blockIdx.x % VS;
+  const int hk = h / (p.HV / p.HK);
+  const int tid = threadIdx.x;
+  const int vloc = tid >> 1, kh = tid & 1;
+  const int v = vs * VR + vloc;
+  const int row0 = p.cu_rows[b];
+  const int n = p.cu_rows[b + 1] - row0;
+  const int shift = p.shift[b];
+  const int stash_stride = 128 + VR + 4;
+  float* sp = p.state + ((static_cast<size_t>(slot) * p.HV + h) * 128 + v) * 128 + kh * 64;
+  float* stash = p.stash + ((static_cast<size_t>(slot) * p.stash_rows) * p.HV * VS +
+                            static_cast<size_t>(h) * VS + vs) * stash_stride;
+  const size_t stash_row = static_cast<size_t>(p.HV) * VS * stash_stride;
+
+  float S[64];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float4 t = reinterpret_cast<const float4*>(sp)[i];
+    S[4 * i] = t.x; S[4 * i + 1] = t.y; S[4 * i + 2] = t.z; S[4 * i + 3] = t.w;
+  }
+  const float neg_a = -__expf(p.A_log[h]);
+  const float dtb = p.dt_bias[h];
+
+  auto apply = [&](const float* kv, const float* qv, float vval, float g, float beta,
+                   bool want_o) -> float {
+    const float decay = __expf(g);
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      S[i] *= decay;
+      dot += S[i] * kv[i];
+    }
+    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+    const float u = (vval - dot) * beta;
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+      S[i] += u * kv[i];
+      if (want_o) o += S[i] * qv[i];
+    }
+    if (want_o) o += __shfl_xor_sync(0xffffffffu, o, 1);
+    return o;
+  };
+
+  // ---- replay the accepted rows of the previous step, then store the committed state
+  int buf = 0;
+  for (int r = 0; r < shift; ++r) {
+    const float* st = stash + static_cast<size_t>(r) * stash_row;
+    for (int i = tid; i < 128; i += NT) ks[buf][(i >> 6) * KP + (i & 63)] = st[i];
+    __syncthreads();
+    const float vval = st[128 + vloc];
+    const float g = st[128 + VR], beta = st[128 + VR + 1];
+    apply(&ks[buf][kh * KP], nullptr, vval, g, beta, false);
+    buf ^= 1;
+  }
+  if (shift > 0) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      reinterpret_cast<float4*>(sp)[i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+  }
+  __syncthreads();
+
+  // ---- this step's rows
+  for (int r = 0; r < n; ++r) {
+    const size_t m = static_cast<size_t>(row0 + r);
+    const float* xr = p.qkv + m * p.C;
+    for (int i = tid; i < 128; i += NT) {
+      qs[buf][(i >> 6) * KP + (i & 63)] = xr[hk * 128 + i];
+      ks[buf][(i >> 6) * KP + (i & 63)] = xr[p.n_q + hk * 128 + i];
+    }
+    const float vval = xr[p.n_q + p.n_k + h * 128 + v];
+    const float bb = __bfloat162float(p.ba[m * p.ldba + h]);
+    const float aa = __bfloat162float(p.ba[m * p.ldba + p.HV + h]);
+    const float g = neg_a * gdn_softplus(aa + dtb);
+    const float beta = 1.f / (1.f + __expf(-bb));
+    __syncthreads();
+    const float o = apply(&ks[buf][kh * KP], &qs[buf][kh * KP], vval, g, beta, true);
+    if (kh == 0) p.out[m * (static_cast<size_t>(p.HV) * 128) + h * 128 + v] = o;
+    if (!p.commit && r < p.stash_rows) {
+      float* st = stash + static_cast<size_t>(r) * stash_row;
+      for (int i = tid; i < 128; i += NT) st[i] = ks[buf][(i >> 6) * KP + (i & 63)];
+      if (kh == 0) st[128 + vloc] = vval;
+      if (tid == 0) { st[128 + VR] = g; st[128 + VR + 1] = beta; }
+    }
+    buf ^= 1;
+  }
+  if (p.commit && n > 0) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      reinterpret_cast<float4*>(sp)[i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+  }
+}
+
+}  // namespace saber
+
+extern "C" int saber_gdn_conv_launch(const saber::GdnConvParams* p, int nseq, cudaStream_t stream) {
+  using namespace saber;
+  if (p->C % 128 || p->n_q % 128 || p->n_k % 128) return static_cast<int>(cudaErrorInvalidValue);
+  dim3 grid(p->C / 128, nseq);
+  gdn_conv_update_kernel<<<grid, 128, 0, stream>>>(*p);
+  if (p->commit) gdn_conv_commit_kernel<<<grid, 128, 0, stream>>>(*p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int saber_gdn_recurrent_launch(const saber::GdnRecParams* p, int nseq, int vs,
+                                          cudaStream_t stream) {
+  using namespace saber;
+  if (p->HV % p->HK) return static_cast<int>(cudaErrorInvalidValue);
+  if (vs == 1) gdn_recurrent_kernel<1><<<dim3(p->HV, nseq), 256, 0, stream>>>(*p);
+  else if (vs == 2) gdn_recurrent_kernel<2><<<dim3(p->HV * 2, nseq), 128, 0, stream>>>(*p);
+  else if (vs == 4) gdn_recurrent_kernel<4><<<dim3(p->HV * 4, nseq), 64, 0, stream>>>(*p);
+  else return static_cast<int>(cudaErrorInvalidValue);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,39 @@
+// Launch interface of the Gated DeltaNet step kernels.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace saber {
+
+struct GdnConvParams {
+  const __nv_bfloat16* x;   // [M][ldx] projected q|k|v channels of this step's rows
+  const float* conv_w;      // [C][4], tap 3 multiplies the current input
+  __nv_bfloat16* hist;      // [nslots][hist_rows][C]: rows 0..2 committed window, 3.. this step's inputs
+  const int32_t* cu_rows;   // [nseq + 1] first row of each sequence
+  const int32_t* slots;     // [nseq] state slot, < 0 = padding sequence
+  const int32_t* shift;     // [nseq] rows of the previous step that were accepted (0 after a commit)
+  float* out;               // [M][C] conv+SiLU (+L2 norm for q,k; q also scaled)
+  int C, n_q, n_k, ldx, hist_rows, commit;
+  float q_scale;
+};
+
+struct GdnRecParams {
+  const float* qkv;         // [M][C] output of the conv kernel
+  const __nv_bfloat16* ba;  // [M][ldba]: b (beta logits) at [0, HV), a (decay input) at [HV, 2 HV)
+  const float* A_log;       // [HV]
+  const float* dt_bias;     // [HV]
+  float* state;             // [nslots][HV][128][128] committed recurrent state
+  float* stash;             // [nslots][stash_rows][HV][VS][128 + 128/VS + 4]
+  const int32_t* cu_rows;
+  const int32_t* slots;
+  const int32_t* shift;
+  float* out;               // [M][HV * 128]
+  int C, n_q, n_k, HV, HK, ldba, stash_rows, commit;
+};
+
+}  // namespace saber
+
+extern "C" int saber_gdn_conv_launch(const saber::GdnConvParams* p, int nseq, cudaStream_t stream);
+extern "C" int saber_gdn_recurrent_launch(const saber::GdnRecParams* p, int nseq, int vs,
+                                          cudaStream_t stream);

@@ -1,0 +1,29 @@
+// Launch interface of the integer (W4A8 / W8A8) tcgen05 GEMM. Plain C types only so that both the
+// torch binding and C callers can use it.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace saber {
+
+struct GemmI8Params {
+  const uint8_t* w;        // pre-tiled weights [N_pad/128][K/128][8 KiB (W4) | 16 KiB (W8)]
+  const float* w_scale;    // [N] per output feature; for W4 it already carries the 1/16
+  const int8_t* a;         // pre-tiled activations [K/128][M_pad][128]
+  const float* a_scale;    // [M_pad] per token
+  __nv_bfloat16* out;      // [M][ldo]
+  int32_t* ws;             // split-K scratch [M_pad][N_pad] int32, all zero between launches
+  uint32_t* counters;      // split-K arrival counters, one per (m tile, n tile), zero between launches
+  uint32_t* err;           // status word: 0, or the code of the first bounded wait that ran out
+  int M, M_pad, N, N_pad, K;
+  int nt;                  // tokens per CTA tile: multiple of 16, <= 256, divides M_pad
+  int splits;              // split-K factor (gridDim.z)
+  int w4;                  // 1: packed int4 tiles, 0: int8 tiles
+  int ldo;                 // row stride of out, in elements
+};
+
+}  // namespace saber
+
+extern "C" int saber_gemm_i8_smem_bytes(int nt, int stages);
+extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cudaStream_t stream);

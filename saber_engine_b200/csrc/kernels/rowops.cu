@@ -1,0 +1,258 @@
+// Row producers: every op that feeds a quantised GEMM, one CTA per token row, 16-byte vector
+// traffic, and the per-token int8 quantisation fused in so that the GEMM's activation operand is
+// written ONCE, already in the tiled/swizzled order the tcgen05 GEMM copies with one bulk copy.
+//
+// Modes (parity with the reference's activation producers, crates/saber-kernels/hip/
+// mxfp4_quant.hip:11-25, macaq_i8.h:1-13, attn_glue.hip attn_gate_quant, saber_gdn_norm.hip):
+//   ADD_RMS    s = x + res (fp32); res_out = bf16(s); n = bf16(s * rsqrt(mean s^2 + eps) * (1 + w))
+//   SILU_MUL   h = bf16(silu(gate) * up), gate = in[:, :K], up = in[:, K:2K]
+//   GATE_SIG   h = bf16(a * sigmoid(b))                          (attention output gate)
+//   GDN_NORM   per 128-wide head: h = bf16(rmsnorm(a) * w * silu(b))   (gated RMSNorm, plain w)
+//   PLAIN      h = a
+// Quantisation law (per token row): amax = max |h|; scale = amax / 127; q = clamp(rint(h * (127 /
+// amax)), -127, 127); a zero row stores scale 0.  Rows in [M, M_pad) are written as zeros.
+#include "rowops.h"
+#include "ptx_sm100.cuh"
+#include <cuda_bf16.h>
+
+namespace saber {
+
+constexpr int kRowThreads = 256;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <bool kMax>
+__device__ __forceinline__ float block_reduce(float v, float* red) {
+  v = kMax ? warp_max(v) : warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // protect `red` against the previous use
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int nw = blockDim.x >> 5;
+  float r = (lane < nw) ? red[lane] : (kMax ? 0.f : 0.f);
+  r = kMax ? warp_max(r) : warp_sum(r);
+  return r;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+
+struct alignas(16) Bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const Bf16x8 raw = *reinterpret_cast<const Bf16x8*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(raw.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  Bf16x8 raw;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) raw.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<Bf16x8*>(p) = raw;
+}
+
+// Quantise the row held in shared memory (bf16, K values) and store it tiled. All threads call.
+__device__ __forceinline__ void quant_store_row(const __nv_bfloat16* h, int K, int m, int M_pad,
+                                                float amax, int8_t* q, float* scale) {
+  const float inv = amax > 0.f ? 127.f / amax : 0.f;
+  if (threadIdx.x == 0) scale[m] = amax / 127.f;
+  const int nchunk = K >> 4;
+  for (int ch = threadIdx.x; ch < nchunk; ch += blockDim.x) {
+    const int k0 = ch << 4;
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float x = __bfloat162float(h[k0 + i * 4 + j]) * inv;
+        int qi = __float2int_rn(x);
+        qi = max(-127, min(127, qi));
+        word |= (static_cast<uint32_t>(qi) & 0xFFu) << (8 * j);
+      }
+      w[i] = word;
+    }
+    const int kb = k0 >> 7, c = (k0 & 127) >> 4;
+    int8_t* dst = q + (static_cast<size_t>(kb) * M_pad + m) * 128 + (((c ^ (m & 7)) & 7) << 4);
+    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpParams p) {
+  extern __shared__ __align__(16) uint8_t row_smem[];
+  __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(row_smem);  // K bf16
+  __shared__ float red[32];
+  const int m = blockIdx.x;
+  const int K = p.K;
+  if (m >= p.M) {  // padding row: zeros
+    if (p.q) {
+      const int nchunk = K >> 4;
+      for (int ch = threadIdx.x; ch < nchunk; ch += blockDim.x) {
+        const int k0 = ch << 4;
+        const int kb = k0 >> 7, c = (k0 & 127) >> 4;
+        int8_t* dst = p.q + (static_cast<size_t>(kb) * p.M_pad + m) * 128 + (((c ^ (m & 7)) & 7) << 4);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+      if (threadIdx.x == 0) p.scale[m] = 0.f;
+    }
+    return;
+  }
+  const int nvec = K >> 3;
+  float amax = 0.f;
+
+  if (MODE == kRowAddRms) {
+    float* s = reinterpret_cast<float*>(row_smem + static_cast<size_t>(K) * 2);  // K fp32 after h
+    float ss = 0.f;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float x[8];
+      if (p.a) load8(p.a + static_cast<size_t>(m) * p.lda + v * 8, x);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = 0.f;
+      }
+      if (p.res) {
+        float r[8];
+        load8(p.res + static_cast<size_t>(m) * p.ldres + v * 8, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] += r[i];
+        store8(p.res + static_cast<size_t>(m) * p.ldres + v * 8, x);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        s[v * 8 + i] = x[i];
+        ss += x[i] * x[i];
+      }
+    }
+    ss = block_reduce<false>(ss, red);
+    const float rstd = rsqrtf(ss / static_cast<float>(K) + p.eps);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float x[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float wv = p.w[v * 8 + i] + p.w_offset;
+        x[i] = __bfloat162float(__float2bfloat16(s[v * 8 + i] * rstd * wv));
+        amax = fmaxf(amax, fabsf(x[i]));
+      }
+      store8(h + v * 8, x);
+      if (p.out) store8(p.out + static_cast<size_t>(m) * p.ldout + v * 8, x);
+    }
+  } else if (MODE == kRowGdnNorm) {
+    // one warp per 128-wide head, heads strided over the warps
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int nheads = K >> 7;
+    for (int hd = warp; hd < nheads; hd += nw) {
+      const int k0 = hd * 128 + lane * 4;
+      float a[4], z[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a[i] = p.a_f32 ? p.a_f32[static_cast<size_t>(m) * p.lda + k0 + i]
+                       : __bfloat162float(p.a[static_cast<size_t>(m) * p.lda + k0 + i]);
+        z[i] = __bfloat162float(p.b[static_cast<size_t>(m) * p.ldb + k0 + i]);
+      }
+      float ss = a[0] * a[0] + a[1] * a[1] + a[2] * a[2] + a[3] * a[3];
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss * (1.f / 128.f) + p.eps);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float wv = p.w[lane * 4 + i] + p.w_offset;
+        const float x = __bfloat162float(__float2bfloat16(a[i] * rstd * wv * silu_f(z[i])));
+        amax = fmaxf(amax, fabsf(x));
+        h[k0 + i] = __float2bfloat16(x);
+        if (p.out) p.out[static_cast<size_t>(m) * p.ldout + k0 + i] = __float2bfloat16(x);
+      }
+    }
+  } else {
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float x[8];
+      if (MODE == kRowSiluMul) {
+        float g[8], u[8];
+        load8(p.a + static_cast<size_t>(m) * p.lda + v * 8, g);
+        load8(p.a + static_cast<size_t>(m) * p.lda + K + v * 8, u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = silu_f(g[i]) * u[i];
+      } else if (MODE == kRowGateSig) {
+        float a[8], b[8];
+        load8(p.a + static_cast<size_t>(m) * p.lda + v * 8, a);
+        load8(p.b + static_cast<size_t>(m) * p.ldb + v * 8, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = a[i] * sigmoid_f(b[i]);
+      } else {
+        load8(p.a + static_cast<size_t>(m) * p.lda + v * 8, x);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        x[i] = __bfloat162float(__float2bfloat16(x[i]));
+        amax = fmaxf(amax, fabsf(x[i]));
+      }
+      store8(h + v * 8, x);
+      if (p.out) store8(p.out + static_cast<size_t>(m) * p.ldout + v * 8, x);
+    }
+  }
+  amax = block_reduce<true>(amax, red);  // its barriers also publish h to the whole block
+  if (p.q) quant_store_row(h, K, m, p.M_pad, amax, p.q, p.scale);
+}
+
+// out[m, :] = table[ids[m], :]   (bf16 rows, 16-byte vectors); ids outside [0, vocab) give zeros.
+__global__ void embed_gather_kernel(const __nv_bfloat16* table, const int32_t* ids,
+                                    __nv_bfloat16* out, int M, int H, int vocab_lo, int vocab_n) {
+  const int m = blockIdx.x;
+  if (m >= M) return;
+  const int id = ids[m] - vocab_lo;
+  const bool ok = id >= 0 && id < vocab_n;
+  const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(ok ? id : 0) * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(m) * H);
+  for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x)
+    dst[v] = ok ? src[v] : make_uint4(0, 0, 0, 0);
+}
+
+}  // namespace saber
+
+extern "C" int saber_row_producer_launch(int mode, const saber::RowOpParams* p, cudaStream_t stream) {
+  using namespace saber;
+  if ((p->K & 127) || p->M_pad < p->M) return static_cast<int>(cudaErrorInvalidValue);
+  const int rows = p->q ? p->M_pad : p->M;
+  size_t smem = static_cast<size_t>(p->K) * 2 + (mode == kRowAddRms ? static_cast<size_t>(p->K) * 4 : 0);
+#define SABER_ROW_CASE(MODE)                                                                     \
+  case MODE: {                                                                                   \
+    if (smem > 48 * 1024)                                                                        \
+      cudaFuncSetAttribute(row_producer_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           static_cast<int>(smem));                                              \
+    row_producer_kernel<MODE><<<rows, kRowThreads, smem, stream>>>(*p);                          \
+    break;                                                                                       \
+  }
+  switch (mode) {
+    SABER_ROW_CASE(kRowAddRms)
+    SABER_ROW_CASE(kRowSiluMul)
+    SABER_ROW_CASE(kRowGateSig)
+    SABER_ROW_CASE(kRowGdnNorm)
+    SABER_ROW_CASE(kRowPlain)
+    default:
+      return static_cast<int>(cudaErrorInvalidValue);
+  }
+#undef SABER_ROW_CASE
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int saber_embed_gather_launch(const void* table, const int32_t* ids, void* out, int M,
+                                         int H, int vocab_lo, int vocab_n, cudaStream_t stream) {
+  if (H & 7) return static_cast<int>(cudaErrorInvalidValue);
+  saber::embed_gather_kernel<<<M, 128, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), M, H,
+      vocab_lo, vocab_n);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,36 @@
+// Launch interface of the row producers (norm / activation / gate ops with fused int8 quant).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace saber {
+
+enum RowMode : int {
+  kRowAddRms = 0,
+  kRowSiluMul = 1,
+  kRowGateSig = 2,
+  kRowGdnNorm = 3,
+  kRowPlain = 4,
+};
+
+struct RowOpParams {
+  const __nv_bfloat16* a;   // primary input (x / gate|up / attn out / raw row)
+  const float* a_f32;       // GDN_NORM only: fp32 primary input instead of `a`
+  const __nv_bfloat16* b;   // secondary input (gate for GATE_SIG, z for GDN_NORM)
+  __nv_bfloat16* res;       // ADD_RMS: residual stream, updated in place (may be null)
+  const float* w;           // norm weight (K for ADD_RMS, 128 for GDN_NORM)
+  float w_offset;           // 1 for the (1 + w) form, 0 for plain w
+  float eps;
+  __nv_bfloat16* out;       // optional bf16 copy of the produced row (may be null)
+  int8_t* q;                // optional tiled int8 output [K/128][M_pad][128] (may be null)
+  float* scale;             // [M_pad]
+  int M, M_pad, K;
+  int lda, ldb, ldres, ldout;  // row strides in elements
+};
+
+}  // namespace saber
+
+extern "C" int saber_row_producer_launch(int mode, const saber::RowOpParams* p, cudaStream_t stream);
+extern "C" int saber_embed_gather_launch(const void* table, const int32_t* ids, void* out, int M,
+                                         int H, int vocab_lo, int vocab_n, cudaStream_t stream);

@@ -1,0 +1,30 @@
+// Launch interface of the head-side kernels (argmax, top-k seam, verify/accept).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace saber {
+
+constexpr int kSeamK = 64;
+
+struct VerifyParams {
+  const int32_t* draft;     // [M] token fed at each row (row 0 of a sequence = last committed token)
+  const int32_t* target;    // [M] model pick after each row
+  const int32_t* cu_rows;   // [nseq + 1]
+  const int32_t* seq_uid;   // [nseq] stable id of the sequence (seeds the oracle)
+  const int32_t* step_no;   // [nseq] decode step index of the sequence (seeds the oracle)
+  int32_t* n_commit;        // [nseq] tokens committed this step (accepted drafts + 1 bonus)
+  int32_t* out_tokens;      // [nseq][max_w]
+  int nseq, max_w;
+  float oracle_p;           // 0: greedy prefix match; > 0: seeded geometric(p) acceptance
+  uint64_t seed;
+};
+
+}  // namespace saber
+
+extern "C" int saber_argmax_launch(const void* logits, int rows, int ld, int V, int id_offset,
+                                   int32_t* out_idx, float* out_val, cudaStream_t stream);
+extern "C" int saber_topk_seam_launch(const void* logits, int rows, int ld, int V, int id_offset,
+                                      const float* temps, int32_t* ids, float* vals, float* lse,
+                                      cudaStream_t stream);
+extern "C" int saber_verify_launch(const saber::VerifyParams* p, cudaStream_t stream);

@@ -1,0 +1,343 @@
+"""Eager wrappers over the native kernels (one launch each, on the current CUDA stream).
+
+These are what tests and the prefill path call; captured decode buckets use `native.Program` with
+the same parameter blocks.  Every wrapper requires a CUDA tensor and the native library: there is
+no PyTorch fallback here (references live in `ops.reference`).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import layouts as L
+from . import native as N
+
+
+@dataclass
+class QuantWeight:
+    """A linear layer's weight in GEMM-ready form."""
+    tiles: torch.Tensor      # uint8 [N_pad/128, K/128, 8192 | 16384]
+    scale: torch.Tensor      # fp32 [N_pad] (W4: already divided by 16)
+    N: int
+    K: int
+    w4: bool
+
+    @property
+    def N_pad(self) -> int:
+        return self.tiles.shape[0] * 128
+
+    @staticmethod
+    def from_float(w: torch.Tensor, bits: int = 4, device=None) -> "QuantWeight":
+        q, s = L.quantize_weight_rows(w, bits)
+        return QuantWeight.from_int(q, s, bits, device)
+
+    @staticmethod
+    def from_int(q: torch.Tensor, s: torch.Tensor, bits: int, device=None) -> "QuantWeight":
+        Nn, K = q.shape
+        tiles = L.tile_weight_int4(q) if bits == 4 else L.tile_weight_int8(q)
+        n_pad = tiles.shape[0] * 128
+        sc = torch.zeros(n_pad, dtype=torch.float32)
+        sc[:Nn] = s.float() / (16.0 if bits == 4 else 1.0)
+        dev = device if device is not None else q.device
+        return QuantWeight(tiles.to(dev).contiguous(), sc.to(dev), Nn, K, bits == 4)
+
+
+@dataclass
+class QuantAct:
+    """Quantised activations in the tiled layout."""
+    q: torch.Tensor          # int8 [K/128, M_pad, 128]
+    scale: torch.Tensor      # fp32 [M_pad]
+    M: int
+    K: int
+
+    @property
+    def M_pad(self) -> int:
+        return self.q.shape[1]
+
+    @staticmethod
+    def alloc(M: int, K: int, device) -> "QuantAct":
+        m_pad = L.padded_rows(M)
+        return QuantAct(torch.empty(K // 128, m_pad, 128, dtype=torch.int8, device=device),
+                        torch.empty(m_pad, dtype=torch.float32, device=device), M, K)
+
+
+class GemmScratch:
+    """Split-K scratch of one device: int32 partial sums, arrival counters and the status word.
+
+    The kernels leave the scratch zeroed, so one instance serves every GEMM launched in stream
+    order on the device.
+    """
+
+    def __init__(self, device, max_rows: int = 256, max_cols: int = 262144):
+        self.ws = torch.zeros(max_rows * max_cols, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(8192, dtype=torch.int32, device=device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=device)
+        self.capacity = max_rows * max_cols
+
+    def check(self) -> None:
+        code = int(self.err.item())
+        if code != 0:
+            self.err.zero_()
+            raise N.NativeError(f"kernel wait timed out: {N.ERR_NAMES.get(code, code)}")
+
+
+_SCRATCH: dict = {}
+
+
+def scratch(device) -> GemmScratch:
+    key = torch.device(device).index or 0
+    if key not in _SCRATCH:
+        _SCRATCH[key] = GemmScratch(device)
+    return _SCRATCH[key]
+
+
+def pick_splits(n_tiles: int, m_tiles: int, kb: int, sms: int = 148) -> int:
+    """Split-K factor that fills the SMs when the tile grid alone does not."""
+    ctas = n_tiles * m_tiles
+    if ctas >= sms or kb < 8:
+        return 1
+    s = min(max(1, (2 * sms) // ctas), max(1, kb // 4), 16)
+    while s > 1 and (s - 1) * math.ceil(kb / s) >= kb:
+        s -= 1
+    return s
+
+
+def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,
+                splits: Optional[int] = None, nt: Optional[int] = None) -> N.GemmI8Params:
+    assert a.K == w.K, (a.K, w.K)
+    nt = nt or L.token_tile(a.M)
+    assert a.M_pad % nt == 0
+    m_tiles = (a.M + nt - 1) // nt
+    if splits is None:
+        splits = pick_splits(w.N_pad // 128, m_tiles, w.K // 128)
+    if splits > 1:
+        assert a.M_pad * w.N_pad <= sc.capacity
+    p = N.GemmI8Params()
+    p.w, p.w_scale, p.a, p.a_scale = w.tiles.data_ptr(), w.scale.data_ptr(), a.q.data_ptr(), a.scale.data_ptr()
+    p.out, p.ws, p.counters, p.err = out.data_ptr(), sc.ws.data_ptr(), sc.counters.data_ptr(), sc.err.data_ptr()
+    p.M, p.M_pad, p.N, p.N_pad, p.K = a.M, a.M_pad, w.N, w.N_pad, w.K
+    p.nt, p.splits, p.w4, p.ldo = nt, splits, int(w.w4), out.stride(0)
+    return p
+
+
+def gemm_i8(w: QuantWeight, a: QuantAct, out: Optional[torch.Tensor] = None,
+            splits: Optional[int] = None, stages: int = 0, nt: Optional[int] = None) -> torch.Tensor:
+    """out[M, N] = bf16(int32 accumulate * a_scale[m] * w_scale[n])."""
+    dev = a.q.device
+    if out is None:
+        out = torch.empty(a.M, w.N, dtype=torch.bfloat16, device=dev)
+    p = gemm_params(w, a, out, scratch(dev), splits, nt)
+    N.check(N.lib().saber_gemm_i8_launch(C.byref(p), stages, N.stream_handle()), "gemm_i8")
+    return out
+
+
+def row_params(M: int, K: int, *, a=None, a_f32=None, b=None, res=None, w=None, w_offset=0.0,
+               eps=1e-6, out=None, qa: Optional[QuantAct] = None, lda=None, ldb=None) -> N.RowOpParams:
+    p = N.RowOpParams()
+    p.a, p.a_f32, p.b, p.res, p.w = N.ptr(a), N.ptr(a_f32), N.ptr(b), N.ptr(res), N.ptr(w)
+    p.w_offset, p.eps = w_offset, eps
+    p.out = N.ptr(out)
+    p.q = qa.q.data_ptr() if qa is not None else None
+    p.scale = qa.scale.data_ptr() if qa is not None else None
+    p.M, p.M_pad, p.K = M, (qa.M_pad if qa is not None else M), K
+    src = a if a is not None else a_f32
+    p.lda = lda if lda is not None else (src.stride(0) if src is not None else 0)
+    p.ldb = ldb if ldb is not None else (b.stride(0) if b is not None else 0)
+    p.ldres = res.stride(0) if res is not None else 0
+    p.ldout = out.stride(0) if out is not None else 0
+    return p
+
+
+def _row(mode: int, p: N.RowOpParams) -> None:
+    N.check(N.lib().saber_row_producer_launch(mode, C.byref(p), N.stream_handle()), "row_producer")
+
+
+def add_rms_quant(x: Optional[torch.Tensor], res: Optional[torch.Tensor], w: torch.Tensor,
+                  eps: float = 1e-6, w_offset: float = 1.0, want_out: bool = False,
+                  quant: bool = True):
+    """res += x (in place); n = rmsnorm(res) * (w_offset + w); returns (QuantAct | None, bf16 n | None)."""
+    src = x if x is not None else res
+    M, K = src.shape
+    qa = QuantAct.alloc(M, K, src.device) if quant else None
+    out = torch.empty(M, K, dtype=torch.bfloat16, device=src.device) if want_out else None
+    _row(N.ROW_ADD_RMS, row_params(M, K, a=x, res=res, w=w, w_offset=w_offset, eps=eps, out=out, qa=qa))
+    return qa, out
+
+
+def silu_mul_quant(gu: torch.Tensor, want_out: bool = False):
+    M, K2 = gu.shape
+    K = K2 // 2
+    qa = QuantAct.alloc(M, K, gu.device)
+    out = torch.empty(M, K, dtype=torch.bfloat16, device=gu.device) if want_out else None
+    _row(N.ROW_SILU_MUL, row_params(M, K, a=gu, out=out, qa=qa))
+    return qa, out
+
+
+def gate_sigmoid_quant(a: torch.Tensor, gate: torch.Tensor, want_out: bool = False):
+    M, K = a.shape
+    qa = QuantAct.alloc(M, K, a.device)
+    out = torch.empty(M, K, dtype=torch.bfloat16, device=a.device) if want_out else None
+    _row(N.ROW_GATE_SIG, row_params(M, K, a=a, b=gate, out=out, qa=qa))
+    return qa, out
+
+
+def gdn_norm_quant(o: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float = 1e-6,
+                   want_out: bool = False):
+    """o fp32 [M, H*128], z bf16 [M, H*128] (may be a strided view), w fp32 [128]."""
+    M, K = o.shape
+    qa = QuantAct.alloc(M, K, o.device)
+    out = torch.empty(M, K, dtype=torch.bfloat16, device=o.device) if want_out else None
+    _row(N.ROW_GDN_NORM, row_params(M, K, a_f32=o, b=z, w=w, eps=eps, out=out, qa=qa))
+    return qa, out
+
+
+def plain_quant(x: torch.Tensor) -> QuantAct:
+    M, K = x.shape
+    qa = QuantAct.alloc(M, K, x.device)
+    _row(N.ROW_PLAIN, row_params(M, K, a=x, qa=qa))
+    return qa
+
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, vocab_lo: int = 0) -> torch.Tensor:
+    M, H = ids.numel(), table.shape[1]
+    out = torch.empty(M, H, dtype=torch.bfloat16, device=table.device)
+    N.check(N.lib().saber_embed_gather_launch(table.data_ptr(), ids.data_ptr(), out.data_ptr(), M, H,
+                                              vocab_lo, table.shape[0], N.stream_handle()), "embed")
+    return out
+
+
+def argmax(logits: torch.Tensor, id_offset: int = 0):
+    R, V = logits.shape
+    idx = torch.empty(R, dtype=torch.int32, device=logits.device)
+    val = torch.empty(R, dtype=torch.float32, device=logits.device)
+    N.check(N.lib().saber_argmax_launch(logits.data_ptr(), R, logits.stride(0), V, id_offset,
+                                        idx.data_ptr(), val.data_ptr(), N.stream_handle()), "argmax")
+    return idx, val
+
+
+def topk_seam(logits: torch.Tensor, temps: Optional[torch.Tensor] = None, id_offset: int = 0):
+    R, V = logits.shape
+    ids = torch.empty(R, N.SEAM_K, dtype=torch.int32, device=logits.device)
+    vals = torch.empty(R, N.SEAM_K, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(R, 2, dtype=torch.float32, device=logits.device)
+    N.check(N.lib().saber_topk_seam_launch(logits.data_ptr(), R, logits.stride(0), V, id_offset,
+                                           N.ptr(temps), ids.data_ptr(), vals.data_ptr(),
+                                           lse.data_ptr(), N.stream_handle()), "topk_seam")
+    return ids, vals, lse
+
+
+def verify_accept(draft, target, cu_rows, seq_uid, step_no, max_w: int, oracle_p: float = 0.0,
+                  seed: int = 0):
+    nseq = cu_rows.numel() - 1
+    n_commit = torch.empty(nseq, dtype=torch.int32, device=draft.device)
+    out_tokens = torch.zeros(nseq, max_w, dtype=torch.int32, device=draft.device)
+    p = N.VerifyParams()
+    p.draft, p.target, p.cu_rows = draft.data_ptr(), target.data_ptr(), cu_rows.data_ptr()
+    p.seq_uid, p.step_no = seq_uid.data_ptr(), step_no.data_ptr()
+    p.n_commit, p.out_tokens = n_commit.data_ptr(), out_tokens.data_ptr()
+    p.nseq, p.max_w, p.oracle_p, p.seed = nseq, max_w, oracle_p, seed
+    N.check(N.lib().saber_verify_launch(C.byref(p), N.stream_handle()), "verify")
+    return n_commit, out_tokens
+
+
+# ----------------------------------------------------------------------------------- GDN
+def gdn_stash_stride(vs: int) -> int:
+    return 128 + 128 // vs + 4
+
+
+def gdn_conv_params(x, conv_w, hist, cu_rows, slots, shift, out, n_q, n_k, commit, ldx=None):
+    p = N.GdnConvParams()
+    p.x, p.conv_w, p.hist = x.data_ptr(), conv_w.data_ptr(), hist.data_ptr()
+    p.cu_rows, p.slots, p.shift, p.out = cu_rows.data_ptr(), slots.data_ptr(), shift.data_ptr(), out.data_ptr()
+    p.C, p.n_q, p.n_k = conv_w.shape[0], n_q, n_k
+    p.ldx = ldx if ldx is not None else x.stride(0)
+    p.hist_rows, p.commit, p.q_scale = hist.shape[1], int(commit), 1.0 / math.sqrt(128.0)
+    return p
+
+
+def gdn_conv(x, conv_w, hist, cu_rows, slots, shift, n_q, n_k, commit=False):
+    """x bf16 [M, >=C] (first C columns are q|k|v); returns fp32 [M, C]."""
+    M = x.shape[0]
+    out = torch.empty(M, conv_w.shape[0], dtype=torch.float32, device=x.device)
+    p = gdn_conv_params(x, conv_w, hist, cu_rows, slots, shift, out, n_q, n_k, commit)
+    N.check(N.lib().saber_gdn_conv_launch(C.byref(p), slots.numel(), N.stream_handle()), "gdn_conv")
+    return out
+
+
+def gdn_rec_params(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, out, n_q, n_k,
+                   HV, HK, commit, ldba=None):
+    p = N.GdnRecParams()
+    p.qkv, p.ba, p.A_log, p.dt_bias = qkv.data_ptr(), ba.data_ptr(), A_log.data_ptr(), dt_bias.data_ptr()
+    p.state, p.stash = state.data_ptr(), stash.data_ptr()
+    p.cu_rows, p.slots, p.shift, p.out = cu_rows.data_ptr(), slots.data_ptr(), shift.data_ptr(), out.data_ptr()
+    p.C, p.n_q, p.n_k, p.HV, p.HK = qkv.shape[1], n_q, n_k, HV, HK
+    p.ldba = ldba if ldba is not None else ba.stride(0)
+    p.stash_rows, p.commit = stash.shape[1], int(commit)
+    return p
+
+
+def gdn_recurrent(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, n_q, n_k, HV, HK,
+                  commit=False, vs=2):
+    M = qkv.shape[0]
+    out = torch.empty(M, HV * 128, dtype=torch.float32, device=qkv.device)
+    p = gdn_rec_params(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, out, n_q, n_k,
+                       HV, HK, commit)
+    N.check(N.lib().saber_gdn_recurrent_launch(C.byref(p), slots.numel(), vs, N.stream_handle()), "gdn_rec")
+    return out
+
+
+# ----------------------------------------------------------------------------------- attention
+def rope_kv_params(qkv, q_out, q_norm_w, k_norm_w, pos, slot_map, kv_cache, nq, nkv, q_off, k_off,
+                   v_off, rot_dim=64, sections=(11, 11, 10), theta=1e7, eps=1e-6, w_offset=1.0,
+                   k_scale=1.0, v_scale=1.0):
+    p = N.RopeKvParams()
+    p.qkv, p.q_out = qkv.data_ptr(), q_out.data_ptr()
+    p.q_norm_w, p.k_norm_w = q_norm_w.data_ptr(), k_norm_w.data_ptr()
+    p.pos, p.slot_map, p.kv_cache = pos.data_ptr(), slot_map.data_ptr(), kv_cache.data_ptr()
+    p.M, p.ld, p.nq, p.nkv = qkv.shape[0], qkv.stride(0), nq, nkv
+    p.q_off, p.k_off, p.v_off = q_off, k_off, v_off
+    p.rot_dim, p.sec_h, p.sec_w = rot_dim, sections[1], sections[2]
+    p.theta, p.eps, p.w_offset = theta, eps, w_offset
+    p.k_inv_scale, p.v_inv_scale = 1.0 / k_scale, 1.0 / v_scale
+    return p
+
+
+def rope_kv(qkv, q_norm_w, k_norm_w, pos, slot_map, kv_cache, nq, nkv, q_off, k_off, v_off, **kw):
+    q_out = torch.empty(qkv.shape[0], nq, 256, dtype=torch.bfloat16, device=qkv.device)
+    p = rope_kv_params(qkv, q_out, q_norm_w, k_norm_w, pos, slot_map, kv_cache, nq, nkv, q_off,
+                       k_off, v_off, **kw)
+    N.check(N.lib().saber_rope_kv_launch(C.byref(p), N.stream_handle()), "rope_kv")
+    return q_out
+
+
+def attn_params(q, kv_cache, block_table, cu_q, kv_len, out, part_o, part_ml, nkv, splits, q_tiles,
+                k_scale=1.0, v_scale=1.0, sm_scale=None):
+    p = N.AttnParams()
+    p.q, p.kv_cache, p.block_table = q.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr()
+    p.cu_q, p.kv_len, p.out = cu_q.data_ptr(), kv_len.data_ptr(), out.data_ptr()
+    p.part_o, p.part_ml = N.ptr(part_o), N.ptr(part_ml)
+    p.nseq, p.nq, p.nkv = kv_len.numel(), q.shape[1], nkv
+    p.max_blocks, p.splits, p.q_tiles = block_table.shape[1], splits, q_tiles
+    p.sm_scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(256.0)
+    p.k_scale, p.v_scale = k_scale, v_scale
+    return p
+
+
+def attention(q, kv_cache, block_table, cu_q, kv_len, nkv, max_rows_per_seq: int, splits: int = 1,
+              k_scale=1.0, v_scale=1.0):
+    """q bf16 [M, nq, 256]; returns bf16 [M, nq, 256]."""
+    out = torch.empty_like(q)
+    nseq, nq = kv_len.numel(), q.shape[1]
+    q_tiles = (max_rows_per_seq + 15) // 16
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty(nseq, nq, splits, 16, 256, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(nseq, nq, splits, 16, 2, dtype=torch.float32, device=q.device)
+    p = attn_params(q, kv_cache, block_table, cu_q, kv_len, out, part_o, part_ml, nkv, splits,
+                    q_tiles, k_scale, v_scale)
+    N.check(N.lib().saber_attn_launch(C.byref(p), N.stream_handle()), "attn")
+    return out

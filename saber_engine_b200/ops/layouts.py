@@ -1,0 +1,125 @@
+"""Operand layouts of the tcgen05 integer GEMM and the quantisation laws, in plain torch (CPU or GPU).
+
+Weights
+    int8 image of one tile = 128 output rows x 128 bytes of K under the 128-byte swizzle
+    (16-byte chunk index XOR (row & 7)); tiles are stored `[n_tile][k_block]`.  A W4 tile is 8 KiB:
+    byte j = (image[j] >> 4) | (image[j + 8192] & 0xF0) where the image holds 16*w.
+Activations
+    `[k_block][M_pad][128]` int8 with the same swizzle keyed on (m & 7), plus one fp32 scale per row.
+
+Quantisation laws (parity: `tools/pack/build_pack.py:22-40` for weights, `macaq_i8.h:1-13` for
+activations, adapted): weights are symmetric per output row, int4 in [-8, 7] or int8 in [-127, 127];
+activations are per-token dynamic int8, scale = amax / 127, q = clamp(rint(x * (127 / amax))).
+"""
+from __future__ import annotations
+
+import torch
+
+TILE_N = 128
+TILE_K = 128
+
+
+def round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+def token_tile(M: int) -> int:
+    """Token-tile width nt the GEMM uses for M rows: a multiple of 16, at most 256."""
+    if M <= 256:
+        return max(16, round_up(M, 16))
+    return 256
+
+
+def padded_rows(M: int) -> int:
+    return round_up(M, token_tile(M))
+
+
+# ------------------------------------------------------------------------------- weights
+def quantize_weight_rows(w: torch.Tensor, bits: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Symmetric per-output-row quantisation. Returns (int8 values, fp32 row scale)."""
+    w = w.float()
+    qmax = 7.0 if bits == 4 else 127.0
+    amax = w.abs().amax(dim=1).clamp_min(1e-12)
+    scale = amax / qmax
+    q = torch.round(w / scale[:, None]).clamp_(-qmax - (1 if bits == 4 else 0), qmax)
+    return q.to(torch.int8), scale
+
+
+def _swizzle_tiles(img: torch.Tensor) -> torch.Tensor:
+    """img [..., 128 rows, 128 bytes] -> same shape with 16-byte chunks XOR-swizzled by row & 7."""
+    lead = img.shape[:-2]
+    x = img.reshape(*lead, 128, 8, 16)
+    rows = torch.arange(128, device=img.device) & 7
+    chunks = torch.arange(8, device=img.device)
+    src = (chunks[None, :] ^ rows[:, None])  # physical chunk c' holds logical chunk c' ^ r
+    idx = src[..., None].expand(128, 8, 16)
+    idx = idx.reshape((1,) * len(lead) + (128, 8, 16)).expand(*lead, 128, 8, 16)
+    return torch.gather(x, -2, idx).reshape(*lead, 128, 128)
+
+
+def tile_weight_int8(q: torch.Tensor) -> torch.Tensor:
+    """int8 [N, K] -> uint8 tiles [N_pad/128, K/128, 16384] (the swizzled image of each tile)."""
+    N, K = q.shape
+    assert K % TILE_K == 0
+    n_pad = round_up(N, TILE_N)
+    if n_pad != N:
+        q = torch.cat([q, torch.zeros(n_pad - N, K, dtype=q.dtype, device=q.device)], 0)
+    t = q.view(torch.uint8).reshape(n_pad // 128, 128, K // 128, 128).permute(0, 2, 1, 3).contiguous()
+    return _swizzle_tiles(t).reshape(n_pad // 128, K // 128, 16384)
+
+
+def tile_weight_int4(q: torch.Tensor) -> torch.Tensor:
+    """int8 values in [-8, 7], [N, K] -> packed W4 tiles [N_pad/128, K/128, 8192]."""
+    img = tile_weight_int8((q.to(torch.int16) * 16).to(torch.int8))  # image holds 16*w
+    lo, hi = img[..., :8192], img[..., 8192:]
+    return ((lo >> 4) & 0x0F) | (hi & 0xF0)
+
+
+def untile_weight_int8(tiles: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """Inverse of tile_weight_int8 (for tests): tiles -> int8 [N, K]."""
+    nt, kb, _ = tiles.shape
+    t = _swizzle_tiles(tiles.reshape(nt, kb, 128, 128))  # the XOR swizzle is an involution
+    return t.permute(0, 2, 1, 3).reshape(nt * 128, kb * 128)[:N, :K].contiguous().view(torch.int8)
+
+
+def unpack_weight_int4(tiles: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """Packed W4 tiles -> int8 values in [-8, 7], [N, K] (for tests)."""
+    lo = (tiles << 4) & 0xF0
+    hi = tiles & 0xF0
+    img = torch.cat([lo, hi], dim=-1)
+    w16 = untile_weight_int8(img, N, K)
+    return (w16.to(torch.int16) // 16).to(torch.int8)
+
+
+# ------------------------------------------------------------------------------- activations
+def quantize_act_rows(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Per-token int8: (q int8 [M, K], scale fp32 [M]). Input is taken at bf16 precision."""
+    x = x.to(torch.bfloat16).float()
+    amax = x.abs().amax(dim=1)
+    inv = torch.where(amax > 0, 127.0 / amax, torch.zeros_like(amax))
+    q = torch.round(x * inv[:, None]).clamp_(-127, 127).to(torch.int8)
+    return q, amax / 127.0
+
+
+def tile_act_int8(q: torch.Tensor, m_pad: int) -> torch.Tensor:
+    """int8 [M, K] -> tiled [K/128, M_pad, 128] with the (m & 7) chunk swizzle."""
+    M, K = q.shape
+    assert K % TILE_K == 0 and m_pad >= M
+    if m_pad != M:
+        q = torch.cat([q, torch.zeros(m_pad - M, K, dtype=q.dtype, device=q.device)], 0)
+    x = q.reshape(m_pad, K // 128, 8, 16).permute(1, 0, 2, 3)  # [kb, m, chunk, 16]
+    rows = torch.arange(m_pad, device=q.device) & 7
+    chunks = torch.arange(8, device=q.device)
+    src = chunks[None, :] ^ rows[:, None]
+    idx = src[None, :, :, None].expand(K // 128, m_pad, 8, 16)
+    return torch.gather(x, 2, idx).reshape(K // 128, m_pad, 128).contiguous()
+
+
+def untile_act_int8(t: torch.Tensor, M: int) -> torch.Tensor:
+    kb, m_pad, _ = t.shape
+    x = t.reshape(kb, m_pad, 8, 16)
+    rows = torch.arange(m_pad, device=t.device) & 7
+    chunks = torch.arange(8, device=t.device)
+    src = chunks[None, :] ^ rows[:, None]
+    idx = src[None, :, :, None].expand(kb, m_pad, 8, 16)
+    return torch.gather(x, 2, idx).permute(1, 0, 2, 3).reshape(m_pad, kb * 128)[:M].contiguous()

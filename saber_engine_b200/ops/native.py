@@ -1,0 +1,292 @@
+"""ctypes binding of the native library (`_lib/libsaber_b200.so`).
+
+The library exposes plain-C launchers that take a parameter block and a CUDA stream.  This module
+mirrors the parameter blocks as `ctypes.Structure`s, loads the library once, and offers:
+
+* `lib()`         the loaded CDLL (raises loudly when the library is missing on a GPU box: a silent
+                  PyTorch fallback would hide that no native code ran),
+* small helpers to turn torch tensors into device pointers,
+* `Program`       the native step program (eager walk or CUDA-graph capture/replay).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+from .. import build as _build
+
+_LIB: Optional[C.CDLL] = None
+
+P = C.c_void_p
+I = C.c_int
+F = C.c_float
+U32 = C.c_uint32
+U64 = C.c_uint64
+MAX_RANKS = 8
+AR_BLOCKS = 32
+SEAM_K = 64
+
+ROW_ADD_RMS, ROW_SILU_MUL, ROW_GATE_SIG, ROW_GDN_NORM, ROW_PLAIN = range(5)
+
+ERR_NAMES = {
+    0: "ok", 1: "wait_full", 2: "wait_empty", 3: "wait_ready", 4: "wait_acc", 5: "wait_peer",
+    6: "wait_drain", 7: "bad_args",
+}
+
+
+class GemmI8Params(C.Structure):
+    _fields_ = [("w", P), ("w_scale", P), ("a", P), ("a_scale", P), ("out", P), ("ws", P),
+                ("counters", P), ("err", P), ("M", I), ("M_pad", I), ("N", I), ("N_pad", I),
+                ("K", I), ("nt", I), ("splits", I), ("w4", I), ("ldo", I)]
+
+
+class RowOpParams(C.Structure):
+    _fields_ = [("a", P), ("a_f32", P), ("b", P), ("res", P), ("w", P), ("w_offset", F),
+                ("eps", F), ("out", P), ("q", P), ("scale", P), ("M", I), ("M_pad", I), ("K", I),
+                ("lda", I), ("ldb", I), ("ldres", I), ("ldout", I)]
+
+
+class GdnConvParams(C.Structure):
+    _fields_ = [("x", P), ("conv_w", P), ("hist", P), ("cu_rows", P), ("slots", P), ("shift", P),
+                ("out", P), ("C", I), ("n_q", I), ("n_k", I), ("ldx", I), ("hist_rows", I),
+                ("commit", I), ("q_scale", F)]
+
+
+class GdnRecParams(C.Structure):
+    _fields_ = [("qkv", P), ("ba", P), ("A_log", P), ("dt_bias", P), ("state", P), ("stash", P),
+                ("cu_rows", P), ("slots", P), ("shift", P), ("out", P), ("C", I), ("n_q", I),
+                ("n_k", I), ("HV", I), ("HK", I), ("ldba", I), ("stash_rows", I), ("commit", I)]
+
+
+class RopeKvParams(C.Structure):
+    _fields_ = [("qkv", P), ("q_out", P), ("q_norm_w", P), ("k_norm_w", P), ("pos", P),
+                ("slot_map", P), ("kv_cache", P), ("M", I), ("ld", I), ("nq", I), ("nkv", I),
+                ("q_off", I), ("k_off", I), ("v_off", I), ("rot_dim", I), ("sec_h", I),
+                ("sec_w", I), ("theta", F), ("eps", F), ("w_offset", F), ("k_inv_scale", F),
+                ("v_inv_scale", F)]
+
+
+class AttnParams(C.Structure):
+    _fields_ = [("q", P), ("kv_cache", P), ("block_table", P), ("cu_q", P), ("kv_len", P),
+                ("out", P), ("part_o", P), ("part_ml", P), ("nseq", I), ("nq", I), ("nkv", I),
+                ("max_blocks", I), ("splits", I), ("q_tiles", I), ("sm_scale", F), ("k_scale", F),
+                ("v_scale", F)]
+
+
+class VerifyParams(C.Structure):
+    _fields_ = [("draft", P), ("target", P), ("cu_rows", P), ("seq_uid", P), ("step_no", P),
+                ("n_commit", P), ("out_tokens", P), ("nseq", I), ("max_w", I), ("oracle_p", F),
+                ("seed", U64)]
+
+
+class AllReduceParams(C.Structure):
+    _fields_ = [("inp", P), ("out", P), ("peer_recv", P * MAX_RANKS), ("peer_flags", P * MAX_RANKS),
+                ("seq_base", P), ("err", P), ("n_elems", I), ("max_elems", I), ("site", I),
+                ("nranks", I), ("rank", I), ("spin_limit_us", U32)]
+
+
+def lib() -> C.CDLL:
+    """Load the native library (building it first when absent and a compiler is present)."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = _build.lib_path()
+    if not path.exists():
+        try:
+            _build.build()
+        except Exception as exc:  # pragma: no cover - depends on the box
+            raise RuntimeError(
+                f"native library {path} is missing and could not be built: {exc}. "
+                "Run `python -m saber_engine_b200.build`.") from exc
+    _LIB = C.CDLL(str(path))
+    _declare(_LIB)
+    return _LIB
+
+
+def available() -> bool:
+    try:
+        lib()
+        return True
+    except Exception:
+        return False
+
+
+def _declare(L: C.CDLL) -> None:
+    S = C.c_void_p  # cudaStream_t
+    sig = {
+        "saber_gemm_i8_launch": (I, [C.POINTER(GemmI8Params), I, S]),
+        "saber_gemm_i8_smem_bytes": (I, [I, I]),
+        "saber_row_producer_launch": (I, [I, C.POINTER(RowOpParams), S]),
+        "saber_embed_gather_launch": (I, [P, P, P, I, I, I, I, S]),
+        "saber_gdn_conv_launch": (I, [C.POINTER(GdnConvParams), I, S]),
+        "saber_gdn_recurrent_launch": (I, [C.POINTER(GdnRecParams), I, I, S]),
+        "saber_rope_kv_launch": (I, [C.POINTER(RopeKvParams), S]),
+        "saber_attn_launch": (I, [C.POINTER(AttnParams), S]),
+        "saber_argmax_launch": (I, [P, I, I, I, I, P, P, S]),
+        "saber_topk_seam_launch": (I, [P, I, I, I, I, P, P, P, P, S]),
+        "saber_verify_launch": (I, [C.POINTER(VerifyParams), S]),
+        "saber_allreduce_launch": (I, [C.POINTER(AllReduceParams), S]),
+        "saber_comm_advance_launch": (I, [P, U32, S]),
+        "saber_ipc_get_handle": (I, [P, P]),
+        "saber_ipc_open_handle": (I, [P, C.POINTER(P)]),
+        "saber_ipc_close": (I, [P]),
+        "saber_dev_malloc": (I, [C.POINTER(P), C.c_size_t]),
+        "saber_dev_free": (I, [P]),
+        "saber_program_create": (P, []),
+        "saber_program_destroy": (None, [P]),
+        "saber_program_add_gemm": (I, [P, C.POINTER(GemmI8Params), I, C.c_char_p]),
+        "saber_program_add_row": (I, [P, I, C.POINTER(RowOpParams), C.c_char_p]),
+        "saber_program_add_embed": (I, [P, P, P, P, I, I, I, I, C.c_char_p]),
+        "saber_program_add_gdn_conv": (I, [P, C.POINTER(GdnConvParams), I, C.c_char_p]),
+        "saber_program_add_gdn_rec": (I, [P, C.POINTER(GdnRecParams), I, I, C.c_char_p]),
+        "saber_program_add_rope": (I, [P, C.POINTER(RopeKvParams), C.c_char_p]),
+        "saber_program_add_attn": (I, [P, C.POINTER(AttnParams), C.c_char_p]),
+        "saber_program_add_argmax": (I, [P, P, I, I, I, I, P, P, C.c_char_p]),
+        "saber_program_add_seam": (I, [P, P, I, I, I, I, P, P, P, P, C.c_char_p]),
+        "saber_program_add_verify": (I, [P, C.POINTER(VerifyParams), C.c_char_p]),
+        "saber_program_add_memset": (I, [P, P, I, C.c_size_t, C.c_char_p]),
+        "saber_program_add_copy": (I, [P, P, P, C.c_size_t, C.c_char_p]),
+        "saber_program_add_allreduce": (I, [P, C.POINTER(AllReduceParams), C.c_char_p]),
+        "saber_program_num_ops": (I, [P]),
+        "saber_program_declared_launches": (I, [P]),
+        "saber_program_op_tag": (C.c_char_p, [P, I]),
+        "saber_program_last_failed_op": (I, [P]),
+        "saber_program_run": (I, [P, S]),
+        "saber_program_run_range": (I, [P, I, I, S]),
+        "saber_program_capture": (I, [P, S]),
+        "saber_program_replay": (I, [P, S]),
+        "saber_program_captured_nodes": (I, [P]),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(L, name, None)
+        if fn is None:
+            continue
+        fn.restype = res
+        fn.argtypes = args
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    """Device pointer of a tensor (None stays a null pointer)."""
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def stream_handle(stream: Optional[torch.cuda.Stream] = None) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise NativeError(f"{what}: CUDA error {code}")
+
+
+class Program:
+    """Native step program: fixed launch list, eager walk or graph capture + replay.
+
+    Tensors named in parameter blocks must outlive the program; `keep()` pins references.
+    """
+
+    def __init__(self, name: str = ""):
+        self.name = name
+        self._L = lib()
+        self._h = self._L.saber_program_create()
+        self._keep: list = []
+        self.captured = False
+
+    def keep(self, *objs) -> None:
+        self._keep.extend(objs)
+
+    # ---- op builders -------------------------------------------------------------------------
+    def gemm(self, p: GemmI8Params, stages: int = 0, tag: str = "gemm") -> int:
+        return self._L.saber_program_add_gemm(self._h, C.byref(p), stages, tag.encode())
+
+    def row(self, mode: int, p: RowOpParams, tag: str = "row") -> int:
+        return self._L.saber_program_add_row(self._h, mode, C.byref(p), tag.encode())
+
+    def embed(self, table, ids, out, M, H, vocab_lo, vocab_n, tag="embed") -> int:
+        return self._L.saber_program_add_embed(self._h, ptr(table), ptr(ids), ptr(out), M, H,
+                                               vocab_lo, vocab_n, tag.encode())
+
+    def gdn_conv(self, p: GdnConvParams, nseq: int, tag="gdn_conv") -> int:
+        return self._L.saber_program_add_gdn_conv(self._h, C.byref(p), nseq, tag.encode())
+
+    def gdn_rec(self, p: GdnRecParams, nseq: int, vs: int, tag="gdn_rec") -> int:
+        return self._L.saber_program_add_gdn_rec(self._h, C.byref(p), nseq, vs, tag.encode())
+
+    def rope(self, p: RopeKvParams, tag="rope_kv") -> int:
+        return self._L.saber_program_add_rope(self._h, C.byref(p), tag.encode())
+
+    def attn(self, p: AttnParams, tag="attn") -> int:
+        return self._L.saber_program_add_attn(self._h, C.byref(p), tag.encode())
+
+    def argmax(self, logits, rows, ld, V, id_offset, idx, val, tag="argmax") -> int:
+        return self._L.saber_program_add_argmax(self._h, ptr(logits), rows, ld, V, id_offset,
+                                                ptr(idx), ptr(val), tag.encode())
+
+    def seam(self, logits, rows, ld, V, id_offset, temps, ids, vals, lse, tag="seam") -> int:
+        return self._L.saber_program_add_seam(self._h, ptr(logits), rows, ld, V, id_offset,
+                                              ptr(temps), ptr(ids), ptr(vals), ptr(lse), tag.encode())
+
+    def verify(self, p: VerifyParams, tag="verify") -> int:
+        return self._L.saber_program_add_verify(self._h, C.byref(p), tag.encode())
+
+    def memset(self, t: torch.Tensor, value: int = 0, tag="memset") -> int:
+        return self._L.saber_program_add_memset(self._h, ptr(t), value, t.numel() * t.element_size(),
+                                                tag.encode())
+
+    def copy(self, dst: torch.Tensor, src: torch.Tensor, tag="copy") -> int:
+        nbytes = src.numel() * src.element_size()
+        return self._L.saber_program_add_copy(self._h, ptr(dst), ptr(src), nbytes, tag.encode())
+
+    def allreduce(self, p: AllReduceParams, tag="allreduce") -> int:
+        return self._L.saber_program_add_allreduce(self._h, C.byref(p), tag.encode())
+
+    # ---- execution ---------------------------------------------------------------------------
+    @property
+    def num_ops(self) -> int:
+        return self._L.saber_program_num_ops(self._h)
+
+    @property
+    def declared_launches(self) -> int:
+        return self._L.saber_program_declared_launches(self._h)
+
+    def tags(self) -> list[str]:
+        return [self._L.saber_program_op_tag(self._h, i).decode() for i in range(self.num_ops)]
+
+    def run(self, stream: Optional[torch.cuda.Stream] = None, first: int = 0, last: int = -1) -> None:
+        code = self._L.saber_program_run_range(self._h, first, last, stream_handle(stream))
+        if code != 0:
+            i = self._L.saber_program_last_failed_op(self._h)
+            tag = self._L.saber_program_op_tag(self._h, i).decode()
+            raise NativeError(f"program {self.name!r}: op {i} ({tag}) failed with CUDA error {code}")
+
+    def capture(self, stream: torch.cuda.Stream) -> int:
+        """Capture into a CUDA graph; returns the node count and asserts it equals the declared one."""
+        n = self._L.saber_program_capture(self._h, stream.cuda_stream)
+        if n < 0:
+            raise NativeError(f"program {self.name!r}: capture failed with CUDA error {-n}")
+        if n != self.declared_launches:
+            raise NativeError(
+                f"program {self.name!r}: captured {n} nodes but ops declared {self.declared_launches}")
+        self.captured = True
+        return n
+
+    def replay(self, stream: Optional[torch.cuda.Stream] = None) -> None:
+        check(self._L.saber_program_replay(self._h, stream_handle(stream)), f"replay {self.name!r}")
+
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                self._L.saber_program_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass

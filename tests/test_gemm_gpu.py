@@ -1,0 +1,57 @@
+"""tcgen05 integer GEMM against the exact integer reference (fp64 accumulate of the true ints)."""
+import pytest
+import torch
+
+from saber_engine_b200.ops import functional as F
+from saber_engine_b200.ops import layouts as L
+from saber_engine_b200.ops import reference as R
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(M, N, K, bits, splits=None, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(N, K, generator=g) * 0.02
+    x = torch.randn(M, K, generator=g)
+    wq, ws = L.quantize_weight_rows(w, bits)
+    aq, asc = L.quantize_act_rows(x)
+    ref = R.gemm_i8(wq, ws, aq, asc).float()
+    dev = torch.device("cuda")
+    qw = F.QuantWeight.from_int(wq, ws, bits, dev)
+    m_pad = L.padded_rows(M)
+    qa = F.QuantAct(L.tile_act_int8(aq, m_pad).to(dev), torch.cat([asc, torch.zeros(m_pad - M)]).to(dev), M, K)
+    out = F.gemm_i8(qw, qa, splits=splits)
+    torch.cuda.synchronize()
+    F.scratch(dev).check()
+    got = out.float().cpu()
+    err = (got - ref).abs().max().item()
+    tol = 1e-2 * ref.abs().max().item() + 1e-6   # bf16 rounding of the same exact value
+    assert err <= tol, f"M={M} N={N} K={K} bits={bits} splits={splits}: max err {err} tol {tol}"
+    return out
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_gemm_small_direct(bits):
+    _case(5, 256, 512, bits, splits=1)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_gemm_ragged_n_and_k_loop(bits):
+    _case(9, 200, 2048, bits, splits=1)   # N not a tile multiple; 16 k-blocks > ring depth
+
+
+def test_gemm_split_k_exact_and_scratch_rezeroed():
+    a = _case(40, 384, 4096, 4, splits=4, seed=1)
+    b = _case(40, 384, 4096, 4, splits=4, seed=1)   # second launch reuses the scratch
+    assert torch.equal(a, b)
+    sc = F.scratch(torch.device("cuda"))
+    assert int(sc.ws.abs().max().item()) == 0 and int(sc.counters.abs().max().item()) == 0
+
+
+def test_gemm_auto_splits_decode_shape():
+    _case(9, 5120, 6144, 4)
+
+
+def test_gemm_prefill_tiles():
+    _case(300, 512, 1024, 4, splits=1)    # nt = 256, two token tiles, second one ragged
+    _case(72, 256, 1024, 8, splits=2)     # nt = 80
