@@ -251,16 +251,24 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   const int KB = p->K >> 7;
   const int kb_per = (KB + p->splits - 1) / p->splits;
   if ((p->splits - 1) * kb_per >= KB) return static_cast<int>(cudaErrorInvalidValue);
+  const int kSmemLimit = 226 * 1024;  // opt-in maximum minus the kernel's static shared memory
+  if (stages <= 0) {
+    // default: small token tiles leave room for two CTAs per SM (one's epilogue overlaps the
+    // other's main loop); wide tiles take the whole SM
+    const int budget = p->nt <= 64 ? 112 * 1024 : kSmemLimit;
+    stages = (budget - 1024) / (16384 + p->nt * 128);
+  }
   if (stages < 2) stages = 2;
   if (stages > kMaxStages) stages = kMaxStages;
-  while (stages > 2 && saber_gemm_i8_smem_bytes(p->nt, stages) > 227 * 1024) --stages;
+  while (stages > 2 && saber_gemm_i8_smem_bytes(p->nt, stages) > kSmemLimit) --stages;
   const int smem = saber_gemm_i8_smem_bytes(p->nt, stages);
-  static int configured = 0;
-  if (configured < smem) {
+  if (smem > kSmemLimit) return static_cast<int>(cudaErrorInvalidValue);
+  static bool configured = false;
+  if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         227 * 1024);
+                                         kSmemLimit);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = 227 * 1024;
+    configured = true;
   }
   dim3 grid(p->N_pad / 128, (p->M + p->nt - 1) / p->nt, p->splits);
   gemm_i8_kernel<<<grid, kGemmThreads, smem, stream>>>(*p, stages);

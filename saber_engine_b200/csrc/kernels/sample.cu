@@ -99,6 +99,9 @@ __global__ void __launch_bounds__(1024) topk_seam_kernel(const __nv_bfloat16* lo
     const float f = __bfloat162float(__ushort_as_bfloat16(bits));
     if (f == f) mx = fmaxf(mx, f);
   }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((tid & 31) == 0) red[tid >> 5] = mx;
   __syncthreads();
   if (tid == 0) {
     uint32_t acc = 0;
@@ -110,6 +113,8 @@ __global__ void __launch_bounds__(1024) topk_seam_kernel(const __nv_bfloat16* lo
     sel_hi = bin;
     above_hi = acc;  // elements strictly above the selected high bin
   }
+  mx = red[0];
+  for (int w = 1; w < 32; ++w) mx = fmaxf(mx, red[w]);   // row maximum, same in every thread
   __syncthreads();
   const uint32_t hi = sel_hi;
   const uint32_t above1 = above_hi;
