@@ -31,7 +31,9 @@ namespace {
 
 struct OpGemm { saber::GemmI8Params p; int stages; };
 struct OpRow { int mode; saber::RowOpParams p; };
-struct OpEmbed { const void* table; const int32_t* ids; void* out; int M, H, vocab_lo, vocab_n; };
+struct OpEmbed { const void* table; const int32_t* ids; void* out; int M, H, vocab_lo, vocab_n, ldout; };
+struct OpExpand { const void* ctx; const void* tok; const void* pos; void* out; int nseq, block, H; };
+struct OpAdvance { uint32_t* seq_base; uint32_t by; };
 struct OpGdnConv { saber::GdnConvParams p; int nseq; };
 struct OpGdnRec { saber::GdnRecParams p; int nseq, vs; };
 struct OpRope { saber::RopeKvParams p; };
@@ -44,7 +46,7 @@ struct OpCopy { void* dst; const void* src; size_t bytes; };
 struct OpAllReduce { saber::AllReduceParams p; };
 
 using Op = std::variant<OpGemm, OpRow, OpEmbed, OpGdnConv, OpGdnRec, OpRope, OpAttn, OpArgmax,
-                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce>;
+                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance>;
 
 struct Entry {
   Op op;
@@ -67,7 +69,10 @@ int launch(const Op& op, cudaStream_t s) {
         if constexpr (std::is_same_v<T, OpGemm>) return saber_gemm_i8_launch(&o.p, o.stages, s);
         else if constexpr (std::is_same_v<T, OpRow>) return saber_row_producer_launch(o.mode, &o.p, s);
         else if constexpr (std::is_same_v<T, OpEmbed>)
-          return saber_embed_gather_launch(o.table, o.ids, o.out, o.M, o.H, o.vocab_lo, o.vocab_n, s);
+          return saber_embed_gather_launch(o.table, o.ids, o.out, o.M, o.H, o.vocab_lo, o.vocab_n, o.ldout, s);
+        else if constexpr (std::is_same_v<T, OpExpand>)
+          return saber_block_expand_launch(o.ctx, o.tok, o.pos, o.out, o.nseq, o.block, o.H, s);
+        else if constexpr (std::is_same_v<T, OpAdvance>) return saber_comm_advance_launch(o.seq_base, o.by, s);
         else if constexpr (std::is_same_v<T, OpGdnConv>) return saber_gdn_conv_launch(&o.p, o.nseq, s);
         else if constexpr (std::is_same_v<T, OpGdnRec>) return saber_gdn_recurrent_launch(&o.p, o.nseq, o.vs, s);
         else if constexpr (std::is_same_v<T, OpRope>) return saber_rope_kv_launch(&o.p, s);
@@ -114,8 +119,15 @@ int saber_program_add_row(void* h, int mode, const saber::RowOpParams* p, const 
   return add(h, OpRow{mode, *p}, 1, tag);
 }
 int saber_program_add_embed(void* h, const void* table, const int32_t* ids, void* out, int M, int H,
-                            int vocab_lo, int vocab_n, const char* tag) {
-  return add(h, OpEmbed{table, ids, out, M, H, vocab_lo, vocab_n}, 1, tag);
+                            int vocab_lo, int vocab_n, int ldout, const char* tag) {
+  return add(h, OpEmbed{table, ids, out, M, H, vocab_lo, vocab_n, ldout}, 1, tag);
+}
+int saber_program_add_expand(void* h, const void* ctx, const void* tok, const void* pos, void* out,
+                             int nseq, int block, int H, const char* tag) {
+  return add(h, OpExpand{ctx, tok, pos, out, nseq, block, H}, 1, tag);
+}
+int saber_program_add_advance(void* h, uint32_t* seq_base, uint32_t by, const char* tag) {
+  return add(h, OpAdvance{seq_base, by}, 1, tag);
 }
 int saber_program_add_gdn_conv(void* h, const saber::GdnConvParams* p, int nseq, const char* tag) {
   return add(h, OpGdnConv{*p, nseq}, p->commit ? 2 : 1, tag);

@@ -209,18 +209,43 @@ __global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpPa
 
 // out[m, :] = table[ids[m], :]   (bf16 rows, 16-byte vectors); ids outside [0, vocab) give zeros.
 __global__ void embed_gather_kernel(const __nv_bfloat16* table, const int32_t* ids,
-                                    __nv_bfloat16* out, int M, int H, int vocab_lo, int vocab_n) {
+                                    __nv_bfloat16* out, int M, int H, int vocab_lo, int vocab_n,
+                                    int ldout) {
   const int m = blockIdx.x;
   if (m >= M) return;
   const int id = ids[m] - vocab_lo;
   const bool ok = id >= 0 && id < vocab_n;
   const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(ok ? id : 0) * H);
-  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(m) * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(m) * ldout);
   for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x)
     dst[v] = ok ? src[v] : make_uint4(0, 0, 0, 0);
 }
 
+// x[(b * block + j), :] = bf16(ctx[b, :] + tok[b, :] + pos[j, :])   (drafter block input rows)
+__global__ void block_expand_kernel(const __nv_bfloat16* ctx, const __nv_bfloat16* tok,
+                                    const __nv_bfloat16* pos, __nv_bfloat16* out, int block, int H) {
+  const int row = blockIdx.x, b = row / block, j = row % block;
+  for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x) {
+    float c[8], t[8], q[8];
+    load8(ctx + static_cast<size_t>(b) * H + v * 8, c);
+    load8(tok + static_cast<size_t>(b) * H + v * 8, t);
+    load8(pos + static_cast<size_t>(j) * H + v * 8, q);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) c[i] += t[i] + q[i];
+    store8(out + static_cast<size_t>(row) * H + v * 8, c);
+  }
+}
+
 }  // namespace saber
+
+extern "C" int saber_block_expand_launch(const void* ctx, const void* tok, const void* pos, void* out,
+                                         int nseq, int block, int H, cudaStream_t stream) {
+  if (H & 7) return static_cast<int>(cudaErrorInvalidValue);
+  saber::block_expand_kernel<<<nseq * block, 128, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(ctx), static_cast<const __nv_bfloat16*>(tok),
+      static_cast<const __nv_bfloat16*>(pos), static_cast<__nv_bfloat16*>(out), block, H);
+  return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" int saber_row_producer_launch(int mode, const saber::RowOpParams* p, cudaStream_t stream) {
   using namespace saber;
@@ -249,10 +274,12 @@ extern "C" int saber_row_producer_launch(int mode, const saber::RowOpParams* p, 
 }
 
 extern "C" int saber_embed_gather_launch(const void* table, const int32_t* ids, void* out, int M,
-                                         int H, int vocab_lo, int vocab_n, cudaStream_t stream) {
-  if (H & 7) return static_cast<int>(cudaErrorInvalidValue);
+                                         int H, int vocab_lo, int vocab_n, int ldout,
+                                         cudaStream_t stream) {
+  if ((H & 7) || (ldout & 7)) return static_cast<int>(cudaErrorInvalidValue);
+  if (ldout == 0) ldout = H;
   saber::embed_gather_kernel<<<M, 128, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), M, H,
-      vocab_lo, vocab_n);
+      vocab_lo, vocab_n, ldout);
   return static_cast<int>(cudaGetLastError());
 }

@@ -33,4 +33,7 @@ struct RowOpParams {
 
 extern "C" int saber_row_producer_launch(int mode, const saber::RowOpParams* p, cudaStream_t stream);
 extern "C" int saber_embed_gather_launch(const void* table, const int32_t* ids, void* out, int M,
-                                         int H, int vocab_lo, int vocab_n, cudaStream_t stream);
+                                         int H, int vocab_lo, int vocab_n, int ldout,
+                                         cudaStream_t stream);
+extern "C" int saber_block_expand_launch(const void* ctx, const void* tok, const void* pos, void* out,
+                                         int nseq, int block, int H, cudaStream_t stream);

@@ -221,7 +221,12 @@ __global__ void verify_accept_kernel(const VerifyParams p) {
   if (b >= p.nseq) return;
   const int r0 = p.cu_rows[b];
   const int w = p.cu_rows[b + 1] - r0;
-  if (w <= 0) { p.n_commit[b] = 0; return; }
+  if (w <= 0) {
+    p.n_commit[b] = 0;
+    if (p.accept_row) p.accept_row[b] = 0;
+    if (p.bonus) p.bonus[b] = 0;
+    return;
+  }
   int a = 0;
   if (p.oracle_p > 0.f) {
     const uint64_t h = splitmix64(p.seed ^ splitmix64(static_cast<uint64_t>(p.seq_uid[b]) * 0x100000001B3ull +
@@ -236,6 +241,8 @@ __global__ void verify_accept_kernel(const VerifyParams p) {
   for (int j = 0; j < a; ++j) p.out_tokens[b * p.max_w + j] = p.draft[r0 + j + 1];
   p.out_tokens[b * p.max_w + a] = p.target[r0 + a];
   p.n_commit[b] = a + 1;
+  if (p.accept_row) p.accept_row[b] = r0 + a;
+  if (p.bonus) p.bonus[b] = p.target[r0 + a];
 }
 
 }  // namespace saber

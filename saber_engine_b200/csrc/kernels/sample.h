@@ -15,6 +15,8 @@ struct VerifyParams {
   const int32_t* step_no;   // [nseq] decode step index of the sequence (seeds the oracle)
   int32_t* n_commit;        // [nseq] tokens committed this step (accepted drafts + 1 bonus)
   int32_t* out_tokens;      // [nseq][max_w]
+  int32_t* accept_row;      // [nseq] global row index of the last committed row (may be null)
+  int32_t* bonus;           // [nseq] the bonus token, i.e. the next step's first row (may be null)
   int nseq, max_w;
   float oracle_p;           // 0: greedy prefix match; > 0: seeded geometric(p) acceptance
   uint64_t seed;

@@ -206,7 +206,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, vocab_lo: int = 0) -> t
     M, H = ids.numel(), table.shape[1]
     out = torch.empty(M, H, dtype=torch.bfloat16, device=table.device)
     N.check(N.lib().saber_embed_gather_launch(table.data_ptr(), ids.data_ptr(), out.data_ptr(), M, H,
-                                              vocab_lo, table.shape[0], N.stream_handle()), "embed")
+                                              vocab_lo, table.shape[0], H, N.stream_handle()), "embed")
     return out
 
 
@@ -239,6 +239,7 @@ def verify_accept(draft, target, cu_rows, seq_uid, step_no, max_w: int, oracle_p
     p.draft, p.target, p.cu_rows = draft.data_ptr(), target.data_ptr(), cu_rows.data_ptr()
     p.seq_uid, p.step_no = seq_uid.data_ptr(), step_no.data_ptr()
     p.n_commit, p.out_tokens = n_commit.data_ptr(), out_tokens.data_ptr()
+    p.accept_row, p.bonus = None, None
     p.nseq, p.max_w, p.oracle_p, p.seed = nseq, max_w, oracle_p, seed
     N.check(N.lib().saber_verify_launch(C.byref(p), N.stream_handle()), "verify")
     return n_commit, out_tokens

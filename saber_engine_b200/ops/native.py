@@ -78,7 +78,7 @@ class AttnParams(C.Structure):
 
 class VerifyParams(C.Structure):
     _fields_ = [("draft", P), ("target", P), ("cu_rows", P), ("seq_uid", P), ("step_no", P),
-                ("n_commit", P), ("out_tokens", P), ("nseq", I), ("max_w", I), ("oracle_p", F),
+                ("n_commit", P), ("out_tokens", P), ("accept_row", P), ("bonus", P), ("nseq", I), ("max_w", I), ("oracle_p", F),
                 ("seed", U64)]
 
 
@@ -120,7 +120,8 @@ def _declare(L: C.CDLL) -> None:
         "saber_gemm_i8_launch": (I, [C.POINTER(GemmI8Params), I, S]),
         "saber_gemm_i8_smem_bytes": (I, [I, I]),
         "saber_row_producer_launch": (I, [I, C.POINTER(RowOpParams), S]),
-        "saber_embed_gather_launch": (I, [P, P, P, I, I, I, I, S]),
+        "saber_embed_gather_launch": (I, [P, P, P, I, I, I, I, I, S]),
+        "saber_block_expand_launch": (I, [P, P, P, P, I, I, I, S]),
         "saber_gdn_conv_launch": (I, [C.POINTER(GdnConvParams), I, S]),
         "saber_gdn_recurrent_launch": (I, [C.POINTER(GdnRecParams), I, I, S]),
         "saber_rope_kv_launch": (I, [C.POINTER(RopeKvParams), S]),
@@ -139,7 +140,9 @@ def _declare(L: C.CDLL) -> None:
         "saber_program_destroy": (None, [P]),
         "saber_program_add_gemm": (I, [P, C.POINTER(GemmI8Params), I, C.c_char_p]),
         "saber_program_add_row": (I, [P, I, C.POINTER(RowOpParams), C.c_char_p]),
-        "saber_program_add_embed": (I, [P, P, P, P, I, I, I, I, C.c_char_p]),
+        "saber_program_add_embed": (I, [P, P, P, P, I, I, I, I, I, C.c_char_p]),
+        "saber_program_add_expand": (I, [P, P, P, P, P, I, I, I, C.c_char_p]),
+        "saber_program_add_advance": (I, [P, P, U32, C.c_char_p]),
         "saber_program_add_gdn_conv": (I, [P, C.POINTER(GdnConvParams), I, C.c_char_p]),
         "saber_program_add_gdn_rec": (I, [P, C.POINTER(GdnRecParams), I, I, C.c_char_p]),
         "saber_program_add_rope": (I, [P, C.POINTER(RopeKvParams), C.c_char_p]),
@@ -212,9 +215,16 @@ class Program:
     def row(self, mode: int, p: RowOpParams, tag: str = "row") -> int:
         return self._L.saber_program_add_row(self._h, mode, C.byref(p), tag.encode())
 
-    def embed(self, table, ids, out, M, H, vocab_lo, vocab_n, tag="embed") -> int:
+    def embed(self, table, ids, out, M, H, vocab_lo, vocab_n, ldout=0, tag="embed") -> int:
         return self._L.saber_program_add_embed(self._h, ptr(table), ptr(ids), ptr(out), M, H,
-                                               vocab_lo, vocab_n, tag.encode())
+                                               vocab_lo, vocab_n, ldout, tag.encode())
+
+    def expand(self, ctx, tok, pos, out, nseq, block, H, tag="block_expand") -> int:
+        return self._L.saber_program_add_expand(self._h, ptr(ctx), ptr(tok), ptr(pos), ptr(out),
+                                                nseq, block, H, tag.encode())
+
+    def advance(self, seq_base, by: int, tag="comm_advance") -> int:
+        return self._L.saber_program_add_advance(self._h, ptr(seq_base), by, tag.encode())
 
     def gdn_conv(self, p: GdnConvParams, nseq: int, tag="gdn_conv") -> int:
         return self._L.saber_program_add_gdn_conv(self._h, C.byref(p), nseq, tag.encode())
