@@ -1,0 +1,512 @@
+"""The hybrid decoder (Gated DeltaNet + gated GQA attention, dense MLP or MoE) as native step
+programs on one rank.
+
+`HybridModel` owns the weights, the paged fp8 KV pool, the GDN state slots and the index blob, and
+builds one `Bucket` per planned shape: decode buckets (batch x width rows, speculative: rows are
+verified and the next block is drafted inside the same program) and prefill buckets (a rung of
+rows, rows are committed for good).  A bucket is a fixed launch list (`ops.native.Program`) that is
+walked eagerly or captured into a CUDA graph; per-step values travel in the index blob only.
+
+Parity: the per-layer op order of the reference's model graph (`crates/saber-model/src/graph.rs:4525-4577`),
+its decode buckets batches x widths and prefill rungs (`models.toml:25-36`), the index tables of
+`crates/saber-exec/src/forward.rs:587-860` (slot 0 is the null slot; padding rows carry slot_map -1),
+and the drafter-after-commit flow of `crates/saber-engine/src/draft_plan.rs:17-30`.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from ..ops import functional as F
+from ..ops import layouts as L
+from ..ops import native as N
+from .config import HybridConfig, shard
+from .weights import ModelWeights, random_init
+
+
+@dataclass
+class BlobLayout:
+    """Offsets (in int32 words) of the per-step index tables inside a bucket's index blob."""
+    M: int
+    nseq: int
+    max_blocks: int
+    ids: int = 0
+    pos: int = 0
+    slot_map: int = 0
+    cu_rows: int = 0
+    slots: int = 0
+    shift: int = 0
+    kv_len: int = 0
+    seq_uid: int = 0
+    step_no: int = 0
+    last_rows: int = 0
+    temps: int = 0
+    block_table: int = 0
+    words: int = 0
+
+    @staticmethod
+    def make(M: int, nseq: int, max_blocks: int) -> "BlobLayout":
+        b = BlobLayout(M, nseq, max_blocks)
+        off = 0
+        def take(n):
+            nonlocal off
+            o = off
+            off += (n + 3) // 4 * 4          # keep every table 16-byte aligned
+            return o
+        b.ids = take(M)
+        b.pos = take(3 * M)
+        b.slot_map = take(M)
+        b.cu_rows = take(nseq + 1)
+        b.slots = take(nseq)
+        b.shift = take(nseq)
+        b.kv_len = take(nseq)
+        b.seq_uid = take(nseq)
+        b.step_no = take(nseq)
+        b.last_rows = take(nseq)
+        b.temps = take(M)
+        b.block_table = take(nseq * max_blocks)
+        b.words = off
+        return b
+
+    @property
+    def header_words(self) -> int:
+        return self.block_table
+
+
+@dataclass
+class Bucket:
+    """One planned shape: its program, blob layout, output tensors."""
+    kind: str                 # "decode" | "prefill"
+    nseq: int
+    width: int                # rows per sequence (decode) or rung rows (prefill, nseq sequences packed)
+    M: int
+    layout: BlobLayout
+    program: N.Program
+    blob_dev: torch.Tensor    # int32 [words]
+    blob_host: torch.Tensor   # pinned int32 [words]
+    out_dev: torch.Tensor     # int32: n_commit[nseq] | out_tokens[nseq*W] | drafts[nseq*block] | picks[M]
+    out_host: torch.Tensor    # pinned mirror
+    captured: bool = False
+    n_launches: int = 0
+    logits: Optional[torch.Tensor] = None
+    keep: list = field(default_factory=list)
+
+
+class HybridModel:
+    def __init__(self, cfg: HybridConfig, tp: int = 1, rank: int = 0, device="cuda",
+                 max_seqs: int = 8, max_ctx: Optional[int] = None, kv_blocks: Optional[int] = None,
+                 max_width: int = 9, weights: Optional[ModelWeights] = None, seed: int = 0,
+                 comm=None, oracle_p: float = 0.0, oracle_seed: int = 0, gdn_vs: int = 2,
+                 use_drafter: bool = True):
+        self.cfg, self.tp, self.rank = cfg, tp, rank
+        self.sh = shard(cfg, tp, rank)
+        self.device = torch.device(device)
+        self.max_seqs = max_seqs
+        self.max_ctx = max_ctx or cfg.max_ctx
+        self.max_blocks = (self.max_ctx + cfg.page_tokens - 1) // cfg.page_tokens
+        self.max_width = max_width
+        self.comm = comm
+        self.oracle_p, self.oracle_seed = oracle_p, oracle_seed
+        self.gdn_vs = gdn_vs
+        self.use_drafter = use_drafter and cfg.drafter is not None
+        self.w = weights if weights is not None else random_init(cfg, tp, rank, self.device, seed)
+        self.scratch = F.scratch(self.device)
+        self.k_scale = self.v_scale = 1.0
+        dev = self.device
+        # ---- paged KV pool (fp8): one tensor per attention layer
+        if kv_blocks is None:
+            kv_blocks = max_seqs * self.max_blocks + 1
+        self.kv_blocks = kv_blocks
+        self.kv = {}
+        for i in range(cfg.n_layers):
+            if cfg.is_attention_layer(i):
+                self.kv[i] = torch.zeros(kv_blocks, self.sh.n_kv_heads, 2, cfg.page_tokens, cfg.head_dim,
+                                         dtype=torch.uint8, device=dev)
+        # ---- GDN state slots (slot 0 = null slot)
+        self.n_slots = max_seqs + 1
+        hv, hk, d = self.sh.gdn_v_heads, self.sh.gdn_k_heads, cfg.gdn_head_dim
+        self.gdn_state, self.gdn_hist, self.gdn_stash = {}, {}, {}
+        for i in range(cfg.n_layers):
+            if not cfg.is_attention_layer(i):
+                self.gdn_state[i] = torch.zeros(self.n_slots, hv, d, d, dtype=torch.float32, device=dev)
+                self.gdn_hist[i] = torch.zeros(self.n_slots, 3 + max_width, self.sh.gdn_conv_c,
+                                               dtype=torch.bfloat16, device=dev)
+                self.gdn_stash[i] = torch.zeros(self.n_slots, max_width, hv, gdn_vs,
+                                                F.gdn_stash_stride(gdn_vs), dtype=torch.float32, device=dev)
+        self.buckets: dict = {}
+        self.stream = torch.cuda.Stream(device=dev)
+
+    # ------------------------------------------------------------------------------ state
+    def reset_slot(self, slot: int) -> None:
+        """Zero the recurrent state of a slot (a new sequence starts from nothing)."""
+        for i in self.gdn_state:
+            self.gdn_state[i][slot].zero_()
+            self.gdn_hist[i][slot].zero_()
+
+    def state_bytes(self) -> dict:
+        kv = sum(t.numel() for t in self.kv.values())
+        gdn = sum(t.numel() * 4 for t in self.gdn_state.values()) + \
+            sum(t.numel() * 2 for t in self.gdn_hist.values()) + \
+            sum(t.numel() * 4 for t in self.gdn_stash.values())
+        return {"weights": self.w.nbytes(), "kv_pool": kv, "gdn": gdn}
+
+    # ------------------------------------------------------------------------------ helpers
+    def _qa(self, M: int, K: int) -> F.QuantAct:
+        return F.QuantAct.alloc(M, K, self.device)
+
+    def _gemm(self, prog: N.Program, w: F.QuantWeight, a: F.QuantAct, out: torch.Tensor, tag: str) -> None:
+        splits = self.pick_splits(w, a)
+        prog.gemm(F.gemm_params(w, a, out, self.scratch, splits=splits), self.gemm_stages(w, a), tag=tag)
+
+    def pick_splits(self, w: F.QuantWeight, a: F.QuantAct) -> int:
+        table = getattr(self, "tune_table", None)
+        if table is not None:
+            hit = table.lookup("gemm_i8", N=w.N_pad, K=w.K, M=a.M, w4=int(w.w4))
+            if hit is not None:
+                return int(hit.get("splits", 1))
+        nt = L.token_tile(a.M)
+        return F.pick_splits(w.N_pad // 128, (a.M + nt - 1) // nt, w.K // 128)
+
+    def gemm_stages(self, w: F.QuantWeight, a: F.QuantAct) -> int:
+        table = getattr(self, "tune_table", None)
+        if table is not None:
+            hit = table.lookup("gemm_i8", N=w.N_pad, K=w.K, M=a.M, w4=int(w.w4))
+            if hit is not None:
+                return int(hit.get("stages", 0))
+        return 0
+
+    def attn_splits(self, nseq: int) -> int:
+        ctas = nseq * self.sh.n_kv_heads
+        return max(1, min(32, (148 + ctas - 1) // ctas))
+
+    def tap_layers(self) -> list:
+        n = self.cfg.drafter.n_taps if self.cfg.drafter else 0
+        L_ = self.cfg.n_layers
+        return sorted({min(L_ - 1, max(1, round((k + 1) * L_ / (n + 1)))) for k in range(n)}) if n else []
+
+    # ------------------------------------------------------------------------------ build
+    def build_bucket(self, kind: str, nseq: int, width: int, capture: bool = True) -> Bucket:
+        """kind='decode': nseq sequences x width rows.  kind='prefill': up to nseq sequences packed in
+        `width` rows in total (ragged through cu_rows), rows committed."""
+        key = (kind, nseq, width)
+        if key in self.buckets:
+            return self.buckets[key]
+        cfg, sh, dev = self.cfg, self.sh, self.device
+        decode = kind == "decode"
+        M = nseq * width if decode else width
+        Mh = M if decode else nseq                      # rows that reach the head
+        H, D, d = cfg.hidden, cfg.head_dim, cfg.gdn_head_dim
+        lay = BlobLayout.make(M, nseq, self.max_blocks)
+        blob = torch.zeros(lay.words, dtype=torch.int32, device=dev)
+        blob_host = torch.zeros(lay.words, dtype=torch.int32).pin_memory()
+        base = blob.data_ptr()
+        at = lambda off: base + 4 * off                 # noqa: E731  device address of a table
+        prog = N.Program(f"{kind}-b{nseq}-w{width}")
+        bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)   # noqa: E731
+        f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)   # noqa: E731
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)     # noqa: E731
+
+        h, delta = bf(M, H), bf(M, H)
+        qa_h = self._qa(M, H)
+        ld_in = (max(sh.qkv_n, sh.gdn_in_n) + 7) // 8 * 8
+        buf_in = bf(M, ld_in)
+        conv_out, gdn_o = f32(M, sh.gdn_conv_c), f32(M, sh.gdn_out_k)
+        qa_gdn = self._qa(M, sh.gdn_out_k)
+        q_rot, attn_out = bf(M, sh.n_q_heads, D), bf(M, sh.n_q_heads, D)
+        qa_attn = self._qa(M, sh.o_k)
+        taps = self.tap_layers() if self.use_drafter else []
+        tap_buf = bf(max(1, len(taps)), M, H)
+        splits = self.attn_splits(nseq) if decode else 1
+        part_o = f32(nseq, sh.n_q_heads, splits, 16, D) if splits > 1 else None
+        part_ml = f32(nseq, sh.n_q_heads, splits, 16, 2) if splits > 1 else None
+        if cfg.moe is None:
+            gu = bf(M, 2 * sh.ffn_inter)
+            qa_i = self._qa(M, sh.ffn_inter)
+        keep = [blob, h, delta, qa_h, buf_in, conv_out, gdn_o, qa_gdn, q_rot, attn_out, qa_attn,
+                tap_buf, part_o, part_ml]
+
+        def row(mode, Mr, K, tag, **kw):
+            prog.row(mode, F.row_params(Mr, K, **kw), tag=tag)
+
+        prog.embed(self.w.embed, at(lay.ids), h, M, H, 0, cfg.vocab, H, tag="embed")
+        first = True
+        ar_site = 0
+        for i, lw in enumerate(self.w.layers):
+            t = f"L{i}"
+            row(N.ROW_ADD_RMS, M, H, f"{t}.in_norm", a=None if first else delta, res=h, w=lw.in_norm,
+                w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa_h)
+            first = False
+            if i in taps:
+                prog.copy(tap_buf[taps.index(i)], h, tag=f"{t}.tap")
+            if lw.kind == "gdn":
+                n_q = n_k = sh.gdn_k_heads * d
+                C_ = sh.gdn_conv_c
+                self._gemm(prog, lw.mixer_in, qa_h, buf_in, f"{t}.gdn.in_proj")
+                cp = F.gdn_conv_params(buf_in, lw.conv_w, self.gdn_hist[i], blob, blob, blob, conv_out,
+                                       n_q, n_k, commit=not decode)
+                cp.cu_rows, cp.slots, cp.shift = at(lay.cu_rows), at(lay.slots), at(lay.shift)
+                prog.gdn_conv(cp, nseq, tag=f"{t}.gdn.conv")
+                ba = buf_in[:, C_ + sh.gdn_out_k:]
+                rp = F.gdn_rec_params(conv_out, ba, lw.A_log, lw.dt_bias, self.gdn_state[i],
+                                      self.gdn_stash[i], blob, blob, blob, gdn_o, n_q, n_k,
+                                      sh.gdn_v_heads, sh.gdn_k_heads, commit=not decode, ldba=ld_in)
+                rp.cu_rows, rp.slots, rp.shift = at(lay.cu_rows), at(lay.slots), at(lay.shift)
+                prog.gdn_rec(rp, nseq, self.gdn_vs, tag=f"{t}.gdn.rec")
+                row(N.ROW_GDN_NORM, M, sh.gdn_out_k, f"{t}.gdn.norm_quant", a_f32=gdn_o,
+                    b=buf_in[:, C_:], w=lw.gdn_norm, eps=cfg.eps, qa=qa_gdn, ldb=ld_in)
+                self._gemm(prog, lw.mixer_out, qa_gdn, delta, f"{t}.gdn.out_proj")
+            else:
+                nq, nkv = sh.n_q_heads, sh.n_kv_heads
+                gate = 2 if cfg.attn_out_gate else 1
+                self._gemm(prog, lw.mixer_in, qa_h, buf_in, f"{t}.attn.qkv")
+                k_off = nq * D * gate
+                rk = F.rope_kv_params(buf_in, q_rot, lw.q_norm, lw.k_norm, blob, blob, self.kv[i], nq, nkv,
+                                      0, k_off, k_off + nkv * D, rot_dim=cfg.rot_dim,
+                                      sections=cfg.mrope_sections, theta=cfg.rope_theta, eps=cfg.eps,
+                                      w_offset=cfg.norm_offset, k_scale=self.k_scale, v_scale=self.v_scale)
+                rk.pos, rk.slot_map, rk.ld = at(lay.pos), at(lay.slot_map), ld_in
+                prog.rope(rk, tag=f"{t}.attn.rope_kv")
+                q_tiles = (width + 15) // 16
+                ap = F.attn_params(q_rot, self.kv[i], blob.view(1, -1), blob, blob[:nseq], attn_out, part_o,
+                                   part_ml, nkv, splits, q_tiles, self.k_scale, self.v_scale)
+                ap.block_table, ap.cu_q, ap.kv_len = at(lay.block_table), at(lay.cu_rows), at(lay.kv_len)
+                ap.max_blocks, ap.nseq = self.max_blocks, nseq
+                prog.attn(ap, tag=f"{t}.attn.core")
+                ao = attn_out.view(M, nq * D)
+                if cfg.attn_out_gate:
+                    row(N.ROW_GATE_SIG, M, nq * D, f"{t}.attn.gate_quant", a=ao, b=buf_in[:, nq * D:],
+                        qa=qa_attn, ldb=ld_in)
+                else:
+                    row(N.ROW_PLAIN, M, nq * D, f"{t}.attn.quant", a=ao, qa=qa_attn)
+                self._gemm(prog, lw.mixer_out, qa_attn, delta, f"{t}.attn.o_proj")
+            ar_site = self._allreduce(prog, delta, M * H, ar_site, f"{t}.mixer.ar")
+            row(N.ROW_ADD_RMS, M, H, f"{t}.post_norm", a=delta, res=h, w=lw.post_norm,
+                w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa_h)
+            if cfg.moe is None:
+                self._gemm(prog, lw.gate_up, qa_h, gu, f"{t}.mlp.gate_up")
+                row(N.ROW_SILU_MUL, M, sh.ffn_inter, f"{t}.mlp.silu_mul_quant", a=gu, qa=qa_i)
+                self._gemm(prog, lw.down, qa_i, delta, f"{t}.mlp.down")
+            else:
+                from .moe_block import add_moe_block
+                add_moe_block(self, prog, lw, qa_h, h, delta, M, t, keep)
+            ar_site = self._allreduce(prog, delta, M * H, ar_site, f"{t}.mlp.ar")
+        self._build_head(prog, kind, nseq, width, M, Mh, lay, at, h, delta, qa_h, tap_buf, taps, keep,
+                         ar_site)
+        if cfg.moe is None:
+            keep += [gu, qa_i]
+        return self._finish_bucket(prog, kind, nseq, width, M, lay, blob, blob_host, keep, capture)
+
+    def _allreduce(self, prog: N.Program, buf: torch.Tensor, n_elems: int, site: int, tag: str) -> int:
+        """Row-parallel partial sums -> full sums on every rank (no-op at TP=1)."""
+        if self.tp == 1:
+            return site
+        prog.allreduce(self.comm.allreduce_params(buf, buf, n_elems, site), tag=tag)
+        return site + 1
+
+    def _build_head(self, prog, kind, nseq, width, M, Mh, lay, at, h, delta, qa_h, tap_buf, taps, keep,
+                    ar_site) -> None:
+        cfg, sh, dev = self.cfg, self.sh, self.device
+        H = cfg.hidden
+        decode = kind == "decode"
+        W = width if decode else 1
+        block = cfg.drafter.block if self.use_drafter else 0
+        # outputs: n_commit[nseq] | out_tokens[nseq * W] | drafts[nseq * block] | picks[Mh]
+        n_out = nseq + nseq * W + nseq * max(block, 1) + Mh
+        out = torch.zeros(n_out, dtype=torch.int32, device=dev)
+        o_commit, o_tokens = out[:nseq], out[nseq:nseq + nseq * W]
+        o_drafts = out[nseq + nseq * W: nseq + nseq * W + nseq * max(block, 1)]
+        o_picks = out[nseq + nseq * W + nseq * max(block, 1):]
+        accept_row = torch.zeros(nseq, dtype=torch.int32, device=dev)
+        bonus = torch.zeros(nseq, dtype=torch.int32, device=dev)
+        pick_val = torch.zeros(Mh, dtype=torch.float32, device=dev)
+        logits = torch.zeros(Mh, (sh.vocab + 7) // 8 * 8, dtype=torch.bfloat16, device=dev)
+        self._out_views = None
+        if decode:
+            prog.row(N.ROW_ADD_RMS, F.row_params(M, H, a=delta, res=h, w=self.w.final_norm,
+                                                 w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa_h),
+                     tag="final_norm")
+            qa_head = qa_h
+        else:
+            normed = torch.zeros(M, H, dtype=torch.bfloat16, device=dev)
+            last = torch.zeros(nseq, H, dtype=torch.bfloat16, device=dev)
+            prog.row(N.ROW_ADD_RMS, F.row_params(M, H, a=delta, res=h, w=self.w.final_norm,
+                                                 w_offset=cfg.norm_offset, eps=cfg.eps, out=normed),
+                     tag="final_norm")
+            prog.embed(normed, at(lay.last_rows), last, nseq, H, 0, M, H, tag="gather_last_rows")
+            qa_head = self._qa(nseq, H)
+            prog.row(N.ROW_PLAIN, F.row_params(nseq, H, a=last, qa=qa_head), tag="head_quant")
+            keep += [normed, last, qa_head]
+        self._gemm(prog, self.w.lm_head, qa_head, logits, "lm_head")
+        prog.argmax(logits, Mh, logits.stride(0), sh.vocab, sh.vocab_first, o_picks, pick_val, tag="argmax")
+        if self.tp > 1:
+            pm = self.comm.pick_merge_params(o_picks, pick_val, Mh, ar_site)
+            prog.pick_merge(pm, tag="pick_merge")
+            ar_site += 1
+        if decode:
+            vp = N.VerifyParams()
+            vp.draft, vp.target, vp.cu_rows = at(lay.ids), o_picks.data_ptr(), at(lay.cu_rows)
+            vp.seq_uid, vp.step_no = at(lay.seq_uid), at(lay.step_no)
+            vp.n_commit, vp.out_tokens = o_commit.data_ptr(), o_tokens.data_ptr()
+            vp.accept_row, vp.bonus = accept_row.data_ptr(), bonus.data_ptr()
+            vp.nseq, vp.max_w, vp.oracle_p, vp.seed = nseq, W, self.oracle_p, self.oracle_seed
+            prog.verify(vp, tag="verify_accept")
+            acc_ptr, bonus_ptr = accept_row.data_ptr(), bonus.data_ptr()
+        else:
+            acc_ptr, bonus_ptr = at(lay.last_rows), o_picks.data_ptr()
+        keep += [out, accept_row, bonus, pick_val, logits]
+        self._last_head = dict(out=out, logits=logits, W=W, block=block, Mh=Mh)
+        if self.use_drafter:
+            self._build_drafter(prog, nseq, M, tap_buf, taps, acc_ptr, bonus_ptr, o_drafts, keep)
+        if self.tp > 1:
+            prog.advance(self.comm.seq_base, ar_site, tag="comm_advance")
+
+    def _build_drafter(self, prog, nseq, M, tap_buf, taps, acc_ptr, bonus_ptr, o_drafts, keep) -> None:
+        """Block drafter: taps of the last committed row -> aux projection -> + token and position
+        embeddings -> MLP layers over the block rows -> head -> `block` draft tokens per sequence."""
+        cfg, dc, dw, dev = self.cfg, self.cfg.drafter, self.w.drafter, self.device
+        H, Hd, B = cfg.hidden, dc.hidden, dc.block
+        assert Hd == H, "the drafter shares the target's token embedding"
+        nt = len(taps)
+        cat = torch.zeros(nseq, dc.n_taps * H, dtype=torch.bfloat16, device=dev)
+        for j in range(nt):
+            prog.embed(tap_buf[j], acc_ptr, cat[:, j * H:], nseq, H, 0, M, dc.n_taps * H, tag=f"draft.tap{j}")
+        qa_cat = self._qa(nseq, dc.n_taps * H)
+        prog.row(N.ROW_PLAIN, F.row_params(nseq, dc.n_taps * H, a=cat, qa=qa_cat), tag="draft.tap_quant")
+        ctx = torch.zeros(nseq, Hd, dtype=torch.bfloat16, device=dev)
+        self._gemm(prog, dw.aux_fc, qa_cat, ctx, "draft.aux_fc")
+        tok = torch.zeros(nseq, Hd, dtype=torch.bfloat16, device=dev)
+        prog.embed(self.w.embed, bonus_ptr, tok, nseq, H, 0, cfg.vocab, H, tag="draft.tok_embed")
+        R = nseq * B
+        x = torch.zeros(R, Hd, dtype=torch.bfloat16, device=dev)
+        dd = torch.zeros(R, Hd, dtype=torch.bfloat16, device=dev)
+        prog.expand(ctx, tok, dw.pos_emb, x, nseq, B, Hd, tag="draft.expand")
+        qa_x, qa_di = self._qa(R, Hd), self._qa(R, dc.inter)
+        gu = torch.zeros(R, 2 * dc.inter, dtype=torch.bfloat16, device=dev)
+        for li, lw in enumerate(dw.layers):
+            prog.row(N.ROW_ADD_RMS, F.row_params(R, Hd, a=None if li == 0 else dd, res=x, w=lw["norm"],
+                                                 w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa_x),
+                     tag=f"draft.L{li}.norm")
+            self._gemm(prog, lw["gate_up"], qa_x, gu, f"draft.L{li}.gate_up")
+            prog.row(N.ROW_SILU_MUL, F.row_params(R, dc.inter, a=gu, qa=qa_di), tag=f"draft.L{li}.silu_mul")
+            self._gemm(prog, lw["down"], qa_di, dd, f"draft.L{li}.down")
+        prog.row(N.ROW_ADD_RMS, F.row_params(R, Hd, a=dd if dw.layers else None, res=x, w=dw.final_norm,
+                                             w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa_x),
+                 tag="draft.final_norm")
+        dlogits = torch.zeros(R, (cfg.vocab + 7) // 8 * 8, dtype=torch.bfloat16, device=dev)
+        self._gemm(prog, dw.head, qa_x, dlogits, "draft.head")
+        prog.argmax(dlogits, R, dlogits.stride(0), cfg.vocab, 0, o_drafts, None, tag="draft.argmax")
+        keep += [cat, qa_cat, ctx, tok, x, dd, qa_x, qa_di, gu, dlogits]
+
+    def _finish_bucket(self, prog, kind, nseq, width, M, lay, blob, blob_host, keep, capture) -> Bucket:
+        head = self._last_head
+        out = head["out"]
+        out_host = torch.zeros(out.numel(), dtype=torch.int32).pin_memory()
+        prog.keep(*[k for k in keep if k is not None], self.w)
+        b = Bucket(kind, nseq, width, M, lay, prog, blob, blob_host, out, out_host,
+                   n_launches=prog.declared_launches, logits=head["logits"], keep=keep)
+        b.W, b.block, b.Mh = head["W"], head["block"], head["Mh"]
+        if capture:
+            # one eager walk first: sets function attributes and warms lazy module loading
+            with torch.cuda.stream(self.stream):
+                prog.run(self.stream)
+                self.stream.synchronize()
+                self.scratch.check()
+                prog.capture(self.stream)
+            self.stream.synchronize()
+            b.captured = True
+        self.buckets[(kind, nseq, width)] = b
+        return b
+
+
+@dataclass
+class SeqStep:
+    """What one sequence contributes to a step."""
+    tokens: list              # token ids of this step's rows (decode: [last committed, drafts...])
+    pos0: int                 # position of the first row
+    slot: int                 # GDN state slot (>= 1)
+    shift: int                # rows of the previous decode step that were committed (0 after prefill)
+    blocks: list              # physical KV block ids covering positions [0, pos0 + len(tokens))
+    uid: int = 0
+    step_no: int = 0
+
+
+@dataclass
+class StepResult:
+    n_commit: list            # per sequence: tokens committed (decode) / 1 (prefill last chunk)
+    tokens: list              # per sequence: committed token ids
+    drafts: list              # per sequence: next block of draft tokens
+    picks: list
+
+
+def fill_blob(b: Bucket, seqs: list, page_tokens: int = 16) -> int:
+    """Write the index tables of one step into the bucket's pinned blob. Returns the words to copy."""
+    import numpy as np
+    lay = b.layout
+    a = b.blob_host.numpy()
+    M, nseq = lay.M, lay.nseq
+    hdr = lay.header_words
+    a[:hdr] = 0
+    a[lay.slot_map:lay.slot_map + M] = -1
+    a[lay.slots:lay.slots + nseq] = -1
+    row = 0
+    max_used = 0
+    for j, s in enumerate(seqs):
+        n = len(s.tokens)
+        a[lay.ids + row: lay.ids + row + n] = s.tokens
+        pos = np.arange(s.pos0, s.pos0 + n, dtype=np.int32)
+        for ax in range(3):
+            a[lay.pos + ax * M + row: lay.pos + ax * M + row + n] = pos
+        blk = np.asarray(s.blocks, dtype=np.int32)
+        a[lay.slot_map + row: lay.slot_map + row + n] = blk[pos // page_tokens] * page_tokens + pos % page_tokens
+        a[lay.cu_rows + j] = row
+        a[lay.slots + j] = s.slot
+        a[lay.shift + j] = s.shift
+        a[lay.kv_len + j] = s.pos0 + n
+        a[lay.seq_uid + j] = s.uid
+        a[lay.step_no + j] = s.step_no
+        a[lay.last_rows + j] = row + n - 1
+        bt = lay.block_table + j * lay.max_blocks
+        a[bt: bt + len(blk)] = blk
+        max_used = max(max_used, len(blk))
+        row += n
+    for j in range(len(seqs), nseq + 1):
+        a[lay.cu_rows + j] = row
+    assert row <= M, (row, M)
+    return lay.words
+
+
+def run_bucket(model: "HybridModel", b: Bucket, seqs: list, eager: bool = False) -> StepResult:
+    """One step: index tables host->device (pinned), the program (graph replay or eager walk),
+    results device->host, then parse."""
+    fill_blob(b, seqs, model.cfg.page_tokens)
+    st = model.stream
+    with torch.cuda.stream(st):
+        b.blob_dev.copy_(b.blob_host, non_blocking=True)
+        if b.captured and not eager:
+            b.program.replay(st)
+        else:
+            b.program.run(st)
+        b.out_host.copy_(b.out_dev, non_blocking=True)
+    st.synchronize()
+    return parse_result(b, len(seqs))
+
+
+def parse_result(b: Bucket, n_live: int) -> StepResult:
+    o = b.out_host.numpy()
+    nseq, W, block, Mh = b.nseq, b.W, b.block, b.Mh
+    o_commit = o[:nseq]
+    o_tokens = o[nseq:nseq + nseq * W].reshape(nseq, W)
+    nd = max(block, 1)
+    o_drafts = o[nseq + nseq * W: nseq + nseq * W + nseq * nd].reshape(nseq, nd)
+    o_picks = o[nseq + nseq * W + nseq * nd:]
+    if b.kind == "decode":
+        n_commit = [int(o_commit[j]) for j in range(n_live)]
+        tokens = [o_tokens[j, :n_commit[j]].tolist() for j in range(n_live)]
+    else:
+        n_commit = [1] * n_live
+        tokens = [[int(o_picks[j])] for j in range(n_live)]
+    drafts = [o_drafts[j, :block].tolist() for j in range(n_live)]
+    return StepResult(n_commit, tokens, drafts, o_picks.tolist())

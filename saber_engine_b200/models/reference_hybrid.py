@@ -1,0 +1,83 @@
+"""Plain PyTorch fp32 forward of the hybrid decoder over a whole sequence (no cache), reading the
+SAME quantised weights the native programs use.  It is the oracle of the end-to-end GPU tests and
+restates the per-layer math in one place: add-RMS(1+w) -> per-token int8 -> integer GEMM -> ...
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import layouts as L
+from ..ops import reference as R
+from ..ops.functional import QuantWeight
+from .config import HybridConfig, shard
+from .weights import ModelWeights
+
+
+def dequant_linear(w: QuantWeight):
+    """(int8 true values [N, K], fp32 row scale [N]) on the CPU."""
+    tiles = w.tiles.cpu()
+    if w.w4:
+        q = L.unpack_weight_int4(tiles, w.N, w.K)
+        s = w.scale.cpu()[: w.N] * 16.0
+    else:
+        q = L.untile_weight_int8(tiles, w.N, w.K)
+        s = w.scale.cpu()[: w.N]
+    return q, s
+
+
+def qlinear(x_bf16_rounded: torch.Tensor, w: QuantWeight) -> torch.Tensor:
+    """Quantise rows per token, exact integer GEMM, scale, round to bf16 (as fp32 values)."""
+    q, s = dequant_linear(w)
+    aq, asc = L.quantize_act_rows(x_bf16_rounded)
+    return R.gemm_i8(q, s, aq, asc).float()
+
+
+@torch.no_grad()
+def forward_full(cfg: HybridConfig, w: ModelWeights, ids: torch.Tensor, kv_fp8: bool = True) -> dict:
+    """ids int [T] (one sequence from position 0). Returns logits [T, vocab] and per-layer residuals."""
+    assert cfg.moe is None, "the dense oracle covers the dense hybrid"
+    sh = shard(cfg, 1, 0)
+    T = ids.numel()
+    H, D, d = cfg.hidden, cfg.head_dim, cfg.gdn_head_dim
+    h = w.embed.cpu()[ids.long()].float()
+    delta = None
+    pos3 = torch.arange(T, dtype=torch.int32)[None, :].repeat(3, 1)
+    taps = []
+    for i, lw in enumerate(w.layers):
+        hb, n = R.add_rms(delta, h.to(torch.bfloat16), lw.in_norm.cpu(), cfg.eps, cfg.norm_offset)
+        h = hb.float()
+        taps.append(h.clone())
+        y = qlinear(n, lw.mixer_in)
+        if lw.kind == "gdn":
+            n_q = n_k = sh.gdn_k_heads * d
+            C = sh.gdn_conv_c
+            hv = sh.gdn_v_heads
+            qkv, _ = R.gdn_conv_step(R.bf16_round(y[:, :C]), torch.zeros(3, C), lw.conv_w.cpu(), n_q, n_k)
+            z = y[:, C:C + hv * d]
+            b, a = y[:, C + hv * d:C + hv * d + hv], y[:, C + hv * d + hv:C + hv * d + 2 * hv]
+            o, _ = R.gdn_recurrent_step(torch.zeros(hv, d, d), qkv, b, a, lw.A_log.cpu(), lw.dt_bias.cpu(),
+                                        n_q, n_k, hv, sh.gdn_k_heads)
+            mix = R.gdn_gated_norm(o, z, lw.gdn_norm.cpu(), cfg.eps)
+        else:
+            nq, nkv = sh.n_q_heads, sh.n_kv_heads
+            gate = 2 if cfg.attn_out_gate else 1
+            q = y[:, :nq * D].reshape(T, nq, D)
+            k_off = nq * D * gate
+            k = y[:, k_off:k_off + nkv * D].reshape(T, nkv, D)
+            v = y[:, k_off + nkv * D:k_off + 2 * nkv * D].reshape(T, nkv, D)
+            kw = dict(rot_dim=cfg.rot_dim, sections=cfg.mrope_sections, theta=cfg.rope_theta, eps=cfg.eps,
+                      w_offset=cfg.norm_offset)
+            qr = R.bf16_round(R.qk_norm_rope(q, lw.q_norm.cpu(), pos3, **kw))
+            kr = R.qk_norm_rope(k, lw.k_norm.cpu(), pos3, **kw)
+            if kv_fp8:
+                kr, v = R.fp8_round(kr), R.fp8_round(v)
+            ao = R.bf16_round(R.attention_rows(qr, kr, v, T)).reshape(T, nq * D)
+            mix = R.gate_sigmoid(ao, y[:, nq * D:2 * nq * D]) if cfg.attn_out_gate else ao
+        delta = qlinear(mix, lw.mixer_out).to(torch.bfloat16)
+        hb, n = R.add_rms(delta, h.to(torch.bfloat16), lw.post_norm.cpu(), cfg.eps, cfg.norm_offset)
+        h = hb.float()
+        gu = qlinear(n, lw.gate_up)
+        delta = qlinear(R.silu_mul(gu), lw.down).to(torch.bfloat16)
+    hb, n = R.add_rms(delta, h.to(torch.bfloat16), w.final_norm.cpu(), cfg.eps, cfg.norm_offset)
+    logits = qlinear(n, w.lm_head)
+    return {"logits": logits, "taps": taps, "final": n}

@@ -1,0 +1,186 @@
+"""Per-rank weights of the hybrid decoder in GEMM-ready form, and their random-init generator.
+
+Record names follow the pack convention (`layers.<i>.<block>.<linear>`); the same names key the
+SBRPACK1 records, so a model is filled either from a pack (`from_records`) or from a seeded
+N(0, 0.02) generator that quantises straight into the device layouts (`random_init`).
+Sharding follows `models.config.shard`: column-parallel linears split output features (merged
+q|gate|k|v and q|k|v|z|b|a by segment), row-parallel linears split the reduction dim.
+
+Parity: linear inventory and shard kinds of `crates/saber-plan/src/model.rs:589-672`; quantisation
+laws of `tools/pack/build_pack.py:22-40` restated for the synthetic W4A8-iu8 pack (symmetric per
+output row, int4, int8 for the designated set, lm_head int8).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Optional
+
+import torch
+
+from ..ops import layouts as L
+from ..ops.functional import QuantWeight
+from .config import HybridConfig, ShardShape, shard
+
+
+@dataclass
+class LayerWeights:
+    kind: str                              # "gdn" | "attn"
+    in_norm: torch.Tensor                  # fp32 [H]
+    post_norm: torch.Tensor                # fp32 [H]
+    mixer_in: QuantWeight                  # gdn: q|k|v|z|b|a ; attn: q|gate|k|v
+    mixer_out: QuantWeight                 # row-parallel
+    gate_up: Optional[QuantWeight] = None  # dense MLP: gate rows then up rows
+    down: Optional[QuantWeight] = None
+    # GDN
+    conv_w: Optional[torch.Tensor] = None  # fp32 [C, 4]
+    A_log: Optional[torch.Tensor] = None
+    dt_bias: Optional[torch.Tensor] = None
+    gdn_norm: Optional[torch.Tensor] = None  # fp32 [128]
+    # attention
+    q_norm: Optional[torch.Tensor] = None  # fp32 [256]
+    k_norm: Optional[torch.Tensor] = None
+    # MoE
+    moe: Optional[dict] = None
+
+
+@dataclass
+class DrafterWeights:
+    aux_fc: QuantWeight
+    pos_emb: torch.Tensor                  # bf16 [block, Hd]
+    layers: list = field(default_factory=list)   # dicts: norm, gate_up, down
+    final_norm: Optional[torch.Tensor] = None
+    head: Optional[QuantWeight] = None
+
+
+@dataclass
+class ModelWeights:
+    embed: torch.Tensor                    # bf16 [vocab, H] (replicated on every rank)
+    layers: list
+    final_norm: torch.Tensor
+    lm_head: QuantWeight                   # column-parallel over the vocab
+    drafter: Optional[DrafterWeights] = None
+
+    def nbytes(self) -> int:
+        tot = self.embed.numel() * 2
+        def qw(w): return 0 if w is None else w.tiles.numel() + w.scale.numel() * 4
+        for lw in self.layers:
+            tot += qw(lw.mixer_in) + qw(lw.mixer_out) + qw(lw.gate_up) + qw(lw.down)
+            if lw.moe:
+                tot += sum(qw(v) if isinstance(v, QuantWeight) else v.numel() * v.element_size()
+                           for v in lw.moe.values() if v is not None and not isinstance(v, (int, float)))
+        tot += qw(self.lm_head)
+        if self.drafter:
+            tot += qw(self.drafter.aux_fc) + qw(self.drafter.head)
+            for d in self.drafter.layers:
+                tot += qw(d["gate_up"]) + qw(d["down"])
+        return tot
+
+
+def linear_bits(cfg: HybridConfig, name: str) -> int:
+    return 8 if name in cfg.w8_linears else 4
+
+
+def _quant_on(dev, w: torch.Tensor, bits: int) -> QuantWeight:
+    q, s = L.quantize_weight_rows(w, bits)
+    return QuantWeight.from_int(q, s, bits, dev)
+
+
+def random_init(cfg: HybridConfig, tp: int, rank: int, device, seed: int = 0,
+                std: float = 0.02) -> ModelWeights:
+    """Seeded N(0, std) weights quantised into the device layouts.
+
+    Every rank draws the FULL tensor of a linear from the same generator state and keeps its own
+    shard, so TP=1 and TP=n describe the same model (the pack builder's `tp1 vs tp2` equality).
+    """
+    sh = shard(cfg, tp, rank)
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(seed)
+    H, d, D = cfg.hidden, cfg.gdn_head_dim, cfg.head_dim
+
+    def rand(n, k):
+        return torch.randn(n, k, generator=g, device=dev, dtype=torch.float32) * std
+
+    def vec(n, scale=0.1, base=0.0):
+        return (torch.randn(n, generator=g, device=dev) * scale + base).float()
+
+    def rows(w, first, count):
+        return w[first:first + count]
+
+    layers = []
+    for i in range(cfg.n_layers):
+        name = f"layers.{i}"
+        if cfg.is_attention_layer(i):
+            gate = 2 if cfg.attn_out_gate else 1
+            wq = rand(cfg.n_q_heads * D * gate, H)      # [q heads | gate heads]
+            wk = rand(cfg.n_kv_heads * D, H)
+            wv = rand(cfg.n_kv_heads * D, H)
+            nq, nkv = sh.n_q_heads, sh.n_kv_heads
+            parts = [rows(wq, sh.q_head_first * D, nq * D)]
+            if cfg.attn_out_gate:
+                parts.append(rows(wq, cfg.n_q_heads * D + sh.q_head_first * D, nq * D))
+            parts += [rows(wk, sh.kv_head_first * D, nkv * D), rows(wv, sh.kv_head_first * D, nkv * D)]
+            mixer_in = _quant_on(dev, torch.cat(parts, 0), linear_bits(cfg, name + ".mixer.in"))
+            wo = rand(H, cfg.n_q_heads * D)
+            mixer_out = _quant_on(dev, wo[:, sh.q_head_first * D:(sh.q_head_first + nq) * D].contiguous(),
+                                  linear_bits(cfg, name + ".mixer.out"))
+            lw = LayerWeights("attn", vec(H), vec(H), mixer_in, mixer_out,
+                              q_norm=vec(D), k_norm=vec(D))
+            del wq, wk, wv, wo
+        else:
+            HK, HV = cfg.gdn_k_heads, cfg.gdn_v_heads
+            wq, wk = rand(HK * d, H), rand(HK * d, H)
+            wv, wz = rand(HV * d, H), rand(HV * d, H)
+            wb, wa = rand(HV, H), rand(HV, H)
+            hk, hv = sh.gdn_k_heads, sh.gdn_v_heads
+            k0, v0 = rank * hk, rank * hv
+            parts = [rows(wq, k0 * d, hk * d), rows(wk, k0 * d, hk * d), rows(wv, v0 * d, hv * d),
+                     rows(wz, v0 * d, hv * d), rows(wb, v0, hv), rows(wa, v0, hv)]
+            mixer_in = _quant_on(dev, torch.cat(parts, 0), linear_bits(cfg, name + ".mixer.in"))
+            wo = rand(H, HV * d)
+            mixer_out = _quant_on(dev, wo[:, v0 * d:(v0 + hv) * d].contiguous(),
+                                  linear_bits(cfg, name + ".mixer.out"))
+            conv_full = torch.randn(2 * HK * d + HV * d, 4, generator=g, device=dev) * 0.5
+            conv = torch.cat([conv_full[k0 * d:(k0 + hk) * d],
+                              conv_full[HK * d + k0 * d:HK * d + (k0 + hk) * d],
+                              conv_full[2 * HK * d + v0 * d:2 * HK * d + (v0 + hv) * d]], 0).contiguous()
+            A_full, dt_full = vec(HV, 0.5), vec(HV, 0.5)
+            lw = LayerWeights("gdn", vec(H), vec(H), mixer_in, mixer_out, conv_w=conv,
+                              A_log=A_full[v0:v0 + hv].contiguous(), dt_bias=dt_full[v0:v0 + hv].contiguous(),
+                              gdn_norm=vec(d, 0.1, 1.0))
+            del wq, wk, wv, wz, wb, wa, wo
+        if cfg.moe is None:
+            I = cfg.ffn_inter
+            wg, wu = rand(I, H), rand(I, H)
+            i0, il = rank * sh.ffn_inter, sh.ffn_inter
+            lw.gate_up = _quant_on(dev, torch.cat([wg[i0:i0 + il], wu[i0:i0 + il]], 0),
+                                   linear_bits(cfg, name + ".mlp.gate_up"))
+            wd = rand(H, I)
+            lw.down = _quant_on(dev, wd[:, i0:i0 + il].contiguous(), linear_bits(cfg, name + ".mlp.down"))
+            del wg, wu, wd
+        else:
+            from .moe_weights import random_moe_layer
+            lw.moe = random_moe_layer(cfg, tp, rank, dev, g, std)
+        layers.append(lw)
+
+    embed = (torch.randn(cfg.vocab, H, generator=g, device=dev) * std).to(torch.bfloat16)
+    if cfg.tie_embeddings:
+        head_w = embed.float()
+    else:
+        head_w = rand(cfg.vocab, H)
+    lm_head = _quant_on(dev, head_w[sh.vocab_first:sh.vocab_first + sh.vocab].contiguous(), cfg.lm_head_bits)
+    del head_w
+    mw = ModelWeights(embed, layers, vec(H), lm_head)
+
+    if cfg.drafter is not None:
+        dc = cfg.drafter
+        Hd = dc.hidden
+        dw = DrafterWeights(aux_fc=_quant_on(dev, rand(Hd, dc.n_taps * H), 4),
+                            pos_emb=(torch.randn(dc.block, Hd, generator=g, device=dev) * std).to(torch.bfloat16))
+        for _ in range(dc.n_layers):
+            dw.layers.append(dict(norm=vec(Hd),
+                                  gate_up=_quant_on(dev, rand(2 * dc.inter, Hd), 4),
+                                  down=_quant_on(dev, rand(Hd, dc.inter), 4)))
+        dw.final_norm = vec(Hd)
+        dw.head = _quant_on(dev, rand(cfg.vocab, Hd), dc.head_bits)
+        mw.drafter = dw
+    return mw

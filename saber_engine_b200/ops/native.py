@@ -175,6 +175,8 @@ def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     """Device pointer of a tensor (None stays a null pointer)."""
     if t is None:
         return None
+    if isinstance(t, int):
+        return t          # already a device address
     return t.data_ptr()
 
 

@@ -1,0 +1,106 @@
+"""End-to-end hybrid model on the GPU: native programs vs the plain PyTorch oracle, graph == eager,
+speculative decoding == plain greedy decoding, chunked prefill == one-shot prefill."""
+import pytest
+import torch
+
+from saber_engine_b200.models import config as C
+from saber_engine_b200.models.hybrid import HybridModel, SeqStep, run_bucket
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def model():
+    cfg = C.scaled_hybrid()
+    return HybridModel(cfg, device="cuda", max_seqs=4, max_ctx=512, max_width=5, seed=1)
+
+
+def _blocks(seq_index, n=32):
+    return list(range(1 + seq_index * n, 1 + (seq_index + 1) * n))
+
+
+def _prefill(model, prompt, slot, blocks, chunks=None, eager=False):
+    model.reset_slot(slot)
+    pos, res = 0, None
+    for n in (chunks or [len(prompt)]):
+        b = model.build_bucket("prefill", 1, 48)
+        res = run_bucket(model, b, [SeqStep(prompt[pos:pos + n], pos, slot, 0, blocks)], eager=eager)
+        pos += n
+    return res
+
+
+def _decode(model, prompt, first, drafts, slot, blocks, steps, width, eager=False):
+    out = [first]
+    shift, pos = 0, len(prompt)
+    b = model.build_bucket("decode", 1, width)
+    n_steps = 0
+    while len(out) < steps:
+        rows = [out[-1]] + list(drafts[:width - 1])
+        res = run_bucket(model, b, [SeqStep(rows, pos, slot, shift, blocks, uid=7, step_no=n_steps)], eager=eager)
+        n = res.n_commit[0]
+        out += res.tokens[0]
+        pos += n
+        shift = n
+        drafts = res.drafts[0]
+        n_steps += 1
+    return out[:steps], n_steps
+
+
+def test_prefill_logits_match_oracle(model):
+    from saber_engine_b200.models.reference_hybrid import forward_full
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, model.cfg.vocab, (40,), generator=g).tolist()
+    res = _prefill(model, prompt, 1, _blocks(0))
+    b = model.buckets[("prefill", 1, 48)]
+    got = b.logits[0, : model.cfg.vocab].float().cpu()
+    ref = forward_full(model.cfg, model.w, torch.tensor(prompt))["logits"][-1]
+    assert (got - ref).abs().max() < 0.05 * ref.abs().max() + 1e-3
+    assert res.tokens[0][0] == int(ref.argmax()) or (ref.max() - ref[res.tokens[0][0]]) < 0.02 * ref.abs().max()
+
+
+def test_spec_decode_equals_plain_greedy_and_graph_equals_eager(model):
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, model.cfg.vocab, (37,), generator=g).tolist()
+    r = _prefill(model, prompt, 1, _blocks(0))
+    plain, n_plain = _decode(model, prompt, r.tokens[0][0], [], 1, _blocks(0), 20, 1)
+    r2 = _prefill(model, prompt, 2, _blocks(1))
+    assert r2.tokens == r.tokens
+    spec, n_spec = _decode(model, prompt, r2.tokens[0][0], r2.drafts[0], 2, _blocks(1), 20, 5)
+    assert spec == plain
+    assert n_spec <= n_plain
+    r3 = _prefill(model, prompt, 3, _blocks(2), eager=True)
+    eager, _ = _decode(model, prompt, r3.tokens[0][0], r3.drafts[0], 3, _blocks(2), 20, 5, eager=True)
+    assert eager == plain
+
+
+def test_chunked_prefill_equals_one_shot(model):
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, model.cfg.vocab, (45,), generator=g).tolist()
+    a = _prefill(model, prompt, 1, _blocks(0))
+    b = _prefill(model, prompt, 2, _blocks(1), chunks=[16, 20, 9])
+    assert a.tokens == b.tokens
+
+
+def test_batched_equals_solo(model):
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, model.cfg.vocab, (n,), generator=g).tolist() for n in (20, 33)]
+    firsts, solo = [], []
+    for j, p in enumerate(prompts):
+        r = _prefill(model, p, j + 1, _blocks(j))
+        firsts.append(r.tokens[0][0])
+        solo.append(_decode(model, p, r.tokens[0][0], [], j + 1, _blocks(j), 8, 1)[0])
+    for j, p in enumerate(prompts):
+        _prefill(model, p, j + 1, _blocks(j))
+    b = model.build_bucket("decode", 2, 1)
+    outs = [[f] for f in firsts]
+    pos = [len(p) for p in prompts]
+    shift = [0, 0]
+    for _ in range(7):
+        seqs = [SeqStep([outs[j][-1]], pos[j], j + 1, shift[j], _blocks(j)) for j in range(2)]
+        res = run_bucket(model, b, seqs)
+        for j in range(2):
+            outs[j] += res.tokens[j]
+            pos[j] += 1
+            shift[j] = 1
+    assert outs == solo
+    assert b.captured and b.program.declared_launches == b.n_launches
