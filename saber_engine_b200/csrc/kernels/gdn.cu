@@ -93,13 +93,19 @@ __global__ void __launch_bounds__(128) gdn_conv_commit_kernel(const GdnConvParam
 
 // ---------------------------------------------------------------------------------- recurrence
 // grid (HV * VS, nseq); block = 2 * (128 / VS) threads; thread = (v row, k half).
+// Rows are staged in shared memory in batches of kRecBatch (all loads of a batch are issued
+// together, so the per-row loop touches no global memory except its one output element).
+constexpr int kRecBatch = 16;
+
 template <int VS>
 __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecParams p) {
   constexpr int VR = 128 / VS;         // v rows per CTA
   constexpr int NT = 2 * VR;           // threads
   constexpr int KP = 64 + 4;           // padded half stride in shared memory (bank spread)
-  __shared__ __align__(16) float ks[2][2 * KP];
-  __shared__ __align__(16) float qs[2][2 * KP];
+  __shared__ __align__(16) float ks[kRecBatch][2 * KP];
+  __shared__ __align__(16) float qs[kRecBatch][2 * KP];
+  __shared__ float vsm[kRecBatch][VR];
+  __shared__ float gsm[kRecBatch], bsm[kRecBatch];
   const int b = blockIdx.y;
   const int slot = p.slots[b];
   if (slot < 0) return;
@@ -110,7 +116,7 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
   const int v = vs * VR + vloc;
   const int row0 = p.cu_rows[b];
   const int n = p.cu_rows[b + 1] - row0;
-  const int shift = p.shift[b];
+  const int shift = min(p.shift[b], min(p.stash_rows, kRecBatch));
   const int stash_stride = 128 + VR + 4;
   float* sp = p.state + ((static_cast<size_t>(slot) * p.HV + h) * 128 + v) * 128 + kh * 64;
   float* stash = p.stash + ((static_cast<size_t>(slot) * p.stash_rows) * p.HV * VS +
@@ -148,46 +154,69 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
   };
 
   // ---- replay the accepted rows of the previous step, then store the committed state
-  int buf = 0;
-  for (int r = 0; r < shift; ++r) {
-    const float* st = stash + static_cast<size_t>(r) * stash_row;
-    for (int i = tid; i < 128; i += NT) ks[buf][(i >> 6) * KP + (i & 63)] = st[i];
-    __syncthreads();
-    const float vval = st[128 + vloc];
-    const float g = st[128 + VR], beta = st[128 + VR + 1];
-    apply(&ks[buf][kh * KP], nullptr, vval, g, beta, false);
-    buf ^= 1;
-  }
   if (shift > 0) {
+    for (int idx = tid; idx < shift * 128; idx += NT) {
+      const int r = idx >> 7, i = idx & 127;
+      ks[r][(i >> 6) * KP + (i & 63)] = stash[static_cast<size_t>(r) * stash_row + i];
+    }
+    for (int idx = tid; idx < shift * VR; idx += NT) {
+      const int r = idx / VR, i = idx % VR;
+      vsm[r][i] = stash[static_cast<size_t>(r) * stash_row + 128 + i];
+    }
+    if (tid < shift) {
+      gsm[tid] = stash[static_cast<size_t>(tid) * stash_row + 128 + VR];
+      bsm[tid] = stash[static_cast<size_t>(tid) * stash_row + 128 + VR + 1];
+    }
+    __syncthreads();
+    for (int r = 0; r < shift; ++r) apply(&ks[r][kh * KP], nullptr, vsm[r][vloc], gsm[r], bsm[r], false);
 #pragma unroll
     for (int i = 0; i < 16; ++i)
       reinterpret_cast<float4*>(sp)[i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
-  }
-  __syncthreads();
-
-  // ---- this step's rows
-  for (int r = 0; r < n; ++r) {
-    const size_t m = static_cast<size_t>(row0 + r);
-    const float* xr = p.qkv + m * p.C;
-    for (int i = tid; i < 128; i += NT) {
-      qs[buf][(i >> 6) * KP + (i & 63)] = xr[hk * 128 + i];
-      ks[buf][(i >> 6) * KP + (i & 63)] = xr[p.n_q + hk * 128 + i];
-    }
-    const float vval = xr[p.n_q + p.n_k + h * 128 + v];
-    const float bb = __bfloat162float(p.ba[m * p.ldba + h]);
-    const float aa = __bfloat162float(p.ba[m * p.ldba + p.HV + h]);
-    const float g = neg_a * gdn_softplus(aa + dtb);
-    const float beta = 1.f / (1.f + __expf(-bb));
     __syncthreads();
-    const float o = apply(&ks[buf][kh * KP], &qs[buf][kh * KP], vval, g, beta, true);
-    if (kh == 0) p.out[m * (static_cast<size_t>(p.HV) * 128) + h * 128 + v] = o;
-    if (!p.commit && r < p.stash_rows) {
-      float* st = stash + static_cast<size_t>(r) * stash_row;
-      for (int i = tid; i < 128; i += NT) st[i] = ks[buf][(i >> 6) * KP + (i & 63)];
-      if (kh == 0) st[128 + vloc] = vval;
-      if (tid == 0) { st[128 + VR] = g; st[128 + VR + 1] = beta; }
+  }
+
+  // ---- this step's rows, a batch at a time
+  for (int r0 = 0; r0 < n; r0 += kRecBatch) {
+    const int nb = min(kRecBatch, n - r0);
+    for (int idx = tid; idx < nb * 128; idx += NT) {
+      const int r = idx >> 7, i = idx & 127;
+      const float* xr = p.qkv + static_cast<size_t>(row0 + r0 + r) * p.C;
+      qs[r][(i >> 6) * KP + (i & 63)] = xr[hk * 128 + i];
+      ks[r][(i >> 6) * KP + (i & 63)] = xr[p.n_q + hk * 128 + i];
     }
-    buf ^= 1;
+    for (int idx = tid; idx < nb * VR; idx += NT) {
+      const int r = idx / VR, i = idx % VR;
+      vsm[r][i] = p.qkv[static_cast<size_t>(row0 + r0 + r) * p.C + p.n_q + p.n_k + h * 128 + vs * VR + i];
+    }
+    if (tid < nb) {
+      const size_t m = static_cast<size_t>(row0 + r0 + tid);
+      const float bb = __bfloat162float(p.ba[m * p.ldba + h]);
+      const float aa = __bfloat162float(p.ba[m * p.ldba + p.HV + h]);
+      gsm[tid] = neg_a * gdn_softplus(aa + dtb);
+      bsm[tid] = 1.f / (1.f + __expf(-bb));
+    }
+    __syncthreads();
+    for (int r = 0; r < nb; ++r) {
+      const float o = apply(&ks[r][kh * KP], &qs[r][kh * KP], vsm[r][vloc], gsm[r], bsm[r], true);
+      if (kh == 0)
+        p.out[static_cast<size_t>(row0 + r0 + r) * (static_cast<size_t>(p.HV) * 128) + h * 128 + v] = o;
+    }
+    if (!p.commit) {
+      for (int idx = tid; idx < nb * 128; idx += NT) {
+        const int r = idx >> 7, i = idx & 127;
+        if (r0 + r < p.stash_rows)
+          stash[static_cast<size_t>(r0 + r) * stash_row + i] = ks[r][(i >> 6) * KP + (i & 63)];
+      }
+      for (int idx = tid; idx < nb * VR; idx += NT) {
+        const int r = idx / VR, i = idx % VR;
+        if (r0 + r < p.stash_rows) stash[static_cast<size_t>(r0 + r) * stash_row + 128 + i] = vsm[r][i];
+      }
+      if (tid < nb && r0 + tid < p.stash_rows) {
+        stash[static_cast<size_t>(r0 + tid) * stash_row + 128 + VR] = gsm[tid];
+        stash[static_cast<size_t>(r0 + tid) * stash_row + 128 + VR + 1] = bsm[tid];
+      }
+    }
+    __syncthreads();
   }
   if (p.commit && n > 0) {
 #pragma unroll

@@ -12,15 +12,15 @@
 // to 256) is the N operand, so a decode step with 1..64 rows wastes no tensor-core rows and a
 // prefill chunk uses nt=256.  Accumulators live in TMEM (128 lanes x nt int32 columns).
 //
-// Warp roles (192 threads):
+// Warp roles (320 threads):
 //   warp 0    one elected lane streams weight tiles and activation tiles with bulk async copies
 //             (TMA, untiled form: both operands are stored pre-tiled, see below) into a ring of
 //             shared-memory stages, completion counted on an mbarrier per stage.
 //   warp 1    allocates TMEM; one lane issues 4 x tcgen05.mma (K=32 each) per stage and commits
 //             the stage's "empty" barrier, then the accumulator barrier.
-//   warps 2-5 W4 only: widen the packed int4 stage in place to int8 (see pack law), then
-//             fence.proxy.async + arrive on the stage's "ready" barrier.  Afterwards the same four
-//             warps are the epilogue: tcgen05.ld their 32 TMEM lanes, scale, store bf16 (direct),
+//   warps 2-9 W4 only, two groups of four warps taking alternate k-blocks: widen the packed
+//             int4 stage in place to int8 (see pack law), then fence.proxy.async + arrive on the
+//             stage's "ready" barrier.  Afterwards warps 2-5 are the epilogue: tcgen05.ld their 32 TMEM lanes, scale, store bf16 (direct),
 //             or add int32 partials to the split-K workspace where the last-arriving CTA of a
 //             tile finishes it (exact: integer addition is order-free) and re-zeroes the scratch.
 //
@@ -37,18 +37,24 @@
 
 namespace saber {
 
-constexpr int kMaxStages = 12;
-constexpr int kGemmThreads = 192;
+constexpr int kMaxStages = 16;
+constexpr int kABufs = 4;           // W4: int8 A-operand buffers in TMEM (32 columns each)
+constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, two groups of four transform warps
 
 __global__ void __launch_bounds__(kGemmThreads)
-gemm_i8_kernel(const GemmI8Params p, const int stages) {
+gemm_i8_kernel(const GemmI8Params p, const int stages, const int n_acc) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bars[3 * kMaxStages + 1];
+  __shared__ uint64_t bars[2 * kMaxStages + 2 * kABufs + 1];
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t is_last_s;
+  __shared__ float a_scale_s[256];
+  __shared__ uint32_t abort_s;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const bool dbg_on = p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+#define SABER_STAMP(i) do { if (dbg_on) p.dbg[i] = globaltimer_ns(); } while (0)
+  if (threadIdx.x == 0) SABER_STAMP(0);
   const int tile_n = blockIdx.x;
   const int tile_m = blockIdx.y;
   const int split = blockIdx.z;
@@ -63,23 +69,34 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
   const uint32_t abytes = static_cast<uint32_t>(p.nt) * 128u;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t w_smem = smem_base;                                   // stages x 16 KiB
-  const uint32_t a_smem = smem_base + static_cast<uint32_t>(stages) * 16384u;  // stages x abytes
+  const uint32_t a_smem = smem_base;                                           // stages x abytes
+  const uint32_t w_smem = smem_base + static_cast<uint32_t>(stages) * abytes;  // stages x wbytes
   const uint32_t bar_full = smem_u32(&bars[0]);
   const uint32_t bar_empty = smem_u32(&bars[kMaxStages]);
-  const uint32_t bar_ready = smem_u32(&bars[2 * kMaxStages]);
-  const uint32_t bar_acc = smem_u32(&bars[3 * kMaxStages]);
+  const uint32_t bar_ready = smem_u32(&bars[2 * kMaxStages]);           // kABufs
+  const uint32_t bar_afree = smem_u32(&bars[2 * kMaxStages + kABufs]);  // kABufs
+  const uint32_t bar_acc = smem_u32(&bars[2 * kMaxStages + 2 * kABufs]);
 
+  uint32_t acc_cols = 32;
+  while (acc_cols < static_cast<uint32_t>(p.nt)) acc_cols <<= 1;
+  // n_acc independent accumulators: consecutive MMAs then do not wait on one another's result
+  // (a chain of dependent tcgen05.mma into one accumulator pays the full MMA latency per link,
+  // which for narrow token tiles is far longer than the MMA's own work); the epilogue adds them.
+  const uint32_t acc_total = acc_cols * static_cast<uint32_t>(n_acc);
   uint32_t tmem_cols = 32;
-  while (tmem_cols < static_cast<uint32_t>(p.nt)) tmem_cols <<= 1;
+  while (tmem_cols < acc_total + (p.w4 ? kABufs * 32u : 0u)) tmem_cols <<= 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
-      mbar_init(bar_ready + 8 * s, 128);
+    }
+    for (int u = 0; u < kABufs; ++u) {
+      mbar_init(bar_ready + 8 * u, 4);  // one arrival per transform warp of the owning group
+      mbar_init(bar_afree + 8 * u, 1);
     }
     mbar_init(bar_acc, 1);
+    abort_s = 0;
     mbar_init_fence();
   }
   if (warp == 1) {
@@ -89,7 +106,9 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_d = tmem_base_s;
+  if (threadIdx.x == 0) SABER_STAMP(1);
+  const uint32_t tmem_d = tmem_base_s;          // accumulator: columns [0, nt)
+  const uint32_t tmem_a = tmem_base_s + acc_total;  // W4: A buffers, 32 columns each
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
@@ -104,11 +123,12 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
         const uint32_t ph = (it / stages) & 1;
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, p.err, kErrWaitEmpty)) { ok = false; break; }
         mbar_arrive_expect_tx(bar_full + 8 * s, wbytes + abytes);
-        bulk_g2s_hint(w_smem + s * 16384u + (p.w4 ? 8192u : 0u), wsrc + static_cast<size_t>(it) * wbytes,
-                      wbytes, bar_full + 8 * s, pol);
+        bulk_g2s_hint(w_smem + s * wbytes, wsrc + static_cast<size_t>(it) * wbytes, wbytes,
+                      bar_full + 8 * s, pol);
         bulk_g2s(a_smem + s * abytes, asrc + static_cast<size_t>(it) * p.M_pad * 128, abytes,
                  bar_full + 8 * s);
         issued = it + 1;
+        if (it == 0) SABER_STAMP(2);
       }
       if (!ok) {
         // Unwinding: do not leave the CTA while one of its own copies is still in flight.
@@ -123,55 +143,95 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
       bool ok = true;
       for (int it = 0; it < nkb; ++it) {
         const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1;
-        const uint32_t wait_bar = (p.w4 ? bar_ready : bar_full) + 8 * s;
-        if (!mbar_wait(wait_bar, ph, p.err, kErrWaitReady)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint64_t a_desc = make_desc_k128(w_smem + s * 16384u);
         const uint64_t b_desc = make_desc_k128(a_smem + s * abytes);
+        if (p.w4) {
+          const int u = it % kABufs;
+          if (!mbar_wait(bar_ready + 8 * u, (it / kABufs) & 1, p.err, kErrWaitReady)) { ok = false; break; }
+          tc_fence_after_sync();
+          if (it == 0) SABER_STAMP(5);
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) {
-          // 32 int8 = 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units.
-          mma_i8_ss(tmem_d, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (it | k4) != 0 ? 1u : 0u);
+          for (int k4 = 0; k4 < 4; ++k4) {  // K = 32 per MMA: 8 TMEM columns of A, 32 bytes of B
+            if (p.dbg_mma && k4 >= p.dbg_mma) break;
+            const int g = it * 4 + k4;
+            mma_i8_ts(tmem_d + (g % n_acc) * acc_cols, tmem_a + u * 32 + k4 * 8, b_desc + 2 * k4, idesc,
+                      g >= n_acc ? 1u : 0u);
+          }
+          mma_commit(bar_afree + 8 * u);
+        } else {
+          if (!mbar_wait(bar_full + 8 * s, (it / stages) & 1, p.err, kErrWaitReady)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint64_t a_desc = make_desc_k128(w_smem + s * wbytes);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            if (p.dbg_mma && k4 >= p.dbg_mma) break;
+            const int g = it * 4 + k4;
+            mma_i8_ss(tmem_d + (g % n_acc) * acc_cols, a_desc + 2 * k4, b_desc + 2 * k4, idesc,
+                      g >= n_acc ? 1u : 0u);
+          }
         }
         mma_commit(bar_empty + 8 * s);
       }
       if (ok) mma_commit(bar_acc);
+      SABER_STAMP(6);
     }
   } else {
     // ---------------------------------------------------------------- transform, then epilogue
-    const int tid_t = threadIdx.x - 64;  // 0..127
+    const int tid_t = (threadIdx.x - 64) & 127;  // 0..127 inside the group
+    const int tgroup = (threadIdx.x - 64) >> 7;  // the two groups take alternate k-blocks
+    const int q4 = warp & 3;                     // TMEM lane quarter this warp may access
     bool ok = true;
+    if (tgroup == 0) {  // epilogue warps stage the per-token scales while the pipeline fills
+      for (int j = tid_t; j < p.nt; j += 128) a_scale_s[j] = (m0 + j < p.M) ? p.a_scale[m0 + j] : 0.f;
+    }
     if (p.w4) {
-      for (int it = 0; it < nkb; ++it) {
+      // Thread = one weight row: 64 packed bytes in, 32 int8 column words out, straight into the
+      // TMEM A buffer (lane = row).  Packed tile order is [16-byte chunk j][row][16 bytes], so a
+      // warp's loads are contiguous; packed word i carries column word i in its low nibbles and
+      // column word 16 + i in its high nibbles.
+      const int row = q4 * 32 + lane;
+      for (int it = tgroup; it < nkb; it += 2) {
         const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1;
-        if (!mbar_wait(bar_full + 8 * s, ph, p.err, kErrWaitFull)) { ok = false; break; }
-        const uint32_t base = w_smem + s * 16384u;
+        const int u = it % kABufs;
+        if (!mbar_wait(bar_full + 8 * s, (it / stages) & 1, p.err, kErrWaitFull)) { ok = false; break; }
+        if (it == 0 && tid_t == 0) SABER_STAMP(3);
+        const uint32_t base = w_smem + s * wbytes + static_cast<uint32_t>(row) * 16u;
+        uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t off = static_cast<uint32_t>(i * 128 + tid_t) * 16u;
-          uint32_t v0, v1, v2, v3;
+        for (int j = 0; j < 4; ++j)
           asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                       : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
-                       : "r"(base + 8192u + off));
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(base + off),
-                       "r"((v0 << 4) & 0xF0F0F0F0u), "r"((v1 << 4) & 0xF0F0F0F0u),
-                       "r"((v2 << 4) & 0xF0F0F0F0u), "r"((v3 << 4) & 0xF0F0F0F0u)
-                       : "memory");
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(base + 8192u + off),
-                       "r"(v0 & 0xF0F0F0F0u), "r"(v1 & 0xF0F0F0F0u), "r"(v2 & 0xF0F0F0F0u),
-                       "r"(v3 & 0xF0F0F0F0u)
-                       : "memory");
+                       : "=r"(pk[4 * j]), "=r"(pk[4 * j + 1]), "=r"(pk[4 * j + 2]), "=r"(pk[4 * j + 3])
+                       : "r"(base + j * 2048u));
+        uint32_t cols[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          cols[i] = (pk[i] << 4) & 0xF0F0F0F0u;
+          cols[16 + i] = pk[i] & 0xF0F0F0F0u;
         }
-        fence_proxy_async_smem();
-        mbar_arrive(bar_ready + 8 * s);
+        if (!mbar_wait(bar_afree + 8 * u, ((it / kABufs) & 1) ^ 1u, p.err, kErrWaitEmpty)) { ok = false; break; }
+        tc_fence_after_sync();
+        tmem_st32(tmem_a + (static_cast<uint32_t>(q4 * 32) << 16) + u * 32, cols);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_ready + 8 * u);
+        if (it == 0 && tid_t == 0) SABER_STAMP(4);
       }
     }
-    if (ok) ok = mbar_wait(bar_acc, 0, p.err, kErrWaitAcc);
+    if (tgroup == 0) {
+      // the four epilogue warps decide TOGETHER whether to run the epilogue: the named barriers
+      // below have no time limit, so no warp may skip one that the others enter
+      if (ok) ok = mbar_wait(bar_acc, 0, p.err, kErrWaitAcc);
+      if (!ok) abort_s = 1u;
+      named_bar_sync(1, 128);  // also publishes a_scale_s
+      ok = abort_s == 0u;
+    } else {
+      ok = false;  // only the first group (TMEM lane quarters 2,3,0,1) is the epilogue
+    }
     if (ok) {
       tc_fence_after_sync();
-      const int q = warp & 3;  // TMEM lane quarter this warp may read
+      if (tid_t == 0) SABER_STAMP(7);
+      const int q = q4;
+      const int n_live_acc = min(n_acc, nkb * 4);  // accumulators that received at least one MMA
       const int row = q * 32 + lane;
       const int n = tile_n * 128 + row;
       const bool n_ok = n < p.N;
@@ -183,12 +243,19 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
           uint32_t r[16];
           tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c * 16, r);
           tmem_ld_wait();
+          for (int a = 1; a < n_live_acc; ++a) {
+            uint32_t r2[16];
+            tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + a * acc_cols + c * 16, r2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] += r2[j];
+          }
           if (n_ok) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int m = m0 + c * 16 + j;
               if (m < p.M) {
-                const float v = static_cast<float>(static_cast<int32_t>(r[j])) * (p.a_scale[m] * wsn);
+                const float v = static_cast<float>(static_cast<int32_t>(r[j])) * (a_scale_s[c * 16 + j] * wsn);
                 p.out[static_cast<size_t>(m) * p.ldo + n] = __float2bfloat16(v);
               }
             }
@@ -199,6 +266,13 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
           uint32_t r[16];
           tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c * 16, r);
           tmem_ld_wait();
+          for (int a = 1; a < n_live_acc; ++a) {
+            uint32_t r2[16];
+            tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + a * acc_cols + c * 16, r2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] += r2[j];
+          }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int m = m0 + c * 16 + j;
@@ -216,14 +290,20 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
         named_bar_sync(1, 128);
         if (is_last_s) {
           __threadfence();
-          for (int j = 0; j < mt; ++j) {
-            const int m = m0 + j;
-            int32_t* wp = p.ws + static_cast<size_t>(m) * p.N_pad + tile_n * 128 + row;
-            const int32_t acc = __ldcg(wp);
-            *wp = 0;  // the scratch is left zeroed for the next launch
-            if (n_ok) {
-              const float v = static_cast<float>(acc) * (p.a_scale[m] * wsn);
-              p.out[static_cast<size_t>(m) * p.ldo + n] = __float2bfloat16(v);
+          int32_t* wbase = p.ws + static_cast<size_t>(m0) * p.N_pad + tile_n * 128 + row;
+          for (int j0 = 0; j0 < mt; j0 += 16) {
+            int32_t acc[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j)   // independent loads first, then the dependent work
+              acc[j] = (j0 + j < mt) ? __ldcg(wbase + static_cast<size_t>(j0 + j) * p.N_pad) : 0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (j0 + j < mt) {
+                wbase[static_cast<size_t>(j0 + j) * p.N_pad] = 0;  // scratch is left zeroed
+                if (n_ok)
+                  p.out[static_cast<size_t>(m0 + j0 + j) * p.ldo + n] =
+                      __float2bfloat16(static_cast<float>(acc[j]) * (a_scale_s[j0 + j] * wsn));
+              }
             }
           }
           if (tid_t == 0) p.counters[tile_id] = 0u;
@@ -232,15 +312,21 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
     }
   }
 
+  if (threadIdx.x == 64) SABER_STAMP(8);
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_d, tmem_cols);
+  if (threadIdx.x == 32) SABER_STAMP(9);
+#undef SABER_STAMP
 }
 
 }  // namespace saber
 
+extern "C" int saber_gemm_i8_smem_bytes_w(int nt, int stages, int w4) {
+  return stages * ((w4 ? 8192 : 16384) + nt * 128) + 1024;
+}
 extern "C" int saber_gemm_i8_smem_bytes(int nt, int stages) {
-  return stages * (16384 + nt * 128) + 1024;
+  return saber_gemm_i8_smem_bytes_w(nt, stages, 0);
 }
 
 extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cudaStream_t stream) {
@@ -251,17 +337,22 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   const int KB = p->K >> 7;
   const int kb_per = (KB + p->splits - 1) / p->splits;
   if ((p->splits - 1) * kb_per >= KB) return static_cast<int>(cudaErrorInvalidValue);
-  const int kSmemLimit = 226 * 1024;  // opt-in maximum minus the kernel's static shared memory
+  const int kSmemLimit = 224 * 1024;  // opt-in maximum minus the kernel's static shared memory
   if (stages <= 0) {
     // default: small token tiles leave room for two CTAs per SM (one's epilogue overlaps the
     // other's main loop); wide tiles take the whole SM
-    const int budget = p->nt <= 64 ? 112 * 1024 : kSmemLimit;
-    stages = (budget - 1024) / (16384 + p->nt * 128);
+    const int budget = p->nt <= 128 ? 112 * 1024 : kSmemLimit;
+    stages = (budget - 1024) / ((p->w4 ? 8192 : 16384) + p->nt * 128);
   }
   if (stages < 2) stages = 2;
   if (stages > kMaxStages) stages = kMaxStages;
-  while (stages > 2 && saber_gemm_i8_smem_bytes(p->nt, stages) > kSmemLimit) --stages;
-  const int smem = saber_gemm_i8_smem_bytes(p->nt, stages);
+  while (stages > 2 && saber_gemm_i8_smem_bytes_w(p->nt, stages, p->w4) > kSmemLimit) --stages;
+  // The two transform groups take alternate k-blocks; with an even ring depth every stage always
+  // belongs to the same group, so each waiter sees every phase of the barriers it waits on (a
+  // parity wait may lag its barrier by at most one phase).
+  if (p->w4 && (stages & 1)) --stages;
+  if (stages < 2) stages = 2;
+  const int smem = saber_gemm_i8_smem_bytes_w(p->nt, stages, p->w4);
   if (smem > kSmemLimit) return static_cast<int>(cudaErrorInvalidValue);
   static bool configured = false;
   if (!configured) {
@@ -271,6 +362,14 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
     configured = true;
   }
   dim3 grid(p->N_pad / 128, (p->M + p->nt - 1) / p->nt, p->splits);
-  gemm_i8_kernel<<<grid, kGemmThreads, smem, stream>>>(*p, stages);
+  // accumulator count: as many as fit beside the A buffers without exceeding 256 TMEM columns
+  // (two CTAs per SM) for narrow tiles, 512 for wide ones
+  int acc_cols = 32;
+  while (acc_cols < p->nt) acc_cols <<= 1;
+  const int a_cols = p->w4 ? kABufs * 32 : 0;
+  int n_acc = 1;
+  const int budget_cols = (acc_cols <= 64) ? 256 : 512;
+  while (n_acc < 4 && acc_cols * (n_acc + 1) + a_cols <= budget_cols) ++n_acc;
+  gemm_i8_kernel<<<grid, kGemmThreads, smem, stream>>>(*p, stages, n_acc);
   return static_cast<int>(cudaGetLastError());
 }

@@ -21,6 +21,8 @@ struct GemmI8Params {
   int splits;              // split-K factor (gridDim.z)
   int w4;                  // 1: packed int4 tiles, 0: int8 tiles
   int ldo;                 // row stride of out, in elements
+  int dbg_mma;             // debugging only: MMAs issued per k-block (0 = all four)
+  unsigned long long* dbg; // optional: 16 global-timer stamps of CTA (0,0,0) (null = off)
 };
 
 }  // namespace saber

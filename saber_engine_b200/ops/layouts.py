@@ -2,8 +2,9 @@
 
 Weights
     int8 image of one tile = 128 output rows x 128 bytes of K under the 128-byte swizzle
-    (16-byte chunk index XOR (row & 7)); tiles are stored `[n_tile][k_block]`.  A W4 tile is 8 KiB:
-    byte j = (image[j] >> 4) | (image[j + 8192] & 0xF0) where the image holds 16*w.
+    (16-byte chunk index XOR (row & 7)); tiles are stored `[n_tile][k_block]`.  A W4 tile is 8 KiB
+    of nibbles in the order `tile_weight_int4` documents (widened to 16*w by the kernel, straight
+    into tensor memory).
 Activations
     `[k_block][M_pad][128]` int8 with the same swizzle keyed on (m & 7), plus one fp32 scale per row.
 
@@ -69,10 +70,23 @@ def tile_weight_int8(q: torch.Tensor) -> torch.Tensor:
 
 
 def tile_weight_int4(q: torch.Tensor) -> torch.Tensor:
-    """int8 values in [-8, 7], [N, K] -> packed W4 tiles [N_pad/128, K/128, 8192]."""
-    img = tile_weight_int8((q.to(torch.int16) * 16).to(torch.int8))  # image holds 16*w
-    lo, hi = img[..., :8192], img[..., 8192:]
-    return ((lo >> 4) & 0x0F) | (hi & 0xF0)
+    """int8 values in [-8, 7], [N, K] -> packed W4 tiles [N_pad/128, K/128, 8192].
+
+    One tile = 128 rows x 128 k.  A row's 128 int8 values 16*w form 32 little-endian 32-bit "column
+    words" (k = 4c .. 4c+3), the order the tensor core reads an A operand held in tensor memory.
+    Packed word i (i < 16) carries column word i in its low nibbles and column word 16 + i in its
+    high nibbles, so the kernel widens with two mask operations per word.  Tile bytes are stored
+    [16-byte chunk j (4)][row (128)][16], which makes a warp's shared-memory reads contiguous.
+    """
+    N, K = q.shape
+    assert K % TILE_K == 0
+    n_pad = round_up(N, TILE_N)
+    if n_pad != N:
+        q = torch.cat([q, torch.zeros(n_pad - N, K, dtype=q.dtype, device=q.device)], 0)
+    nib = (q.view(torch.uint8) & 0x0F).reshape(n_pad // 128, 128, K // 128, 32, 4)   # [nt, r, kb, c, byte]
+    lo, hi = nib[:, :, :, :16, :], nib[:, :, :, 16:, :]
+    packed = (lo | (hi << 4)).reshape(n_pad // 128, 128, K // 128, 4, 16)             # [nt, r, kb, j, 16]
+    return packed.permute(0, 2, 3, 1, 4).reshape(n_pad // 128, K // 128, 8192).contiguous()
 
 
 def untile_weight_int8(tiles: torch.Tensor, N: int, K: int) -> torch.Tensor:
@@ -83,12 +97,13 @@ def untile_weight_int8(tiles: torch.Tensor, N: int, K: int) -> torch.Tensor:
 
 
 def unpack_weight_int4(tiles: torch.Tensor, N: int, K: int) -> torch.Tensor:
-    """Packed W4 tiles -> int8 values in [-8, 7], [N, K] (for tests)."""
-    lo = (tiles << 4) & 0xF0
-    hi = tiles & 0xF0
-    img = torch.cat([lo, hi], dim=-1)
-    w16 = untile_weight_int8(img, N, K)
-    return (w16.to(torch.int16) // 16).to(torch.int8)
+    """Packed W4 tiles -> int8 values in [-8, 7], [N, K] (for tests and the CPU oracle)."""
+    nt, kb, _ = tiles.shape
+    p = tiles.reshape(nt, kb, 4, 128, 16).permute(0, 3, 1, 2, 4).reshape(nt, 128, kb, 16, 4)  # words i
+    lo = ((p << 4) & 0xF0).view(torch.int8)      # column words 0..15, value 16*w
+    hi = (p & 0xF0).view(torch.int8)             # column words 16..31
+    w16 = torch.cat([lo, hi], dim=3).reshape(nt * 128, kb * 128)[:N, :K]
+    return (w16.to(torch.int16) // 16).to(torch.int8).contiguous()
 
 
 # ------------------------------------------------------------------------------- activations

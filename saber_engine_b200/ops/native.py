@@ -40,7 +40,7 @@ ERR_NAMES = {
 class GemmI8Params(C.Structure):
     _fields_ = [("w", P), ("w_scale", P), ("a", P), ("a_scale", P), ("out", P), ("ws", P),
                 ("counters", P), ("err", P), ("M", I), ("M_pad", I), ("N", I), ("N_pad", I),
-                ("K", I), ("nt", I), ("splits", I), ("w4", I), ("ldo", I)]
+                ("K", I), ("nt", I), ("splits", I), ("w4", I), ("ldo", I), ("dbg_mma", I), ("dbg", P)]
 
 
 class RowOpParams(C.Structure):
@@ -119,6 +119,7 @@ def _declare(L: C.CDLL) -> None:
     sig = {
         "saber_gemm_i8_launch": (I, [C.POINTER(GemmI8Params), I, S]),
         "saber_gemm_i8_smem_bytes": (I, [I, I]),
+        "saber_gemm_i8_smem_bytes_w": (I, [I, I, I]),
         "saber_row_producer_launch": (I, [I, C.POINTER(RowOpParams), S]),
         "saber_embed_gather_launch": (I, [P, P, P, I, I, I, I, I, S]),
         "saber_block_expand_launch": (I, [P, P, P, P, I, I, I, S]),

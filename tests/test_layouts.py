@@ -16,9 +16,15 @@ def test_weight_int4_pack_roundtrip_and_widen_law():
     p = L.tile_weight_int4(q)
     assert p.shape == (1, 2, 8192) and p.dtype == torch.uint8
     assert torch.equal(L.unpack_weight_int4(p, 128, 256), q)
-    # the kernel's widening: low half = (byte << 4) & 0xF0, high half = byte & 0xF0, image = 16*w
-    img = torch.cat([(p << 4) & 0xF0, p & 0xF0], -1)
-    assert torch.equal(L.untile_weight_int8(img, 128, 256).to(torch.int16), q.to(torch.int16) * 16)
+    # the kernel's view: thread = row r reads 16-byte chunk j at j*2048 + r*16; packed word i gives
+    # column word i = (word << 4) & 0xF0F0F0F0 and column word 16+i = word & 0xF0F0F0F0
+    r, kb = 37, 1
+    tile = p[0, kb]
+    words = torch.cat([tile[j * 2048 + r * 16: j * 2048 + r * 16 + 16] for j in range(4)])  # 64 bytes
+    lo = ((words << 4) & 0xF0).view(torch.int8).to(torch.int16)
+    hi = (words & 0xF0).view(torch.int8).to(torch.int16)
+    row16 = torch.cat([lo, hi])                       # 128 int8 values, k order
+    assert torch.equal(row16, q[r, kb * 128:(kb + 1) * 128].to(torch.int16) * 16)
 
 
 def test_swizzle_places_chunk_at_xor_position():
@@ -44,5 +50,5 @@ def test_act_tile_roundtrip_and_quant_law():
 def test_negative_control_nibble_swap_is_caught():
     q = torch.randint(-8, 8, (128, 128), dtype=torch.int8)
     p = L.tile_weight_int4(q)
-    swapped = ((p << 4) & 0xF0) | ((p >> 4) & 0x0F)
+    swapped = ((p << 4) & 0xF0) | ((p >> 4) & 0x0F)   # nibble-swapped pack must not decode
     assert not torch.equal(L.unpack_weight_int4(swapped, 128, 128), q)
