@@ -5,30 +5,38 @@
 // per-token activation scales and per-row weight scales where int4 weights are widened to
 // 16*w int8 (crates/saber-kernels/hip/macaq_iu8.hip:1-25), including its split-K "last arriver
 // reduces" decode form (macaq_iu8.hip:52-150).  The design is not the reference's: it is built
-// for the Blackwell tensor core.
+// around how the Blackwell tensor core spends its time.
 //
-// Shape of the kernel ("swap-AB"): the WEIGHT tile (128 output features x 128 k) is the M=128
-// operand of tcgen05.mma.kind::i8 and the TOKEN tile (nt tokens x 128 k, nt a multiple of 16 up
-// to 256) is the N operand, so a decode step with 1..64 rows wastes no tensor-core rows and a
-// prefill chunk uses nt=256.  Accumulators live in TMEM (128 lanes x nt int32 columns).
+// Orientation.  A tcgen05.mma of shape M x N x 32 bytes takes about M clocks whatever N is (the
+// array is N <= 256 wide and streams the M rows), so a weight-streaming GEMM wants the WEIGHTS on
+// the N side, 256 output features per instruction, and the few token rows on the M side.  Measured
+// on B200: with weights as the M = 128 operand a single CTA retired one 128 x 128-byte k-block
+// per ~0.4 us, capping W4 decode near 4.5 TB/s of packed weights; this orientation halves the
+// tensor time per weight byte.  Token rows beyond the live ones are never loaded: D rows are
+// independent, so whatever shared memory holds there only lands in accumulator rows nobody reads.
 //
 // Warp roles (320 threads):
-//   warp 0    one elected lane streams weight tiles and activation tiles with bulk async copies
-//             (TMA, untiled form: both operands are stored pre-tiled, see below) into a ring of
-//             shared-memory stages, completion counted on an mbarrier per stage.
-//   warp 1    allocates TMEM; one lane issues 4 x tcgen05.mma (K=32 each) per stage and commits
-//             the stage's "empty" barrier, then the accumulator barrier.
-//   warps 2-9 W4 only, two groups of four warps taking alternate k-blocks: widen the packed
-//             int4 stage in place to int8 (see pack law), then fence.proxy.async + arrive on the
-//             stage's "ready" barrier.  Afterwards warps 2-5 are the epilogue: tcgen05.ld their 32 TMEM lanes, scale, store bf16 (direct),
-//             or add int32 partials to the split-K workspace where the last-arriving CTA of a
-//             tile finishes it (exact: integer addition is order-free) and re-zeroes the scratch.
+//   warp 0    one lane streams weight and activation tiles with bulk async copies (TMA, untiled
+//             form: both operands are stored pre-tiled) into a deep ring of stages (packed int4
+//             stages are 16 KiB, so six of them keep ~100 KB of weights in flight per SM),
+//             completion counted on one mbarrier per stage.
+//   warp 1    allocates TMEM (256 int32 columns x 128 lanes); one lane issues 4 x
+//             tcgen05.mma.kind::i8 (K = 32 each) per stage and commits the stage's "empty" barrier.
+//   warps 2-9 W4 only: all eight warps widen a packed int4 stage into one of three int8 operand
+//             buffers (two mask operations per word, conflict-free), then
+//             fence.proxy.async and one elected arrive per warp on the stage's "ready" barrier.
+//             Afterwards warps 2-5 are the epilogue: tcgen05.ld their 32 TMEM lanes (lane = token),
+//             scale, 16-byte bf16 stores (direct), or int32 red.add into the split-K scratch where
+//             the last-arriving CTA of a tile finishes it (exact: integer addition is order-free)
+//             and re-zeroes the scratch.
+//   Loop indices in the single-thread roles advance incrementally: a division by a run-time value
+//   costs that lone thread more than the copy or MMA it is about to issue.
 //
 // Operand storage (no tensor maps needed, every copy is one contiguous 16-byte-aligned span):
-//   weights      [n_tile][k_block][tile]; an int8 tile is the 16 KiB image of 128 rows x 128 bytes
-//                under the 128-byte swizzle (16-byte chunk index XOR (row & 7)).  A W4 tile is
-//                8 KiB: byte j = (image[j] >> 4) | (image[j + 8192] & 0xF0) where image holds
-//                16*w, so widening is two mask operations per word and lands conflict-free.
+//   weights      [n_tile (256 rows)][k_block (128)][tile]; an int8 tile is the 32 KiB image of 256
+//                rows x 128 bytes under the 128-byte swizzle (16-byte chunk index XOR (row & 7)).
+//                A W4 tile is 16 KiB: byte j = (image[j] >> 4) | (image[j + 16384] & 0xF0) where
+//                image holds 16*w.
 //   activations  [k_block][M_pad][128 bytes], the same swizzle keyed on (m & 7); written in that
 //                order by the quantising producers.
 #include "gemm_i8.h"
@@ -37,18 +45,20 @@
 
 namespace saber {
 
-constexpr int kMaxStages = 16;
-constexpr int kABufs = 4;           // W4: int8 A-operand buffers in TMEM (32 columns each)
-constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, two groups of four transform warps
+constexpr int kMaxStages = 12;
+constexpr int kGemmThreads = 320;
+constexpr uint32_t kTileBytes = 32768;   // int8 image of one weight tile (256 x 128)
+constexpr int kUBufs = 3;                // W4: widened int8 operand buffers (transform, MMA and
+                                         // the buffer-free round trip overlap with three)
 
 __global__ void __launch_bounds__(kGemmThreads)
-gemm_i8_kernel(const GemmI8Params p, const int stages, const int n_acc) {
+gemm_i8_kernel(const GemmI8Params p, const int stages) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t bars[2 * kMaxStages + 2 * kABufs + 1];
+  __shared__ uint64_t bars[2 * kMaxStages + 2 * kUBufs + 1];
   __shared__ uint32_t tmem_base_s;
   __shared__ uint32_t is_last_s;
-  __shared__ float a_scale_s[256];
   __shared__ uint32_t abort_s;
+  __shared__ float w_scale_s[256];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -65,70 +75,65 @@ gemm_i8_kernel(const GemmI8Params p, const int stages, const int n_acc) {
   const int kb1 = min(KB, kb0 + kb_per);
   const int nkb = kb1 - kb0;  // host guarantees >= 1
   const int m0 = tile_m * p.nt;
-  const uint32_t wbytes = p.w4 ? 8192u : 16384u;
+  const int n0 = tile_n * 256;
+  const uint32_t wbytes = p.w4 ? 16384u : 32768u;
   const uint32_t abytes = static_cast<uint32_t>(p.nt) * 128u;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t a_smem = smem_base;                                           // stages x abytes
-  const uint32_t w_smem = smem_base + static_cast<uint32_t>(stages) * abytes;  // stages x wbytes
+  // token ring | W4: three int8 operand buffers | weight ring (W4: packed 16 KiB stages, W8: 32 KiB)
+  const uint32_t a_smem = smem_base;
+  const uint32_t u_smem = smem_base + static_cast<uint32_t>(stages) * abytes;
+  const uint32_t w_smem = u_smem + (p.w4 ? kUBufs * kTileBytes : 0u);
   const uint32_t bar_full = smem_u32(&bars[0]);
   const uint32_t bar_empty = smem_u32(&bars[kMaxStages]);
-  const uint32_t bar_ready = smem_u32(&bars[2 * kMaxStages]);           // kABufs
-  const uint32_t bar_afree = smem_u32(&bars[2 * kMaxStages + kABufs]);  // kABufs
-  const uint32_t bar_acc = smem_u32(&bars[2 * kMaxStages + 2 * kABufs]);
-
-  uint32_t acc_cols = 32;
-  while (acc_cols < static_cast<uint32_t>(p.nt)) acc_cols <<= 1;
-  // n_acc independent accumulators: consecutive MMAs then do not wait on one another's result
-  // (a chain of dependent tcgen05.mma into one accumulator pays the full MMA latency per link,
-  // which for narrow token tiles is far longer than the MMA's own work); the epilogue adds them.
-  const uint32_t acc_total = acc_cols * static_cast<uint32_t>(n_acc);
-  uint32_t tmem_cols = 32;
-  while (tmem_cols < acc_total + (p.w4 ? kABufs * 32u : 0u)) tmem_cols <<= 1;
+  const uint32_t bar_ready = smem_u32(&bars[2 * kMaxStages]);           // kUBufs
+  const uint32_t bar_ufree = smem_u32(&bars[2 * kMaxStages + kUBufs]);  // kUBufs
+  const uint32_t bar_acc = smem_u32(&bars[2 * kMaxStages + 2 * kUBufs]);
+  constexpr uint32_t kTmemCols = 256;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int u = 0; u < kABufs; ++u) {
-      mbar_init(bar_ready + 8 * u, 4);  // one arrival per transform warp of the owning group
-      mbar_init(bar_afree + 8 * u, 1);
+    for (int u = 0; u < kUBufs; ++u) {
+      mbar_init(bar_ready + 8 * u, 8);  // one arrival per transform warp
+      mbar_init(bar_ufree + 8 * u, 1);
     }
     mbar_init(bar_acc, 1);
     abort_s = 0;
     mbar_init_fence();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_base_s), tmem_cols);
+    tmem_alloc(smem_u32(&tmem_base_s), kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   if (threadIdx.x == 0) SABER_STAMP(1);
-  const uint32_t tmem_d = tmem_base_s;          // accumulator: columns [0, nt)
-  const uint32_t tmem_a = tmem_base_s + acc_total;  // W4: A buffers, 32 columns each
+  const uint32_t tmem_d = tmem_base_s;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       const uint64_t pol = l2_policy_evict_first();
-      const uint8_t* wsrc = p.w + (static_cast<size_t>(tile_n) * KB + kb0) * wbytes;
-      const int8_t* asrc = p.a + (static_cast<size_t>(kb0) * p.M_pad + m0) * 128;
-      int issued = 0;
+      const uint8_t* wp = p.w + (static_cast<size_t>(tile_n) * KB + kb0) * wbytes;
+      const int8_t* ap = p.a + (static_cast<size_t>(kb0) * p.M_pad + m0) * 128;
+      const size_t a_kb_stride = static_cast<size_t>(p.M_pad) * 128;
+      int issued = 0, s = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int it = 0; it < nkb; ++it) {
-        const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1;
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, p.err, kErrWaitEmpty)) { ok = false; break; }
         mbar_arrive_expect_tx(bar_full + 8 * s, wbytes + abytes);
-        bulk_g2s_hint(w_smem + s * wbytes, wsrc + static_cast<size_t>(it) * wbytes, wbytes,
-                      bar_full + 8 * s, pol);
-        bulk_g2s(a_smem + s * abytes, asrc + static_cast<size_t>(it) * p.M_pad * 128, abytes,
-                 bar_full + 8 * s);
+        bulk_g2s_hint(w_smem + s * wbytes, wp, wbytes, bar_full + 8 * s, pol);
+        bulk_g2s(a_smem + s * abytes, ap, abytes, bar_full + 8 * s);
+        wp += wbytes;
+        ap += a_kb_stride;
         issued = it + 1;
         if (it == 0) SABER_STAMP(2);
+        if (++s == stages) { s = 0; ph ^= 1u; }
       }
       if (!ok) {
         // Unwinding: do not leave the CTA while one of its own copies is still in flight.
@@ -139,82 +144,87 @@ gemm_i8_kernel(const GemmI8Params p, const int stages, const int n_acc) {
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc(kCFmtS32, kFmtS8, kFmtS8, 128, p.nt);
+      // M = 128 token rows (only the first nt are real), N = 256 output features
+      const uint32_t idesc = make_idesc(kCFmtS32, kFmtS8, kFmtS8, 128, 256);
+      const uint64_t desc_hi = make_desc_k128(0);  // everything but the start address
+      uint32_t a_addr = a_smem;
+      int s = 0, u = 0;
+      uint32_t ph = 0, uph = 0;
       bool ok = true;
       for (int it = 0; it < nkb; ++it) {
-        const int s = it % stages;
-        const uint64_t b_desc = make_desc_k128(a_smem + s * abytes);
+        uint32_t w_addr;
         if (p.w4) {
-          const int u = it % kABufs;
-          if (!mbar_wait(bar_ready + 8 * u, (it / kABufs) & 1, p.err, kErrWaitReady)) { ok = false; break; }
-          tc_fence_after_sync();
-          if (it == 0) SABER_STAMP(5);
-#pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {  // K = 32 per MMA: 8 TMEM columns of A, 32 bytes of B
-            if (p.dbg_mma && k4 >= p.dbg_mma) break;
-            const int g = it * 4 + k4;
-            mma_i8_ts(tmem_d + (g % n_acc) * acc_cols, tmem_a + u * 32 + k4 * 8, b_desc + 2 * k4, idesc,
-                      g >= n_acc ? 1u : 0u);
-          }
-          mma_commit(bar_afree + 8 * u);
+          if (!mbar_wait(bar_ready + 8 * u, uph, p.err, kErrWaitReady)) { ok = false; break; }
+          w_addr = u_smem + u * kTileBytes;
         } else {
-          if (!mbar_wait(bar_full + 8 * s, (it / stages) & 1, p.err, kErrWaitReady)) { ok = false; break; }
-          tc_fence_after_sync();
-          const uint64_t a_desc = make_desc_k128(w_smem + s * wbytes);
-#pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4) {
-            if (p.dbg_mma && k4 >= p.dbg_mma) break;
-            const int g = it * 4 + k4;
-            mma_i8_ss(tmem_d + (g % n_acc) * acc_cols, a_desc + 2 * k4, b_desc + 2 * k4, idesc,
-                      g >= n_acc ? 1u : 0u);
-          }
+          if (!mbar_wait(bar_full + 8 * s, ph, p.err, kErrWaitReady)) { ok = false; break; }
+          w_addr = w_smem + s * kTileBytes;
         }
+        tc_fence_after_sync();
+        if (it == 0) SABER_STAMP(5);
+        const uint64_t a_desc = desc_hi | static_cast<uint64_t>((a_addr & 0x3FFFFu) >> 4);
+        const uint64_t b_desc = desc_hi | static_cast<uint64_t>((w_addr & 0x3FFFFu) >> 4);
+        // 32 int8 = 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
+        mma_i8_ss(tmem_d, a_desc, b_desc, idesc, it != 0 ? 1u : 0u);
+        mma_i8_ss(tmem_d, a_desc + 2, b_desc + 2, idesc, 1u);
+        mma_i8_ss(tmem_d, a_desc + 4, b_desc + 4, idesc, 1u);
+        mma_i8_ss(tmem_d, a_desc + 6, b_desc + 6, idesc, 1u);
         mma_commit(bar_empty + 8 * s);
+        if (p.w4) {
+          mma_commit(bar_ufree + 8 * u);
+          if (++u == kUBufs) { u = 0; uph ^= 1u; }
+        }
+        a_addr += abytes;
+        if (++s == stages) { s = 0; ph ^= 1u; a_addr = a_smem; }
       }
       if (ok) mma_commit(bar_acc);
       SABER_STAMP(6);
     }
   } else {
     // ---------------------------------------------------------------- transform, then epilogue
-    const int tid_t = (threadIdx.x - 64) & 127;  // 0..127 inside the group
-    const int tgroup = (threadIdx.x - 64) >> 7;  // the two groups take alternate k-blocks
+    const int tid_t = (threadIdx.x - 64) & 127;  // 0..127: index inside the epilogue group
+    const int tgroup = (threadIdx.x - 64) >> 7;  // 0: warps 2-5 (also the epilogue), 1: warps 6-9
+    const int tid8 = threadIdx.x - 64;           // 0..255 over all eight transform warps
     const int q4 = warp & 3;                     // TMEM lane quarter this warp may access
     bool ok = true;
-    if (tgroup == 0) {  // epilogue warps stage the per-token scales while the pipeline fills
-      for (int j = tid_t; j < p.nt; j += 128) a_scale_s[j] = (m0 + j < p.M) ? p.a_scale[m0 + j] : 0.f;
+    if (tgroup == 0) {  // epilogue warps stage the per-feature scales while the pipeline fills
+      for (int j = tid_t; j < 256; j += 128) w_scale_s[j] = (n0 + j < p.N) ? p.w_scale[n0 + j] : 0.f;
     }
     if (p.w4) {
-      // Thread = one weight row: 64 packed bytes in, 32 int8 column words out, straight into the
-      // TMEM A buffer (lane = row).  Packed tile order is [16-byte chunk j][row][16 bytes], so a
-      // warp's loads are contiguous; packed word i carries column word i in its low nibbles and
-      // column word 16 + i in its high nibbles.
-      const int row = q4 * 32 + lane;
-      for (int it = tgroup; it < nkb; it += 2) {
-        const int s = it % stages;
-        const int u = it % kABufs;
-        if (!mbar_wait(bar_full + 8 * s, (it / stages) & 1, p.err, kErrWaitFull)) { ok = false; break; }
-        if (it == 0 && tid_t == 0) SABER_STAMP(3);
-        const uint32_t base = w_smem + s * wbytes + static_cast<uint32_t>(row) * 16u;
-        uint32_t pk[16];
+      int s = 0, u = 0;
+      uint32_t ph = 0, ufree_ph = 1;
+      for (int it = 0; it < nkb; ++it) {
+        if (!mbar_wait(bar_full + 8 * s, ph, p.err, kErrWaitFull)) { ok = false; break; }
+        if (it == 0 && tid8 == 0) SABER_STAMP(3);
+        const uint32_t src = w_smem + s * wbytes;
+        const uint32_t dst = u_smem + u * kTileBytes;
+        uint32_t v[4][4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t off = static_cast<uint32_t>(i * 256 + tid8) * 16u;
           asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                       : "=r"(pk[4 * j]), "=r"(pk[4 * j + 1]), "=r"(pk[4 * j + 2]), "=r"(pk[4 * j + 3])
-                       : "r"(base + j * 2048u));
-        uint32_t cols[32];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          cols[i] = (pk[i] << 4) & 0xF0F0F0F0u;
-          cols[16 + i] = pk[i] & 0xF0F0F0F0u;
+                       : "=r"(v[i][0]), "=r"(v[i][1]), "=r"(v[i][2]), "=r"(v[i][3])
+                       : "r"(src + off));
         }
-        if (!mbar_wait(bar_afree + 8 * u, ((it / kABufs) & 1) ^ 1u, p.err, kErrWaitEmpty)) { ok = false; break; }
-        tc_fence_after_sync();
-        tmem_st32(tmem_a + (static_cast<uint32_t>(q4 * 32) << 16) + u * 32, cols);
-        tmem_st_wait();
-        tc_fence_before_sync();
+        if (!mbar_wait(bar_ufree + 8 * u, ufree_ph, p.err, kErrWaitEmpty)) { ok = false; break; }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t off = static_cast<uint32_t>(i * 256 + tid8) * 16u;
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + off),
+                       "r"((v[i][0] << 4) & 0xF0F0F0F0u), "r"((v[i][1] << 4) & 0xF0F0F0F0u),
+                       "r"((v[i][2] << 4) & 0xF0F0F0F0u), "r"((v[i][3] << 4) & 0xF0F0F0F0u)
+                       : "memory");
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16384u + off),
+                       "r"(v[i][0] & 0xF0F0F0F0u), "r"(v[i][1] & 0xF0F0F0F0u),
+                       "r"(v[i][2] & 0xF0F0F0F0u), "r"(v[i][3] & 0xF0F0F0F0u)
+                       : "memory");
+        }
+        fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_ready + 8 * u);
-        if (it == 0 && tid_t == 0) SABER_STAMP(4);
+        if (it == 0 && tid8 == 0) SABER_STAMP(4);
+        if (++s == stages) { s = 0; ph ^= 1u; }
+        if (++u == kUBufs) { u = 0; ufree_ph ^= 1u; }
       }
     }
     if (tgroup == 0) {
@@ -222,7 +232,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages, const int n_acc) {
       // below have no time limit, so no warp may skip one that the others enter
       if (ok) ok = mbar_wait(bar_acc, 0, p.err, kErrWaitAcc);
       if (!ok) abort_s = 1u;
-      named_bar_sync(1, 128);  // also publishes a_scale_s
+      named_bar_sync(1, 128);  // also publishes w_scale_s
       ok = abort_s == 0u;
     } else {
       ok = false;  // only the first group (TMEM lane quarters 2,3,0,1) is the epilogue
@@ -230,54 +240,58 @@ gemm_i8_kernel(const GemmI8Params p, const int stages, const int n_acc) {
     if (ok) {
       tc_fence_after_sync();
       if (tid_t == 0) SABER_STAMP(7);
-      const int q = q4;
-      const int n_live_acc = min(n_acc, nkb * 4);  // accumulators that received at least one MMA
-      const int row = q * 32 + lane;
-      const int n = tile_n * 128 + row;
-      const bool n_ok = n < p.N;
-      const float wsn = n_ok ? p.w_scale[n] : 0.f;
-      const int mt = min(p.nt, p.M - m0);  // live token rows of this tile
-      const int nchunks = (mt + 15) >> 4;
+      const int mt = min(p.nt, p.M - m0);   // live token rows of this tile
+      const int row = q4 * 32 + lane;       // token row inside the tile = TMEM lane
+      const int m = m0 + row;
+      const bool live = row < mt;
+      const bool warp_live = q4 * 32 < mt;  // warp-uniform: this lane quarter holds live rows
+      const uint32_t t_lane = tmem_d + (static_cast<uint32_t>(q4 * 32) << 16);
+      const int ncols = min(256, p.N_pad - n0);
       if (p.splits == 1) {
-        for (int c = 0; c < nchunks; ++c) {
-          uint32_t r[16];
-          tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c * 16, r);
-          tmem_ld_wait();
-          for (int a = 1; a < n_live_acc; ++a) {
-            uint32_t r2[16];
-            tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + a * acc_cols + c * 16, r2);
+        if (warp_live) {
+          const float asc = live ? p.a_scale[m] : 0.f;
+          __nv_bfloat16* orow = p.out + static_cast<size_t>(live ? m : m0) * p.ldo + n0;
+          for (int c = 0; c < ncols; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(t_lane + c, r);
             tmem_ld_wait();
+            if (live) {
+              uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] += r2[j];
-          }
-          if (n_ok) {
+              for (int j = 0; j < 16; ++j) {
+                const float lo = static_cast<float>(static_cast<int32_t>(r[2 * j])) * (asc * w_scale_s[c + 2 * j]);
+                const float hi = static_cast<float>(static_cast<int32_t>(r[2 * j + 1])) * (asc * w_scale_s[c + 2 * j + 1]);
+                const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                pk[j] = *reinterpret_cast<const uint32_t*>(&b2);
+              }
+              if (n0 + c + 32 <= p.N) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = m0 + c * 16 + j;
-              if (m < p.M) {
-                const float v = static_cast<float>(static_cast<int32_t>(r[j])) * (a_scale_s[c * 16 + j] * wsn);
-                p.out[static_cast<size_t>(m) * p.ldo + n] = __float2bfloat16(v);
+                for (int j = 0; j < 4; ++j)
+                  *reinterpret_cast<uint4*>(orow + c + 8 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+              } else {
+                const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(pk);
+                for (int j = 0; j < 32; ++j)
+                  if (n0 + c + j < p.N) orow[c + j] = pb[j];
               }
             }
           }
         }
       } else {
-        for (int c = 0; c < nchunks; ++c) {
-          uint32_t r[16];
-          tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + c * 16, r);
-          tmem_ld_wait();
-          for (int a = 1; a < n_live_acc; ++a) {
-            uint32_t r2[16];
-            tmem_ld16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + a * acc_cols + c * 16, r2);
+        // each split writes its own partial tile [split][m][n] with plain vector stores; the
+        // last-arriving CTA of the tile adds the splits (integers: exact in any order)
+        const size_t split_stride = static_cast<size_t>(p.M_pad) * p.N_pad;
+        if (warp_live) {
+          int32_t* wrow = p.ws + split * split_stride + static_cast<size_t>(live ? m : m0) * p.N_pad + n0;
+          for (int c = 0; c < ncols; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(t_lane + c, r);
             tmem_ld_wait();
+            if (live) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] += r2[j];
-          }
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c * 16 + j;
-            if (m < p.M) atomicAdd(p.ws + static_cast<size_t>(m) * p.N_pad + tile_n * 128 + row,
-                                   static_cast<int32_t>(r[j]));
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(wrow + c + 4 * j) =
+                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            }
           }
         }
         __threadfence();
@@ -290,19 +304,59 @@ gemm_i8_kernel(const GemmI8Params p, const int stages, const int n_acc) {
         named_bar_sync(1, 128);
         if (is_last_s) {
           __threadfence();
-          int32_t* wbase = p.ws + static_cast<size_t>(m0) * p.N_pad + tile_n * 128 + row;
-          for (int j0 = 0; j0 < mt; j0 += 16) {
-            int32_t acc[16];
+          // all 128 threads share the tile: a thread takes 8 features of a row at a time, four
+          // such items per round with every load of the round issued before any is used (this
+          // pass runs in ONE CTA while the rest of the grid has left: it is latency that counts)
+          const int vec_per_row = ncols >> 3;
+          const int n_items = mt * vec_per_row;
+          constexpr int kIlp = 4;
+          for (int base = tid_t; base < n_items; base += 128 * kIlp) {
+            int4 x0[kIlp], x1[kIlp];
+            int rr[kIlp], cc[kIlp];
+            float asc[kIlp];
 #pragma unroll
-            for (int j = 0; j < 16; ++j)   // independent loads first, then the dependent work
-              acc[j] = (j0 + j < mt) ? __ldcg(wbase + static_cast<size_t>(j0 + j) * p.N_pad) : 0;
+            for (int u = 0; u < kIlp; ++u) {
+              const int idx = min(base + u * 128, n_items - 1);
+              rr[u] = idx / vec_per_row;
+              cc[u] = (idx - rr[u] * vec_per_row) << 3;
+              x0[u] = make_int4(0, 0, 0, 0);
+              x1[u] = make_int4(0, 0, 0, 0);
+              asc[u] = p.a_scale[m0 + rr[u]];
+            }
+            for (int sp = 0; sp < p.splits; ++sp) {
+              int4 y0[kIlp], y1[kIlp];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (j0 + j < mt) {
-                wbase[static_cast<size_t>(j0 + j) * p.N_pad] = 0;  // scratch is left zeroed
-                if (n_ok)
-                  p.out[static_cast<size_t>(m0 + j0 + j) * p.ldo + n] =
-                      __float2bfloat16(static_cast<float>(acc[j]) * (a_scale_s[j0 + j] * wsn));
+              for (int u = 0; u < kIlp; ++u) {
+                const int32_t* wp = p.ws + sp * split_stride + static_cast<size_t>(m0 + rr[u]) * p.N_pad + n0 + cc[u];
+                y0[u] = __ldcg(reinterpret_cast<const int4*>(wp));
+                y1[u] = __ldcg(reinterpret_cast<const int4*>(wp) + 1);
+              }
+#pragma unroll
+              for (int u = 0; u < kIlp; ++u) {
+                x0[u].x += y0[u].x; x0[u].y += y0[u].y; x0[u].z += y0[u].z; x0[u].w += y0[u].w;
+                x1[u].x += y1[u].x; x1[u].y += y1[u].y; x1[u].z += y1[u].z; x1[u].w += y1[u].w;
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < kIlp; ++u) {
+              if (base + u * 128 >= n_items) break;
+              const int c = cc[u];
+              const int acc[8] = {x0[u].x, x0[u].y, x0[u].z, x0[u].w, x1[u].x, x1[u].y, x1[u].z, x1[u].w};
+              uint32_t pk[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 b2 = __floats2bfloat162_rn(
+                    static_cast<float>(acc[2 * j]) * (asc[u] * w_scale_s[c + 2 * j]),
+                    static_cast<float>(acc[2 * j + 1]) * (asc[u] * w_scale_s[c + 2 * j + 1]));
+                pk[j] = *reinterpret_cast<const uint32_t*>(&b2);
+              }
+              __nv_bfloat16* o = p.out + static_cast<size_t>(m0 + rr[u]) * p.ldo + n0 + c;
+              if (n0 + c + 8 <= p.N) {
+                *reinterpret_cast<uint4*>(o) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              } else {
+                const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(pk);
+                for (int j = 0; j < 8; ++j)
+                  if (n0 + c + j < p.N) o[j] = pb[j];
               }
             }
           }
@@ -315,43 +369,35 @@ gemm_i8_kernel(const GemmI8Params p, const int stages, const int n_acc) {
   if (threadIdx.x == 64) SABER_STAMP(8);
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_d, tmem_cols);
+  if (warp == 1) tmem_dealloc(tmem_d, kTmemCols);
   if (threadIdx.x == 32) SABER_STAMP(9);
 #undef SABER_STAMP
 }
 
 }  // namespace saber
 
-extern "C" int saber_gemm_i8_smem_bytes_w(int nt, int stages, int w4) {
-  return stages * ((w4 ? 8192 : 16384) + nt * 128) + 1024;
-}
 extern "C" int saber_gemm_i8_smem_bytes(int nt, int stages) {
   return saber_gemm_i8_smem_bytes_w(nt, stages, 0);
+}
+// The token-side descriptor spans 128 rows although only nt are loaded: its reads run on into the
+// operand buffers / weight ring, which lie behind the token ring inside the same allocation.
+extern "C" int saber_gemm_i8_smem_bytes_w(int nt, int stages, int w4) {
+  return w4 ? stages * (16384 + nt * 128) + 3 * 32768 + 1024 : stages * (32768 + nt * 128) + 1024;
 }
 
 extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cudaStream_t stream) {
   using namespace saber;
-  if (p->nt < 16 || p->nt > 256 || (p->nt & 15) || (p->K & 127) || p->K <= 0 || p->M <= 0 ||
-      (p->N_pad & 127) || p->splits < 1 || (p->M_pad % p->nt) != 0)
+  if (p->nt < 16 || p->nt > 128 || (p->nt & 15) || (p->K & 127) || p->K <= 0 || p->M <= 0 ||
+      (p->N_pad & 255) || p->splits < 1 || (p->M_pad % p->nt) != 0 || (p->ldo & 7))
     return static_cast<int>(cudaErrorInvalidValue);
   const int KB = p->K >> 7;
   const int kb_per = (KB + p->splits - 1) / p->splits;
   if ((p->splits - 1) * kb_per >= KB) return static_cast<int>(cudaErrorInvalidValue);
   const int kSmemLimit = 224 * 1024;  // opt-in maximum minus the kernel's static shared memory
-  if (stages <= 0) {
-    // default: small token tiles leave room for two CTAs per SM (one's epilogue overlaps the
-    // other's main loop); wide tiles take the whole SM
-    const int budget = p->nt <= 128 ? 112 * 1024 : kSmemLimit;
-    stages = (budget - 1024) / ((p->w4 ? 8192 : 16384) + p->nt * 128);
-  }
+  if (stages <= 0) stages = p->w4 ? 8 : 5;   // one CTA per SM, as deep a ring as fits
   if (stages < 2) stages = 2;
   if (stages > kMaxStages) stages = kMaxStages;
   while (stages > 2 && saber_gemm_i8_smem_bytes_w(p->nt, stages, p->w4) > kSmemLimit) --stages;
-  // The two transform groups take alternate k-blocks; with an even ring depth every stage always
-  // belongs to the same group, so each waiter sees every phase of the barriers it waits on (a
-  // parity wait may lag its barrier by at most one phase).
-  if (p->w4 && (stages & 1)) --stages;
-  if (stages < 2) stages = 2;
   const int smem = saber_gemm_i8_smem_bytes_w(p->nt, stages, p->w4);
   if (smem > kSmemLimit) return static_cast<int>(cudaErrorInvalidValue);
   static bool configured = false;
@@ -361,15 +407,7 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  dim3 grid(p->N_pad / 128, (p->M + p->nt - 1) / p->nt, p->splits);
-  // accumulator count: as many as fit beside the A buffers without exceeding 256 TMEM columns
-  // (two CTAs per SM) for narrow tiles, 512 for wide ones
-  int acc_cols = 32;
-  while (acc_cols < p->nt) acc_cols <<= 1;
-  const int a_cols = p->w4 ? kABufs * 32 : 0;
-  int n_acc = 1;
-  const int budget_cols = (acc_cols <= 64) ? 256 : 512;
-  while (n_acc < 4 && acc_cols * (n_acc + 1) + a_cols <= budget_cols) ++n_acc;
-  gemm_i8_kernel<<<grid, kGemmThreads, smem, stream>>>(*p, stages, n_acc);
+  dim3 grid(p->N_pad / 256, (p->M + p->nt - 1) / p->nt, p->splits);
+  gemm_i8_kernel<<<grid, kGemmThreads, smem, stream>>>(*p, stages);
   return static_cast<int>(cudaGetLastError());
 }

@@ -13,7 +13,7 @@ struct GemmI8Params {
   const int8_t* a;         // pre-tiled activations [K/128][M_pad][128]
   const float* a_scale;    // [M_pad] per token
   __nv_bfloat16* out;      // [M][ldo]
-  int32_t* ws;             // split-K scratch [M_pad][N_pad] int32, all zero between launches
+  int32_t* ws;             // split-K scratch [splits][M_pad][N_pad] int32 (contents do not persist)
   uint32_t* counters;      // split-K arrival counters, one per (m tile, n tile), zero between launches
   uint32_t* err;           // status word: 0, or the code of the first bounded wait that ran out
   int M, M_pad, N, N_pad, K;
@@ -28,4 +28,5 @@ struct GemmI8Params {
 }  // namespace saber
 
 extern "C" int saber_gemm_i8_smem_bytes(int nt, int stages);
+extern "C" int saber_gemm_i8_smem_bytes_w(int nt, int stages, int w4);
 extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cudaStream_t stream);

@@ -168,7 +168,7 @@ class HybridModel:
             if hit is not None:
                 return int(hit.get("splits", 1))
         nt = L.token_tile(a.M)
-        return F.pick_splits(w.N_pad // 128, (a.M + nt - 1) // nt, w.K // 128)
+        return F.pick_splits(w.N_pad // L.TILE_N, (a.M + nt - 1) // nt, w.K // 128)
 
     def gemm_stages(self, w: F.QuantWeight, a: F.QuantAct) -> int:
         table = getattr(self, "tune_table", None)

@@ -20,7 +20,7 @@ from . import native as N
 @dataclass
 class QuantWeight:
     """A linear layer's weight in GEMM-ready form."""
-    tiles: torch.Tensor      # uint8 [N_pad/128, K/128, 8192 | 16384]
+    tiles: torch.Tensor      # uint8 [N_pad/256, K/128, 16384 | 32768]
     scale: torch.Tensor      # fp32 [N_pad] (W4: already divided by 16)
     N: int
     K: int
@@ -28,7 +28,7 @@ class QuantWeight:
 
     @property
     def N_pad(self) -> int:
-        return self.tiles.shape[0] * 128
+        return self.tiles.shape[0] * L.TILE_N
 
     @staticmethod
     def from_float(w: torch.Tensor, bits: int = 4, device=None) -> "QuantWeight":
@@ -39,7 +39,7 @@ class QuantWeight:
     def from_int(q: torch.Tensor, s: torch.Tensor, bits: int, device=None) -> "QuantWeight":
         Nn, K = q.shape
         tiles = L.tile_weight_int4(q) if bits == 4 else L.tile_weight_int8(q)
-        n_pad = tiles.shape[0] * 128
+        n_pad = tiles.shape[0] * L.TILE_N
         sc = torch.zeros(n_pad, dtype=torch.float32)
         sc[:Nn] = s.float() / (16.0 if bits == 4 else 1.0)
         dev = device if device is not None else q.device
@@ -66,10 +66,9 @@ class QuantAct:
 
 
 class GemmScratch:
-    """Split-K scratch of one device: int32 partial sums, arrival counters and the status word.
-
-    The kernels leave the scratch zeroed, so one instance serves every GEMM launched in stream
-    order on the device.
+    """Split-K scratch of one device: int32 partial tiles [split][M_pad][N_pad], arrival counters
+    and the status word.  Partials are overwritten by every launch and counters are left at zero,
+    so one instance serves every GEMM launched in stream order on the device.
     """
 
     def __init__(self, device, max_rows: int = 256, max_cols: int = 262144):
@@ -113,14 +112,15 @@ def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,
     assert a.M_pad % nt == 0
     m_tiles = (a.M + nt - 1) // nt
     if splits is None:
-        splits = pick_splits(w.N_pad // 128, m_tiles, w.K // 128)
+        splits = pick_splits(w.N_pad // L.TILE_N, m_tiles, w.K // 128)
     if splits > 1:
-        assert a.M_pad * w.N_pad <= sc.capacity
+        assert splits * a.M_pad * w.N_pad <= sc.capacity, "split-K scratch too small"
     p = N.GemmI8Params()
     p.w, p.w_scale, p.a, p.a_scale = w.tiles.data_ptr(), w.scale.data_ptr(), a.q.data_ptr(), a.scale.data_ptr()
     p.out, p.ws, p.counters, p.err = out.data_ptr(), sc.ws.data_ptr(), sc.counters.data_ptr(), sc.err.data_ptr()
     p.M, p.M_pad, p.N, p.N_pad, p.K = a.M, a.M_pad, w.N, w.N_pad, w.K
     p.nt, p.splits, p.w4, p.ldo = nt, splits, int(w.w4), out.stride(0)
+    assert out.stride(0) % 8 == 0, "GEMM output rows must be 16-byte aligned"
     return p
 
 

@@ -1,10 +1,9 @@
 """Operand layouts of the tcgen05 integer GEMM and the quantisation laws, in plain torch (CPU or GPU).
 
 Weights
-    int8 image of one tile = 128 output rows x 128 bytes of K under the 128-byte swizzle
-    (16-byte chunk index XOR (row & 7)); tiles are stored `[n_tile][k_block]`.  A W4 tile is 8 KiB
-    of nibbles in the order `tile_weight_int4` documents (widened to 16*w by the kernel, straight
-    into tensor memory).
+    int8 image of one tile = 256 output rows x 128 bytes of K under the 128-byte swizzle
+    (16-byte chunk index XOR (row & 7)); tiles are stored `[n_tile][k_block]`.  A W4 tile is 16 KiB:
+    byte j = (image[j] >> 4) | (image[j + 16384] & 0xF0) where the image holds 16*w.
 Activations
     `[k_block][M_pad][128]` int8 with the same swizzle keyed on (m & 7), plus one fp32 scale per row.
 
@@ -16,7 +15,7 @@ from __future__ import annotations
 
 import torch
 
-TILE_N = 128
+TILE_N = 256          # output features per weight tile (the N side of one MMA)
 TILE_K = 128
 
 
@@ -25,10 +24,10 @@ def round_up(x: int, m: int) -> int:
 
 
 def token_tile(M: int) -> int:
-    """Token-tile width nt the GEMM uses for M rows: a multiple of 16, at most 256."""
-    if M <= 256:
+    """Token-tile width nt the GEMM uses for M rows: a multiple of 16, at most 128."""
+    if M <= 128:
         return max(16, round_up(M, 16))
-    return 256
+    return 128
 
 
 def padded_rows(M: int) -> int:
@@ -47,63 +46,54 @@ def quantize_weight_rows(w: torch.Tensor, bits: int) -> tuple[torch.Tensor, torc
 
 
 def _swizzle_tiles(img: torch.Tensor) -> torch.Tensor:
-    """img [..., 128 rows, 128 bytes] -> same shape with 16-byte chunks XOR-swizzled by row & 7."""
+    """img [..., R rows, 128 bytes] -> same shape with 16-byte chunks XOR-swizzled by row & 7."""
     lead = img.shape[:-2]
-    x = img.reshape(*lead, 128, 8, 16)
-    rows = torch.arange(128, device=img.device) & 7
+    R = img.shape[-2]
+    x = img.reshape(*lead, R, 8, 16)
+    rows = torch.arange(R, device=img.device) & 7
     chunks = torch.arange(8, device=img.device)
     src = (chunks[None, :] ^ rows[:, None])  # physical chunk c' holds logical chunk c' ^ r
-    idx = src[..., None].expand(128, 8, 16)
-    idx = idx.reshape((1,) * len(lead) + (128, 8, 16)).expand(*lead, 128, 8, 16)
-    return torch.gather(x, -2, idx).reshape(*lead, 128, 128)
+    idx = src[..., None].expand(R, 8, 16)
+    idx = idx.reshape((1,) * len(lead) + (R, 8, 16)).expand(*lead, R, 8, 16)
+    return torch.gather(x, -2, idx).reshape(*lead, R, 128)
 
 
 def tile_weight_int8(q: torch.Tensor) -> torch.Tensor:
-    """int8 [N, K] -> uint8 tiles [N_pad/128, K/128, 16384] (the swizzled image of each tile)."""
+    """int8 [N, K] -> uint8 tiles [N_pad/256, K/128, 32768] (the swizzled image of each tile)."""
     N, K = q.shape
     assert K % TILE_K == 0
     n_pad = round_up(N, TILE_N)
     if n_pad != N:
         q = torch.cat([q, torch.zeros(n_pad - N, K, dtype=q.dtype, device=q.device)], 0)
-    t = q.view(torch.uint8).reshape(n_pad // 128, 128, K // 128, 128).permute(0, 2, 1, 3).contiguous()
-    return _swizzle_tiles(t).reshape(n_pad // 128, K // 128, 16384)
+    t = q.view(torch.uint8).reshape(n_pad // TILE_N, TILE_N, K // 128, 128).permute(0, 2, 1, 3).contiguous()
+    return _swizzle_tiles(t).reshape(n_pad // TILE_N, K // 128, TILE_N * 128)
 
 
 def tile_weight_int4(q: torch.Tensor) -> torch.Tensor:
-    """int8 values in [-8, 7], [N, K] -> packed W4 tiles [N_pad/128, K/128, 8192].
+    """int8 values in [-8, 7], [N, K] -> packed W4 tiles [N_pad/256, K/128, 16384].
 
-    One tile = 128 rows x 128 k.  A row's 128 int8 values 16*w form 32 little-endian 32-bit "column
-    words" (k = 4c .. 4c+3), the order the tensor core reads an A operand held in tensor memory.
-    Packed word i (i < 16) carries column word i in its low nibbles and column word 16 + i in its
-    high nibbles, so the kernel widens with two mask operations per word.  Tile bytes are stored
-    [16-byte chunk j (4)][row (128)][16], which makes a warp's shared-memory reads contiguous.
+    The int8 image of a tile holds 16*w; packed byte j = (image[j] >> 4) | (image[j + 16384] & 0xF0),
+    so the kernel widens a stage in place with two mask operations per word: low nibbles rebuild the
+    first half of the image, high nibbles the second half.
     """
-    N, K = q.shape
-    assert K % TILE_K == 0
-    n_pad = round_up(N, TILE_N)
-    if n_pad != N:
-        q = torch.cat([q, torch.zeros(n_pad - N, K, dtype=q.dtype, device=q.device)], 0)
-    nib = (q.view(torch.uint8) & 0x0F).reshape(n_pad // 128, 128, K // 128, 32, 4)   # [nt, r, kb, c, byte]
-    lo, hi = nib[:, :, :, :16, :], nib[:, :, :, 16:, :]
-    packed = (lo | (hi << 4)).reshape(n_pad // 128, 128, K // 128, 4, 16)             # [nt, r, kb, j, 16]
-    return packed.permute(0, 2, 3, 1, 4).reshape(n_pad // 128, K // 128, 8192).contiguous()
+    img = tile_weight_int8((q.to(torch.int16) * 16).to(torch.int8))
+    half = TILE_N * 128 // 2
+    lo, hi = img[..., :half], img[..., half:]
+    return ((lo >> 4) & 0x0F) | (hi & 0xF0)
 
 
 def untile_weight_int8(tiles: torch.Tensor, N: int, K: int) -> torch.Tensor:
     """Inverse of tile_weight_int8 (for tests): tiles -> int8 [N, K]."""
     nt, kb, _ = tiles.shape
-    t = _swizzle_tiles(tiles.reshape(nt, kb, 128, 128))  # the XOR swizzle is an involution
-    return t.permute(0, 2, 1, 3).reshape(nt * 128, kb * 128)[:N, :K].contiguous().view(torch.int8)
+    t = _swizzle_tiles(tiles.reshape(nt, kb, TILE_N, 128))  # the XOR swizzle is an involution
+    return t.permute(0, 2, 1, 3).reshape(nt * TILE_N, kb * 128)[:N, :K].contiguous().view(torch.int8)
 
 
 def unpack_weight_int4(tiles: torch.Tensor, N: int, K: int) -> torch.Tensor:
     """Packed W4 tiles -> int8 values in [-8, 7], [N, K] (for tests and the CPU oracle)."""
-    nt, kb, _ = tiles.shape
-    p = tiles.reshape(nt, kb, 4, 128, 16).permute(0, 3, 1, 2, 4).reshape(nt, 128, kb, 16, 4)  # words i
-    lo = ((p << 4) & 0xF0).view(torch.int8)      # column words 0..15, value 16*w
-    hi = (p & 0xF0).view(torch.int8)             # column words 16..31
-    w16 = torch.cat([lo, hi], dim=3).reshape(nt * 128, kb * 128)[:N, :K]
-    return (w16.to(torch.int16) // 16).to(torch.int8).contiguous()
+    img = torch.cat([(tiles << 4) & 0xF0, tiles & 0xF0], dim=-1)
+    w16 = untile_weight_int8(img, N, K)
+    return (w16.to(torch.int16) // 16).to(torch.int8)
 
 
 # ------------------------------------------------------------------------------- activations

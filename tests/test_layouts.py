@@ -7,28 +7,22 @@ from saber_engine_b200.ops import layouts as L
 def test_weight_int8_tile_roundtrip():
     q = torch.randint(-127, 128, (200, 384), dtype=torch.int8)
     t = L.tile_weight_int8(q)
-    assert t.shape == (2, 3, 16384)
+    assert t.shape == (1, 3, 32768)
     assert torch.equal(L.untile_weight_int8(t, 200, 384), q)
 
 
 def test_weight_int4_pack_roundtrip_and_widen_law():
-    q = torch.randint(-8, 8, (128, 256), dtype=torch.int8)
+    q = torch.randint(-8, 8, (300, 256), dtype=torch.int8)
     p = L.tile_weight_int4(q)
-    assert p.shape == (1, 2, 8192) and p.dtype == torch.uint8
-    assert torch.equal(L.unpack_weight_int4(p, 128, 256), q)
-    # the kernel's view: thread = row r reads 16-byte chunk j at j*2048 + r*16; packed word i gives
-    # column word i = (word << 4) & 0xF0F0F0F0 and column word 16+i = word & 0xF0F0F0F0
-    r, kb = 37, 1
-    tile = p[0, kb]
-    words = torch.cat([tile[j * 2048 + r * 16: j * 2048 + r * 16 + 16] for j in range(4)])  # 64 bytes
-    lo = ((words << 4) & 0xF0).view(torch.int8).to(torch.int16)
-    hi = (words & 0xF0).view(torch.int8).to(torch.int16)
-    row16 = torch.cat([lo, hi])                       # 128 int8 values, k order
-    assert torch.equal(row16, q[r, kb * 128:(kb + 1) * 128].to(torch.int16) * 16)
+    assert p.shape == (2, 2, 16384) and p.dtype == torch.uint8
+    assert torch.equal(L.unpack_weight_int4(p, 300, 256), q)
+    # the kernel's widening: low half = (byte << 4) & 0xF0, high half = byte & 0xF0, image = 16*w
+    img = torch.cat([(p << 4) & 0xF0, p & 0xF0], -1)
+    assert torch.equal(L.untile_weight_int8(img, 300, 256).to(torch.int16), q.to(torch.int16) * 16)
 
 
 def test_swizzle_places_chunk_at_xor_position():
-    q = torch.zeros(128, 128, dtype=torch.int8)
+    q = torch.zeros(256, 128, dtype=torch.int8)
     q[5, 16 * 3] = 77            # row 5, logical chunk 3
     t = L.tile_weight_int8(q)[0, 0]
     off = 5 * 128 + ((3 ^ 5) * 16)
@@ -44,7 +38,7 @@ def test_act_tile_roundtrip_and_quant_law():
     t = L.tile_act_int8(q, 16)
     assert t.shape == (2, 16, 128)
     assert torch.equal(L.untile_act_int8(t, 9), q)
-    assert L.token_tile(9) == 16 and L.token_tile(72) == 80 and L.token_tile(4096) == 256
+    assert L.token_tile(9) == 16 and L.token_tile(72) == 80 and L.token_tile(4096) == 128
 
 
 def test_negative_control_nibble_swap_is_caught():
