@@ -95,14 +95,16 @@ def scratch(device) -> GemmScratch:
 
 
 def pick_splits(n_tiles: int, m_tiles: int, kb: int, sms: int = 148) -> int:
-    """Split-K factor that fills the SMs when the tile grid alone does not."""
+    """Split-K factor that fills the SMs when the tile grid alone does not.  The GEMM runs one CTA
+    per SM, so the target is ONE wave: tiles x splits <= SMs (a second, partial wave costs more
+    than the parallelism gains)."""
     ctas = n_tiles * m_tiles
-    if ctas >= sms or kb < 8:
+    if ctas * 2 > sms or kb < 8:
         return 1
-    s = min(max(1, (2 * sms) // ctas), max(1, kb // 4), 16)
+    s = min(sms // ctas, max(1, kb // 4), 16)
     while s > 1 and (s - 1) * math.ceil(kb / s) >= kb:
         s -= 1
-    return s
+    return max(1, s)
 
 
 def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,

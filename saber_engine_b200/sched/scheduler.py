@@ -1,0 +1,386 @@
+"""Continuous-batching scheduler: admission against the two allocators, prefix-cache reuse, chunked
+prefill at planned rungs, speculative decode steps at a (batch, width) bucket, commit with stop
+rules, one StepEvent per live sequence per step.
+
+Parity: `crates/saber-sched/src/sched.rs:1452-1600` (three phases: prepare under the core lock,
+execute without it, commit under it), `:1924` admit_waiting, `:4190` commit_half, `:4777`
+commit_tokens; implements the serving plane's Engine trait (`:4911-4951` submit).
+"""
+from __future__ import annotations
+
+import itertools
+import threading
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Optional
+
+from ..serve.engine_api import (EngineRefused, EngineRequest, SamplingParams, StepEvent, StepStream,
+                                Submission)
+from . import buckets as B
+from .alloc import Arenas, GdnStateAllocator, OutOfBlocks, PagedKvAllocator
+from .executor import SeqOut, SeqRun
+from .prefix_cache import PrefixCache
+from .width import WidthByBatch
+
+
+@dataclass
+class SchedulerConfig:
+    max_seqs: int = 8
+    max_ctx: int = 262144
+    max_waiting: int = 256
+    prefix_cache: bool = True
+    prefix_cache_bytes: int = 6 << 30
+    prefix_cache_min_tokens: int = 512
+    prefix_cache_interval: int = 1024
+    prefill_pack_seqs: int = 1           # sequences packed in one prefill step
+    width_table: Optional[WidthByBatch] = None
+    model_name: str = "saber"
+
+
+@dataclass
+class Sequence:
+    seq_id: int
+    req: EngineRequest
+    stream: StepStream
+    prompt: list
+    blocks: list = field(default_factory=list)
+    slot: int = 0
+    pos: int = 0                          # tokens whose KV / state are committed
+    output: list = field(default_factory=list)
+    drafts: list = field(default_factory=list)
+    shift: int = 0
+    step_no: int = 0
+    chunks: deque = field(default_factory=deque)   # pending prefill chunks (pos, n)
+    cut_points: set = field(default_factory=set)
+    cached_tokens: int = 0
+    finished: bool = False
+    aborted: bool = False
+    t_submit: float = field(default_factory=time.monotonic)
+    t_first: Optional[float] = None
+    t_admit: Optional[float] = None
+    n_drafted: int = 0
+    n_accepted: int = 0
+
+    @property
+    def prefilling(self) -> bool:
+        return bool(self.chunks)
+
+
+class Scheduler:
+    """Implements Engine over a StepExecutor. `step()` runs one engine step; `spawn_step_loop()`
+    runs steps on a thread until `shutdown()`."""
+
+    def __init__(self, executor, config: Optional[SchedulerConfig] = None, sampler=None):
+        self.ex = executor
+        self.cfg = config or SchedulerConfig(max_seqs=executor.max_seqs)
+        self.cfg.max_seqs = min(self.cfg.max_seqs, executor.max_seqs)
+        self.page = executor.page_tokens
+        kv = PagedKvAllocator(executor.n_kv_blocks, self.page)
+        self.arenas = Arenas(kv, GdnStateAllocator(self.cfg.max_seqs + 1))
+        self.prefix = PrefixCache(kv, self.page, self.cfg.prefix_cache_bytes, self.cfg.prefix_cache_min_tokens,
+                                  self.cfg.prefix_cache_interval, self.cfg.prefix_cache,
+                                  free_snapshot=getattr(executor, "free_snapshot", None))
+        self.width_table = self.cfg.width_table or WidthByBatch(
+            {1: max(executor.decode_widths)}, tuple(sorted(executor.decode_widths)))
+        self.sampler = sampler
+        self.waiting: deque = deque()
+        self.running: list = []
+        self._ids = itertools.count(1)
+        self._lock = threading.Lock()
+        self._wake = threading.Condition(self._lock)
+        self._stop = False
+        self._thread: Optional[threading.Thread] = None
+        self.fatal: Optional[str] = None
+        self.counters = dict(steps=0, prefill_steps=0, decode_steps=0, prompt_tokens=0, generation_tokens=0,
+                             drafts=0, draft_tokens=0, accepted_tokens=0, requests_finished=0,
+                             requests_refused=0, requests_aborted=0, padding_slots=0)
+        self.accepted_per_pos = [0] * 16
+        self.last_step_s = 0.0
+        self.on_step = None                 # optional callback(timing dict) for metrics
+
+    # ------------------------------------------------------------------------------ Engine trait
+    def submit(self, req: EngineRequest) -> Submission:
+        if self.fatal:
+            raise EngineRefused(f"engine is down: {self.fatal}", 503)
+        n = len(req.prompt_token_ids)
+        if n == 0:
+            raise EngineRefused("empty prompt", 400)
+        problems = req.params.validate(self.ex.vocab, self.cfg.max_ctx, n)
+        if problems:
+            raise EngineRefused("; ".join(problems), 400)
+        with self._lock:
+            if len(self.waiting) >= self.cfg.max_waiting:
+                self.counters["requests_refused"] += 1
+                raise EngineRefused("waiting queue is full", 503)
+            seq = Sequence(next(self._ids), req, StepStream(), list(req.prompt_token_ids))
+            self.waiting.append(seq)
+            self._wake.notify_all()
+        return Submission(seq.seq_id, seq.stream)
+
+    def abort(self, seq_id: int) -> None:
+        with self._lock:
+            for s in itertools.chain(self.waiting, self.running):
+                if s.seq_id == seq_id:
+                    s.aborted = True
+            self._wake.notify_all()
+
+    def stats(self) -> dict:
+        with self._lock:
+            return dict(self.counters, running=len(self.running), waiting=len(self.waiting),
+                        kv_free_blocks=self.arenas.kv.free_blocks, kv_total_blocks=self.arenas.kv.n_blocks,
+                        gdn_free_slots=self.arenas.gdn.free_slots, prefix_entries=len(self.prefix),
+                        prefix_hits=self.prefix.stats.hits, prefix_hit_tokens=self.prefix.stats.hit_tokens,
+                        prefix_lookups=self.prefix.stats.lookups, last_step_s=self.last_step_s,
+                        accepted_per_pos=list(self.accepted_per_pos), fatal=self.fatal)
+
+    def model(self) -> dict:
+        return {"id": self.cfg.model_name, "max_model_len": self.cfg.max_ctx, "vocab": self.ex.vocab}
+
+    # ------------------------------------------------------------------------------ phase 1
+    def _drain_aborted(self) -> None:
+        for s in [s for s in self.waiting if s.aborted]:
+            self.waiting.remove(s)
+            self._finish(s, "abort")
+        for s in [s for s in self.running if s.aborted]:
+            self._finish(s, "abort")
+
+    def _admit_waiting(self) -> None:
+        while self.waiting and len(self.running) < self.cfg.max_seqs:
+            s = self.waiting[0]
+            # speculative rows write KV past the last committed token: keep one step of head-room
+            total = len(s.prompt) + s.req.params.max_tokens + max(self.ex.decode_widths)
+            hit = self.prefix.lookup(s.prompt)
+            shared = list(hit.blocks) if hit else []
+            need = self.arenas.kv.blocks_for(total) - len(shared)
+            if not self.arenas.can_admit(total, len(shared)):
+                self.prefix.evict_for_blocks(need)          # cached pages yield to live requests
+                hit = self.prefix.lookup(s.prompt)          # the entry itself may have been evicted
+                shared = list(hit.blocks) if hit else []
+                if not self.arenas.can_admit(total, len(shared)):
+                    if not self.running:                    # can never fit
+                        self.waiting.popleft()
+                        self.counters["requests_refused"] += 1
+                        self._emit(s, StepEvent(s.seq_id, [], True, "error",
+                                                error="request does not fit the KV pool", prompt_tokens=len(s.prompt)))
+                        continue
+                    break
+            self.waiting.popleft()
+            s.blocks, s.slot = self.arenas.admit(total, shared)
+            s.t_admit = time.monotonic()
+            start = 0
+            if hit:
+                self.ex.restore_state(s.slot, hit.snapshot)
+                start = hit.n_tokens
+                s.cached_tokens = start
+            else:
+                self.ex.reset_slot(s.slot)
+            s.pos = start
+            cuts = self.prefix.cut_points(len(s.prompt), start)
+            s.cut_points = set(cuts)
+            s.chunks = deque(B.cut_prompt(len(s.prompt), start, self.ex.prefill_rungs, cuts))
+            self.running.append(s)
+
+    def _plan(self):
+        """Returns ("prefill", [(seq, pos, n)]) | ("decode", seqs, width, batch) | None."""
+        pre = [s for s in self.running if s.prefilling]
+        if pre:
+            picks, rows = [], 0
+            top = max(self.ex.prefill_rungs)
+            for s in pre[: max(1, self.cfg.prefill_pack_seqs)]:
+                pos, n = s.chunks[0]
+                if picks and rows + n > top:
+                    break
+                picks.append((s, pos, n))
+                rows += n
+            return ("prefill", picks)
+        dec = [s for s in self.running if not s.finished]
+        if not dec:
+            return None
+        batch = B.select_batch(len(dec), self.ex.decode_batches)
+        width = self.width_table.width_for(len(dec))
+        return ("decode", dec, width, batch)
+
+    # ------------------------------------------------------------------------------ the step
+    def step(self) -> bool:
+        """One engine step. Returns False when there was nothing to do."""
+        t0 = time.monotonic()
+        with self._lock:
+            self._drain_aborted()
+            self._admit_waiting()
+            plan = self._plan()
+        if plan is None:
+            return False
+        try:
+            if plan[0] == "prefill":
+                runs = [SeqRun(s.seq_id, s.prompt[pos:pos + n], pos, s.slot, 0, s.blocks, uid=s.seq_id,
+                               last_chunk=(pos + n == len(s.prompt)),
+                               temperature=s.req.params.temperature, want_seam=not s.req.params.greedy)
+                        for s, pos, n in plan[1]]
+                outs = self.ex.prefill(runs)
+            else:
+                _, dec, width, batch = plan
+                runs = []
+                for s in dec:
+                    drafts = (s.drafts + [0] * width)[: width - 1]
+                    runs.append(SeqRun(s.seq_id, [s.output[-1]] + drafts, s.pos, s.slot, s.shift, s.blocks,
+                                       uid=s.seq_id, step_no=s.step_no, temperature=s.req.params.temperature,
+                                       want_seam=not s.req.params.greedy))
+                outs = self.ex.decode(runs, width)
+        except Exception as exc:       # the executor failed: every request learns why (fatal law)
+            self.set_fatal(f"executor failed: {exc!r}")
+            raise
+        dt = time.monotonic() - t0
+        with self._lock:
+            if plan[0] == "prefill":
+                self._commit_prefill(plan[1], outs, dt)
+            else:
+                self._commit_decode(plan[1], plan[2], plan[3], outs, dt)
+            self.counters["steps"] += 1
+            self.last_step_s = dt
+        if self.on_step:
+            self.on_step({"kind": plan[0], "seconds": dt, "live": len(plan[1])})
+        return True
+
+    # ------------------------------------------------------------------------------ phase 3
+    def _commit_prefill(self, picks, outs, dt) -> None:
+        self.counters["prefill_steps"] += 1
+        for (s, pos, n), out in zip(picks, outs):
+            s.chunks.popleft()
+            s.pos = pos + n
+            self.counters["prompt_tokens"] += n
+            if s.pos in s.cut_points:
+                snap = self.ex.snapshot_state(s.slot)
+                self.prefix.insert(s.prompt, s.pos, s.blocks, snap, self.ex.snapshot_bytes())
+            if s.pos == len(s.prompt):
+                tok = self._choose(s, out, 0, out.tokens[0] if out.tokens else 0)
+                s.drafts = list(out.drafts)
+                s.shift = 0
+                s.t_first = time.monotonic()
+                self._append(s, [tok], dt, first=True)
+
+    def _commit_decode(self, dec, width, batch, outs, dt) -> None:
+        self.counters["decode_steps"] += 1
+        self.counters["padding_slots"] += batch - len(dec)
+        for s, out in zip(dec, outs):
+            toks = list(out.tokens)
+            if not s.req.params.greedy and self.sampler is not None and out.seam is not None:
+                toks = self._accept_sampled(s, out, width)
+            n = len(toks)
+            self.counters["drafts"] += 1
+            self.counters["draft_tokens"] += width - 1
+            self.counters["accepted_tokens"] += n - 1
+            for k in range(min(n - 1, len(self.accepted_per_pos))):
+                self.accepted_per_pos[k] += 1
+            s.n_drafted += width - 1
+            s.n_accepted += n - 1
+            s.pos += n
+            s.shift = n
+            s.step_no += 1
+            s.drafts = list(out.drafts)
+            self._append(s, toks, dt, drafted=width - 1, accepted=n - 1)
+
+    def _choose(self, s: Sequence, out: SeqOut, row: int, greedy_tok: int) -> int:
+        if s.req.params.greedy or self.sampler is None or out.seam is None:
+            return greedy_tok
+        return self.sampler.sample_row(out.seam, row, s.req.params, s.prompt, s.output, len(s.output), s.seq_id)
+
+    def _accept_sampled(self, s: Sequence, out: SeqOut, width: int) -> list:
+        """Sampled rows: the token at each output position is a function of (seed, position), so the
+        longest draft prefix that matches what the sampler draws is accepted, exactly as in greedy
+        verification (`crates/saber-exec/src/forward.rs:475`, `seeded_invariance.rs:1-20`)."""
+        drafts = (s.drafts + [0] * width)[: width - 1]
+        toks, hist = [], list(s.output)
+        for r in range(width):
+            t = self.sampler.sample_row(out.seam, r, s.req.params, s.prompt, hist, len(hist), s.seq_id)
+            toks.append(t)
+            hist.append(t)
+            if r >= width - 1 or drafts[r] != t:
+                break
+        return toks
+
+    def _append(self, s: Sequence, toks: list, dt: float, first: bool = False, drafted: int = 0,
+                accepted: int = 0) -> None:
+        p = s.req.params
+        kept, reason = [], None
+        for t in toks:
+            kept.append(t)
+            s.output.append(t)
+            if not p.ignore_eos and s.req.eos_token_id is not None and t == s.req.eos_token_id:
+                reason = "stop"
+            elif t in p.stop_token_ids:
+                reason = "stop"
+            elif len(s.output) >= p.max_tokens:
+                reason = "length"
+            if reason:
+                break
+        if len(kept) < len(toks):             # tokens past the stop are not committed
+            s.pos -= len(toks) - len(kept)
+            s.shift = len(kept)
+        self.counters["generation_tokens"] += len(kept)
+        ev = StepEvent(s.seq_id, kept, reason is not None, reason, prompt_tokens=len(s.prompt),
+                       cached_tokens=s.cached_tokens, n_drafted=drafted, n_accepted=accepted,
+                       step_time_s=dt, first_token=first)
+        if reason:
+            self._finish(s, reason, ev)
+        else:
+            self._emit(s, ev)
+
+    def _finish(self, s: Sequence, reason: str, ev: Optional[StepEvent] = None) -> None:
+        if s.finished:
+            return
+        s.finished = True
+        if s in self.running:
+            self.running.remove(s)
+            self.arenas.release(s.blocks, s.slot)
+        if reason == "abort":
+            self.counters["requests_aborted"] += 1
+        else:
+            self.counters["requests_finished"] += 1
+        self._emit(s, ev or StepEvent(s.seq_id, [], True, reason, prompt_tokens=len(s.prompt)))
+
+    def _emit(self, s: Sequence, ev: StepEvent) -> None:
+        s.stream.put(ev)
+
+    # ------------------------------------------------------------------------------ loop / fatal
+    def set_fatal(self, reason: str) -> None:
+        """Teardown law: every queued and in-flight request gets the reason, new ones are refused."""
+        with self._lock:
+            if self.fatal:
+                return
+            self.fatal = reason
+            for s in list(self.waiting) + list(self.running):
+                s.finished = True
+                s.stream.put(StepEvent(s.seq_id, [], True, "error", error=reason, prompt_tokens=len(s.prompt)))
+            self.waiting.clear()
+            self.running.clear()
+            self._wake.notify_all()
+
+    def spawn_step_loop(self) -> threading.Thread:
+        def loop():
+            while True:
+                with self._lock:
+                    while not self._stop and not self.fatal and not self.waiting and not self.running:
+                        self._wake.wait(timeout=0.5)
+                    if self._stop or self.fatal:
+                        return
+                try:
+                    self.step()
+                except Exception:
+                    return
+        self._thread = threading.Thread(target=loop, name="saber-step-loop", daemon=True)
+        self._thread.start()
+        return self._thread
+
+    def shutdown(self) -> None:
+        with self._lock:
+            self._stop = True
+            self._wake.notify_all()
+        if self._thread:
+            self._thread.join(timeout=5)
+
+    def run_until_idle(self, max_steps: int = 100000) -> int:
+        n = 0
+        while n < max_steps and self.step():
+            n += 1
+        return n
