@@ -142,9 +142,10 @@ class HybridModel:
     # ------------------------------------------------------------------------------ state
     def reset_slot(self, slot: int) -> None:
         """Zero the recurrent state of a slot (a new sequence starts from nothing)."""
-        for i in self.gdn_state:
-            self.gdn_state[i][slot].zero_()
-            self.gdn_hist[i][slot].zero_()
+        with torch.cuda.stream(self.stream):     # ordered with the programs, which run on this stream
+            for i in self.gdn_state:
+                self.gdn_state[i][slot].zero_()
+                self.gdn_hist[i][slot].zero_()
 
     def state_bytes(self) -> dict:
         kv = sum(t.numel() for t in self.kv.values())

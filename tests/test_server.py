@@ -1,0 +1,132 @@
+"""HTTP plane over the scheduler + device mock: real ASGI app, streaming and non-streaming."""
+import json
+
+import pytest
+from starlette.testclient import TestClient
+
+from saber_engine_b200.sched.mock import NullExecutor, reference_generation
+from saber_engine_b200.sched.scheduler import Scheduler, SchedulerConfig
+from saber_engine_b200.serve.parse import ReasoningParser, StopStrings, parse_tool_calls
+from saber_engine_b200.serve.server import ServerState, create_app
+from saber_engine_b200.serve.tokenizer import ByteCodec, IncrementalDetok, render_chat
+
+
+class CountingEngine:
+    """Wraps the scheduler and counts the events each request was sent (= engine steps it took)."""
+
+    def __init__(self, inner):
+        self.inner, self.events = inner, {}
+
+    def submit(self, req):
+        sub = self.inner.submit(req)
+        put = sub.events.put
+        def counted(ev, sid=sub.seq_id):
+            self.events[sid] = self.events.get(sid, 0) + 1
+            put(ev)
+        # the scheduler holds the same StepStream object: patch its put
+        sub.events.put = counted
+        self.last = sub.seq_id
+        return sub
+
+    def __getattr__(self, k):
+        return getattr(self.inner, k)
+
+
+@pytest.fixture()
+def client():
+    sched = Scheduler(NullExecutor(seed=2, vocab=300), SchedulerConfig(max_seqs=8, max_ctx=4096, model_name="mock"))
+    sched.spawn_step_loop()
+    eng = CountingEngine(sched)
+    app = create_app(ServerState(eng, ByteCodec(300), model_name="mock", api_keys=["sk-test"]))
+    c = TestClient(app)
+    c.headers.update({"Authorization": "Bearer sk-test"})
+    c.engine = eng
+    yield c
+    sched.shutdown()
+
+
+def test_models_health_auth(client):
+    assert client.get("/health").text == "ok"
+    assert client.get("/v1/models").json()["data"][0]["id"] == "mock"
+    assert client.get("/v1/models", headers={"Authorization": "Bearer nope"}).status_code == 401
+
+
+def test_completion_matches_engine_ids(client):
+    prompt = [1, 2, 3, 4, 5]
+    r = client.post("/v1/completions", json={"model": "mock", "prompt": prompt, "max_tokens": 10, "temperature": 0,
+                                               "ignore_eos": True})
+    assert r.status_code == 200
+    body = r.json()
+    want = ByteCodec(300).decode(reference_generation(prompt, 10, 300))
+    assert body["choices"][0]["text"] == want
+    assert body["usage"] == {"prompt_tokens": 5, "completion_tokens": 10, "total_tokens": 15,
+                             "prompt_tokens_details": {"cached_tokens": 0}}
+    assert body["choices"][0]["finish_reason"] == "length"
+
+
+def test_stream_has_exactly_one_chunk_per_engine_step(client):
+    with client.stream("POST", "/v1/chat/completions", json={
+            "messages": [{"role": "user", "content": "hello"}], "max_tokens": 24, "temperature": 0, "ignore_eos": True,
+            "stream": True, "stream_options": {"include_usage": True}}) as r:
+        assert r.status_code == 200
+        lines = [l for l in r.iter_lines() if l.startswith("data: ")]
+    assert lines[-1] == "data: [DONE]"
+    chunks = [json.loads(l[6:]) for l in lines[:-1]]
+    usage = chunks[-1]
+    assert usage["choices"] == [] and usage["usage"]["completion_tokens"] == 24
+    content_chunks = chunks[:-1]
+    assert len(content_chunks) == client.engine.events[client.engine.last]
+    assert content_chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+    assert content_chunks[-1]["choices"][0]["finish_reason"] == "length"
+    assert len(content_chunks) < 24          # speculation: several tokens per step, still one chunk each
+
+
+def test_request_validation_lists_every_problem(client):
+    r = client.post("/v1/chat/completions", json={"model": "other", "messages": [], "n": 2, "temperature": "hot"})
+    assert r.status_code == 400
+    msg = r.json()["error"]["message"]
+    assert "not served" in msg and "n > 1" in msg and "temperature" in msg and "messages" in msg
+    assert client.post("/v1/completions", json={"prompt": "x", "max_tokens": 100000}).status_code == 400
+    assert client.post("/v1/completions", content=b"not json").status_code == 400
+
+
+def test_metrics_stats_requests(client):
+    client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 5, "temperature": 0, "ignore_eos": True})
+    m = client.get("/metrics").text
+    for fam in ("saber:num_requests_running", "saber:prompt_tokens_total", "saber:generation_tokens_total",
+                "saber:time_to_first_token_seconds_bucket", "saber:inter_token_latency_seconds_count",
+                "saber:spec_decode_num_draft_tokens_total", "saber:request_success_total",
+                'engine="0",model_name="mock"'):
+        assert fam in m, fam
+    s = client.get("/v1/stats").json()
+    assert s["generation_tokens"] >= 5 and "ttft_p50_s" in s
+    ring = client.get("/v1/requests").json()["data"]
+    assert ring and "prompt" not in ring[-1] and ring[-1]["status"] == "length"
+
+
+def test_fatal_turns_into_503(client):
+    client.engine.inner.set_fatal("rank 1 exited with code 86")
+    r = client.post("/v1/completions", json={"prompt": "abc"})
+    assert r.status_code == 503 and "rank 1" in r.json()["error"]["message"]
+    assert client.get("/health").status_code == 503
+
+
+def test_parsers_and_detok():
+    p = ReasoningParser()
+    out = [p.push(t) for t in ["<thi", "nk>plan", " it</th", "ink>\nThe ", "answer"]]
+    assert "".join(o["reasoning"] for o in out) == "plan it"
+    assert "".join(o["content"] for o in out) == "The answer"
+    assert ReasoningParser().push("plain text", final=True)["content"] == "plain text"
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {
+        "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"}}}}}]
+    text = "ok <tool_call>\n<function=get_weather>\n<parameter=city>\nParis\n</parameter>\n<parameter=days>\n3\n</parameter>\n</function>\n</tool_call>"
+    content, calls = parse_tool_calls(text, tools)
+    assert content == "ok" and calls[0]["function"]["name"] == "get_weather"
+    assert json.loads(calls[0]["function"]["arguments"]) == {"city": "Paris", "days": 3}
+    st = StopStrings(["END"])
+    assert st.push("abcE") == "abc" and st.push("ND tail") == "" and st.hit
+    tok = ByteCodec()
+    d = IncrementalDetok(tok)
+    ids = tok.encode("héllo")
+    assert d.push(ids[:2]) == "h" and d.push(ids[2:]) == "éllo"       # never splits a UTF-8 sequence
+    assert "<|im_start|>user\nhi<|im_end|>" in render_chat([{"role": "user", "content": "hi"}])
