@@ -80,6 +80,44 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const AllReduceP
   }
 }
 
+__global__ void __launch_bounds__(1024) pick_merge_kernel(const PickMergeParams p) {
+  const int tid = threadIdx.x;
+  const uint32_t seq = *p.seq_base + static_cast<uint32_t>(p.site) + 1u;
+  const uint32_t par = seq & 1u;
+  const size_t slot = (static_cast<size_t>(par) * p.nranks + p.rank) * p.rows_max;
+  for (int r = tid; r < p.rows; r += blockDim.x) {
+    const unsigned long long w = (static_cast<unsigned long long>(__float_as_uint(p.val[r])) << 32) |
+                                 static_cast<uint32_t>(p.idx[r]);
+    for (int peer = 0; peer < p.nranks; ++peer)
+      if (peer != p.rank) static_cast<unsigned long long*>(p.peer_win[peer])[slot + r] = w;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < p.nranks && tid != p.rank) {
+    st_release_sys(p.peer_flags[tid] + par * p.nranks + p.rank, seq);
+    const uint32_t* f = p.peer_flags[p.rank] + par * p.nranks + tid;
+    const unsigned long long t0 = ar_now_ns();
+    while (static_cast<int32_t>(ld_acquire_sys(f) - seq) < 0) {
+      if (ar_now_ns() - t0 > 1000000000ull) { atomicCAS(p.err, 0u, 5u); break; }
+    }
+  }
+  __syncthreads();
+  const unsigned long long* win = static_cast<const unsigned long long*>(p.peer_win[p.rank]);
+  for (int r = tid; r < p.rows; r += blockDim.x) {
+    float bv = p.val[r];
+    int bi = p.idx[r];
+    for (int src = 0; src < p.nranks; ++src) {
+      if (src == p.rank) continue;
+      const unsigned long long w = __ldcg(win + (static_cast<size_t>(par) * p.nranks + src) * p.rows_max + r);
+      const float v = __uint_as_float(static_cast<uint32_t>(w >> 32));
+      const int i = static_cast<int>(static_cast<uint32_t>(w));
+      if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+    p.val[r] = bv;
+    p.idx[r] = bi;
+  }
+}
+
 __global__ void comm_advance_kernel(uint32_t* seq_base, uint32_t by) { *seq_base += by; }
 
 }  // namespace saber
@@ -95,6 +133,14 @@ extern "C" int saber_allreduce_launch(const saber::AllReduceParams* p, cudaStrea
     return 0;
   }
   allreduce_oneshot_kernel<<<kArBlocks, 512, 0, stream>>>(*p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int saber_pick_merge_launch(const saber::PickMergeParams* p, cudaStream_t stream) {
+  using namespace saber;
+  if (p->nranks < 1 || p->nranks > kMaxRanks || p->rows > p->rows_max) return static_cast<int>(cudaErrorInvalidValue);
+  if (p->nranks == 1) return 0;
+  pick_merge_kernel<<<1, 1024, 0, stream>>>(*p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -121,3 +167,11 @@ extern "C" int saber_dev_malloc(void** out, size_t bytes) {
   return static_cast<int>(cudaMalloc(out, bytes));
 }
 extern "C" int saber_dev_free(void* p) { return static_cast<int>(cudaFree(p)); }
+extern "C" int saber_dev_memset(void* p, int value, size_t bytes) {
+  cudaError_t e = cudaMemset(p, value, bytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(cudaDeviceSynchronize());
+}
+extern "C" int saber_dev_read_u32(const void* p, uint32_t* out) {
+  return static_cast<int>(cudaMemcpy(out, p, 4, cudaMemcpyDeviceToHost));
+}

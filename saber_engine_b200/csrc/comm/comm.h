@@ -32,8 +32,21 @@ struct AllReduceParams {
   uint32_t spin_limit_us;       // 0 = default bound
 };
 
+// Vocab-parallel head: every rank holds (value, id) of its shard's best token per row; the ranks
+// swap them through peer windows and each keeps the global winner (value desc, id asc).
+struct PickMergeParams {
+  int32_t* idx;                 // [rows] in: local pick (global id), out: winner
+  float* val;                   // [rows] in: local value, out: winner's value
+  void* peer_win[kMaxRanks];    // each rank's window: [2][nranks][rows_max] x 8 bytes
+  uint32_t* peer_flags[kMaxRanks];  // each rank's flags: [2][nranks]
+  const uint32_t* seq_base;
+  uint32_t* err;
+  int rows, rows_max, site, nranks, rank;
+};
+
 }  // namespace saber
 
+extern "C" int saber_pick_merge_launch(const saber::PickMergeParams* p, cudaStream_t stream);
 extern "C" int saber_allreduce_launch(const saber::AllReduceParams* p, cudaStream_t stream);
 extern "C" int saber_comm_advance_launch(uint32_t* seq_base, uint32_t by, cudaStream_t stream);
 extern "C" int saber_ipc_get_handle(void* dev_ptr, void* out_handle_64);

@@ -44,9 +44,10 @@ struct OpVerify { saber::VerifyParams p; };
 struct OpMemset { void* dst; int value; size_t bytes; };
 struct OpCopy { void* dst; const void* src; size_t bytes; };
 struct OpAllReduce { saber::AllReduceParams p; };
+struct OpPickMerge { saber::PickMergeParams p; };
 
 using Op = std::variant<OpGemm, OpRow, OpEmbed, OpGdnConv, OpGdnRec, OpRope, OpAttn, OpArgmax,
-                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance>;
+                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge>;
 
 struct Entry {
   Op op;
@@ -87,6 +88,7 @@ int launch(const Op& op, cudaStream_t s) {
         else if constexpr (std::is_same_v<T, OpCopy>)
           return static_cast<int>(cudaMemcpyAsync(o.dst, o.src, o.bytes, cudaMemcpyDeviceToDevice, s));
         else if constexpr (std::is_same_v<T, OpAllReduce>) return saber_allreduce_launch(&o.p, s);
+        else if constexpr (std::is_same_v<T, OpPickMerge>) return saber_pick_merge_launch(&o.p, s);
         else return static_cast<int>(cudaErrorInvalidValue);
       },
       op);
@@ -157,6 +159,9 @@ int saber_program_add_memset(void* h, void* dst, int value, size_t bytes, const 
 }
 int saber_program_add_copy(void* h, void* dst, const void* src, size_t bytes, const char* tag) {
   return add(h, OpCopy{dst, src, bytes}, 1, tag);
+}
+int saber_program_add_pick_merge(void* h, const saber::PickMergeParams* p, const char* tag) {
+  return add(h, OpPickMerge{*p}, p->nranks > 1 ? 1 : 0, tag);
 }
 int saber_program_add_allreduce(void* h, const saber::AllReduceParams* p, const char* tag) {
   return add(h, OpAllReduce{*p}, 1, tag);

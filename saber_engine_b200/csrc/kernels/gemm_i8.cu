@@ -247,6 +247,27 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
       const bool warp_live = q4 * 32 < mt;  // warp-uniform: this lane quarter holds live rows
       const uint32_t t_lane = tmem_d + (static_cast<uint32_t>(q4 * 32) << 16);
       const int ncols = min(256, p.N_pad - n0);
+      // tensor-parallel mode: a finished 16-byte group of outputs goes to every rank's receive
+      // region (slot = parity of the call's sequence number, source = this rank)
+      const bool tp = p.tp_nranks > 1;
+      uint32_t tp_seq = 0, tp_par = 0;
+      if (tp) {
+        tp_seq = *p.tp_seq_base + static_cast<uint32_t>(p.tp_site) + 1u;
+        tp_par = tp_seq & 1u;
+      }
+      auto tp_push16 = [&](int mm, int nn, const uint4& v) {
+        const size_t off = ((static_cast<size_t>(tp_par) * p.tp_nranks + p.tp_rank) * p.tp_rows + mm) * p.tp_ld + nn;
+        for (int peer = 0; peer < p.tp_nranks; ++peer)
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.tp_recv[peer]) + off) = v;
+      };
+      auto tp_signal = [&](int tile_id) {   // called by all 128 epilogue threads after their stores
+        __threadfence_system();
+        named_bar_sync(1, 128);
+        if (tid_t < p.tp_nranks) {
+          uint32_t* f = p.tp_flags[tid_t] + (static_cast<size_t>(tp_par) * p.tp_nranks + p.tp_rank) * kTpMaxTiles + tile_id;
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tp_seq) : "memory");
+        }
+      };
       if (p.splits == 1) {
         if (warp_live) {
           const float asc = live ? p.a_scale[m] : 0.f;
@@ -264,7 +285,12 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
                 const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
                 pk[j] = *reinterpret_cast<const uint32_t*>(&b2);
               }
-              if (n0 + c + 32 <= p.N) {
+              if (tp) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  if (n0 + c + 8 * j < p.N)
+                    tp_push16(m, n0 + c + 8 * j, make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]));
+              } else if (n0 + c + 32 <= p.N) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
                   *reinterpret_cast<uint4*>(orow + c + 8 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
@@ -276,6 +302,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
             }
           }
         }
+        if (tp) tp_signal(tile_m * gridDim.x + tile_n);
       } else {
         // each split writes its own partial tile [split][m][n] with plain vector stores; the
         // last-arriving CTA of the tile adds the splits (integers: exact in any order)
@@ -351,7 +378,9 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
                 pk[j] = *reinterpret_cast<const uint32_t*>(&b2);
               }
               __nv_bfloat16* o = p.out + static_cast<size_t>(m0 + rr[u]) * p.ldo + n0 + c;
-              if (n0 + c + 8 <= p.N) {
+              if (tp) {
+                if (n0 + c < p.N) tp_push16(m0 + rr[u], n0 + c, make_uint4(pk[0], pk[1], pk[2], pk[3]));
+              } else if (n0 + c + 8 <= p.N) {
                 *reinterpret_cast<uint4*>(o) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
               } else {
                 const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(pk);
@@ -361,6 +390,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
             }
           }
           if (tid_t == 0) p.counters[tile_id] = 0u;
+          if (tp) tp_signal(tile_id);
         }
       }
     }
@@ -393,6 +423,11 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   const int KB = p->K >> 7;
   const int kb_per = (KB + p->splits - 1) / p->splits;
   if ((p->splits - 1) * kb_per >= KB) return static_cast<int>(cudaErrorInvalidValue);
+  if (p->tp_nranks > 1) {
+    const int tiles = (p->N_pad / 256) * ((p->M + p->nt - 1) / p->nt);
+    if (p->tp_nranks > 8 || (p->N & 7) || (p->tp_ld & 7) || tiles > kTpMaxTiles || p->M > p->tp_rows)
+      return static_cast<int>(cudaErrorInvalidValue);
+  }
   const int kSmemLimit = 224 * 1024;  // opt-in maximum minus the kernel's static shared memory
   if (stages <= 0) stages = p->w4 ? 8 : 5;   // one CTA per SM, as deep a ring as fits
   if (stages < 2) stages = 2;

@@ -7,6 +7,8 @@
 
 namespace saber {
 
+constexpr int kTpMaxTiles = 64;   // flag words per (parity, source rank): one per (m tile, n tile)
+
 struct GemmI8Params {
   const uint8_t* w;        // pre-tiled weights [N_pad/128][K/128][8 KiB (W4) | 16 KiB (W8)]
   const float* w_scale;    // [N] per output feature; for W4 it already carries the 1/16
@@ -22,6 +24,14 @@ struct GemmI8Params {
   int w4;                  // 1: packed int4 tiles, 0: int8 tiles
   int ldo;                 // row stride of out, in elements
   int dbg_mma;             // debugging only: MMAs issued per k-block (0 = all four)
+  // Tensor-parallel fused epilogue (tp_nranks > 1): the finished tile is not written to `out`
+  // but pushed, as bf16 partial sums, into EVERY rank's receive region over NVLink, followed by
+  // one release flag per (destination, tile); the consumer kernel of the next op waits on the
+  // flags and adds the partials in rank order.
+  void* tp_recv[8];        // each rank's receive region: [2 parity][nranks src][tp_rows][tp_ld] bf16
+  uint32_t* tp_flags[8];   // each rank's flag region:    [2 parity][nranks src][kTpMaxTiles]
+  const uint32_t* tp_seq_base;
+  int tp_nranks, tp_rank, tp_site, tp_rows, tp_ld;
   unsigned long long* dbg; // optional: 16 global-timer stamps of CTA (0,0,0) (null = off)
 };
 

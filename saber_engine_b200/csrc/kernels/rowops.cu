@@ -115,12 +115,52 @@ __global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpPa
   const int nvec = K >> 3;
   float amax = 0.f;
 
+  uint32_t tp_par = 0;
+  if (MODE == kRowAddRms && p.tp_nranks > 1) {
+    // wait for the tiles of this row from every rank: one thread per (source rank, feature tile)
+    const uint32_t seq = *p.tp_seq_base + static_cast<uint32_t>(p.tp_site) + 1u;
+    tp_par = seq & 1u;
+    const int nflags = p.tp_nranks * p.tp_tiles_n;
+    for (int f = threadIdx.x; f < nflags; f += blockDim.x) {
+      const int src = f / p.tp_tiles_n, tn = f - src * p.tp_tiles_n;
+      const int tile_id = (m / p.tp_nt) * p.tp_tiles_n + tn;
+      const uint32_t* flag = p.tp_flags + (static_cast<size_t>(tp_par) * p.tp_nranks + src) * 64 + tile_id;
+      const long long t0 = clock64();
+      uint32_t spins = 0;
+      while (true) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (static_cast<int32_t>(v - seq) >= 0) break;
+        if ((++spins & 1023u) == 0u && clock64() - t0 > kWaitLimitCycles) {
+          if (p.err) atomicCAS(p.err, 0u, static_cast<uint32_t>(kErrWaitPeer));
+          break;
+        }
+      }
+    }
+    __syncthreads();
+  }
   if (MODE == kRowAddRms) {
     float* s = reinterpret_cast<float*>(row_smem + static_cast<size_t>(K) * 2);  // K fp32 after h
     float ss = 0.f;
     for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
       float x[8];
-      if (p.a) load8(p.a + static_cast<size_t>(m) * p.lda + v * 8, x);
+      if (p.tp_nranks > 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = 0.f;
+        for (int src = 0; src < p.tp_nranks; ++src) {   // fixed order: identical sums on every rank
+          const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(
+              p.tp_recv + ((static_cast<size_t>(tp_par) * p.tp_nranks + src) * p.tp_rows + m) * p.tp_ld + v * 8));
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(h2[i]);
+            x[2 * i] += f.x;
+            x[2 * i + 1] += f.y;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = __bfloat162float(__float2bfloat16(x[i]));  // the all-reduced bf16 value
+      } else if (p.a) load8(p.a + static_cast<size_t>(m) * p.lda + v * 8, x);
       else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = 0.f;

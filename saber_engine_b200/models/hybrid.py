@@ -158,9 +158,23 @@ class HybridModel:
     def _qa(self, M: int, K: int) -> F.QuantAct:
         return F.QuantAct.alloc(M, K, self.device)
 
-    def _gemm(self, prog: N.Program, w: F.QuantWeight, a: F.QuantAct, out: torch.Tensor, tag: str) -> None:
+    def _gemm(self, prog: N.Program, w: F.QuantWeight, a: F.QuantAct, out: torch.Tensor, tag: str,
+              tp_site: int = -1) -> None:
+        """tp_site >= 0: a row-parallel GEMM whose epilogue pushes its partial sums to every rank."""
         splits = self.pick_splits(w, a)
-        prog.gemm(F.gemm_params(w, a, out, self.scratch, splits=splits), self.gemm_stages(w, a), tag=tag)
+        p = F.gemm_params(w, a, out, self.scratch, splits=splits)
+        if tp_site >= 0 and self.tp > 1:
+            self.comm.gemm_tp(p, tp_site)
+        prog.gemm(p, self.gemm_stages(w, a), tag=tag)
+
+    def _add_rms(self, prog: N.Program, M: int, tag: str, w, res, qa, delta, tp_site: int = -1, out=None) -> None:
+        """residual += (delta | the all-reduced GEMM output of `tp_site`); norm; int8 quant."""
+        cfg = self.cfg
+        p = F.row_params(M, cfg.hidden, a=delta, res=res, w=w, w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa, out=out)
+        if tp_site >= 0 and self.tp > 1:
+            nt = L.token_tile(M)
+            self.comm.row_tp(p, tp_site, nt, L.round_up(cfg.hidden, L.TILE_N) // L.TILE_N)
+        prog.row(N.ROW_ADD_RMS, p, tag=tag)
 
     def pick_splits(self, w: F.QuantWeight, a: F.QuantAct) -> int:
         table = getattr(self, "tune_table", None)
@@ -235,10 +249,10 @@ class HybridModel:
         prog.embed(self.w.embed, at(lay.ids), h, M, H, 0, cfg.vocab, H, tag="embed")
         first = True
         ar_site = 0
+        pending = -1          # site of the TP GEMM whose pushed output the next add-norm consumes
         for i, lw in enumerate(self.w.layers):
             t = f"L{i}"
-            row(N.ROW_ADD_RMS, M, H, f"{t}.in_norm", a=None if first else delta, res=h, w=lw.in_norm,
-                w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa_h)
+            self._add_rms(prog, M, f"{t}.in_norm", lw.in_norm, h, qa_h, None if first else delta, pending)
             first = False
             if i in taps:
                 prog.copy(tap_buf[taps.index(i)], h, tag=f"{t}.tap")
@@ -258,7 +272,7 @@ class HybridModel:
                 prog.gdn_rec(rp, nseq, self.gdn_vs, tag=f"{t}.gdn.rec")
                 row(N.ROW_GDN_NORM, M, sh.gdn_out_k, f"{t}.gdn.norm_quant", a_f32=gdn_o,
                     b=buf_in[:, C_:], w=lw.gdn_norm, eps=cfg.eps, qa=qa_gdn, ldb=ld_in)
-                self._gemm(prog, lw.mixer_out, qa_gdn, delta, f"{t}.gdn.out_proj")
+                self._gemm(prog, lw.mixer_out, qa_gdn, delta, f"{t}.gdn.out_proj", tp_site=ar_site)
             else:
                 nq, nkv = sh.n_q_heads, sh.n_kv_heads
                 gate = 2 if cfg.attn_out_gate else 1
@@ -282,20 +296,19 @@ class HybridModel:
                         qa=qa_attn, ldb=ld_in)
                 else:
                     row(N.ROW_PLAIN, M, nq * D, f"{t}.attn.quant", a=ao, qa=qa_attn)
-                self._gemm(prog, lw.mixer_out, qa_attn, delta, f"{t}.attn.o_proj")
-            ar_site = self._allreduce(prog, delta, M * H, ar_site, f"{t}.mixer.ar")
-            row(N.ROW_ADD_RMS, M, H, f"{t}.post_norm", a=delta, res=h, w=lw.post_norm,
-                w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa_h)
+                self._gemm(prog, lw.mixer_out, qa_attn, delta, f"{t}.attn.o_proj", tp_site=ar_site)
+            pending, ar_site = (ar_site, ar_site + 1) if self.tp > 1 else (-1, ar_site)
+            self._add_rms(prog, M, f"{t}.post_norm", lw.post_norm, h, qa_h, delta, pending)
             if cfg.moe is None:
                 self._gemm(prog, lw.gate_up, qa_h, gu, f"{t}.mlp.gate_up")
                 row(N.ROW_SILU_MUL, M, sh.ffn_inter, f"{t}.mlp.silu_mul_quant", a=gu, qa=qa_i)
-                self._gemm(prog, lw.down, qa_i, delta, f"{t}.mlp.down")
+                self._gemm(prog, lw.down, qa_i, delta, f"{t}.mlp.down", tp_site=ar_site)
             else:
                 from .moe_block import add_moe_block
                 add_moe_block(self, prog, lw, qa_h, h, delta, M, t, keep)
-            ar_site = self._allreduce(prog, delta, M * H, ar_site, f"{t}.mlp.ar")
+            pending, ar_site = (ar_site, ar_site + 1) if self.tp > 1 else (-1, ar_site)
         self._build_head(prog, kind, nseq, width, M, Mh, lay, at, h, delta, qa_h, tap_buf, taps, keep,
-                         ar_site)
+                         ar_site, pending)
         if cfg.moe is None:
             keep += [gu, qa_i]
         return self._finish_bucket(prog, kind, nseq, width, M, lay, blob, blob_host, keep, capture)
@@ -308,7 +321,7 @@ class HybridModel:
         return site + 1
 
     def _build_head(self, prog, kind, nseq, width, M, Mh, lay, at, h, delta, qa_h, tap_buf, taps, keep,
-                    ar_site) -> None:
+                    ar_site, pending=-1) -> None:
         cfg, sh, dev = self.cfg, self.sh, self.device
         H = cfg.hidden
         decode = kind == "decode"
@@ -326,16 +339,12 @@ class HybridModel:
         logits = torch.zeros(Mh, (sh.vocab + 7) // 8 * 8, dtype=torch.bfloat16, device=dev)
         self._out_views = None
         if decode:
-            prog.row(N.ROW_ADD_RMS, F.row_params(M, H, a=delta, res=h, w=self.w.final_norm,
-                                                 w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa_h),
-                     tag="final_norm")
+            self._add_rms(prog, M, "final_norm", self.w.final_norm, h, qa_h, delta, pending)
             qa_head = qa_h
         else:
             normed = torch.zeros(M, H, dtype=torch.bfloat16, device=dev)
             last = torch.zeros(nseq, H, dtype=torch.bfloat16, device=dev)
-            prog.row(N.ROW_ADD_RMS, F.row_params(M, H, a=delta, res=h, w=self.w.final_norm,
-                                                 w_offset=cfg.norm_offset, eps=cfg.eps, out=normed),
-                     tag="final_norm")
+            self._add_rms(prog, M, "final_norm", self.w.final_norm, h, None, delta, pending, out=normed)
             prog.embed(normed, at(lay.last_rows), last, nseq, H, 0, M, H, tag="gather_last_rows")
             qa_head = self._qa(nseq, H)
             prog.row(N.ROW_PLAIN, F.row_params(nseq, H, a=last, qa=qa_head), tag="head_quant")

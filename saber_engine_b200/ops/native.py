@@ -28,6 +28,7 @@ U64 = C.c_uint64
 MAX_RANKS = 8
 AR_BLOCKS = 32
 SEAM_K = 64
+TP_MAX_TILES = 64
 
 ROW_ADD_RMS, ROW_SILU_MUL, ROW_GATE_SIG, ROW_GDN_NORM, ROW_PLAIN = range(5)
 
@@ -40,13 +41,16 @@ ERR_NAMES = {
 class GemmI8Params(C.Structure):
     _fields_ = [("w", P), ("w_scale", P), ("a", P), ("a_scale", P), ("out", P), ("ws", P),
                 ("counters", P), ("err", P), ("M", I), ("M_pad", I), ("N", I), ("N_pad", I),
-                ("K", I), ("nt", I), ("splits", I), ("w4", I), ("ldo", I), ("dbg_mma", I), ("dbg", P)]
+                ("K", I), ("nt", I), ("splits", I), ("w4", I), ("ldo", I), ("dbg_mma", I), ("tp_recv", P * 8), ("tp_flags", P * 8), ("tp_seq_base", P),
+                ("tp_nranks", I), ("tp_rank", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I), ("dbg", P)]
 
 
 class RowOpParams(C.Structure):
     _fields_ = [("a", P), ("a_f32", P), ("b", P), ("res", P), ("w", P), ("w_offset", F),
                 ("eps", F), ("out", P), ("q", P), ("scale", P), ("M", I), ("M_pad", I), ("K", I),
-                ("lda", I), ("ldb", I), ("ldres", I), ("ldout", I)]
+                ("lda", I), ("ldb", I), ("ldres", I), ("ldout", I), ("tp_recv", P), ("tp_flags", P),
+                ("tp_seq_base", P), ("err", P), ("tp_nranks", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I),
+                ("tp_nt", I), ("tp_tiles_n", I)]
 
 
 class GdnConvParams(C.Structure):
@@ -86,6 +90,11 @@ class AllReduceParams(C.Structure):
     _fields_ = [("inp", P), ("out", P), ("peer_recv", P * MAX_RANKS), ("peer_flags", P * MAX_RANKS),
                 ("seq_base", P), ("err", P), ("n_elems", I), ("max_elems", I), ("site", I),
                 ("nranks", I), ("rank", I), ("spin_limit_us", U32)]
+
+
+class PickMergeParams(C.Structure):
+    _fields_ = [("idx", P), ("val", P), ("peer_win", P * MAX_RANKS), ("peer_flags", P * MAX_RANKS),
+                ("seq_base", P), ("err", P), ("rows", I), ("rows_max", I), ("site", I), ("nranks", I), ("rank", I)]
 
 
 def lib() -> C.CDLL:
@@ -131,12 +140,16 @@ def _declare(L: C.CDLL) -> None:
         "saber_topk_seam_launch": (I, [P, I, I, I, I, P, P, P, P, S]),
         "saber_verify_launch": (I, [C.POINTER(VerifyParams), S]),
         "saber_allreduce_launch": (I, [C.POINTER(AllReduceParams), S]),
+        "saber_pick_merge_launch": (I, [C.POINTER(PickMergeParams), S]),
+        "saber_program_add_pick_merge": (I, [P, C.POINTER(PickMergeParams), C.c_char_p]),
         "saber_comm_advance_launch": (I, [P, U32, S]),
         "saber_ipc_get_handle": (I, [P, P]),
         "saber_ipc_open_handle": (I, [P, C.POINTER(P)]),
         "saber_ipc_close": (I, [P]),
         "saber_dev_malloc": (I, [C.POINTER(P), C.c_size_t]),
         "saber_dev_free": (I, [P]),
+        "saber_dev_memset": (I, [P, I, C.c_size_t]),
+        "saber_dev_read_u32": (I, [P, C.POINTER(U32)]),
         "saber_program_create": (P, []),
         "saber_program_destroy": (None, [P]),
         "saber_program_add_gemm": (I, [P, C.POINTER(GemmI8Params), I, C.c_char_p]),
@@ -259,6 +272,9 @@ class Program:
     def copy(self, dst: torch.Tensor, src: torch.Tensor, tag="copy") -> int:
         nbytes = src.numel() * src.element_size()
         return self._L.saber_program_add_copy(self._h, ptr(dst), ptr(src), nbytes, tag.encode())
+
+    def pick_merge(self, p: "PickMergeParams", tag="pick_merge") -> int:
+        return self._L.saber_program_add_pick_merge(self._h, C.byref(p), tag.encode())
 
     def allreduce(self, p: AllReduceParams, tag="allreduce") -> int:
         return self._L.saber_program_add_allreduce(self._h, C.byref(p), tag.encode())
