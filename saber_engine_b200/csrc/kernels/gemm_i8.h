@@ -7,7 +7,7 @@
 
 namespace saber {
 
-constexpr int kTpMaxTiles = 64;   // flag words per (parity, source rank): one per (m tile, n tile)
+constexpr int kTpMaxTiles = 512;   // flag words per (parity, source rank): one per (m tile, n tile)
 
 struct GemmI8Params {
   const uint8_t* w;        // pre-tiled weights [N_pad/128][K/128][8 KiB (W4) | 16 KiB (W8)]

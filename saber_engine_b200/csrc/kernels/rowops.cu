@@ -12,6 +12,7 @@
 // Quantisation law (per token row): amax = max |h|; scale = amax / 127; q = clamp(rint(h * (127 /
 // amax)), -127, 127); a zero row stores scale 0.  Rows in [M, M_pad) are written as zeros.
 #include "rowops.h"
+#include "gemm_i8.h"
 #include "ptx_sm100.cuh"
 #include <cuda_bf16.h>
 
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpPa
     for (int f = threadIdx.x; f < nflags; f += blockDim.x) {
       const int src = f / p.tp_tiles_n, tn = f - src * p.tp_tiles_n;
       const int tile_id = (m / p.tp_nt) * p.tp_tiles_n + tn;
-      const uint32_t* flag = p.tp_flags + (static_cast<size_t>(tp_par) * p.tp_nranks + src) * 64 + tile_id;
+      const uint32_t* flag = p.tp_flags + (static_cast<size_t>(tp_par) * p.tp_nranks + src) * kTpMaxTiles + tile_id;
       const long long t0 = clock64();
       uint32_t spins = 0;
       while (true) {

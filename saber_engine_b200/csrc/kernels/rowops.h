@@ -30,7 +30,7 @@ struct RowOpParams {
   // ADD_RMS as the consumer of a tensor-parallel GEMM (tp_nranks > 1): instead of reading `a`,
   // wait (bounded) for every rank's tiles of this row and add the bf16 partials in rank order.
   const __nv_bfloat16* tp_recv;   // THIS rank's receive region [2][nranks][tp_rows][tp_ld]
-  const uint32_t* tp_flags;       // THIS rank's flag region    [2][nranks][64]
+  const uint32_t* tp_flags;       // THIS rank's flag region    [2][nranks][kTpMaxTiles]
   const uint32_t* tp_seq_base;
   uint32_t* err;
   int tp_nranks, tp_site, tp_rows, tp_ld, tp_nt, tp_tiles_n;

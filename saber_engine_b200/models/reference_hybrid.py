@@ -32,9 +32,26 @@ def qlinear(x_bf16_rounded: torch.Tensor, w: QuantWeight) -> torch.Tensor:
     return R.gemm_i8(q, s, aq, asc).float()
 
 
+def qlinear_row_parallel(x_bf16_rounded: torch.Tensor, w: QuantWeight, tp: int) -> torch.Tensor:
+    """What `tp` ranks compute for a row-parallel linear: every rank quantises ITS slice of the
+    activations per token, multiplies with its slice of the integers (full-row weight scales),
+    rounds its partial to bf16; the partials are added in fp32 in rank order and rounded once."""
+    if tp == 1:
+        return qlinear(x_bf16_rounded, w)
+    q, s = dequant_linear(w)
+    K = q.shape[1]
+    ks = K // tp
+    acc = torch.zeros(x_bf16_rounded.shape[0], q.shape[0])
+    for r in range(tp):
+        aq, asc = L.quantize_act_rows(x_bf16_rounded[:, r * ks:(r + 1) * ks])
+        acc += R.gemm_i8(q[:, r * ks:(r + 1) * ks], s, aq, asc).float()
+    return R.bf16_round(acc)
+
+
 @torch.no_grad()
-def forward_full(cfg: HybridConfig, w: ModelWeights, ids: torch.Tensor, kv_fp8: bool = True) -> dict:
-    """ids int [T] (one sequence from position 0). Returns logits [T, vocab] and per-layer residuals."""
+def forward_full(cfg: HybridConfig, w: ModelWeights, ids: torch.Tensor, kv_fp8: bool = True, tp: int = 1) -> dict:
+    """ids int [T] (one sequence from position 0). Returns logits [T, vocab] and per-layer residuals.
+    `w` are the UNSHARDED weights; tp > 1 restates the arithmetic of a tensor-parallel run."""
     assert cfg.moe is None, "the dense oracle covers the dense hybrid"
     sh = shard(cfg, 1, 0)
     T = ids.numel()
@@ -73,11 +90,11 @@ def forward_full(cfg: HybridConfig, w: ModelWeights, ids: torch.Tensor, kv_fp8: 
                 kr, v = R.fp8_round(kr), R.fp8_round(v)
             ao = R.bf16_round(R.attention_rows(qr, kr, v, T)).reshape(T, nq * D)
             mix = R.gate_sigmoid(ao, y[:, nq * D:2 * nq * D]) if cfg.attn_out_gate else ao
-        delta = qlinear(mix, lw.mixer_out).to(torch.bfloat16)
+        delta = qlinear_row_parallel(mix, lw.mixer_out, tp).to(torch.bfloat16)
         hb, n = R.add_rms(delta, h.to(torch.bfloat16), lw.post_norm.cpu(), cfg.eps, cfg.norm_offset)
         h = hb.float()
         gu = qlinear(n, lw.gate_up)
-        delta = qlinear(R.silu_mul(gu), lw.down).to(torch.bfloat16)
+        delta = qlinear_row_parallel(R.silu_mul(gu), lw.down, tp).to(torch.bfloat16)
     hb, n = R.add_rms(delta, h.to(torch.bfloat16), w.final_norm.cpu(), cfg.eps, cfg.norm_offset)
     logits = qlinear(n, w.lm_head)
     return {"logits": logits, "taps": taps, "final": n}

@@ -85,6 +85,14 @@ def _quant_on(dev, w: torch.Tensor, bits: int) -> QuantWeight:
     return QuantWeight.from_int(q, s, bits, dev)
 
 
+def _quant_cols(dev, w_full: torch.Tensor, bits: int, c0: int, c1: int) -> QuantWeight:
+    """Row-parallel shard: quantise the FULL rows (one scale per output feature over the whole
+    reduction dim), then keep columns [c0, c1).  Every TP degree therefore holds the same integers
+    and the same scales as TP=1, split along K."""
+    q, s = L.quantize_weight_rows(w_full, bits)
+    return QuantWeight.from_int(q[:, c0:c1].contiguous(), s, bits, dev)
+
+
 def random_init(cfg: HybridConfig, tp: int, rank: int, device, seed: int = 0,
                 std: float = 0.02) -> ModelWeights:
     """Seeded N(0, std) weights quantised into the device layouts.
@@ -121,8 +129,8 @@ def random_init(cfg: HybridConfig, tp: int, rank: int, device, seed: int = 0,
             parts += [rows(wk, sh.kv_head_first * D, nkv * D), rows(wv, sh.kv_head_first * D, nkv * D)]
             mixer_in = _quant_on(dev, torch.cat(parts, 0), linear_bits(cfg, name + ".mixer.in"))
             wo = rand(H, cfg.n_q_heads * D)
-            mixer_out = _quant_on(dev, wo[:, sh.q_head_first * D:(sh.q_head_first + nq) * D].contiguous(),
-                                  linear_bits(cfg, name + ".mixer.out"))
+            mixer_out = _quant_cols(dev, wo, linear_bits(cfg, name + ".mixer.out"),
+                                    sh.q_head_first * D, (sh.q_head_first + nq) * D)
             lw = LayerWeights("attn", vec(H), vec(H), mixer_in, mixer_out,
                               q_norm=vec(D), k_norm=vec(D))
             del wq, wk, wv, wo
@@ -137,8 +145,7 @@ def random_init(cfg: HybridConfig, tp: int, rank: int, device, seed: int = 0,
                      rows(wz, v0 * d, hv * d), rows(wb, v0, hv), rows(wa, v0, hv)]
             mixer_in = _quant_on(dev, torch.cat(parts, 0), linear_bits(cfg, name + ".mixer.in"))
             wo = rand(H, HV * d)
-            mixer_out = _quant_on(dev, wo[:, v0 * d:(v0 + hv) * d].contiguous(),
-                                  linear_bits(cfg, name + ".mixer.out"))
+            mixer_out = _quant_cols(dev, wo, linear_bits(cfg, name + ".mixer.out"), v0 * d, (v0 + hv) * d)
             conv_full = torch.randn(2 * HK * d + HV * d, 4, generator=g, device=dev) * 0.5
             conv = torch.cat([conv_full[k0 * d:(k0 + hk) * d],
                               conv_full[HK * d + k0 * d:HK * d + (k0 + hk) * d],
@@ -155,7 +162,7 @@ def random_init(cfg: HybridConfig, tp: int, rank: int, device, seed: int = 0,
             lw.gate_up = _quant_on(dev, torch.cat([wg[i0:i0 + il], wu[i0:i0 + il]], 0),
                                    linear_bits(cfg, name + ".mlp.gate_up"))
             wd = rand(H, I)
-            lw.down = _quant_on(dev, wd[:, i0:i0 + il].contiguous(), linear_bits(cfg, name + ".mlp.down"))
+            lw.down = _quant_cols(dev, wd, linear_bits(cfg, name + ".mlp.down"), i0, i0 + il)
             del wg, wu, wd
         else:
             from .moe_weights import random_moe_layer

