@@ -1,0 +1,278 @@
+"""The `saber` command: models | serve | engine | explain | tune | pack | probe | bench | tp-gate | gate.
+
+Everything the engine needs arrives as explicit flags or in the plan: no environment variables on
+the engine path (only the model front door reads HOME / XDG_* / SABER_PACKS / HF_ENDPOINT).
+
+Parity: `crates/saber-cli/src/main.rs:153-3603` (subcommands), `:22-28` (no env on the engine path),
+`docs/MODELS.md:8-17` (front door), `crates/saber-cli/src/explain.rs`.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+
+def _ints(s: str) -> tuple:
+    return tuple(int(x) for x in s.split(",") if x)
+
+
+# ------------------------------------------------------------------------------------------ models
+def cmd_models(a) -> int:
+    from ..registry import registry as R
+    try:
+        reg = R.load()
+        if a.action == "list":
+            rows = []
+            for m in reg.models.values():
+                rows.append({"name": m.name, "kind": m.kind, "aliases": m.aliases, "tp": sorted(m.tp),
+                             "present": {t: (R.pack_dir(m, t, a.packs_dir) / "manifest.json").exists() for t in m.tp},
+                             "default": m.name == reg.default})
+            if a.json:
+                print(json.dumps(rows, indent=1))
+            else:
+                for r in rows:
+                    have = ",".join(f"tp{t}" for t, ok in r["present"].items() if ok) or "-"
+                    print(f"{'*' if r['default'] else ' '} {r['name']:34s} {r['kind']:8s} tp {r['tp']}  on disk: {have}  aliases: {', '.join(r['aliases'])}")
+        elif a.action == "info":
+            m = reg.resolve(a.name)
+            d = {"name": m.name, "kind": m.kind, "description": m.description, "repo": m.repo, "license": m.license,
+                 "requires_tag": m.requires_tag, "drafter": m.drafter,
+                 "tp": {t: vars(e) | {"pack_dir": str(R.pack_dir(m, t, a.packs_dir))} for t, e in m.tp.items()}}
+            print(json.dumps(d, indent=1, default=str) if a.json else "\n".join(f"{k}: {v}" for k, v in d.items()))
+        elif a.action == "pull":
+            print(json.dumps(R.pull(reg, a.name, a.tp, a.packs_dir, a.dry_run), indent=1))
+        elif a.action == "rm":
+            for p in R.remove(reg, a.name, a.tp, a.packs_dir, a.dry_run):
+                print(("would remove " if a.dry_run else "removed ") + p)
+        return 0
+    except R.RegistryError as exc:
+        for p in exc.problems:
+            print(f"saber: {p}", file=sys.stderr)
+        return 2
+
+
+# ------------------------------------------------------------------------------------------ serve
+def cmd_serve(a, extra) -> int:
+    from ..registry import registry as R
+    try:
+        plan = R.plan_serve(R.load(), a.model, a.tp, a.port, a.packs_dir, extra)
+    except R.RegistryError as exc:
+        for p in exc.problems:
+            print(f"saber: {p}", file=sys.stderr)
+        return 2
+    if a.print_argv:
+        print(" ".join(plan["argv"]))
+        return 0
+    if a.dry_run:
+        print(json.dumps(plan, indent=1))
+        return 0
+    argv = plan["argv"][1:]
+    if not plan["pack_present"] and not a.random_init:
+        print(f"saber: no pack at {plan['pack_dir']} (pull it, or pass --random-init to serve seeded random weights)",
+              file=sys.stderr)
+        return 2
+    if a.random_init:
+        argv += ["--random-init"]
+    return main(argv)
+
+
+def build_engine(a):
+    """Executor + scheduler for `saber engine` (also used by tests)."""
+    from ..sched.scheduler import Scheduler, SchedulerConfig
+    from ..serve.sampler import HostSampler
+    if a.engine == "mock":
+        from ..sched.mock import NullExecutor
+        ex = NullExecutor(vocab=a.mock_vocab, max_seqs=a.engine_max_seqs, decode_widths=_ints(a.engine_decode_widths),
+                          decode_batches=_ints(a.engine_decode_batches))
+    elif a.engine == "tiny":
+        from ..models.tiny_qwen3 import TinyExecutor
+        ex = TinyExecutor(max_seqs=a.engine_max_seqs)
+    else:
+        import torch
+        from ..models import config as MC
+        from ..models.hybrid import HybridModel
+        from ..runtime.hybrid_executor import HybridExecutor
+        cfg = MC.by_name(a.engine_config)
+        weights = None
+        if a.pack and not a.random_init:
+            from ..pack.build import load_weights
+            weights = load_weights(a.pack, cfg, a.engine_tp, 0, "cuda")
+        widths = _ints(a.engine_decode_widths)
+        model = HybridModel(cfg, tp=a.engine_tp, rank=0, device="cuda", max_seqs=a.engine_max_seqs,
+                            max_ctx=a.engine_max_ctx, kv_blocks=a.engine_kv_blocks or None, max_width=max(widths),
+                            weights=weights, seed=a.seed)
+        if a.autotune:
+            from ..plan.autotune import TuneTable
+            model.tune_table = TuneTable.load(a.autotune)
+        ex = HybridExecutor(model, _ints(a.engine_decode_batches), widths, _ints(a.engine_prefill_rows),
+                            prebuild=a.prebuild)
+    cfg_s = SchedulerConfig(max_seqs=a.engine_max_seqs, max_ctx=a.engine_max_ctx, prefix_cache=not a.no_prefix_cache,
+                            prefix_cache_bytes=a.prefix_cache_host_mib << 20, model_name=a.served_model_name)
+    return ex, Scheduler(ex, cfg_s, sampler=HostSampler())
+
+
+def cmd_engine(a) -> int:
+    import uvicorn
+    from ..serve.server import ServerState, create_app
+    from ..serve.tokenizer import ByteCodec, HfTokenizer
+    ex, sched = build_engine(a)
+    tok = HfTokenizer(str(Path(a.tokenizer).parent)) if a.tokenizer and Path(a.tokenizer).exists() else ByteCodec(ex.vocab)
+    template = Path(a.chat_template).read_text() if a.chat_template and Path(a.chat_template).exists() else None
+    state = ServerState(sched, tok, a.served_model_name, api_keys=a.api_key or (), chat_template=template,
+                        census_fn=(lambda: dict(getattr(ex, "census", {}))))
+    sched.spawn_step_loop()
+    try:
+        uvicorn.run(create_app(state), host=a.host, port=a.port, log_level="warning")
+    finally:
+        sched.shutdown()
+    return 0
+
+
+# ------------------------------------------------------------------------------------------ plan
+def cmd_explain(a) -> int:
+    from ..plan import launch_plan as LP
+    try:
+        man = LP.Manifest.from_toml(Path(a.manifest).read_text()) if a.manifest else LP.Manifest(
+            model=a.model, tp=a.tp, allow_untuned=True, autotune=a.autotune)
+        plan = LP.resolve(man, LP.DeviceProfile.measured())
+        print(plan.explain())
+        if a.bind:
+            LP.bind(plan)
+        return 0
+    except LP.PlanError as exc:
+        for p in exc.problems:
+            print(f"saber: {p}", file=sys.stderr)
+        return 2
+
+
+def cmd_tune(a) -> int:
+    from ..plan import tune_gemm
+    return tune_gemm.main(["--model", a.model, "--tp", str(a.tp), "--rows", a.rows, "--out", a.out])
+
+
+def cmd_pack(a) -> int:
+    from ..pack import format as PF
+    if a.action == "build":
+        from ..models import config as MC
+        from ..pack.build import write_pack
+        d = write_pack(MC.by_name(a.model), a.out, a.tp, a.seed, a.device)
+        print(d)
+        return 0
+    problems = PF.check_manifest(a.dir)
+    for p in problems:
+        print(f"saber: {p}", file=sys.stderr)
+    print("pack ok" if not problems else f"{len(problems)} problems")
+    return 1 if problems else 0
+
+
+def cmd_probe(a) -> int:
+    import torch
+    info = {"cuda": torch.cuda.is_available(), "gpus": torch.cuda.device_count() if torch.cuda.is_available() else 0}
+    if info["cuda"]:
+        p = torch.cuda.get_device_properties(0)
+        info.update(name=p.name, sms=p.multi_processor_count, mem_gib=round(p.total_memory / 2 ** 30, 1),
+                    capability=f"{p.major}.{p.minor}")
+    from ..ops import native
+    info["native_library"] = native.available()
+    print(json.dumps(info, indent=1))
+    return 0
+
+
+def cmd_gate(a) -> int:
+    import pytest
+    return pytest.main(["-q", "-m", "gpu", str(Path(__file__).resolve().parents[2] / "tests")] + (["-k", a.k] if a.k else []))
+
+
+def make_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="saber")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    m = sub.add_parser("models")
+    m.add_argument("action", nargs="?", default="list", choices=["list", "info", "pull", "rm"])
+    m.add_argument("name", nargs="?")
+    m.add_argument("--tp", type=int)
+    m.add_argument("--json", action="store_true")
+    m.add_argument("--dry-run", action="store_true")
+    m.add_argument("--yes", action="store_true")
+    m.add_argument("--packs-dir")
+    s = sub.add_parser("serve")
+    s.add_argument("--model")
+    s.add_argument("--tp", type=int)
+    s.add_argument("--port", type=int, default=8000)
+    s.add_argument("--dry-run", action="store_true")
+    s.add_argument("--print-argv", action="store_true")
+    s.add_argument("--packs-dir")
+    s.add_argument("--random-init", action="store_true")
+    e = sub.add_parser("engine")
+    e.add_argument("--engine", default="real", choices=["real", "mock", "tiny"])
+    e.add_argument("--engine-tp", type=int, default=1)
+    e.add_argument("--pack")
+    e.add_argument("--engine-config", default="qwen38-27b")
+    e.add_argument("--engine-max-ctx", type=int, default=262144)
+    e.add_argument("--engine-max-seqs", type=int, default=8)
+    e.add_argument("--engine-prefill-rows", default="128,512,2048")
+    e.add_argument("--engine-decode-batches", default="1,2,3,4,8")
+    e.add_argument("--engine-decode-widths", default="1,5,9")
+    e.add_argument("--engine-draft-block", type=int, default=8)
+    e.add_argument("--engine-budget-mib", type=int, default=160000)
+    e.add_argument("--engine-kv-blocks", type=int, default=0)
+    e.add_argument("--served-model-name", default="saber")
+    e.add_argument("--host", default="127.0.0.1")
+    e.add_argument("--port", type=int, default=8000)
+    e.add_argument("--tokenizer")
+    e.add_argument("--chat-template")
+    e.add_argument("--api-key", action="append")
+    e.add_argument("--no-prefix-cache", action="store_true")
+    e.add_argument("--prefix-cache-host-mib", type=int, default=6144)
+    e.add_argument("--autotune")
+    e.add_argument("--random-init", action="store_true")
+    e.add_argument("--prebuild", action="store_true")
+    e.add_argument("--seed", type=int, default=0)
+    e.add_argument("--mock-vocab", type=int, default=1024)
+    x = sub.add_parser("explain")
+    x.add_argument("--manifest")
+    x.add_argument("--model", default="qwen38-27b")
+    x.add_argument("--tp", type=int, default=1)
+    x.add_argument("--autotune")
+    x.add_argument("--bind", action="store_true")
+    t = sub.add_parser("tune")
+    t.add_argument("--model", default="qwen38-27b")
+    t.add_argument("--tp", type=int, default=1)
+    t.add_argument("--rows", default="9,72")
+    t.add_argument("--out", default="autotune.json")
+    p = sub.add_parser("pack")
+    p.add_argument("action", choices=["build", "check"])
+    p.add_argument("--model", default="hybrid-mini")
+    p.add_argument("--tp", type=int, default=1)
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--out", default="packs")
+    p.add_argument("--dir")
+    p.add_argument("--device", default="cpu")
+    sub.add_parser("probe")
+    g = sub.add_parser("gate")
+    g.add_argument("-k")
+    return ap
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    ap = make_parser()
+    if argv and argv[0] == "serve":
+        a, extra = ap.parse_known_args(argv)
+        return cmd_serve(a, extra)
+    if argv and argv[0] == "bench":
+        import runpy
+        sys.argv = ["bench.py"] + argv[1:]
+        runpy.run_path(str(Path(__file__).resolve().parents[2] / "bench.py"), run_name="__main__")
+        return 0
+    if argv and argv[0] == "tp-gate":
+        from ..parallel import tp_gate
+        return tp_gate.main(argv[1:])
+    a = ap.parse_args(argv)
+    return {"models": cmd_models, "engine": cmd_engine, "explain": cmd_explain, "tune": cmd_tune,
+            "pack": cmd_pack, "probe": cmd_probe, "gate": cmd_gate}[a.cmd](a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

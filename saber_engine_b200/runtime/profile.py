@@ -50,3 +50,42 @@ def format_profile(p: dict) -> str:
         lines.append(f"  {r['op']:28s} {r['ms']:9.3f} ms  x{r['count']:<4d} {100 * r['share']:5.1f}%"
                      f"  ({1e3 * r['ms'] / r['count']:8.1f} us each)")
     return "\n".join(lines)
+
+
+def main(argv=None) -> int:
+    """`python -m saber_engine_b200.runtime.profile --batch 8`: build the model, replay the decode
+    bucket a few times and bracket ONE replay with cudaProfilerStart/Stop (for
+    `ncu --profile-from-start off`), or print the eager per-op walk with --walk."""
+    import argparse
+    from ..models import config as C
+    from ..models.hybrid import SeqStep, run_bucket
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="qwen38-27b")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--width", type=int, default=9)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--walk", action="store_true")
+    args = ap.parse_args(argv)
+    cfg = C.by_name(args.model)
+    model = HybridModel(cfg, device="cuda", max_seqs=args.batch, max_ctx=args.ctx + 512, max_width=args.width,
+                        seed=1, oracle_p=0.75)
+    bp = (args.ctx + 512) // cfg.page_tokens
+    b = model.build_bucket("decode", args.batch, args.width)
+    seqs = [SeqStep([1] * args.width, args.ctx, j + 1, 3, list(range(1 + j * bp, 1 + (j + 1) * bp)), uid=j)
+            for j in range(args.batch)]
+    if args.walk:
+        print(format_profile(profile_bucket(model, b, seqs)))
+        return 0
+    for _ in range(2):
+        run_bucket(model, b, seqs)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    run_bucket(model, b, seqs)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print("profiled one replay:", b.n_launches, "launches")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
