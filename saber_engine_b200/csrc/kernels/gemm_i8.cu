@@ -40,6 +40,7 @@
 //   activations  [k_block][M_pad][128 bytes], the same swizzle keyed on (m & 7); written in that
 //                order by the quantising producers.
 #include "gemm_i8.h"
+#include "gemm_i8_noalloc.h"
 #include "ptx_sm100.cuh"
 #include <cuda_bf16.h>
 
@@ -445,4 +446,63 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   dim3 grid(p->N_pad / 256, (p->M + p->nt - 1) / p->nt, p->splits);
   gemm_i8_kernel<<<grid, kGemmThreads, smem, stream>>>(*p, stages);
   return static_cast<int>(cudaGetLastError());
+}
+
+// ------------------------------------------------------------------------------------------------
+// Entry point that allocates nothing (declared in gemm_i8_noalloc.h).
+//
+// Some callers of this library may not allocate device memory at all: code that runs inside a
+// region where cudaMalloc is forbidden or would deadlock (a stream that is being captured, a
+// latency-critical loop that must never touch the allocator's locks, a host that gave the whole
+// device to a framework-owned pool and exposes no allocator to plug-ins).  For them the split-K
+// scratch of the GEMM (partial tiles, arrival counters, status word) lives in the array below,
+// inside the library image: every GPU that loads the library holds these bytes until the process
+// exits, whether or not the entry point is ever called.
+namespace saber {
+constexpr size_t kNoAllocPartialInts = 4u * 1024u * 1024u;           // 16 MiB of int32 partial sums
+constexpr size_t kNoAllocCounterWords = 1024;                         // one per (m tile, n tile)
+constexpr size_t kNoAllocHeaderBytes = 256 + kNoAllocCounterWords * 4;  // status word (padded) + counters
+constexpr size_t kNoAllocBytes = kNoAllocHeaderBytes + kNoAllocPartialInts * 4;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+constexpr int kNoAllocMaxDevices = 64;
+static void* g_noalloc_ptr[kNoAllocMaxDevices];        // device address of the array, per device
+}  // namespace saber
+
+extern "C" int saber_gemm_i8_noalloc(const uint8_t* w, const float* w_scale, const int8_t* a,
+                                     const float* a_scale, __nv_bfloat16* out, uint32_t* status,
+                                     int M, int M_pad, int N, int N_pad, int K, int nt, int splits,
+                                     int w4, int ldo, cudaStream_t stream) {
+  using namespace saber;
+  if (splits < 1 || M_pad <= 0 || N_pad <= 0) return kNoAllocBadArgs;
+  const size_t need = static_cast<size_t>(splits) * static_cast<size_t>(M_pad) * static_cast<size_t>(N_pad);
+  const size_t tiles = static_cast<size_t>(N_pad / 256) * static_cast<size_t>((M + nt - 1) / (nt > 0 ? nt : 1));
+  if ((splits > 1 && need > kNoAllocPartialInts) || tiles > kNoAllocCounterWords) return kNoAllocTooLarge;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return kNoAllocBadArgs;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // Set-up, once per device and with that device current.  In host code the array's NAME is only
+    // a host-side stand-in: handing it to a kernel would fault (or, where the GPU can reach host
+    // memory, quietly use the wrong bytes); the device address has to be asked for.
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    e = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_noalloc_ptr[dev] = p;
+  }
+  unsigned char* base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
+  // The array keeps whatever the last call left: the status word and the counters must start at
+  // zero (a call that gave up half-way leaves counters behind); partial tiles are overwritten.
+  e = cudaMemsetAsync(base, 0, kNoAllocHeaderBytes, stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  GemmI8Params p{};
+  p.w = w; p.w_scale = w_scale; p.a = a; p.a_scale = a_scale; p.out = out;
+  p.err = status ? status : reinterpret_cast<uint32_t*>(base);
+  p.counters = reinterpret_cast<uint32_t*>(base + 256);
+  p.ws = reinterpret_cast<int32_t*>(base + kNoAllocHeaderBytes);
+  p.M = M; p.M_pad = M_pad; p.N = N; p.N_pad = N_pad; p.K = K;
+  p.nt = nt; p.splits = splits; p.w4 = w4; p.ldo = ldo;
+  return saber_gemm_i8_launch(&p, 0, stream);
 }
