@@ -24,6 +24,7 @@
 #include "../kernels/attn.h"
 #include "../kernels/gdn.h"
 #include "../kernels/gemm_i8.h"
+#include "../kernels/moe.h"
 #include "../kernels/rowops.h"
 #include "../kernels/sample.h"
 
@@ -45,9 +46,13 @@ struct OpMemset { void* dst; int value; size_t bytes; };
 struct OpCopy { void* dst; const void* src; size_t bytes; };
 struct OpAllReduce { saber::AllReduceParams p; };
 struct OpPickMerge { saber::PickMergeParams p; };
+struct OpMoeRoute { saber::MoeRouteParams p; };
+struct OpMoeCombine { saber::MoeCombineParams p; };
+struct OpMoeGather { const int8_t* q; const float* scale; int M_pad; const int32_t* src_row; const int32_t* ntiles;
+                     int8_t* q_out; float* scale_out; int rows_cap, M_pad_out, K; };
 
 using Op = std::variant<OpGemm, OpRow, OpEmbed, OpGdnConv, OpGdnRec, OpRope, OpAttn, OpArgmax,
-                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge>;
+                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather>;
 
 struct Entry {
   Op op;
@@ -89,6 +94,11 @@ int launch(const Op& op, cudaStream_t s) {
           return static_cast<int>(cudaMemcpyAsync(o.dst, o.src, o.bytes, cudaMemcpyDeviceToDevice, s));
         else if constexpr (std::is_same_v<T, OpAllReduce>) return saber_allreduce_launch(&o.p, s);
         else if constexpr (std::is_same_v<T, OpPickMerge>) return saber_pick_merge_launch(&o.p, s);
+        else if constexpr (std::is_same_v<T, OpMoeRoute>) return saber_moe_route_launch(&o.p, s);
+        else if constexpr (std::is_same_v<T, OpMoeCombine>) return saber_moe_combine_launch(&o.p, s);
+        else if constexpr (std::is_same_v<T, OpMoeGather>)
+          return saber_moe_gather_launch(o.q, o.scale, o.M_pad, o.src_row, o.ntiles, o.q_out, o.scale_out, o.rows_cap,
+                                         o.M_pad_out, o.K, s);
         else return static_cast<int>(cudaErrorInvalidValue);
       },
       op);
@@ -162,6 +172,17 @@ int saber_program_add_copy(void* h, void* dst, const void* src, size_t bytes, co
 }
 int saber_program_add_pick_merge(void* h, const saber::PickMergeParams* p, const char* tag) {
   return add(h, OpPickMerge{*p}, p->nranks > 1 ? 1 : 0, tag);
+}
+int saber_program_add_moe_route(void* h, const saber::MoeRouteParams* p, const char* tag) {
+  return add(h, OpMoeRoute{*p}, 4, tag);
+}
+int saber_program_add_moe_gather(void* h, const int8_t* q, const float* scale, int M_pad, const int32_t* src_row,
+                                 const int32_t* ntiles, int8_t* q_out, float* scale_out, int rows_cap,
+                                 int M_pad_out, int K, const char* tag) {
+  return add(h, OpMoeGather{q, scale, M_pad, src_row, ntiles, q_out, scale_out, rows_cap, M_pad_out, K}, 1, tag);
+}
+int saber_program_add_moe_combine(void* h, const saber::MoeCombineParams* p, const char* tag) {
+  return add(h, OpMoeCombine{*p}, 1, tag);
 }
 int saber_program_add_allreduce(void* h, const saber::AllReduceParams* p, const char* tag) {
   return add(h, OpAllReduce{*p}, 1, tag);

@@ -75,7 +75,19 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
   const int kb0 = split * kb_per;
   const int kb1 = min(KB, kb0 + kb_per);
   const int nkb = kb1 - kb0;  // host guarantees >= 1
-  const int m0 = tile_m * p.nt;
+  // grouped mode: this CTA's token rows and expert come from the tile table
+  int m0 = tile_m * p.nt;
+  int rows_here = -1;
+  const uint8_t* w_base = p.w;
+  const float* w_scale_base = p.w_scale;
+  if (p.group_tiles != nullptr) {
+    if (tile_m >= *p.group_ntiles) return;      // uniform for the whole CTA, before any barrier
+    const int4 t = p.group_tiles[tile_m];
+    m0 = t.y;
+    rows_here = t.z;
+    w_base += static_cast<size_t>(t.x) * p.group_w_stride;
+    w_scale_base += static_cast<size_t>(t.x) * p.N_pad;
+  }
   const int n0 = tile_n * 256;
   const uint32_t wbytes = p.w4 ? 16384u : 32768u;
   const uint32_t abytes = static_cast<uint32_t>(p.nt) * 128u;
@@ -119,7 +131,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       const uint64_t pol = l2_policy_evict_first();
-      const uint8_t* wp = p.w + (static_cast<size_t>(tile_n) * KB + kb0) * wbytes;
+      const uint8_t* wp = w_base + (static_cast<size_t>(tile_n) * KB + kb0) * wbytes;
       const int8_t* ap = p.a + (static_cast<size_t>(kb0) * p.M_pad + m0) * 128;
       const size_t a_kb_stride = static_cast<size_t>(p.M_pad) * 128;
       int issued = 0, s = 0;
@@ -189,7 +201,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
     const int q4 = warp & 3;                     // TMEM lane quarter this warp may access
     bool ok = true;
     if (tgroup == 0) {  // epilogue warps stage the per-feature scales while the pipeline fills
-      for (int j = tid_t; j < 256; j += 128) w_scale_s[j] = (n0 + j < p.N) ? p.w_scale[n0 + j] : 0.f;
+      for (int j = tid_t; j < 256; j += 128) w_scale_s[j] = (n0 + j < p.N) ? w_scale_base[n0 + j] : 0.f;
     }
     if (p.w4) {
       int s = 0, u = 0;
@@ -241,7 +253,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
     if (ok) {
       tc_fence_after_sync();
       if (tid_t == 0) SABER_STAMP(7);
-      const int mt = min(p.nt, p.M - m0);   // live token rows of this tile
+      const int mt = rows_here >= 0 ? rows_here : min(p.nt, p.M - m0);   // live token rows of this tile
       const int row = q4 * 32 + lane;       // token row inside the tile = TMEM lane
       const int m = m0 + row;
       const bool live = row < mt;
@@ -443,7 +455,9 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  dim3 grid(p->N_pad / 256, (p->M + p->nt - 1) / p->nt, p->splits);
+  // grouped mode: every tile holds at least 16 rows of the padded expert-major row space
+  const int grid_y = p->group_tiles ? p->M_pad / 16 : (p->M + p->nt - 1) / p->nt;
+  dim3 grid(p->N_pad / 256, grid_y, p->splits);
   gemm_i8_kernel<<<grid, kGemmThreads, smem, stream>>>(*p, stages);
   return static_cast<int>(cudaGetLastError());
 }

@@ -32,6 +32,13 @@ struct GemmI8Params {
   uint32_t* tp_flags[8];   // each rank's flag region:    [2 parity][nranks src][kTpMaxTiles]
   const uint32_t* tp_seq_base;
   int tp_nranks, tp_rank, tp_site, tp_rows, tp_ld;
+  // Grouped (mixture-of-experts) mode, group_tiles != null: blockIdx.y walks a device-built tile
+  // table {expert, first row, live rows, 0}; rows are the expert-major sorted token rows.  CTAs
+  // beyond *group_ntiles leave at once, so the grid is static (graph-capturable) and sized for the
+  // worst case.  Weights / scales of expert e start at w + e * group_w_stride / w_scale + e * N_pad.
+  const int4* group_tiles;
+  const int* group_ntiles;
+  unsigned long long group_w_stride;
   unsigned long long* dbg; // optional: 16 global-timer stamps of CTA (0,0,0) (null = off)
 };
 

@@ -1,0 +1,232 @@
+// Mixture-of-experts routing for sm_100a: softmax over the router logits, top-k (lower id wins
+// ties), optional renormalisation, then an expert-major placement of the routes into 16-row-padded
+// segments plus the tile table the grouped GEMM walks, and the weighted combine.
+//
+// Parity: crates/saber-kernels/hip/moe_route.hip:1-30 (softmax fp32 -> top-10, lower id wins ties ->
+// renorm -> expert-major sort into 16-row blocks + tile tables; only this rank's experts are placed)
+// and moe_combine_bf16 (sum of w * Y in top-k order + shared expert).  Three launches here:
+// topk (warp per token), plan (one block: scan, tile table), place (thread per route).
+#include "moe.h"
+#include "gemm_i8.h"
+#include <math.h>
+
+namespace saber {
+
+constexpr int kMoeTpMaxTiles = kTpMaxTiles;   // same flag regions as the row-parallel GEMM
+
+__device__ __forceinline__ float e_safe(float x, float mx) { return x == -INFINITY ? 0.f : __expf(x - mx); }
+
+// grid = ceil(M / 8), block 256: one warp per token.
+__global__ void __launch_bounds__(256) moe_topk_kernel(const MoeRouteParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = blockIdx.x * 8 + warp;
+  if (m >= p.M) return;
+  constexpr int kPerLane = 32;                 // up to 1024 experts
+  float v[kPerLane];
+  const int per = (p.E + 31) / 32;
+  float mx = -INFINITY;
+  for (int i = 0; i < per; ++i) {
+    const int e = i * 32 + lane;
+    v[i] = e < p.E ? __bfloat162float(p.logits[static_cast<size_t>(m) * p.ld + e]) : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  for (int i = 0; i < per; ++i) {
+    v[i] = e_safe(v[i], mx);
+    sum += v[i];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.f / sum;
+  float picked_w[kMoeMaxTopK];
+  int picked_e[kMoeMaxTopK];
+  float wsum = 0.f;
+  for (int k = 0; k < p.top_k; ++k) {
+    float bv = -1.f;
+    int be = p.E;
+    for (int i = 0; i < per; ++i) {
+      const int e = i * 32 + lane;
+      if (v[i] > bv) { bv = v[i]; be = e; }     // ascending e per lane: the lower id wins ties
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+    }
+    picked_w[k] = bv * inv;
+    picked_e[k] = be;
+    wsum += picked_w[k];
+    if ((be & 31) == lane) v[be >> 5] = -1.f;   // taken
+  }
+  if (lane == 0) {
+    const float rn = p.norm_topk ? 1.f / wsum : 1.f;
+    for (int k = 0; k < p.top_k; ++k) {
+      p.topk_id[m * p.top_k + k] = picked_e[k];
+      p.topk_w[m * p.top_k + k] = picked_w[k] * rn;
+      const int le = picked_e[k] - p.e_lo;
+      if (le >= 0 && le < p.e_n) atomicAdd(p.counts + le, 1);
+    }
+  }
+}
+
+// one block of 1024 threads: padded exclusive scan of the counts, tile table, reset of the cursors.
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const MoeRouteParams p) {
+  __shared__ int padded[1024];
+  __shared__ int offs[1025];
+  const int t = threadIdx.x;
+  int c = 0;
+  if (t < p.e_n) {
+    c = p.counts[t];
+    p.cursors[t] = 0;
+  }
+  padded[t] = t < p.e_n ? ((c + 15) & ~15) : 0;
+  __syncthreads();
+  if (t == 0) {
+    int acc = 0, nt_live = 0;
+    for (int e = 0; e < p.e_n; ++e) {
+      offs[e] = acc;
+      const int cnt = p.counts[e];
+      for (int r = 0; r < cnt; r += p.nt)
+        p.tiles[nt_live++] = make_int4(e, acc + r, min(p.nt, cnt - r), 0);
+      acc += padded[e];
+    }
+    offs[p.e_n] = acc;
+    p.ntiles[0] = nt_live;
+    p.ntiles[1] = acc;
+  }
+  __syncthreads();
+  if (t <= p.e_n) p.offsets[t] = offs[t];
+  for (int i = t; i < p.rows_cap; i += blockDim.x) p.src_row[i] = -1;
+}
+
+// thread per route: claim a row in the expert's segment.
+__global__ void moe_place_kernel(const MoeRouteParams p) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= p.M * p.top_k) return;
+  const int le = p.topk_id[i] - p.e_lo;
+  if (le < 0 || le >= p.e_n) { p.slot_of[i] = -1; return; }
+  const int pos = p.offsets[le] + atomicAdd(p.cursors + le, 1);
+  p.slot_of[i] = pos;
+  p.src_row[pos] = i / p.top_k;
+}
+
+// grid = rows_cap, block = K / 16 threads (one 16-byte chunk each).
+__global__ void moe_gather_kernel(const int8_t* __restrict__ q, const float* __restrict__ scale, int M_pad,
+                                  const int32_t* __restrict__ src_row, const int32_t* __restrict__ ntiles,
+                                  int8_t* __restrict__ q_out, float* __restrict__ scale_out, int M_pad_out) {
+  const int r = blockIdx.x;
+  if (r >= ntiles[1]) return;
+  const int m = src_row[r];
+  const int kb = threadIdx.x >> 3, c = threadIdx.x & 7;       // k-block, logical 16-byte chunk
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (m >= 0)
+    v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(kb) * M_pad + m) * 128 + ((c ^ (m & 7)) << 4));
+  *reinterpret_cast<uint4*>(q_out + (static_cast<size_t>(kb) * M_pad_out + r) * 128 + ((c ^ (r & 7)) << 4)) = v;
+  if (threadIdx.x == 0) scale_out[r] = m >= 0 ? scale[m] : 0.f;
+}
+
+// clears the counts for the next step (after place has consumed them)
+__global__ void moe_reset_kernel(int32_t* counts, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) counts[i] = 0;
+}
+
+// grid = (ceil(H / 256), ceil(M / nt)), block 256: lane -> 8 columns, warp -> rows w, w + 8, ...
+// out[m] = sum_k w[m,k] * y[slot_of[m,k]] (+ sigmoid(g[m]) * shared[m]), routes in top-k order.
+__global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombineParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 256 + lane * 8;
+  const int m0 = blockIdx.y * p.nt;
+  const bool tp = p.tp_nranks > 1;
+  uint32_t seq = 0, par = 0;
+  if (tp) {
+    seq = *p.tp_seq_base + static_cast<uint32_t>(p.tp_site) + 1u;
+    par = seq & 1u;
+  }
+  if (n < p.H) {
+    for (int r = warp; r < p.nt; r += 8) {
+      const int m = m0 + r;
+      if (m >= p.M) break;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int k = 0; k < p.top_k; ++k) {
+        const int slot = p.slot_of[m * p.top_k + k];
+        if (slot < 0) continue;
+        const float w = p.topk_w[m * p.top_k + k];
+        const uint4 raw = *reinterpret_cast<const uint4*>(p.y + static_cast<size_t>(slot) * p.H + n);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          acc[2 * i] += w * f.x;
+          acc[2 * i + 1] += w * f.y;
+        }
+      }
+      if (p.shared) {
+        float gs = 1.f;
+        if (p.shared_gate) gs = 1.f / (1.f + __expf(-__bfloat162float(p.shared_gate[static_cast<size_t>(m) * p.ldg])));
+        const uint4 raw = *reinterpret_cast<const uint4*>(p.shared + static_cast<size_t>(m) * p.H + n);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          acc[2 * i] += gs * f.x;
+          acc[2 * i + 1] += gs * f.y;
+        }
+      }
+      uint4 o;
+      __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+      if (tp) {
+        const size_t off = ((static_cast<size_t>(par) * p.tp_nranks + p.tp_rank) * p.tp_rows + m) * p.tp_ld + n;
+        for (int peer = 0; peer < p.tp_nranks; ++peer)
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.tp_recv[peer]) + off) = o;
+      } else {
+        *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(m) * p.H + n) = o;
+      }
+    }
+  }
+  if (tp) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < p.tp_nranks) {
+      const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+      uint32_t* f = p.tp_flags[threadIdx.x] + (static_cast<size_t>(par) * p.tp_nranks + p.tp_rank) * kMoeTpMaxTiles + tile_id;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(seq) : "memory");
+    }
+  }
+}
+
+}  // namespace saber
+
+extern "C" int saber_moe_route_launch(const saber::MoeRouteParams* p, cudaStream_t stream) {
+  using namespace saber;
+  if (p->E > 1024 || p->e_n > 1024 || p->top_k > kMoeMaxTopK || p->top_k < 1 || p->nt < 16 || (p->nt & 15))
+    return static_cast<int>(cudaErrorInvalidValue);
+  moe_topk_kernel<<<(p->M + 7) / 8, 256, 0, stream>>>(*p);
+  moe_plan_kernel<<<1, 1024, 0, stream>>>(*p);
+  moe_place_kernel<<<(p->M * p->top_k + 255) / 256, 256, 0, stream>>>(*p);
+  moe_reset_kernel<<<(p->e_n + 255) / 256, 256, 0, stream>>>(p->counts, p->e_n);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int saber_moe_gather_launch(const int8_t* q, const float* scale, int M_pad, const int32_t* src_row,
+                                       const int32_t* ntiles, int8_t* q_out, float* scale_out, int rows_cap,
+                                       int M_pad_out, int K, cudaStream_t stream) {
+  if ((K & 127) || K / 16 > 1024 || rows_cap > M_pad_out) return static_cast<int>(cudaErrorInvalidValue);
+  saber::moe_gather_kernel<<<rows_cap, K / 16, 0, stream>>>(q, scale, M_pad, src_row, ntiles, q_out, scale_out, M_pad_out);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int saber_moe_combine_launch(const saber::MoeCombineParams* p, cudaStream_t stream) {
+  if ((p->H & 7) || p->nt < 1) return static_cast<int>(cudaErrorInvalidValue);
+  dim3 grid((p->H + 255) / 256, (p->M + p->nt - 1) / p->nt);
+  if (p->tp_nranks > 1 &&
+      (p->tp_nranks > 8 || static_cast<int>(grid.x * grid.y) > saber::kMoeTpMaxTiles || p->M > p->tp_rows || (p->tp_ld & 7)))
+    return static_cast<int>(cudaErrorInvalidValue);
+  saber::moe_combine_kernel<<<grid, 256, 0, stream>>>(*p);
+  return static_cast<int>(cudaGetLastError());
+}

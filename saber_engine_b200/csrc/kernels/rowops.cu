@@ -100,6 +100,7 @@ __global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpPa
   __shared__ float red[32];
   const int m = blockIdx.x;
   const int K = p.K;
+  if (p.m_live != nullptr && m >= *p.m_live) return;   // whole block: rows past the live count
   if (m >= p.M) {  // padding row: zeros
     if (p.q) {
       const int nchunk = K >> 4;

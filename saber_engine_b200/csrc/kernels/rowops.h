@@ -34,6 +34,9 @@ struct RowOpParams {
   const uint32_t* tp_seq_base;
   uint32_t* err;
   int tp_nranks, tp_site, tp_rows, tp_ld, tp_nt, tp_tiles_n;
+  // optional device row count: blocks of rows >= *m_live leave without writing (expert-major row
+  // spaces whose live length is only known on the device)
+  const int32_t* m_live;
 };
 
 }  // namespace saber

@@ -124,7 +124,8 @@ class ShardShape:
 def shard(cfg: HybridConfig, tp: int, rank: int) -> ShardShape:
     if tp not in (1, 2, 4, 8):
         raise ValueError(f"tensor-parallel degree {tp} is not supported (1, 2, 4 or 8)")
-    if cfg.n_q_heads % tp or cfg.gdn_k_heads % tp or cfg.gdn_v_heads % tp or cfg.ffn_inter % (tp * 128):
+    if cfg.n_q_heads % tp or cfg.gdn_k_heads % tp or cfg.gdn_v_heads % tp or \
+            (cfg.moe is None and cfg.ffn_inter % (tp * 128)) or (cfg.moe is not None and cfg.moe.n_experts % tp):
         raise ValueError(f"{cfg.name}: heads / FFN do not divide by tp={tp}")
     nq = cfg.n_q_heads // tp
     if cfg.n_kv_heads >= tp:

@@ -172,7 +172,7 @@ class HybridModel:
         cfg = self.cfg
         p = F.row_params(M, cfg.hidden, a=delta, res=res, w=w, w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa, out=out)
         if tp_site >= 0 and self.tp > 1:
-            nt = L.token_tile(M)
+            nt = self._site_nt.get(tp_site, L.token_tile(M))
             self.comm.row_tp(p, tp_site, nt, L.round_up(cfg.hidden, L.TILE_N) // L.TILE_N)
         prog.row(N.ROW_ADD_RMS, p, tag=tag)
 
@@ -220,6 +220,7 @@ class HybridModel:
         base = blob.data_ptr()
         at = lambda off: base + 4 * off                 # noqa: E731  device address of a table
         prog = N.Program(f"{kind}-b{nseq}-w{width}")
+        self._site_nt = {}                              # TP site -> row-tile height its producer signals with
         bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)   # noqa: E731
         f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)   # noqa: E731
         i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)     # noqa: E731
@@ -305,7 +306,7 @@ class HybridModel:
                 self._gemm(prog, lw.down, qa_i, delta, f"{t}.mlp.down", tp_site=ar_site)
             else:
                 from .moe_block import add_moe_block
-                add_moe_block(self, prog, lw, qa_h, h, delta, M, t, keep)
+                self._site_nt[ar_site] = add_moe_block(self, prog, lw, qa_h, h, delta, M, t, keep, tp_site=ar_site)
             pending, ar_site = (ar_site, ar_site + 1) if self.tp > 1 else (-1, ar_site)
         self._build_head(prog, kind, nseq, width, M, Mh, lay, at, h, delta, qa_h, tap_buf, taps, keep,
                          ar_site, pending)

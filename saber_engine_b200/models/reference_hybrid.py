@@ -48,11 +48,59 @@ def qlinear_row_parallel(x_bf16_rounded: torch.Tensor, w: QuantWeight, tp: int) 
     return R.bf16_round(acc)
 
 
+def moe_route_ref(logits: torch.Tensor, top_k: int, norm: bool = True):
+    """softmax fp32 -> top-k with the lower id winning ties -> optional renormalisation."""
+    p = torch.softmax(logits.float(), dim=-1)
+    order = torch.sort(-p, dim=-1, stable=True).indices[:, :top_k]
+    w = torch.gather(p, 1, order)
+    if norm:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return order, w
+
+
+def moe_mlp_ref(cfg: HybridConfig, moe: dict, n: torch.Tensor, tp: int = 1) -> torch.Tensor:
+    """The MoE MLP on bf16-rounded normed rows `n` with UNSHARDED weights; tp > 1 restates the
+    expert-parallel arithmetic (local sums rounded to bf16 per rank, added in rank order)."""
+    from .moe_weights import shared_ranks
+    m = cfg.moe
+    M, H = n.shape
+    I = m.expert_inter
+    logits = qlinear(n, moe["router"])
+    ids, wts = moe_route_ref(logits, m.top_k, m.norm_topk_prob)
+    per = m.n_experts // tp
+    # routed experts: each (token, k) route is an independent row
+    y = torch.zeros(M, m.top_k, H)
+    for e in ids.unique().tolist():
+        tok, kk = (ids == e).nonzero(as_tuple=True)
+        x = n[tok]
+        gu = qlinear(x, moe["gate_up"].expert(e))
+        y[tok, kk] = qlinear(R.silu_mul(gu), moe["down"].expert(e))
+    # shared expert
+    sgu = qlinear(n, moe["shared_gate_up"])
+    Is = m.shared_inter
+    gate = torch.sigmoid(sgu[:, 2 * Is])
+    n_sh = shared_ranks(cfg, tp)
+    isl = Is // n_sh
+    q_d, s_d = dequant_linear(moe["shared_down"])
+    total = torch.zeros(M, H)
+    for r in range(tp):
+        acc = torch.zeros(M, H)
+        for k in range(m.top_k):
+            own = (ids[:, k] // per) == r
+            acc += torch.where(own[:, None], wts[:, k, None] * y[:, k], torch.zeros(()))
+        if r < n_sh:
+            sl = slice(r * isl, (r + 1) * isl)
+            act = R.silu_mul(torch.cat([sgu[:, sl], sgu[:, Is + r * isl:Is + (r + 1) * isl]], 1))
+            aq, asc = L.quantize_act_rows(act)
+            acc += gate[:, None] * R.gemm_i8(q_d[:, sl], s_d, aq, asc).float()
+        total += R.bf16_round(acc)
+    return R.bf16_round(total)
+
+
 @torch.no_grad()
 def forward_full(cfg: HybridConfig, w: ModelWeights, ids: torch.Tensor, kv_fp8: bool = True, tp: int = 1) -> dict:
     """ids int [T] (one sequence from position 0). Returns logits [T, vocab] and per-layer residuals.
     `w` are the UNSHARDED weights; tp > 1 restates the arithmetic of a tensor-parallel run."""
-    assert cfg.moe is None, "the dense oracle covers the dense hybrid"
     sh = shard(cfg, 1, 0)
     T = ids.numel()
     H, D, d = cfg.hidden, cfg.head_dim, cfg.gdn_head_dim
@@ -93,8 +141,11 @@ def forward_full(cfg: HybridConfig, w: ModelWeights, ids: torch.Tensor, kv_fp8: 
         delta = qlinear_row_parallel(mix, lw.mixer_out, tp).to(torch.bfloat16)
         hb, n = R.add_rms(delta, h.to(torch.bfloat16), lw.post_norm.cpu(), cfg.eps, cfg.norm_offset)
         h = hb.float()
-        gu = qlinear(n, lw.gate_up)
-        delta = qlinear_row_parallel(R.silu_mul(gu), lw.down, tp).to(torch.bfloat16)
+        if cfg.moe is None:
+            gu = qlinear(n, lw.gate_up)
+            delta = qlinear_row_parallel(R.silu_mul(gu), lw.down, tp).to(torch.bfloat16)
+        else:
+            delta = moe_mlp_ref(cfg, lw.moe, n, tp).to(torch.bfloat16)
     hb, n = R.add_rms(delta, h.to(torch.bfloat16), w.final_norm.cpu(), cfg.eps, cfg.norm_offset)
     logits = qlinear(n, w.lm_head)
     return {"logits": logits, "taps": taps, "final": n}

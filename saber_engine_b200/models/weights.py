@@ -66,8 +66,7 @@ class ModelWeights:
         for lw in self.layers:
             tot += qw(lw.mixer_in) + qw(lw.mixer_out) + qw(lw.gate_up) + qw(lw.down)
             if lw.moe:
-                tot += sum(qw(v) if isinstance(v, QuantWeight) else v.numel() * v.element_size()
-                           for v in lw.moe.values() if v is not None and not isinstance(v, (int, float)))
+                tot += sum(qw(v) for v in lw.moe.values() if hasattr(v, "tiles"))
         tot += qw(self.lm_head)
         if self.drafter:
             tot += qw(self.drafter.aux_fc) + qw(self.drafter.head)

@@ -42,7 +42,8 @@ class GemmI8Params(C.Structure):
     _fields_ = [("w", P), ("w_scale", P), ("a", P), ("a_scale", P), ("out", P), ("ws", P),
                 ("counters", P), ("err", P), ("M", I), ("M_pad", I), ("N", I), ("N_pad", I),
                 ("K", I), ("nt", I), ("splits", I), ("w4", I), ("ldo", I), ("dbg_mma", I), ("tp_recv", P * 8), ("tp_flags", P * 8), ("tp_seq_base", P),
-                ("tp_nranks", I), ("tp_rank", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I), ("dbg", P)]
+                ("tp_nranks", I), ("tp_rank", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I),
+                ("group_tiles", P), ("group_ntiles", P), ("group_w_stride", U64), ("dbg", P)]
 
 
 class RowOpParams(C.Structure):
@@ -50,7 +51,7 @@ class RowOpParams(C.Structure):
                 ("eps", F), ("out", P), ("q", P), ("scale", P), ("M", I), ("M_pad", I), ("K", I),
                 ("lda", I), ("ldb", I), ("ldres", I), ("ldout", I), ("tp_recv", P), ("tp_flags", P),
                 ("tp_seq_base", P), ("err", P), ("tp_nranks", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I),
-                ("tp_nt", I), ("tp_tiles_n", I)]
+                ("tp_nt", I), ("tp_tiles_n", I), ("m_live", P)]
 
 
 class GdnConvParams(C.Structure):
@@ -95,6 +96,19 @@ class AllReduceParams(C.Structure):
 class PickMergeParams(C.Structure):
     _fields_ = [("idx", P), ("val", P), ("peer_win", P * MAX_RANKS), ("peer_flags", P * MAX_RANKS),
                 ("seq_base", P), ("err", P), ("rows", I), ("rows_max", I), ("site", I), ("nranks", I), ("rank", I)]
+
+
+class MoeRouteParams(C.Structure):
+    _fields_ = [("logits", P), ("topk_id", P), ("topk_w", P), ("counts", P), ("offsets", P), ("cursors", P),
+                ("tiles", P), ("ntiles", P), ("src_row", P), ("slot_of", P), ("M", I), ("ld", I), ("E", I),
+                ("top_k", I), ("nt", I), ("rows_cap", I), ("e_lo", I), ("e_n", I), ("norm_topk", I)]
+
+
+class MoeCombineParams(C.Structure):
+    _fields_ = [("y", P), ("shared", P), ("shared_gate", P), ("topk_w", P), ("slot_of", P), ("out", P),
+                ("M", I), ("H", I), ("top_k", I), ("nt", I), ("ldg", I), ("tp_recv", P * MAX_RANKS),
+                ("tp_flags", P * MAX_RANKS), ("tp_seq_base", P), ("tp_nranks", I), ("tp_rank", I),
+                ("tp_site", I), ("tp_rows", I), ("tp_ld", I)]
 
 
 def lib() -> C.CDLL:
@@ -167,6 +181,12 @@ def _declare(L: C.CDLL) -> None:
         "saber_program_add_memset": (I, [P, P, I, C.c_size_t, C.c_char_p]),
         "saber_program_add_copy": (I, [P, P, P, C.c_size_t, C.c_char_p]),
         "saber_program_add_allreduce": (I, [P, C.POINTER(AllReduceParams), C.c_char_p]),
+        "saber_moe_route_launch": (I, [C.POINTER(MoeRouteParams), S]),
+        "saber_moe_combine_launch": (I, [C.POINTER(MoeCombineParams), S]),
+        "saber_moe_gather_launch": (I, [P, P, I, P, P, P, P, I, I, I, S]),
+        "saber_program_add_moe_gather": (I, [P, P, P, I, P, P, P, P, I, I, I, C.c_char_p]),
+        "saber_program_add_moe_route": (I, [P, C.POINTER(MoeRouteParams), C.c_char_p]),
+        "saber_program_add_moe_combine": (I, [P, C.POINTER(MoeCombineParams), C.c_char_p]),
         "saber_program_num_ops": (I, [P]),
         "saber_program_declared_launches": (I, [P]),
         "saber_program_op_tag": (C.c_char_p, [P, I]),
@@ -278,6 +298,18 @@ class Program:
 
     def allreduce(self, p: AllReduceParams, tag="allreduce") -> int:
         return self._L.saber_program_add_allreduce(self._h, C.byref(p), tag.encode())
+
+    def add_moe_route(self, p: "MoeRouteParams", tag: str = "moe_route") -> int:
+        return self._L.saber_program_add_moe_route(self._h, C.byref(p), tag.encode())
+
+    def add_moe_gather(self, src, src_row, ntiles, dst, rows_cap: int, tag: str = "moe_gather") -> int:
+        """src / dst: objects with .q (tiled int8), .scale, .M_pad, .K (QuantAct)."""
+        return self._L.saber_program_add_moe_gather(self._h, ptr(src.q), ptr(src.scale), src.M_pad, ptr(src_row),
+                                                    ptr(ntiles), ptr(dst.q), ptr(dst.scale), rows_cap, dst.M_pad,
+                                                    src.K, tag.encode())
+
+    def add_moe_combine(self, p: "MoeCombineParams", tag: str = "moe_combine") -> int:
+        return self._L.saber_program_add_moe_combine(self._h, C.byref(p), tag.encode())
 
     # ---- execution ---------------------------------------------------------------------------
     @property

@@ -147,6 +147,9 @@ def load_weights(pack_dir, cfg, tp: int, rank: int, device, verify: bool = True)
         for key in ("conv_w", "A_log", "dt_bias", "gdn_norm", "q_norm", "k_norm"):
             if r.has(f"{p}.{kind}.{key}"):
                 setattr(lw, key, f32(f"{p}.{kind}.{key}"))
+        if cfg.moe is not None:
+            from .moe_records import load_moe
+            lw.moe = load_moe(r, p, device, verify)
         layers.append(lw)
     mw = ModelWeights(_tensor(r, "embed_tokens.weight", device, torch.bfloat16, None, verify), layers,
                       f32("norm.weight"), _load_qw(r, "lm_head", device, verify))

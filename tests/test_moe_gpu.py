@@ -1,0 +1,136 @@
+"""Mixture-of-experts path on the GPU: routing / placement against the PyTorch law, the whole block
+(router -> route -> gather -> grouped GEMMs -> combine) against the fp32 oracle, and the MoE hybrid
+model end to end (prefill logits vs oracle, speculative == greedy)."""
+import pytest
+import torch
+
+from saber_engine_b200.models import config as C
+from saber_engine_b200.ops import functional as F
+from saber_engine_b200.ops import layouts as L
+from saber_engine_b200.ops import native as N
+
+pytestmark = pytest.mark.gpu
+
+MOE = C.MoEConfig(n_experts=32, top_k=4, expert_inter=128, shared_inter=128)
+
+
+def _cfg(**kw):
+    return C.scaled_hybrid(name="hybrid-mini-moe", moe=MOE, **kw)
+
+
+def _moe_layer(cfg, seed=3):
+    from saber_engine_b200.models.moe_weights import random_moe_layer
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return random_moe_layer(cfg, 1, 0, torch.device("cuda"), g, 0.02)
+
+
+@pytest.mark.parametrize("M", [1, 9, 72, 300])
+def test_route_placement(M):
+    from saber_engine_b200.models.moe_block import MoeWorkspace, route_params
+    from saber_engine_b200.models.reference_hybrid import moe_route_ref
+    cfg = _cfg()
+    ws = MoeWorkspace(cfg, MOE.n_experts, M, "cuda", 0)
+    g = torch.Generator().manual_seed(M)
+    logits = (torch.randn(M, MOE.n_experts, generator=g) * 2).to(torch.bfloat16)
+    ws.logits[:, : MOE.n_experts] = logits.cuda()
+    prog = N.Program("route")
+    prog.add_moe_route(route_params(ws, cfg, 0))
+    for _ in range(2):                 # twice: the counts must come back to zero by themselves
+        prog.run()
+    torch.cuda.synchronize()
+    ids, wts = moe_route_ref(logits.float(), MOE.top_k, True)
+    assert torch.equal(ws.topk_id.cpu().long(), ids)
+    assert torch.allclose(ws.topk_w.cpu(), wts, rtol=2e-3, atol=1e-6)
+    # placement: every route sits inside its expert's segment and points back at its token
+    counts = torch.bincount(ids.flatten(), minlength=MOE.n_experts)
+    offs = ws.offsets.cpu()
+    padded = (counts + 15) // 16 * 16
+    assert torch.equal(offs[1:] - offs[:-1], padded.int())
+    slot = ws.slot_of.cpu().long()
+    src = ws.src_row.cpu()
+    assert len(set(slot.flatten().tolist())) == M * MOE.top_k
+    for m in range(M):
+        for k in range(MOE.top_k):
+            e, s = int(ids[m, k]), int(slot[m, k])
+            assert offs[e] <= s < offs[e] + counts[e]
+            assert int(src[s]) == m
+    total = int(padded.sum())
+    assert int(ws.ntiles.cpu()[1]) == total
+    live = src[:total] >= 0
+    assert int(live.sum()) == M * MOE.top_k
+    # tile table covers every live row exactly once
+    nt_live = int(ws.ntiles.cpu()[0])
+    tiles = ws.tiles.cpu()[:nt_live]
+    covered = torch.zeros(total, dtype=torch.int32)
+    for e, r0, rows, _ in tiles.tolist():
+        assert offs[e] <= r0 and r0 + rows <= offs[e] + counts[e] and r0 % 16 == 0 and 0 < rows <= ws.nt
+        covered[r0:r0 + rows] += 1
+    assert torch.equal(covered.bool(), live) and int(covered.max()) == 1
+    assert int(ws.counts.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("M", [5, 72, 200])
+def test_moe_block_matches_oracle(M):
+    from saber_engine_b200.models.moe_block import MoeWorkspace, add_moe_ops
+    from saber_engine_b200.models.reference_hybrid import moe_mlp_ref
+    cfg = _cfg()
+    moe = _moe_layer(cfg)
+    H = cfg.hidden
+    g = torch.Generator().manual_seed(100 + M)
+    x = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    qa = F.plain_quant(x.cuda())
+    ws = MoeWorkspace(cfg, MOE.n_experts, M, "cuda", moe["shared_inter"])
+    out = torch.zeros(M, H, dtype=torch.bfloat16, device="cuda")
+    prog = N.Program("moe")
+    add_moe_ops(prog, ws, cfg, moe, qa, out, F.scratch("cuda"), "L0.moe")
+    prog.run()
+    torch.cuda.synchronize()
+    F.scratch("cuda").check()
+    ref = moe_mlp_ref(cfg, moe, x.float())
+    got = out.float().cpu()
+    err = (got - ref).abs().max()
+    assert err <= 0.02 * ref.abs().max() + 1e-4, (float(err), float(ref.abs().max()))
+    # graph replay gives the same bytes as the eager walk
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        assert prog.capture(st) == prog.declared_launches
+        out.zero_()
+        prog.replay(st)
+    st.synchronize()
+    assert torch.equal(out.float().cpu(), got)
+
+
+def test_moe_model_prefill_and_spec_decode():
+    from saber_engine_b200.models.hybrid import HybridModel, SeqStep, run_bucket
+    from saber_engine_b200.models.reference_hybrid import forward_full
+    cfg = _cfg()
+    model = HybridModel(cfg, device="cuda", max_seqs=4, max_ctx=512, max_width=5, seed=1)
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
+    blocks = list(range(1, 33))
+    model.reset_slot(1)
+    pb = model.build_bucket("prefill", 1, 48)
+    res = run_bucket(model, pb, [SeqStep(prompt, 0, 1, 0, blocks)])
+    got = pb.logits[0, : cfg.vocab].float().cpu()
+    ref = forward_full(cfg, model.w, torch.tensor(prompt))["logits"][-1]
+    assert (got - ref).abs().max() < 0.05 * ref.abs().max() + 1e-3
+
+    def decode(slot, blocks, first, drafts, width, steps=16):
+        out, pos, shift, k = [first], len(prompt), 0, 0
+        b = model.build_bucket("decode", 1, width)
+        while len(out) < steps:
+            rows = [out[-1]] + list(drafts[: width - 1])
+            r = run_bucket(model, b, [SeqStep(rows, pos, slot, shift, blocks, uid=3, step_no=k)])
+            out += r.tokens[0]
+            pos += r.n_commit[0]
+            shift, drafts, k = r.n_commit[0], r.drafts[0], k + 1
+        return out[:steps]
+
+    plain = decode(1, blocks, res.tokens[0][0], [], 1)
+    model.reset_slot(2)
+    b2 = list(range(40, 72))
+    res2 = run_bucket(model, pb, [SeqStep(prompt, 0, 2, 0, b2)])
+    assert res2.tokens == res.tokens
+    assert decode(2, b2, res2.tokens[0][0], res2.drafts[0], 5) == plain
+    model.scratch.check()
