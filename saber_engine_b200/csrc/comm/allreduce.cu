@@ -2,6 +2,7 @@
 // rank order (every rank adds the same values in the same order, so results are bit-identical
 // across ranks).  Block b owns chunk b of the message end to end: push own chunk into every
 // peer's receive slot, release a flag per peer, wait (bounded) for every peer's flag, reduce.
+#include "../kernels/launch.cuh"
 #include "comm.h"
 #include <string.h>
 
@@ -22,6 +23,7 @@ __device__ __forceinline__ unsigned long long ar_now_ns() {
 }
 
 __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const AllReduceParams p) {
+  pdl_wait();
   const int b = blockIdx.x, tid = threadIdx.x;
   const uint32_t seq = *p.seq_base + static_cast<uint32_t>(p.site) + 1u;
   const uint32_t par = seq & 1u;
@@ -81,6 +83,7 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const AllReduceP
 }
 
 __global__ void __launch_bounds__(1024) pick_merge_kernel(const PickMergeParams p) {
+  pdl_wait();
   const int tid = threadIdx.x;
   const uint32_t seq = *p.seq_base + static_cast<uint32_t>(p.site) + 1u;
   const uint32_t par = seq & 1u;
@@ -118,7 +121,10 @@ __global__ void __launch_bounds__(1024) pick_merge_kernel(const PickMergeParams 
   }
 }
 
-__global__ void comm_advance_kernel(uint32_t* seq_base, uint32_t by) { *seq_base += by; }
+__global__ void comm_advance_kernel(uint32_t* seq_base, uint32_t by) {
+  pdl_wait();
+  *seq_base += by;
+}
 
 }  // namespace saber
 
@@ -132,7 +138,7 @@ extern "C" int saber_allreduce_launch(const saber::AllReduceParams* p, cudaStrea
                                               cudaMemcpyDeviceToDevice, stream));
     return 0;
   }
-  allreduce_oneshot_kernel<<<kArBlocks, 512, 0, stream>>>(*p);
+  saber::launch(allreduce_oneshot_kernel, dim3(kArBlocks), dim3(512), 0, stream, 0, *p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -140,12 +146,12 @@ extern "C" int saber_pick_merge_launch(const saber::PickMergeParams* p, cudaStre
   using namespace saber;
   if (p->nranks < 1 || p->nranks > kMaxRanks || p->rows > p->rows_max) return static_cast<int>(cudaErrorInvalidValue);
   if (p->nranks == 1) return 0;
-  pick_merge_kernel<<<1, 1024, 0, stream>>>(*p);
+  saber::launch(pick_merge_kernel, dim3(1), dim3(1024), 0, stream, 0, *p);
   return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int saber_comm_advance_launch(uint32_t* seq_base, uint32_t by, cudaStream_t stream) {
-  saber::comm_advance_kernel<<<1, 1, 0, stream>>>(seq_base, by);
+  saber::launch(saber::comm_advance_kernel, dim3(1), dim3(1), 0, stream, 0, seq_base, by);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -14,6 +14,7 @@
 //
 // The contraction here runs on warp-level mma (m16n8k16 bf16): decode attention is bound by the
 // KV bytes it streams, not by tensor throughput.
+#include "launch.cuh"
 #include "attn.h"
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -22,6 +23,7 @@ namespace saber {
 
 // ------------------------------------------------------------------------------- rope + kv append
 __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeKvParams p) {
+  pdl_wait();
   __shared__ float y[kHeadDim];
   __shared__ float red[4];
   const int m = blockIdx.x;
@@ -128,6 +130,7 @@ constexpr int kAttnMaxWarps = 6;
 __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const AttnParams p,
                                                                         const int hpb,
                                                                         const int hgroups) {
+  pdl_wait();
   extern __shared__ __align__(16) uint8_t attn_smem[];
   // layout: Q [hpb][16][256] bf16 | K [16][256] bf16 | V [16][256] bf16, 512-byte rows, 16-byte
   // chunk index XOR (row & 7)
@@ -343,6 +346,7 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
 
 // grid (nseq * nq, 16), block 256: merge the split partials of one (sequence, head, row).
 __global__ void __launch_bounds__(256) attn_combine_kernel(const AttnParams p) {
+  pdl_wait();
   const int b = blockIdx.x / p.nq, head = blockIdx.x % p.nq;
   const int rr = blockIdx.y;
   const int row0 = p.cu_q[b];
@@ -369,7 +373,7 @@ extern "C" int saber_rope_kv_launch(const saber::RopeKvParams* p, cudaStream_t s
   using namespace saber;
   if (p->M <= 0) return 0;
   if (p->rot_dim > kHeadDim || (p->rot_dim & 3)) return static_cast<int>(cudaErrorInvalidValue);
-  rope_kv_kernel<<<dim3(p->M, p->nq + p->nkv), 128, 0, stream>>>(*p);
+  saber::launch(rope_kv_kernel, dim3(dim3(p->M, p->nq + p->nkv)), dim3(128), 0, stream, 0, *p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -387,8 +391,8 @@ extern "C" int saber_attn_launch(const saber::AttnParams* p, cudaStream_t stream
     configured = true;
   }
   dim3 grid(p->q_tiles, p->nkv * hgroups, p->nseq * p->splits);
-  attn_paged_kernel<<<grid, 32 * hpb, smem, stream>>>(*p, hpb, hgroups);
+  saber::launch(attn_paged_kernel, dim3(grid), dim3(32 * hpb), smem, stream, 0, *p, hpb, hgroups);
   if (p->splits > 1)
-    attn_combine_kernel<<<dim3(p->nseq * p->nq, 16), 256, 0, stream>>>(*p);
+    saber::launch(attn_combine_kernel, dim3(dim3(p->nseq * p->nq, 16)), dim3(256), 0, stream, 0, *p);
   return static_cast<int>(cudaGetLastError());
 }

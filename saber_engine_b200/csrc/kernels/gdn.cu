@@ -14,6 +14,7 @@
 // norm is a block reduction) and recurrent (CTA = (value head, v-slice, sequence), two threads per
 // state row holding 64 fp32 each).  Prefill chunks use the same kernels with commit=1: rows are
 // consumed for good, the final state is stored and conv_commit rewrites the conv window.
+#include "launch.cuh"
 #include "gdn.h"
 #include <cuda_bf16.h>
 
@@ -25,6 +26,7 @@ __device__ __forceinline__ float gdn_softplus(float x) { return x > 20.f ? x : l
 // ---------------------------------------------------------------------------------- conv update
 // grid (C / 128, nseq), block 128.
 __global__ void __launch_bounds__(128) gdn_conv_update_kernel(const GdnConvParams p) {
+  pdl_wait();
   __shared__ float red[4];
   const int b = blockIdx.y;
   const int slot = p.slots[b];
@@ -71,6 +73,7 @@ __global__ void __launch_bounds__(128) gdn_conv_update_kernel(const GdnConvParam
 
 // After a committing (prefill) step: window = last three inputs of (old window ++ this step's rows).
 __global__ void __launch_bounds__(128) gdn_conv_commit_kernel(const GdnConvParams p) {
+  pdl_wait();
   const int b = blockIdx.y;
   const int slot = p.slots[b];
   if (slot < 0) return;
@@ -99,6 +102,7 @@ constexpr int kRecBatch = 16;
 
 template <int VS>
 __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecParams p) {
+  pdl_wait();
   constexpr int VR = 128 / VS;         // v rows per CTA
   constexpr int NT = 2 * VR;           // threads
   constexpr int KP = 64 + 4;           // padded half stride in shared memory (bank spread)
@@ -231,8 +235,8 @@ extern "C" int saber_gdn_conv_launch(const saber::GdnConvParams* p, int nseq, cu
   using namespace saber;
   if (p->C % 128 || p->n_q % 128 || p->n_k % 128) return static_cast<int>(cudaErrorInvalidValue);
   dim3 grid(p->C / 128, nseq);
-  gdn_conv_update_kernel<<<grid, 128, 0, stream>>>(*p);
-  if (p->commit) gdn_conv_commit_kernel<<<grid, 128, 0, stream>>>(*p);
+  saber::launch(gdn_conv_update_kernel, dim3(grid), dim3(128), 0, stream, 0, *p);
+  if (p->commit) saber::launch(gdn_conv_commit_kernel, dim3(grid), dim3(128), 0, stream, 0, *p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -240,9 +244,9 @@ extern "C" int saber_gdn_recurrent_launch(const saber::GdnRecParams* p, int nseq
                                           cudaStream_t stream) {
   using namespace saber;
   if (p->HV % p->HK) return static_cast<int>(cudaErrorInvalidValue);
-  if (vs == 1) gdn_recurrent_kernel<1><<<dim3(p->HV, nseq), 256, 0, stream>>>(*p);
-  else if (vs == 2) gdn_recurrent_kernel<2><<<dim3(p->HV * 2, nseq), 128, 0, stream>>>(*p);
-  else if (vs == 4) gdn_recurrent_kernel<4><<<dim3(p->HV * 4, nseq), 64, 0, stream>>>(*p);
+  if (vs == 1) saber::launch(gdn_recurrent_kernel<1>, dim3(dim3(p->HV, nseq)), dim3(256), 0, stream, 0, *p);
+  else if (vs == 2) saber::launch(gdn_recurrent_kernel<2>, dim3(dim3(p->HV * 2, nseq)), dim3(128), 0, stream, 0, *p);
+  else if (vs == 4) saber::launch(gdn_recurrent_kernel<4>, dim3(dim3(p->HV * 4, nseq)), dim3(64), 0, stream, 0, *p);
   else return static_cast<int>(cudaErrorInvalidValue);
   return static_cast<int>(cudaGetLastError());
 }

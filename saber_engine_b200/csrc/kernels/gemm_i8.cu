@@ -40,6 +40,7 @@
 //   activations  [k_block][M_pad][128 bytes], the same swizzle keyed on (m & 7); written in that
 //                order by the quantising producers.
 #include "gemm_i8.h"
+#include "launch.cuh"
 #include "gemm_i8_noalloc.h"
 #include "ptx_sm100.cuh"
 #include <cuda_bf16.h>
@@ -66,6 +67,10 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
   const bool dbg_on = p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 #define SABER_STAMP(i) do { if (dbg_on) p.dbg[i] = globaltimer_ns(); } while (0)
   if (threadIdx.x == 0) SABER_STAMP(0);
+  // Programmatic dependent launch: this kernel may be running ahead of its predecessor, so only
+  // WEIGHTS (which no kernel writes) are touched before pdl_wait().  It never triggers its own
+  // dependents early: CTAs of a successor placed while this grid holds the SMs would pile up on
+  // the few SMs it leaves free.
   const int tile_n = blockIdx.x;
   const int tile_m = blockIdx.y;
   const int split = blockIdx.z;
@@ -81,6 +86,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
   const uint8_t* w_base = p.w;
   const float* w_scale_base = p.w_scale;
   if (p.group_tiles != nullptr) {
+    pdl_wait();                                 // the tile table is the routing kernels' output
     if (tile_m >= *p.group_ntiles) return;      // uniform for the whole CTA, before any barrier
     const int4 t = p.group_tiles[tile_m];
     m0 = t.y;
@@ -137,7 +143,23 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
       int issued = 0, s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int it = 0; it < nkb; ++it) {
+      // first pass over the ring: the weight tiles go out at once, the token tiles only after the
+      // predecessor kernel (which produced them) has completed
+      const int pre = min(stages, nkb);
+      for (int it = 0; it < pre; ++it) {
+        mbar_arrive_expect_tx(bar_full + 8 * it, wbytes + abytes);
+        bulk_g2s_hint(w_smem + it * wbytes, wp, wbytes, bar_full + 8 * it, pol);
+        wp += wbytes;
+        if (it == 0) SABER_STAMP(2);
+      }
+      pdl_wait();
+      for (int it = 0; it < pre; ++it) {
+        bulk_g2s(a_smem + it * abytes, ap, abytes, bar_full + 8 * it);
+        ap += a_kb_stride;
+      }
+      issued = pre;
+      if (pre == stages) { s = 0; ph = 1u; } else { s = pre; }
+      for (int it = pre; it < nkb; ++it) {
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, p.err, kErrWaitEmpty)) { ok = false; break; }
         mbar_arrive_expect_tx(bar_full + 8 * s, wbytes + abytes);
         bulk_g2s_hint(w_smem + s * wbytes, wp, wbytes, bar_full + 8 * s, pol);
@@ -145,7 +167,6 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
         wp += wbytes;
         ap += a_kb_stride;
         issued = it + 1;
-        if (it == 0) SABER_STAMP(2);
         if (++s == stages) { s = 0; ph ^= 1u; }
       }
       if (!ok) {
@@ -252,6 +273,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
     }
     if (ok) {
       tc_fence_after_sync();
+      pdl_wait();   // already satisfied (the token tiles have landed); orders this thread's reads and writes
       if (tid_t == 0) SABER_STAMP(7);
       const int mt = rows_here >= 0 ? rows_here : min(p.nt, p.M - m0);   // live token rows of this tile
       const int row = q4 * 32 + lane;       // token row inside the tile = TMEM lane
@@ -337,7 +359,31 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
         __threadfence();
         named_bar_sync(1, 128);
         const int tile_id = tile_m * gridDim.x + tile_n;
-        if (tid_t == 0) {
+        // Two ways to add the splits.  Cooperative (every CTA of the grid is resident, the launcher
+        // guarantees it): all splits of a tile wait for one another and each reduces the rows
+        // r = split (mod splits), so the pass is spread over `splits` SMs.  Otherwise the last
+        // arriver reduces the whole tile alone.
+        int part = 0, nparts = 1;
+        if (p.coop) {
+          if (tid_t == 0) {
+            atomicAdd(p.counters + tile_id, 1u);
+            uint32_t seen = 0;
+            const long long t0 = clock64();
+            uint32_t okw = 1u;
+            for (uint32_t polls = 0;; ++polls) {
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.counters + tile_id) : "memory");
+              if (seen >= static_cast<uint32_t>(p.splits)) break;
+              if ((polls & 1023u) == 1023u && clock64() - t0 > kWaitLimitCycles) {
+                atomicCAS(p.err, 0, kErrWaitSplit);
+                okw = 0u;
+                break;
+              }
+            }
+            is_last_s = okw;
+          }
+          part = split;
+          nparts = p.splits;
+        } else if (tid_t == 0) {
           const uint32_t old = atomicAdd(p.counters + tile_id, 1u);
           is_last_s = (old == static_cast<uint32_t>(p.splits - 1)) ? 1u : 0u;
         }
@@ -348,7 +394,8 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
           // such items per round with every load of the round issued before any is used (this
           // pass runs in ONE CTA while the rest of the grid has left: it is latency that counts)
           const int vec_per_row = ncols >> 3;
-          const int n_items = mt * vec_per_row;
+          const int rows_part = mt > part ? (mt - part + nparts - 1) / nparts : 0;
+          const int n_items = rows_part * vec_per_row;
           constexpr int kIlp = 4;
           for (int base = tid_t; base < n_items; base += 128 * kIlp) {
             int4 x0[kIlp], x1[kIlp];
@@ -357,8 +404,9 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
 #pragma unroll
             for (int u = 0; u < kIlp; ++u) {
               const int idx = min(base + u * 128, n_items - 1);
-              rr[u] = idx / vec_per_row;
-              cc[u] = (idx - rr[u] * vec_per_row) << 3;
+              const int ri = idx / vec_per_row;
+              rr[u] = part + ri * nparts;
+              cc[u] = (idx - ri * vec_per_row) << 3;
               x0[u] = make_int4(0, 0, 0, 0);
               x1[u] = make_int4(0, 0, 0, 0);
               asc[u] = p.a_scale[m0 + rr[u]];
@@ -402,8 +450,24 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
               }
             }
           }
-          if (tid_t == 0) p.counters[tile_id] = 0u;
-          if (tp) tp_signal(tile_id);
+          if (!p.coop) {
+            if (tid_t == 0) p.counters[tile_id] = 0u;
+            if (tp) tp_signal(tile_id);
+          }
+        }
+        if (p.coop) {
+          // second round of arrivals: the CTA that finishes last re-arms the counter and, in
+          // tensor-parallel mode, raises the tile's flags (every slice has been pushed by then)
+          if (tp) __threadfence_system();
+          named_bar_sync(1, 128);
+          if (tid_t == 0) {
+            const uint32_t old = atomicAdd(p.counters + tile_id, 1u);
+            const bool fin = old == static_cast<uint32_t>(2 * p.splits - 1);
+            if (fin) p.counters[tile_id] = 0u;
+            is_last_s = fin ? 1u : 0u;
+          }
+          named_bar_sync(1, 128);
+          if (tp && is_last_s) tp_signal(tile_id);
         }
       }
     }
@@ -458,8 +522,16 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   // grouped mode: every tile holds at least 16 rows of the padded expert-major row space
   const int grid_y = p->group_tiles ? p->M_pad / 16 : (p->M + p->nt - 1) / p->nt;
   dim3 grid(p->N_pad / 256, grid_y, p->splits);
-  gemm_i8_kernel<<<grid, kGemmThreads, smem, stream>>>(*p, stages);
-  return static_cast<int>(cudaGetLastError());
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  GemmI8Params q = *p;
+  // one CTA per SM (shared memory): the whole grid is resident iff it has no more CTAs than SMs
+  q.coop = (p->splits > 1 && p->coop >= 0 && static_cast<int>(grid.x * grid.y * grid.z) <= sm_count) ? 1 : 0;
+  return static_cast<int>(saber::launch(gemm_i8_kernel, grid, dim3(kGemmThreads), smem, stream, (q.coop != 0 ? 1 : 0) | 2, q, stages));
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -39,6 +39,9 @@ struct GemmI8Params {
   const int4* group_tiles;
   const int* group_ntiles;
   unsigned long long group_w_stride;
+  // split-K reduction mode. Callers leave 0 (the launcher turns the cooperative form on when the
+  // whole grid is resident) or set -1 to force the last-arriver form.
+  int coop;
   unsigned long long* dbg; // optional: 16 global-timer stamps of CTA (0,0,0) (null = off)
 };
 

@@ -6,6 +6,7 @@
 // renorm -> expert-major sort into 16-row blocks + tile tables; only this rank's experts are placed)
 // and moe_combine_bf16 (sum of w * Y in top-k order + shared expert).  Three launches here:
 // topk (warp per token), plan (one block: scan, tile table), place (thread per route).
+#include "launch.cuh"
 #include "moe.h"
 #include "gemm_i8.h"
 #include <math.h>
@@ -18,6 +19,7 @@ __device__ __forceinline__ float e_safe(float x, float mx) { return x == -INFINI
 
 // grid = ceil(M / 8), block 256: one warp per token.
 __global__ void __launch_bounds__(256) moe_topk_kernel(const MoeRouteParams p) {
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m = blockIdx.x * 8 + warp;
   if (m >= p.M) return;
@@ -74,6 +76,7 @@ __global__ void __launch_bounds__(256) moe_topk_kernel(const MoeRouteParams p) {
 
 // one block of 1024 threads: padded exclusive scan of the counts, tile table, reset of the cursors.
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const MoeRouteParams p) {
+  pdl_wait();
   __shared__ int padded[1024];
   __shared__ int offs[1025];
   const int t = threadIdx.x;
@@ -104,6 +107,7 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const MoeRouteParams p) 
 
 // thread per route: claim a row in the expert's segment.
 __global__ void moe_place_kernel(const MoeRouteParams p) {
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= p.M * p.top_k) return;
   const int le = p.topk_id[i] - p.e_lo;
@@ -117,6 +121,8 @@ __global__ void moe_place_kernel(const MoeRouteParams p) {
 __global__ void moe_gather_kernel(const int8_t* __restrict__ q, const float* __restrict__ scale, int M_pad,
                                   const int32_t* __restrict__ src_row, const int32_t* __restrict__ ntiles,
                                   int8_t* __restrict__ q_out, float* __restrict__ scale_out, int M_pad_out) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   if (r >= ntiles[1]) return;
   const int m = src_row[r];
@@ -130,6 +136,7 @@ __global__ void moe_gather_kernel(const int8_t* __restrict__ q, const float* __r
 
 // clears the counts for the next step (after place has consumed them)
 __global__ void moe_reset_kernel(int32_t* counts, int n) {
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) counts[i] = 0;
 }
@@ -137,6 +144,7 @@ __global__ void moe_reset_kernel(int32_t* counts, int n) {
 // grid = (ceil(H / 256), ceil(M / nt)), block 256: lane -> 8 columns, warp -> rows w, w + 8, ...
 // out[m] = sum_k w[m,k] * y[slot_of[m,k]] (+ sigmoid(g[m]) * shared[m]), routes in top-k order.
 __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombineParams p) {
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * 256 + lane * 8;
   const int m0 = blockIdx.y * p.nt;
@@ -206,10 +214,10 @@ extern "C" int saber_moe_route_launch(const saber::MoeRouteParams* p, cudaStream
   using namespace saber;
   if (p->E > 1024 || p->e_n > 1024 || p->top_k > kMoeMaxTopK || p->top_k < 1 || p->nt < 16 || (p->nt & 15))
     return static_cast<int>(cudaErrorInvalidValue);
-  moe_topk_kernel<<<(p->M + 7) / 8, 256, 0, stream>>>(*p);
-  moe_plan_kernel<<<1, 1024, 0, stream>>>(*p);
-  moe_place_kernel<<<(p->M * p->top_k + 255) / 256, 256, 0, stream>>>(*p);
-  moe_reset_kernel<<<(p->e_n + 255) / 256, 256, 0, stream>>>(p->counts, p->e_n);
+  saber::launch(moe_topk_kernel, dim3((p->M + 7) / 8), dim3(256), 0, stream, 0, *p);
+  saber::launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, 0, *p);
+  saber::launch(moe_place_kernel, dim3((p->M * p->top_k + 255) / 256), dim3(256), 0, stream, 0, *p);
+  saber::launch(moe_reset_kernel, dim3((p->e_n + 255) / 256), dim3(256), 0, stream, 0, p->counts, p->e_n);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -217,7 +225,7 @@ extern "C" int saber_moe_gather_launch(const int8_t* q, const float* scale, int 
                                        const int32_t* ntiles, int8_t* q_out, float* scale_out, int rows_cap,
                                        int M_pad_out, int K, cudaStream_t stream) {
   if ((K & 127) || K / 16 > 1024 || rows_cap > M_pad_out) return static_cast<int>(cudaErrorInvalidValue);
-  saber::moe_gather_kernel<<<rows_cap, K / 16, 0, stream>>>(q, scale, M_pad, src_row, ntiles, q_out, scale_out, M_pad_out);
+  saber::launch(saber::moe_gather_kernel, dim3(rows_cap), dim3(K / 16), 0, stream, 0, q, scale, M_pad, src_row, ntiles, q_out, scale_out, M_pad_out);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -227,6 +235,6 @@ extern "C" int saber_moe_combine_launch(const saber::MoeCombineParams* p, cudaSt
   if (p->tp_nranks > 1 &&
       (p->tp_nranks > 8 || static_cast<int>(grid.x * grid.y) > saber::kMoeTpMaxTiles || p->M > p->tp_rows || (p->tp_ld & 7)))
     return static_cast<int>(cudaErrorInvalidValue);
-  saber::moe_combine_kernel<<<grid, 256, 0, stream>>>(*p);
+  saber::launch(saber::moe_combine_kernel, dim3(grid), dim3(256), 0, stream, 0, *p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -11,6 +11,7 @@
 //   PLAIN      h = a
 // Quantisation law (per token row): amax = max |h|; scale = amax / 127; q = clamp(rint(h * (127 /
 // amax)), -127, 127); a zero row stores scale 0.  Rows in [M, M_pad) are written as zeros.
+#include "launch.cuh"
 #include "rowops.h"
 #include "gemm_i8.h"
 #include "ptx_sm100.cuh"
@@ -95,6 +96,8 @@ __device__ __forceinline__ void quant_store_row(const __nv_bfloat16* h, int K, i
 
 template <int MODE>
 __global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpParams p) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ __align__(16) uint8_t row_smem[];
   __nv_bfloat16* h = reinterpret_cast<__nv_bfloat16*>(row_smem);  // K bf16
   __shared__ float red[32];
@@ -253,6 +256,8 @@ __global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpPa
 __global__ void embed_gather_kernel(const __nv_bfloat16* table, const int32_t* ids,
                                     __nv_bfloat16* out, int M, int H, int vocab_lo, int vocab_n,
                                     int ldout) {
+  pdl_trigger();
+  pdl_wait();
   const int m = blockIdx.x;
   if (m >= M) return;
   const int id = ids[m] - vocab_lo;
@@ -266,6 +271,8 @@ __global__ void embed_gather_kernel(const __nv_bfloat16* table, const int32_t* i
 // x[(b * block + j), :] = bf16(ctx[b, :] + tok[b, :] + pos[j, :])   (drafter block input rows)
 __global__ void block_expand_kernel(const __nv_bfloat16* ctx, const __nv_bfloat16* tok,
                                     const __nv_bfloat16* pos, __nv_bfloat16* out, int block, int H) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x, b = row / block, j = row % block;
   for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x) {
     float c[8], t[8], q[8];
@@ -283,7 +290,7 @@ __global__ void block_expand_kernel(const __nv_bfloat16* ctx, const __nv_bfloat1
 extern "C" int saber_block_expand_launch(const void* ctx, const void* tok, const void* pos, void* out,
                                          int nseq, int block, int H, cudaStream_t stream) {
   if (H & 7) return static_cast<int>(cudaErrorInvalidValue);
-  saber::block_expand_kernel<<<nseq * block, 128, 0, stream>>>(
+  saber::launch(saber::block_expand_kernel, dim3(nseq * block), dim3(128), 0, stream, 0, 
       static_cast<const __nv_bfloat16*>(ctx), static_cast<const __nv_bfloat16*>(tok),
       static_cast<const __nv_bfloat16*>(pos), static_cast<__nv_bfloat16*>(out), block, H);
   return static_cast<int>(cudaGetLastError());
@@ -299,7 +306,7 @@ extern "C" int saber_row_producer_launch(int mode, const saber::RowOpParams* p, 
     if (smem > 48 * 1024)                                                                        \
       cudaFuncSetAttribute(row_producer_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            static_cast<int>(smem));                                              \
-    row_producer_kernel<MODE><<<rows, kRowThreads, smem, stream>>>(*p);                          \
+    saber::launch(row_producer_kernel<MODE>, dim3(rows), dim3(kRowThreads), smem, stream, 0, *p);                          \
     break;                                                                                       \
   }
   switch (mode) {
@@ -320,7 +327,7 @@ extern "C" int saber_embed_gather_launch(const void* table, const int32_t* ids, 
                                          cudaStream_t stream) {
   if ((H & 7) || (ldout & 7)) return static_cast<int>(cudaErrorInvalidValue);
   if (ldout == 0) ldout = H;
-  saber::embed_gather_kernel<<<M, 128, 0, stream>>>(
+  saber::launch(saber::embed_gather_kernel, dim3(M), dim3(128), 0, stream, 0, 
       static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), M, H,
       vocab_lo, vocab_n, ldout);
   return static_cast<int>(cudaGetLastError());

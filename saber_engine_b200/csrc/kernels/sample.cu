@@ -6,6 +6,7 @@
 // the laws of crates/saber-kernels/hip/head.hip:116-145; greedy prefix acceptance is
 // crates/saber-exec/src/forward.rs:475 (accept_prefix); the seeded acceptance oracle mirrors the
 // reference's RandomAcceptanceExecutor (crates/saber-sched/src/mock.rs:1-20) on the device.
+#include "launch.cuh"
 #include "sample.h"
 #include <cuda_bf16.h>
 #include <math.h>
@@ -20,6 +21,7 @@ __device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
 __global__ void __launch_bounds__(1024) argmax_kernel(const __nv_bfloat16* logits, int ld, int V,
                                                       int id_offset, int32_t* out_idx,
                                                       float* out_val) {
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   const int r = blockIdx.x;
@@ -78,6 +80,7 @@ __device__ __forceinline__ uint32_t bf16_key(uint16_t bits) {
 __global__ void __launch_bounds__(1024) topk_seam_kernel(const __nv_bfloat16* logits, int ld, int V,
                                                          int id_offset, const float* temps,
                                                          int32_t* ids, float* vals, float* lse) {
+  pdl_wait();
   __shared__ uint32_t hist[256];
   __shared__ uint32_t sel_hi, sel_lo, above_hi, above_lo;
   __shared__ float cand_v[kSeamK];
@@ -217,6 +220,7 @@ __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
 //   oracle:  a = min(w - 1, G) with G ~ geometric(p_accept) drawn from (seed, seq uid, step)
 // Outputs: n_commit[b] = a + 1; out_tokens[b][0..a) = accepted drafts, out_tokens[b][a] = bonus.
 __global__ void verify_accept_kernel(const VerifyParams p) {
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= p.nseq) return;
   const int r0 = p.cu_rows[b];
@@ -251,7 +255,7 @@ extern "C" int saber_argmax_launch(const void* logits, int rows, int ld, int V, 
                                    int32_t* out_idx, float* out_val, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (ld & 7) return static_cast<int>(cudaErrorInvalidValue);
-  saber::argmax_kernel<<<rows, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), ld, V,
+  saber::launch(saber::argmax_kernel, dim3(rows), dim3(1024), 0, stream, 0, static_cast<const __nv_bfloat16*>(logits), ld, V,
                                                   id_offset, out_idx, out_val);
   return static_cast<int>(cudaGetLastError());
 }
@@ -261,13 +265,13 @@ extern "C" int saber_topk_seam_launch(const void* logits, int rows, int ld, int 
                                       cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (V < saber::kSeamK) return static_cast<int>(cudaErrorInvalidValue);
-  saber::topk_seam_kernel<<<rows, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), ld,
+  saber::launch(saber::topk_seam_kernel, dim3(rows), dim3(1024), 0, stream, 0, static_cast<const __nv_bfloat16*>(logits), ld,
                                                      V, id_offset, temps, ids, vals, lse);
   return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" int saber_verify_launch(const saber::VerifyParams* p, cudaStream_t stream) {
   if (p->nseq <= 0) return 0;
-  saber::verify_accept_kernel<<<(p->nseq + 63) / 64, 64, 0, stream>>>(*p);
+  saber::launch(saber::verify_accept_kernel, dim3((p->nseq + 63) / 64), dim3(64), 0, stream, 0, *p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -34,7 +34,7 @@ ROW_ADD_RMS, ROW_SILU_MUL, ROW_GATE_SIG, ROW_GDN_NORM, ROW_PLAIN = range(5)
 
 ERR_NAMES = {
     0: "ok", 1: "wait_full", 2: "wait_empty", 3: "wait_ready", 4: "wait_acc", 5: "wait_peer",
-    6: "wait_drain", 7: "bad_args",
+    6: "wait_drain", 7: "bad_args", 8: "wait_split",
 }
 
 
@@ -43,7 +43,7 @@ class GemmI8Params(C.Structure):
                 ("counters", P), ("err", P), ("M", I), ("M_pad", I), ("N", I), ("N_pad", I),
                 ("K", I), ("nt", I), ("splits", I), ("w4", I), ("ldo", I), ("dbg_mma", I), ("tp_recv", P * 8), ("tp_flags", P * 8), ("tp_seq_base", P),
                 ("tp_nranks", I), ("tp_rank", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I),
-                ("group_tiles", P), ("group_ntiles", P), ("group_w_stride", U64), ("dbg", P)]
+                ("group_tiles", P), ("group_ntiles", P), ("group_w_stride", U64), ("coop", I), ("dbg", P)]
 
 
 class RowOpParams(C.Structure):
@@ -129,6 +129,12 @@ def lib() -> C.CDLL:
     return _LIB
 
 
+def set_pdl(mode: int) -> None:
+    """Programmatic dependent launch for kernels launched from now on: 0 off, 1 every kernel,
+    2 only the GEMMs."""
+    lib().saber_set_pdl(int(mode))
+
+
 def available() -> bool:
     try:
         lib()
@@ -181,6 +187,8 @@ def _declare(L: C.CDLL) -> None:
         "saber_program_add_memset": (I, [P, P, I, C.c_size_t, C.c_char_p]),
         "saber_program_add_copy": (I, [P, P, P, C.c_size_t, C.c_char_p]),
         "saber_program_add_allreduce": (I, [P, C.POINTER(AllReduceParams), C.c_char_p]),
+        "saber_set_pdl": (None, [I]),
+        "saber_get_pdl": (I, []),
         "saber_moe_route_launch": (I, [C.POINTER(MoeRouteParams), S]),
         "saber_moe_combine_launch": (I, [C.POINTER(MoeCombineParams), S]),
         "saber_moe_gather_launch": (I, [P, P, I, P, P, P, P, I, I, I, S]),

@@ -80,6 +80,9 @@ def timed_decode(model: HybridModel, bucket, seqs_state: list, steps: int, warmu
 
 def run_benchmark(args, ClockSampler):
     rank, local, world = _dist_setup(args.gpus)
+    if getattr(args, "pdl", -1) >= 0:
+        from ..ops import native as _N
+        _N.set_pdl(args.pdl)
     dev = torch.device("cuda", local)
     cfg = C.by_name(args.model)
     streams, W = args.streams, args.width

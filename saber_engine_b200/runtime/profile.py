@@ -71,8 +71,9 @@ def main(argv=None) -> int:
                         seed=1, oracle_p=0.75)
     bp = (args.ctx + 512) // cfg.page_tokens
     b = model.build_bucket("decode", args.batch, args.width)
-    seqs = [SeqStep([1] * args.width, args.ctx, j + 1, 3, list(range(1 + j * bp, 1 + (j + 1) * bp)), uid=j)
-            for j in range(args.batch)]
+    g = torch.Generator().manual_seed(3)
+    seqs = [SeqStep(torch.randint(0, cfg.vocab, (args.width,), generator=g).tolist(), args.ctx, j + 1, 3,
+                    list(range(1 + j * bp, 1 + (j + 1) * bp)), uid=j) for j in range(args.batch)]
     if args.walk:
         print(format_profile(profile_bucket(model, b, seqs)))
         return 0

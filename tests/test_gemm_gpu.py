@@ -9,7 +9,7 @@ from saber_engine_b200.ops import reference as R
 pytestmark = pytest.mark.gpu
 
 
-def _case(M, N, K, bits, splits=None, seed=0):
+def _case(M, N, K, bits, splits=None, seed=0, coop=0):
     g = torch.Generator().manual_seed(seed)
     w = torch.randn(N, K, generator=g) * 0.02
     x = torch.randn(M, K, generator=g)
@@ -20,7 +20,7 @@ def _case(M, N, K, bits, splits=None, seed=0):
     qw = F.QuantWeight.from_int(wq, ws, bits, dev)
     m_pad = L.padded_rows(M)
     qa = F.QuantAct(L.tile_act_int8(aq, m_pad).to(dev), torch.cat([asc, torch.zeros(m_pad - M)]).to(dev), M, K)
-    out = F.gemm_i8(qw, qa, splits=splits)
+    out = F.gemm_i8(qw, qa, splits=splits, coop=coop)
     torch.cuda.synchronize()
     F.scratch(dev).check()
     got = out.float().cpu()
@@ -46,6 +46,13 @@ def test_gemm_split_k_exact_and_counters_rezeroed():
     assert torch.equal(a, b)
     sc = F.scratch(torch.device("cuda"))
     assert int(sc.counters.abs().max().item()) == 0
+    # the last-arriver form (what a grid larger than the SM count falls back to) gives the same bytes
+    c = _case(40, 384, 4096, 4, splits=4, seed=1, coop=-1)
+    assert torch.equal(a, c)
+    assert int(sc.counters.abs().max().item()) == 0
+    d = _case(72, 304, 2048, 4, splits=8, seed=2)       # ragged N, more splits than row residues of some tiles
+    e = _case(72, 304, 2048, 4, splits=8, seed=2, coop=-1)
+    assert torch.equal(d, e)
 
 
 def test_gemm_auto_splits_decode_shape():

@@ -134,3 +134,58 @@ def test_moe_model_prefill_and_spec_decode():
     assert res2.tokens == res.tokens
     assert decode(2, b2, res2.tokens[0][0], res2.drafts[0], 5) == plain
     model.scratch.check()
+
+
+@pytest.mark.parametrize("nranks,M", [(2, 9), (4, 72)])
+def test_expert_parallel_combine_push(nranks, M):
+    """Expert parallelism on ONE GPU with emulated ranks: every rank routes the replicated rows,
+    runs its own experts and pushes its partial sums into every rank's receive region; afterwards
+    every rank's add-norm sums the ranks.  All producers run before any consumer."""
+    import ctypes as Ct
+    from saber_engine_b200.models.moe_block import MoeWorkspace, add_moe_ops
+    from saber_engine_b200.models.moe_weights import random_moe_layer
+    from saber_engine_b200.models.reference_hybrid import moe_mlp_ref
+    from saber_engine_b200.ops import reference as R
+    from saber_engine_b200.parallel.symm import SymmetricComm
+    cfg = _cfg()
+    H = cfg.hidden
+    full = _moe_layer(cfg, seed=11)
+    group = SymmetricComm.local_group(nranks, "cuda", max_elems=128 * H, rows_max=128, hidden=H)
+    for g_ in group:
+        g_._local = True
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(M, H, generator=gen).to(torch.bfloat16)
+    res = torch.randn(M, H, generator=gen).to(torch.bfloat16)
+    nw = torch.randn(H, generator=gen) * 0.1
+    qa = F.plain_quant(x.cuda())
+    sc = F.scratch("cuda")
+    keep, nts = [], []
+    for r, comm in enumerate(group):
+        gg = torch.Generator(device="cuda").manual_seed(11)
+        moe = random_moe_layer(cfg, nranks, r, torch.device("cuda"), gg, 0.02)
+        ws = MoeWorkspace(cfg, moe["e_n"], M, "cuda", moe["shared_inter"])
+        dummy = torch.zeros(M, H, dtype=torch.bfloat16, device="cuda")
+        prog = N.Program(f"moe-r{r}")
+        nts.append(add_moe_ops(prog, ws, cfg, moe, qa, dummy, sc, "moe", comm, 0))
+        prog.run()
+        keep.append((moe, ws, dummy, prog))
+    torch.cuda.synchronize()
+    sc.check()
+    ref_delta = moe_mlp_ref(cfg, full, x.float(), tp=nranks)
+    res_ref, n_ref = R.add_rms(ref_delta, res, nw)
+    first = None
+    for r, comm in enumerate(group):
+        res_d = res.cuda().clone()
+        qa_out = F.QuantAct.alloc(M, H, "cuda")
+        normed = torch.zeros(M, H, dtype=torch.bfloat16, device="cuda")
+        p = F.row_params(M, H, a=None, res=res_d, w=nw.cuda(), w_offset=1.0, qa=qa_out, out=normed)
+        comm.row_tp(p, 0, nts[r], H // 256)
+        N.check(N.lib().saber_row_producer_launch(N.ROW_ADD_RMS, Ct.byref(p), N.stream_handle()), "consumer")
+        torch.cuda.synchronize()
+        comm.check()
+        assert torch.allclose(res_d.float().cpu(), res_ref.float(), atol=3e-2, rtol=2e-2), r
+        if first is None:
+            first = normed.clone()
+        else:
+            assert torch.equal(normed, first)
+    group[0].close()
