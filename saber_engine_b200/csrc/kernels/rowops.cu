@@ -252,6 +252,176 @@ __global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpPa
   if (p.q) quant_store_row(h, K, m, p.M_pad, amax, p.q, p.scale);
 }
 
+// Register-resident form of ADD_RMS / SILU_MUL / GATE_SIG / PLAIN: a thread owns whole 16-value
+// chunks (the unit of the tiled int8 store) and keeps them in registers between the passes, so the
+// kernel needs no dynamic shared memory and its CTAs fit beside a resident GEMM CTA: the GEMM that
+// follows a row kernel is launched programmatically, gets resident while the row kernel runs and
+// streams its first weight tiles meanwhile.  MAXC bounds the chunks per thread: K <= MAXC * 4096.
+template <int MODE, int MAXC>
+__global__ void __launch_bounds__(kRowThreads) row_reg_kernel(const RowOpParams p) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[32];
+  const int m = blockIdx.x;
+  const int K = p.K;
+  if (p.m_live != nullptr && m >= *p.m_live) return;
+  const int nchunk = K >> 4;
+  if (m >= p.M) {  // padding row: zeros
+    if (p.q) {
+      for (int ch = threadIdx.x; ch < nchunk; ch += kRowThreads) {
+        const int kb = ch >> 3, c = ch & 7;
+        int8_t* dst = p.q + (static_cast<size_t>(kb) * p.M_pad + m) * 128 + (((c ^ (m & 7)) & 7) << 4);
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
+      if (threadIdx.x == 0) p.scale[m] = 0.f;
+    }
+    return;
+  }
+  uint32_t tp_par = 0;
+  if (MODE == kRowAddRms && p.tp_nranks > 1) {
+    const uint32_t seq = *p.tp_seq_base + static_cast<uint32_t>(p.tp_site) + 1u;
+    tp_par = seq & 1u;
+    const int nflags = p.tp_nranks * p.tp_tiles_n;
+    for (int f = threadIdx.x; f < nflags; f += kRowThreads) {
+      const int src = f / p.tp_tiles_n, tn = f - src * p.tp_tiles_n;
+      const int tile_id = (m / p.tp_nt) * p.tp_tiles_n + tn;
+      const uint32_t* flag = p.tp_flags + (static_cast<size_t>(tp_par) * p.tp_nranks + src) * kTpMaxTiles + tile_id;
+      const long long t0 = clock64();
+      uint32_t spins = 0;
+      while (true) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (static_cast<int32_t>(v - seq) >= 0) break;
+        if ((++spins & 1023u) == 0u && clock64() - t0 > kWaitLimitCycles) {
+          if (p.err) atomicCAS(p.err, 0u, static_cast<uint32_t>(kErrWaitPeer));
+          break;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  float hv[MAXC][16];   // the row's values of this thread (ADD_RMS: first the sums, then the normed row)
+  float amax = 0.f;
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int ch = threadIdx.x + c * kRowThreads;
+    if (ch >= nchunk) continue;
+    const int k0 = ch << 4;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int k = k0 + half * 8;
+      float x[8];
+      if (MODE == kRowAddRms) {
+        if (p.tp_nranks > 1) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[i] = 0.f;
+          for (int src = 0; src < p.tp_nranks; ++src) {   // fixed order: identical sums on every rank
+            const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(
+                p.tp_recv + ((static_cast<size_t>(tp_par) * p.tp_nranks + src) * p.tp_rows + m) * p.tp_ld + k));
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = __bfloat1622float2(h2[i]);
+              x[2 * i] += f.x;
+              x[2 * i + 1] += f.y;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[i] = __bfloat162float(__float2bfloat16(x[i]));
+        } else if (p.a) {
+          load8(p.a + static_cast<size_t>(m) * p.lda + k, x);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[i] = 0.f;
+        }
+        if (p.res) {
+          float r[8];
+          load8(p.res + static_cast<size_t>(m) * p.ldres + k, r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[i] += r[i];
+          store8(p.res + static_cast<size_t>(m) * p.ldres + k, x);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+      } else {
+        if (MODE == kRowSiluMul) {
+          float g[8], u[8];
+          load8(p.a + static_cast<size_t>(m) * p.lda + k, g);
+          load8(p.a + static_cast<size_t>(m) * p.lda + K + k, u);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[i] = silu_f(g[i]) * u[i];
+        } else if (MODE == kRowGateSig) {
+          float a[8], b[8];
+          load8(p.a + static_cast<size_t>(m) * p.lda + k, a);
+          load8(p.b + static_cast<size_t>(m) * p.ldb + k, b);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[i] = a[i] * sigmoid_f(b[i]);
+        } else {
+          load8(p.a + static_cast<size_t>(m) * p.lda + k, x);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          x[i] = __bfloat162float(__float2bfloat16(x[i]));
+          amax = fmaxf(amax, fabsf(x[i]));
+        }
+        if (p.out) store8(p.out + static_cast<size_t>(m) * p.ldout + k, x);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) hv[c][half * 8 + i] = x[i];
+    }
+  }
+  if (MODE == kRowAddRms) {
+    ss = block_reduce<false>(ss, red);
+    const float rstd = rsqrtf(ss / static_cast<float>(K) + p.eps);
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = threadIdx.x + c * kRowThreads;
+      if (ch >= nchunk) continue;
+      const int k0 = ch << 4;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float x[8];
+        const float4 w0 = *reinterpret_cast<const float4*>(p.w + k0 + half * 8);
+        const float4 w1 = *reinterpret_cast<const float4*>(p.w + k0 + half * 8 + 4);
+        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          x[i] = __bfloat162float(__float2bfloat16(hv[c][half * 8 + i] * rstd * (wv[i] + p.w_offset)));
+          amax = fmaxf(amax, fabsf(x[i]));
+          hv[c][half * 8 + i] = x[i];
+        }
+        if (p.out) store8(p.out + static_cast<size_t>(m) * p.ldout + k0 + half * 8, x);
+      }
+    }
+  }
+  amax = block_reduce<true>(amax, red);
+  if (p.q) {
+    const float inv = amax > 0.f ? 127.f / amax : 0.f;
+    if (threadIdx.x == 0) p.scale[m] = amax / 127.f;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = threadIdx.x + c * kRowThreads;
+      if (ch >= nchunk) continue;
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          int qi = __float2int_rn(hv[c][i * 4 + j] * inv);
+          qi = max(-127, min(127, qi));
+          word |= (static_cast<uint32_t>(qi) & 0xFFu) << (8 * j);
+        }
+        w[i] = word;
+      }
+      const int kb = ch >> 3, cc = ch & 7;
+      int8_t* dst = p.q + (static_cast<size_t>(kb) * p.M_pad + m) * 128 + (((cc ^ (m & 7)) & 7) << 4);
+      *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
 // out[m, :] = table[ids[m], :]   (bf16 rows, 16-byte vectors); ids outside [0, vocab) give zeros.
 __global__ void embed_gather_kernel(const __nv_bfloat16* table, const int32_t* ids,
                                     __nv_bfloat16* out, int M, int H, int vocab_lo, int vocab_n,
@@ -300,6 +470,25 @@ extern "C" int saber_row_producer_launch(int mode, const saber::RowOpParams* p, 
   using namespace saber;
   if ((p->K & 127) || p->M_pad < p->M) return static_cast<int>(cudaErrorInvalidValue);
   const int rows = p->q ? p->M_pad : p->M;
+  // register-resident forms (no dynamic shared memory) wherever the row fits the chunk budget
+#define SABER_ROW_REG(MODE, MAXC)                                                                \
+  if (mode == MODE && p->K <= MAXC * 4096) {                                                     \
+    static bool carve = false;                                                                   \
+    if (!carve) {   /* same shared-memory carve-out as the GEMM, so both can share an SM */      \
+      cudaFuncSetAttribute(row_reg_kernel<MODE, MAXC>, cudaFuncAttributePreferredSharedMemoryCarveout, \
+                           cudaSharedmemCarveoutMaxShared);                                      \
+      carve = true;                                                                              \
+    }                                                                                            \
+    saber::launch(row_reg_kernel<MODE, MAXC>, dim3(rows), dim3(kRowThreads), 0, stream, 0, *p);  \
+    return static_cast<int>(cudaGetLastError());                                                 \
+  }
+  SABER_ROW_REG(kRowAddRms, 2)
+  SABER_ROW_REG(kRowSiluMul, 2)
+  SABER_ROW_REG(kRowSiluMul, 5)
+  SABER_ROW_REG(kRowGateSig, 2)
+  SABER_ROW_REG(kRowPlain, 2)
+  SABER_ROW_REG(kRowPlain, 7)
+#undef SABER_ROW_REG
   size_t smem = static_cast<size_t>(p->K) * 2 + (mode == kRowAddRms ? static_cast<size_t>(p->K) * 4 : 0);
 #define SABER_ROW_CASE(MODE)                                                                     \
   case MODE: {                                                                                   \
