@@ -95,6 +95,30 @@ __global__ void __launch_bounds__(128) gdn_conv_commit_kernel(const GdnConvParam
 }
 
 // ---------------------------------------------------------------------------------- recurrence
+// Packed fp32 pairs: sm_100 issues two fp32 FMAs per instruction (fma.rn.f32x2), which halves the
+// instruction count of the state update -- the kernel is bound by issue slots, not by memory.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ float sum2(f32x2 v) {
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+  return lo + hi;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 // grid (HV * VS, nseq); block = 2 * (128 / VS) threads; thread = (v row, k half).
 // Rows are staged in shared memory in batches of kRecBatch (all loads of a batch are issued
 // together, so the per-row loop touches no global memory except its one output element).
@@ -127,33 +151,52 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
                             static_cast<size_t>(h) * VS + vs) * stash_stride;
   const size_t stash_row = static_cast<size_t>(p.HV) * VS * stash_stride;
 
-  float S[64];
+  f32x2 S[32];   // this thread's 64 state values as packed pairs
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    const float4 t = reinterpret_cast<const float4*>(sp)[i];
-    S[4 * i] = t.x; S[4 * i + 1] = t.y; S[4 * i + 2] = t.z; S[4 * i + 3] = t.w;
+    const ulonglong2 t = reinterpret_cast<const ulonglong2*>(sp)[i];
+    S[2 * i] = t.x;
+    S[2 * i + 1] = t.y;
   }
   const float neg_a = -__expf(p.A_log[h]);
   const float dtb = p.dt_bias[h];
 
   auto apply = [&](const float* kv, const float* qv, float vval, float g, float beta,
                    bool want_o) -> float {
+    const ulonglong2* kv2 = reinterpret_cast<const ulonglong2*>(kv);   // 16-byte aligned rows
+    const ulonglong2* qv2 = reinterpret_cast<const ulonglong2*>(qv);
     const float decay = __expf(g);
-    float dot = 0.f;
+    const f32x2 dec2 = pack2(decay, decay);
+    f32x2 acc[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      S[i] *= decay;
-      dot += S[i] * kv[i];
+    for (int i = 0; i < 16; ++i) {
+      const ulonglong2 kk = kv2[i];
+      S[2 * i] = mul2(S[2 * i], dec2);
+      S[2 * i + 1] = mul2(S[2 * i + 1], dec2);
+      acc[(2 * i) & 3] = fma2(S[2 * i], kk.x, acc[(2 * i) & 3]);
+      acc[(2 * i + 1) & 3] = fma2(S[2 * i + 1], kk.y, acc[(2 * i + 1) & 3]);
     }
+    float dot = (sum2(acc[0]) + sum2(acc[1])) + (sum2(acc[2]) + sum2(acc[3]));
     dot += __shfl_xor_sync(0xffffffffu, dot, 1);
     const float u = (vval - dot) * beta;
-    float o = 0.f;
+    const f32x2 u2 = pack2(u, u);
+    f32x2 oac[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      S[i] += u * kv[i];
-      if (want_o) o += S[i] * qv[i];
+    for (int i = 0; i < 16; ++i) {
+      const ulonglong2 kk = kv2[i];
+      S[2 * i] = fma2(u2, kk.x, S[2 * i]);
+      S[2 * i + 1] = fma2(u2, kk.y, S[2 * i + 1]);
+      if (want_o) {
+        const ulonglong2 qq = qv2[i];
+        oac[(2 * i) & 3] = fma2(S[2 * i], qq.x, oac[(2 * i) & 3]);
+        oac[(2 * i + 1) & 3] = fma2(S[2 * i + 1], qq.y, oac[(2 * i + 1) & 3]);
+      }
     }
-    if (want_o) o += __shfl_xor_sync(0xffffffffu, o, 1);
+    float o = 0.f;
+    if (want_o) {
+      o = (sum2(oac[0]) + sum2(oac[1])) + (sum2(oac[2]) + sum2(oac[3]));
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+    }
     return o;
   };
 
@@ -175,7 +218,7 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
     for (int r = 0; r < shift; ++r) apply(&ks[r][kh * KP], nullptr, vsm[r][vloc], gsm[r], bsm[r], false);
 #pragma unroll
     for (int i = 0; i < 16; ++i)
-      reinterpret_cast<float4*>(sp)[i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+      reinterpret_cast<ulonglong2*>(sp)[i] = make_ulonglong2(S[2 * i], S[2 * i + 1]);
     __syncthreads();
   }
 
@@ -225,7 +268,7 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
   if (p.commit && n > 0) {
 #pragma unroll
     for (int i = 0; i < 16; ++i)
-      reinterpret_cast<float4*>(sp)[i] = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+      reinterpret_cast<ulonglong2*>(sp)[i] = make_ulonglong2(S[2 * i], S[2 * i + 1]);
   }
 }
 

@@ -44,6 +44,7 @@
 #include "gemm_i8_noalloc.h"
 #include "ptx_sm100.cuh"
 #include <cuda_bf16.h>
+#include <type_traits>
 
 namespace saber {
 
@@ -64,8 +65,11 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const bool dbg_on = p.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-#define SABER_STAMP(i) do { if (dbg_on) p.dbg[i] = globaltimer_ns(); } while (0)
+  // debug stamps: CTA (0,0,0) only, or (dbg_mma == 2) 16 slots for every CTA
+  const bool dbg_all = p.dbg != nullptr && p.dbg_mma == 2;
+  const bool dbg_on = p.dbg != nullptr && (dbg_all || (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0));
+  const size_t dbg_base = dbg_all ? 16u * ((static_cast<size_t>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : 0u;
+#define SABER_STAMP(i) do { if (dbg_on) p.dbg[dbg_base + (i)] = globaltimer_ns(); } while (0)
   if (threadIdx.x == 0) SABER_STAMP(0);
   // Programmatic dependent launch: this kernel may be running ahead of its predecessor, so only
   // WEIGHTS (which no kernel writes) are touched before pdl_wait().  It never triggers its own
@@ -109,6 +113,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
   const uint32_t bar_ufree = smem_u32(&bars[2 * kMaxStages + kUBufs]);  // kUBufs
   const uint32_t bar_acc = smem_u32(&bars[2 * kMaxStages + 2 * kUBufs]);
   constexpr uint32_t kTmemCols = 256;
+  constexpr int kMaxSplits = 8;   // split-K factor the reduction is unrolled for
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -339,11 +344,13 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
         }
         if (tp) tp_signal(tile_m * gridDim.x + tile_n);
       } else {
-        // each split writes its own partial tile [split][m][n] with plain vector stores; the
-        // last-arriving CTA of the tile adds the splits (integers: exact in any order)
-        const size_t split_stride = static_cast<size_t>(p.M_pad) * p.N_pad;
+        // each split writes its own partial tile; inside a (split, tile) block the 16-byte group of
+        // four columns c4 of row r sits at (c4 * 128 + r) * 16 bytes, so the 32 lanes of a warp
+        // (32 consecutive rows) store -- and later load -- 512 contiguous bytes
+        const int tile_lin = tile_m * gridDim.x + tile_n;
+        const size_t blk_stride = 128u * 256u;   // ints per (split, tile) block
+        int32_t* wblk = p.ws + (static_cast<size_t>(split) * (gridDim.x * gridDim.y) + tile_lin) * blk_stride;
         if (warp_live) {
-          int32_t* wrow = p.ws + split * split_stride + static_cast<size_t>(live ? m : m0) * p.N_pad + n0;
           for (int c = 0; c < ncols; c += 32) {
             uint32_t r[32];
             tmem_ld32(t_lane + c, r);
@@ -351,17 +358,18 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
             if (live) {
 #pragma unroll
               for (int j = 0; j < 8; ++j)
-                *reinterpret_cast<uint4*>(wrow + c + 4 * j) =
+                *reinterpret_cast<uint4*>(wblk + (static_cast<size_t>((c >> 2) + j) * 128 + row) * 4) =
                     make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
             }
           }
         }
         __threadfence();
         named_bar_sync(1, 128);
-        const int tile_id = tile_m * gridDim.x + tile_n;
+        if (tid_t == 0) SABER_STAMP(10);
+        const int tile_id = tile_lin;
         // Two ways to add the splits.  Cooperative (every CTA of the grid is resident, the launcher
         // guarantees it): all splits of a tile wait for one another and each reduces the rows
-        // r = split (mod splits), so the pass is spread over `splits` SMs.  Otherwise the last
+        // c4 = split (mod splits) -- four-column groups -- so the pass is spread over `splits` SMs.  Otherwise the last
         // arriver reduces the whole tile alone.
         int part = 0, nparts = 1;
         if (p.coop) {
@@ -388,73 +396,78 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
           is_last_s = (old == static_cast<uint32_t>(p.splits - 1)) ? 1u : 0u;
         }
         named_bar_sync(1, 128);
+        if (tid_t == 0) SABER_STAMP(11);
         if (is_last_s) {
           __threadfence();
-          // all 128 threads share the tile: a thread takes 8 features of a row at a time, four
-          // such items per round with every load of the round issued before any is used (this
-          // pass runs in ONE CTA while the rest of the grid has left: it is latency that counts)
-          const int vec_per_row = ncols >> 3;
-          const int rows_part = mt > part ? (mt - part + nparts - 1) / nparts : 0;
-          const int n_items = rows_part * vec_per_row;
-          constexpr int kIlp = 4;
+          // items = (four-column group of this part, live row), rows fastest: consecutive threads
+          // read consecutive 16-byte groups.  All splits of an item are loaded before any is
+          // used, two items per round: one memory round trip per round.
+          const int n_c4 = ncols >> 2;
+          const int c4_part = n_c4 > part ? (n_c4 - part + nparts - 1) / nparts : 0;
+          const int n_items = c4_part * mt;
+          const size_t tiles_all = static_cast<size_t>(gridDim.x) * gridDim.y;
+          const int32_t* rblk = p.ws + static_cast<size_t>(tile_lin) * blk_stride;
+          auto reduce_items = [&](auto ilp_c, auto maxs_c) {
+          constexpr int kIlp = decltype(ilp_c)::value;
+          constexpr int kMaxS = decltype(maxs_c)::value;
           for (int base = tid_t; base < n_items; base += 128 * kIlp) {
-            int4 x0[kIlp], x1[kIlp];
-            int rr[kIlp], cc[kIlp];
-            float asc[kIlp];
+            int4 y[kIlp][kMaxS];
+            int rr[kIlp], c4[kIlp];
 #pragma unroll
             for (int u = 0; u < kIlp; ++u) {
               const int idx = min(base + u * 128, n_items - 1);
-              const int ri = idx / vec_per_row;
-              rr[u] = part + ri * nparts;
-              cc[u] = (idx - ri * vec_per_row) << 3;
-              x0[u] = make_int4(0, 0, 0, 0);
-              x1[u] = make_int4(0, 0, 0, 0);
-              asc[u] = p.a_scale[m0 + rr[u]];
-            }
-            for (int sp = 0; sp < p.splits; ++sp) {
-              int4 y0[kIlp], y1[kIlp];
+              const int ci = idx / mt;
+              rr[u] = idx - ci * mt;
+              c4[u] = part + ci * nparts;
 #pragma unroll
-              for (int u = 0; u < kIlp; ++u) {
-                const int32_t* wp = p.ws + sp * split_stride + static_cast<size_t>(m0 + rr[u]) * p.N_pad + n0 + cc[u];
-                y0[u] = __ldcg(reinterpret_cast<const int4*>(wp));
-                y1[u] = __ldcg(reinterpret_cast<const int4*>(wp) + 1);
-              }
-#pragma unroll
-              for (int u = 0; u < kIlp; ++u) {
-                x0[u].x += y0[u].x; x0[u].y += y0[u].y; x0[u].z += y0[u].z; x0[u].w += y0[u].w;
-                x1[u].x += y1[u].x; x1[u].y += y1[u].y; x1[u].z += y1[u].z; x1[u].w += y1[u].w;
-              }
+              for (int sp = 0; sp < kMaxS; ++sp)
+                if (sp < p.splits)
+                  y[u][sp] = __ldcg(reinterpret_cast<const int4*>(
+                      rblk + static_cast<size_t>(sp) * tiles_all * blk_stride + (static_cast<size_t>(c4[u]) * 128 + rr[u]) * 4));
             }
 #pragma unroll
             for (int u = 0; u < kIlp; ++u) {
-              if (base + u * 128 >= n_items) break;
-              const int c = cc[u];
-              const int acc[8] = {x0[u].x, x0[u].y, x0[u].z, x0[u].w, x1[u].x, x1[u].y, x1[u].z, x1[u].w};
-              uint32_t pk[4];
+              if (base + u * 128 >= n_items) continue;
+              int4 x = make_int4(0, 0, 0, 0);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const __nv_bfloat162 b2 = __floats2bfloat162_rn(
-                    static_cast<float>(acc[2 * j]) * (asc[u] * w_scale_s[c + 2 * j]),
-                    static_cast<float>(acc[2 * j + 1]) * (asc[u] * w_scale_s[c + 2 * j + 1]));
-                pk[j] = *reinterpret_cast<const uint32_t*>(&b2);
-              }
-              __nv_bfloat16* o = p.out + static_cast<size_t>(m0 + rr[u]) * p.ldo + n0 + c;
+              for (int sp = 0; sp < kMaxS; ++sp)
+                if (sp < p.splits) { x.x += y[u][sp].x; x.y += y[u][sp].y; x.z += y[u][sp].z; x.w += y[u][sp].w; }
+              const int c = c4[u] << 2;
+              const float asc = p.a_scale[m0 + rr[u]];
+              const __nv_bfloat162 b0 = __floats2bfloat162_rn(static_cast<float>(x.x) * (asc * w_scale_s[c]),
+                                                              static_cast<float>(x.y) * (asc * w_scale_s[c + 1]));
+              const __nv_bfloat162 b1 = __floats2bfloat162_rn(static_cast<float>(x.z) * (asc * w_scale_s[c + 2]),
+                                                              static_cast<float>(x.w) * (asc * w_scale_s[c + 3]));
+              const uint2 pk = make_uint2(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1));
               if (tp) {
-                if (n0 + c < p.N) tp_push16(m0 + rr[u], n0 + c, make_uint4(pk[0], pk[1], pk[2], pk[3]));
-              } else if (n0 + c + 8 <= p.N) {
-                *reinterpret_cast<uint4*>(o) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                if (n0 + c < p.N) {
+                  const size_t off = ((static_cast<size_t>(tp_par) * p.tp_nranks + p.tp_rank) * p.tp_rows + m0 + rr[u]) * p.tp_ld + n0 + c;
+                  for (int peer = 0; peer < p.tp_nranks; ++peer)
+                    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.tp_recv[peer]) + off) = pk;
+                }
               } else {
-                const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(pk);
-                for (int j = 0; j < 8; ++j)
-                  if (n0 + c + j < p.N) o[j] = pb[j];
+                __nv_bfloat16* o = p.out + static_cast<size_t>(m0 + rr[u]) * p.ldo + n0 + c;
+                if (n0 + c + 4 <= p.N) {
+                  *reinterpret_cast<uint2*>(o) = pk;
+                } else {
+                  const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&pk);
+                  for (int j = 0; j < 4; ++j)
+                    if (n0 + c + j < p.N) o[j] = pb[j];
+                }
               }
             }
           }
+          };
+          // the budget is ~16 loads in flight per thread: more items per round when there are few splits
+          if (p.splits <= 2) reduce_items(std::integral_constant<int, 8>{}, std::integral_constant<int, 2>{});
+          else if (p.splits <= 4) reduce_items(std::integral_constant<int, 4>{}, std::integral_constant<int, 4>{});
+          else reduce_items(std::integral_constant<int, 2>{}, std::integral_constant<int, 8>{});
           if (!p.coop) {
             if (tid_t == 0) p.counters[tile_id] = 0u;
             if (tp) tp_signal(tile_id);
           }
         }
+        if (tid_t == 0) SABER_STAMP(12);
         if (p.coop) {
           // second round of arrivals: the CTA that finishes last re-arms the counter and, in
           // tensor-parallel mode, raises the tile's flags (every slice has been pushed by then)
@@ -495,7 +508,7 @@ extern "C" int saber_gemm_i8_smem_bytes_w(int nt, int stages, int w4) {
 extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cudaStream_t stream) {
   using namespace saber;
   if (p->nt < 16 || p->nt > 128 || (p->nt & 15) || (p->K & 127) || p->K <= 0 || p->M <= 0 ||
-      (p->N_pad & 255) || p->splits < 1 || (p->M_pad % p->nt) != 0 || (p->ldo & 7))
+      (p->N_pad & 255) || p->splits < 1 || p->splits > 8 || (p->M_pad % p->nt) != 0 || (p->ldo & 7))
     return static_cast<int>(cudaErrorInvalidValue);
   const int KB = p->K >> 7;
   const int kb_per = (KB + p->splits - 1) / p->splits;
@@ -560,8 +573,8 @@ extern "C" int saber_gemm_i8_noalloc(const uint8_t* w, const float* w_scale, con
                                      int w4, int ldo, cudaStream_t stream) {
   using namespace saber;
   if (splits < 1 || M_pad <= 0 || N_pad <= 0) return kNoAllocBadArgs;
-  const size_t need = static_cast<size_t>(splits) * static_cast<size_t>(M_pad) * static_cast<size_t>(N_pad);
   const size_t tiles = static_cast<size_t>(N_pad / 256) * static_cast<size_t>((M + nt - 1) / (nt > 0 ? nt : 1));
+  const size_t need = static_cast<size_t>(splits) * tiles * 128u * 256u;   // one 128 x 256 block per (split, tile)
   if ((splits > 1 && need > kNoAllocPartialInts) || tiles > kNoAllocCounterWords) return kNoAllocTooLarge;
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);

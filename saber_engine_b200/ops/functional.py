@@ -101,7 +101,7 @@ def pick_splits(n_tiles: int, m_tiles: int, kb: int, sms: int = 148) -> int:
     ctas = n_tiles * m_tiles
     if ctas * 2 > sms or kb < 8:
         return 1
-    s = min(sms // ctas, max(1, kb // 4), 16)
+    s = min(sms // ctas, max(1, kb // 4), 8)
     while s > 1 and (s - 1) * math.ceil(kb / s) >= kb:
         s -= 1
     return max(1, s)
@@ -115,8 +115,8 @@ def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,
     m_tiles = (a.M + nt - 1) // nt
     if splits is None:
         splits = pick_splits(w.N_pad // L.TILE_N, m_tiles, w.K // 128)
-    if splits > 1:
-        assert splits * a.M_pad * w.N_pad <= sc.capacity, "split-K scratch too small"
+    if splits > 1:   # one 128 x 256 int32 block per (split, tile)
+        assert splits * m_tiles * (w.N_pad // L.TILE_N) * 32768 <= sc.capacity, "split-K scratch too small"
     p = N.GemmI8Params()
     p.w, p.w_scale, p.a, p.a_scale = w.tiles.data_ptr(), w.scale.data_ptr(), a.q.data_ptr(), a.scale.data_ptr()
     p.out, p.ws, p.counters, p.err = out.data_ptr(), sc.ws.data_ptr(), sc.counters.data_ptr(), sc.err.data_ptr()
