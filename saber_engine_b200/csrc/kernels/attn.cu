@@ -15,6 +15,7 @@
 // The contraction here runs on warp-level mma (m16n8k16 bf16): decode attention is bound by the
 // KV bytes it streams, not by tensor throughput.
 #include "launch.cuh"
+#include "ptx_sm100.cuh"
 #include "attn.h"
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -95,20 +96,19 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t (&r)[4]) {
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(addr));
 }
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
-                                         uint32_t b1) {
+__device__ __forceinline__ void mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
-// 16 fp8 e4m3 (one uint4) -> 16 bf16 (two uint4)
-__device__ __forceinline__ void fp8x16_to_bf16(const uint4 in, uint4& lo, uint4& hi) {
+// 16 fp8 e4m3 (one uint4) -> 16 fp16 (two uint4): one conversion instruction per pair, exact
+__device__ __forceinline__ void fp8x16_to_f16(const uint4 in, uint4& lo, uint4& hi) {
   const uint32_t w[4] = {in.x, in.y, in.z, in.w};
   uint32_t o[8];
 #pragma unroll
@@ -117,8 +117,7 @@ __device__ __forceinline__ void fp8x16_to_bf16(const uint4 in, uint4& lo, uint4&
     for (int h = 0; h < 2; ++h) {
       const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(
           static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * h)) & 0xFFFFu), __NV_E4M3);
-      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
-      o[2 * i + h] = pack_bf16(f.x, f.y);
+      o[2 * i + h] = static_cast<uint32_t>(hr.x) | (static_cast<uint32_t>(hr.y) << 16);
     }
   }
   lo = make_uint4(o[0], o[1], o[2], o[3]);
@@ -126,17 +125,27 @@ __device__ __forceinline__ void fp8x16_to_bf16(const uint4 in, uint4& lo, uint4&
 }
 
 constexpr int kAttnMaxWarps = 6;
+constexpr int kAttnRing = 8;          // raw fp8 pages in flight per CTA (8 KiB each)
+constexpr int kAttnOpBytes = 32768;   // one operand buffer: K [32 keys][256] fp16 | V [32 keys][256] fp16
 
+// One CTA = one (sequence, KV head, 16-token query tile, KV split); one warp per query head of the
+// GQA group.  The raw fp8 pages of the split stream through a ring in shared memory, filled by
+// bulk copies that complete on mbarriers (eight pages in flight per CTA: the kernel is bound by
+// how much it keeps in flight, not by arithmetic).  Each iteration takes two pages: all threads
+// widen them to fp16 into one of two operand buffers, one barrier, then every warp runs
+// S = Q K^T (16 x 32), the online softmax and O += P V on its own head.
 __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const AttnParams p,
                                                                         const int hpb,
                                                                         const int hgroups) {
   pdl_wait();
-  extern __shared__ __align__(16) uint8_t attn_smem[];
-  // layout: Q [hpb][16][256] bf16 | K [16][256] bf16 | V [16][256] bf16, 512-byte rows, 16-byte
-  // chunk index XOR (row & 7)
+  extern __shared__ __align__(128) uint8_t attn_smem[];
+  __shared__ uint64_t full_bar[kAttnRing];
+  // layout: Q [hpb][16][256] fp16 | 2 operand buffers | raw ring; 512-byte rows, 16-byte chunk
+  // index XOR (row & 7)
   const uint32_t q_s = static_cast<uint32_t>(__cvta_generic_to_shared(attn_smem));
-  const uint32_t k_s = q_s + hpb * 8192;
-  const uint32_t v_s = k_s + 8192;
+  const uint32_t op_s = q_s + hpb * 8192;
+  const uint32_t ring_s = op_s + 2 * kAttnOpBytes;
+  const uint32_t bar_s = static_cast<uint32_t>(__cvta_generic_to_shared(full_bar));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -157,15 +166,47 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
   const int pages = (kmax + kPageTokens - 1) / kPageTokens;
   const int per = (pages + p.splits - 1) / p.splits;
   const int pg0 = sp * per, pg1 = min(pages, pg0 + per);
+  const int npages = max(0, pg1 - pg0);
+  const int key_end = pg1 * kPageTokens;   // keys at or beyond belong to the next split
 
-  // ---- Q tile
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kAttnRing; ++i) mbar_init(bar_s + 8 * i, 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  auto issue = [&](int i) {   // page i of this split -> ring stage i % kAttnRing (thread 0 only)
+    const int st = i % kAttnRing;
+    int blk = pg0 + i < p.max_blocks ? p.block_table[static_cast<size_t>(b) * p.max_blocks + pg0 + i] : -1;
+    if (blk < 0 || (p.n_blocks > 0 && blk >= p.n_blocks)) {   // never follow a bad table entry
+      if (p.err) atomicCAS(p.err, 0u, static_cast<uint32_t>(kErrBadIndex));
+      blk = 0;
+    }
+    const uint8_t* src = p.kv_cache + (static_cast<size_t>(blk) * p.nkv + kvh) * (2 * kPageTokens * kHeadDim);
+    mbar_arrive_expect_tx(bar_s + 8 * st, 2 * kPageTokens * kHeadDim);
+    bulk_g2s(ring_s + st * 8192, src, 2 * kPageTokens * kHeadDim, bar_s + 8 * st);
+  };
+  int issued = 0;
+  if (threadIdx.x == 0) {
+    for (; issued < min(kAttnRing, npages); ++issued) issue(issued);
+  }
+
+  // ---- Q tile (bf16 -> fp16: exact for every value the normed, rotated q can take)
   if (active) {
     for (int i = lane; i < 16 * 32; i += 32) {
       const int r = i >> 5, c = i & 31;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (r < ntok)
-        v = *reinterpret_cast<const uint4*>(
+      if (r < ntok) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(
             p.q + (static_cast<size_t>(row0 + t0 + r) * p.nq + head) * kHeadDim + c * 8);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h2[j]);
+          o[j] = pack_f16(f.x, f.y);
+        }
+        v = make_uint4(o[0], o[1], o[2], o[3]);
+      }
       asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
                        q_s + warp * 8192 + r * 512 + ((c ^ (r & 7)) << 4)),
                    "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
@@ -179,94 +220,87 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.f, 0.f};
   const float scale_log2 = p.sm_scale * p.k_scale * 1.4426950408889634f;
-
-  // ---- page prefetch into registers
   const int nthreads = blockDim.x;
-  uint4 pre[3];
-  auto prefetch = [&](int pg) {
-    const int blk = p.block_table[static_cast<size_t>(b) * p.max_blocks + pg];
-    const uint8_t* src =
-        p.kv_cache + (static_cast<size_t>(blk) * p.nkv + kvh) * (2 * kPageTokens * kHeadDim);
-#pragma unroll
-    for (int i = 0; i < 3; ++i) {
-      const int idx = threadIdx.x + i * nthreads;
-      if (idx < 512) pre[i] = __ldg(reinterpret_cast<const uint4*>(src) + idx);
-    }
-  };
-  // with fewer than 171 threads three chunks per thread do not cover 512: loop variant below
-  const int rounds = (512 + nthreads * 3 - 1) / (nthreads * 3);  // 1 for >= 171 threads
-  if (pg0 < pg1 && rounds == 1) prefetch(pg0);
+  const int niter = (npages + 1) >> 1;
+  bool ok = true;
 
-  for (int pg = pg0; pg < pg1; ++pg) {
-    __syncthreads();  // everyone is done with the previous page (and Q is written)
-    if (rounds == 1) {
+  for (int it = 0; it < niter; ++it) {
+    const uint32_t k_s = op_s + (it & 1) * kAttnOpBytes;
+    const uint32_t v_s = k_s + 16384;
+    // ---- widen the two pages of this iteration into the operand buffer
 #pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        const int idx = threadIdx.x + i * nthreads;
-        if (idx < 512) {
-          const int isv = idx >> 8, key = (idx & 255) >> 4, c = (idx & 15) * 2;
-          uint4 lo, hi;
-          fp8x16_to_bf16(pre[i], lo, hi);
+    for (int half = 0; half < 2; ++half) {
+      const int i = 2 * it + half;
+      if (i < npages) {
+        const int st = i % kAttnRing;
+        if (ok) ok = mbar_wait(bar_s + 8 * st, (i / kAttnRing) & 1, p.err, kErrWaitFull);
+        for (int idx = threadIdx.x; idx < 512; idx += nthreads) {
+          const int isv = idx >> 8, key = half * 16 + ((idx & 255) >> 4), c = (idx & 15) * 2;
+          uint4 raw, lo, hi;
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                       : "r"(ring_s + st * 8192 + idx * 16));
+          fp8x16_to_f16(raw, lo, hi);
           const uint32_t base = (isv ? v_s : k_s) + key * 512;
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(base + ((c ^ (key & 7)) << 4)),
                        "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w)
                        : "memory");
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
-                           base + (((c + 1) ^ (key & 7)) << 4)),
+          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(base + (((c + 1) ^ (key & 7)) << 4)),
                        "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
                        : "memory");
         }
-      }
-    } else {
-      const int blk = p.block_table[static_cast<size_t>(b) * p.max_blocks + pg];
-      const uint8_t* src =
-          p.kv_cache + (static_cast<size_t>(blk) * p.nkv + kvh) * (2 * kPageTokens * kHeadDim);
-      for (int idx = threadIdx.x; idx < 512; idx += nthreads) {
-        const int isv = idx >> 8, key = (idx & 255) >> 4, c = (idx & 15) * 2;
-        uint4 lo, hi;
-        fp8x16_to_bf16(__ldg(reinterpret_cast<const uint4*>(src) + idx), lo, hi);
-        const uint32_t base = (isv ? v_s : k_s) + key * 512;
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(base + ((c ^ (key & 7)) << 4)),
-                     "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w)
-                     : "memory");
-        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
-                         base + (((c + 1) ^ (key & 7)) << 4)),
-                     "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
-                     : "memory");
+      } else {
+        // no second page: its keys are masked, but V must hold finite numbers (0 * inf = nan)
+        for (int idx = threadIdx.x; idx < 512; idx += nthreads) {
+          const int key = 16 + (idx >> 5), c = idx & 31;
+          asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(v_s + key * 512 + (c << 4)), "r"(0u) : "memory");
+        }
       }
     }
-    __syncthreads();
-    if (rounds == 1 && pg + 1 < pg1) prefetch(pg + 1);
+    // one barrier per iteration: the operand buffer is complete, the two ring stages are free,
+    // and (the buffers alternate) every warp has left the buffer the next iteration overwrites
+    if (__syncthreads_or(ok ? 0 : 1)) { ok = false; break; }
+    if (threadIdx.x == 0) {
+      fence_proxy_async_smem();   // order the generic reads of the stages before the async refill
+      for (int half = 0; half < 2; ++half)
+        if (issued < npages && issued - kAttnRing <= 2 * it + half) { issue(issued); ++issued; }
+    }
     if (!active) continue;
 
-    // S = Q K^T  (16 x 16 per warp)
-    float S[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    // ---- S = Q K^T  (16 x 32 per warp)
+    float S[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < 16; ++ks) {
-      uint32_t a[4], kb[4];
+      uint32_t a[4], kb0[4], kb1[4];
       {
         const int r = (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * ks + (lane >> 4);
         ldsm_x4(q_s + warp * 8192 + r * 512 + ((c ^ (r & 7)) << 4), a);
       }
       {
         const int r = (lane & 7) + (lane >> 4) * 8, c = 2 * ks + ((lane >> 3) & 1);
-        ldsm_x4(k_s + r * 512 + ((c ^ (r & 7)) << 4), kb);
+        ldsm_x4(k_s + r * 512 + ((c ^ (r & 7)) << 4), kb0);
+        ldsm_x4(k_s + (16 + r) * 512 + ((c ^ (r & 7)) << 4), kb1);
       }
-      mma_bf16(S[0], a, kb[0], kb[1]);
-      mma_bf16(S[1], a, kb[2], kb[3]);
+      mma_f16(S[0], a, kb0[0], kb0[1]);
+      mma_f16(S[1], a, kb0[2], kb0[3]);
+      mma_f16(S[2], a, kb1[0], kb1[1]);
+      mma_f16(S[3], a, kb1[2], kb1[3]);
     }
-    // scale, mask, online softmax (rows g and g + 8)
+    // ---- scale, mask, online softmax (rows g and g + 8)
     float rmax[2] = {-INFINITY, -INFINITY};
+    const int key0 = (pg0 + 2 * it) * kPageTokens;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
+    for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int rr = g + (e >> 1) * 8;
-        const int key = pg * kPageTokens + nt * 8 + 2 * t + (e & 1);
-        const bool ok = rr < ntok && key < kbase + rr;
-        const float s = ok ? S[nt][e] * scale_log2 : -INFINITY;
-        S[nt][e] = s;
-        rmax[e >> 1] = fmaxf(rmax[e >> 1], s);
+        const int key = key0 + nt * 8 + 2 * t + (e & 1);
+        const bool live = rr < ntok && key < kbase + rr && key < key_end;
+        const float sv = live ? S[nt][e] * scale_log2 : -INFINITY;
+        S[nt][e] = sv;
+        rmax[e >> 1] = fmaxf(rmax[e >> 1], sv);
       }
     }
     float alpha[2], msafe[2];
@@ -279,34 +313,49 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
       alpha[h2] = exp2f(m_run[h2] - msafe[h2]);
       m_run[h2] = mnew;
     }
-    uint32_t pa[4];
-    {
+    uint32_t pa[2][4];
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {   // 16 keys each
       float pv[2][4];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) pv[nt][e] = exp2f(S[nt][e] - msafe[e >> 1]);
-      l_run[0] = l_run[0] * alpha[0] + pv[0][0] + pv[0][1] + pv[1][0] + pv[1][1];
-      l_run[1] = l_run[1] * alpha[1] + pv[0][2] + pv[0][3] + pv[1][2] + pv[1][3];
-      pa[0] = pack_bf16(pv[0][0], pv[0][1]);
-      pa[1] = pack_bf16(pv[0][2], pv[0][3]);
-      pa[2] = pack_bf16(pv[1][0], pv[1][1]);
-      pa[3] = pack_bf16(pv[1][2], pv[1][3]);
+        for (int e = 0; e < 4; ++e) pv[nt][e] = exp2f(S[2 * kk + nt][e] - msafe[e >> 1]);
+      if (kk == 0) {
+        l_run[0] *= alpha[0];
+        l_run[1] *= alpha[1];
+      }
+      l_run[0] += pv[0][0] + pv[0][1] + pv[1][0] + pv[1][1];
+      l_run[1] += pv[0][2] + pv[0][3] + pv[1][2] + pv[1][3];
+      pa[kk][0] = pack_f16(pv[0][0], pv[0][1]);
+      pa[kk][1] = pack_f16(pv[0][2], pv[0][3]);
+      pa[kk][2] = pack_f16(pv[1][0], pv[1][1]);
+      pa[kk][3] = pack_f16(pv[1][2], pv[1][3]);
     }
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       O[i][0] *= alpha[0]; O[i][1] *= alpha[0];
       O[i][2] *= alpha[1]; O[i][3] *= alpha[1];
     }
-    // O += P V
+    // ---- O += P V
 #pragma unroll
     for (int dt = 0; dt < 16; ++dt) {
-      uint32_t vb[4];
-      const int r = (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * dt + (lane >> 4);
-      ldsm_x4_t(v_s + r * 512 + ((c ^ (r & 7)) << 4), vb);
-      mma_bf16(O[2 * dt], pa, vb[0], vb[1]);
-      mma_bf16(O[2 * dt + 1], pa, vb[2], vb[3]);
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        uint32_t vb[4];
+        const int r = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * dt + (lane >> 4);
+        ldsm_x4_t(v_s + r * 512 + ((c ^ (r & 7)) << 4), vb);
+        mma_f16(O[2 * dt], pa[kk], vb[0], vb[1]);
+        mma_f16(O[2 * dt + 1], pa[kk], vb[2], vb[3]);
+      }
     }
+  }
+  if (!ok) {
+    // a page never arrived: the status word is set; do not leave while own copies may still land
+    if (threadIdx.x == 0)
+      for (int i = max(0, issued - kAttnRing); i < issued; ++i)
+        mbar_wait(bar_s + 8 * (i % kAttnRing), (i / kAttnRing) & 1, p.err, kErrWaitDrain);
+    return;
   }
   if (!active) return;
 
@@ -384,10 +433,11 @@ extern "C" int saber_attn_launch(const saber::AttnParams* p, cudaStream_t stream
   const int group = p->nq / p->nkv;
   const int hgroups = (group + kAttnMaxWarps - 1) / kAttnMaxWarps;
   const int hpb = (group + hgroups - 1) / hgroups;
-  const int smem = hpb * 8192 + 16384;
+  const int smem = hpb * 8192 + 2 * kAttnOpBytes + kAttnRing * 8192;
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(attn_paged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 6 * 8192 + 16384);
+    cudaFuncSetAttribute(attn_paged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         kAttnMaxWarps * 8192 + 2 * kAttnOpBytes + kAttnRing * 8192);
     configured = true;
   }
   dim3 grid(p->q_tiles, p->nkv * hgroups, p->nseq * p->splits);

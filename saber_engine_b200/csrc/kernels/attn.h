@@ -35,6 +35,9 @@ struct AttnParams {
   float* part_ml;              // [nseq][nq][splits][16][2]
   int nseq, nq, nkv, max_blocks, splits, q_tiles;
   float sm_scale, k_scale, v_scale;
+  uint32_t* err;               // status word of the bounded waits (may be null)
+  int n_blocks;                // blocks in kv_cache (0 = unknown): a table entry outside [0, n_blocks) is
+                               // recorded in the status word and its page is treated as empty
 };
 
 }  // namespace saber

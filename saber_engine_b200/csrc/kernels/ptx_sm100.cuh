@@ -23,6 +23,7 @@ enum : uint32_t {
   kErrWaitAcc = 4,     // epilogue timed out waiting for the accumulator
   kErrWaitPeer = 5,    // a cross-GPU flag wait ran out
   kErrWaitDrain = 6,   // unwinding: a copy in flight never landed
+  kErrBadIndex = 9,    // an index table entry pointed outside its pool; the access was skipped
   kErrWaitSplit = 8,   // a split-K CTA waited for the other splits of its tile
   kErrBadArgs = 7,
 };

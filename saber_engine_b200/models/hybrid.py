@@ -194,8 +194,8 @@ class HybridModel:
         return 0
 
     def attn_splits(self, nseq: int) -> int:
-        ctas = nseq * self.sh.n_kv_heads
-        return max(1, min(32, (148 + ctas - 1) // ctas))
+        ctas = nseq * self.sh.n_kv_heads     # one CTA per SM (shared memory): never more CTAs than SMs
+        return max(1, min(32, 148 // ctas))
 
     def tap_layers(self) -> list:
         n = self.cfg.drafter.n_taps if self.cfg.drafter else 0
@@ -290,6 +290,7 @@ class HybridModel:
                                    part_ml, nkv, splits, q_tiles, self.k_scale, self.v_scale)
                 ap.block_table, ap.cu_q, ap.kv_len = at(lay.block_table), at(lay.cu_rows), at(lay.kv_len)
                 ap.max_blocks, ap.nseq = self.max_blocks, nseq
+                ap.err = self.scratch.err.data_ptr()
                 prog.attn(ap, tag=f"{t}.attn.core")
                 ao = attn_out.view(M, nq * D)
                 if cfg.attn_out_gate:

@@ -328,6 +328,8 @@ def attn_params(q, kv_cache, block_table, cu_q, kv_len, out, part_o, part_ml, nk
     p.max_blocks, p.splits, p.q_tiles = block_table.shape[1], splits, q_tiles
     p.sm_scale = sm_scale if sm_scale is not None else 1.0 / math.sqrt(256.0)
     p.k_scale, p.v_scale = k_scale, v_scale
+    p.err = scratch(q.device).err.data_ptr()
+    p.n_blocks = kv_cache.shape[0]
     return p
 
 

@@ -34,7 +34,7 @@ ROW_ADD_RMS, ROW_SILU_MUL, ROW_GATE_SIG, ROW_GDN_NORM, ROW_PLAIN = range(5)
 
 ERR_NAMES = {
     0: "ok", 1: "wait_full", 2: "wait_empty", 3: "wait_ready", 4: "wait_acc", 5: "wait_peer",
-    6: "wait_drain", 7: "bad_args", 8: "wait_split",
+    6: "wait_drain", 7: "bad_args", 8: "wait_split", 9: "bad_index",
 }
 
 
@@ -78,7 +78,7 @@ class AttnParams(C.Structure):
     _fields_ = [("q", P), ("kv_cache", P), ("block_table", P), ("cu_q", P), ("kv_len", P),
                 ("out", P), ("part_o", P), ("part_ml", P), ("nseq", I), ("nq", I), ("nkv", I),
                 ("max_blocks", I), ("splits", I), ("q_tiles", I), ("sm_scale", F), ("k_scale", F),
-                ("v_scale", F)]
+                ("v_scale", F), ("err", P), ("n_blocks", I)]
 
 
 class VerifyParams(C.Structure):
