@@ -24,7 +24,10 @@ __device__ __forceinline__ float gdn_silu(float x) { return x / (1.f + __expf(-x
 __device__ __forceinline__ float gdn_softplus(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
 
 // ---------------------------------------------------------------------------------- conv update
-// grid (C / 128, nseq), block 128.
+// grid (C / 128, nseq, row chunks), block 128.  The conv is causal with a 4-tap window, so chunks of
+// kConvChunk rows are independent: a chunk reads the three inputs before its first row from x (or,
+// for the first rows of the step, from the committed window in `hist`).
+constexpr int kConvChunk = 32;
 __global__ void __launch_bounds__(128) gdn_conv_update_kernel(const GdnConvParams p) {
   pdl_wait();
   __shared__ float red[4];
@@ -34,14 +37,19 @@ __global__ void __launch_bounds__(128) gdn_conv_update_kernel(const GdnConvParam
   const int ch = blockIdx.x * 128 + threadIdx.x;
   const int row0 = p.cu_rows[b];
   const int n = p.cu_rows[b + 1] - row0;
-  if (n <= 0) return;
+  const int r_first = blockIdx.z * kConvChunk;
+  if (r_first >= n) return;
+  const int r_last = min(n, r_first + kConvChunk);
   const int shift = p.shift[b];
   __nv_bfloat16* hp = p.hist + static_cast<size_t>(slot) * p.hist_rows * p.C + ch;
-  // window = the three committed inputs that precede this step's first row
-  float b0 = __bfloat162float(hp[static_cast<size_t>(shift) * p.C]);
-  float b1 = __bfloat162float(hp[static_cast<size_t>(shift + 1) * p.C]);
-  float b2 = __bfloat162float(hp[static_cast<size_t>(shift + 2) * p.C]);
-  if (!p.commit) {
+  // window = the three inputs that precede this chunk's first row: input j < 0 of the step is row
+  // shift + 3 + j of the history (the committed window shifted by the accepted rows)
+  auto input_at = [&](int j) -> float {
+    return j >= 0 ? __bfloat162float(p.x[static_cast<size_t>(row0 + j) * p.ldx + ch])
+                  : __bfloat162float(hp[static_cast<size_t>(shift + 3 + j) * p.C]);
+  };
+  float b0 = input_at(r_first - 3), b1 = input_at(r_first - 2), b2 = input_at(r_first - 1);
+  if (!p.commit && r_first == 0) {
     hp[0] = __float2bfloat16(b0);
     hp[p.C] = __float2bfloat16(b1);
     hp[2 * static_cast<size_t>(p.C)] = __float2bfloat16(b2);
@@ -50,7 +58,7 @@ __global__ void __launch_bounds__(128) gdn_conv_update_kernel(const GdnConvParam
               w3 = p.conv_w[ch * 4 + 3];
   const bool is_q = ch < p.n_q, is_k = !is_q && ch < p.n_q + p.n_k;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int r = 0; r < n; ++r) {
+  for (int r = r_first; r < r_last; ++r) {
     const __nv_bfloat16 xb = p.x[static_cast<size_t>(row0 + r) * p.ldx + ch];
     const float x = __bfloat162float(xb);
     float y = gdn_silu(w0 * b0 + w1 * b1 + w2 * b2 + w3 * x);
@@ -278,7 +286,8 @@ extern "C" int saber_gdn_conv_launch(const saber::GdnConvParams* p, int nseq, cu
   using namespace saber;
   if (p->C % 128 || p->n_q % 128 || p->n_k % 128) return static_cast<int>(cudaErrorInvalidValue);
   dim3 grid(p->C / 128, nseq);
-  saber::launch(gdn_conv_update_kernel, dim3(grid), dim3(128), 0, stream, 0, *p);
+  dim3 grid_u(p->C / 128, nseq, (max(1, p->max_rows) + kConvChunk - 1) / kConvChunk);
+  saber::launch(gdn_conv_update_kernel, grid_u, dim3(128), 0, stream, 0, *p);
   if (p->commit) saber::launch(gdn_conv_commit_kernel, dim3(grid), dim3(128), 0, stream, 0, *p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -16,6 +16,7 @@ struct GdnConvParams {
   float* out;               // [M][C] conv+SiLU (+L2 norm for q,k; q also scaled)
   int C, n_q, n_k, ldx, hist_rows, commit;
   float q_scale;
+  int max_rows;             // upper bound of the rows of one sequence in this step (sizes the grid)
 };
 
 struct GdnRecParams {

@@ -260,6 +260,7 @@ def gdn_conv_params(x, conv_w, hist, cu_rows, slots, shift, out, n_q, n_k, commi
     p.C, p.n_q, p.n_k = conv_w.shape[0], n_q, n_k
     p.ldx = ldx if ldx is not None else x.stride(0)
     p.hist_rows, p.commit, p.q_scale = hist.shape[1], int(commit), 1.0 / math.sqrt(128.0)
+    p.max_rows = x.shape[0]
     return p
 
 

@@ -57,7 +57,7 @@ class RowOpParams(C.Structure):
 class GdnConvParams(C.Structure):
     _fields_ = [("x", P), ("conv_w", P), ("hist", P), ("cu_rows", P), ("slots", P), ("shift", P),
                 ("out", P), ("C", I), ("n_q", I), ("n_k", I), ("ldx", I), ("hist_rows", I),
-                ("commit", I), ("q_scale", F)]
+                ("commit", I), ("q_scale", F), ("max_rows", I)]
 
 
 class GdnRecParams(C.Structure):

@@ -65,6 +65,7 @@ def main(argv=None) -> int:
     ap.add_argument("--width", type=int, default=9)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--walk", action="store_true")
+    ap.add_argument("--prefill", type=int, default=0, help="profile a prefill bucket of this many rows instead")
     args = ap.parse_args(argv)
     cfg = C.by_name(args.model)
     model = HybridModel(cfg, device="cuda", max_seqs=args.batch, max_ctx=args.ctx + 512, max_width=args.width,
@@ -74,6 +75,10 @@ def main(argv=None) -> int:
     g = torch.Generator().manual_seed(3)
     seqs = [SeqStep(torch.randint(0, cfg.vocab, (args.width,), generator=g).tolist(), args.ctx, j + 1, 3,
                     list(range(1 + j * bp, 1 + (j + 1) * bp)), uid=j) for j in range(args.batch)]
+    if args.prefill:
+        b = model.build_bucket("prefill", 1, args.prefill)
+        seqs = [SeqStep(torch.randint(0, cfg.vocab, (args.prefill,), generator=g).tolist(), args.ctx - args.prefill, 1, 0,
+                        list(range(1, 1 + bp)), uid=0)]
     if args.walk:
         print(format_profile(profile_bucket(model, b, seqs)))
         return 0
