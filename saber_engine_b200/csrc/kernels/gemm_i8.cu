@@ -301,17 +301,22 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
           *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.tp_recv[peer]) + off) = v;
       };
       auto tp_signal = [&](int tile_id) {   // called by all 128 epilogue threads after their stores
-        __threadfence_system();
-        named_bar_sync(1, 128);
+        named_bar_sync(1, 128);             // every thread's pushes precede the barrier ...
         if (tid_t < p.tp_nranks) {
+          __threadfence_system();           // ... and this fence is cumulative over what the barrier ordered
           uint32_t* f = p.tp_flags[tid_t] + (static_cast<size_t>(tp_par) * p.tp_nranks + p.tp_rank) * kTpMaxTiles + tile_id;
           asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tp_seq) : "memory");
         }
       };
       if (p.splits == 1) {
+        // The accumulator arrives one token row per thread; stored like that, the 32 lanes of a
+        // warp would write 32 different rows (16-byte pieces, and over NVLink 16-byte packets).
+        // So the bf16 tile is first staged in shared memory -- the operand buffers are idle by
+        // now -- with its 16-byte chunks XOR-swizzled by the row, then every warp writes whole
+        // rows: 512 contiguous bytes per store instruction, to local memory or to every rank.
+        const uint32_t stage_s = p.w4 ? u_smem : w_smem;     // >= 64 KiB in either mode
         if (warp_live) {
           const float asc = live ? p.a_scale[m] : 0.f;
-          __nv_bfloat16* orow = p.out + static_cast<size_t>(live ? m : m0) * p.ldo + n0;
           for (int c = 0; c < ncols; c += 32) {
             uint32_t r[32];
             tmem_ld32(t_lane + c, r);
@@ -325,20 +330,38 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
                 const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
                 pk[j] = *reinterpret_cast<const uint32_t*>(&b2);
               }
-              if (tp) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  if (n0 + c + 8 * j < p.N)
-                    tp_push16(m, n0 + c + 8 * j, make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]));
-              } else if (n0 + c + 32 <= p.N) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                  *reinterpret_cast<uint4*>(orow + c + 8 * j) = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-              } else {
-                const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(pk);
-                for (int j = 0; j < 32; ++j)
-                  if (n0 + c + j < p.N) orow[c + j] = pb[j];
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t chunk = static_cast<uint32_t>((c >> 3) + j) ^ (static_cast<uint32_t>(row) & 31u);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(stage_s + row * 512 + (chunk << 4)),
+                             "r"(pk[4 * j]), "r"(pk[4 * j + 1]), "r"(pk[4 * j + 2]), "r"(pk[4 * j + 3])
+                             : "memory");
               }
+            }
+          }
+        }
+        named_bar_sync(1, 128);
+        {
+          const int wq = tid_t >> 5;                  // 0..3: rows wq, wq + 4, ...
+          const int col = lane * 8;                   // this lane's 8 output features of the row
+          const bool col_ok = n0 + col < p.N;         // (N is a multiple of 8 whenever ldo is)
+          const bool full = n0 + col + 8 <= p.N;
+          for (int rw = wq; rw < mt; rw += 4) {
+            uint4 v;
+            const uint32_t chunk = static_cast<uint32_t>(lane) ^ (static_cast<uint32_t>(rw) & 31u);
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                         : "r"(stage_s + rw * 512 + (chunk << 4)));
+            if (!col_ok || col >= ncols) continue;
+            if (tp) {
+              tp_push16(m0 + rw, n0 + col, v);
+            } else if (full) {
+              *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(m0 + rw) * p.ldo + n0 + col) = v;
+            } else {
+              const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&v);
+              __nv_bfloat16* o = p.out + static_cast<size_t>(m0 + rw) * p.ldo + n0 + col;
+              for (int j = 0; j < 8; ++j)
+                if (n0 + col + j < p.N) o[j] = pb[j];
             }
           }
         }
@@ -404,7 +427,10 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
           // used, two items per round: one memory round trip per round.
           const int n_c4 = ncols >> 2;
           const int c4_part = n_c4 > part ? (n_c4 - part + nparts - 1) / nparts : 0;
-          const int n_items = c4_part * mt;
+          // tensor-parallel: the parts split the ROWS and lanes run over the column groups, so
+          // that a warp's pushes to a peer are contiguous bytes of one row
+          const int rows_part = mt > part ? (mt - part + nparts - 1) / nparts : 0;
+          const int n_items = tp ? rows_part * n_c4 : c4_part * mt;
           const size_t tiles_all = static_cast<size_t>(gridDim.x) * gridDim.y;
           const int32_t* rblk = p.ws + static_cast<size_t>(tile_lin) * blk_stride;
           auto reduce_items = [&](auto ilp_c, auto maxs_c) {
@@ -416,9 +442,15 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
 #pragma unroll
             for (int u = 0; u < kIlp; ++u) {
               const int idx = min(base + u * 128, n_items - 1);
-              const int ci = idx / mt;
-              rr[u] = idx - ci * mt;
-              c4[u] = part + ci * nparts;
+              if (tp) {
+                const int ri = idx / n_c4;
+                c4[u] = idx - ri * n_c4;
+                rr[u] = part + ri * nparts;
+              } else {
+                const int ci = idx / mt;
+                rr[u] = idx - ci * mt;
+                c4[u] = part + ci * nparts;
+              }
 #pragma unroll
               for (int sp = 0; sp < kMaxS; ++sp)
                 if (sp < p.splits)
@@ -469,18 +501,14 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
         }
         if (tid_t == 0) SABER_STAMP(12);
         if (p.coop) {
-          // second round of arrivals: the CTA that finishes last re-arms the counter and, in
-          // tensor-parallel mode, raises the tile's flags (every slice has been pushed by then)
-          if (tp) __threadfence_system();
-          named_bar_sync(1, 128);
+          // tensor-parallel: every part raises its OWN flag (index tile * splits + split) as soon as
+          // its rows are pushed; the consumer waits for all parts of the tiles it reads
+          if (tp) tp_signal(tile_id * p.splits + split);
+          // second round of arrivals, off the critical path: the CTA that finishes last re-arms the counter
           if (tid_t == 0) {
             const uint32_t old = atomicAdd(p.counters + tile_id, 1u);
-            const bool fin = old == static_cast<uint32_t>(2 * p.splits - 1);
-            if (fin) p.counters[tile_id] = 0u;
-            is_last_s = fin ? 1u : 0u;
+            if (old == static_cast<uint32_t>(2 * p.splits - 1)) p.counters[tile_id] = 0u;
           }
-          named_bar_sync(1, 128);
-          if (tp && is_last_s) tp_signal(tile_id);
         }
       }
     }
@@ -495,6 +523,17 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
 }
 
 }  // namespace saber
+
+// Number of flags per output tile a tensor-parallel launch of `p` raises (the consumer must wait
+// for all of them): the split-K factor when the cooperative reduction runs, else one.
+extern "C" int saber_gemm_i8_parts(const saber::GemmI8Params* p) {
+  int sm_count = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  const int grid_y = p->group_tiles ? p->M_pad / 16 : (p->M + p->nt - 1) / p->nt;
+  const bool coop = p->splits > 1 && p->coop >= 0 && (p->N_pad / 256) * grid_y * p->splits <= sm_count;
+  return coop ? p->splits : 1;
+}
 
 extern "C" int saber_gemm_i8_smem_bytes(int nt, int stages) {
   return saber_gemm_i8_smem_bytes_w(nt, stages, 0);
@@ -515,7 +554,7 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   if ((p->splits - 1) * kb_per >= KB) return static_cast<int>(cudaErrorInvalidValue);
   if (p->tp_nranks > 1) {
     const int tiles = (p->N_pad / 256) * ((p->M + p->nt - 1) / p->nt);
-    if (p->tp_nranks > 8 || (p->N & 7) || (p->tp_ld & 7) || tiles > kTpMaxTiles || p->M > p->tp_rows)
+    if (p->tp_nranks > 8 || (p->N & 7) || (p->tp_ld & 7) || tiles * saber_gemm_i8_parts(p) > kTpMaxTiles || p->M > p->tp_rows)
       return static_cast<int>(cudaErrorInvalidValue);
   }
   const int kSmemLimit = 224 * 1024;  // opt-in maximum minus the kernel's static shared memory

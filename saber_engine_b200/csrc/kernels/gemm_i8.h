@@ -49,4 +49,5 @@ struct GemmI8Params {
 
 extern "C" int saber_gemm_i8_smem_bytes(int nt, int stages);
 extern "C" int saber_gemm_i8_smem_bytes_w(int nt, int stages, int w4);
+extern "C" int saber_gemm_i8_parts(const saber::GemmI8Params* p);
 extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cudaStream_t stream);

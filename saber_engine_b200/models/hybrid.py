@@ -14,6 +14,7 @@ and the drafter-after-commit flow of `crates/saber-engine/src/draft_plan.rs:17-3
 """
 from __future__ import annotations
 
+import ctypes as C
 import math
 from dataclasses import dataclass, field
 from typing import Optional
@@ -165,6 +166,7 @@ class HybridModel:
         p = F.gemm_params(w, a, out, self.scratch, splits=splits)
         if tp_site >= 0 and self.tp > 1:
             self.comm.gemm_tp(p, tp_site)
+            self._site_parts[tp_site] = N.lib().saber_gemm_i8_parts(C.byref(p))
         prog.gemm(p, self.gemm_stages(w, a), tag=tag)
 
     def _add_rms(self, prog: N.Program, M: int, tag: str, w, res, qa, delta, tp_site: int = -1, out=None) -> None:
@@ -173,7 +175,8 @@ class HybridModel:
         p = F.row_params(M, cfg.hidden, a=delta, res=res, w=w, w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa, out=out)
         if tp_site >= 0 and self.tp > 1:
             nt = self._site_nt.get(tp_site, L.token_tile(M))
-            self.comm.row_tp(p, tp_site, nt, L.round_up(cfg.hidden, L.TILE_N) // L.TILE_N)
+            # a producer that signals per split-K part shows up as that many flags per feature tile
+            self.comm.row_tp(p, tp_site, nt, L.round_up(cfg.hidden, L.TILE_N) // L.TILE_N * self._site_parts.get(tp_site, 1))
         prog.row(N.ROW_ADD_RMS, p, tag=tag)
 
     def pick_splits(self, w: F.QuantWeight, a: F.QuantAct) -> int:
@@ -221,6 +224,7 @@ class HybridModel:
         at = lambda off: base + 4 * off                 # noqa: E731  device address of a table
         prog = N.Program(f"{kind}-b{nseq}-w{width}")
         self._site_nt = {}                              # TP site -> row-tile height its producer signals with
+        self._site_parts = {}                           # TP site -> flags per feature tile (split-K parts)
         bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)   # noqa: E731
         f32 = lambda *s: torch.zeros(*s, dtype=torch.float32, device=dev)   # noqa: E731
         i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)     # noqa: E731

@@ -147,6 +147,7 @@ def _declare(L: C.CDLL) -> None:
     S = C.c_void_p  # cudaStream_t
     sig = {
         "saber_gemm_i8_launch": (I, [C.POINTER(GemmI8Params), I, S]),
+        "saber_gemm_i8_parts": (I, [C.POINTER(GemmI8Params)]),
         "saber_gemm_i8_smem_bytes": (I, [I, I]),
         "saber_gemm_i8_smem_bytes_w": (I, [I, I, I]),
         "saber_row_producer_launch": (I, [I, C.POINTER(RowOpParams), S]),

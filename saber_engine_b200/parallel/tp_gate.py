@@ -51,12 +51,15 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens", type=int, default=24)
     ap.add_argument("--prompt", type=int, default=48)
     ap.add_argument("--width", type=int, default=5)
+    ap.add_argument("--moe", action="store_true", help="gate the expert-parallel MoE hybrid instead of the dense one")
     args = ap.parse_args(argv)
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
-    cfg = C.scaled_hybrid(q_heads=8, kv_heads=2, k_heads=8, v_heads=8, ffn=1024 * max(1, world // 2), hidden=512)
+    moe = C.MoEConfig(n_experts=32, top_k=4, expert_inter=128, shared_inter=256) if args.moe else None
+    cfg = C.scaled_hybrid(q_heads=8, kv_heads=2, k_heads=8, v_heads=8, ffn=1024 * max(1, world // 2), hidden=512,
+                          moe=moe)
     comm = SymmetricComm(rank, world, dev, max_elems=128 * cfg.hidden, rows_max=128, hidden=cfg.hidden)
     model = HybridModel(cfg, tp=world, rank=rank, device=dev, max_seqs=2, max_ctx=512, max_width=args.width,
                         seed=5, comm=comm)

@@ -67,9 +67,20 @@ def main(argv=None) -> int:
     ap.add_argument("--walk", action="store_true")
     ap.add_argument("--prefill", type=int, default=0, help="profile a prefill bucket of this many rows instead")
     args = ap.parse_args(argv)
+    import os
     cfg = C.by_name(args.model)
-    model = HybridModel(cfg, device="cuda", max_seqs=args.batch, max_ctx=args.ctx + 512, max_width=args.width,
-                        seed=1, oracle_p=0.75)
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    comm = None
+    torch.cuda.set_device(local)
+    if world > 1:       # under torchrun: the tensor-parallel shard of every rank, walked in lock step
+        import torch.distributed as dist
+        from ..parallel.symm import SymmetricComm
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        rows_max = max(args.prefill, args.batch * args.width, 128)
+        comm = SymmetricComm(rank, world, torch.device("cuda", local), max_elems=rows_max * cfg.hidden,
+                             rows_max=rows_max, hidden=cfg.hidden)
+    model = HybridModel(cfg, tp=world, rank=rank, device=torch.device("cuda", local), max_seqs=args.batch,
+                        max_ctx=args.ctx + 512, max_width=args.width, seed=1, oracle_p=0.75, comm=comm)
     bp = (args.ctx + 512) // cfg.page_tokens
     b = model.build_bucket("decode", args.batch, args.width)
     g = torch.Generator().manual_seed(3)
@@ -80,7 +91,12 @@ def main(argv=None) -> int:
         seqs = [SeqStep(torch.randint(0, cfg.vocab, (args.prefill,), generator=g).tolist(), args.ctx - args.prefill, 1, 0,
                         list(range(1, 1 + bp)), uid=0)]
     if args.walk:
-        print(format_profile(profile_bucket(model, b, seqs)))
+        prof = profile_bucket(model, b, seqs)
+        if rank == 0:
+            print(format_profile(prof))
+        if world > 1:
+            torch.distributed.barrier()
+            torch.distributed.destroy_process_group()
         return 0
     for _ in range(2):
         run_bucket(model, b, seqs)

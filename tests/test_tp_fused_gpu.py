@@ -44,6 +44,7 @@ def test_gemm_push_then_reduce_norm_quant(nranks, M, splits):
             dummy = torch.zeros(M, H, dtype=torch.bfloat16, device=DEV)
             p = F.gemm_params(qw, qa, dummy, sc, splits=splits)
             g.gemm_tp(p, site)
+            parts = N.lib().saber_gemm_i8_parts(C.byref(p))
             N.check(N.lib().saber_gemm_i8_launch(C.byref(p), 0, N.stream_handle()), "gemm")
             outs.append((qw, qa, dummy))
         torch.cuda.synchronize()
@@ -55,7 +56,7 @@ def test_gemm_push_then_reduce_norm_quant(nranks, M, splits):
             qa_out = F.QuantAct.alloc(M, H, DEV)
             normed = torch.zeros(M, H, dtype=torch.bfloat16, device=DEV)
             p = F.row_params(M, H, a=None, res=res_d, w=nw.to(DEV), w_offset=1.0, qa=qa_out, out=normed)
-            g.row_tp(p, site, L.token_tile(M), H // 256)
+            g.row_tp(p, site, L.token_tile(M), H // 256 * parts)
             N.check(N.lib().saber_row_producer_launch(N.ROW_ADD_RMS, C.byref(p), N.stream_handle()), "consumer")
             torch.cuda.synchronize()
             g.check()
