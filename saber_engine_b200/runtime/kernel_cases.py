@@ -1,0 +1,162 @@
+"""Small stand-alone cases of the hot kernels, one per `--case`, for profiler captures and quick
+timings: each case builds a few GB of operands at most, launches its kernel a handful of times on
+distinct operand copies (so every launch streams from HBM, not from L2) and prints the CUDA-event
+time of the last launches.
+
+    python -m saber_engine_b200.runtime.kernel_cases --case gemm_w4_gate_up_m72
+    ncu --set full --clock-control none -k regex:gemm_i8_kernel -s 2 -c 1 -o prof \\
+        python -m saber_engine_b200.runtime.kernel_cases --case gemm_w4_gate_up_m72
+
+Parity: the role of the reference's per-op timing arms and `chain-bench` instrument
+(`crates/saber-exec/src/steploop.rs:1-25`).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+
+import torch
+
+from ..ops import functional as F
+from ..ops import layouts as L
+from ..ops import native as N
+
+DEV = "cuda"
+
+
+def _time(fns, label: str, nbytes: float = 0.0) -> None:
+    """fns: one callable per operand copy; warm-up over all, then time a second pass."""
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(len(fns) + 1)]
+    e[0].record()
+    for i, f in enumerate(fns):
+        f()
+        e[i + 1].record()
+    torch.cuda.synchronize()
+    us = sorted(e[i].elapsed_time(e[i + 1]) * 1e3 for i in range(len(fns)))
+    med = us[len(us) // 2]
+    extra = f"  {nbytes / med / 1e6:.2f} TB/s algorithmic" if nbytes else ""
+    print(f"{label}: median {med:.1f} us over {len(fns)} launches (host-launched, includes ~5 us of launch){extra}")
+    F.scratch(DEV).check()
+
+
+def _gemm(Nn, K, M, w4, splits, copies=3):
+    n_pad = L.round_up(Nn, 256)
+    tile = 16384 if w4 else 32768
+    ws = [F.QuantWeight(torch.randint(0, 255, (n_pad // 256, K // 128, tile), dtype=torch.uint8, device=DEV),
+                        torch.rand(n_pad, device=DEV) * 1e-3, Nn, K, bool(w4)) for _ in range(copies)]
+    qa = F.plain_quant(torch.randn(M, K, device=DEV).to(torch.bfloat16))
+    out = torch.empty(M, Nn, dtype=torch.bfloat16, device=DEV)
+    sc = F.scratch(DEV)
+    ps = [F.gemm_params(w, qa, out, sc, splits=splits) for w in ws]
+    lib = N.lib()
+    fns = [lambda p=p: N.check(lib.saber_gemm_i8_launch(C.byref(p), 0, N.stream_handle()), "gemm") for p in ps]
+    _time(fns, f"gemm_i8 N={Nn} K={K} M={M} w4={w4} splits={ps[0].splits}", n_pad * K * (0.5 if w4 else 1.0))
+    return ws, qa, out
+
+
+def _attn(nseq, n, ctx, splits, copies=3):
+    nq, nkv, D = 24, 4, 256
+    M = nseq * n
+    pages = (ctx + n + 15) // 16
+    nblocks = nseq * pages + 1
+    kvs = [(torch.randn(nblocks, nkv, 2, 16, D, device=DEV) * 0.5).to(torch.float8_e4m3fn).view(torch.uint8)
+           for _ in range(copies)]
+    q = torch.randn(M, nq, D, device=DEV).to(torch.bfloat16)
+    bt = torch.arange(1, 1 + nseq * pages, dtype=torch.int32, device=DEV).view(nseq, pages)
+    cu = torch.arange(0, M + 1, n, dtype=torch.int32, device=DEV)
+    kvl = torch.full((nseq,), ctx + n, dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    po = torch.empty(nseq, nq, splits, 16, D, device=DEV) if splits > 1 else None
+    pm = torch.empty(nseq, nq, splits, 16, 2, device=DEV) if splits > 1 else None
+    ps = [F.attn_params(q, kv, bt, cu, kvl, out, po, pm, nkv, splits, 1) for kv in kvs]
+    torch.cuda.synchronize()
+    lib = N.lib()
+    fns = [lambda p=p: N.check(lib.saber_attn_launch(C.byref(p), N.stream_handle()), "attn") for p in ps]
+    _time(fns, f"attn_paged nseq={nseq} rows={n} ctx={ctx} splits={splits}", nseq * (ctx + n) * nkv * 2 * D)
+    return kvs, q, out, po, pm
+
+
+def _gdn(nseq, n, shift, vs=2, copies=3):
+    HV, HK, d = 48, 16, 128
+    M = nseq * n
+    C_ = 2 * HK * d + HV * d
+    qkv = torch.randn(M, C_, device=DEV) * 0.1
+    ba = torch.randn(M, 2 * HV, device=DEV).to(torch.bfloat16)
+    A_log, dtb = torch.randn(HV, device=DEV) * 0.5, torch.randn(HV, device=DEV) * 0.5
+    states = [torch.randn(nseq + 1, HV, d, d, device=DEV) * 0.01 for _ in range(copies)]
+    stashes = [torch.randn(nseq + 1, 9, HV, vs, F.gdn_stash_stride(vs), device=DEV) * 0.1 for _ in range(copies)]
+    cu = torch.arange(0, M + 1, n, dtype=torch.int32, device=DEV)
+    slots = torch.arange(1, nseq + 1, dtype=torch.int32, device=DEV)
+    sh = torch.full((nseq,), shift, dtype=torch.int32, device=DEV)
+    out = torch.empty(M, HV * d, device=DEV)
+    ps = [F.gdn_rec_params(qkv, ba, A_log, dtb, states[i], stashes[i], cu, slots, sh, out, HK * d, HK * d, HV, HK, False)
+          for i in range(copies)]
+    torch.cuda.synchronize()
+    lib = N.lib()
+    fns = [lambda p=p: N.check(lib.saber_gdn_recurrent_launch(C.byref(p), nseq, vs, N.stream_handle()), "gdn") for p in ps]
+    _time(fns, f"gdn_recurrent nseq={nseq} rows={n} replay={shift}", 2.0 * nseq * HV * d * d * 4)
+    return states, stashes, out
+
+
+def _row(M, K, copies=3):
+    xs = [torch.randn(M, K, device=DEV).to(torch.bfloat16) for _ in range(copies)]
+    res = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = torch.randn(K, device=DEV) * 0.1
+    qa = F.QuantAct.alloc(M, K, DEV)
+    lib = N.lib()
+    ps = [F.row_params(M, K, a=x, res=res, w=w, w_offset=1.0, qa=qa) for x in xs]
+    fns = [lambda p=p: N.check(lib.saber_row_producer_launch(N.ROW_ADD_RMS, C.byref(p), N.stream_handle()), "row") for p in ps]
+    _time(fns, f"row add_rms_quant M={M} K={K}", M * K * 7.0)
+    return xs, res, qa
+
+
+def _moe(M):
+    from ..models import config as MC
+    from ..models.moe_block import MoeWorkspace, add_moe_ops
+    from ..models.moe_weights import random_moe_layer
+    cfg = MC.flashnext_moe()
+    g = torch.Generator(device=DEV).manual_seed(1)
+    layers = [random_moe_layer(cfg, 1, 0, torch.device(DEV), g, 0.02) for _ in range(2)]
+    qa = F.plain_quant(torch.randn(M, cfg.hidden, device=DEV).to(torch.bfloat16))
+    ws = MoeWorkspace(cfg, cfg.moe.n_experts, M, DEV, layers[0]["shared_inter"])
+    out = torch.zeros(M, cfg.hidden, dtype=torch.bfloat16, device=DEV)
+    progs = []
+    for i, moe in enumerate(layers):
+        prog = N.Program(f"moe{i}")
+        add_moe_ops(prog, ws, cfg, moe, qa, out, F.scratch(DEV), "moe")
+        progs.append(prog)
+    torch.cuda.synchronize()
+    _time([p.run for p in progs] * 2, f"moe block (13 launches) M={M} experts={cfg.moe.n_experts} top_k={cfg.moe.top_k}")
+    return layers, ws, out, progs
+
+
+CASES = {
+    "gemm_w4_gate_up_m72": lambda: _gemm(34816, 5120, 72, 1, 1),
+    "gemm_w4_down_m72_split": lambda: _gemm(5120, 17408, 72, 1, 7, copies=4),
+    "gemm_w4_in_proj_m9_split": lambda: _gemm(10496, 5120, 9, 1, 3, copies=6),
+    "gemm_w8_lm_head_m72": lambda: _gemm(248320, 5120, 72, 0, 1, copies=2),
+    "gemm_w4_gate_up_m2048": lambda: _gemm(34816, 5120, 2048, 1, 1, copies=2),
+    "attn_decode_b8_ctx4096": lambda: _attn(8, 9, 4096, 4),
+    "attn_decode_b1_ctx32768": lambda: _attn(1, 9, 32768, 32, copies=2),
+    "gdn_rec_b8": lambda: _gdn(8, 9, 5),
+    "row_add_rms_m72": lambda: _row(72, 5120),
+    "moe_block_m72": lambda: _moe(72),
+}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", required=True, choices=sorted(CASES) + ["all"])
+    args = ap.parse_args(argv)
+    for name in (sorted(CASES) if args.case == "all" else [args.case]):
+        keep = CASES[name]()        # keep the operands alive until the launches have finished
+        torch.cuda.synchronize()
+        del keep
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
