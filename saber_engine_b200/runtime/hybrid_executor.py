@@ -91,3 +91,47 @@ class HybridExecutor:
     def free_snapshot(self, snap) -> None:
         if isinstance(snap, dict):
             snap.clear()
+
+    # ---- session parking: KV pages + the slot's recurrent state and conv window as one image
+    def export_session(self, slot: int, blocks: list, n_tokens: int):
+        """(header, payload): every tensor of the sequence, in a declared order, read back over a
+        pinned staging buffer.  Parity: `crates/saber-engine/src/park.rs:1-30`."""
+        m = self.model
+        npages = (n_tokens + self.page_tokens - 1) // self.page_tokens
+        idx = torch.tensor(blocks[:npages], dtype=torch.long, device=m.device)
+        parts, layout, off = [], [], 0
+        with torch.cuda.stream(m.stream):
+            def add(name, t):
+                nonlocal off
+                raw = t.contiguous().view(torch.uint8).reshape(-1)
+                host = torch.empty(raw.numel(), dtype=torch.uint8).pin_memory()
+                host.copy_(raw, non_blocking=True)
+                layout.append((name, str(t.dtype), list(t.shape), off, raw.numel()))
+                parts.append(host)
+                off += raw.numel()
+            for i, kv in m.kv.items():
+                add(f"kv.{i}", kv[idx])
+            for i in m.gdn_state:
+                add(f"gdn_state.{i}", m.gdn_state[i][slot])
+                add(f"gdn_stash.{i}", m.gdn_stash[i][slot])
+                add(f"gdn_hist.{i}", m.gdn_hist[i][slot])
+            m.stream.synchronize()
+        payload = b"".join(p.numpy().tobytes() for p in parts)
+        return {"kind": "hybrid", "n_tokens": n_tokens, "npages": npages, "tensors": layout}, payload
+
+    def import_session(self, slot: int, blocks: list, header: dict, payload: bytes) -> None:
+        m = self.model
+        npages = header["npages"]
+        idx = torch.tensor(blocks[:npages], dtype=torch.long, device=m.device)
+        buf = torch.frombuffer(bytearray(payload), dtype=torch.uint8)
+        with torch.cuda.stream(m.stream):
+            for name, dtype, shape, off, nbytes in header["tensors"]:
+                kind, i = name.rsplit(".", 1)
+                i = int(i)
+                dst = {"kv": m.kv, "gdn_state": m.gdn_state, "gdn_stash": m.gdn_stash, "gdn_hist": m.gdn_hist}[kind][i]
+                src = buf[off:off + nbytes].to(m.device).view(dst.dtype).reshape(shape)
+                if kind == "kv":
+                    dst[idx] = src
+                else:
+                    dst[slot].copy_(src)
+            m.stream.synchronize()

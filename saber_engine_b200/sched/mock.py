@@ -126,6 +126,21 @@ class NullExecutor:
     def snapshot_bytes(self) -> int:
         return 1 << 20
 
+    # ---- session parking hooks
+    def export_session(self, slot: int, blocks: list, n_tokens: int):
+        import pickle
+        payload = pickle.dumps((self._state[slot], self._stash.get(slot)))
+        return {"kind": "null-executor", "n_tokens": n_tokens}, payload
+
+    def import_session(self, slot: int, blocks: list, header: dict, payload: bytes) -> None:
+        import pickle
+        state, stash = pickle.loads(payload)
+        self._state[slot] = state
+        if stash is None:
+            self._stash.pop(slot, None)
+        else:
+            self._stash[slot] = stash
+
     def free_snapshot(self, snap) -> None:
         pass
 

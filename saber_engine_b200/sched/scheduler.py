@@ -98,6 +98,11 @@ class Scheduler:
         self.accepted_per_pos = [0] * 16
         self.last_step_s = 0.0
         self.on_step = None                 # optional callback(timing dict) for metrics
+        from ..utils.host_trace import HostTrace
+        from .park import ParkTier
+        self.trace = HostTrace(False)       # named host phases per step; off unless asked for
+        self.park_tier = ParkTier()
+        self.parked: dict = {}              # key -> Sequence whose device state lives in the park tier
 
     # ------------------------------------------------------------------------------ Engine trait
     def submit(self, req: EngineRequest) -> Submission:
@@ -205,42 +210,87 @@ class Scheduler:
     def step(self) -> bool:
         """One engine step. Returns False when there was nothing to do."""
         t0 = time.monotonic()
-        with self._lock:
+        with self.trace.phase("Plan"), self._lock:
             self._drain_aborted()
             self._admit_waiting()
             plan = self._plan()
         if plan is None:
             return False
         try:
-            if plan[0] == "prefill":
-                runs = [SeqRun(s.seq_id, s.prompt[pos:pos + n], pos, s.slot, 0, s.blocks, uid=s.seq_id,
-                               last_chunk=(pos + n == len(s.prompt)),
-                               temperature=s.req.params.temperature, want_seam=not s.req.params.greedy)
-                        for s, pos, n in plan[1]]
-                outs = self.ex.prefill(runs)
-            else:
-                _, dec, width, batch = plan
-                runs = []
-                for s in dec:
-                    drafts = (s.drafts + [0] * width)[: width - 1]
-                    runs.append(SeqRun(s.seq_id, [s.output[-1]] + drafts, s.pos, s.slot, s.shift, s.blocks,
-                                       uid=s.seq_id, step_no=s.step_no, temperature=s.req.params.temperature,
-                                       want_seam=not s.req.params.greedy))
-                outs = self.ex.decode(runs, width)
+          with self.trace.phase("Launch"):
+                if plan[0] == "prefill":
+                    runs = [SeqRun(s.seq_id, s.prompt[pos:pos + n], pos, s.slot, 0, s.blocks, uid=s.seq_id,
+                                   last_chunk=(pos + n == len(s.prompt)),
+                                   temperature=s.req.params.temperature, want_seam=not s.req.params.greedy)
+                            for s, pos, n in plan[1]]
+                    outs = self.ex.prefill(runs)
+                else:
+                    _, dec, width, batch = plan
+                    runs = []
+                    for s in dec:
+                        drafts = (s.drafts + [0] * width)[: width - 1]
+                        runs.append(SeqRun(s.seq_id, [s.output[-1]] + drafts, s.pos, s.slot, s.shift, s.blocks,
+                                           uid=s.seq_id, step_no=s.step_no, temperature=s.req.params.temperature,
+                                           want_seam=not s.req.params.greedy))
+                    outs = self.ex.decode(runs, width)
         except Exception as exc:       # the executor failed: every request learns why (fatal law)
             self.set_fatal(f"executor failed: {exc!r}")
             raise
         dt = time.monotonic() - t0
-        with self._lock:
+        with self.trace.phase("Accept"), self._lock:
             if plan[0] == "prefill":
                 self._commit_prefill(plan[1], outs, dt)
             else:
                 self._commit_decode(plan[1], plan[2], plan[3], outs, dt)
             self.counters["steps"] += 1
             self.last_step_s = dt
+        self.trace.end_step()
         if self.on_step:
             self.on_step({"kind": plan[0], "seconds": dt, "live": len(plan[1])})
         return True
+
+    # ------------------------------------------------------------------------------ parking / warm prompts
+    def park(self, seq_id: int) -> str:
+        """Moves a decoding sequence off the device: its KV pages and state slot become one verified
+        image in the park tier, its blocks and slot are released.  Returns the key to restore with."""
+        with self._lock:
+            s = next((x for x in self.running if x.seq_id == seq_id), None)
+            if s is None or s.prefilling or s.finished:
+                raise EngineRefused(f"sequence {seq_id} is not a decoding sequence", 409)
+            from .park import ParkImage
+            header, payload = self.ex.export_session(s.slot, s.blocks, s.pos)
+            key = f"seq{seq_id}"
+            header.update(seq_id=seq_id, pos=s.pos, shift=s.shift, step_no=s.step_no)
+            self.park_tier.put(key, ParkImage.build(header, payload))
+            self.running.remove(s)
+            self.arenas.release(s.blocks, s.slot)
+            s.blocks, s.slot = [], 0
+            self.parked[key] = s
+            return key
+
+    def restore(self, key: str) -> int:
+        """Brings a parked sequence back (fresh blocks and slot, bytes verified first)."""
+        with self._lock:
+            s = self.parked.get(key)
+            if s is None:
+                raise EngineRefused(f"no parked session {key!r}", 404)
+            total = len(s.prompt) + s.req.params.max_tokens + max(self.ex.decode_widths)
+            if len(self.running) >= self.cfg.max_seqs or not self.arenas.can_admit(total, 0):
+                raise EngineRefused("no room to restore the session now", 503)
+            img = self.park_tier.take(key)            # raises ParkError on a corrupt image: nothing reached the device
+            s.blocks, s.slot = self.arenas.admit(total, [])
+            self.ex.import_session(s.slot, s.blocks, img.header, img.payload)
+            del self.parked[key]
+            self.running.append(s)
+            self._wake.notify_all()
+            return s.seq_id
+
+    def warm(self, prompts: list) -> int:
+        """Warm prompts: run each prompt once (one generated token) so that its pages and state
+        snapshots are in the prefix cache before the first user request arrives."""
+        subs = [self.submit(EngineRequest(list(p), SamplingParams(max_tokens=1, ignore_eos=True))) for p in prompts]
+        self.run_until_idle()
+        return len(subs)
 
     # ------------------------------------------------------------------------------ phase 3
     def _commit_prefill(self, picks, outs, dt) -> None:

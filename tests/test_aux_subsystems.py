@@ -1,0 +1,155 @@
+"""Auxiliary subsystems on the CPU: session parking (byte-identical resume, corrupt images refused,
+RAM -> drive demotion with the crash law), warm prompts, host trace, step ledger, memory valve,
+rank watch with a fake rank process that exits 86."""
+import subprocess
+import sys
+import time
+
+import pytest
+
+from saber_engine_b200.sched.mem_valve import MemValve
+from saber_engine_b200.sched.mock import NullExecutor, reference_generation
+from saber_engine_b200.sched.park import ParkError, ParkImage, ParkTier
+from saber_engine_b200.sched.scheduler import Scheduler, SchedulerConfig
+from saber_engine_b200.serve import fatal
+from saber_engine_b200.serve.engine_api import EngineRequest, SamplingParams
+from saber_engine_b200.utils.host_trace import HostTrace, StartupLedger, StepLedger
+
+
+def _drain(sub):
+    toks = []
+    while True:
+        ev = sub.events.get_nowait()
+        if ev is None:
+            return toks, False
+        toks += ev.new_token_ids
+        if ev.finished:
+            return toks, True
+
+
+def test_park_and_restore_resumes_byte_identically(tmp_path):
+    ex = NullExecutor(vocab=997, max_seqs=2)
+    sch = Scheduler(ex, SchedulerConfig(max_seqs=2, max_ctx=4096))
+    sch.park_tier = ParkTier(ram_budget=1, directory=str(tmp_path))     # force the drive tier
+    prompt = list(range(5, 45))
+    sub = sch.submit(EngineRequest(prompt, SamplingParams(max_tokens=60, ignore_eos=True)))
+    for _ in range(6):
+        sch.step()
+    got, done = _drain(sub)
+    assert not done and len(got) > 0
+    other = sch.submit(EngineRequest(list(range(100, 130)), SamplingParams(max_tokens=8, ignore_eos=True)))
+    key = sch.park(sub.seq_id)
+    assert key in sch.park_tier and sch.park_tier.counters["demoted_to_drive"] >= 0
+    sch.run_until_idle()                       # the other request runs while the first is parked
+    assert _drain(other)[1]
+    assert sch.restore(key) == sub.seq_id
+    sch.run_until_idle()
+    rest, done = _drain(sub)
+    assert done
+    assert got + rest == reference_generation(prompt, 60, 997)
+
+
+def test_corrupt_parked_image_is_refused_before_it_reaches_the_device(tmp_path):
+    tier = ParkTier(ram_budget=1 << 30)
+    img = ParkImage.build({"kind": "t"}, bytes(range(256)) * 100)
+    tier.put("a", img)
+    img.payload = img.payload[:100] + b"\x00" + img.payload[101:] if img.payload[100:101] != b"\x00" else img.payload[:100] + b"\x01" + img.payload[101:]
+    with pytest.raises(ParkError, match="sha256"):
+        tier.take("a")
+    assert tier.counters["restore_failures"] == 1
+    # truncated file on the drive tier
+    t2 = ParkTier(ram_budget=0, directory=str(tmp_path))
+    t2.put("b", ParkImage.build({"kind": "t"}, b"x" * 5000))
+    t2.put("c", ParkImage.build({"kind": "t"}, b"y" * 5000))       # demotes b
+    path = tmp_path / "b.park"
+    assert path.exists() and not (tmp_path / ".b.park.tmp").exists()
+    path.write_bytes(path.read_bytes()[:-10])
+    with pytest.raises(ParkError, match="truncated"):
+        t2.take("b")
+
+
+def test_warm_prompts_fill_the_prefix_cache():
+    ex = NullExecutor(vocab=997, max_seqs=2)
+    sch = Scheduler(ex, SchedulerConfig(max_seqs=2, max_ctx=8192, prefix_cache_min_tokens=64, prefix_cache_interval=64))
+    system = list(range(1, 400))
+    assert sch.warm([system]) == 1
+    before = sch.prefix.stats.hits
+    sub = sch.submit(EngineRequest(system + [7, 8, 9], SamplingParams(max_tokens=4, ignore_eos=True)))
+    sch.run_until_idle()
+    toks, done = _drain(sub)
+    assert done and toks == reference_generation(system + [7, 8, 9], 4, 997)
+    assert sch.prefix.stats.hits == before + 1
+
+
+def test_host_trace_is_free_when_off_and_named_when_on():
+    ex = NullExecutor(vocab=997, max_seqs=1)
+    sch = Scheduler(ex, SchedulerConfig(max_seqs=1, max_ctx=2048))
+    sch.submit(EngineRequest([1, 2, 3], SamplingParams(max_tokens=5, ignore_eos=True)))
+    sch.run_until_idle()
+    assert sch.trace.steps == []
+    sch.trace = HostTrace(True)
+    sch.submit(EngineRequest([1, 2, 3], SamplingParams(max_tokens=5, ignore_eos=True)))
+    sch.run_until_idle()
+    s = sch.trace.summary()
+    assert s["steps"] >= 2 and {"Plan", "Launch", "Accept"} <= set(s["mean_us"])
+    with pytest.raises(KeyError):
+        with sch.trace.phase("NotAPhase"):
+            pass
+    led = StartupLedger()
+    with led.phase("boot"):
+        with led.phase("weights"):
+            pass
+    assert "boot/weights" in led.render()
+
+
+def test_step_ledger_writes_jsonl(tmp_path):
+    path = tmp_path / "steps.jsonl"
+    led = StepLedger(str(path))
+    for i in range(10):
+        led.record("decode", 8, 0.001 * (i + 1), device_ms=float(i))
+    led.close()
+    assert len(path.read_text().strip().splitlines()) == 10
+    assert led.percentiles("device_ms")["p50"] == 5.0
+
+
+def test_memory_valve_escalates_at_once_and_relaxes_with_hysteresis():
+    avail = {"v": 64 << 30}
+    v = MemValve(reader=lambda: avail["v"])
+    assert v.poll() == "ok"
+    avail["v"] = 7 << 30
+    assert v.poll() == "park"
+    avail["v"] = 9 << 30                    # above the park threshold but inside the hysteresis band
+    assert v.poll() == "park"
+    avail["v"] = 11 << 30                   # 8 GiB * 1.25 = 10 GiB cleared, demote still holds (< 16 GiB)
+    assert v.poll() == "demote"
+    avail["v"] = 3 << 30
+    assert v.poll() == "refuse" and not v.admits()
+    avail["v"] = 64 << 30
+    assert v.poll() == "ok"
+
+
+def test_rank_watch_sees_a_fake_rank_exit_86():
+    """Failure detection without a GPU: the failing rank is a CPU-only child process."""
+    fatal.reset_for_tests()
+    child = subprocess.Popen([sys.executable, "-c",
+                              "import sys, time; time.sleep(0.2); print('saber: FATAL rank 1: injected', file=sys.stderr); sys.exit(86)"],
+                             stderr=subprocess.PIPE)
+    seen = {}
+    fatal.RankWatch(child, 1, lambda rank, reason: seen.update(rank=rank, reason=reason))
+    for _ in range(100):
+        if seen:
+            break
+        time.sleep(0.05)
+    assert seen["rank"] == 1 and "FATAL rank 1: injected" in seen["reason"]
+    assert child.returncode == fatal.EXIT_FATAL
+    # the serving side turns it into the teardown law
+    ex = NullExecutor(vocab=97, max_seqs=1)
+    sch = Scheduler(ex, SchedulerConfig(max_seqs=1, max_ctx=512))
+    sub = sch.submit(EngineRequest([1, 2, 3], SamplingParams(max_tokens=50, ignore_eos=True)))
+    sch.step()
+    sch.set_fatal(seen["reason"])
+    evs = []
+    while (ev := sub.events.get_nowait()) is not None:
+        evs.append(ev)
+    assert evs[-1].finished and "injected" in evs[-1].error
+    fatal.reset_for_tests()

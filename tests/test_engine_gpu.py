@@ -71,3 +71,26 @@ def test_prefix_cache_reuse_keeps_ids(executor):
     tb, lb = _collect(b)
     assert [ta, tb] == cold
     assert lb.cached_tokens == 256
+
+
+def test_park_and_restore_on_the_device_resumes_with_the_same_ids(executor, tmp_path):
+    from saber_engine_b200.sched.park import ParkTier
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, executor.vocab, (90,), generator=g).tolist()
+    s = _sched(executor, prefix_cache=False)
+    sub = s.submit(EngineRequest(prompt, SamplingParams(max_tokens=40, ignore_eos=True)))
+    s.run_until_idle()
+    want = _collect(sub)[0]
+    s = _sched(executor, prefix_cache=False)
+    s.park_tier = ParkTier(ram_budget=1, directory=str(tmp_path))
+    sub = s.submit(EngineRequest(prompt, SamplingParams(max_tokens=40, ignore_eos=True)))
+    for _ in range(5):
+        s.step()
+    key = s.park(sub.seq_id)
+    # another request takes the slot and overwrites pages while the first one is away
+    other = s.submit(EngineRequest(prompt[::-1], SamplingParams(max_tokens=12, ignore_eos=True)))
+    s.run_until_idle()
+    assert _collect(other)[1].finished
+    s.restore(key)
+    s.run_until_idle()
+    assert _collect(sub)[0] == want
