@@ -28,6 +28,9 @@
 #include "../kernels/rowops.h"
 #include "../kernels/sample.h"
 
+extern "C" int saber_digest_launch(const void* buf, size_t bytes, unsigned long long* out, cudaStream_t stream);
+extern "C" int saber_digest_clear_launch(unsigned long long* out, int n, cudaStream_t stream);
+
 namespace {
 
 struct OpGemm { saber::GemmI8Params p; int stages; };
@@ -48,11 +51,13 @@ struct OpAllReduce { saber::AllReduceParams p; };
 struct OpPickMerge { saber::PickMergeParams p; };
 struct OpMoeRoute { saber::MoeRouteParams p; };
 struct OpMoeCombine { saber::MoeCombineParams p; };
+struct OpDigest { const void* buf; size_t bytes; unsigned long long* out; };
+struct OpDigestClear { unsigned long long* out; int n; };
 struct OpMoeGather { const int8_t* q; const float* scale; int M_pad; const int32_t* src_row; const int32_t* ntiles;
                      int8_t* q_out; float* scale_out; int rows_cap, M_pad_out, K; };
 
 using Op = std::variant<OpGemm, OpRow, OpEmbed, OpGdnConv, OpGdnRec, OpRope, OpAttn, OpArgmax,
-                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather>;
+                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather, OpDigest, OpDigestClear>;
 
 struct Entry {
   Op op;
@@ -96,6 +101,8 @@ int launch(const Op& op, cudaStream_t s) {
         else if constexpr (std::is_same_v<T, OpPickMerge>) return saber_pick_merge_launch(&o.p, s);
         else if constexpr (std::is_same_v<T, OpMoeRoute>) return saber_moe_route_launch(&o.p, s);
         else if constexpr (std::is_same_v<T, OpMoeCombine>) return saber_moe_combine_launch(&o.p, s);
+        else if constexpr (std::is_same_v<T, OpDigest>) return saber_digest_launch(o.buf, o.bytes, o.out, s);
+        else if constexpr (std::is_same_v<T, OpDigestClear>) return saber_digest_clear_launch(o.out, o.n, s);
         else if constexpr (std::is_same_v<T, OpMoeGather>)
           return saber_moe_gather_launch(o.q, o.scale, o.M_pad, o.src_row, o.ntiles, o.q_out, o.scale_out, o.rows_cap,
                                          o.M_pad_out, o.K, s);
@@ -180,6 +187,12 @@ int saber_program_add_moe_gather(void* h, const int8_t* q, const float* scale, i
                                  const int32_t* ntiles, int8_t* q_out, float* scale_out, int rows_cap,
                                  int M_pad_out, int K, const char* tag) {
   return add(h, OpMoeGather{q, scale, M_pad, src_row, ntiles, q_out, scale_out, rows_cap, M_pad_out, K}, 1, tag);
+}
+int saber_program_add_digest(void* h, const void* buf, size_t bytes, unsigned long long* out, const char* tag) {
+  return add(h, OpDigest{buf, bytes, out}, 1, tag);
+}
+int saber_program_add_digest_clear(void* h, unsigned long long* out, int n, const char* tag) {
+  return add(h, OpDigestClear{out, n}, 1, tag);
 }
 int saber_program_add_moe_combine(void* h, const saber::MoeCombineParams* p, const char* tag) {
   return add(h, OpMoeCombine{*p}, 1, tag);

@@ -94,6 +94,8 @@ class Bucket:
     n_launches: int = 0
     logits: Optional[torch.Tensor] = None
     keep: list = field(default_factory=list)
+    arenas: list = field(default_factory=list)     # pure activation buffers: written before read in every step
+    digests: Optional[torch.Tensor] = None         # int64 [n_layers + 1] stage digests (race_check = "shadow")
 
 
 class HybridModel:
@@ -101,8 +103,11 @@ class HybridModel:
                  max_seqs: int = 8, max_ctx: Optional[int] = None, kv_blocks: Optional[int] = None,
                  max_width: int = 9, weights: Optional[ModelWeights] = None, seed: int = 0,
                  comm=None, oracle_p: float = 0.0, oracle_seed: int = 0, gdn_vs: int = 2,
-                 use_drafter: bool = True):
+                 use_drafter: bool = True, race_check: str = "off"):
         self.cfg, self.tp, self.rank = cfg, tp, rank
+        if race_check not in ("off", "shadow"):
+            raise ValueError("race_check must be 'off' or 'shadow'")
+        self.race_check = race_check        # "shadow": a digest of the residual stream after every layer rides with the result
         self.sh = shard(cfg, tp, rank)
         self.device = torch.device(device)
         self.max_seqs = max_seqs
@@ -251,6 +256,10 @@ class HybridModel:
         def row(mode, Mr, K, tag, **kw):
             prog.row(mode, F.row_params(Mr, K, **kw), tag=tag)
 
+        digests = None
+        if self.race_check == "shadow":
+            digests = torch.zeros(cfg.n_layers + 1, dtype=torch.int64, device=dev)
+            prog.digest_clear(digests, cfg.n_layers + 1, tag="digest.clear")
         prog.embed(self.w.embed, at(lay.ids), h, M, H, 0, cfg.vocab, H, tag="embed")
         first = True
         ar_site = 0
@@ -313,11 +322,20 @@ class HybridModel:
                 from .moe_block import add_moe_block
                 self._site_nt[ar_site] = add_moe_block(self, prog, lw, qa_h, h, delta, M, t, keep, tp_site=ar_site)
             pending, ar_site = (ar_site, ar_site + 1) if self.tp > 1 else (-1, ar_site)
+            if digests is not None:     # what the layer left in the residual stream and in its MLP output
+                prog.digest(h, M * H * 2, digests.data_ptr() + 8 * i, tag=f"{t}.digest")
         self._build_head(prog, kind, nseq, width, M, Mh, lay, at, h, delta, qa_h, tap_buf, taps, keep,
                          ar_site, pending)
+        arenas = [h, delta, buf_in, conv_out, gdn_o, q_rot, attn_out, tap_buf, part_o, part_ml,
+                  qa_h.q, qa_h.scale, qa_gdn.q, qa_gdn.scale, qa_attn.q, qa_attn.scale]
         if cfg.moe is None:
             keep += [gu, qa_i]
-        return self._finish_bucket(prog, kind, nseq, width, M, lay, blob, blob_host, keep, capture)
+            arenas += [gu, qa_i.q, qa_i.scale]
+        keep.append(digests)
+        b = self._finish_bucket(prog, kind, nseq, width, M, lay, blob, blob_host, keep, capture)
+        b.arenas = [a for a in arenas if a is not None]
+        b.digests = digests
+        return b
 
     def _allreduce(self, prog: N.Program, buf: torch.Tensor, n_elems: int, site: int, tag: str) -> int:
         """Row-parallel partial sums -> full sums on every rank (no-op at TP=1)."""

@@ -188,6 +188,10 @@ def _declare(L: C.CDLL) -> None:
         "saber_program_add_memset": (I, [P, P, I, C.c_size_t, C.c_char_p]),
         "saber_program_add_copy": (I, [P, P, P, C.c_size_t, C.c_char_p]),
         "saber_program_add_allreduce": (I, [P, C.POINTER(AllReduceParams), C.c_char_p]),
+        "saber_digest_launch": (I, [P, C.c_size_t, P, S]),
+        "saber_digest_clear_launch": (I, [P, I, S]),
+        "saber_program_add_digest": (I, [P, P, C.c_size_t, P, C.c_char_p]),
+        "saber_program_add_digest_clear": (I, [P, P, I, C.c_char_p]),
         "saber_set_pdl": (None, [I]),
         "saber_get_pdl": (I, []),
         "saber_moe_route_launch": (I, [C.POINTER(MoeRouteParams), S]),
@@ -307,6 +311,13 @@ class Program:
 
     def allreduce(self, p: AllReduceParams, tag="allreduce") -> int:
         return self._L.saber_program_add_allreduce(self._h, C.byref(p), tag.encode())
+
+    def digest(self, buf, nbytes: int, out_word, tag: str = "digest") -> int:
+        """XOR-splitmix digest of `nbytes` of `buf` into the 8-byte word at `out_word` (cleared by digest_clear)."""
+        return self._L.saber_program_add_digest(self._h, ptr(buf), nbytes, ptr(out_word), tag.encode())
+
+    def digest_clear(self, out, n: int, tag: str = "digest_clear") -> int:
+        return self._L.saber_program_add_digest_clear(self._h, ptr(out), n, tag.encode())
 
     def add_moe_route(self, p: "MoeRouteParams", tag: str = "moe_route") -> int:
         return self._L.saber_program_add_moe_route(self._h, C.byref(p), tag.encode())
