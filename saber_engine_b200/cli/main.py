@@ -102,7 +102,7 @@ def build_engine(a):
         widths = _ints(a.engine_decode_widths)
         model = HybridModel(cfg, tp=a.engine_tp, rank=0, device="cuda", max_seqs=a.engine_max_seqs,
                             max_ctx=a.engine_max_ctx, kv_blocks=a.engine_kv_blocks or None, max_width=max(widths),
-                            weights=weights, seed=a.seed)
+                            weights=weights, seed=a.seed, race_check=a.engine_race_check)
         if a.autotune:
             from ..plan.autotune import TuneTable
             model.tune_table = TuneTable.load(a.autotune)
@@ -110,7 +110,37 @@ def build_engine(a):
                             prebuild=a.prebuild)
     cfg_s = SchedulerConfig(max_seqs=a.engine_max_seqs, max_ctx=a.engine_max_ctx, prefix_cache=not a.no_prefix_cache,
                             prefix_cache_bytes=a.prefix_cache_host_mib << 20, model_name=a.served_model_name)
-    return ex, Scheduler(ex, cfg_s, sampler=HostSampler())
+    sched = Scheduler(ex, cfg_s, sampler=HostSampler())
+    from ..sched.park import ParkTier
+    from ..utils.host_trace import HostTrace, StepLedger
+    sched.trace = HostTrace(bool(getattr(a, "engine_host_trace", False)))
+    sched.park_tier = ParkTier(getattr(a, "park_ram_mib", 8192) << 20, getattr(a, "park_dir", None))
+    ledger = StepLedger(getattr(a, "step_trace", None))
+    sched.step_ledger = ledger
+    fail = getattr(a, "fail_rank_after_steps", None)
+    fail_rank, fail_n = (int(x) for x in fail.split(":")) if fail else (None, None)
+
+    def on_step(info):
+        ledger.record(info["kind"], info["live"], info["seconds"])
+        if fail_n is not None and sched.counters["steps"] >= fail_n:     # host-side fault injection
+            from ..serve import fatal
+            sched.set_fatal(f"rank {fail_rank} failed after {fail_n} steps (injected)")
+            fatal.set_fatal(fail_rank, f"failed after {fail_n} steps (injected)", exit_process=True,
+                            watchdog_s=getattr(a, "fatal_watchdog_s", 10.0))
+    sched.on_step = on_step
+    poison = getattr(a, "poison_boot", None)
+    if poison is not None and hasattr(ex, "model"):
+        from ..runtime.race_check import poison_arenas
+        build = ex.model.build_bucket
+
+        def build_poisoned(*args, **kw):
+            fresh = tuple(args[:3]) not in ex.model.buckets
+            b = build(*args, **kw)
+            if fresh:
+                poison_arenas(b, poison & 0xFF)
+            return b
+        ex.model.build_bucket = build_poisoned
+    return ex, sched
 
 
 def cmd_engine(a) -> int:
@@ -122,6 +152,9 @@ def cmd_engine(a) -> int:
     template = Path(a.chat_template).read_text() if a.chat_template and Path(a.chat_template).exists() else None
     state = ServerState(sched, tok, a.served_model_name, api_keys=a.api_key or (), chat_template=template,
                         census_fn=(lambda: dict(getattr(ex, "census", {}))))
+    for path in getattr(a, "warm_prompt", []):
+        ids = tok.encode(Path(path).read_text())
+        sched.warm([ids])
     sched.spawn_step_loop()
     try:
         uvicorn.run(create_app(state), host=a.host, port=a.port, log_level="warning")
@@ -230,6 +263,17 @@ def make_parser() -> argparse.ArgumentParser:
     e.add_argument("--prebuild", action="store_true")
     e.add_argument("--seed", type=int, default=0)
     e.add_argument("--mock-vocab", type=int, default=1024)
+    e.add_argument("--engine-host-trace", action="store_true", help="named host phases per step (an attribution, not a published time)")
+    e.add_argument("--engine-race-check", default="off", choices=["off", "shadow"])
+    e.add_argument("--poison-boot", type=lambda v: int(v, 0), default=None, metavar="BYTE",
+                   help="fill every activation arena with this byte when a bucket is built (write-before-read proof)")
+    e.add_argument("--warm-prompt", action="append", default=[], metavar="FILE",
+                   help="text file whose content is prefilled at boot so its pages are in the prefix cache")
+    e.add_argument("--step-trace", metavar="PATH", help="append one JSON line per engine step")
+    e.add_argument("--park-dir", help="drive tier of parked sessions")
+    e.add_argument("--park-ram-mib", type=int, default=8192)
+    e.add_argument("--fatal-watchdog-s", type=float, default=10.0)
+    e.add_argument("--fail-rank-after-steps", default=None, metavar="R:N", help=argparse.SUPPRESS)
     x = sub.add_parser("explain")
     x.add_argument("--manifest")
     x.add_argument("--model", default="qwen38-27b")
