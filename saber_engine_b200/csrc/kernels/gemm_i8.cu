@@ -99,7 +99,9 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
     w_scale_base += static_cast<size_t>(t.x) * p.N_pad;
   }
   const int n0 = tile_n * 256;
-  const uint32_t wbytes = p.w4 ? 16384u : 32768u;
+  // weight formats: 0 = int8 tiles, 1 = packed int4, 2 = MXFP4 (packed e2m1 + 1 KiB of block shifts)
+  const bool mx = p.w4 == 2;
+  const uint32_t wbytes = mx ? 17408u : (p.w4 ? 16384u : 32768u);
   const uint32_t abytes = static_cast<uint32_t>(p.nt) * 128u;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -184,7 +186,8 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       // M = 128 token rows (only the first nt are real), N = 256 output features
-      const uint32_t idesc = make_idesc(kCFmtS32, kFmtS8, kFmtS8, 128, 256);
+      const uint32_t idesc = mx ? make_idesc(kCFmtF32, kFmtE4M3, kFmtE4M3, 128, 256)
+                                : make_idesc(kCFmtS32, kFmtS8, kFmtS8, 128, 256);
       const uint64_t desc_hi = make_desc_k128(0);  // everything but the start address
       uint32_t a_addr = a_smem;
       int s = 0, u = 0;
@@ -204,10 +207,17 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
         const uint64_t a_desc = desc_hi | static_cast<uint64_t>((a_addr & 0x3FFFFu) >> 4);
         const uint64_t b_desc = desc_hi | static_cast<uint64_t>((w_addr & 0x3FFFFu) >> 4);
         // 32 int8 = 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
-        mma_i8_ss(tmem_d, a_desc, b_desc, idesc, it != 0 ? 1u : 0u);
-        mma_i8_ss(tmem_d, a_desc + 2, b_desc + 2, idesc, 1u);
-        mma_i8_ss(tmem_d, a_desc + 4, b_desc + 4, idesc, 1u);
-        mma_i8_ss(tmem_d, a_desc + 6, b_desc + 6, idesc, 1u);
+        if (mx) {   // fp8 x fp8 -> fp32 (the weights were folded to e4m3 by the transform warps)
+          mma_f8_ss(tmem_d, a_desc, b_desc, idesc, it != 0 ? 1u : 0u);
+          mma_f8_ss(tmem_d, a_desc + 2, b_desc + 2, idesc, 1u);
+          mma_f8_ss(tmem_d, a_desc + 4, b_desc + 4, idesc, 1u);
+          mma_f8_ss(tmem_d, a_desc + 6, b_desc + 6, idesc, 1u);
+        } else {
+          mma_i8_ss(tmem_d, a_desc, b_desc, idesc, it != 0 ? 1u : 0u);
+          mma_i8_ss(tmem_d, a_desc + 2, b_desc + 2, idesc, 1u);
+          mma_i8_ss(tmem_d, a_desc + 4, b_desc + 4, idesc, 1u);
+          mma_i8_ss(tmem_d, a_desc + 6, b_desc + 6, idesc, 1u);
+        }
         mma_commit(bar_empty + 8 * s);
         if (p.w4) {
           mma_commit(bar_ufree + 8 * u);
@@ -246,6 +256,43 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
                        : "r"(src + off));
         }
         if (!mbar_wait(bar_ufree + 8 * u, ufree_ph, p.err, kErrWaitEmpty)) { ok = false; break; }
+        if (mx) {
+          // MXFP4: a 16-bit half of a packed word = four e2m1 codes of one row = the selector of a
+          // byte permute over the eight e4m3 magnitudes, shifted down by the block's exponent
+          // distance k to the row's largest block (entries whose exponent field would reach 0
+          // are flushed); the sign bits come from a second permute over {0x00, 0x80}.
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t ci = static_cast<uint32_t>(i * 256 + tid8);
+            const uint32_t r = ci >> 3, lc = (ci & 7u) ^ (r & 7u);
+            uint32_t klo, khi;
+            asm volatile("ld.shared.u8 %0, [%1];" : "=r"(klo) : "r"(src + 16384u + r * 4u + (lc >> 1)));
+            asm volatile("ld.shared.u8 %0, [%1];" : "=r"(khi) : "r"(src + 16384u + (r + 128u) * 4u + (lc >> 1)));
+            uint32_t ta[2], tb[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint32_t k = h ? khi : klo;
+              const uint32_t ma = (k < 11u ? 0x0000FF00u : 0u) | (k < 12u ? 0xFFFF0000u : 0u);
+              const uint32_t mb = (k < 13u ? 0x0000FFFFu : 0u) | (k < 14u ? 0xFFFF0000u : 0u);
+              const uint32_t sub = (k << 3) * 0x01010101u;
+              ta[h] = (0x64605800u & ma) - (sub & ma);
+              tb[h] = (0x74706C68u & mb) - (sub & mb);
+            }
+            uint32_t olo[4], ohi[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t w = v[i][j];
+              const uint32_t wl = w & 0xFFFFu, wh = w >> 16;
+              olo[j] = __byte_perm(ta[0], tb[0], wl & 0x7777u) | __byte_perm(0x00008000u, 0u, (wl >> 3) & 0x1111u);
+              ohi[j] = __byte_perm(ta[1], tb[1], wh & 0x7777u) | __byte_perm(0x00008000u, 0u, (wh >> 3) & 0x1111u);
+            }
+            const uint32_t off = ci * 16u;
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + off), "r"(olo[0]), "r"(olo[1]),
+                         "r"(olo[2]), "r"(olo[3]) : "memory");
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16384u + off), "r"(ohi[0]), "r"(ohi[1]),
+                         "r"(ohi[2]), "r"(ohi[3]) : "memory");
+          }
+        } else
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const uint32_t off = static_cast<uint32_t>(i * 256 + tid8) * 16u;
@@ -287,6 +334,10 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
       const bool warp_live = q4 * 32 < mt;  // warp-uniform: this lane quarter holds live rows
       const uint32_t t_lane = tmem_d + (static_cast<uint32_t>(q4 * 32) << 16);
       const int ncols = min(256, p.N_pad - n0);
+      // accumulator words are int32 (integer formats) or fp32 bits (MXFP4)
+      auto acc_f = [&](uint32_t raw) -> float {
+        return mx ? __uint_as_float(raw) : static_cast<float>(static_cast<int32_t>(raw));
+      };
       // tensor-parallel mode: a finished 16-byte group of outputs goes to every rank's receive
       // region (slot = parity of the call's sequence number, source = this rank)
       const bool tp = p.tp_nranks > 1;
@@ -325,8 +376,8 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
               uint32_t pk[16];
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                const float lo = static_cast<float>(static_cast<int32_t>(r[2 * j])) * (asc * w_scale_s[c + 2 * j]);
-                const float hi = static_cast<float>(static_cast<int32_t>(r[2 * j + 1])) * (asc * w_scale_s[c + 2 * j + 1]);
+                const float lo = acc_f(r[2 * j]) * (asc * w_scale_s[c + 2 * j]);
+                const float hi = acc_f(r[2 * j + 1]) * (asc * w_scale_s[c + 2 * j + 1]);
                 const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
                 pk[j] = *reinterpret_cast<const uint32_t*>(&b2);
               }
@@ -460,16 +511,27 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
 #pragma unroll
             for (int u = 0; u < kIlp; ++u) {
               if (base + u * 128 >= n_items) continue;
-              int4 x = make_int4(0, 0, 0, 0);
+              float f[4];
+              if (mx) {   // fp32 partials: added in split order, the same on every launch
+                f[0] = f[1] = f[2] = f[3] = 0.f;
 #pragma unroll
-              for (int sp = 0; sp < kMaxS; ++sp)
-                if (sp < p.splits) { x.x += y[u][sp].x; x.y += y[u][sp].y; x.z += y[u][sp].z; x.w += y[u][sp].w; }
+                for (int sp = 0; sp < kMaxS; ++sp)
+                  if (sp < p.splits) {
+                    f[0] += __int_as_float(y[u][sp].x); f[1] += __int_as_float(y[u][sp].y);
+                    f[2] += __int_as_float(y[u][sp].z); f[3] += __int_as_float(y[u][sp].w);
+                  }
+              } else {
+                int4 x = make_int4(0, 0, 0, 0);
+#pragma unroll
+                for (int sp = 0; sp < kMaxS; ++sp)
+                  if (sp < p.splits) { x.x += y[u][sp].x; x.y += y[u][sp].y; x.z += y[u][sp].z; x.w += y[u][sp].w; }
+                f[0] = static_cast<float>(x.x); f[1] = static_cast<float>(x.y);
+                f[2] = static_cast<float>(x.z); f[3] = static_cast<float>(x.w);
+              }
               const int c = c4[u] << 2;
               const float asc = p.a_scale[m0 + rr[u]];
-              const __nv_bfloat162 b0 = __floats2bfloat162_rn(static_cast<float>(x.x) * (asc * w_scale_s[c]),
-                                                              static_cast<float>(x.y) * (asc * w_scale_s[c + 1]));
-              const __nv_bfloat162 b1 = __floats2bfloat162_rn(static_cast<float>(x.z) * (asc * w_scale_s[c + 2]),
-                                                              static_cast<float>(x.w) * (asc * w_scale_s[c + 3]));
+              const __nv_bfloat162 b0 = __floats2bfloat162_rn(f[0] * (asc * w_scale_s[c]), f[1] * (asc * w_scale_s[c + 1]));
+              const __nv_bfloat162 b1 = __floats2bfloat162_rn(f[2] * (asc * w_scale_s[c + 2]), f[3] * (asc * w_scale_s[c + 3]));
               const uint2 pk = make_uint2(*reinterpret_cast<const uint32_t*>(&b0), *reinterpret_cast<const uint32_t*>(&b1));
               if (tp) {
                 if (n0 + c < p.N) {
@@ -541,6 +603,7 @@ extern "C" int saber_gemm_i8_smem_bytes(int nt, int stages) {
 // The token-side descriptor spans 128 rows although only nt are loaded: its reads run on into the
 // operand buffers / weight ring, which lie behind the token ring inside the same allocation.
 extern "C" int saber_gemm_i8_smem_bytes_w(int nt, int stages, int w4) {
+  if (w4 == 2) return stages * (17408 + nt * 128) + 3 * 32768 + 1024;
   return w4 ? stages * (16384 + nt * 128) + 3 * 32768 + 1024 : stages * (32768 + nt * 128) + 1024;
 }
 

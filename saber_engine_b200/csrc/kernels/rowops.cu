@@ -16,6 +16,7 @@
 #include "gemm_i8.h"
 #include "ptx_sm100.cuh"
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 namespace saber {
 
@@ -47,6 +48,24 @@ __device__ __forceinline__ float block_reduce(float v, float* red) {
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
 
+// four values -> four quantised bytes (int8 round-to-nearest with clamp, or fp8 e4m3 saturating)
+__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, float inv, int qfmt) {
+  if (qfmt == 1) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a * inv, b * inv), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c * inv, d * inv), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+  }
+  const float x[4] = {a, b, c, d};
+  uint32_t word = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    int qi = __float2int_rn(x[j] * inv);
+    qi = max(-127, min(127, qi));
+    word |= (static_cast<uint32_t>(qi) & 0xFFu) << (8 * j);
+  }
+  return word;
+}
+
 struct alignas(16) Bf16x8 {
   __nv_bfloat162 v[4];
 };
@@ -69,24 +88,18 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
 
 // Quantise the row held in shared memory (bf16, K values) and store it tiled. All threads call.
 __device__ __forceinline__ void quant_store_row(const __nv_bfloat16* h, int K, int m, int M_pad,
-                                                float amax, int8_t* q, float* scale) {
-  const float inv = amax > 0.f ? 127.f / amax : 0.f;
-  if (threadIdx.x == 0) scale[m] = amax / 127.f;
+                                                float amax, int8_t* q, float* scale, int qfmt) {
+  const float qmax = qfmt == 1 ? 448.f : 127.f;
+  const float inv = amax > 0.f ? qmax / amax : 0.f;
+  if (threadIdx.x == 0) scale[m] = amax / qmax;
   const int nchunk = K >> 4;
   for (int ch = threadIdx.x; ch < nchunk; ch += blockDim.x) {
     const int k0 = ch << 4;
     uint32_t w[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      uint32_t word = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float x = __bfloat162float(h[k0 + i * 4 + j]) * inv;
-        int qi = __float2int_rn(x);
-        qi = max(-127, min(127, qi));
-        word |= (static_cast<uint32_t>(qi) & 0xFFu) << (8 * j);
-      }
-      w[i] = word;
+      w[i] = quant4(__bfloat162float(h[k0 + i * 4]), __bfloat162float(h[k0 + i * 4 + 1]),
+                    __bfloat162float(h[k0 + i * 4 + 2]), __bfloat162float(h[k0 + i * 4 + 3]), inv, qfmt);
     }
     const int kb = k0 >> 7, c = (k0 & 127) >> 4;
     int8_t* dst = q + (static_cast<size_t>(kb) * M_pad + m) * 128 + (((c ^ (m & 7)) & 7) << 4);
@@ -249,7 +262,7 @@ __global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpPa
     }
   }
   amax = block_reduce<true>(amax, red);  // its barriers also publish h to the whole block
-  if (p.q) quant_store_row(h, K, m, p.M_pad, amax, p.q, p.scale);
+  if (p.q) quant_store_row(h, K, m, p.M_pad, amax, p.q, p.scale, p.qfmt);
 }
 
 // Register-resident form of ADD_RMS / SILU_MUL / GATE_SIG / PLAIN: a thread owns whole 16-value
@@ -397,24 +410,17 @@ __global__ void __launch_bounds__(kRowThreads) row_reg_kernel(const RowOpParams 
   }
   amax = block_reduce<true>(amax, red);
   if (p.q) {
-    const float inv = amax > 0.f ? 127.f / amax : 0.f;
-    if (threadIdx.x == 0) p.scale[m] = amax / 127.f;
+    const float qmax = p.qfmt == 1 ? 448.f : 127.f;
+    const float inv = amax > 0.f ? qmax / amax : 0.f;
+    if (threadIdx.x == 0) p.scale[m] = amax / qmax;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
       const int ch = threadIdx.x + c * kRowThreads;
       if (ch >= nchunk) continue;
       uint32_t w[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t word = 0;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          int qi = __float2int_rn(hv[c][i * 4 + j] * inv);
-          qi = max(-127, min(127, qi));
-          word |= (static_cast<uint32_t>(qi) & 0xFFu) << (8 * j);
-        }
-        w[i] = word;
-      }
+      for (int i = 0; i < 4; ++i)
+        w[i] = quant4(hv[c][i * 4], hv[c][i * 4 + 1], hv[c][i * 4 + 2], hv[c][i * 4 + 3], inv, p.qfmt);
       const int kb = ch >> 3, cc = ch & 7;
       int8_t* dst = p.q + (static_cast<size_t>(kb) * p.M_pad + m) * 128 + (((cc ^ (m & 7)) & 7) << 4);
       *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);

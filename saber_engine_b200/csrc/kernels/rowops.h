@@ -37,6 +37,8 @@ struct RowOpParams {
   // optional device row count: blocks of rows >= *m_live leave without writing (expert-major row
   // spaces whose live length is only known on the device)
   const int32_t* m_live;
+  // quantised output format: 0 = int8 (scale amax / 127), 1 = fp8 e4m3 (scale amax / 448)
+  int qfmt;
 };
 
 }  // namespace saber

@@ -25,10 +25,28 @@ class QuantWeight:
     N: int
     K: int
     w4: bool
+    mx: bool = False         # MXFP4 tiles (e2m1 codes + block shifts): fp8 activations, fp32 accumulate
 
     @property
     def N_pad(self) -> int:
         return self.tiles.shape[0] * L.TILE_N
+
+    @property
+    def fmt_code(self) -> int:
+        """The kernel's weight-format selector: 0 int8, 1 int4, 2 MXFP4."""
+        return 2 if self.mx else int(self.w4)
+
+    @staticmethod
+    def from_mxfp4(codes: torch.Tensor, e8m0: torch.Tensor, device=None) -> "QuantWeight":
+        """e2m1 codes uint8 [N, K] + e8m0 block scales uint8 [N, K/32] (the pack's MXFP4 records)."""
+        from ..pack import quant_fp4 as Q
+        Nn, K = codes.shape
+        shift, row_scale = Q.fold_mxfp4(codes, e8m0)
+        tiles = L.tile_weight_mxfp4(codes, shift)
+        sc = torch.zeros(tiles.shape[0] * L.TILE_N, dtype=torch.float32)
+        sc[:Nn] = row_scale
+        dev = device if device is not None else codes.device
+        return QuantWeight(tiles.to(dev).contiguous(), sc.to(dev), Nn, K, True, mx=True)
 
     @staticmethod
     def from_float(w: torch.Tensor, bits: int = 4, device=None) -> "QuantWeight":
@@ -53,16 +71,17 @@ class QuantAct:
     scale: torch.Tensor      # fp32 [M_pad]
     M: int
     K: int
+    fp8: bool = False        # bytes are fp8 e4m3 (scale = amax / 448) instead of int8 (amax / 127)
 
     @property
     def M_pad(self) -> int:
         return self.q.shape[1]
 
     @staticmethod
-    def alloc(M: int, K: int, device) -> "QuantAct":
+    def alloc(M: int, K: int, device, fp8: bool = False) -> "QuantAct":
         m_pad = L.padded_rows(M)
         return QuantAct(torch.empty(K // 128, m_pad, 128, dtype=torch.int8, device=device),
-                        torch.empty(m_pad, dtype=torch.float32, device=device), M, K)
+                        torch.empty(m_pad, dtype=torch.float32, device=device), M, K, fp8)
 
 
 class GemmScratch:
@@ -121,7 +140,8 @@ def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,
     p.w, p.w_scale, p.a, p.a_scale = w.tiles.data_ptr(), w.scale.data_ptr(), a.q.data_ptr(), a.scale.data_ptr()
     p.out, p.ws, p.counters, p.err = out.data_ptr(), sc.ws.data_ptr(), sc.counters.data_ptr(), sc.err.data_ptr()
     p.M, p.M_pad, p.N, p.N_pad, p.K = a.M, a.M_pad, w.N, w.N_pad, w.K
-    p.nt, p.splits, p.w4, p.ldo = nt, splits, int(w.w4), out.stride(0)
+    assert bool(getattr(w, 'mx', False)) == bool(a.fp8), "MXFP4 weights take fp8 activations, integer weights int8"
+    p.nt, p.splits, p.w4, p.ldo = nt, splits, w.fmt_code, out.stride(0)
     p.coop = coop
     assert out.stride(0) % 8 == 0, "GEMM output rows must be 16-byte aligned"
     return p
@@ -152,6 +172,7 @@ def row_params(M: int, K: int, *, a=None, a_f32=None, b=None, res=None, w=None, 
     p.ldb = ldb if ldb is not None else (b.stride(0) if b is not None else 0)
     p.ldres = res.stride(0) if res is not None else 0
     p.ldout = out.stride(0) if out is not None else 0
+    p.qfmt = int(qa.fp8) if qa is not None else 0
     return p
 
 
@@ -198,9 +219,9 @@ def gdn_norm_quant(o: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float
     return qa, out
 
 
-def plain_quant(x: torch.Tensor) -> QuantAct:
+def plain_quant(x: torch.Tensor, fp8: bool = False) -> QuantAct:
     M, K = x.shape
-    qa = QuantAct.alloc(M, K, x.device)
+    qa = QuantAct.alloc(M, K, x.device, fp8)
     _row(N.ROW_PLAIN, row_params(M, K, a=x, qa=qa))
     return qa
 

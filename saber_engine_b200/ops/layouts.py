@@ -128,3 +128,34 @@ def untile_act_int8(t: torch.Tensor, M: int) -> torch.Tensor:
     src = chunks[None, :] ^ rows[:, None]
     idx = src[None, :, :, None].expand(kb, m_pad, 8, 16)
     return torch.gather(x, 2, idx).permute(1, 0, 2, 3).reshape(m_pad, kb * 128)[:M].contiguous()
+
+
+# ------------------------------------------------------------------------------- MXFP4 (folded to fp8 in the kernel)
+MX_TILE_BYTES = 16384 + 1024
+
+
+def tile_weight_mxfp4(codes: torch.Tensor, shift: torch.Tensor) -> torch.Tensor:
+    """e2m1 codes uint8 [N, K] + per-(row, 32-block) shifts uint8 [N, K/32] -> uint8 tiles
+    [N_pad/256, K/128, 17408].
+
+    The first 16 KiB of a tile follow the int8 image's chunk order (row-major 128-byte rows, 16-byte
+    chunks XOR-swizzled by row & 7): packed chunk `ci` carries the 16 codes of image chunk `ci`
+    (row r < 128) and of image chunk `ci + 1024` (row r + 128) as four 32-bit words, word j = codes
+    4j..4j+3 of row r in its low 16 bits (one nibble each) and of row r + 128 in its high 16 bits, so
+    a 16-bit half is directly the selector of one byte-permute.  The last 1 KiB holds the shifts,
+    [256 rows][4 blocks]."""
+    N, K = codes.shape
+    img = tile_weight_int8(codes.to(torch.int8)).view(torch.uint8)            # [nt, kb, 32768] one code per byte
+    nt, kb, _ = img.shape
+    lo = img[..., :16384].reshape(nt, kb, 1024, 4, 4).to(torch.int32)         # chunk, word, code
+    hi = img[..., 16384:].reshape(nt, kb, 1024, 4, 4).to(torch.int32)
+    b0 = lo[..., 0] | (lo[..., 1] << 4)
+    b1 = lo[..., 2] | (lo[..., 3] << 4)
+    b2 = hi[..., 0] | (hi[..., 1] << 4)
+    b3 = hi[..., 2] | (hi[..., 3] << 4)
+    packed = torch.stack([b0, b1, b2, b3], dim=-1).to(torch.uint8).reshape(nt, kb, 16384)
+    n_pad = nt * TILE_N
+    sh = torch.zeros(n_pad, K // 32, dtype=torch.uint8, device=codes.device)
+    sh[:N] = shift
+    sh = sh.reshape(nt, TILE_N, kb, 4).permute(0, 2, 1, 3).reshape(nt, kb, 1024)
+    return torch.cat([packed, sh], dim=-1).contiguous()

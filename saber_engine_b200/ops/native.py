@@ -51,7 +51,7 @@ class RowOpParams(C.Structure):
                 ("eps", F), ("out", P), ("q", P), ("scale", P), ("M", I), ("M_pad", I), ("K", I),
                 ("lda", I), ("ldb", I), ("ldres", I), ("ldout", I), ("tp_recv", P), ("tp_flags", P),
                 ("tp_seq_base", P), ("err", P), ("tp_nranks", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I),
-                ("tp_nt", I), ("tp_tiles_n", I), ("m_live", P)]
+                ("tp_nt", I), ("tp_tiles_n", I), ("m_live", P), ("qfmt", I)]
 
 
 class GdnConvParams(C.Structure):
