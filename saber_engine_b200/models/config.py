@@ -58,6 +58,7 @@ class HybridConfig:
     norm_offset: float = 1.0            # Gemma-style (1 + w)
     attn_out_gate: bool = True
     tie_embeddings: bool = False
+    weight_format: str = "iu8"         # 4-bit linears: "iu8" (int4 x int8 acts) | "mxfp4" (e2m1/e8m0 x fp8 acts)
     max_ctx: int = 262144
     page_tokens: int = 16
     moe: Optional[MoEConfig] = None
@@ -217,6 +218,7 @@ class TinyQwen3Config:
 def by_name(name: str):
     table = {"qwen38-27b": qwen38_27b, "flashnext-moe": flashnext_moe,
              "flashnext-ref": lambda: flashnext_moe(True), "hybrid-mini": scaled_hybrid,
+             "qwen38-27b-mxfp4": lambda: dataclasses.replace(qwen38_27b(), name="qwen38-27b-mxfp4", weight_format="mxfp4"),
              "tiny-qwen3": TinyQwen3Config}
     if name not in table:
         raise KeyError(f"unknown model {name!r}; known: {sorted(table)}")

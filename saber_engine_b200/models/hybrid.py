@@ -164,9 +164,18 @@ class HybridModel:
     def _qa(self, M: int, K: int) -> F.QuantAct:
         return F.QuantAct.alloc(M, K, self.device)
 
+    @staticmethod
+    def _fmt(a: Optional[F.QuantAct], w) -> Optional[F.QuantAct]:
+        """The activation buffer seen in the byte format the consuming linear multiplies with
+        (int8 for integer weights, fp8 e4m3 for MXFP4): same storage, different law."""
+        if a is None:
+            return None
+        return F.QuantAct(a.q, a.scale, a.M, a.K, fp8=bool(getattr(w, "mx", False)))
+
     def _gemm(self, prog: N.Program, w: F.QuantWeight, a: F.QuantAct, out: torch.Tensor, tag: str,
               tp_site: int = -1) -> None:
         """tp_site >= 0: a row-parallel GEMM whose epilogue pushes its partial sums to every rank."""
+        a = self._fmt(a, w)
         splits = self.pick_splits(w, a)
         p = F.gemm_params(w, a, out, self.scratch, splits=splits)
         if tp_site >= 0 and self.tp > 1:
@@ -266,7 +275,7 @@ class HybridModel:
         pending = -1          # site of the TP GEMM whose pushed output the next add-norm consumes
         for i, lw in enumerate(self.w.layers):
             t = f"L{i}"
-            self._add_rms(prog, M, f"{t}.in_norm", lw.in_norm, h, qa_h, None if first else delta, pending)
+            self._add_rms(prog, M, f"{t}.in_norm", lw.in_norm, h, self._fmt(qa_h, lw.mixer_in), None if first else delta, pending)
             first = False
             if i in taps:
                 prog.copy(tap_buf[taps.index(i)], h, tag=f"{t}.tap")
@@ -285,7 +294,7 @@ class HybridModel:
                 rp.cu_rows, rp.slots, rp.shift = at(lay.cu_rows), at(lay.slots), at(lay.shift)
                 prog.gdn_rec(rp, nseq, self.gdn_vs, tag=f"{t}.gdn.rec")
                 row(N.ROW_GDN_NORM, M, sh.gdn_out_k, f"{t}.gdn.norm_quant", a_f32=gdn_o,
-                    b=buf_in[:, C_:], w=lw.gdn_norm, eps=cfg.eps, qa=qa_gdn, ldb=ld_in)
+                    b=buf_in[:, C_:], w=lw.gdn_norm, eps=cfg.eps, qa=self._fmt(qa_gdn, lw.mixer_out), ldb=ld_in)
                 self._gemm(prog, lw.mixer_out, qa_gdn, delta, f"{t}.gdn.out_proj", tp_site=ar_site)
             else:
                 nq, nkv = sh.n_q_heads, sh.n_kv_heads
@@ -308,15 +317,15 @@ class HybridModel:
                 ao = attn_out.view(M, nq * D)
                 if cfg.attn_out_gate:
                     row(N.ROW_GATE_SIG, M, nq * D, f"{t}.attn.gate_quant", a=ao, b=buf_in[:, nq * D:],
-                        qa=qa_attn, ldb=ld_in)
+                        qa=self._fmt(qa_attn, lw.mixer_out), ldb=ld_in)
                 else:
-                    row(N.ROW_PLAIN, M, nq * D, f"{t}.attn.quant", a=ao, qa=qa_attn)
+                    row(N.ROW_PLAIN, M, nq * D, f"{t}.attn.quant", a=ao, qa=self._fmt(qa_attn, lw.mixer_out))
                 self._gemm(prog, lw.mixer_out, qa_attn, delta, f"{t}.attn.o_proj", tp_site=ar_site)
             pending, ar_site = (ar_site, ar_site + 1) if self.tp > 1 else (-1, ar_site)
-            self._add_rms(prog, M, f"{t}.post_norm", lw.post_norm, h, qa_h, delta, pending)
+            self._add_rms(prog, M, f"{t}.post_norm", lw.post_norm, h, self._fmt(qa_h, lw.gate_up), delta, pending)
             if cfg.moe is None:
                 self._gemm(prog, lw.gate_up, qa_h, gu, f"{t}.mlp.gate_up")
-                row(N.ROW_SILU_MUL, M, sh.ffn_inter, f"{t}.mlp.silu_mul_quant", a=gu, qa=qa_i)
+                row(N.ROW_SILU_MUL, M, sh.ffn_inter, f"{t}.mlp.silu_mul_quant", a=gu, qa=self._fmt(qa_i, lw.down))
                 self._gemm(prog, lw.down, qa_i, delta, f"{t}.mlp.down", tp_site=ar_site)
             else:
                 from .moe_block import add_moe_block
@@ -363,7 +372,7 @@ class HybridModel:
         logits = torch.zeros(Mh, (sh.vocab + 7) // 8 * 8, dtype=torch.bfloat16, device=dev)
         self._out_views = None
         if decode:
-            self._add_rms(prog, M, "final_norm", self.w.final_norm, h, qa_h, delta, pending)
+            self._add_rms(prog, M, "final_norm", self.w.final_norm, h, self._fmt(qa_h, self.w.lm_head), delta, pending)
             qa_head = qa_h
         else:
             normed = torch.zeros(M, H, dtype=torch.bfloat16, device=dev)
@@ -371,7 +380,7 @@ class HybridModel:
             self._add_rms(prog, M, "final_norm", self.w.final_norm, h, None, delta, pending, out=normed)
             prog.embed(normed, at(lay.last_rows), last, nseq, H, 0, M, H, tag="gather_last_rows")
             qa_head = self._qa(nseq, H)
-            prog.row(N.ROW_PLAIN, F.row_params(nseq, H, a=last, qa=qa_head), tag="head_quant")
+            prog.row(N.ROW_PLAIN, F.row_params(nseq, H, a=last, qa=self._fmt(qa_head, self.w.lm_head)), tag="head_quant")
             keep += [normed, last, qa_head]
         self._gemm(prog, self.w.lm_head, qa_head, logits, "lm_head")
         prog.argmax(logits, Mh, logits.stride(0), sh.vocab, sh.vocab_first, o_picks, pick_val, tag="argmax")
@@ -408,7 +417,7 @@ class HybridModel:
         for j in range(nt):
             prog.embed(tap_buf[j], acc_ptr, cat[:, j * H:], nseq, H, 0, M, dc.n_taps * H, tag=f"draft.tap{j}")
         qa_cat = self._qa(nseq, dc.n_taps * H)
-        prog.row(N.ROW_PLAIN, F.row_params(nseq, dc.n_taps * H, a=cat, qa=qa_cat), tag="draft.tap_quant")
+        prog.row(N.ROW_PLAIN, F.row_params(nseq, dc.n_taps * H, a=cat, qa=self._fmt(qa_cat, dw.aux_fc)), tag="draft.tap_quant")
         ctx = torch.zeros(nseq, Hd, dtype=torch.bfloat16, device=dev)
         self._gemm(prog, dw.aux_fc, qa_cat, ctx, "draft.aux_fc")
         tok = torch.zeros(nseq, Hd, dtype=torch.bfloat16, device=dev)
@@ -421,13 +430,13 @@ class HybridModel:
         gu = torch.zeros(R, 2 * dc.inter, dtype=torch.bfloat16, device=dev)
         for li, lw in enumerate(dw.layers):
             prog.row(N.ROW_ADD_RMS, F.row_params(R, Hd, a=None if li == 0 else dd, res=x, w=lw["norm"],
-                                                 w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa_x),
+                                                 w_offset=cfg.norm_offset, eps=cfg.eps, qa=self._fmt(qa_x, lw["gate_up"])),
                      tag=f"draft.L{li}.norm")
             self._gemm(prog, lw["gate_up"], qa_x, gu, f"draft.L{li}.gate_up")
-            prog.row(N.ROW_SILU_MUL, F.row_params(R, dc.inter, a=gu, qa=qa_di), tag=f"draft.L{li}.silu_mul")
+            prog.row(N.ROW_SILU_MUL, F.row_params(R, dc.inter, a=gu, qa=self._fmt(qa_di, lw["down"])), tag=f"draft.L{li}.silu_mul")
             self._gemm(prog, lw["down"], qa_di, dd, f"draft.L{li}.down")
         prog.row(N.ROW_ADD_RMS, F.row_params(R, Hd, a=dd if dw.layers else None, res=x, w=dw.final_norm,
-                                             w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa_x),
+                                             w_offset=cfg.norm_offset, eps=cfg.eps, qa=self._fmt(qa_x, dw.head)),
                  tag="draft.final_norm")
         dlogits = torch.zeros(R, (cfg.vocab + 7) // 8 * 8, dtype=torch.bfloat16, device=dev)
         self._gemm(prog, dw.head, qa_x, dlogits, "draft.head")

@@ -25,8 +25,23 @@ def dequant_linear(w: QuantWeight):
     return q, s
 
 
+def _mx_dense(w: QuantWeight) -> torch.Tensor:
+    """The fp32 matrix an MXFP4 linear multiplies with (fold and flush included)."""
+    from ..pack import quant_fp4 as Q
+    codes, shift = L.untile_weight_mxfp4(w.tiles.cpu(), w.N, w.K)
+    return Q.dequant_folded(codes, shift, w.scale.cpu()[: w.N])
+
+
+def _mx_linear(x: torch.Tensor, wq: torch.Tensor) -> torch.Tensor:
+    from ..pack import quant_fp4 as Q
+    aq, asc = Q.quantize_act_rows_e4m3(x)
+    return ((aq.float().double() @ wq.double().t()).float() * asc[:, None]).to(torch.bfloat16)
+
+
 def qlinear(x_bf16_rounded: torch.Tensor, w: QuantWeight) -> torch.Tensor:
     """Quantise rows per token, exact integer GEMM, scale, round to bf16 (as fp32 values)."""
+    if getattr(w, "mx", False):
+        return _mx_linear(x_bf16_rounded, _mx_dense(w)).float()
     q, s = dequant_linear(w)
     aq, asc = L.quantize_act_rows(x_bf16_rounded)
     return R.gemm_i8(q, s, aq, asc).float()
@@ -38,6 +53,13 @@ def qlinear_row_parallel(x_bf16_rounded: torch.Tensor, w: QuantWeight, tp: int) 
     rounds its partial to bf16; the partials are added in fp32 in rank order and rounded once."""
     if tp == 1:
         return qlinear(x_bf16_rounded, w)
+    if getattr(w, "mx", False):
+        wq = _mx_dense(w)
+        ks = wq.shape[1] // tp
+        acc = torch.zeros(x_bf16_rounded.shape[0], wq.shape[0])
+        for r in range(tp):
+            acc += _mx_linear(x_bf16_rounded[:, r * ks:(r + 1) * ks], wq[:, r * ks:(r + 1) * ks]).float()
+        return R.bf16_round(acc)
     q, s = dequant_linear(w)
     K = q.shape[1]
     ks = K // tp

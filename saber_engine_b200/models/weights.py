@@ -79,7 +79,14 @@ def linear_bits(cfg: HybridConfig, name: str) -> int:
     return 8 if name in cfg.w8_linears else 4
 
 
+_FORMAT = {"fmt": "iu8"}     # 4-bit format of the model being generated (set by random_init)
+
+
 def _quant_on(dev, w: torch.Tensor, bits: int) -> QuantWeight:
+    if bits == 4 and _FORMAT["fmt"] == "mxfp4":
+        from ..pack import quant_fp4 as Q
+        codes, e = Q.quantize_mxfp4(w)
+        return QuantWeight.from_mxfp4(codes, e, dev)
     q, s = L.quantize_weight_rows(w, bits)
     return QuantWeight.from_int(q, s, bits, dev)
 
@@ -88,6 +95,14 @@ def _quant_cols(dev, w_full: torch.Tensor, bits: int, c0: int, c1: int) -> Quant
     """Row-parallel shard: quantise the FULL rows (one scale per output feature over the whole
     reduction dim), then keep columns [c0, c1).  Every TP degree therefore holds the same integers
     and the same scales as TP=1, split along K."""
+    if bits == 4 and _FORMAT["fmt"] == "mxfp4":
+        from ..pack import quant_fp4 as Q
+        codes, e = Q.quantize_mxfp4(w_full)
+        shift, row_scale = Q.fold_mxfp4(codes, e)          # row reference over the FULL row
+        tiles = L.tile_weight_mxfp4(codes[:, c0:c1].contiguous(), shift[:, c0 // 32:c1 // 32].contiguous())
+        sc = torch.zeros(tiles.shape[0] * L.TILE_N, dtype=torch.float32, device=w_full.device)
+        sc[:w_full.shape[0]] = row_scale
+        return QuantWeight(tiles.to(dev).contiguous(), sc.to(dev), w_full.shape[0], c1 - c0, True, mx=True)
     q, s = L.quantize_weight_rows(w_full, bits)
     return QuantWeight.from_int(q[:, c0:c1].contiguous(), s, bits, dev)
 
@@ -101,6 +116,7 @@ def random_init(cfg: HybridConfig, tp: int, rank: int, device, seed: int = 0,
     """
     sh = shard(cfg, tp, rank)
     dev = torch.device(device)
+    _FORMAT["fmt"] = cfg.weight_format
     g = torch.Generator(device=dev).manual_seed(seed)
     H, d, D = cfg.hidden, cfg.gdn_head_dim, cfg.head_dim
 

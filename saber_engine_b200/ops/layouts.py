@@ -159,3 +159,15 @@ def tile_weight_mxfp4(codes: torch.Tensor, shift: torch.Tensor) -> torch.Tensor:
     sh[:N] = shift
     sh = sh.reshape(nt, TILE_N, kb, 4).permute(0, 2, 1, 3).reshape(nt, kb, 1024)
     return torch.cat([packed, sh], dim=-1).contiguous()
+
+
+def untile_weight_mxfp4(tiles: torch.Tensor, N: int, K: int):
+    """Inverse of tile_weight_mxfp4 (tests, CPU oracle): -> (codes uint8 [N, K], shift uint8 [N, K/32])."""
+    nt, kb, _ = tiles.shape
+    packed = tiles[..., :16384].reshape(nt, kb, 1024, 4, 4).to(torch.int32)      # chunk, word, byte
+    lo = torch.stack([packed[..., 0] & 15, packed[..., 0] >> 4, packed[..., 1] & 15, packed[..., 1] >> 4], dim=-1)
+    hi = torch.stack([packed[..., 2] & 15, packed[..., 2] >> 4, packed[..., 3] & 15, packed[..., 3] >> 4], dim=-1)
+    img = torch.cat([lo.reshape(nt, kb, 16384), hi.reshape(nt, kb, 16384)], dim=-1).to(torch.uint8)
+    codes = untile_weight_int8(img, N, K).view(torch.uint8)
+    sh = tiles[..., 16384:].reshape(nt, kb, TILE_N, 4).permute(0, 2, 1, 3).reshape(nt * TILE_N, kb * 4)
+    return codes, sh[:N].contiguous()

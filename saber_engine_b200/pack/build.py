@@ -36,7 +36,11 @@ def _np(t: torch.Tensor) -> np.ndarray:
 def _qw_records(name: str, w: Optional[QuantWeight], shard: int):
     if w is None:
         return
-    if w.w4:
+    if getattr(w, "mx", False):
+        # MXFP4: e2m1 codes + block shifts in the GEMM's tile order, and the per-row 2^wref scale
+        yield (f"{name}.weight_mxfp4", _np(w.tiles), "u8", (w.N, w.K), PF.LAYOUT_MXFP4_TILE, shard)
+        yield (f"{name}.weight_mxfp4_scale", _np(w.scale), "f32", (w.N,), PF.LAYOUT_ROW_SCALE_F32, shard)
+    elif w.w4:
         yield (f"{name}.weight_i4", _np(w.tiles), "u8", (w.N, w.K), PF.LAYOUT_W4_TILE256, shard)
         yield (f"{name}.weight_i4_scale", _np(w.scale), "f32", (w.N,), PF.LAYOUT_ROW_SCALE_F32, shard)
     else:
@@ -78,6 +82,10 @@ def weight_records(mw: ModelWeights):
 
 
 def plan_descriptor(cfg, tp: int) -> dict:
+    if getattr(cfg, "weight_format", "iu8") == "mxfp4":
+        return {"format": "mxfp4_fold_b200/1", "model": cfg.name, "tp": tp, "config": MC.as_dict(cfg),
+                "transforms": ["mxfp4_e2m1_e8m0_per32", "fold_shift_vs_row_max", "rowwise_int8_sym(w8 set, lm_head)",
+                               "tile256x128_sw128"]}
     return {"format": FORMAT_TAG, "model": cfg.name, "tp": tp, "config": MC.as_dict(cfg),
             "transforms": ["rowwise_int4_sym", "rowwise_int8_sym(w8 set, lm_head)", "tile256x128_sw128"]}
 
@@ -115,6 +123,13 @@ def _tensor(reader: PF.PackReader, name: str, device, dtype: torch.dtype, shape=
 
 
 def _load_qw(reader, name: str, device, verify=True) -> Optional[QuantWeight]:
+    key = f"{name}.weight_mxfp4"
+    if reader.has(key):          # the record that exists decides the kernel, not a flag
+        Nn, K = reader.records[key].shape
+        n_tiles, kb = (Nn + 255) // 256, K // 128
+        tiles = _tensor(reader, key, device, torch.uint8, (n_tiles, kb, 17408), verify)
+        scale = _tensor(reader, key + "_scale", device, torch.float32, (n_tiles * 256,), verify)
+        return QuantWeight(tiles, scale, Nn, K, True, mx=True)
     for bits, tag in ((4, "i4"), (8, "i8")):
         key = f"{name}.weight_{tag}"
         if reader.has(key):

@@ -189,3 +189,40 @@ def test_expert_parallel_combine_push(nranks, M):
         else:
             assert torch.equal(normed, first)
     group[0].close()
+
+
+def test_mxfp4_hybrid_prefill_matches_oracle_and_spec_equals_greedy():
+    """The dense hybrid with MXFP4 linears (fp8 activations) end to end."""
+    import dataclasses
+    from saber_engine_b200.models.hybrid import HybridModel, SeqStep, run_bucket
+    from saber_engine_b200.models.reference_hybrid import forward_full
+    cfg = dataclasses.replace(C.scaled_hybrid(name="hybrid-mini-mx"), weight_format="mxfp4")
+    model = HybridModel(cfg, device="cuda", max_seqs=2, max_ctx=512, max_width=5, seed=2)
+    assert model.w.layers[0].mixer_in.mx and not model.w.lm_head.mx
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
+    blocks = list(range(1, 33))
+    model.reset_slot(1)
+    pb = model.build_bucket("prefill", 1, 48)
+    res = run_bucket(model, pb, [SeqStep(prompt, 0, 1, 0, blocks)])
+    got = pb.logits[0, : cfg.vocab].float().cpu()
+    ref = forward_full(cfg, model.w, torch.tensor(prompt))["logits"][-1]
+    assert (got - ref).abs().max() < 0.06 * ref.abs().max() + 1e-3
+
+    def decode(slot, blk, first, drafts, width, steps=14):
+        out, pos, shift, k = [first], len(prompt), 0, 0
+        b = model.build_bucket("decode", 1, width)
+        while len(out) < steps:
+            rows = [out[-1]] + list(drafts[: width - 1])
+            r = run_bucket(model, b, [SeqStep(rows, pos, slot, shift, blk, uid=3, step_no=k)])
+            out += r.tokens[0]
+            pos += r.n_commit[0]
+            shift, drafts, k = r.n_commit[0], r.drafts[0], k + 1
+        return out[:steps]
+
+    plain = decode(1, blocks, res.tokens[0][0], [], 1)
+    model.reset_slot(2)
+    b2 = list(range(40, 72))
+    res2 = run_bucket(model, pb, [SeqStep(prompt, 0, 2, 0, b2)])
+    assert decode(2, b2, res2.tokens[0][0], res2.drafts[0], 5) == plain
+    model.scratch.check()

@@ -103,3 +103,32 @@ def test_tp2_pack_shards_and_wrong_config_is_refused(tmp_path):
     other = C.scaled_hybrid(n_layers=4, hidden=256, ffn=512, vocab=1024)
     with pytest.raises(PF.PackError, match="plan_hash"):
         PB.load_weights(tmp_path, other, 2, 0, "cpu", verify=False)
+
+
+def test_mxfp4_and_moe_packs_roundtrip(tmp_path):
+    import dataclasses
+    from saber_engine_b200.models.weights import random_init
+    cfg = dataclasses.replace(C.scaled_hybrid(n_layers=2, hidden=256, ffn=512, vocab=512, drafter=False), weight_format="mxfp4")
+    d = PB.write_pack(cfg, tmp_path / "mx", tp=1, seed=4)
+    assert PF.check_manifest(d) == []
+    mw = PB.load_weights(tmp_path / "mx", cfg, 1, 0, "cpu")
+    ref = random_init(cfg, 1, 0, "cpu", 4)
+    assert mw.layers[1].gate_up.mx and torch.equal(mw.layers[1].gate_up.tiles, ref.layers[1].gate_up.tiles)
+    assert not mw.layers[0].down.mx and not mw.layers[0].down.w4          # the designated W8 linear stays int8
+    man = json.loads((d / "manifest.json").read_text())
+    assert man["plan"]["descriptor"]["format"].startswith("mxfp4")
+    # an iu8 config refuses the MXFP4 pack (plan hash binds the format)
+    with pytest.raises(PF.PackError):
+        PB.load_weights(tmp_path / "mx", dataclasses.replace(cfg, weight_format="iu8"), 1, 0, "cpu")
+    moe = C.scaled_hybrid(n_layers=2, hidden=256, ffn=512, vocab=512, drafter=False, name="mini-moe",
+                          moe=C.MoEConfig(n_experts=8, top_k=2, expert_inter=128, shared_inter=128))
+    d2 = PB.write_pack(moe, tmp_path / "moe", tp=2, seed=5)
+    assert PF.check_manifest(d2) == []
+    for rank in range(2):
+        got = PB.load_weights(tmp_path / "moe", moe, 2, rank, "cpu")
+        want = random_init(moe, 2, rank, "cpu", 5)
+        m0, w0 = got.layers[0].moe, want.layers[0].moe
+        assert m0["e_lo"] == 4 * rank and m0["e_n"] == 4
+        assert torch.equal(m0["gate_up"].tiles, w0["gate_up"].tiles) and torch.equal(m0["down"].scale, w0["down"].scale)
+        assert torch.equal(m0["router"].tiles, w0["router"].tiles)
+        assert (m0["shared_gate_up"] is None) == (w0["shared_gate_up"] is None)
