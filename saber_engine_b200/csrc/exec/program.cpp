@@ -40,6 +40,7 @@ struct OpExpand { const void* ctx; const void* tok; const void* pos; void* out; 
 struct OpAdvance { uint32_t* seq_base; uint32_t by; };
 struct OpGdnConv { saber::GdnConvParams p; int nseq; };
 struct OpGdnRec { saber::GdnRecParams p; int nseq, vs; };
+struct OpGdnChunk { saber::GdnRecParams p; int nseq, max_rows; float* scratch; };
 struct OpRope { saber::RopeKvParams p; };
 struct OpAttn { saber::AttnParams p; };
 struct OpArgmax { const void* logits; int rows, ld, V, id_offset; int32_t* idx; float* val; };
@@ -57,7 +58,7 @@ struct OpMoeGather { const int8_t* q; const float* scale; int M_pad; const int32
                      int8_t* q_out; float* scale_out; int rows_cap, M_pad_out, K; };
 
 using Op = std::variant<OpGemm, OpRow, OpEmbed, OpGdnConv, OpGdnRec, OpRope, OpAttn, OpArgmax,
-                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather, OpDigest, OpDigestClear>;
+                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather, OpDigest, OpDigestClear, OpGdnChunk>;
 
 struct Entry {
   Op op;
@@ -86,6 +87,7 @@ int launch(const Op& op, cudaStream_t s) {
         else if constexpr (std::is_same_v<T, OpAdvance>) return saber_comm_advance_launch(o.seq_base, o.by, s);
         else if constexpr (std::is_same_v<T, OpGdnConv>) return saber_gdn_conv_launch(&o.p, o.nseq, s);
         else if constexpr (std::is_same_v<T, OpGdnRec>) return saber_gdn_recurrent_launch(&o.p, o.nseq, o.vs, s);
+        else if constexpr (std::is_same_v<T, OpGdnChunk>) return saber_gdn_chunk_launch(&o.p, o.nseq, o.max_rows, o.scratch, s);
         else if constexpr (std::is_same_v<T, OpRope>) return saber_rope_kv_launch(&o.p, s);
         else if constexpr (std::is_same_v<T, OpAttn>) return saber_attn_launch(&o.p, s);
         else if constexpr (std::is_same_v<T, OpArgmax>)
@@ -153,6 +155,10 @@ int saber_program_add_gdn_conv(void* h, const saber::GdnConvParams* p, int nseq,
 }
 int saber_program_add_gdn_rec(void* h, const saber::GdnRecParams* p, int nseq, int vs, const char* tag) {
   return add(h, OpGdnRec{*p, nseq, vs}, 1, tag);
+}
+int saber_program_add_gdn_chunk(void* h, const saber::GdnRecParams* p, int nseq, int max_rows, float* scratch,
+                                const char* tag) {
+  return add(h, OpGdnChunk{*p, nseq, max_rows, scratch}, 2, tag);
 }
 int saber_program_add_rope(void* h, const saber::RopeKvParams* p, const char* tag) {
   return add(h, OpRope{*p}, 1, tag);

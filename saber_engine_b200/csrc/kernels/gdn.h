@@ -36,5 +36,8 @@ struct GdnRecParams {
 }  // namespace saber
 
 extern "C" int saber_gdn_conv_launch(const saber::GdnConvParams* p, int nseq, cudaStream_t stream);
+extern "C" size_t saber_gdn_chunk_scratch_bytes(int max_rows, int nseq, int HV);
+extern "C" int saber_gdn_chunk_launch(const saber::GdnRecParams* p, int nseq, int max_rows, float* scratch,
+                                      cudaStream_t stream);
 extern "C" int saber_gdn_recurrent_launch(const saber::GdnRecParams* p, int nseq, int vs,
                                           cudaStream_t stream);

@@ -103,10 +103,11 @@ class HybridModel:
                  max_seqs: int = 8, max_ctx: Optional[int] = None, kv_blocks: Optional[int] = None,
                  max_width: int = 9, weights: Optional[ModelWeights] = None, seed: int = 0,
                  comm=None, oracle_p: float = 0.0, oracle_seed: int = 0, gdn_vs: int = 2,
-                 use_drafter: bool = True, race_check: str = "off"):
+                 use_drafter: bool = True, race_check: str = "off", gdn_prefill: str = "rows"):
         self.cfg, self.tp, self.rank = cfg, tp, rank
         if race_check not in ("off", "shadow"):
             raise ValueError("race_check must be 'off' or 'shadow'")
+        self.gdn_prefill = gdn_prefill      # "rows" (row-by-row recurrence) | "chunked" (64-row chunks, fp32)
         self.race_check = race_check        # "shadow": a digest of the residual stream after every layer rides with the result
         self.sh = shard(cfg, tp, rank)
         self.device = torch.device(device)
@@ -271,6 +272,7 @@ class HybridModel:
             prog.digest_clear(digests, cfg.n_layers + 1, tag="digest.clear")
         prog.embed(self.w.embed, at(lay.ids), h, M, H, 0, cfg.vocab, H, tag="embed")
         first = True
+        chunk_scratch = None
         ar_site = 0
         pending = -1          # site of the TP GEMM whose pushed output the next add-norm consumes
         for i, lw in enumerate(self.w.layers):
@@ -292,7 +294,14 @@ class HybridModel:
                                       self.gdn_stash[i], blob, blob, blob, gdn_o, n_q, n_k,
                                       sh.gdn_v_heads, sh.gdn_k_heads, commit=not decode, ldba=ld_in)
                 rp.cu_rows, rp.slots, rp.shift = at(lay.cu_rows), at(lay.slots), at(lay.shift)
-                prog.gdn_rec(rp, nseq, self.gdn_vs, tag=f"{t}.gdn.rec")
+                if not decode and width >= 64 and self.gdn_prefill == "chunked":
+                    # prefill: the chunked (64-row) form; one scratch shared by every layer of the bucket
+                    if chunk_scratch is None:
+                        chunk_scratch = F.gdn_chunk_scratch(M, nseq, sh.gdn_v_heads, dev)
+                        keep.append(chunk_scratch)
+                    prog.gdn_chunk(rp, nseq, M, chunk_scratch, tag=f"{t}.gdn.rec")
+                else:
+                    prog.gdn_rec(rp, nseq, self.gdn_vs, tag=f"{t}.gdn.rec")
                 row(N.ROW_GDN_NORM, M, sh.gdn_out_k, f"{t}.gdn.norm_quant", a_f32=gdn_o,
                     b=buf_in[:, C_:], w=lw.gdn_norm, eps=cfg.eps, qa=self._fmt(qa_gdn, lw.mixer_out), ldb=ld_in)
                 self._gemm(prog, lw.mixer_out, qa_gdn, delta, f"{t}.gdn.out_proj", tp_site=ar_site)

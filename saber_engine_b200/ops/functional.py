@@ -316,6 +316,22 @@ def gdn_recurrent(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, 
     return out
 
 
+def gdn_chunk_scratch(total_rows: int, nseq: int, HV: int, device) -> torch.Tensor:
+    n = N.lib().saber_gdn_chunk_scratch_bytes(total_rows, nseq, HV)
+    return torch.empty(n // 4, dtype=torch.float32, device=device)
+
+
+def gdn_chunked(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, n_q, n_k, HV, HK, max_rows: int):
+    """Committing (prefill) recurrence by 64-row chunks; same contract as gdn_recurrent(commit=True)."""
+    M = qkv.shape[0]
+    out = torch.empty(M, HV * 128, dtype=torch.float32, device=qkv.device)
+    p = gdn_rec_params(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, out, n_q, n_k, HV, HK, True)
+    scratch_t = gdn_chunk_scratch(M, slots.numel(), HV, qkv.device)
+    N.check(N.lib().saber_gdn_chunk_launch(C.byref(p), slots.numel(), max_rows, scratch_t.data_ptr(), N.stream_handle()),
+            "gdn_chunk")
+    return out
+
+
 # ----------------------------------------------------------------------------------- attention
 def rope_kv_params(qkv, q_out, q_norm_w, k_norm_w, pos, slot_map, kv_cache, nq, nkv, q_off, k_off,
                    v_off, rot_dim=64, sections=(11, 11, 10), theta=1e7, eps=1e-6, w_offset=1.0,

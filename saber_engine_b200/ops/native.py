@@ -155,6 +155,9 @@ def _declare(L: C.CDLL) -> None:
         "saber_block_expand_launch": (I, [P, P, P, P, I, I, I, S]),
         "saber_gdn_conv_launch": (I, [C.POINTER(GdnConvParams), I, S]),
         "saber_gdn_recurrent_launch": (I, [C.POINTER(GdnRecParams), I, I, S]),
+        "saber_gdn_chunk_scratch_bytes": (C.c_size_t, [I, I, I]),
+        "saber_gdn_chunk_launch": (I, [C.POINTER(GdnRecParams), I, I, P, S]),
+        "saber_program_add_gdn_chunk": (I, [P, C.POINTER(GdnRecParams), I, I, P, C.c_char_p]),
         "saber_rope_kv_launch": (I, [C.POINTER(RopeKvParams), S]),
         "saber_attn_launch": (I, [C.POINTER(AttnParams), S]),
         "saber_argmax_launch": (I, [P, I, I, I, I, P, P, S]),
@@ -311,6 +314,9 @@ class Program:
 
     def allreduce(self, p: AllReduceParams, tag="allreduce") -> int:
         return self._L.saber_program_add_allreduce(self._h, C.byref(p), tag.encode())
+
+    def gdn_chunk(self, p: "GdnRecParams", nseq: int, max_rows: int, scratch, tag: str = "gdn_chunk") -> int:
+        return self._L.saber_program_add_gdn_chunk(self._h, C.byref(p), nseq, max_rows, ptr(scratch), tag.encode())
 
     def digest(self, buf, nbytes: int, out_word, tag: str = "digest") -> int:
         """XOR-splitmix digest of `nbytes` of `buf` into the 8-byte word at `out_word` (cleared by digest_clear)."""

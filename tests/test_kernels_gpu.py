@@ -301,3 +301,31 @@ def test_program_capture_replay_counts_nodes():
     aq, asc = L.quantize_act_rows(n_ref)
     ref = R.gemm_i8(wq, ws, aq, asc).float()
     assert (out.float().cpu() - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3
+
+
+def test_gdn_chunked_prefill_equals_row_by_row_kernel():
+    """The 64-row chunked form against the row-by-row kernel (commit mode): same outputs and the
+    same final state up to summation order, on two ragged sequences (one not a chunk multiple)."""
+    HV, HK = 6, 2
+    s = _gdn_setup(2, 4, HV=HV, HK=HK, seed=9)
+    n_q, n_k, Cc = s["n_q"], s["n_k"], s["C"]
+    lens = [150, 64]
+    M = sum(lens)
+    torch.manual_seed(10)
+    qk = torch.nn.functional.normalize(torch.randn(M, 2 * HK, 128), dim=-1).reshape(M, n_q + n_k)
+    qk[:, :n_q] /= 128 ** 0.5
+    qkv = torch.cat([qk, torch.randn(M, HV * 128)], 1).to(DEV)
+    ba = torch.randn(M, 2 * HV).to(torch.bfloat16).to(DEV)
+    cu = torch.tensor([0, lens[0], M], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([1, 2], dtype=torch.int32, device=DEV)
+    sh = torch.zeros(2, dtype=torch.int32, device=DEV)
+    A_log, dtb = s["A_log"].to(DEV), s["dt_bias"].to(DEV)
+    st_a, st_b = s["state"].to(DEV).clone(), s["state"].to(DEV).clone()
+    stash = torch.zeros(3, 4, HV, 2, F.gdn_stash_stride(2), device=DEV)
+    want = F.gdn_recurrent(qkv, ba, A_log, dtb, st_a, stash, cu, slots, sh, n_q, n_k, HV, HK, commit=True, vs=2)
+    got = F.gdn_chunked(qkv, ba, A_log, dtb, st_b, stash, cu, slots, sh, n_q, n_k, HV, HK, max_rows=max(lens))
+    torch.cuda.synchronize()
+    scale = want.abs().max().item()
+    assert (got - want).abs().max().item() <= 2e-4 * scale + 1e-5, ((got - want).abs().max().item(), scale)
+    assert (st_a[1:] - st_b[1:]).abs().max().item() <= 2e-4 * st_a.abs().max().item() + 1e-5
+    assert torch.equal(st_a[0], st_b[0])            # the padding slot is untouched
