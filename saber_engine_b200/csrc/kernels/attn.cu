@@ -128,15 +128,19 @@ constexpr int kAttnMaxWarps = 6;
 constexpr int kAttnRing = 8;          // raw fp8 pages in flight per CTA (8 KiB each)
 constexpr int kAttnOpBytes = 32768;   // one operand buffer: K [32 keys][256] fp16 | V [32 keys][256] fp16
 
-// One CTA = one (sequence, KV head, 16-token query tile, KV split); one warp per query head of the
-// GQA group.  The raw fp8 pages of the split stream through a ring in shared memory, filled by
+// One CTA = one (sequence, KV head, 16-token query tile, KV split); one warp per 16-row tile.  A
+// tile holds `hpt` query heads of the GQA group, `pack` rows each (tile row = head * pack + row): the
+// heads of a group share K and V, so with few rows per sequence (decode) several heads ride in one
+// MMA tile -- 2 heads at 8 rows, 3 at 5, all 6 at one row -- instead of padding each to 16 rows.  The raw fp8 pages of the split stream through a ring in shared memory, filled by
 // bulk copies that complete on mbarriers (eight pages in flight per CTA: the kernel is bound by
 // how much it keeps in flight, not by arithmetic).  Each iteration takes two pages: all threads
 // widen them to fp16 into one of two operand buffers, one barrier, then every warp runs
 // S = Q K^T (16 x 32), the online softmax and O += P V on its own head.
 __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const AttnParams p,
                                                                         const int hpb,
-                                                                        const int hgroups) {
+                                                                        const int hgroups,
+                                                                        const int hpt,
+                                                                        const int pack) {
   pdl_wait();
   extern __shared__ __align__(128) uint8_t attn_smem[];
   __shared__ uint64_t full_bar[kAttnRing];
@@ -152,9 +156,12 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
   const int group = p.nq / p.nkv;
   const int kvh = blockIdx.y / hgroups, hg = blockIdx.y % hgroups;
   const int b = blockIdx.z / p.splits, sp = blockIdx.z % p.splits;
-  const int hin = hg * hpb + warp;
+  const int hin = (hg * hpb + warp) * hpt;     // first head (inside the group) of this warp's tile
   const bool active = hin < group;
-  const int head = kvh * group + hin;
+  const int head0 = kvh * group + hin;
+  // tile row -> (head, sequence row); rows beyond the packed heads / live rows are dead
+  auto row_head = [&](int rr) { return rr / pack; };
+  auto row_tok = [&](int rr) { return rr - (rr / pack) * pack; };
   const int row0 = p.cu_q[b];
   const int n = p.cu_q[b + 1] - row0;
   const int t0 = blockIdx.x * 16;
@@ -195,9 +202,10 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
     for (int i = lane; i < 16 * 32; i += 32) {
       const int r = i >> 5, c = i & 31;
       uint4 v = make_uint4(0, 0, 0, 0);
-      if (r < ntok) {
+      const int qh = row_head(r), qr = row_tok(r);
+      if (qh < hpt && hin + qh < group && qr < ntok) {
         const uint4 raw = *reinterpret_cast<const uint4*>(
-            p.q + (static_cast<size_t>(row0 + t0 + r) * p.nq + head) * kHeadDim + c * 8);
+            p.q + (static_cast<size_t>(row0 + t0 + qr) * p.nq + head0 + qh) * kHeadDim + c * 8);
         const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
         uint32_t o[4];
 #pragma unroll
@@ -297,7 +305,8 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
       for (int e = 0; e < 4; ++e) {
         const int rr = g + (e >> 1) * 8;
         const int key = key0 + nt * 8 + 2 * t + (e & 1);
-        const bool live = rr < ntok && key < kbase + rr && key < key_end;
+        const int mh = row_head(rr), mr = row_tok(rr);
+        const bool live = mh < hpt && hin + mh < group && mr < ntok && key < kbase + mr && key < key_end;
         const float sv = live ? S[nt][e] * scale_log2 : -INFINITY;
         S[nt][e] = sv;
         rmax[e >> 1] = fmaxf(rmax[e >> 1], sv);
@@ -368,19 +377,22 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
       const int rr = g + h2 * 8;
-      if (rr >= ntok) continue;
+      const int oh = row_head(rr), orow = row_tok(rr);
+      if (oh >= hpt || hin + oh >= group || orow >= ntok) continue;
       const float inv = l_run[h2] > 0.f ? p.v_scale / l_run[h2] : 0.f;
-      __nv_bfloat16* dst = p.out + (static_cast<size_t>(row0 + t0 + rr) * p.nq + head) * kHeadDim;
+      __nv_bfloat16* dst = p.out + (static_cast<size_t>(row0 + t0 + orow) * p.nq + head0 + oh) * kHeadDim;
 #pragma unroll
       for (int i = 0; i < 32; ++i)
         *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + 2 * t) =
             __floats2bfloat162_rn(O[i][2 * h2] * inv, O[i][2 * h2 + 1] * inv);
     }
   } else {
-    const size_t pbase = ((static_cast<size_t>(b) * p.nq + head) * p.splits + sp) * 16;
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
-      const int rr = g + h2 * 8;
+      const int rr0 = g + h2 * 8;
+      const int oh = row_head(rr0), rr = row_tok(rr0);
+      if (oh >= hpt || hin + oh >= group) continue;
+      const size_t pbase = ((static_cast<size_t>(b) * p.nq + head0 + oh) * p.splits + sp) * 16;
       float* dst = p.part_o + (pbase + rr) * kHeadDim;
 #pragma unroll
       for (int i = 0; i < 32; ++i)
@@ -431,8 +443,15 @@ extern "C" int saber_attn_launch(const saber::AttnParams* p, cudaStream_t stream
   if (p->nq % p->nkv || p->splits < 1) return static_cast<int>(cudaErrorInvalidValue);
   if (p->splits > 1 && p->q_tiles != 1) return static_cast<int>(cudaErrorInvalidValue);
   const int group = p->nq / p->nkv;
-  const int hgroups = (group + kAttnMaxWarps - 1) / kAttnMaxWarps;
-  const int hpb = (group + hgroups - 1) / hgroups;
+  // decode (one query tile): pack several heads of the group into one 16-row tile
+  int hpt = 1, pack = 16;
+  if (p->q_tiles == 1 && p->pack_rows >= 1 && p->pack_rows <= 8) {
+    pack = p->pack_rows;
+    hpt = 16 / pack < group ? 16 / pack : group;
+  }
+  const int tiles = (group + hpt - 1) / hpt;              // 16-row tiles (= warps) per KV head
+  const int hgroups = (tiles + kAttnMaxWarps - 1) / kAttnMaxWarps;
+  const int hpb = (tiles + hgroups - 1) / hgroups;
   const int smem = hpb * 8192 + 2 * kAttnOpBytes + kAttnRing * 8192;
   static bool configured = false;
   if (!configured) {
@@ -441,7 +460,7 @@ extern "C" int saber_attn_launch(const saber::AttnParams* p, cudaStream_t stream
     configured = true;
   }
   dim3 grid(p->q_tiles, p->nkv * hgroups, p->nseq * p->splits);
-  saber::launch(attn_paged_kernel, dim3(grid), dim3(32 * hpb), smem, stream, 0, *p, hpb, hgroups);
+  saber::launch(attn_paged_kernel, dim3(grid), dim3(32 * hpb), smem, stream, 0, *p, hpb, hgroups, hpt, pack);
   if (p->splits > 1)
     saber::launch(attn_combine_kernel, dim3(dim3(p->nseq * p->nq, 16)), dim3(256), 0, stream, 0, *p);
   return static_cast<int>(cudaGetLastError());

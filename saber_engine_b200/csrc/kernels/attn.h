@@ -36,6 +36,7 @@ struct AttnParams {
   int nseq, nq, nkv, max_blocks, splits, q_tiles;
   float sm_scale, k_scale, v_scale;
   uint32_t* err;               // status word of the bounded waits (may be null)
+  int pack_rows;               // decode: upper bound of the rows of one sequence (1..8 packs heads into a tile; 0 = off)
   int n_blocks;                // blocks in kv_cache (0 = unknown): a table entry outside [0, n_blocks) is
                                // recorded in the status word and its page is treated as empty
 };

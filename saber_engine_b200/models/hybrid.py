@@ -322,6 +322,7 @@ class HybridModel:
                 ap.block_table, ap.cu_q, ap.kv_len = at(lay.block_table), at(lay.cu_rows), at(lay.kv_len)
                 ap.max_blocks, ap.nseq = self.max_blocks, nseq
                 ap.err = self.scratch.err.data_ptr()
+                ap.pack_rows = width if (decode and q_tiles == 1) else 0
                 prog.attn(ap, tag=f"{t}.attn.core")
                 ao = attn_out.view(M, nq * D)
                 if cfg.attn_out_gate:

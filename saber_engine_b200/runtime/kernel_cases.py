@@ -71,7 +71,7 @@ def _attn(nseq, n, ctx, splits, copies=3):
     out = torch.empty_like(q)
     po = torch.empty(nseq, nq, splits, 16, D, device=DEV) if splits > 1 else None
     pm = torch.empty(nseq, nq, splits, 16, 2, device=DEV) if splits > 1 else None
-    ps = [F.attn_params(q, kv, bt, cu, kvl, out, po, pm, nkv, splits, 1) for kv in kvs]
+    ps = [F.attn_params(q, kv, bt, cu, kvl, out, po, pm, nkv, splits, 1, pack_rows=n) for kv in kvs]
     torch.cuda.synchronize()
     lib = N.lib()
     fns = [lambda p=p: N.check(lib.saber_attn_launch(C.byref(p), N.stream_handle()), "attn") for p in ps]
@@ -141,6 +141,8 @@ CASES = {
     "gemm_w4_gate_up_m2048": lambda: _gemm(34816, 5120, 2048, 1, 1, copies=2),
     "attn_decode_b8_ctx4096": lambda: _attn(8, 9, 4096, 4),
     "attn_decode_b1_ctx32768": lambda: _attn(1, 9, 32768, 32, copies=2),
+    "attn_decode_b8_w8_ctx4096": lambda: _attn(8, 8, 4096, 4),
+    "attn_decode_b8_w1_ctx4096": lambda: _attn(8, 1, 4096, 4),
     "gdn_rec_b8": lambda: _gdn(8, 9, 5),
     "row_add_rms_m72": lambda: _row(72, 5120),
     "moe_block_m72": lambda: _moe(72),

@@ -329,3 +329,12 @@ def test_gdn_chunked_prefill_equals_row_by_row_kernel():
     assert (got - want).abs().max().item() <= 2e-4 * scale + 1e-5, ((got - want).abs().max().item(), scale)
     assert (st_a[1:] - st_b[1:]).abs().max().item() <= 2e-4 * st_a.abs().max().item() + 1e-5
     assert torch.equal(st_a[0], st_b[0])            # the padding slot is untouched
+
+
+def test_attention_packs_several_heads_into_one_tile():
+    """Few rows per sequence: 2 heads per 16-row tile at 8 rows, 3 at 5, all 6 at 1 or 2 rows."""
+    _attn_case([200, 31], [8, 8], splits=2, nq=24, nkv=4, seed=5)
+    _attn_case([77, 300, 16], [1, 1, 1], splits=1, nq=12, nkv=2, seed=6)
+    _attn_case([77, 300, 16], [1, 1, 1], splits=3, nq=24, nkv=4, seed=7)
+    _attn_case([40, 90, 130], [5, 3, 1], splits=2, nq=12, nkv=2, seed=8)    # ragged: packing stride = widest sequence
+    _attn_case([64, 64], [2, 2], splits=1, nq=16, nkv=2, seed=9)            # group of 8 heads, 2 rows: 8 heads per tile
