@@ -97,7 +97,7 @@ def main() -> int:
     ap.add_argument("--streams", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=4096)
     ap.add_argument("--shared-prefix", type=int, default=2048)
-    ap.add_argument("--width", type=int, default=9)
+    ap.add_argument("--width", type=int, default=8)
     ap.add_argument("--accept-p", type=float, default=0.75)
     ap.add_argument("--rung", type=int, default=2048)
     ap.add_argument("--pdl", type=int, default=-1, help="programmatic dependent launch: 0 off, 1 all kernels, 2 GEMMs only (A/B)")

@@ -246,7 +246,7 @@ def make_parser() -> argparse.ArgumentParser:
     e.add_argument("--engine-max-seqs", type=int, default=8)
     e.add_argument("--engine-prefill-rows", default="128,512,2048")
     e.add_argument("--engine-decode-batches", default="1,2,3,4,8")
-    e.add_argument("--engine-decode-widths", default="1,5,9")
+    e.add_argument("--engine-decode-widths", default="1,5,8")
     e.add_argument("--engine-draft-block", type=int, default=8)
     e.add_argument("--engine-budget-mib", type=int, default=160000)
     e.add_argument("--engine-kv-blocks", type=int, default=0)

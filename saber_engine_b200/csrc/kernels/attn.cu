@@ -124,42 +124,46 @@ __device__ __forceinline__ void fp8x16_to_f16(const uint4 in, uint4& lo, uint4& 
   hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
-constexpr int kAttnMaxWarps = 6;
-constexpr int kAttnRing = 8;          // raw fp8 pages in flight per CTA (8 KiB each)
-constexpr int kAttnOpBytes = 32768;   // one operand buffer: K [32 keys][256] fp16 | V [32 keys][256] fp16
+constexpr int kAttnMaxWarps = 8;      // two warps (head-dim halves) per 16-row tile, up to four tiles per CTA
+constexpr int kAttnMaxRing = 8;       // raw fp8 pages in flight per CTA (8 KiB each), fewer when shared memory is short
+constexpr int kAttnOpBytes = 32768;   // the operand buffer: K [32 keys][256] fp16 | V [32 keys][256] fp16
+constexpr int kAttnSmemBudget = 112 * 1024;   // two CTAs per SM
 
-// One CTA = one (sequence, KV head, 16-token query tile, KV split); one warp per 16-row tile.  A
-// tile holds `hpt` query heads of the GQA group, `pack` rows each (tile row = head * pack + row): the
-// heads of a group share K and V, so with few rows per sequence (decode) several heads ride in one
-// MMA tile -- 2 heads at 8 rows, 3 at 5, all 6 at one row -- instead of padding each to 16 rows.  The raw fp8 pages of the split stream through a ring in shared memory, filled by
-// bulk copies that complete on mbarriers (eight pages in flight per CTA: the kernel is bound by
-// how much it keeps in flight, not by arithmetic).  Each iteration takes two pages: all threads
-// widen them to fp16 into one of two operand buffers, one barrier, then every warp runs
-// S = Q K^T (16 x 32), the online softmax and O += P V on its own head.
-__global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const AttnParams p,
-                                                                        const int hpb,
-                                                                        const int hgroups,
-                                                                        const int hpt,
-                                                                        const int pack) {
+// One CTA = one (sequence, KV head, 16-token query tile, KV split).  A 16-row tile holds `hpt` query
+// heads of the GQA group, `pack` rows each (tile row = head * pack + row): the heads of a group
+// share K and V, so with few rows per sequence (decode) several heads ride in one MMA tile -- 2
+// heads at 8 rows, 3 at 5, all 6 at one row -- instead of padding each to 16 rows.  Two warps work
+// on a tile: both compute S = Q K^T (16 x 32) and the softmax, each accumulates one half of the
+// head dim of O (64 accumulator registers instead of 128), which lets two CTAs share an SM.
+// The raw fp8 pages of the split stream through a ring in shared memory, filled by bulk copies
+// that complete on mbarriers; each iteration takes two pages, all threads widen them to fp16 into
+// the operand buffer.
+__global__ void __launch_bounds__(32 * kAttnMaxWarps, 2) attn_paged_kernel(const AttnParams p,
+                                                                           const int tpb,
+                                                                           const int hgroups,
+                                                                           const int hpt,
+                                                                           const int pack,
+                                                                           const int ring) {
   pdl_wait();
   extern __shared__ __align__(128) uint8_t attn_smem[];
-  __shared__ uint64_t full_bar[kAttnRing];
-  // layout: Q [hpb][16][256] fp16 | 2 operand buffers | raw ring; 512-byte rows, 16-byte chunk
-  // index XOR (row & 7)
+  __shared__ uint64_t full_bar[kAttnMaxRing];
+  // layout: Q [tpb][16][256] fp16 | operand buffer | raw ring; 512-byte rows, 16-byte chunk index
+  // XOR (row & 7)
   const uint32_t q_s = static_cast<uint32_t>(__cvta_generic_to_shared(attn_smem));
-  const uint32_t op_s = q_s + hpb * 8192;
-  const uint32_t ring_s = op_s + 2 * kAttnOpBytes;
+  const uint32_t k_s = q_s + tpb * 8192;
+  const uint32_t v_s = k_s + 16384;
+  const uint32_t ring_s = k_s + kAttnOpBytes;
   const uint32_t bar_s = static_cast<uint32_t>(__cvta_generic_to_shared(full_bar));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = warp >> 1, dh = warp & 1;       // tile of this warp, half of the head dim it accumulates
   const int g = lane >> 2, t = lane & 3;
   const int group = p.nq / p.nkv;
   const int kvh = blockIdx.y / hgroups, hg = blockIdx.y % hgroups;
   const int b = blockIdx.z / p.splits, sp = blockIdx.z % p.splits;
-  const int hin = (hg * hpb + warp) * hpt;     // first head (inside the group) of this warp's tile
+  const int hin = (hg * tpb + tile) * hpt;         // first head (inside the group) of this warp's tile
   const bool active = hin < group;
   const int head0 = kvh * group + hin;
-  // tile row -> (head, sequence row); rows beyond the packed heads / live rows are dead
   auto row_head = [&](int rr) { return rr / pack; };
   auto row_tok = [&](int rr) { return rr - (rr / pack) * pack; };
   const int row0 = p.cu_q[b];
@@ -177,12 +181,12 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
   const int key_end = pg1 * kPageTokens;   // keys at or beyond belong to the next split
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kAttnRing; ++i) mbar_init(bar_s + 8 * i, 1);
+    for (int i = 0; i < ring; ++i) mbar_init(bar_s + 8 * i, 1);
     mbar_init_fence();
   }
   __syncthreads();
-  auto issue = [&](int i) {   // page i of this split -> ring stage i % kAttnRing (thread 0 only)
-    const int st = i % kAttnRing;
+  auto issue = [&](int i) {   // page i of this split -> ring stage i % ring (thread 0 only)
+    const int st = i % ring;
     int blk = pg0 + i < p.max_blocks ? p.block_table[static_cast<size_t>(b) * p.max_blocks + pg0 + i] : -1;
     if (blk < 0 || (p.n_blocks > 0 && blk >= p.n_blocks)) {   // never follow a bad table entry
       if (p.err) atomicCAS(p.err, 0u, static_cast<uint32_t>(kErrBadIndex));
@@ -194,12 +198,12 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
   };
   int issued = 0;
   if (threadIdx.x == 0) {
-    for (; issued < min(kAttnRing, npages); ++issued) issue(issued);
+    for (; issued < min(ring, npages); ++issued) issue(issued);
   }
 
-  // ---- Q tile (bf16 -> fp16: exact for every value the normed, rotated q can take)
+  // ---- Q tile (bf16 -> fp16: exact for every value the normed, rotated q can take); both warps of a tile load it
   if (active) {
-    for (int i = lane; i < 16 * 32; i += 32) {
+    for (int i = lane + 32 * dh; i < 16 * 32; i += 64) {
       const int r = i >> 5, c = i & 31;
       uint4 v = make_uint4(0, 0, 0, 0);
       const int qh = row_head(r), qr = row_tok(r);
@@ -216,15 +220,15 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
         v = make_uint4(o[0], o[1], o[2], o[3]);
       }
       asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(
-                       q_s + warp * 8192 + r * 512 + ((c ^ (r & 7)) << 4)),
+                       q_s + tile * 8192 + r * 512 + ((c ^ (r & 7)) << 4)),
                    "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                    : "memory");
     }
   }
 
-  float O[32][4];
+  float O[16][4];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
+  for (int i = 0; i < 16; ++i) O[i][0] = O[i][1] = O[i][2] = O[i][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.f, 0.f};
   const float scale_log2 = p.sm_scale * p.k_scale * 1.4426950408889634f;
@@ -233,15 +237,13 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
   bool ok = true;
 
   for (int it = 0; it < niter; ++it) {
-    const uint32_t k_s = op_s + (it & 1) * kAttnOpBytes;
-    const uint32_t v_s = k_s + 16384;
     // ---- widen the two pages of this iteration into the operand buffer
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int i = 2 * it + half;
       if (i < npages) {
-        const int st = i % kAttnRing;
-        if (ok) ok = mbar_wait(bar_s + 8 * st, (i / kAttnRing) & 1, p.err, kErrWaitFull);
+        const int st = i % ring;
+        if (ok) ok = mbar_wait(bar_s + 8 * st, (i / ring) & 1, p.err, kErrWaitFull);
         for (int idx = threadIdx.x; idx < 512; idx += nthreads) {
           const int isv = idx >> 8, key = half * 16 + ((idx & 255) >> 4), c = (idx & 15) * 2;
           uint4 raw, lo, hi;
@@ -265,105 +267,105 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
         }
       }
     }
-    // one barrier per iteration: the operand buffer is complete, the two ring stages are free,
-    // and (the buffers alternate) every warp has left the buffer the next iteration overwrites
+    // the operand buffer is complete and the two ring stages are free
     if (__syncthreads_or(ok ? 0 : 1)) { ok = false; break; }
     if (threadIdx.x == 0) {
       fence_proxy_async_smem();   // order the generic reads of the stages before the async refill
       for (int half = 0; half < 2; ++half)
-        if (issued < npages && issued - kAttnRing <= 2 * it + half) { issue(issued); ++issued; }
+        if (issued < npages && issued - ring <= 2 * it + half) { issue(issued); ++issued; }
     }
-    if (!active) continue;
-
-    // ---- S = Q K^T  (16 x 32 per warp)
-    float S[4][4];
+    if (active) {
+      // ---- S = Q K^T  (16 x 32, computed by both warps of the tile)
+      float S[4][4];
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f;
+      for (int nt = 0; nt < 4; ++nt) S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f;
 #pragma unroll
-    for (int ks = 0; ks < 16; ++ks) {
-      uint32_t a[4], kb0[4], kb1[4];
-      {
-        const int r = (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * ks + (lane >> 4);
-        ldsm_x4(q_s + warp * 8192 + r * 512 + ((c ^ (r & 7)) << 4), a);
+      for (int ks = 0; ks < 16; ++ks) {
+        uint32_t a[4], kb0[4], kb1[4];
+        {
+          const int r = (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * ks + (lane >> 4);
+          ldsm_x4(q_s + tile * 8192 + r * 512 + ((c ^ (r & 7)) << 4), a);
+        }
+        {
+          const int r = (lane & 7) + (lane >> 4) * 8, c = 2 * ks + ((lane >> 3) & 1);
+          ldsm_x4(k_s + r * 512 + ((c ^ (r & 7)) << 4), kb0);
+          ldsm_x4(k_s + (16 + r) * 512 + ((c ^ (r & 7)) << 4), kb1);
+        }
+        mma_f16(S[0], a, kb0[0], kb0[1]);
+        mma_f16(S[1], a, kb0[2], kb0[3]);
+        mma_f16(S[2], a, kb1[0], kb1[1]);
+        mma_f16(S[3], a, kb1[2], kb1[3]);
       }
-      {
-        const int r = (lane & 7) + (lane >> 4) * 8, c = 2 * ks + ((lane >> 3) & 1);
-        ldsm_x4(k_s + r * 512 + ((c ^ (r & 7)) << 4), kb0);
-        ldsm_x4(k_s + (16 + r) * 512 + ((c ^ (r & 7)) << 4), kb1);
+      // ---- scale, mask, online softmax (rows g and g + 8)
+      float rmax[2] = {-INFINITY, -INFINITY};
+      const int key0 = (pg0 + 2 * it) * kPageTokens;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int rr = g + (e >> 1) * 8;
+          const int key = key0 + nt * 8 + 2 * t + (e & 1);
+          const int mh = row_head(rr), mr = row_tok(rr);
+          const bool live = mh < hpt && hin + mh < group && mr < ntok && key < kbase + mr && key < key_end;
+          const float sv = live ? S[nt][e] * scale_log2 : -INFINITY;
+          S[nt][e] = sv;
+          rmax[e >> 1] = fmaxf(rmax[e >> 1], sv);
+        }
       }
-      mma_f16(S[0], a, kb0[0], kb0[1]);
-      mma_f16(S[1], a, kb0[2], kb0[3]);
-      mma_f16(S[2], a, kb1[0], kb1[1]);
-      mma_f16(S[3], a, kb1[2], kb1[3]);
-    }
-    // ---- scale, mask, online softmax (rows g and g + 8)
-    float rmax[2] = {-INFINITY, -INFINITY};
-    const int key0 = (pg0 + 2 * it) * kPageTokens;
+      float alpha[2], msafe[2];
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int rr = g + (e >> 1) * 8;
-        const int key = key0 + nt * 8 + 2 * t + (e & 1);
-        const int mh = row_head(rr), mr = row_tok(rr);
-        const bool live = mh < hpt && hin + mh < group && mr < ntok && key < kbase + mr && key < key_end;
-        const float sv = live ? S[nt][e] * scale_log2 : -INFINITY;
-        S[nt][e] = sv;
-        rmax[e >> 1] = fmaxf(rmax[e >> 1], sv);
+      for (int h2 = 0; h2 < 2; ++h2) {
+        rmax[h2] = fmaxf(rmax[h2], __shfl_xor_sync(0xffffffffu, rmax[h2], 1));
+        rmax[h2] = fmaxf(rmax[h2], __shfl_xor_sync(0xffffffffu, rmax[h2], 2));
+        const float mnew = fmaxf(m_run[h2], rmax[h2]);
+        msafe[h2] = mnew == -INFINITY ? 0.f : mnew;
+        alpha[h2] = exp2f(m_run[h2] - msafe[h2]);
+        m_run[h2] = mnew;
       }
-    }
-    float alpha[2], msafe[2];
+      uint32_t pa[2][4];
 #pragma unroll
-    for (int h2 = 0; h2 < 2; ++h2) {
-      rmax[h2] = fmaxf(rmax[h2], __shfl_xor_sync(0xffffffffu, rmax[h2], 1));
-      rmax[h2] = fmaxf(rmax[h2], __shfl_xor_sync(0xffffffffu, rmax[h2], 2));
-      const float mnew = fmaxf(m_run[h2], rmax[h2]);
-      msafe[h2] = mnew == -INFINITY ? 0.f : mnew;
-      alpha[h2] = exp2f(m_run[h2] - msafe[h2]);
-      m_run[h2] = mnew;
-    }
-    uint32_t pa[2][4];
+      for (int kk = 0; kk < 2; ++kk) {   // 16 keys each
+        float pv[2][4];
 #pragma unroll
-    for (int kk = 0; kk < 2; ++kk) {   // 16 keys each
-      float pv[2][4];
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) pv[nt][e] = exp2f(S[2 * kk + nt][e] - msafe[e >> 1]);
-      if (kk == 0) {
-        l_run[0] *= alpha[0];
-        l_run[1] *= alpha[1];
+          for (int e = 0; e < 4; ++e) pv[nt][e] = exp2f(S[2 * kk + nt][e] - msafe[e >> 1]);
+        if (kk == 0) {
+          l_run[0] *= alpha[0];
+          l_run[1] *= alpha[1];
+        }
+        l_run[0] += pv[0][0] + pv[0][1] + pv[1][0] + pv[1][1];
+        l_run[1] += pv[0][2] + pv[0][3] + pv[1][2] + pv[1][3];
+        pa[kk][0] = pack_f16(pv[0][0], pv[0][1]);
+        pa[kk][1] = pack_f16(pv[0][2], pv[0][3]);
+        pa[kk][2] = pack_f16(pv[1][0], pv[1][1]);
+        pa[kk][3] = pack_f16(pv[1][2], pv[1][3]);
       }
-      l_run[0] += pv[0][0] + pv[0][1] + pv[1][0] + pv[1][1];
-      l_run[1] += pv[0][2] + pv[0][3] + pv[1][2] + pv[1][3];
-      pa[kk][0] = pack_f16(pv[0][0], pv[0][1]);
-      pa[kk][1] = pack_f16(pv[0][2], pv[0][3]);
-      pa[kk][2] = pack_f16(pv[1][0], pv[1][1]);
-      pa[kk][3] = pack_f16(pv[1][2], pv[1][3]);
-    }
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      O[i][0] *= alpha[0]; O[i][1] *= alpha[0];
-      O[i][2] *= alpha[1]; O[i][3] *= alpha[1];
-    }
-    // ---- O += P V
+      for (int i = 0; i < 16; ++i) {
+        O[i][0] *= alpha[0]; O[i][1] *= alpha[0];
+        O[i][2] *= alpha[1]; O[i][3] *= alpha[1];
+      }
+      // ---- O += P V on this warp's half of the head dim
 #pragma unroll
-    for (int dt = 0; dt < 16; ++dt) {
+      for (int dt = 0; dt < 8; ++dt) {
 #pragma unroll
-      for (int kk = 0; kk < 2; ++kk) {
-        uint32_t vb[4];
-        const int r = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * dt + (lane >> 4);
-        ldsm_x4_t(v_s + r * 512 + ((c ^ (r & 7)) << 4), vb);
-        mma_f16(O[2 * dt], pa[kk], vb[0], vb[1]);
-        mma_f16(O[2 * dt + 1], pa[kk], vb[2], vb[3]);
+        for (int kk = 0; kk < 2; ++kk) {
+          uint32_t vb[4];
+          const int r = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, c = 2 * (dh * 8 + dt) + (lane >> 4);
+          ldsm_x4_t(v_s + r * 512 + ((c ^ (r & 7)) << 4), vb);
+          mma_f16(O[2 * dt], pa[kk], vb[0], vb[1]);
+          mma_f16(O[2 * dt + 1], pa[kk], vb[2], vb[3]);
+        }
       }
     }
+    __syncthreads();    // every warp is done with the operand buffer before the next pages are widened into it
   }
   if (!ok) {
     // a page never arrived: the status word is set; do not leave while own copies may still land
     if (threadIdx.x == 0)
-      for (int i = max(0, issued - kAttnRing); i < issued; ++i)
-        mbar_wait(bar_s + 8 * (i % kAttnRing), (i / kAttnRing) & 1, p.err, kErrWaitDrain);
+      for (int i = max(0, issued - ring); i < issued; ++i)
+        mbar_wait(bar_s + 8 * (i % ring), (i / ring) & 1, p.err, kErrWaitDrain);
     return;
   }
   if (!active) return;
@@ -380,9 +382,9 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
       const int oh = row_head(rr), orow = row_tok(rr);
       if (oh >= hpt || hin + oh >= group || orow >= ntok) continue;
       const float inv = l_run[h2] > 0.f ? p.v_scale / l_run[h2] : 0.f;
-      __nv_bfloat16* dst = p.out + (static_cast<size_t>(row0 + t0 + orow) * p.nq + head0 + oh) * kHeadDim;
+      __nv_bfloat16* dst = p.out + (static_cast<size_t>(row0 + t0 + orow) * p.nq + head0 + oh) * kHeadDim + dh * 128;
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
+      for (int i = 0; i < 16; ++i)
         *reinterpret_cast<__nv_bfloat162*>(dst + i * 8 + 2 * t) =
             __floats2bfloat162_rn(O[i][2 * h2] * inv, O[i][2 * h2 + 1] * inv);
     }
@@ -393,11 +395,11 @@ __global__ void __launch_bounds__(32 * kAttnMaxWarps) attn_paged_kernel(const At
       const int oh = row_head(rr0), rr = row_tok(rr0);
       if (oh >= hpt || hin + oh >= group) continue;
       const size_t pbase = ((static_cast<size_t>(b) * p.nq + head0 + oh) * p.splits + sp) * 16;
-      float* dst = p.part_o + (pbase + rr) * kHeadDim;
+      float* dst = p.part_o + (pbase + rr) * kHeadDim + dh * 128;
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
+      for (int i = 0; i < 16; ++i)
         *reinterpret_cast<float2*>(dst + i * 8 + 2 * t) = make_float2(O[i][2 * h2], O[i][2 * h2 + 1]);
-      if (t == 0) {
+      if (t == 0 && dh == 0) {
         p.part_ml[(pbase + rr) * 2] = m_run[h2];
         p.part_ml[(pbase + rr) * 2 + 1] = l_run[h2];
       }
@@ -449,18 +451,20 @@ extern "C" int saber_attn_launch(const saber::AttnParams* p, cudaStream_t stream
     pack = p->pack_rows;
     hpt = 16 / pack < group ? 16 / pack : group;
   }
-  const int tiles = (group + hpt - 1) / hpt;              // 16-row tiles (= warps) per KV head
-  const int hgroups = (tiles + kAttnMaxWarps - 1) / kAttnMaxWarps;
-  const int hpb = (tiles + hgroups - 1) / hgroups;
-  const int smem = hpb * 8192 + 2 * kAttnOpBytes + kAttnRing * 8192;
+  const int tiles = (group + hpt - 1) / hpt;              // 16-row tiles per KV head, two warps each
+  const int max_tpb = kAttnMaxWarps / 2;
+  const int hgroups = (tiles + max_tpb - 1) / max_tpb;
+  const int tpb = (tiles + hgroups - 1) / hgroups;
+  int ring = (kAttnSmemBudget - tpb * 8192 - kAttnOpBytes) / 8192;
+  ring = ring > kAttnMaxRing ? kAttnMaxRing : ring;
+  const int smem = tpb * 8192 + kAttnOpBytes + ring * 8192;
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(attn_paged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         kAttnMaxWarps * 8192 + 2 * kAttnOpBytes + kAttnRing * 8192);
+    cudaFuncSetAttribute(attn_paged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBudget);
     configured = true;
   }
   dim3 grid(p->q_tiles, p->nkv * hgroups, p->nseq * p->splits);
-  saber::launch(attn_paged_kernel, dim3(grid), dim3(32 * hpb), smem, stream, 0, *p, hpb, hgroups, hpt, pack);
+  saber::launch(attn_paged_kernel, dim3(grid), dim3(64 * tpb), smem, stream, 0, *p, tpb, hgroups, hpt, pack, ring);
   if (p->splits > 1)
     saber::launch(attn_combine_kernel, dim3(dim3(p->nseq * p->nq, 16)), dim3(256), 0, stream, 0, *p);
   return static_cast<int>(cudaGetLastError());

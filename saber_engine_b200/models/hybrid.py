@@ -101,7 +101,7 @@ class Bucket:
 class HybridModel:
     def __init__(self, cfg: HybridConfig, tp: int = 1, rank: int = 0, device="cuda",
                  max_seqs: int = 8, max_ctx: Optional[int] = None, kv_blocks: Optional[int] = None,
-                 max_width: int = 9, weights: Optional[ModelWeights] = None, seed: int = 0,
+                 max_width: int = 8, weights: Optional[ModelWeights] = None, seed: int = 0,
                  comm=None, oracle_p: float = 0.0, oracle_seed: int = 0, gdn_vs: int = 2,
                  use_drafter: bool = True, race_check: str = "off", gdn_prefill: str = "rows"):
         self.cfg, self.tp, self.rank = cfg, tp, rank
@@ -211,9 +211,15 @@ class HybridModel:
                 return int(hit.get("stages", 0))
         return 0
 
-    def attn_splits(self, nseq: int) -> int:
-        ctas = nseq * self.sh.n_kv_heads     # one CTA per SM (shared memory): never more CTAs than SMs
-        return max(1, min(32, 148 // ctas))
+    def attn_splits(self, nseq: int, width: int = 16) -> int:
+        """KV splits of the decode attention: fill the GPU once.  The kernel runs two CTAs per SM;
+        a CTA holds up to four 16-row tiles and a tile holds floor(16 / width) heads of a GQA group."""
+        group = self.sh.n_q_heads // self.sh.n_kv_heads
+        hpt = min(group, 16 // width) if 1 <= width <= 8 else 1
+        tiles = -(-group // hpt)
+        hgroups = -(-tiles // 4)
+        ctas = nseq * self.sh.n_kv_heads * hgroups
+        return max(1, min(32, (2 * 148) // ctas))
 
     def tap_layers(self) -> list:
         n = self.cfg.drafter.n_taps if self.cfg.drafter else 0
@@ -254,7 +260,7 @@ class HybridModel:
         qa_attn = self._qa(M, sh.o_k)
         taps = self.tap_layers() if self.use_drafter else []
         tap_buf = bf(max(1, len(taps)), M, H)
-        splits = self.attn_splits(nseq) if decode else 1
+        splits = self.attn_splits(nseq, width) if decode else 1
         part_o = f32(nseq, sh.n_q_heads, splits, 16, D) if splits > 1 else None
         part_ml = f32(nseq, sh.n_q_heads, splits, 16, 2) if splits > 1 else None
         if cfg.moe is None:

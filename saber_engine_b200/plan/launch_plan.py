@@ -56,7 +56,7 @@ class Manifest:
     max_ctx: int = 262144
     max_seqs: int = 8
     decode_batches: tuple = (1, 2, 3, 4, 8)
-    decode_widths: tuple = (1, 5, 9)
+    decode_widths: tuple = (1, 5, 8)
     prefill_rows: tuple = (128, 512, 2048)
     draft_block: int = 8
     budget_mib: int = 160000

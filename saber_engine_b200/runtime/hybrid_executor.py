@@ -18,7 +18,7 @@ from ..sched.executor import SeqOut, SeqRun
 
 
 class HybridExecutor:
-    def __init__(self, model: HybridModel, decode_batches=DEFAULT_DECODE_BATCHES, decode_widths=(1, 5, 9),
+    def __init__(self, model: HybridModel, decode_batches=DEFAULT_DECODE_BATCHES, decode_widths=(1, 5, 8),
                  prefill_rungs=(128, 512, 2048), prefill_pack: int = 1, capture: bool = True,
                  prebuild: bool = False):
         self.model = model

@@ -141,8 +141,9 @@ CASES = {
     "gemm_w4_gate_up_m2048": lambda: _gemm(34816, 5120, 2048, 1, 1, copies=2),
     "attn_decode_b8_ctx4096": lambda: _attn(8, 9, 4096, 4),
     "attn_decode_b1_ctx32768": lambda: _attn(1, 9, 32768, 32, copies=2),
-    "attn_decode_b8_w8_ctx4096": lambda: _attn(8, 8, 4096, 4),
-    "attn_decode_b8_w1_ctx4096": lambda: _attn(8, 1, 4096, 4),
+    "attn_decode_b8_w8_ctx4096": lambda: _attn(8, 8, 4096, 9),
+    "attn_decode_b8_w1_ctx4096": lambda: _attn(8, 1, 4096, 9),
+    "attn_decode_b8_w5_ctx4096": lambda: _attn(8, 5, 4096, 4),
     "gdn_rec_b8": lambda: _gdn(8, 9, 5),
     "row_add_rms_m72": lambda: _row(72, 5120),
     "moe_block_m72": lambda: _moe(72),

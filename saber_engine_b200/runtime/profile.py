@@ -62,7 +62,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="qwen38-27b")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--width", type=int, default=9)
+    ap.add_argument("--width", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--walk", action="store_true")
     ap.add_argument("--prefill", type=int, default=0, help="profile a prefill bucket of this many rows instead")

@@ -26,7 +26,7 @@ class NullExecutor:
     scheduler changes the generated ids."""
 
     def __init__(self, vocab: int = 1024, max_seqs: int = 8, n_kv_blocks: int = 4096, page_tokens: int = 16,
-                 decode_widths=(1, 5, 9), decode_batches=DEFAULT_DECODE_BATCHES,
+                 decode_widths=(1, 5, 8), decode_batches=DEFAULT_DECODE_BATCHES,
                  prefill_rungs=DEFAULT_PREFILL_RUNGS, draft_hit_rate: float = 0.7, seed: int = 0,
                  leaky: bool = False):
         self.vocab, self.max_seqs, self.n_kv_blocks, self.page_tokens = vocab, max_seqs, n_kv_blocks, page_tokens

@@ -13,10 +13,10 @@ from dataclasses import dataclass, field
 @dataclass
 class WidthByBatch:
     table: dict                      # min batch -> width
-    captured: tuple = (1, 5, 9)
+    captured: tuple = (1, 5, 8)
 
     @staticmethod
-    def parse(spec: str, captured=(1, 5, 9)) -> "WidthByBatch":
+    def parse(spec: str, captured=(1, 5, 8)) -> "WidthByBatch":
         t = {}
         for part in spec.split(","):
             b, w = part.split(":")
@@ -30,7 +30,7 @@ class WidthByBatch:
         return WidthByBatch.parse("1:8,4:5", captured=(1, 5, 8))
 
     @staticmethod
-    def b200(max_width: int = 9) -> "WidthByBatch":
+    def b200(max_width: int = 8) -> "WidthByBatch":
         return WidthByBatch({1: max_width}, captured=tuple(sorted({1, 5, max_width})))
 
     def width_for(self, batch: int) -> int:

@@ -22,7 +22,7 @@ def test_registry_loads_and_plans_tp_by_gpu_count(tmp_path):
     p = R.plan_serve(reg, "27b", tp=4, port=9000, packs=str(tmp_path))
     a = p["argv"]
     assert a[:2] == ["saber", "engine"] and a[a.index("--engine-tp") + 1] == "4"
-    assert a[a.index("--engine-decode-widths") + 1] == "1,5,9" and a[a.index("--port") + 1] == "9000"
+    assert a[a.index("--engine-decode-widths") + 1] == "1,5,8" and a[a.index("--port") + 1] == "9000"
     assert p["pack_present"] is False
 
 
@@ -66,7 +66,7 @@ def test_manifest_unknown_keys_and_plan_hash():
     other = LP.resolve(LP.Manifest(model="qwen38-27b", tp=4, allow_untuned=True))
     assert other.plan_hash != plan.plan_hash
     text = plan.explain()
-    assert "kv_pool (derived)" in text and "mlp.gate_up M=72" in text and "[default]" in text
+    assert "kv_pool (derived)" in text and "mlp.gate_up M=64" in text and "[default]" in text
     with pytest.raises(LP.PlanError, match="no measurement"):
         LP.bind(LP.resolve(LP.Manifest(model="qwen38-27b", tp=2)))          # untuned routes are refused
     with pytest.raises(LP.PlanError, match="KV blocks"):
