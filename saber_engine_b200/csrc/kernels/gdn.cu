@@ -280,6 +280,101 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
   }
 }
 
+// ---------------------------------------------------------------------------------- prefill rows
+// Committing (prefill) form of the recurrence for long row runs: the same row-by-row rule, but eight
+// threads per state row (16 values each) instead of two.  A prefill rung is one sequence walking
+// thousands of rows in order, so what counts is the latency of one row step, not throughput: the
+// dependent FMA chains are four times shorter, at the price of two more shuffle rounds per
+// reduction.  No stash and no replay (a prefill chunk starts from the committed state: shift is 0).
+// grid (HV * 4, nseq), block 256: thread = (v row of a 32-row slice, k part); the thread's values of
+// row v are k = 32 x + 4 kq + c (x, c < 4), so the eight parts read 128 contiguous bytes per x.
+__global__ void __launch_bounds__(256) gdn_prefill_rows_kernel(const GdnRecParams p) {
+  pdl_wait();
+  __shared__ __align__(16) float ks[kRecBatch][128];
+  __shared__ __align__(16) float qs[kRecBatch][128];
+  __shared__ float vsm[kRecBatch][32];
+  __shared__ float gsm[kRecBatch], bsm[kRecBatch];
+  const int b = blockIdx.y;
+  const int slot = p.slots[b];
+  if (slot < 0) return;
+  const int h = blockIdx.x >> 2, vs = blockIdx.x & 3;
+  const int hk = h / (p.HV / p.HK);
+  const int tid = threadIdx.x;
+  const int vloc = tid >> 3, kq = tid & 7;
+  const int v = vs * 32 + vloc;
+  const int row0 = p.cu_rows[b];
+  const int n = p.cu_rows[b + 1] - row0;
+  if (n <= 0) return;
+  float* sp = p.state + ((static_cast<size_t>(slot) * p.HV + h) * 128 + v) * 128 + kq * 4;
+  f32x2 S[8];
+#pragma unroll
+  for (int x = 0; x < 4; ++x) {
+    const ulonglong2 t = *reinterpret_cast<const ulonglong2*>(sp + 32 * x);
+    S[2 * x] = t.x;
+    S[2 * x + 1] = t.y;
+  }
+  const float neg_a = -__expf(p.A_log[h]);
+  const float dtb = p.dt_bias[h];
+  for (int r0 = 0; r0 < n; r0 += kRecBatch) {
+    const int nb = min(kRecBatch, n - r0);
+    __syncthreads();                         // the previous batch is consumed
+    for (int idx = tid; idx < nb * 128; idx += 256) {
+      const int r = idx >> 7, i = idx & 127;
+      const float* xr = p.qkv + static_cast<size_t>(row0 + r0 + r) * p.C;
+      qs[r][i] = xr[hk * 128 + i];
+      ks[r][i] = xr[p.n_q + hk * 128 + i];
+    }
+    for (int idx = tid; idx < nb * 32; idx += 256) {
+      const int r = idx >> 5, i = idx & 31;
+      vsm[r][i] = p.qkv[static_cast<size_t>(row0 + r0 + r) * p.C + p.n_q + p.n_k + h * 128 + vs * 32 + i];
+    }
+    if (tid < nb) {
+      const size_t m = static_cast<size_t>(row0 + r0 + tid);
+      const float bb = __bfloat162float(p.ba[m * p.ldba + h]);
+      const float aa = __bfloat162float(p.ba[m * p.ldba + p.HV + h]);
+      gsm[tid] = neg_a * gdn_softplus(aa + dtb);
+      bsm[tid] = 1.f / (1.f + __expf(-bb));
+    }
+    __syncthreads();
+    for (int r = 0; r < nb; ++r) {
+      const float decay = __expf(gsm[r]);
+      const f32x2 dec2 = pack2(decay, decay);
+      ulonglong2 kk[4];
+      f32x2 a0 = 0ull, a1 = 0ull;
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        kk[x] = *reinterpret_cast<const ulonglong2*>(&ks[r][32 * x + 4 * kq]);
+        S[2 * x] = mul2(S[2 * x], dec2);
+        S[2 * x + 1] = mul2(S[2 * x + 1], dec2);
+        a0 = fma2(S[2 * x], kk[x].x, a0);
+        a1 = fma2(S[2 * x + 1], kk[x].y, a1);
+      }
+      float dot = sum2(a0) + sum2(a1);
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float u = (vsm[r][vloc] - dot) * bsm[r];
+      const f32x2 u2 = pack2(u, u);
+      f32x2 o0 = 0ull, o1 = 0ull;
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const ulonglong2 qq = *reinterpret_cast<const ulonglong2*>(&qs[r][32 * x + 4 * kq]);
+        S[2 * x] = fma2(u2, kk[x].x, S[2 * x]);
+        S[2 * x + 1] = fma2(u2, kk[x].y, S[2 * x + 1]);
+        o0 = fma2(S[2 * x], qq.x, o0);
+        o1 = fma2(S[2 * x + 1], qq.y, o1);
+      }
+      float o = sum2(o0) + sum2(o1);
+#pragma unroll
+      for (int s2 = 1; s2 < 8; s2 <<= 1) o += __shfl_xor_sync(0xffffffffu, o, s2);
+      if (kq == 0)
+        p.out[static_cast<size_t>(row0 + r0 + r) * (static_cast<size_t>(p.HV) * 128) + h * 128 + v] = o;
+    }
+  }
+#pragma unroll
+  for (int x = 0; x < 4; ++x)
+    *reinterpret_cast<ulonglong2*>(sp + 32 * x) = make_ulonglong2(S[2 * x], S[2 * x + 1]);
+}
+
 }  // namespace saber
 
 extern "C" int saber_gdn_conv_launch(const saber::GdnConvParams* p, int nseq, cudaStream_t stream) {
@@ -296,6 +391,10 @@ extern "C" int saber_gdn_recurrent_launch(const saber::GdnRecParams* p, int nseq
                                           cudaStream_t stream) {
   using namespace saber;
   if (p->HV % p->HK) return static_cast<int>(cudaErrorInvalidValue);
+  if (p->commit && p->prefill_rows) {      // long committing runs: the latency-oriented form
+    saber::launch(gdn_prefill_rows_kernel, dim3(p->HV * 4, nseq), dim3(256), 0, stream, 0, *p);
+    return static_cast<int>(cudaGetLastError());
+  }
   if (vs == 1) saber::launch(gdn_recurrent_kernel<1>, dim3(dim3(p->HV, nseq)), dim3(256), 0, stream, 0, *p);
   else if (vs == 2) saber::launch(gdn_recurrent_kernel<2>, dim3(dim3(p->HV * 2, nseq)), dim3(128), 0, stream, 0, *p);
   else if (vs == 4) saber::launch(gdn_recurrent_kernel<4>, dim3(dim3(p->HV * 4, nseq)), dim3(64), 0, stream, 0, *p);

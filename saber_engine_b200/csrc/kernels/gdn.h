@@ -31,6 +31,7 @@ struct GdnRecParams {
   const int32_t* shift;
   float* out;               // [M][HV * 128]
   int C, n_q, n_k, HV, HK, ldba, stash_rows, commit;
+  int prefill_rows;         // commit mode only: 1 = use the eight-threads-per-row kernel (every shift must be 0)
 };
 
 }  // namespace saber

@@ -408,6 +408,38 @@ __global__ void __launch_bounds__(kRowThreads) row_reg_kernel(const RowOpParams 
       }
     }
   }
+  if (p.had_sign != nullptr && p.q) {
+    // 32-point Hadamard per block = this thread's 16 values (one chunk) and its lane neighbour's
+    // (chunks 2j and 2j + 1 belong to lanes 2i and 2i + 1): four butterfly stages in registers,
+    // the fifth across the lane pair.  The quantisation scale is taken AFTER the rotation.
+    amax = 0.f;
+    const bool odd = threadIdx.x & 1;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = threadIdx.x + c * kRowThreads;
+      const bool on = ch < nchunk;               // (nchunk is even: K is a multiple of 128)
+      if (on) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) hv[c][i] *= p.had_sign[(ch << 4) + i];
+#pragma unroll
+        for (int st = 1; st < 16; st <<= 1)
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if ((i & st) == 0) {
+              const float a = hv[c][i], b2 = hv[c][i | st];
+              hv[c][i] = a + b2;
+              hv[c][i | st] = a - b2;
+            }
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, hv[c][i], 1);
+        const float r = (odd ? other - hv[c][i] : hv[c][i] + other) * 0.17677669529663687f;   // 1 / sqrt(32)
+        hv[c][i] = __bfloat162float(__float2bfloat16(r));
+        if (on) amax = fmaxf(amax, fabsf(hv[c][i]));
+      }
+    }
+  }
   amax = block_reduce<true>(amax, red);
   if (p.q) {
     const float qmax = p.qfmt == 1 ? 448.f : 127.f;

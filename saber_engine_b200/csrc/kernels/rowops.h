@@ -39,6 +39,11 @@ struct RowOpParams {
   const int32_t* m_live;
   // quantised output format: 0 = int8 (scale amax / 127), 1 = fp8 e4m3 (scale amax / 448)
   int qfmt;
+  // optional rotation before the quantisation (register-resident modes only): every 32-block of the
+  // row is multiplied by the signs had_sign[k] (+-1) and by the orthonormal 32-point Hadamard matrix;
+  // the consuming linear's weights were rotated the same way, so the product is unchanged while
+  // outliers are spread over the block.  Null = off.
+  const float* had_sign;
 };
 
 }  // namespace saber

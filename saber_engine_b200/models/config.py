@@ -58,6 +58,7 @@ class HybridConfig:
     norm_offset: float = 1.0            # Gemma-style (1 + w)
     attn_out_gate: bool = True
     tie_embeddings: bool = False
+    act_hadamard: bool = False          # rotate activations (sign + 32-point Hadamard) before int8/fp8 quant; weights pre-rotated
     weight_format: str = "iu8"         # 4-bit linears: "iu8" (int4 x int8 acts) | "mxfp4" (e2m1/e8m0 x fp8 acts)
     max_ctx: int = 262144
     page_tokens: int = 16

@@ -171,7 +171,7 @@ class HybridModel:
         (int8 for integer weights, fp8 e4m3 for MXFP4): same storage, different law."""
         if a is None:
             return None
-        return F.QuantAct(a.q, a.scale, a.M, a.K, fp8=bool(getattr(w, "mx", False)))
+        return F.QuantAct(a.q, a.scale, a.M, a.K, fp8=bool(getattr(w, "mx", False)), had_sign=getattr(w, "had_sign", None))
 
     def _gemm(self, prog: N.Program, w: F.QuantWeight, a: F.QuantAct, out: torch.Tensor, tag: str,
               tp_site: int = -1) -> None:
@@ -298,7 +298,8 @@ class HybridModel:
                 ba = buf_in[:, C_ + sh.gdn_out_k:]
                 rp = F.gdn_rec_params(conv_out, ba, lw.A_log, lw.dt_bias, self.gdn_state[i],
                                       self.gdn_stash[i], blob, blob, blob, gdn_o, n_q, n_k,
-                                      sh.gdn_v_heads, sh.gdn_k_heads, commit=not decode, ldba=ld_in)
+                                      sh.gdn_v_heads, sh.gdn_k_heads, commit=not decode, ldba=ld_in,
+                                      prefill_rows=(not decode and width >= 32))
                 rp.cu_rows, rp.slots, rp.shift = at(lay.cu_rows), at(lay.slots), at(lay.shift)
                 if not decode and width >= 64 and self.gdn_prefill == "chunked":
                     # prefill: the chunked (64-row) form; one scratch shared by every layer of the bucket

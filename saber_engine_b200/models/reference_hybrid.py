@@ -40,6 +40,8 @@ def _mx_linear(x: torch.Tensor, wq: torch.Tensor) -> torch.Tensor:
 
 def qlinear(x_bf16_rounded: torch.Tensor, w: QuantWeight) -> torch.Tensor:
     """Quantise rows per token, exact integer GEMM, scale, round to bf16 (as fp32 values)."""
+    if getattr(w, "had_sign", None) is not None:      # the producer rotates before it quantises
+        x_bf16_rounded = R.bf16_round(L.hadamard32_rows(x_bf16_rounded, w.had_sign.cpu()))
     if getattr(w, "mx", False):
         return _mx_linear(x_bf16_rounded, _mx_dense(w)).float()
     q, s = dequant_linear(w)
@@ -53,6 +55,8 @@ def qlinear_row_parallel(x_bf16_rounded: torch.Tensor, w: QuantWeight, tp: int) 
     rounds its partial to bf16; the partials are added in fp32 in rank order and rounded once."""
     if tp == 1:
         return qlinear(x_bf16_rounded, w)
+    if getattr(w, "had_sign", None) is not None:
+        x_bf16_rounded = R.bf16_round(L.hadamard32_rows(x_bf16_rounded, w.had_sign.cpu()))
     if getattr(w, "mx", False):
         wq = _mx_dense(w)
         ks = wq.shape[1] // tp

@@ -79,10 +79,25 @@ def linear_bits(cfg: HybridConfig, name: str) -> int:
     return 8 if name in cfg.w8_linears else 4
 
 
-_FORMAT = {"fmt": "iu8"}     # 4-bit format of the model being generated (set by random_init)
+_FORMAT = {"fmt": "iu8", "had": False, "gen": None}     # format of the model being generated (set by random_init)
 
 
-def _quant_on(dev, w: torch.Tensor, bits: int) -> QuantWeight:
+def _rotate(w: torch.Tensor):
+    """(rotated weight, sign vector) when the model rotates activations, else (w, None).  The signs
+    are drawn from the model's generator, so every rank draws the same vector for the same linear."""
+    if not _FORMAT["had"]:
+        return w, None
+    K = w.shape[1]
+    sign = (torch.randint(0, 2, (K,), generator=_FORMAT["gen"], device=w.device).float() * 2 - 1)
+    return L.hadamard32_rows(w, sign), sign
+
+
+def _quant_on(dev, w: torch.Tensor, bits: int, rotate: bool = False) -> QuantWeight:
+    if rotate:
+        w, sign = _rotate(w)
+        qw = _quant_on(dev, w, bits)
+        qw.had_sign = None if sign is None else sign.to(dev)
+        return qw
     if bits == 4 and _FORMAT["fmt"] == "mxfp4":
         from ..pack import quant_fp4 as Q
         codes, e = Q.quantize_mxfp4(w)
@@ -91,7 +106,16 @@ def _quant_on(dev, w: torch.Tensor, bits: int) -> QuantWeight:
     return QuantWeight.from_int(q, s, bits, dev)
 
 
-def _quant_cols(dev, w_full: torch.Tensor, bits: int, c0: int, c1: int) -> QuantWeight:
+def _quant_cols(dev, w_full: torch.Tensor, bits: int, c0: int, c1: int, rotate: bool = False) -> QuantWeight:
+    if rotate:
+        w_full, sign = _rotate(w_full)
+        qw = _quant_cols(dev, w_full, bits, c0, c1)
+        qw.had_sign = None if sign is None else sign[c0:c1].contiguous().to(dev)
+        return qw
+    return _quant_cols_plain(dev, w_full, bits, c0, c1)
+
+
+def _quant_cols_plain(dev, w_full: torch.Tensor, bits: int, c0: int, c1: int) -> QuantWeight:
     """Row-parallel shard: quantise the FULL rows (one scale per output feature over the whole
     reduction dim), then keep columns [c0, c1).  Every TP degree therefore holds the same integers
     and the same scales as TP=1, split along K."""
@@ -116,8 +140,8 @@ def random_init(cfg: HybridConfig, tp: int, rank: int, device, seed: int = 0,
     """
     sh = shard(cfg, tp, rank)
     dev = torch.device(device)
-    _FORMAT["fmt"] = cfg.weight_format
     g = torch.Generator(device=dev).manual_seed(seed)
+    _FORMAT.update(fmt=cfg.weight_format, had=bool(cfg.act_hadamard), gen=g)
     H, d, D = cfg.hidden, cfg.gdn_head_dim, cfg.head_dim
 
     def rand(n, k):
@@ -142,10 +166,10 @@ def random_init(cfg: HybridConfig, tp: int, rank: int, device, seed: int = 0,
             if cfg.attn_out_gate:
                 parts.append(rows(wq, cfg.n_q_heads * D + sh.q_head_first * D, nq * D))
             parts += [rows(wk, sh.kv_head_first * D, nkv * D), rows(wv, sh.kv_head_first * D, nkv * D)]
-            mixer_in = _quant_on(dev, torch.cat(parts, 0), linear_bits(cfg, name + ".mixer.in"))
+            mixer_in = _quant_on(dev, torch.cat(parts, 0), linear_bits(cfg, name + ".mixer.in"), rotate=True)
             wo = rand(H, cfg.n_q_heads * D)
             mixer_out = _quant_cols(dev, wo, linear_bits(cfg, name + ".mixer.out"),
-                                    sh.q_head_first * D, (sh.q_head_first + nq) * D)
+                                    sh.q_head_first * D, (sh.q_head_first + nq) * D, rotate=True)
             lw = LayerWeights("attn", vec(H), vec(H), mixer_in, mixer_out,
                               q_norm=vec(D), k_norm=vec(D))
             del wq, wk, wv, wo
@@ -158,7 +182,7 @@ def random_init(cfg: HybridConfig, tp: int, rank: int, device, seed: int = 0,
             k0, v0 = rank * hk, rank * hv
             parts = [rows(wq, k0 * d, hk * d), rows(wk, k0 * d, hk * d), rows(wv, v0 * d, hv * d),
                      rows(wz, v0 * d, hv * d), rows(wb, v0, hv), rows(wa, v0, hv)]
-            mixer_in = _quant_on(dev, torch.cat(parts, 0), linear_bits(cfg, name + ".mixer.in"))
+            mixer_in = _quant_on(dev, torch.cat(parts, 0), linear_bits(cfg, name + ".mixer.in"), rotate=True)
             wo = rand(H, HV * d)
             mixer_out = _quant_cols(dev, wo, linear_bits(cfg, name + ".mixer.out"), v0 * d, (v0 + hv) * d)
             conv_full = torch.randn(2 * HK * d + HV * d, 4, generator=g, device=dev) * 0.5
@@ -175,9 +199,9 @@ def random_init(cfg: HybridConfig, tp: int, rank: int, device, seed: int = 0,
             wg, wu = rand(I, H), rand(I, H)
             i0, il = rank * sh.ffn_inter, sh.ffn_inter
             lw.gate_up = _quant_on(dev, torch.cat([wg[i0:i0 + il], wu[i0:i0 + il]], 0),
-                                   linear_bits(cfg, name + ".mlp.gate_up"))
+                                   linear_bits(cfg, name + ".mlp.gate_up"), rotate=True)
             wd = rand(H, I)
-            lw.down = _quant_cols(dev, wd, linear_bits(cfg, name + ".mlp.down"), i0, i0 + il)
+            lw.down = _quant_cols(dev, wd, linear_bits(cfg, name + ".mlp.down"), i0, i0 + il, rotate=True)
             del wg, wu, wd
         else:
             from .moe_weights import random_moe_layer

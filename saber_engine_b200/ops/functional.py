@@ -26,6 +26,7 @@ class QuantWeight:
     K: int
     w4: bool
     mx: bool = False         # MXFP4 tiles (e2m1 codes + block shifts): fp8 activations, fp32 accumulate
+    had_sign: Optional[torch.Tensor] = None   # fp32 [K] +-1: the input must be rotated (sign, 32-point Hadamard) before quantisation
 
     @property
     def N_pad(self) -> int:
@@ -72,6 +73,7 @@ class QuantAct:
     M: int
     K: int
     fp8: bool = False        # bytes are fp8 e4m3 (scale = amax / 448) instead of int8 (amax / 127)
+    had_sign: Optional[torch.Tensor] = None   # rotation the producer applies before it quantises into this buffer
 
     @property
     def M_pad(self) -> int:
@@ -173,6 +175,7 @@ def row_params(M: int, K: int, *, a=None, a_f32=None, b=None, res=None, w=None, 
     p.ldres = res.stride(0) if res is not None else 0
     p.ldout = out.stride(0) if out is not None else 0
     p.qfmt = int(qa.fp8) if qa is not None else 0
+    p.had_sign = N.ptr(qa.had_sign) if qa is not None else None
     return p
 
 
@@ -295,7 +298,7 @@ def gdn_conv(x, conv_w, hist, cu_rows, slots, shift, n_q, n_k, commit=False):
 
 
 def gdn_rec_params(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, out, n_q, n_k,
-                   HV, HK, commit, ldba=None):
+                   HV, HK, commit, ldba=None, prefill_rows: bool = False):
     p = N.GdnRecParams()
     p.qkv, p.ba, p.A_log, p.dt_bias = qkv.data_ptr(), ba.data_ptr(), A_log.data_ptr(), dt_bias.data_ptr()
     p.state, p.stash = state.data_ptr(), stash.data_ptr()
@@ -303,15 +306,16 @@ def gdn_rec_params(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift,
     p.C, p.n_q, p.n_k, p.HV, p.HK = qkv.shape[1], n_q, n_k, HV, HK
     p.ldba = ldba if ldba is not None else ba.stride(0)
     p.stash_rows, p.commit = stash.shape[1], int(commit)
+    p.prefill_rows = int(bool(prefill_rows and commit))
     return p
 
 
 def gdn_recurrent(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, n_q, n_k, HV, HK,
-                  commit=False, vs=2):
+                  commit=False, vs=2, prefill_rows: bool = False):
     M = qkv.shape[0]
     out = torch.empty(M, HV * 128, dtype=torch.float32, device=qkv.device)
     p = gdn_rec_params(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, out, n_q, n_k,
-                       HV, HK, commit)
+                       HV, HK, commit, prefill_rows=prefill_rows)
     N.check(N.lib().saber_gdn_recurrent_launch(C.byref(p), slots.numel(), vs, N.stream_handle()), "gdn_rec")
     return out
 

@@ -13,6 +13,8 @@ activations are per-token dynamic int8, scale = amax / 127, q = clamp(rint(x * (
 """
 from __future__ import annotations
 
+import math
+
 import torch
 
 TILE_N = 256          # output features per weight tile (the N side of one MMA)
@@ -171,3 +173,20 @@ def untile_weight_mxfp4(tiles: torch.Tensor, N: int, K: int):
     codes = untile_weight_int8(img, N, K).view(torch.uint8)
     sh = tiles[..., 16384:].reshape(nt, kb, TILE_N, 4).permute(0, 2, 1, 3).reshape(nt * TILE_N, kb * 4)
     return codes, sh[:N].contiguous()
+
+
+# ------------------------------------------------------------------------------- Hadamard rotation
+def hadamard32_matrix(device=None) -> torch.Tensor:
+    """Orthonormal 32 x 32 Hadamard matrix (Sylvester order, entries +-1/sqrt(32))."""
+    h = torch.ones(1, 1, device=device)
+    for _ in range(5):
+        h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
+    return h / math.sqrt(32.0)
+
+
+def hadamard32_rows(x: torch.Tensor, sign: torch.Tensor) -> torch.Tensor:
+    """x [M, K] -> every 32-block of (x * sign) times the orthonormal Hadamard matrix (the rotation
+    the row producers apply before they quantise; H is symmetric, so the same call rotates weights)."""
+    M, K = x.shape
+    h = hadamard32_matrix(x.device)
+    return ((x.float() * sign.float()).reshape(M, K // 32, 32) @ h).reshape(M, K)

@@ -51,7 +51,7 @@ class RowOpParams(C.Structure):
                 ("eps", F), ("out", P), ("q", P), ("scale", P), ("M", I), ("M_pad", I), ("K", I),
                 ("lda", I), ("ldb", I), ("ldres", I), ("ldout", I), ("tp_recv", P), ("tp_flags", P),
                 ("tp_seq_base", P), ("err", P), ("tp_nranks", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I),
-                ("tp_nt", I), ("tp_tiles_n", I), ("m_live", P), ("qfmt", I)]
+                ("tp_nt", I), ("tp_tiles_n", I), ("m_live", P), ("qfmt", I), ("had_sign", P)]
 
 
 class GdnConvParams(C.Structure):
@@ -63,7 +63,7 @@ class GdnConvParams(C.Structure):
 class GdnRecParams(C.Structure):
     _fields_ = [("qkv", P), ("ba", P), ("A_log", P), ("dt_bias", P), ("state", P), ("stash", P),
                 ("cu_rows", P), ("slots", P), ("shift", P), ("out", P), ("C", I), ("n_q", I),
-                ("n_k", I), ("HV", I), ("HK", I), ("ldba", I), ("stash_rows", I), ("commit", I)]
+                ("n_k", I), ("HV", I), ("HK", I), ("ldba", I), ("stash_rows", I), ("commit", I), ("prefill_rows", I)]
 
 
 class RopeKvParams(C.Structure):

@@ -324,7 +324,12 @@ def test_gdn_chunked_prefill_equals_row_by_row_kernel():
     stash = torch.zeros(3, 4, HV, 2, F.gdn_stash_stride(2), device=DEV)
     want = F.gdn_recurrent(qkv, ba, A_log, dtb, st_a, stash, cu, slots, sh, n_q, n_k, HV, HK, commit=True, vs=2)
     got = F.gdn_chunked(qkv, ba, A_log, dtb, st_b, stash, cu, slots, sh, n_q, n_k, HV, HK, max_rows=max(lens))
+    st_c = s["state"].to(DEV).clone()
+    rows8 = F.gdn_recurrent(qkv, ba, A_log, dtb, st_c, stash, cu, slots, sh, n_q, n_k, HV, HK, commit=True, prefill_rows=True)
     torch.cuda.synchronize()
+    # the eight-threads-per-row prefill form: same rule, another summation order
+    assert (rows8 - want).abs().max().item() <= 2e-4 * want.abs().max().item() + 1e-5
+    assert (st_a[1:] - st_c[1:]).abs().max().item() <= 2e-4 * st_a.abs().max().item() + 1e-5
     scale = want.abs().max().item()
     assert (got - want).abs().max().item() <= 2e-4 * scale + 1e-5, ((got - want).abs().max().item(), scale)
     assert (st_a[1:] - st_b[1:]).abs().max().item() <= 2e-4 * st_a.abs().max().item() + 1e-5

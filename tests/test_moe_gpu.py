@@ -226,3 +226,33 @@ def test_mxfp4_hybrid_prefill_matches_oracle_and_spec_equals_greedy():
     res2 = run_bucket(model, pb, [SeqStep(prompt, 0, 2, 0, b2)])
     assert decode(2, b2, res2.tokens[0][0], res2.drafts[0], 5) == plain
     model.scratch.check()
+
+
+def test_hadamard_rotated_activations_match_oracle():
+    """act_hadamard: the row producers rotate (sign, 32-point Hadamard) before they quantise, the
+    weights are rotated the same way; logits follow the oracle that restates the rotation."""
+    import dataclasses
+    from saber_engine_b200.models.hybrid import HybridModel, SeqStep, run_bucket
+    from saber_engine_b200.models.reference_hybrid import forward_full
+    from saber_engine_b200.ops import layouts as LL
+    # the kernel's rotation alone: quantised bytes of a rotated row
+    x = torch.randn(7, 512).to(torch.bfloat16)
+    sign = (torch.randint(0, 2, (512,)).float() * 2 - 1)
+    qa = F.QuantAct.alloc(7, 512, "cuda")
+    qa.had_sign = sign.cuda()
+    F._row(N.ROW_PLAIN, F.row_params(7, 512, a=x.cuda(), qa=qa))
+    torch.cuda.synchronize()
+    want = LL.hadamard32_rows(x.float(), sign).to(torch.bfloat16).float()
+    assert torch.allclose(qa.scale[:7].cpu(), want.abs().amax(1) / 127.0, rtol=1e-2, atol=1e-6)
+    cfg = dataclasses.replace(C.scaled_hybrid(name="hybrid-mini-had"), act_hadamard=True)
+    model = HybridModel(cfg, device="cuda", max_seqs=2, max_ctx=512, max_width=5, seed=2)
+    assert model.w.layers[0].mixer_in.had_sign is not None
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
+    model.reset_slot(1)
+    pb = model.build_bucket("prefill", 1, 48)
+    run_bucket(model, pb, [SeqStep(prompt, 0, 1, 0, list(range(1, 33)))])
+    got = pb.logits[0, : cfg.vocab].float().cpu()
+    ref = forward_full(cfg, model.w, torch.tensor(prompt))["logits"][-1]
+    assert (got - ref).abs().max() < 0.06 * ref.abs().max() + 1e-3
+    model.scratch.check()
