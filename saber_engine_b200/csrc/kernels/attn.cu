@@ -138,7 +138,8 @@ constexpr int kAttnSmemBudget = 112 * 1024;   // two CTAs per SM
 // The raw fp8 pages of the split stream through a ring in shared memory, filled by bulk copies
 // that complete on mbarriers; each iteration takes two pages, all threads widen them to fp16 into
 // the operand buffer.
-__global__ void __launch_bounds__(32 * kAttnMaxWarps, 2) attn_paged_kernel(const AttnParams p,
+template <int MAXW, int MINB>
+__global__ void __launch_bounds__(32 * MAXW, MINB) attn_paged_kernel(const AttnParams p,
                                                                            const int tpb,
                                                                            const int hgroups,
                                                                            const int hpt,
@@ -452,19 +453,27 @@ extern "C" int saber_attn_launch(const saber::AttnParams* p, cudaStream_t stream
     hpt = 16 / pack < group ? 16 / pack : group;
   }
   const int tiles = (group + hpt - 1) / hpt;              // 16-row tiles per KV head, two warps each
-  const int max_tpb = kAttnMaxWarps / 2;
+  // decode: up to four tiles per CTA, two CTAs per SM.  Prefill (many query tiles, no packing): one
+  // CTA with all six tiles of the group, so that every page is widened once per KV head.
+  const bool wide = p->q_tiles > 1 && tiles > kAttnMaxWarps / 2 && tiles <= 6;
+  const int max_tpb = wide ? 6 : kAttnMaxWarps / 2;
   const int hgroups = (tiles + max_tpb - 1) / max_tpb;
   const int tpb = (tiles + hgroups - 1) / hgroups;
-  int ring = (kAttnSmemBudget - tpb * 8192 - kAttnOpBytes) / 8192;
+  const int budget = wide ? 200 * 1024 : kAttnSmemBudget;
+  int ring = (budget - tpb * 8192 - kAttnOpBytes) / 8192;
   ring = ring > kAttnMaxRing ? kAttnMaxRing : ring;
   const int smem = tpb * 8192 + kAttnOpBytes + ring * 8192;
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(attn_paged_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBudget);
+    cudaFuncSetAttribute(attn_paged_kernel<kAttnMaxWarps, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemBudget);
+    cudaFuncSetAttribute(attn_paged_kernel<12, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     configured = true;
   }
   dim3 grid(p->q_tiles, p->nkv * hgroups, p->nseq * p->splits);
-  saber::launch(attn_paged_kernel, dim3(grid), dim3(64 * tpb), smem, stream, 0, *p, tpb, hgroups, hpt, pack, ring);
+  if (wide)
+    saber::launch(attn_paged_kernel<12, 1>, dim3(grid), dim3(64 * tpb), smem, stream, 0, *p, tpb, hgroups, hpt, pack, ring);
+  else
+    saber::launch(attn_paged_kernel<kAttnMaxWarps, 2>, dim3(grid), dim3(64 * tpb), smem, stream, 0, *p, tpb, hgroups, hpt, pack, ring);
   if (p->splits > 1)
     saber::launch(attn_combine_kernel, dim3(dim3(p->nseq * p->nq, 16)), dim3(256), 0, stream, 0, *p);
   return static_cast<int>(cudaGetLastError());
