@@ -54,8 +54,13 @@ constexpr uint32_t kTileBytes = 32768;   // int8 image of one weight tile (256 x
 constexpr int kUBufs = 3;                // W4: widened int8 operand buffers (transform, MMA and
                                          // the buffer-free round trip overlap with three)
 
-__global__ void __launch_bounds__(kGemmThreads)
-gemm_i8_kernel(const GemmI8Params p, const int stages) {
+// kLean: the grouped (mixture-of-experts) instantiation -- no split-K and no tensor-parallel code,
+// two operand buffers instead of three, at most 102 registers -- so that TWO CTAs share an SM: an
+// expert tile is only 16 k-blocks long, and the second CTA's main loop hides the first one's
+// start-up latency (cold weights: 3-4 us to the first MMA) and epilogue.
+template <bool kLean>
+__device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int stages) {
+  constexpr int nub = kLean ? 2 : kUBufs;     // operand buffers in use
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bars[2 * kMaxStages + 2 * kUBufs + 1];
   __shared__ uint32_t tmem_base_s;
@@ -108,7 +113,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
   // token ring | W4: three int8 operand buffers | weight ring (W4: packed 16 KiB stages, W8: 32 KiB)
   const uint32_t a_smem = smem_base;
   const uint32_t u_smem = smem_base + static_cast<uint32_t>(stages) * abytes;
-  const uint32_t w_smem = u_smem + (p.w4 ? kUBufs * kTileBytes : 0u);
+  const uint32_t w_smem = u_smem + (p.w4 ? nub * kTileBytes : 0u);
   const uint32_t bar_full = smem_u32(&bars[0]);
   const uint32_t bar_empty = smem_u32(&bars[kMaxStages]);
   const uint32_t bar_ready = smem_u32(&bars[2 * kMaxStages]);           // kUBufs
@@ -122,7 +127,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int u = 0; u < kUBufs; ++u) {
+    for (int u = 0; u < nub; ++u) {
       mbar_init(bar_ready + 8 * u, 8);  // one arrival per transform warp
       mbar_init(bar_ufree + 8 * u, 1);
     }
@@ -221,7 +226,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
         mma_commit(bar_empty + 8 * s);
         if (p.w4) {
           mma_commit(bar_ufree + 8 * u);
-          if (++u == kUBufs) { u = 0; uph ^= 1u; }
+          if (++u == nub) { u = 0; uph ^= 1u; }
         }
         a_addr += abytes;
         if (++s == stages) { s = 0; ph ^= 1u; a_addr = a_smem; }
@@ -310,7 +315,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
         if (lane == 0) mbar_arrive(bar_ready + 8 * u);
         if (it == 0 && tid8 == 0) SABER_STAMP(4);
         if (++s == stages) { s = 0; ph ^= 1u; }
-        if (++u == kUBufs) { u = 0; ufree_ph ^= 1u; }
+        if (++u == nub) { u = 0; ufree_ph ^= 1u; }
       }
     }
     if (tgroup == 0) {
@@ -340,7 +345,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
       };
       // tensor-parallel mode: a finished 16-byte group of outputs goes to every rank's receive
       // region (slot = parity of the call's sequence number, source = this rank)
-      const bool tp = p.tp_nranks > 1;
+      const bool tp = !kLean && p.tp_nranks > 1;
       uint32_t tp_seq = 0, tp_par = 0;
       if (tp) {
         tp_seq = *p.tp_seq_base + static_cast<uint32_t>(p.tp_site) + 1u;
@@ -359,7 +364,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
           asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tp_seq) : "memory");
         }
       };
-      if (p.splits == 1) {
+      if (kLean || p.splits == 1) {
         // The accumulator arrives one token row per thread; stored like that, the 32 lanes of a
         // warp would write 32 different rows (16-byte pieces, and over NVLink 16-byte packets).
         // So the bf16 tile is first staged in shared memory -- the operand buffers are idle by
@@ -417,7 +422,7 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
           }
         }
         if (tp) tp_signal(tile_m * gridDim.x + tile_n);
-      } else {
+      } else if constexpr (!kLean) {
         // each split writes its own partial tile; inside a (split, tile) block the 16-byte group of
         // four columns c4 of row r sits at (c4 * 128 + r) * 16 bytes, so the 32 lanes of a warp
         // (32 consecutive rows) store -- and later load -- 512 contiguous bytes
@@ -584,6 +589,13 @@ gemm_i8_kernel(const GemmI8Params p, const int stages) {
 #undef SABER_STAMP
 }
 
+__global__ void __launch_bounds__(kGemmThreads) gemm_i8_kernel(const GemmI8Params p, const int stages) {
+  gemm_i8_body<false>(p, stages);
+}
+__global__ void __launch_bounds__(kGemmThreads, 2) gemm_i8_lean_kernel(const GemmI8Params p, const int stages) {
+  gemm_i8_body<true>(p, stages);
+}
+
 }  // namespace saber
 
 // Number of flags per output tile a tensor-parallel launch of `p` raises (the consumer must wait
@@ -629,6 +641,7 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   if (smem > kSmemLimit) return static_cast<int>(cudaErrorInvalidValue);
   static bool configured = false;
   if (!configured) {
+    cudaFuncSetAttribute(gemm_i8_lean_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
     cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemLimit);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -646,6 +659,12 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   GemmI8Params q = *p;
   // one CTA per SM (shared memory): the whole grid is resident iff it has no more CTAs than SMs
   q.coop = (p->splits > 1 && p->coop >= 0 && static_cast<int>(grid.x * grid.y * grid.z) <= sm_count) ? 1 : 0;
+  // grouped tiles: the lean instantiation, two CTAs per SM, when two ring stages fit its budget
+  if (p->group_tiles && p->w4 == 1 && p->splits == 1) {
+    const int lean_smem = 2 * (16384 + p->nt * 128) + 2 * 32768 + 1024;
+    if (lean_smem <= 112 * 1024)
+      return static_cast<int>(saber::launch(gemm_i8_lean_kernel, grid, dim3(kGemmThreads), lean_smem, stream, 2, q, 2));
+  }
   return static_cast<int>(saber::launch(gemm_i8_kernel, grid, dim3(kGemmThreads), smem, stream, (q.coop != 0 ? 1 : 0) | 2, q, stages));
 }
 
