@@ -165,6 +165,24 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         if (it == 0) SABER_STAMP(2);
       }
       pdl_wait();
+      if (!kLean && p.ag_flags != nullptr) {
+        // all-gather fused into the operand load: the owners of these token rows push them into
+        // local memory and raise one flag per 128-row tile; wait for it (bounded) before the
+        // first token-tile copy of this CTA
+        const uint32_t seq = *p.ag_seq_base + static_cast<uint32_t>(p.ag_site) + 1u;
+        const uint32_t* flag = p.ag_flags + (seq & 1u) * 64u + static_cast<uint32_t>(m0 >> 7);
+        const long long t0 = clock64();
+        for (uint32_t polls = 0;; ++polls) {
+          uint32_t v;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+          if (static_cast<int32_t>(v - seq) >= 0) break;
+          // (half the limit of the pipeline's own waits, so that this cause is the one recorded)
+          if ((polls & 1023u) == 1023u && clock64() - t0 > kWaitLimitCycles / 2) {
+            atomicCAS(p.err, 0u, static_cast<uint32_t>(kErrWaitPeer));
+            break;     // the status word is set; the copies below read whatever is there
+          }
+        }
+      }
       for (int it = 0; it < pre; ++it) {
         bulk_g2s(a_smem + it * abytes, ap, abytes, bar_full + 8 * it);
         ap += a_kb_stride;
@@ -351,14 +369,19 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         tp_seq = *p.tp_seq_base + static_cast<uint32_t>(p.tp_site) + 1u;
         tp_par = tp_seq & 1u;
       }
+      const int tp_owner = (!kLean && p.tp_rpr > 0) ? m0 / p.tp_rpr : -1;   // reduce-scatter: the one destination
       auto tp_push16 = [&](int mm, int nn, const uint4& v) {
         const size_t off = ((static_cast<size_t>(tp_par) * p.tp_nranks + p.tp_rank) * p.tp_rows + mm) * p.tp_ld + nn;
+        if (tp_owner >= 0) {
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.tp_recv[tp_owner]) + off) = v;
+          return;
+        }
         for (int peer = 0; peer < p.tp_nranks; ++peer)
           *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.tp_recv[peer]) + off) = v;
       };
       auto tp_signal = [&](int tile_id) {   // called by all 128 epilogue threads after their stores
         named_bar_sync(1, 128);             // every thread's pushes precede the barrier ...
-        if (tid_t < p.tp_nranks) {
+        if (tp_owner >= 0 ? tid_t == tp_owner : tid_t < p.tp_nranks) {
           __threadfence_system();           // ... and this fence is cumulative over what the barrier ordered
           uint32_t* f = p.tp_flags[tid_t] + (static_cast<size_t>(tp_par) * p.tp_nranks + p.tp_rank) * kTpMaxTiles + tile_id;
           asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(tp_seq) : "memory");
@@ -541,8 +564,11 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
               if (tp) {
                 if (n0 + c < p.N) {
                   const size_t off = ((static_cast<size_t>(tp_par) * p.tp_nranks + p.tp_rank) * p.tp_rows + m0 + rr[u]) * p.tp_ld + n0 + c;
-                  for (int peer = 0; peer < p.tp_nranks; ++peer)
-                    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.tp_recv[peer]) + off) = pk;
+                  if (tp_owner >= 0)
+                    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.tp_recv[tp_owner]) + off) = pk;
+                  else
+                    for (int peer = 0; peer < p.tp_nranks; ++peer)
+                      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.tp_recv[peer]) + off) = pk;
                 }
               } else {
                 __nv_bfloat16* o = p.out + static_cast<size_t>(m0 + rr[u]) * p.ldo + n0 + c;
@@ -621,6 +647,7 @@ extern "C" int saber_gemm_i8_smem_bytes_w(int nt, int stages, int w4) {
 
 extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cudaStream_t stream) {
   using namespace saber;
+  if (p->ag_flags != nullptr && (p->M + 127) / 128 > 64) return static_cast<int>(cudaErrorInvalidValue);
   if (p->nt < 16 || p->nt > 128 || (p->nt & 15) || (p->K & 127) || p->K <= 0 || p->M <= 0 ||
       (p->N_pad & 255) || p->splits < 1 || p->splits > 8 || (p->M_pad % p->nt) != 0 || (p->ldo & 7))
     return static_cast<int>(cudaErrorInvalidValue);
@@ -629,7 +656,7 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   if ((p->splits - 1) * kb_per >= KB) return static_cast<int>(cudaErrorInvalidValue);
   if (p->tp_nranks > 1) {
     const int tiles = (p->N_pad / 256) * ((p->M + p->nt - 1) / p->nt);
-    if (p->tp_nranks > 8 || (p->N & 7) || (p->tp_ld & 7) || tiles * saber_gemm_i8_parts(p) > kTpMaxTiles || p->M > p->tp_rows)
+    if ((p->tp_rpr > 0 && (p->tp_rpr % p->nt) != 0) || p->tp_nranks > 8 || (p->N & 7) || (p->tp_ld & 7) || tiles * saber_gemm_i8_parts(p) > kTpMaxTiles || p->M > p->tp_rows)
       return static_cast<int>(cudaErrorInvalidValue);
   }
   const int kSmemLimit = 224 * 1024;  // opt-in maximum minus the kernel's static shared memory

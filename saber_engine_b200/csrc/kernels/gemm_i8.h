@@ -32,6 +32,16 @@ struct GemmI8Params {
   uint32_t* tp_flags[8];   // each rank's flag region:    [2 parity][nranks src][kTpMaxTiles]
   const uint32_t* tp_seq_base;
   int tp_nranks, tp_rank, tp_site, tp_rows, tp_ld;
+  // Sequence-parallel forms.  tp_rpr > 0: reduce-scatter -- a row's partial sums go ONLY to the rank
+  // that owns the row (owner = row / tp_rpr; tp_rpr is a multiple of the token tile) and only that
+  // rank's flags are raised.  ag_flags != null: all-gather fused into the operand load -- the token
+  // rows of this GEMM were written into local memory by their owners (the add-norm-quant kernel of
+  // every rank pushes its rows to all ranks); the producer warp waits (bounded) for the arrival flag
+  // of its 128-row tile before it issues the first token-tile copy.
+  int tp_rpr;
+  const uint32_t* ag_flags;      // THIS rank's arrival flags [2 parity][64 row tiles]
+  const uint32_t* ag_seq_base;
+  int ag_site;
   // Grouped (mixture-of-experts) mode, group_tiles != null: blockIdx.y walks a device-built tile
   // table {expert, first row, live rows, 0}; rows are the expert-major sorted token rows.  CTAs
   // beyond *group_ntiles leave at once, so the grid is static (graph-capturable) and sized for the

@@ -279,6 +279,8 @@ __global__ void __launch_bounds__(kRowThreads) row_reg_kernel(const RowOpParams 
   const int K = p.K;
   if (p.m_live != nullptr && m >= *p.m_live) return;
   const int nchunk = K >> 4;
+  const bool sp = MODE == kRowAddRms && p.sp_rpr > 0 && p.tp_nranks > 1;
+  if (sp && (m >= p.M || m / p.sp_rpr != p.sp_rank)) return;   // sequence parallel: not this rank's row
   if (m >= p.M) {  // padding row: zeros
     if (p.q) {
       for (int ch = threadIdx.x; ch < nchunk; ch += kRowThreads) {
@@ -444,7 +446,7 @@ __global__ void __launch_bounds__(kRowThreads) row_reg_kernel(const RowOpParams 
   if (p.q) {
     const float qmax = p.qfmt == 1 ? 448.f : 127.f;
     const float inv = amax > 0.f ? qmax / amax : 0.f;
-    if (threadIdx.x == 0) p.scale[m] = amax / qmax;
+    if (threadIdx.x == 0 && !sp) p.scale[m] = amax / qmax;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
       const int ch = threadIdx.x + c * kRowThreads;
@@ -454,8 +456,33 @@ __global__ void __launch_bounds__(kRowThreads) row_reg_kernel(const RowOpParams 
       for (int i = 0; i < 4; ++i)
         w[i] = quant4(hv[c][i * 4], hv[c][i * 4 + 1], hv[c][i * 4 + 2], hv[c][i * 4 + 3], inv, p.qfmt);
       const int kb = ch >> 3, cc = ch & 7;
-      int8_t* dst = p.q + (static_cast<size_t>(kb) * p.M_pad + m) * 128 + (((cc ^ (m & 7)) & 7) << 4);
-      *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+      const size_t off = (static_cast<size_t>(kb) * p.M_pad + m) * 128 + (((cc ^ (m & 7)) & 7) << 4);
+      if (sp) {
+        for (int peer = 0; peer < p.tp_nranks; ++peer)
+          *reinterpret_cast<uint4*>(p.sp_q[peer] + off) = make_uint4(w[0], w[1], w[2], w[3]);
+      } else {
+        *reinterpret_cast<uint4*>(p.q + off) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    if (sp) {
+      if (threadIdx.x == 0)
+        for (int peer = 0; peer < p.tp_nranks; ++peer) p.sp_scale[peer][m] = amax / qmax;
+      // the row is on every rank once these stores are visible; the CTA that completes the 128-row
+      // tile raises its arrival flag everywhere
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        const int tile = m >> 7;
+        const int rows_in_tile = min(128, p.M - (tile << 7));
+        const uint32_t old = atomicAdd(p.sp_counter + tile, 1u);
+        if (old == static_cast<uint32_t>(rows_in_tile - 1)) {
+          p.sp_counter[tile] = 0u;
+          __threadfence_system();
+          const uint32_t seq = *p.tp_seq_base + static_cast<uint32_t>(p.tp_site) + 1u;
+          for (int peer = 0; peer < p.tp_nranks; ++peer)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.sp_flags[peer] + (seq & 1u) * 64u + tile), "r"(seq) : "memory");
+        }
+      }
     }
   }
 }

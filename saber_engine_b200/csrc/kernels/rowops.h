@@ -44,6 +44,16 @@ struct RowOpParams {
   // the consuming linear's weights were rotated the same way, so the product is unchanged while
   // outliers are spread over the block.  Null = off.
   const float* had_sign;
+  // Sequence-parallel ADD_RMS (sp_rpr > 0, with tp_nranks > 1): only the rows this rank owns are
+  // processed (owner = row / sp_rpr); their partial sums arrive by reduce-scatter; the residual
+  // stream is sharded by rows; the quantised row and its scale are stored into EVERY rank's
+  // activation buffer (all-gather by peer stores), and the CTA that completes a 128-row tile
+  // raises that tile's arrival flag on every rank.
+  int8_t* sp_q[8];
+  float* sp_scale[8];
+  uint32_t* sp_flags[8];        // each rank's arrival flags [2 parity][64 row tiles]
+  uint32_t* sp_counter;         // this rank's rows-done counters [64 row tiles] (zero between uses)
+  int sp_rpr, sp_rank;
 };
 
 }  // namespace saber

@@ -42,7 +42,7 @@ class GemmI8Params(C.Structure):
     _fields_ = [("w", P), ("w_scale", P), ("a", P), ("a_scale", P), ("out", P), ("ws", P),
                 ("counters", P), ("err", P), ("M", I), ("M_pad", I), ("N", I), ("N_pad", I),
                 ("K", I), ("nt", I), ("splits", I), ("w4", I), ("ldo", I), ("dbg_mma", I), ("tp_recv", P * 8), ("tp_flags", P * 8), ("tp_seq_base", P),
-                ("tp_nranks", I), ("tp_rank", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I),
+                ("tp_nranks", I), ("tp_rank", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I), ("tp_rpr", I), ("ag_flags", P), ("ag_seq_base", P), ("ag_site", I),
                 ("group_tiles", P), ("group_ntiles", P), ("group_w_stride", U64), ("coop", I), ("dbg", P)]
 
 
@@ -51,7 +51,9 @@ class RowOpParams(C.Structure):
                 ("eps", F), ("out", P), ("q", P), ("scale", P), ("M", I), ("M_pad", I), ("K", I),
                 ("lda", I), ("ldb", I), ("ldres", I), ("ldout", I), ("tp_recv", P), ("tp_flags", P),
                 ("tp_seq_base", P), ("err", P), ("tp_nranks", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I),
-                ("tp_nt", I), ("tp_tiles_n", I), ("m_live", P), ("qfmt", I), ("had_sign", P)]
+                ("tp_nt", I), ("tp_tiles_n", I), ("m_live", P), ("qfmt", I), ("had_sign", P),
+                ("sp_q", P * MAX_RANKS), ("sp_scale", P * MAX_RANKS), ("sp_flags", P * MAX_RANKS), ("sp_counter", P),
+                ("sp_rpr", I), ("sp_rank", I)]
 
 
 class GdnConvParams(C.Structure):

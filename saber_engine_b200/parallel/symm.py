@@ -23,6 +23,17 @@ import torch
 from ..ops import native as N
 
 
+class _Raw:
+    """A raw device allocation seen through the CUDA array interface (zero-copy torch view)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+def _raw_tensor(ptr: int, nbytes: int, device) -> torch.Tensor:
+    return torch.as_tensor(_Raw(ptr, nbytes), device=device)
+
+
 def _align(x: int, a: int = 256) -> int:
     return (x + a - 1) // a * a
 
@@ -38,6 +49,11 @@ class HeapLayout:
     ar_flags: int = 0
     pick_win: int = 0
     pick_flags: int = 0
+    ag_q: int = 0          # all-gathered quantised activations [hidden / 128][rows_pad][128] bytes
+    ag_scale: int = 0      # [rows_pad] fp32
+    ag_flags: int = 0      # [2 parity][64 row tiles] arrival flags
+    ag_counter: int = 0    # [64 row tiles] rows-done counters (local use)
+    rows_pad: int = 0
     total: int = 0
 
     @staticmethod
@@ -55,14 +71,20 @@ class HeapLayout:
         L.ar_flags = take(2 * nranks * N.AR_BLOCKS * 4)
         L.pick_win = take(2 * nranks * rows_max * 8)
         L.pick_flags = take(2 * nranks * 4)
+        L.rows_pad = (rows_max + 127) // 128 * 128
+        L.ag_q = take(L.rows_pad * max(128, (hidden + 127) // 128 * 128))
+        L.ag_scale = take(L.rows_pad * 4)
+        L.ag_flags = take(2 * 64 * 4)
+        L.ag_counter = take(64 * 4)
         L.total = off
         L.ar_max_elems = ar_max_elems
         return L
 
     def digest(self) -> str:
         d = {k: getattr(self, k) for k in ("nranks", "rows_max", "hidden", "gemm_recv", "gemm_flags", "ar_recv",
-                                            "ar_flags", "pick_win", "pick_flags", "total")}
-        d["protocol"] = "saber-b200-symm/1"
+                                            "ar_flags", "pick_win", "pick_flags", "ag_q", "ag_scale", "ag_flags",
+                                            "ag_counter", "total")}
+        d["protocol"] = "saber-b200-symm/2"
         return hashlib.sha256(json.dumps(d, sort_keys=True).encode()).hexdigest()
 
 
@@ -145,6 +167,40 @@ class SymmetricComm:
         p.tp_seq_base = self.seq_base.data_ptr()
         p.tp_nranks, p.tp_rank, p.tp_site = self.nranks, self.rank, site
         p.tp_rows, p.tp_ld = lay.rows_max, lay.hidden
+
+    # ---- sequence-parallel building blocks (reduce-scatter epilogue, all-gather by peer stores)
+    def heap_qact(self, M: int, K: int):
+        """The all-gather target as a QuantAct: tiled int8 rows + scales living in THIS rank's heap at
+        the same offset on every rank, so that owners can store their rows into every rank's copy."""
+        from ..ops.functional import QuantAct
+        lay = self.layout
+        assert K <= max(128, (lay.hidden + 127) // 128 * 128) and M <= lay.rows_max and K % 128 == 0
+        q = _raw_tensor(self.own + lay.ag_q, (K // 128) * lay.rows_pad * 128, self.device).view(torch.int8)
+        sc = _raw_tensor(self.own + lay.ag_scale, lay.rows_pad * 4, self.device).view(torch.float32)
+        return QuantAct(q.reshape(K // 128, lay.rows_pad, 128), sc, M, K)
+
+    def gemm_rs(self, p: N.GemmI8Params, site: int, rows_per_rank: int) -> None:
+        """Row-parallel GEMM whose epilogue reduce-scatters: a row's partial goes to its owner only."""
+        self.gemm_tp(p, site)
+        p.tp_rpr = rows_per_rank
+
+    def gemm_ag(self, p: N.GemmI8Params, site: int) -> None:
+        """A GEMM whose token rows arrive by all-gather: wait per 128-row tile for the owners' flags."""
+        p.ag_flags = self.own + self.layout.ag_flags
+        p.ag_seq_base = self.seq_base.data_ptr()
+        p.ag_site = site
+        p.err = self.err.data_ptr()
+
+    def row_sp(self, p: N.RowOpParams, site: int, nt: int, tiles_n: int, rows_per_rank: int) -> None:
+        """ADD_RMS on the rows this rank owns; the quantised rows go to every rank's heap_qact."""
+        self.row_tp(p, site, nt, tiles_n)
+        lay = self.layout
+        for r in range(self.nranks):
+            p.sp_q[r] = self.bases[r] + lay.ag_q
+            p.sp_scale[r] = self.bases[r] + lay.ag_scale
+            p.sp_flags[r] = self.bases[r] + lay.ag_flags
+        p.sp_counter = self.own + lay.ag_counter
+        p.sp_rpr, p.sp_rank = rows_per_rank, self.rank
 
     def row_tp(self, p: N.RowOpParams, site: int, nt: int, tiles_n: int) -> None:
         """Make an ADD_RMS producer the consumer of the GEMM pushed at `site`."""

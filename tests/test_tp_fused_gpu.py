@@ -87,3 +87,96 @@ def test_consumer_wait_runs_out_cleanly_when_a_rank_never_pushes():
         g.check()
     assert float((torch.ones(4, device=DEV) * 2).sum()) == 8.0      # the context still answers
     group[0].close()
+
+
+@pytest.mark.parametrize("nranks,M", [(2, 256), (4, 512)])
+def test_sequence_parallel_reduce_scatter_norm_allgather_gemm(nranks, M):
+    """The sequence-parallel chain on ONE GPU with emulated ranks, phase by phase:
+    (1) every rank's row-parallel GEMM pushes each row's partial to the row's OWNER only,
+    (2) every rank's add-norm-quant handles the rows it owns and stores the quantised rows into EVERY
+        rank's buffer, raising one arrival flag per 128-row tile,
+    (3) every rank's next GEMM waits for those flags before it loads its token tiles.
+    Every producer runs before its consumers, so no launch waits for a later one."""
+    torch.manual_seed(20 + nranks)
+    H, K = 512, 256 * nranks
+    Kr, rpr = K // nranks, M // nranks
+    group = SymmetricComm.local_group(nranks, DEV, max_elems=M * H, rows_max=M, hidden=H)
+    for g in group:
+        g._local = True
+    w = torch.randn(H, K) * 0.02
+    w2 = torch.randn(384, H) * 0.02
+    x = torch.randn(M, K)
+    res = torch.randn(M, H).to(torch.bfloat16)
+    nw = torch.randn(H) * 0.1
+    sc = F.scratch(DEV)
+    wq_full, ws_full = L.quantize_weight_rows(w, 4)
+    partial_ref, keep = [], []
+    for r, g in enumerate(group):                          # phase 1: reduce-scatter epilogues
+        aq, asc = L.quantize_act_rows(x[:, r * Kr:(r + 1) * Kr])
+        partial_ref.append(R.gemm_i8(wq_full[:, r * Kr:(r + 1) * Kr], ws_full, aq, asc).float())
+        qw = F.QuantWeight.from_int(wq_full[:, r * Kr:(r + 1) * Kr].contiguous(), ws_full, 4, DEV)
+        m_pad = L.padded_rows(M)
+        qa = F.QuantAct(L.tile_act_int8(aq, m_pad).to(DEV), torch.cat([asc, torch.zeros(m_pad - M)]).to(DEV), M, Kr)
+        dummy = torch.zeros(M, H, dtype=torch.bfloat16, device=DEV)
+        p = F.gemm_params(qw, qa, dummy, sc, splits=1)
+        g.gemm_rs(p, 0, rpr)
+        N.check(N.lib().saber_gemm_i8_launch(C.byref(p), 0, N.stream_handle()), "gemm rs")
+        keep.append((qw, qa, dummy))
+    torch.cuda.synchronize()
+    sc.check()
+    ref_sum = R.bf16_round(sum(partial_ref))
+    res_ref, n_ref = R.add_rms(ref_sum, res, nw)
+    res_shards = []
+    for r, g in enumerate(group):                          # phase 2: owners norm + quantise + all-gather
+        res_d = res.to(DEV).clone()
+        qa_heap = g.heap_qact(M, H)
+        p = F.row_params(M, H, a=None, res=res_d, w=nw.to(DEV), w_offset=1.0, qa=qa_heap)
+        g.row_sp(p, 0, L.token_tile(M), H // 256, rpr)
+        N.check(N.lib().saber_row_producer_launch(N.ROW_ADD_RMS, C.byref(p), N.stream_handle()), "sp consumer")
+        res_shards.append(res_d)
+    torch.cuda.synchronize()
+    for r, g in enumerate(group):
+        g.check()
+        own = slice(r * rpr, (r + 1) * rpr)
+        assert torch.allclose(res_shards[r][own].float().cpu(), res_ref[own].float(), atol=3e-2, rtol=2e-2)
+        if r + 1 < nranks:                                  # rows of other ranks are not touched here
+            other = slice((r + 1) * rpr, (r + 2) * rpr)
+            assert torch.equal(res_shards[r][other].cpu(), res[other])
+    aq2, asc2 = L.quantize_act_rows(n_ref)
+    qw2 = F.QuantWeight.from_float(w2, 4, DEV)
+    want = R.gemm_i8(*L.quantize_weight_rows(w2, 4), aq2, asc2).float()
+    outs = []
+    for r, g in enumerate(group):                          # phase 3: the next GEMM waits on the arrival flags
+        qa_heap = g.heap_qact(M, H)
+        assert torch.allclose(qa_heap.scale[:M].cpu(), asc2, rtol=2e-2, atol=1e-6)
+        out = torch.zeros(M, 384, dtype=torch.bfloat16, device=DEV)
+        p = F.gemm_params(qw2, qa_heap, out, sc, splits=1)
+        g.gemm_ag(p, 0)
+        N.check(N.lib().saber_gemm_i8_launch(C.byref(p), 0, N.stream_handle()), "gemm ag")
+        outs.append(out)
+    torch.cuda.synchronize()
+    sc.check()
+    for r, g in enumerate(group):
+        g.check()
+        err = (outs[r].float().cpu() - want).abs().max().item()
+        assert err <= 0.05 * want.abs().max().item() + 1e-3, (r, err)
+        assert torch.equal(outs[r], outs[0])                # every rank holds the same gathered rows
+    group[0].close()
+
+
+def test_allgather_wait_runs_out_cleanly_when_no_owner_pushes():
+    """The fused all-gather wait is bounded: a flag nothing sets ends in a status word, not a hang."""
+    group = SymmetricComm.local_group(2, DEV, max_elems=128 * 256, rows_max=128, hidden=256)
+    g = group[0]
+    g._local = True
+    qw = F.QuantWeight.from_float(torch.randn(256, 256) * 0.02, 4, DEV)
+    qa = g.heap_qact(16, 256)
+    out = torch.zeros(16, 256, dtype=torch.bfloat16, device=DEV)
+    p = F.gemm_params(qw, qa, out, F.scratch(DEV), splits=1)
+    g.gemm_ag(p, 5)
+    N.check(N.lib().saber_gemm_i8_launch(C.byref(p), 0, N.stream_handle()), "gemm ag")
+    torch.cuda.synchronize()
+    with pytest.raises(N.NativeError, match="wait_peer"):
+        g.check()
+    assert float((torch.ones(4, device=DEV) * 2).sum()) == 8.0
+    group[0].close()
