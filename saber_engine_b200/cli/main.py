@@ -115,6 +115,9 @@ def build_engine(a):
     from ..utils.host_trace import HostTrace, StepLedger
     sched.trace = HostTrace(bool(getattr(a, "engine_host_trace", False)))
     sched.park_tier = ParkTier(getattr(a, "park_ram_mib", 8192) << 20, getattr(a, "park_dir", None))
+    if getattr(a, "prompt_cache_dir", None):
+        from ..sched.prompt_store import PromptStore
+        sched.prompt_store = PromptStore(a.prompt_cache_dir, page=ex.page_tokens)
     ledger = StepLedger(getattr(a, "step_trace", None))
     sched.step_ledger = ledger
     fail = getattr(a, "fail_rank_after_steps", None)
@@ -271,6 +274,7 @@ def make_parser() -> argparse.ArgumentParser:
                    help="text file whose content is prefilled at boot so its pages are in the prefix cache")
     e.add_argument("--step-trace", metavar="PATH", help="append one JSON line per engine step")
     e.add_argument("--park-dir", help="drive tier of parked sessions")
+    e.add_argument("--prompt-cache-dir", help="keep prefilled prefixes on this drive across restarts")
     e.add_argument("--park-ram-mib", type=int, default=8192)
     e.add_argument("--fatal-watchdog-s", type=float, default=10.0)
     e.add_argument("--fail-rank-after-steps", default=None, metavar="R:N", help=argparse.SUPPRESS)

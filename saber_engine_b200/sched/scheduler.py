@@ -103,6 +103,7 @@ class Scheduler:
         self.trace = HostTrace(False)       # named host phases per step; off unless asked for
         self.park_tier = ParkTier()
         self.parked: dict = {}              # key -> Sequence whose device state lives in the park tier
+        self.prompt_store = None            # optional sched.prompt_store.PromptStore (prefixes that survive restarts)
 
     # ------------------------------------------------------------------------------ Engine trait
     def submit(self, req: EngineRequest) -> Submission:
@@ -174,9 +175,17 @@ class Scheduler:
             s.blocks, s.slot = self.arenas.admit(total, shared)
             s.t_admit = time.monotonic()
             start = 0
+            stored = None
+            if not hit and self.prompt_store is not None and hasattr(self.ex, "import_session"):
+                stored = self.prompt_store.get(s.prompt)     # verified before anything reaches the device
             if hit:
                 self.ex.restore_state(s.slot, hit.snapshot)
                 start = hit.n_tokens
+                s.cached_tokens = start
+            elif stored is not None:
+                self.ex.reset_slot(s.slot)
+                self.ex.import_session(s.slot, s.blocks, stored.header, stored.payload)
+                start = stored.header["n_tokens"]
                 s.cached_tokens = start
             else:
                 self.ex.reset_slot(s.slot)
@@ -302,6 +311,12 @@ class Scheduler:
             if s.pos in s.cut_points:
                 snap = self.ex.snapshot_state(s.slot)
                 self.prefix.insert(s.prompt, s.pos, s.blocks, snap, self.ex.snapshot_bytes())
+                st = self.prompt_store
+                if st is not None and hasattr(self.ex, "export_session") and not st.has(s.prompt, s.pos):
+                    from .park import ParkImage
+                    header, payload = self.ex.export_session(s.slot, s.blocks, s.pos)
+                    header["n_tokens"] = s.pos
+                    st.put(s.prompt, s.pos, ParkImage.build(header, payload))
             if s.pos == len(s.prompt):
                 tok = self._choose(s, out, 0, out.tokens[0] if out.tokens else 0)
                 s.drafts = list(out.drafts)

@@ -153,3 +153,40 @@ def test_rank_watch_sees_a_fake_rank_exit_86():
         evs.append(ev)
     assert evs[-1].finished and "injected" in evs[-1].error
     fatal.reset_for_tests()
+
+
+def test_prompt_store_survives_restart_and_obeys_the_crash_law(tmp_path):
+    from saber_engine_b200.sched.prompt_store import PromptStore
+    system = list(range(1, 700))
+    tail = [9, 8, 7]
+
+    def engine():
+        ex = NullExecutor(vocab=997, max_seqs=2)
+        sch = Scheduler(ex, SchedulerConfig(max_seqs=2, max_ctx=8192, prefix_cache_min_tokens=64, prefix_cache_interval=256))
+        sch.prompt_store = PromptStore(str(tmp_path), min_tokens=64)
+        return ex, sch
+
+    ex1, s1 = engine()
+    sub = s1.submit(EngineRequest(system + tail, SamplingParams(max_tokens=5, ignore_eos=True)))
+    s1.run_until_idle()
+    want, done = _drain(sub)
+    assert done and want == reference_generation(system + tail, 5, 997)
+    assert s1.prompt_store.counters["puts"] >= 1
+    # a new process: empty prefix cache, the prefix comes back from the drive
+    ex2, s2 = engine()
+    assert len(s2.prompt_store.records) == s1.prompt_store.counters["puts"]
+    sub2 = s2.submit(EngineRequest(system + [5, 5, 5], SamplingParams(max_tokens=5, ignore_eos=True)))
+    s2.run_until_idle()
+    got, done = _drain(sub2)
+    assert done and got == reference_generation(system + [5, 5, 5], 5, 997)
+    assert s2.prompt_store.counters["hits"] == 1
+    prefilled = sum(rows for kind, _, rows in ex2.launch_log if kind == "prefill")
+    assert prefilled < len(system) // 2                    # most of the prompt was not prefilled again
+    # crash law: a record whose file is missing or truncated is dropped at boot, a torn index line too
+    files = sorted(tmp_path.glob("*.prompt"))
+    files[0].write_bytes(files[0].read_bytes()[:-7])
+    with open(tmp_path / "index.jsonl", "a") as fh:
+        fh.write('{"rec": {"key": "zz", "n_to')
+    st = PromptStore(str(tmp_path), min_tokens=64)
+    assert st.counters["dropped_at_boot"] >= 2 and files[0].stem not in st.records
+    assert not any(p.name.startswith(".") for p in tmp_path.iterdir())      # no temporary files left behind
