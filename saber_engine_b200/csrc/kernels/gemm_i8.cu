@@ -60,7 +60,7 @@ constexpr int kUBufs = 3;                // W4: widened int8 operand buffers (tr
 // start-up latency (cold weights: 3-4 us to the first MMA) and epilogue.
 template <bool kLean>
 __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int stages) {
-  constexpr int nub = kLean ? 2 : kUBufs;     // operand buffers in use
+  const int nub = (kLean || p.mtiles == 2) ? 2 : kUBufs;     // operand buffers in use
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bars[2 * kMaxStages + 2 * kUBufs + 1];
   __shared__ uint32_t tmem_base_s;
@@ -90,7 +90,9 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
   const int kb1 = min(KB, kb0 + kb_per);
   const int nkb = kb1 - kb0;  // host guarantees >= 1
   // grouped mode: this CTA's token rows and expert come from the tile table
-  int m0 = tile_m * p.nt;
+  // token tiles per CTA: 2 (prefill) = every widened weight block feeds two MMAs into two accumulators
+  const int mt2 = (!kLean && p.mtiles == 2) ? 2 : 1;
+  int m0 = tile_m * p.nt * mt2;
   int rows_here = -1;
   const uint8_t* w_base = p.w;
   const float* w_scale_base = p.w_scale;
@@ -107,7 +109,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
   // weight formats: 0 = int8 tiles, 1 = packed int4, 2 = MXFP4 (packed e2m1 + 1 KiB of block shifts)
   const bool mx = p.w4 == 2;
   const uint32_t wbytes = mx ? 17408u : (p.w4 ? 16384u : 32768u);
-  const uint32_t abytes = static_cast<uint32_t>(p.nt) * 128u;
+  const uint32_t abytes = static_cast<uint32_t>(p.nt) * 128u * static_cast<uint32_t>(mt2);
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   // token ring | W4: three int8 operand buffers | weight ring (W4: packed 16 KiB stages, W8: 32 KiB)
@@ -119,7 +121,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
   const uint32_t bar_ready = smem_u32(&bars[2 * kMaxStages]);           // kUBufs
   const uint32_t bar_ufree = smem_u32(&bars[2 * kMaxStages + kUBufs]);  // kUBufs
   const uint32_t bar_acc = smem_u32(&bars[2 * kMaxStages + 2 * kUBufs]);
-  constexpr uint32_t kTmemCols = 256;
+  const uint32_t kTmemCols = (!kLean && p.mtiles == 2) ? 512u : 256u;
   constexpr int kMaxSplits = 8;   // split-K factor the reduction is unrolled for
 
   if (threadIdx.x == 0) {
@@ -171,11 +173,13 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         // first token-tile copy of this CTA
         const uint32_t seq = *p.ag_seq_base + static_cast<uint32_t>(p.ag_site) + 1u;
         const uint32_t* flag = p.ag_flags + (seq & 1u) * 64u + static_cast<uint32_t>(m0 >> 7);
+        const int last_tile = min((p.M - 1) >> 7, (m0 + p.nt * mt2 - 1) >> 7) - (m0 >> 7);   // 0, or 1 with two token tiles
         const long long t0 = clock64();
         for (uint32_t polls = 0;; ++polls) {
-          uint32_t v;
+          uint32_t v, v2;
           asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-          if (static_cast<int32_t>(v - seq) >= 0) break;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v2) : "l"(flag + last_tile) : "memory");
+          if (static_cast<int32_t>(v - seq) >= 0 && static_cast<int32_t>(v2 - seq) >= 0) break;
           // (half the limit of the pipeline's own waits, so that this cause is the one recorded)
           if ((polls & 1023u) == 1023u && clock64() - t0 > kWaitLimitCycles / 2) {
             atomicCAS(p.err, 0u, static_cast<uint32_t>(kErrWaitPeer));
@@ -230,16 +234,20 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         const uint64_t a_desc = desc_hi | static_cast<uint64_t>((a_addr & 0x3FFFFu) >> 4);
         const uint64_t b_desc = desc_hi | static_cast<uint64_t>((w_addr & 0x3FFFFu) >> 4);
         // 32 int8 = 32 bytes along K inside the 128-byte swizzle row: +2 in 16-byte units
-        if (mx) {   // fp8 x fp8 -> fp32 (the weights were folded to e4m3 by the transform warps)
-          mma_f8_ss(tmem_d, a_desc, b_desc, idesc, it != 0 ? 1u : 0u);
-          mma_f8_ss(tmem_d, a_desc + 2, b_desc + 2, idesc, 1u);
-          mma_f8_ss(tmem_d, a_desc + 4, b_desc + 4, idesc, 1u);
-          mma_f8_ss(tmem_d, a_desc + 6, b_desc + 6, idesc, 1u);
-        } else {
-          mma_i8_ss(tmem_d, a_desc, b_desc, idesc, it != 0 ? 1u : 0u);
-          mma_i8_ss(tmem_d, a_desc + 2, b_desc + 2, idesc, 1u);
-          mma_i8_ss(tmem_d, a_desc + 4, b_desc + 4, idesc, 1u);
-          mma_i8_ss(tmem_d, a_desc + 6, b_desc + 6, idesc, 1u);
+        for (int j2 = 0; j2 < mt2; ++j2) {
+          const uint32_t dj = tmem_d + static_cast<uint32_t>(j2) * 256u;             // accumulator of token tile j2
+          const uint64_t aj = a_desc + static_cast<uint64_t>(j2) * (static_cast<uint64_t>(p.nt) * 128u >> 4);
+          if (mx) {   // fp8 x fp8 -> fp32 (the weights were folded to e4m3 by the transform warps)
+            mma_f8_ss(dj, aj, b_desc, idesc, it != 0 ? 1u : 0u);
+            mma_f8_ss(dj, aj + 2, b_desc + 2, idesc, 1u);
+            mma_f8_ss(dj, aj + 4, b_desc + 4, idesc, 1u);
+            mma_f8_ss(dj, aj + 6, b_desc + 6, idesc, 1u);
+          } else {
+            mma_i8_ss(dj, aj, b_desc, idesc, it != 0 ? 1u : 0u);
+            mma_i8_ss(dj, aj + 2, b_desc + 2, idesc, 1u);
+            mma_i8_ss(dj, aj + 4, b_desc + 4, idesc, 1u);
+            mma_i8_ss(dj, aj + 6, b_desc + 6, idesc, 1u);
+          }
         }
         mma_commit(bar_empty + 8 * s);
         if (p.w4) {
@@ -369,7 +377,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         tp_seq = *p.tp_seq_base + static_cast<uint32_t>(p.tp_site) + 1u;
         tp_par = tp_seq & 1u;
       }
-      const int tp_owner = (!kLean && p.tp_rpr > 0) ? m0 / p.tp_rpr : -1;   // reduce-scatter: the one destination
+      int tp_owner = (!kLean && p.tp_rpr > 0) ? m0 / p.tp_rpr : -1;   // reduce-scatter: the one destination
       auto tp_push16 = [&](int mm, int nn, const uint4& v) {
         const size_t off = ((static_cast<size_t>(tp_par) * p.tp_nranks + p.tp_rank) * p.tp_rows + mm) * p.tp_ld + nn;
         if (tp_owner >= 0) {
@@ -394,13 +402,21 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         // now -- with its 16-byte chunks XOR-swizzled by the row, then every warp writes whole
         // rows: 512 contiguous bytes per store instruction, to local memory or to every rank.
         const uint32_t stage_s = p.w4 ? u_smem : w_smem;     // >= 64 KiB in either mode
-        if (warp_live) {
-          const float asc = live ? p.a_scale[m] : 0.f;
+        for (int j2 = 0; j2 < mt2; ++j2) {
+        const int mb = m0 + j2 * p.nt;             // first row of this accumulator's token tile
+        const int mtj = rows_here >= 0 ? rows_here : min(p.nt, p.M - mb);
+        if (mtj <= 0) break;                       // (uniform) the second tile of a ragged pair is empty
+        const bool livej = row < mtj, warp_livej = q4 * 32 < mtj;
+        const uint32_t tl = t_lane + static_cast<uint32_t>(j2) * 256u;
+        if (!kLean && p.tp_rpr > 0) tp_owner = mb / p.tp_rpr;
+        if (j2) named_bar_sync(1, 128);            // the staging buffer is free again
+        if (warp_livej) {
+          const float asc = livej ? p.a_scale[mb + row] : 0.f;
           for (int c = 0; c < ncols; c += 32) {
             uint32_t r[32];
-            tmem_ld32(t_lane + c, r);
+            tmem_ld32(tl + c, r);
             tmem_ld_wait();
-            if (live) {
+            if (livej) {
               uint32_t pk[16];
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
@@ -425,7 +441,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
           const int col = lane * 8;                   // this lane's 8 output features of the row
           const bool col_ok = n0 + col < p.N;         // (N is a multiple of 8 whenever ldo is)
           const bool full = n0 + col + 8 <= p.N;
-          for (int rw = wq; rw < mt; rw += 4) {
+          for (int rw = wq; rw < mtj; rw += 4) {
             uint4 v;
             const uint32_t chunk = static_cast<uint32_t>(lane) ^ (static_cast<uint32_t>(rw) & 31u);
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -433,18 +449,19 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
                          : "r"(stage_s + rw * 512 + (chunk << 4)));
             if (!col_ok || col >= ncols) continue;
             if (tp) {
-              tp_push16(m0 + rw, n0 + col, v);
+              tp_push16(mb + rw, n0 + col, v);
             } else if (full) {
-              *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(m0 + rw) * p.ldo + n0 + col) = v;
+              *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(mb + rw) * p.ldo + n0 + col) = v;
             } else {
               const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(&v);
-              __nv_bfloat16* o = p.out + static_cast<size_t>(m0 + rw) * p.ldo + n0 + col;
+              __nv_bfloat16* o = p.out + static_cast<size_t>(mb + rw) * p.ldo + n0 + col;
               for (int j = 0; j < 8; ++j)
                 if (n0 + col + j < p.N) o[j] = pb[j];
             }
           }
         }
-        if (tp) tp_signal(tile_m * gridDim.x + tile_n);
+        if (tp) tp_signal((tile_m * mt2 + j2) * gridDim.x + tile_n);
+        }
       } else if constexpr (!kLean) {
         // each split writes its own partial tile; inside a (split, tile) block the 16-byte group of
         // four columns c4 of row r sits at (c4 * 128 + r) * 16 bytes, so the 32 lanes of a warp
@@ -691,6 +708,20 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
     const int lean_smem = 2 * (16384 + p->nt * 128) + 2 * 32768 + 1024;
     if (lean_smem <= 112 * 1024)
       return static_cast<int>(saber::launch(gemm_i8_lean_kernel, grid, dim3(kGemmThreads), lean_smem, stream, 2, q, 2));
+  }
+  // long row runs of 4-bit weights: two token tiles per CTA (pairs must be whole inside M_pad)
+  q.mtiles = 1;
+  if (p->mtiles >= 0 && !p->group_tiles && p->splits == 1 && p->w4 != 0 && p->nt == 128 && p->M > 128 &&
+      (p->M_pad / 128) % 2 == 0 && p->ag_flags == nullptr) {
+    const int wb = p->w4 == 2 ? 17408 : 16384;
+    int st2 = 3;
+    while (st2 > 2 && st2 * (wb + 2 * 16384) + 2 * 32768 + 1024 > kSmemLimit) --st2;
+    const int smem2 = st2 * (wb + 2 * 16384) + 2 * 32768 + 1024;
+    if (smem2 <= kSmemLimit) {
+      q.mtiles = 2;
+      dim3 grid2(p->N_pad / 256, (p->M + 255) / 256, 1);
+      return static_cast<int>(saber::launch(gemm_i8_kernel, grid2, dim3(kGemmThreads), smem2, stream, 2, q, st2));
+    }
   }
   return static_cast<int>(saber::launch(gemm_i8_kernel, grid, dim3(kGemmThreads), smem, stream, (q.coop != 0 ? 1 : 0) | 2, q, stages));
 }

@@ -43,7 +43,7 @@ class GemmI8Params(C.Structure):
                 ("counters", P), ("err", P), ("M", I), ("M_pad", I), ("N", I), ("N_pad", I),
                 ("K", I), ("nt", I), ("splits", I), ("w4", I), ("ldo", I), ("dbg_mma", I), ("tp_recv", P * 8), ("tp_flags", P * 8), ("tp_seq_base", P),
                 ("tp_nranks", I), ("tp_rank", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I), ("tp_rpr", I), ("ag_flags", P), ("ag_seq_base", P), ("ag_site", I),
-                ("group_tiles", P), ("group_ntiles", P), ("group_w_stride", U64), ("coop", I), ("dbg", P)]
+                ("group_tiles", P), ("group_ntiles", P), ("group_w_stride", U64), ("coop", I), ("mtiles", I), ("dbg", P)]
 
 
 class RowOpParams(C.Structure):

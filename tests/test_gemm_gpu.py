@@ -62,3 +62,11 @@ def test_gemm_auto_splits_decode_shape():
 def test_gemm_prefill_tiles():
     _case(300, 512, 1024, 4, splits=1)    # nt = 128, three token tiles, last one ragged
     _case(72, 256, 1024, 8, splits=2)     # nt = 80
+
+
+def test_gemm_two_token_tiles_per_cta():
+    """Long row runs of 4-bit weights: one widened weight block feeds two 128-row MMAs."""
+    _case(512, 512, 1024, 4, splits=1, seed=11)        # two pairs, whole
+    _case(400, 300 + 4, 2048, 4, splits=1, seed=12)    # last pair: second tile ragged (16 live rows), ragged N
+    _case(700, 256, 512, 4, splits=1, seed=13)         # M_pad = 768: three pairs, the last one half empty
+    _case(512, 512, 1024, 8, splits=1, seed=14)        # int8 weights keep one tile per CTA

@@ -43,3 +43,8 @@ def test_mxfp4_split_k_and_token_tiles():
     assert torch.equal(a, b)                                    # fixed split order: same bits every launch
     _case(300, 512, 1024, 1, seed=3)
     _case(72, 5120, 2048, 2, seed=4)
+
+
+def test_mxfp4_two_token_tiles_per_cta():
+    _case(512, 512, 1024, 1, seed=5)
+    _case(900, 256, 2048, 1, seed=6)
