@@ -54,6 +54,13 @@ constexpr uint32_t kTileBytes = 32768;   // int8 image of one weight tile (256 x
 constexpr int kUBufs = 3;                // W4: widened int8 operand buffers (transform, MMA and
                                          // the buffer-free round trip overlap with three)
 
+// GELU of a rounded linear output: tanh form (x * 0.5 * (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))) or erf form.
+__device__ __forceinline__ float gelu_f(float x, bool erf_form) {
+  if (erf_form) return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.f + tanhf(u));
+}
+
 // kLean: the grouped (mixture-of-experts) instantiation -- no split-K and no tensor-parallel code,
 // two operand buffers instead of three, at most 102 registers -- so that TWO CTAs share an SM: an
 // expert tile is only 16 k-blocks long, and the second CTA's main loop hides the first one's
@@ -67,6 +74,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
   __shared__ uint32_t is_last_s;
   __shared__ uint32_t abort_s;
   __shared__ float w_scale_s[256];
+  __shared__ float bias_s[256];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -107,15 +115,18 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
   }
   const int n0 = tile_n * 256;
   // weight formats: 0 = int8 tiles, 1 = packed int4, 2 = MXFP4 (packed e2m1 + 1 KiB of block shifts)
+  // 3 = bf16 x bf16: both operands pass through like int8 tiles (K counted in bytes), fp32 accumulators
   const bool mx = p.w4 == 2;
-  const uint32_t wbytes = mx ? 17408u : (p.w4 ? 16384u : 32768u);
+  const bool bf = p.w4 == 3;
+  const bool widen = p.w4 == 1 || mx;
+  const uint32_t wbytes = mx ? 17408u : (widen ? 16384u : 32768u);
   const uint32_t abytes = static_cast<uint32_t>(p.nt) * 128u * static_cast<uint32_t>(mt2);
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   // token ring | W4: three int8 operand buffers | weight ring (W4: packed 16 KiB stages, W8: 32 KiB)
   const uint32_t a_smem = smem_base;
   const uint32_t u_smem = smem_base + static_cast<uint32_t>(stages) * abytes;
-  const uint32_t w_smem = u_smem + (p.w4 ? nub * kTileBytes : 0u);
+  const uint32_t w_smem = u_smem + (widen ? nub * kTileBytes : 0u);
   const uint32_t bar_full = smem_u32(&bars[0]);
   const uint32_t bar_empty = smem_u32(&bars[kMaxStages]);
   const uint32_t bar_ready = smem_u32(&bars[2 * kMaxStages]);           // kUBufs
@@ -214,6 +225,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
     if (lane == 0) {
       // M = 128 token rows (only the first nt are real), N = 256 output features
       const uint32_t idesc = mx ? make_idesc(kCFmtF32, kFmtE4M3, kFmtE4M3, 128, 256)
+                           : bf ? make_idesc(kCFmtF32, kFmtBF16, kFmtBF16, 128, 256)
                                 : make_idesc(kCFmtS32, kFmtS8, kFmtS8, 128, 256);
       const uint64_t desc_hi = make_desc_k128(0);  // everything but the start address
       uint32_t a_addr = a_smem;
@@ -222,7 +234,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
       bool ok = true;
       for (int it = 0; it < nkb; ++it) {
         uint32_t w_addr;
-        if (p.w4) {
+        if (widen) {
           if (!mbar_wait(bar_ready + 8 * u, uph, p.err, kErrWaitReady)) { ok = false; break; }
           w_addr = u_smem + u * kTileBytes;
         } else {
@@ -242,6 +254,11 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
             mma_f8_ss(dj, aj + 2, b_desc + 2, idesc, 1u);
             mma_f8_ss(dj, aj + 4, b_desc + 4, idesc, 1u);
             mma_f8_ss(dj, aj + 6, b_desc + 6, idesc, 1u);
+          } else if (bf) {   // 16 bf16 = 32 bytes along K per instruction: the same +2 steps
+            mma_f16_ss(dj, aj, b_desc, idesc, it != 0 ? 1u : 0u);
+            mma_f16_ss(dj, aj + 2, b_desc + 2, idesc, 1u);
+            mma_f16_ss(dj, aj + 4, b_desc + 4, idesc, 1u);
+            mma_f16_ss(dj, aj + 6, b_desc + 6, idesc, 1u);
           } else {
             mma_i8_ss(dj, aj, b_desc, idesc, it != 0 ? 1u : 0u);
             mma_i8_ss(dj, aj + 2, b_desc + 2, idesc, 1u);
@@ -250,7 +267,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
           }
         }
         mma_commit(bar_empty + 8 * s);
-        if (p.w4) {
+        if (widen) {
           mma_commit(bar_ufree + 8 * u);
           if (++u == nub) { u = 0; uph ^= 1u; }
         }
@@ -268,9 +285,12 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
     const int q4 = warp & 3;                     // TMEM lane quarter this warp may access
     bool ok = true;
     if (tgroup == 0) {  // epilogue warps stage the per-feature scales while the pipeline fills
-      for (int j = tid_t; j < 256; j += 128) w_scale_s[j] = (n0 + j < p.N) ? w_scale_base[n0 + j] : 0.f;
+      for (int j = tid_t; j < 256; j += 128) {
+        w_scale_s[j] = (n0 + j < p.N) ? (p.w_scale ? w_scale_base[n0 + j] : 1.f) : 0.f;
+        bias_s[j] = (p.bias && n0 + j < p.N) ? p.bias[n0 + j] : 0.f;
+      }
     }
-    if (p.w4) {
+    if (widen) {
       int s = 0, u = 0;
       uint32_t ph = 0, ufree_ph = 1;
       for (int it = 0; it < nkb; ++it) {
@@ -367,7 +387,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
       const int ncols = min(256, p.N_pad - n0);
       // accumulator words are int32 (integer formats) or fp32 bits (MXFP4)
       auto acc_f = [&](uint32_t raw) -> float {
-        return mx ? __uint_as_float(raw) : static_cast<float>(static_cast<int32_t>(raw));
+        return (mx || bf) ? __uint_as_float(raw) : static_cast<float>(static_cast<int32_t>(raw));
       };
       // tensor-parallel mode: a finished 16-byte group of outputs goes to every rank's receive
       // region (slot = parity of the call's sequence number, source = this rank)
@@ -401,7 +421,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         // So the bf16 tile is first staged in shared memory -- the operand buffers are idle by
         // now -- with its 16-byte chunks XOR-swizzled by the row, then every warp writes whole
         // rows: 512 contiguous bytes per store instruction, to local memory or to every rank.
-        const uint32_t stage_s = p.w4 ? u_smem : w_smem;     // >= 64 KiB in either mode
+        const uint32_t stage_s = widen ? u_smem : w_smem;     // >= 64 KiB in either mode
         for (int j2 = 0; j2 < mt2; ++j2) {
         const int mb = m0 + j2 * p.nt;             // first row of this accumulator's token tile
         const int mtj = rows_here >= 0 ? rows_here : min(p.nt, p.M - mb);
@@ -411,7 +431,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         if (!kLean && p.tp_rpr > 0) tp_owner = mb / p.tp_rpr;
         if (j2) named_bar_sync(1, 128);            // the staging buffer is free again
         if (warp_livej) {
-          const float asc = livej ? p.a_scale[mb + row] : 0.f;
+          const float asc = livej ? (p.a_scale ? p.a_scale[mb + row] : 1.f) : 0.f;
           for (int c = 0; c < ncols; c += 32) {
             uint32_t r[32];
             tmem_ld32(tl + c, r);
@@ -420,9 +440,13 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
               uint32_t pk[16];
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                const float lo = acc_f(r[2 * j]) * (asc * w_scale_s[c + 2 * j]);
-                const float hi = acc_f(r[2 * j + 1]) * (asc * w_scale_s[c + 2 * j + 1]);
-                const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                const float lo = acc_f(r[2 * j]) * (asc * w_scale_s[c + 2 * j]) + bias_s[c + 2 * j];
+                const float hi = acc_f(r[2 * j + 1]) * (asc * w_scale_s[c + 2 * j + 1]) + bias_s[c + 2 * j + 1];
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                if (p.epi == 1 || p.epi == 2) {   // the activation works on the rounded linear output
+                  const float2 y = __bfloat1622float2(b2);
+                  b2 = __floats2bfloat162_rn(gelu_f(y.x, p.epi == 2), gelu_f(y.y, p.epi == 2));
+                }
                 pk[j] = *reinterpret_cast<const uint32_t*>(&b2);
               }
 #pragma unroll
@@ -448,6 +472,19 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
                          : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                          : "r"(stage_s + rw * 512 + (chunk << 4)));
             if (!col_ok || col >= ncols) continue;
+            if (p.epi == 3 && p.res != nullptr) {     // residual add on the rounded linear output
+              const __nv_bfloat16* rp = p.res + static_cast<size_t>(mb + rw) * p.ldo + n0 + col;
+              __nv_bfloat16* pv = reinterpret_cast<__nv_bfloat16*>(&v);
+              if (full) {
+                const uint4 rv = *reinterpret_cast<const uint4*>(rp);
+                const __nv_bfloat16* pr = reinterpret_cast<const __nv_bfloat16*>(&rv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) pv[j] = __float2bfloat16(__bfloat162float(pv[j]) + __bfloat162float(pr[j]));
+              } else {
+                for (int j = 0; j < 8; ++j)
+                  if (n0 + col + j < p.N) pv[j] = __float2bfloat16(__bfloat162float(pv[j]) + __bfloat162float(rp[j]));
+              }
+            }
             if (tp) {
               tp_push16(mb + rw, n0 + col, v);
             } else if (full) {
@@ -659,7 +696,7 @@ extern "C" int saber_gemm_i8_smem_bytes(int nt, int stages) {
 // operand buffers / weight ring, which lie behind the token ring inside the same allocation.
 extern "C" int saber_gemm_i8_smem_bytes_w(int nt, int stages, int w4) {
   if (w4 == 2) return stages * (17408 + nt * 128) + 3 * 32768 + 1024;
-  return w4 ? stages * (16384 + nt * 128) + 3 * 32768 + 1024 : stages * (32768 + nt * 128) + 1024;
+  return w4 == 1 ? stages * (16384 + nt * 128) + 3 * 32768 + 1024 : stages * (32768 + nt * 128) + 1024;
 }
 
 extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cudaStream_t stream) {
@@ -677,7 +714,10 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
       return static_cast<int>(cudaErrorInvalidValue);
   }
   const int kSmemLimit = 224 * 1024;  // opt-in maximum minus the kernel's static shared memory
-  if (stages <= 0) stages = p->w4 ? 8 : 5;   // one CTA per SM, as deep a ring as fits
+  const bool widen_l = p->w4 == 1 || p->w4 == 2;
+  if (p->w4 < 0 || p->w4 > 3 || (p->w4 == 3 && (p->splits != 1 || p->group_tiles))) return static_cast<int>(cudaErrorInvalidValue);
+  if ((p->bias || p->epi) && p->splits != 1) return static_cast<int>(cudaErrorInvalidValue);
+  if (stages <= 0) stages = widen_l ? 8 : 5;   // one CTA per SM, as deep a ring as fits
   if (stages < 2) stages = 2;
   if (stages > kMaxStages) stages = kMaxStages;
   while (stages > 2 && saber_gemm_i8_smem_bytes_w(p->nt, stages, p->w4) > kSmemLimit) --stages;
@@ -711,7 +751,7 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   }
   // long row runs of 4-bit weights: two token tiles per CTA (pairs must be whole inside M_pad)
   q.mtiles = 1;
-  if (p->mtiles >= 0 && !p->group_tiles && p->splits == 1 && p->w4 != 0 && p->nt == 128 && p->M > 128 &&
+  if (p->mtiles >= 0 && !p->group_tiles && p->splits == 1 && widen_l && p->nt == 128 && p->M > 128 &&
       (p->M_pad / 128) % 2 == 0 && p->ag_flags == nullptr) {
     const int wb = p->w4 == 2 ? 17408 : 16384;
     int st2 = 3;

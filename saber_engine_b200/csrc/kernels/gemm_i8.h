@@ -21,7 +21,7 @@ struct GemmI8Params {
   int M, M_pad, N, N_pad, K;
   int nt;                  // tokens per CTA tile: multiple of 16, <= 256, divides M_pad
   int splits;              // split-K factor (gridDim.z)
-  int w4;                  // 1: packed int4 tiles, 0: int8 tiles
+  int w4;                  // 0: int8 tiles, 1: packed int4, 2: MXFP4, 3: bf16 x bf16 (both operands bf16, K counted in bytes)
   int ldo;                 // row stride of out, in elements
   int dbg_mma;             // debugging only: MMAs issued per k-block (0 = all four)
   // Tensor-parallel fused epilogue (tp_nranks > 1): the finished tile is not written to `out`
@@ -57,6 +57,13 @@ struct GemmI8Params {
   // accumulators, which halves the widening work per output.
   int mtiles;
   unsigned long long* dbg; // optional: 16 global-timer stamps of CTA (0,0,0) (null = off)
+  // bf16 mode (w4 == 3; splits == 1): operands are bf16 in the same byte tiling (a 128-byte row of a
+  // k-block holds 64 values; K is the reduction length in BYTES), fp32 accumulation, scales optional
+  // (null = 1).  y = bf16(acc + bias[n]); then epi 1: gelu_tanh(y), 2: gelu_erf(y), 3: y + res[m][n]
+  // (res has out's row stride and may alias out), each rounded to bf16 once more.
+  const float* bias;           // [N] or null (any mode with splits == 1)
+  const __nv_bfloat16* res;    // epi 3
+  int epi;
 };
 
 }  // namespace saber

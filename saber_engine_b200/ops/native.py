@@ -43,7 +43,7 @@ class GemmI8Params(C.Structure):
                 ("counters", P), ("err", P), ("M", I), ("M_pad", I), ("N", I), ("N_pad", I),
                 ("K", I), ("nt", I), ("splits", I), ("w4", I), ("ldo", I), ("dbg_mma", I), ("tp_recv", P * 8), ("tp_flags", P * 8), ("tp_seq_base", P),
                 ("tp_nranks", I), ("tp_rank", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I), ("tp_rpr", I), ("ag_flags", P), ("ag_seq_base", P), ("ag_site", I),
-                ("group_tiles", P), ("group_ntiles", P), ("group_w_stride", U64), ("coop", I), ("mtiles", I), ("dbg", P)]
+                ("group_tiles", P), ("group_ntiles", P), ("group_w_stride", U64), ("coop", I), ("mtiles", I), ("dbg", P), ("bias", P), ("res", P), ("epi", I)]
 
 
 class RowOpParams(C.Structure):
@@ -111,6 +111,20 @@ class MoeCombineParams(C.Structure):
                 ("M", I), ("H", I), ("top_k", I), ("nt", I), ("ldg", I), ("tp_recv", P * MAX_RANKS),
                 ("tp_flags", P * MAX_RANKS), ("tp_seq_base", P), ("tp_nranks", I), ("tp_rank", I),
                 ("tp_site", I), ("tp_rows", I), ("tp_ld", I)]
+
+
+class VisRowsParams(C.Structure):
+    _fields_ = [("x", P), ("x_f32", I), ("ldx", I), ("ln_w", P), ("ln_b", P), ("eps", F), ("tiled", P),
+                ("M", I), ("K", I), ("K_pad", I), ("M_pad", I), ("group", I)]
+
+
+class VisPosAddParams(C.Structure):
+    _fields_ = [("x", P), ("ldx", I), ("table", P), ("ldt", I), ("idx", P), ("wt", P), ("M", I), ("K", I)]
+
+
+class VisAttnParams(C.Structure):
+    _fields_ = [("qkv", P), ("ldq", I), ("cos_t", P), ("sin_t", P), ("out_tiled", P), ("M_pad", I),
+                ("blocks", P), ("heads", I), ("width", I), ("scale", F)]
 
 
 def lib() -> C.CDLL:
@@ -205,6 +219,9 @@ def _declare(L: C.CDLL) -> None:
         "saber_program_add_moe_gather": (I, [P, P, P, I, P, P, P, P, I, I, I, C.c_char_p]),
         "saber_program_add_moe_route": (I, [P, C.POINTER(MoeRouteParams), C.c_char_p]),
         "saber_program_add_moe_combine": (I, [P, C.POINTER(MoeCombineParams), C.c_char_p]),
+        "saber_vis_rows_launch": (I, [C.POINTER(VisRowsParams), S]),
+        "saber_vis_pos_add_launch": (I, [C.POINTER(VisPosAddParams), S]),
+        "saber_vis_attn_launch": (I, [C.POINTER(VisAttnParams), I, S]),
         "saber_program_num_ops": (I, [P]),
         "saber_program_declared_launches": (I, [P]),
         "saber_program_op_tag": (C.c_char_p, [P, I]),
