@@ -103,7 +103,8 @@ class HybridModel:
                  max_seqs: int = 8, max_ctx: Optional[int] = None, kv_blocks: Optional[int] = None,
                  max_width: int = 8, weights: Optional[ModelWeights] = None, seed: int = 0,
                  comm=None, oracle_p: float = 0.0, oracle_seed: int = 0, gdn_vs: int = 2,
-                 use_drafter: bool = True, race_check: str = "off", gdn_prefill: str = "rows"):
+                 use_drafter: bool = True, race_check: str = "off", gdn_prefill: str = "rows",
+                 image_rows: int = 0):
         self.cfg, self.tp, self.rank = cfg, tp, rank
         if race_check not in ("off", "shadow"):
             raise ValueError("race_check must be 'off' or 'shadow'")
@@ -122,6 +123,15 @@ class HybridModel:
         self.w = weights if weights is not None else random_init(cfg, tp, rank, self.device, seed)
         self.scratch = F.scratch(self.device)
         self.k_scale = self.v_scale = 1.0
+        # Image rows: the token table is extended by `image_rows` rows that the vision tower writes; a
+        # prompt names them as token ids vocab + r, so the embedding gather of every (captured) prefill
+        # program splices them in without a kernel of its own.
+        self.image_rows = int(image_rows)
+        self.embed_table = self.w.embed
+        if self.image_rows > 0:
+            ext = torch.zeros(cfg.vocab + self.image_rows, cfg.hidden, dtype=torch.bfloat16, device=self.device)
+            ext[:cfg.vocab].copy_(self.w.embed)
+            self.embed_table = ext
         dev = self.device
         # ---- paged KV pool (fp8): one tensor per attention layer
         if kv_blocks is None:
@@ -276,7 +286,7 @@ class HybridModel:
         if self.race_check == "shadow":
             digests = torch.zeros(cfg.n_layers + 1, dtype=torch.int64, device=dev)
             prog.digest_clear(digests, cfg.n_layers + 1, tag="digest.clear")
-        prog.embed(self.w.embed, at(lay.ids), h, M, H, 0, cfg.vocab, H, tag="embed")
+        prog.embed(self.embed_table, at(lay.ids), h, M, H, 0, cfg.vocab + self.image_rows, H, tag="embed")
         first = True
         chunk_scratch = None
         ar_site = 0
@@ -491,6 +501,8 @@ class SeqStep:
     blocks: list              # physical KV block ids covering positions [0, pos0 + len(tokens))
     uid: int = 0
     step_no: int = 0
+    rope_pos: Optional[object] = None   # int [3, rows]: three-axis rotary positions of the rows (prompts with images)
+    rope_delta: int = 0       # added to the index of every row for the rotary position (after an image)
 
 
 @dataclass
@@ -518,7 +530,8 @@ def fill_blob(b: Bucket, seqs: list, page_tokens: int = 16) -> int:
         a[lay.ids + row: lay.ids + row + n] = s.tokens
         pos = np.arange(s.pos0, s.pos0 + n, dtype=np.int32)
         for ax in range(3):
-            a[lay.pos + ax * M + row: lay.pos + ax * M + row + n] = pos
+            a[lay.pos + ax * M + row: lay.pos + ax * M + row + n] = \
+                pos + s.rope_delta if s.rope_pos is None else np.asarray(s.rope_pos[ax], dtype=np.int32)[:n]
         blk = np.asarray(s.blocks, dtype=np.int32)
         a[lay.slot_map + row: lay.slot_map + row + n] = blk[pos // page_tokens] * page_tokens + pos % page_tokens
         a[lay.cu_rows + j] = row

@@ -25,6 +25,8 @@ class SeqRun:
     last_chunk: bool = True      # prefill: does this chunk end the prompt?
     temperature: float = 0.0
     want_seam: bool = False
+    rope_pos: Optional[object] = None   # int [3, rows]: rotary positions of a chunk of a prompt with images
+    rope_delta: int = 0          # rotary position - index for rows after the prompt's images
 
 
 @dataclass

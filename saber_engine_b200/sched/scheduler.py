@@ -156,12 +156,13 @@ class Scheduler:
             s = self.waiting[0]
             # speculative rows write KV past the last committed token: keep one step of head-room
             total = len(s.prompt) + s.req.params.max_tokens + max(self.ex.decode_widths)
-            hit = self.prefix.lookup(s.prompt)
+            mm = s.req.mm is not None         # image rows are arena addresses, not content: no prefix sharing
+            hit = None if mm else self.prefix.lookup(s.prompt)
             shared = list(hit.blocks) if hit else []
             need = self.arenas.kv.blocks_for(total) - len(shared)
             if not self.arenas.can_admit(total, len(shared)):
                 self.prefix.evict_for_blocks(need)          # cached pages yield to live requests
-                hit = self.prefix.lookup(s.prompt)          # the entry itself may have been evicted
+                hit = None if mm else self.prefix.lookup(s.prompt)   # the entry itself may have been evicted
                 shared = list(hit.blocks) if hit else []
                 if not self.arenas.can_admit(total, len(shared)):
                     if not self.running:                    # can never fit
@@ -176,7 +177,7 @@ class Scheduler:
             s.t_admit = time.monotonic()
             start = 0
             stored = None
-            if not hit and self.prompt_store is not None and hasattr(self.ex, "import_session"):
+            if not hit and not mm and self.prompt_store is not None and hasattr(self.ex, "import_session"):
                 stored = self.prompt_store.get(s.prompt)     # verified before anything reaches the device
             if hit:
                 self.ex.restore_state(s.slot, hit.snapshot)
@@ -190,7 +191,7 @@ class Scheduler:
             else:
                 self.ex.reset_slot(s.slot)
             s.pos = start
-            cuts = self.prefix.cut_points(len(s.prompt), start)
+            cuts = [] if mm else self.prefix.cut_points(len(s.prompt), start)
             s.cut_points = set(cuts)
             s.chunks = deque(B.cut_prompt(len(s.prompt), start, self.ex.prefill_rungs, cuts))
             self.running.append(s)
@@ -230,7 +231,9 @@ class Scheduler:
                 if plan[0] == "prefill":
                     runs = [SeqRun(s.seq_id, s.prompt[pos:pos + n], pos, s.slot, 0, s.blocks, uid=s.seq_id,
                                    last_chunk=(pos + n == len(s.prompt)),
-                                   temperature=s.req.params.temperature, want_seam=not s.req.params.greedy)
+                                   temperature=s.req.params.temperature, want_seam=not s.req.params.greedy,
+                                   rope_pos=(None if s.req.mm is None else
+                                             [list(ax[pos:pos + n]) for ax in s.req.mm["rope_pos"]]))
                             for s, pos, n in plan[1]]
                     outs = self.ex.prefill(runs)
                 else:
@@ -240,7 +243,8 @@ class Scheduler:
                         drafts = (s.drafts + [0] * width)[: width - 1]
                         runs.append(SeqRun(s.seq_id, [s.output[-1]] + drafts, s.pos, s.slot, s.shift, s.blocks,
                                            uid=s.seq_id, step_no=s.step_no, temperature=s.req.params.temperature,
-                                           want_seam=not s.req.params.greedy))
+                                           want_seam=not s.req.params.greedy,
+                                           rope_delta=(0 if s.req.mm is None else int(s.req.mm.get("rope_delta", 0)))))
                     outs = self.ex.decode(runs, width)
         except Exception as exc:       # the executor failed: every request learns why (fatal law)
             self.set_fatal(f"executor failed: {exc!r}")
@@ -398,6 +402,9 @@ class Scheduler:
         if s in self.running:
             self.running.remove(s)
             self.arenas.release(s.blocks, s.slot)
+        if s.req.mm is not None and callable(s.req.mm.get("release")):
+            s.req.mm["release"]()              # the request's rows of the image arena
+            s.req.mm["release"] = None
         if reason == "abort":
             self.counters["requests_aborted"] += 1
         else:

@@ -60,6 +60,10 @@ class EngineRequest:
     params: SamplingParams = field(default_factory=SamplingParams)
     request_id: Optional[str] = None
     eos_token_id: Optional[int] = None
+    # prompts with images: {"rope_pos": int [3, N], "rope_delta": int, "release": callable | None};
+    # image rows are token ids >= vocab (rows of the executor's image arena), so such a prompt is
+    # neither looked up in nor added to the prefix caches
+    mm: Optional[dict] = None
 
 
 @dataclass

@@ -50,10 +50,33 @@ def sampling_from_body(body: dict, default_max: int) -> SamplingParams:
         logprobs=lp, prompt_logprobs=body.get("prompt_logprobs"))
 
 
+def _collect_images(msgs: list, have_vision: bool) -> list:
+    """RGB arrays of every image part of a conversation, in order (`data:` URLs only).  Parity:
+    `crates/saber-vision-input/src/url.rs`, `src/decode.rs`."""
+    urls = []
+    for m in msgs:
+        if isinstance(m.get("content"), list):
+            for part in m["content"]:
+                if not isinstance(part, dict) or part.get("type") not in ("text", "image", "image_url"):
+                    raise ValueError("content parts must be of type text or image_url")
+                if part["type"] in ("image", "image_url"):
+                    u = part.get("image_url")
+                    u = u.get("url") if isinstance(u, dict) else (u or part.get("image"))
+                    if not isinstance(u, str):
+                        raise ValueError("image_url part needs a url")
+                    urls.append(u)
+    if urls and not have_vision:
+        raise ValueError("this server was started without a vision tower: image parts are not accepted")
+    if not urls:
+        return []
+    from ..vision import processor as VP
+    return [VP.decode_image(VP.fetch_image_url(u)) for u in urls]
+
+
 class ServerState:
     def __init__(self, engine, tokenizer=None, model_name: str = "saber", api_keys=(), chat_template=None,
                  default_max_tokens: int = 256, reasoning_parser: Optional[str] = "qwen3",
-                 tool_parser: Optional[str] = "qwen3_coder", census_fn=None):
+                 tool_parser: Optional[str] = "qwen3_coder", census_fn=None, vision=None):
         self.engine, self.tok = engine, tokenizer or ByteCodec()
         self.model_name, self.api_keys = model_name, set(api_keys)
         self.chat_template, self.default_max_tokens = chat_template, default_max_tokens
@@ -62,6 +85,7 @@ class ServerState:
         self.requests = deque(maxlen=256)       # ring: no bodies are stored
         self.started = time.time()
         self.census_fn = census_fn
+        self.vision = vision                     # vision.engine.VisionFrontend, or None: a text-only plane
 
 
 def create_app(state: ServerState) -> FastAPI:
@@ -136,9 +160,11 @@ def create_app(state: ServerState) -> FastAPI:
             stops = []
         tools = body.get("tools") if chat else None
         starts_in_reasoning = False
+        images = []
         try:
             if chat:
                 msgs = normalise_messages(body.get("messages"))
+                images = _collect_images(msgs, state.vision is not None)
                 kw = body.get("chat_template_kwargs") or {}
                 text = render_chat(msgs, state.chat_template, True, tools, **kw)
                 starts_in_reasoning = text.rstrip().endswith("<think>")
@@ -157,9 +183,21 @@ def create_app(state: ServerState) -> FastAPI:
         if problems:
             return _err(400, "; ".join(problems))
         rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
+        ereq = None
         try:
-            sub = state.engine.submit(EngineRequest(prompt_ids, params, rid, getattr(state.tok, "eos_token_id", None)))
+            eos = getattr(state.tok, "eos_token_id", None)
+            if images:      # tower forward into the image arena, placeholders -> arena rows, three-axis positions
+                ereq = await asyncio.get_running_loop().run_in_executor(
+                    None, lambda: state.vision.build_request(prompt_ids, images, params, request_id=rid, eos_token_id=eos))
+                prompt_ids = ereq.prompt_token_ids
+            else:
+                ereq = EngineRequest(prompt_ids, params, rid, eos)
+            sub = state.engine.submit(ereq)
+        except ValueError as exc:             # an image the processor refuses (aspect ratio, placeholders)
+            return _err(400, str(exc))
         except EngineRefused as exc:
+            if ereq is not None and ereq.mm and callable(ereq.mm.get("release")):
+                ereq.mm["release"]()
             state.metrics.inc("request_refused_total")
             return _err(exc.status, exc.reason, "service_unavailable" if exc.status == 503 else "invalid_request_error")
         loop = asyncio.get_running_loop()

@@ -99,3 +99,74 @@ def test_tower_reference_runs_and_is_image_local():
     alone = VT.tower_reference(cfg, w, a, [(1, 4, 4)])
     assert both.shape == (10, 64)
     assert torch.allclose(both[:4], alone, atol=1e-6)           # attention never crosses images
+
+
+# ------------------------------------------------------------------ image arena, request builder, scheduler plumbing
+class _FakeModel:
+    def __init__(self, vocab=1024, rows=64, hidden=32):
+        from types import SimpleNamespace
+        self.cfg = SimpleNamespace(vocab=vocab)
+        self.image_rows = rows
+        self.embed_table = torch.zeros(vocab + rows, hidden, dtype=torch.bfloat16)
+        self.stream = None
+
+
+def test_row_arena_first_fit_and_merge():
+    from saber_engine_b200.vision.engine import RowArena
+    a = RowArena(10)
+    x, y, z = a.alloc(4), a.alloc(4), a.alloc(4)
+    assert (x, y, z) == (0, 4, None)
+    a.free(0, 4)
+    assert a.alloc(2) == 0 and a.free_rows == 4
+    a.free(4, 4)
+    a.free(0, 2)
+    assert a.free_rows == 10 and a.alloc(10) == 0
+
+
+def test_request_builder_and_scheduler_carry_image_rows_and_positions():
+    from types import SimpleNamespace
+    from saber_engine_b200.sched.mock import NullExecutor
+    from saber_engine_b200.sched.scheduler import Scheduler, SchedulerConfig
+    from saber_engine_b200.serve.engine_api import SamplingParams
+    from saber_engine_b200.vision.engine import VisionFrontend
+    ex = NullExecutor(vocab=2048, max_seqs=2, prefill_rungs=(16, 64))
+    ex.model = _FakeModel(vocab=1024, rows=64)
+    seen = []
+    pre = ex.prefill
+    ex.prefill = lambda runs: (seen.extend(runs), pre(runs))[1]
+    dec = ex.decode
+    ex.decode = lambda runs, w: (seen.extend(runs), dec(runs, w))[1]
+    calls = []
+
+    def encode(px, grids, out_rows):
+        calls.append((tuple(px.shape), list(grids)))
+        out_rows.fill_(1.0)
+    PAD = 300
+    vis = VisionFrontend(ex, SimpleNamespace(max_patches=4096), PAD, VP.ProcessorConfig(min_pixels=0), encode=encode)
+    img = np.random.default_rng(0).integers(0, 256, size=(64, 96, 3), dtype=np.uint8)
+    req = vis.build_request([5, 6, PAD, 7], [img], SamplingParams(max_tokens=4, ignore_eos=True))
+    assert calls == [((24, 1536), [(1, 4, 6)])]
+    assert req.prompt_token_ids == [5, 6] + list(range(1024, 1030)) + [7]
+    assert req.mm["rope_delta"] == -3 and vis.arena.free_rows == 58
+    assert float(ex.model.embed_table[1024:1030].float().min()) == 1.0
+    s = Scheduler(ex, SchedulerConfig(max_seqs=2, max_ctx=512, prefix_cache_min_tokens=4, prefix_cache_interval=4))
+    sub = s.submit(req)
+    s.run_until_idle()
+    assert s.prefix.stats.lookups == 0 and s.prefix.stats.inserts == 0      # image rows are not content
+    first = seen[0]
+    assert first.rope_pos is not None and first.rope_pos[1][:5] == [0, 1, 2, 2, 2] and first.rope_pos[2][2:5] == [2, 3, 4]
+    assert all(r.rope_delta == -3 for r in seen if r.rope_pos is None)
+    assert vis.arena.free_rows == 64                                         # released when the request finished
+    ev = sub.events.get(timeout=5)
+    assert ev is not None
+
+
+def test_text_only_server_refuses_image_parts():
+    from saber_engine_b200.serve.server import _collect_images
+    msgs = [{"role": "user", "content": [{"type": "text", "text": "hi"},
+                                         {"type": "image_url", "image_url": {"url": "data:image/png;base64,AAAA"}}]}]
+    with pytest.raises(ValueError):
+        _collect_images(msgs, False)
+    with pytest.raises(ValueError):
+        _collect_images(msgs, True)              # not a decodable image
+    assert _collect_images([{"role": "user", "content": "plain"}], False) == []
