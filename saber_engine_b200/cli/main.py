@@ -102,7 +102,8 @@ def build_engine(a):
         widths = _ints(a.engine_decode_widths)
         model = HybridModel(cfg, tp=a.engine_tp, rank=0, device="cuda", max_seqs=a.engine_max_seqs,
                             max_ctx=a.engine_max_ctx, kv_blocks=a.engine_kv_blocks or None, max_width=max(widths),
-                            weights=weights, seed=a.seed, race_check=a.engine_race_check)
+                            weights=weights, seed=a.seed, race_check=a.engine_race_check,
+                            image_rows=(getattr(a, "vision_arena_patches", 0) // 4 if getattr(a, "vision", False) else 0))
         if a.autotune:
             from ..plan.autotune import TuneTable
             model.tune_table = TuneTable.load(a.autotune)
@@ -153,8 +154,20 @@ def cmd_engine(a) -> int:
     ex, sched = build_engine(a)
     tok = HfTokenizer(str(Path(a.tokenizer).parent)) if a.tokenizer and Path(a.tokenizer).exists() else ByteCodec(ex.vocab)
     template = Path(a.chat_template).read_text() if a.chat_template and Path(a.chat_template).exists() else None
+    vision = None
+    if getattr(a, "vision", False) and hasattr(ex, "model") and getattr(ex.model, "image_rows", 0) > 0:
+        # the tower (random-init unless a pack carries it), its arena clamps the processor's pixel ceiling
+        from ..vision.engine import VisionFrontend
+        from ..vision.tower import VisionConfig, VisionWeights
+        from ..vision.tower_gpu import VisionTowerGPU
+        vcfg = VisionConfig.qwen38(out_hidden=ex.model.cfg.hidden)
+        tower = VisionTowerGPU(vcfg, VisionWeights.random(vcfg, seed=a.seed), "cuda", max_patches=a.vision_arena_patches)
+        pad = getattr(tok, "special_ids", {}).get("<|image_pad|>") if hasattr(tok, "special_ids") else None
+        if pad is None:
+            pad = tok.encode("<|image_pad|>")[0]
+        vision = VisionFrontend(ex, tower, pad)
     state = ServerState(sched, tok, a.served_model_name, api_keys=a.api_key or (), chat_template=template,
-                        census_fn=(lambda: dict(getattr(ex, "census", {}))))
+                        census_fn=(lambda: dict(getattr(ex, "census", {}))), vision=vision)
     for path in getattr(a, "warm_prompt", []):
         ids = tok.encode(Path(path).read_text())
         sched.warm([ids])
@@ -266,6 +279,8 @@ def make_parser() -> argparse.ArgumentParser:
     e.add_argument("--prebuild", action="store_true")
     e.add_argument("--seed", type=int, default=0)
     e.add_argument("--mock-vocab", type=int, default=1024)
+    e.add_argument("--vision", action="store_true", help="load the vision tower and accept image parts in chat requests")
+    e.add_argument("--vision-arena-patches", type=int, default=16384, help="patch rows the tower arena holds (larger images are downscaled)")
     e.add_argument("--engine-host-trace", action="store_true", help="named host phases per step (an attribution, not a published time)")
     e.add_argument("--engine-race-check", default="off", choices=["off", "shadow"])
     e.add_argument("--poison-boot", type=lambda v: int(v, 0), default=None, metavar="BYTE",

@@ -133,6 +133,22 @@ def _moe(M):
     return layers, ws, out, progs
 
 
+def _vision(side):
+    """The full 27-block tower on one side x side image (side / 16 squared patch rows)."""
+    from ..vision.tower import VisionConfig, VisionWeights
+    from ..vision.tower_gpu import VisionTowerGPU
+    cfg = VisionConfig.qwen38()
+    tower = VisionTowerGPU(cfg, VisionWeights.random(cfg, seed=0), DEV, max_patches=(side // 16) ** 2)
+    g = side // 16
+    px = torch.randn(g * g, cfg.patch_row).pin_memory()
+    out = torch.empty(g * g // 4, cfg.out_hidden, dtype=torch.bfloat16, device=DEV)
+    tower.forward(px, [(1, g, g)], out=out)
+    n0 = tower.launches
+    _time([lambda: tower.forward(px, [(1, g, g)], out=out)] * 3,
+          f"vision tower {side}x{side}: {g * g} patch rows -> {g * g // 4} tokens, {n0} launches")
+    return tower, out
+
+
 CASES = {
     "gemm_w4_gate_up_m72": lambda: _gemm(34816, 5120, 72, 1, 1),
     "gemm_w4_down_m72_split": lambda: _gemm(5120, 17408, 72, 1, 7, copies=4),
@@ -147,6 +163,8 @@ CASES = {
     "gdn_rec_b8": lambda: _gdn(8, 9, 5),
     "row_add_rms_m72": lambda: _row(72, 5120),
     "moe_block_m72": lambda: _moe(72),
+    "vision_tower_512": lambda: _vision(512),
+    "vision_tower_1024": lambda: _vision(1024),
 }
 
 
