@@ -5,7 +5,8 @@
 //
 // Parity: the reference tower's op list and rounding points (crates/saber-kernels/hip/vision.hip:1-30):
 // every linear rounds to bf16 once and the activation / residual work on the rounded value;
-// LayerNorm, softmax and rotary arithmetic run in fp32; rotated q and k are rounded to bf16.
+// LayerNorm, softmax and rotary arithmetic run in fp32; rotated q and k are rounded to bf16; the
+// attention products run on mma.sync (bf16 operands, fp32 accumulators).
 #include "vision.h"
 #include "launch.cuh"
 
@@ -106,114 +107,166 @@ __global__ void __launch_bounds__(kVisThreads) vis_pos_add_kernel(const VisPosAd
   }
 }
 
+// ------------------------------------------------------------------------------------ rotary
+// In place on the q and k parts of qkv: out[d] = x[d] cos - x[d+36] sin, out[d+36] = x[d+36] cos + x[d] sin
+// (fp32 arithmetic, one rounding to bf16).  One CTA per row.
+constexpr int kHd = 72, kHalf = 36;
+
+__global__ void __launch_bounds__(kVisThreads) vis_rope_kernel(const VisAttnParams p, int rows) {
+  pdl_wait();
+  const int m = blockIdx.x;
+  if (m >= rows) return;
+  __nv_bfloat16* base = const_cast<__nv_bfloat16*>(p.qkv) + static_cast<size_t>(m) * p.ldq;
+  const float* cs = p.cos_t + static_cast<size_t>(m) * kHalf;
+  const float* sn = p.sin_t + static_cast<size_t>(m) * kHalf;
+  const int pairs = 2 * p.heads * kHalf;              // q heads, then k heads
+  for (int i = threadIdx.x; i < pairs; i += kVisThreads) {
+    const int hd = i / kHalf, d = i - hd * kHalf;     // hd < heads: q head, else k head (k starts at width = heads * 72)
+    __nv_bfloat16* x = base + hd * kHd;
+    const float x1 = __bfloat162float(x[d]), x2 = __bfloat162float(x[d + kHalf]);
+    x[d] = __float2bfloat16(x1 * cs[d] - x2 * sn[d]);
+    x[d + kHalf] = __float2bfloat16(x2 * cs[d] + x1 * sn[d]);
+  }
+}
+
 // ------------------------------------------------------------------------------------ attention
-// One thread per query row (128 rows per CTA), one head per blockIdx.y.  Keys and values of the
-// image stream through shared memory 32 rows at a time as fp32 (keys rotated on the way in); a
-// thread scores eight keys, folds their maximum into its running softmax and accumulates.
-constexpr int kHd = 72, kHalf = 36, kKeys = 32;
+// Non-causal attention inside one image on rotated q / k.  A CTA of four warps owns 64 query rows of
+// one head (16 per warp, the m16n8k16 tile); keys and values stream through shared memory 64 rows at
+// a time (keys row-major with the head dim padded to 80, values transposed so that two consecutive
+// keys of one dim are one 32-bit word); S = Q K^T and O += P V run on mma.sync with fp32
+// accumulators, the softmax is the running-maximum form in the base-2 domain.
+constexpr int kQRows = 64, kKT = 64, kKStride = 88, kVStride = 72;
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
 
 __global__ void __launch_bounds__(kVisThreads) vis_attn_kernel(const VisAttnParams p) {
-  __shared__ __align__(16) float k_s[kKeys][kHd];
-  __shared__ __align__(16) float v_s[kKeys][kHd];
+  __shared__ __align__(16) __nv_bfloat16 k_s[kKT][kKStride];
+  __shared__ __align__(16) __nv_bfloat16 vt_s[kHd][kVStride];
   pdl_wait();
   const int4 blk = p.blocks[blockIdx.x];
-  const int seq0 = blk.x, len = blk.y, qrel = blk.z + threadIdx.x;
+  const int seq0 = blk.x, len = blk.y, q0 = blk.z;
   const int h = blockIdx.y;
-  const bool live = qrel < len;
-  const int qrow = seq0 + (live ? qrel : 0);
-  const float qs = p.scale * 1.4426950408889634f;       // scores in the base-2 domain
-  float q[kHd], acc[kHd];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  // the padding columns of the key tile are never written again
+  for (int i = threadIdx.x; i < kKT * 8; i += kVisThreads) k_s[i >> 3][kHd + (i & 7)] = __float2bfloat16(0.f);
+  // this warp's query fragments, straight from global memory (rows past the image read row 0, never stored)
+  uint32_t qf[5][4];
   {
-    const __nv_bfloat16* qp = p.qkv + static_cast<size_t>(qrow) * p.ldq + h * kHd;
-    const float* cs = p.cos_t + static_cast<size_t>(qrow) * kHalf;
-    const float* sn = p.sin_t + static_cast<size_t>(qrow) * kHalf;
+    const int r0 = q0 + warp * 16 + g, r1 = r0 + 8;
+    const __nv_bfloat16* qa = p.qkv + static_cast<size_t>(seq0 + (r0 < len ? r0 : 0)) * p.ldq + h * kHd;
+    const __nv_bfloat16* qb = p.qkv + static_cast<size_t>(seq0 + (r1 < len ? r1 : 0)) * p.ldq + h * kHd;
 #pragma unroll
-    for (int d = 0; d < kHalf; ++d) {
-      const float x1 = __bfloat162float(qp[d]), x2 = __bfloat162float(qp[d + kHalf]);
-      q[d] = rbf(x1 * cs[d] - x2 * sn[d]) * qs;
-      q[d + kHalf] = rbf(x2 * cs[d] + x1 * sn[d]) * qs;
-    }
-#pragma unroll
-    for (int d = 0; d < kHd; ++d) acc[d] = 0.f;
-  }
-  float mrun = -INFINITY, lrun = 0.f;
-  for (int k0 = 0; k0 < len; k0 += kKeys) {
-    __syncthreads();
-    {   // stage 32 keys (rotated) and values: thread = (key, quarter of the 36 rotary pairs)
-      const int j = threadIdx.x >> 2, part = threadIdx.x & 3;
-      const bool kin = k0 + j < len;
-      const int krow = seq0 + (kin ? k0 + j : 0);
-      const __nv_bfloat16* kp = p.qkv + static_cast<size_t>(krow) * p.ldq + p.width + h * kHd;
-      const __nv_bfloat16* vp = kp + p.width;
-      const float* cs = p.cos_t + static_cast<size_t>(krow) * kHalf;
-      const float* sn = p.sin_t + static_cast<size_t>(krow) * kHalf;
-#pragma unroll
-      for (int i = 0; i < 9; ++i) {
-        const int d = part * 9 + i;
-        const float x1 = __bfloat162float(kp[d]), x2 = __bfloat162float(kp[d + kHalf]);
-        k_s[j][d] = kin ? rbf(x1 * cs[d] - x2 * sn[d]) : 0.f;
-        k_s[j][d + kHalf] = kin ? rbf(x2 * cs[d] + x1 * sn[d]) : 0.f;
-        v_s[j][d] = kin ? __bfloat162float(vp[d]) : 0.f;
-        v_s[j][d + kHalf] = kin ? __bfloat162float(vp[d + kHalf]) : 0.f;
-      }
-    }
-    __syncthreads();
-    const int valid = min(kKeys, len - k0);
-#pragma unroll 1
-    for (int jb = 0; jb < kKeys; jb += 8) {
-      if (jb >= valid) break;
-      float s[8];
-      float tmax = -INFINITY;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4* kr = reinterpret_cast<const float4*>(k_s[jb + j]);
-        float a = 0.f;
-#pragma unroll
-        for (int d4 = 0; d4 < kHd / 4; ++d4) {
-          const float4 kv = kr[d4];
-          a = fmaf(q[4 * d4], kv.x, a);
-          a = fmaf(q[4 * d4 + 1], kv.y, a);
-          a = fmaf(q[4 * d4 + 2], kv.z, a);
-          a = fmaf(q[4 * d4 + 3], kv.w, a);
-        }
-        s[j] = (jb + j < valid) ? a : -INFINITY;
-        tmax = fmaxf(tmax, s[j]);
-      }
-      const float mnew = fmaxf(mrun, tmax);          // finite: key jb is valid
-      const float corr = exp2f(mrun - mnew);         // 0 on the first group (mrun = -inf)
-      mrun = mnew;
-      lrun *= corr;
-#pragma unroll
-      for (int d = 0; d < kHd; ++d) acc[d] *= corr;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float pj = exp2f(s[j] - mnew);
-        lrun += pj;
-        const float4* vr = reinterpret_cast<const float4*>(v_s[jb + j]);
-#pragma unroll
-        for (int d4 = 0; d4 < kHd / 4; ++d4) {
-          const float4 vv = vr[d4];
-          acc[4 * d4] = fmaf(pj, vv.x, acc[4 * d4]);
-          acc[4 * d4 + 1] = fmaf(pj, vv.y, acc[4 * d4 + 1]);
-          acc[4 * d4 + 2] = fmaf(pj, vv.z, acc[4 * d4 + 2]);
-          acc[4 * d4 + 3] = fmaf(pj, vv.w, acc[4 * d4 + 3]);
-        }
-      }
+    for (int ks = 0; ks < 5; ++ks) {
+      const int c0 = ks * 16 + 2 * t, c1 = c0 + 8;
+      qf[ks][0] = *reinterpret_cast<const uint32_t*>(qa + c0);
+      qf[ks][1] = *reinterpret_cast<const uint32_t*>(qb + c0);
+      qf[ks][2] = c1 < kHd ? *reinterpret_cast<const uint32_t*>(qa + c1) : 0u;
+      qf[ks][3] = c1 < kHd ? *reinterpret_cast<const uint32_t*>(qb + c1) : 0u;
     }
   }
-  if (live) {
-    const float inv = 1.f / lrun;
-    const int mrow = seq0 + qrel;
+  const float qs = p.scale * 1.4426950408889634f;
+  float o[9][4];
 #pragma unroll
-    for (int c = 0; c < kHd / 8; ++c) {
-      uint4 o;
-      __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(&o);
+  for (int j = 0; j < 9; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  for (int k0 = 0; k0 < len; k0 += kKT) {
+    __syncthreads();                                    // the previous tile has been consumed
+    for (int i = threadIdx.x; i < kKT * 9; i += kVisThreads) {
+      const int j = i / 9, c = i - j * 9;               // key row of the tile, 8-value chunk of the head
+      uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+      if (k0 + j < len) {
+        const __nv_bfloat16* kp = p.qkv + static_cast<size_t>(seq0 + k0 + j) * p.ldq + p.width + h * kHd + c * 8;
+        kv = *reinterpret_cast<const uint4*>(kp);
+        vv = *reinterpret_cast<const uint4*>(kp + p.width);
+      }
+      *reinterpret_cast<uint4*>(&k_s[j][c * 8]) = kv;
+      const __nv_bfloat16* vb = reinterpret_cast<const __nv_bfloat16*>(&vv);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ob[j] = __float2bfloat16(acc[c * 8 + j] * inv);
-      const int col0 = h * kHd + c * 8;
-      const int kb = col0 >> 6, chunk = (col0 & 63) >> 3;
-      *reinterpret_cast<uint4*>(p.out_tiled + (static_cast<size_t>(kb) * p.M_pad + mrow) * 128 +
-                                ((chunk ^ (mrow & 7)) << 4)) = o;
+      for (int e = 0; e < 8; ++e) vt_s[c * 8 + e][j] = vb[e];
+    }
+    __syncthreads();
+    const int valid = min(kKT, len - k0);
+    float s[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+      const __nv_bfloat16* kr = &k_s[nt * 8 + g][2 * t];
+#pragma unroll
+      for (int ks = 0; ks < 5; ++ks)
+        mma_bf16(s[nt], qf[ks], *reinterpret_cast<const uint32_t*>(kr + ks * 16),
+                 *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8));
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int key = nt * 8 + 2 * t + (c & 1);
+        s[nt][c] = key < valid ? s[nt][c] * qs : -INFINITY;
+      }
+      mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+      mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);      // finite: key 0 of the tile is valid
+    const float c0 = exp2f(m0 - n0), c1 = exp2f(m1 - n1);      // 0 on the first tile
+    m0 = n0; m1 = n1;
+    l0 *= c0; l1 *= c1;
+#pragma unroll
+    for (int j = 0; j < 9; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      s[nt][0] = exp2f(s[nt][0] - n0); s[nt][1] = exp2f(s[nt][1] - n0);
+      s[nt][2] = exp2f(s[nt][2] - n1); s[nt][3] = exp2f(s[nt][3] - n1);
+      l0 += s[nt][0] + s[nt][1];
+      l1 += s[nt][2] + s[nt][3];
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {                    // 16 keys per step: score tiles 2kk and 2kk + 1
+      uint32_t a[4];
+      a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int j = 0; j < 9; ++j) {
+        const __nv_bfloat16* vr = &vt_s[j * 8 + g][kk * 16 + 2 * t];
+        mma_bf16(o[j], a, *reinterpret_cast<const uint32_t*>(vr), *reinterpret_cast<const uint32_t*>(vr + 8));
+      }
+    }
+  }
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  const float i0 = 1.f / l0, i1 = 1.f / l1;
+  const int r0 = q0 + warp * 16 + g, r1 = r0 + 8;
+#pragma unroll
+  for (int j = 0; j < 9; ++j) {
+    const int ch = h * 9 + j;                           // 16-byte chunk of the output row (72 = 9 chunks per head)
+    const int kb = ch >> 3, chunk = ch & 7;
+    if (r0 < len) {
+      const int mrow = seq0 + r0;
+      *reinterpret_cast<uint32_t*>(p.out_tiled + (static_cast<size_t>(kb) * p.M_pad + mrow) * 128 +
+                                   ((chunk ^ (mrow & 7)) << 4) + 4 * t) = pack_bf16(o[j][0] * i0, o[j][1] * i0);
+    }
+    if (r1 < len) {
+      const int mrow = seq0 + r1;
+      *reinterpret_cast<uint32_t*>(p.out_tiled + (static_cast<size_t>(kb) * p.M_pad + mrow) * 128 +
+                                   ((chunk ^ (mrow & 7)) << 4) + 4 * t) = pack_bf16(o[j][2] * i1, o[j][3] * i1);
     }
   }
 }
@@ -241,4 +294,11 @@ extern "C" int saber_vis_attn_launch(const saber::VisAttnParams* p, int n_blocks
   if (n_blocks <= 0) return 0;
   if ((p->width & 7) || p->heads * kHd != p->width || (p->ldq & 7)) return static_cast<int>(cudaErrorInvalidValue);
   return static_cast<int>(saber::launch(vis_attn_kernel, dim3(n_blocks, p->heads), dim3(kVisThreads), 0, stream, 0, *p));
+}
+
+extern "C" int saber_vis_rope_launch(const saber::VisAttnParams* p, int rows, cudaStream_t stream) {
+  using namespace saber;
+  if (rows <= 0) return 0;
+  if (p->heads * kHd != p->width) return static_cast<int>(cudaErrorInvalidValue);
+  return static_cast<int>(saber::launch(vis_rope_kernel, dim3(rows), dim3(kVisThreads), 0, stream, 0, *p, rows));
 }

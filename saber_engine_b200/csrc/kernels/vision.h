@@ -33,7 +33,8 @@ struct VisPosAddParams {
   int M, K;
 };
 
-// Non-causal attention inside each image with 2-D rotary embedding; head dim 72.
+// Non-causal attention inside each image; head dim 72.  The rotary kernel (in place on the q and k
+// parts of qkv, before the attention kernel) takes the same block; `blocks` rows cover 64 queries.
 struct VisAttnParams {
   const __nv_bfloat16* qkv; int ldq;     // [L][3 * width]: q | k | v, head-major inside each
   const float* cos_t; const float* sin_t; // [L][36]
@@ -48,3 +49,4 @@ struct VisAttnParams {
 extern "C" int saber_vis_rows_launch(const saber::VisRowsParams* p, cudaStream_t stream);
 extern "C" int saber_vis_pos_add_launch(const saber::VisPosAddParams* p, cudaStream_t stream);
 extern "C" int saber_vis_attn_launch(const saber::VisAttnParams* p, int n_blocks, cudaStream_t stream);
+extern "C" int saber_vis_rope_launch(const saber::VisAttnParams* p, int rows, cudaStream_t stream);

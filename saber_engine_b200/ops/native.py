@@ -222,6 +222,7 @@ def _declare(L: C.CDLL) -> None:
         "saber_vis_rows_launch": (I, [C.POINTER(VisRowsParams), S]),
         "saber_vis_pos_add_launch": (I, [C.POINTER(VisPosAddParams), S]),
         "saber_vis_attn_launch": (I, [C.POINTER(VisAttnParams), I, S]),
+        "saber_vis_rope_launch": (I, [C.POINTER(VisAttnParams), I, S]),
         "saber_program_num_ops": (I, [P]),
         "saber_program_declared_launches": (I, [P]),
         "saber_program_op_tag": (C.c_char_p, [P, I]),

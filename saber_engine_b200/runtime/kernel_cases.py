@@ -146,6 +146,8 @@ def _vision(side):
     n0 = tower.launches
     _time([lambda: tower.forward(px, [(1, g, g)], out=out)] * 3,
           f"vision tower {side}x{side}: {g * g} patch rows -> {g * g // 4} tokens, {n0} launches")
+    tower.forward(px, [(1, g, g)], out=out, graph=True)
+    _time([lambda: tower.forward(px, [(1, g, g)], out=out, graph=True)] * 3, f"vision tower {side}x{side}, graph replay")
     return tower, out
 
 

@@ -79,7 +79,7 @@ class VisionFrontend:
     def _encode_tower(self, pixel_values: torch.Tensor, grids, out_rows: torch.Tensor) -> None:
         stream = self.ex.model.stream                # ordered before the prefill programs that read the rows
         with torch.cuda.stream(stream):
-            self.tower.forward(pixel_values, grids, out=out_rows)
+            self.tower.forward(pixel_values, grids, out=out_rows, graph=True)
 
     def build_request(self, token_ids: Sequence[int], images: Sequence[np.ndarray],
                       params: Optional[SamplingParams] = None, **kw) -> EngineRequest:

@@ -118,7 +118,7 @@ def rope_tables(grids: Sequence[tuple], cfg: VisionConfig):
     return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
 
 
-def attn_blocks(grids: Sequence[tuple], rows_per_block: int = 128) -> np.ndarray:
+def attn_blocks(grids: Sequence[tuple], rows_per_block: int = 64) -> np.ndarray:
     """int32 [n_blocks, 4]: {first row of the image, rows of the image, first query (relative), 0}."""
     out, row = [], 0
     for t, h, w in grids:

@@ -1,6 +1,7 @@
 """The vision tower on the device: every linear is one launch of the tcgen05 GEMM in its bf16 mode
 (bias, GELU and the residual add in the epilogue), every normalisation writes the next GEMM's token
-operand directly, attention writes the projection's operand.  Eight launches per block.
+operand directly, attention writes the projection's operand.  Attention is a rotary kernel in place on q / k and a
+flash-style mma.sync kernel.  Nine launches per block.
 
     tower = VisionTowerGPU(cfg, weights, "cuda")
     rows = tower.forward(pixel_values, grids)        # bf16 [L / 4, out_hidden]
@@ -98,51 +99,47 @@ class VisionTowerGPU:
         self.launches += 1
 
     # ------------------------------------------------------------------ forward
-    @torch.no_grad()
-    def forward(self, pixel_values: torch.Tensor, grids: Sequence[tuple],
-                out: Optional[torch.Tensor] = None, return_hidden: bool = False) -> torch.Tensor:
+    def _meta(self, grids) -> dict:
+        """Host tables of a grid list on the device: position gather, rotary tables, attention blocks."""
         cfg, d = self.cfg, self.dev
-        Lr = int(pixel_values.shape[0])
-        assert Lr == sum(t * h * w for t, h, w in grids) and Lr % (cfg.merge ** 2) == 0
-        if Lr > self.max_patches:
-            raise ValueError(f"{Lr} patch rows exceed the tower arena ({self.max_patches})")
-        self._reserve(Lr)
-        m_pad = L.padded_rows(Lr)
-        W = cfg.width
-        px = pixel_values.to(d, non_blocking=True).float().contiguous()
         idx, wt = pos_gather_table(grids, cfg)
         cos, sin = rope_tables(grids, cfg)
         blocks = attn_blocks(grids)
-        idx_d, wt_d = torch.from_numpy(idx).to(d), torch.from_numpy(wt).to(d)
-        cos_d, sin_d = torch.from_numpy(cos).to(d), torch.from_numpy(sin).to(d)
-        blk_d = torch.from_numpy(blocks).to(d)
+        return dict(idx=torch.from_numpy(idx).to(d), wt=torch.from_numpy(wt).to(d), cos=torch.from_numpy(cos).to(d),
+                    sin=torch.from_numpy(sin).to(d), blk=torch.from_numpy(blocks).to(d), n_blocks=int(blocks.shape[0]))
+
+    def _run(self, px: torch.Tensor, Lr: int, meta: dict, out: Optional[torch.Tensor], stop_at_hidden: bool) -> None:
+        """The launches of one forward on the current stream (nothing here synchronises)."""
+        cfg = self.cfg
+        m_pad = L.padded_rows(Lr)
+        W = cfg.width
         x, qkv, h = self.x[:Lr], self.qkv[:Lr], self.h[:Lr]
         lib = N.lib()
-        # patch embed + position table
         self._rows(px, Lr, cfg.patch_row, self.patch.K_pad, m_pad)
         self._gemm(self.patch, Lr, m_pad, x)
         pp = N.VisPosAddParams()
         pp.x, pp.ldx, pp.table, pp.ldt = x.data_ptr(), x.stride(0), self.pos_table.data_ptr(), self.pos_table.stride(0)
-        pp.idx, pp.wt, pp.M, pp.K = idx_d.data_ptr(), wt_d.data_ptr(), Lr, W
+        pp.idx, pp.wt, pp.M, pp.K = meta["idx"].data_ptr(), meta["wt"].data_ptr(), Lr, W
         N.check(lib.saber_vis_pos_add_launch(C.byref(pp), N.stream_handle()), "vis_pos_add")
         self.launches += 1
         pa = N.VisAttnParams()
-        pa.qkv, pa.ldq, pa.cos_t, pa.sin_t = qkv.data_ptr(), qkv.stride(0), cos_d.data_ptr(), sin_d.data_ptr()
-        pa.out_tiled, pa.M_pad, pa.blocks = self.a_buf.data_ptr(), m_pad, blk_d.data_ptr()
+        pa.qkv, pa.ldq = qkv.data_ptr(), qkv.stride(0)
+        pa.cos_t, pa.sin_t = meta["cos"].data_ptr(), meta["sin"].data_ptr()
+        pa.out_tiled, pa.M_pad, pa.blocks = self.a_buf.data_ptr(), m_pad, meta["blk"].data_ptr()
         pa.heads, pa.width, pa.scale = cfg.heads, W, 1.0 / math.sqrt(cfg.head_dim)
         for b in self.blocks:
             self._rows(x, Lr, W, W, m_pad, ln=b["ln1"])
             self._gemm(b["qkv"], Lr, m_pad, qkv)
-            N.check(lib.saber_vis_attn_launch(C.byref(pa), int(blocks.shape[0]), N.stream_handle()), "vis_attn")
-            self.launches += 1
+            N.check(lib.saber_vis_rope_launch(C.byref(pa), Lr, N.stream_handle()), "vis_rope")
+            N.check(lib.saber_vis_attn_launch(C.byref(pa), meta["n_blocks"], N.stream_handle()), "vis_attn")
+            self.launches += 2
             self._gemm(b["proj"], Lr, m_pad, x, EPI_RES, res=x)
             self._rows(x, Lr, W, W, m_pad, ln=b["ln2"])
             self._gemm(b["fc1"], Lr, m_pad, h, EPI_GELU_TANH)
             self._rows(h, Lr, b["fc1"].N, b["fc2"].K_pad, m_pad)
             self._gemm(b["fc2"], Lr, m_pad, x, EPI_RES, res=x)
-        if return_hidden:
-            F.scratch(d).check()
-            return x.clone()
+        if stop_at_hidden:
+            return
         # merger: four consecutive rows (one 2 x 2 neighbourhood) become one row of 4 * width values
         Lm = Lr // (cfg.merge ** 2)
         mm_pad = L.padded_rows(Lm)
@@ -151,9 +148,59 @@ class VisionTowerGPU:
         mh = self.mh[:Lm]
         self._gemm(self.m_fc1, Lm, mm_pad, mh, EPI_GELU_ERF)
         self._rows(mh, Lm, W4, W4, mm_pad)
-        if out is None:
-            out = torch.empty(Lm, cfg.out_hidden, dtype=torch.bfloat16, device=d)
-        assert out.shape[0] >= Lm and out.dtype == torch.bfloat16
         self._gemm(self.m_fc2, Lm, mm_pad, out)
+
+    @torch.no_grad()
+    def forward(self, pixel_values: torch.Tensor, grids: Sequence[tuple],
+                out: Optional[torch.Tensor] = None, return_hidden: bool = False,
+                graph: bool = False) -> torch.Tensor:
+        """`graph=True`: the launches of a grid list are captured once into a CUDA graph (static input
+        and output buffers, at most `max_graphs` shapes kept) and replayed afterwards."""
+        cfg, d = self.cfg, self.dev
+        grids = [tuple(g) for g in grids]
+        Lr = int(pixel_values.shape[0])
+        assert Lr == sum(t * h * w for t, h, w in grids) and Lr % (cfg.merge ** 2) == 0
+        if Lr > self.max_patches:
+            raise ValueError(f"{Lr} patch rows exceed the tower arena ({self.max_patches})")
+        Lm = Lr // (cfg.merge ** 2)
+        if out is None and not return_hidden:
+            out = torch.empty(Lm, cfg.out_hidden, dtype=torch.bfloat16, device=d)
+        assert return_hidden or (out.shape[0] >= Lm and out.dtype == torch.bfloat16)
+        if graph and not return_hidden:
+            self._replay(pixel_values, grids, Lr, out[:Lm])
+        else:
+            self._reserve(Lr)
+            px = pixel_values.to(d, non_blocking=True).float().contiguous()
+            self._run(px, Lr, self._meta(grids), out, return_hidden)
         F.scratch(d).check()
-        return out[:Lm]
+        return self.x[:Lr].clone() if return_hidden else out[:Lm]
+
+    max_graphs = 8
+
+    def _replay(self, pixel_values: torch.Tensor, grids: list, Lr: int, out: torch.Tensor) -> None:
+        cfg, d = self.cfg, self.dev
+        if not hasattr(self, "_graphs"):
+            self._reserve(self.max_patches)          # buffers never move under a captured graph
+            self._graphs = {}
+            self.px_buf = torch.empty(self.max_patches, cfg.patch_row, dtype=torch.float32, device=d)
+            self.out_buf = torch.empty(self.max_patches // cfg.merge ** 2, cfg.out_hidden, dtype=torch.bfloat16, device=d)
+        key = tuple(grids)
+        px, ob = self.px_buf[:Lr], self.out_buf[:out.shape[0]]
+        px.copy_(pixel_values, non_blocking=True)
+        ent = self._graphs.get(key)
+        if ent is None:
+            meta = self._meta(grids)
+            self._run(px, Lr, meta, ob, False)       # warm-up outside the capture (function attributes, allocator)
+            cur = torch.cuda.current_stream(d)
+            side = torch.cuda.Stream(device=d)
+            side.wait_stream(cur)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                self._run(px, Lr, meta, ob, False)
+            cur.wait_stream(side)
+            if len(self._graphs) >= self.max_graphs:
+                self._graphs.pop(next(iter(self._graphs)))
+            ent = self._graphs[key] = (g, meta)
+            self.graphs_captured = getattr(self, "graphs_captured", 0) + 1
+        ent[0].replay()
+        out.copy_(ob, non_blocking=True)

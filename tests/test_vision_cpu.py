@@ -86,7 +86,7 @@ def test_tower_metadata_shapes_and_merge_order():
     # row 2 is patch (1, 0) (second row of the first 2 x 2 block)
     assert np.isclose(sin[2, 0], np.sin(1.0)) and np.allclose(sin[2, 18:], 0.0)
     blocks = VT.attn_blocks([(1, 16, 16), (1, 4, 6)])
-    assert blocks.tolist() == [[0, 256, 0, 0], [0, 256, 128, 0], [256, 24, 0, 0]]
+    assert blocks.tolist() == [[0, 256, 0, 0], [0, 256, 64, 0], [0, 256, 128, 0], [0, 256, 192, 0], [256, 24, 0, 0]]
 
 
 def test_tower_reference_runs_and_is_image_local():

@@ -55,7 +55,11 @@ def test_tower_matches_cpu_restatement():
     assert got.shape == (Lr // 4, 256)
     err = (got - want).abs().max().item()
     assert err <= 3e-2 * want.abs().max().item() + 1e-3, err
-    assert tower.launches == 2 * (3 + 8 * cfg.depth) + 4        # two forwards; the first stops before the merger
+    assert tower.launches == 2 * (3 + 9 * cfg.depth) + 4        # two forwards; the first stops before the merger
+    # the captured form: same launches replayed from a CUDA graph, one graph per grid list
+    g1 = tower.forward(px, grids, graph=True).float().cpu()
+    g2 = tower.forward(px, grids, graph=True).float().cpu()
+    assert torch.equal(g1, got.float().cpu() if got.is_cuda else got) and torch.equal(g1, g2) and tower.graphs_captured == 1
 
 
 def test_image_prompt_through_scheduler_uses_tower_rows_and_three_axis_positions():
