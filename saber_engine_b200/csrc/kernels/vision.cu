@@ -131,11 +131,13 @@ __global__ void __launch_bounds__(kVisThreads) vis_rope_kernel(const VisAttnPara
 
 // ------------------------------------------------------------------------------------ attention
 // Non-causal attention inside one image on rotated q / k.  A CTA of four warps owns 64 query rows of
-// one head (16 per warp, the m16n8k16 tile); keys and values stream through shared memory 64 rows at
-// a time (keys row-major with the head dim padded to 80, values transposed so that two consecutive
-// keys of one dim are one 32-bit word); S = Q K^T and O += P V run on mma.sync with fp32
-// accumulators, the softmax is the running-maximum form in the base-2 domain.
-constexpr int kQRows = 64, kKT = 64, kKStride = 88, kVStride = 72;
+// one head (16 per warp, the m16n8k16 tile).  Keys and values stream through a double-buffered
+// shared-memory ring, 64 rows at a time, by 16-byte asynchronous copies (rows past the image are
+// zero filled); both stay row-major -- row strides of 176 and 144 bytes put the eight rows of an
+// 8 x 8 matrix load on eight different 16-byte bank groups -- and reach the MMA as ldmatrix
+// fragments (values through the transposing form).  S = Q K^T and O += P V run on mma.sync with
+// fp32 accumulators; the softmax is the running-maximum form in the base-2 domain.
+constexpr int kKT = 64, kKStride = 88, kVStride = 72;
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -148,17 +150,47 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
+__device__ __forceinline__ void vis_ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void vis_ldsm_x4_t(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void vis_ldsm_x2_t(uint32_t addr, uint32_t (&r)[2]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+               : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+// 16-byte asynchronous copy; src_bytes = 0 writes zeros
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
 
-__global__ void __launch_bounds__(kVisThreads) vis_attn_kernel(const VisAttnParams p) {
-  __shared__ __align__(16) __nv_bfloat16 k_s[kKT][kKStride];
-  __shared__ __align__(16) __nv_bfloat16 vt_s[kHd][kVStride];
+__global__ void __launch_bounds__(kVisThreads, 4) vis_attn_kernel(const VisAttnParams p) {
+  __shared__ __align__(16) __nv_bfloat16 k_s[2][kKT][kKStride];
+  __shared__ __align__(16) __nv_bfloat16 v_s[2][kKT][kVStride];
   pdl_wait();
   const int4 blk = p.blocks[blockIdx.x];
   const int seq0 = blk.x, len = blk.y, q0 = blk.z;
   const int h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  // the padding columns of the key tile are never written again
-  for (int i = threadIdx.x; i < kKT * 8; i += kVisThreads) k_s[i >> 3][kHd + (i & 7)] = __float2bfloat16(0.f);
+  // the padding columns (head dim 72 -> 80) of the key tiles are never written again
+  for (int i = threadIdx.x; i < 2 * kKT * 8; i += kVisThreads)
+    k_s[i >> 9][(i >> 3) & (kKT - 1)][kHd + (i & 7)] = __float2bfloat16(0.f);
+  const __nv_bfloat16* kbase = p.qkv + static_cast<size_t>(seq0) * p.ldq + p.width + h * kHd;
+  auto issue = [&](int tile, int buf) {
+    const int k0 = tile * kKT;
+    for (int i = threadIdx.x; i < kKT * 9; i += kVisThreads) {
+      const int j = i / 9, c = i - j * 9;               // key row of the tile, 8-value chunk of the head
+      const bool in = k0 + j < len;
+      const __nv_bfloat16* kp = kbase + static_cast<size_t>(in ? k0 + j : 0) * p.ldq + c * 8;
+      cp_async16(static_cast<uint32_t>(__cvta_generic_to_shared(&k_s[buf][j][c * 8])), kp, in ? 16 : 0);
+      cp_async16(static_cast<uint32_t>(__cvta_generic_to_shared(&v_s[buf][j][c * 8])), kp + p.width, in ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  issue(0, 0);
   // this warp's query fragments, straight from global memory (rows past the image read row 0, never stored)
   uint32_t qf[5][4];
   {
@@ -179,32 +211,35 @@ __global__ void __launch_bounds__(kVisThreads) vis_attn_kernel(const VisAttnPara
 #pragma unroll
   for (int j = 0; j < 9; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-  for (int k0 = 0; k0 < len; k0 += kKT) {
-    __syncthreads();                                    // the previous tile has been consumed
-    for (int i = threadIdx.x; i < kKT * 9; i += kVisThreads) {
-      const int j = i / 9, c = i - j * 9;               // key row of the tile, 8-value chunk of the head
-      uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-      if (k0 + j < len) {
-        const __nv_bfloat16* kp = p.qkv + static_cast<size_t>(seq0 + k0 + j) * p.ldq + p.width + h * kHd + c * 8;
-        kv = *reinterpret_cast<const uint4*>(kp);
-        vv = *reinterpret_cast<const uint4*>(kp + p.width);
-      }
-      *reinterpret_cast<uint4*>(&k_s[j][c * 8]) = kv;
-      const __nv_bfloat16* vb = reinterpret_cast<const __nv_bfloat16*>(&vv);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) vt_s[c * 8 + e][j] = vb[e];
+  const int ntiles = (len + kKT - 1) / kKT;
+  // ldmatrix lane addressing: keys (lane & 7) + 8 * (lane >> 4) and column half (lane >> 3) & 1 for
+  // the key operand; keys (lane & 7) + 8 * ((lane >> 3) & 1) and dim block (lane >> 4) for values
+  const int kr = (lane & 7) + (lane >> 4) * 8, kc = ((lane >> 3) & 1) * 8;
+  const int vr = (lane & 7) + ((lane >> 3) & 1) * 8, vc = (lane >> 4) * 8;
+  for (int it = 0; it < ntiles; ++it) {
+    const int buf = it & 1;
+    if (it + 1 < ntiles) {
+      issue(it + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    const int valid = min(kKT, len - k0);
+    const int valid = min(kKT, len - it * kKT);
+    const uint32_t kb = static_cast<uint32_t>(__cvta_generic_to_shared(&k_s[buf][0][0]));
+    const uint32_t vb = static_cast<uint32_t>(__cvta_generic_to_shared(&v_s[buf][0][0]));
     float s[8][4];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-      const __nv_bfloat16* kr = &k_s[nt * 8 + g][2 * t];
+    for (int np = 0; np < 4; ++np) {                    // pairs of 8-key score tiles
+      s[2 * np][0] = s[2 * np][1] = s[2 * np][2] = s[2 * np][3] = 0.f;
+      s[2 * np + 1][0] = s[2 * np + 1][1] = s[2 * np + 1][2] = s[2 * np + 1][3] = 0.f;
 #pragma unroll
-      for (int ks = 0; ks < 5; ++ks)
-        mma_bf16(s[nt], qf[ks], *reinterpret_cast<const uint32_t*>(kr + ks * 16),
-                 *reinterpret_cast<const uint32_t*>(kr + ks * 16 + 8));
+      for (int ks = 0; ks < 5; ++ks) {
+        uint32_t b[4];
+        vis_ldsm_x4(kb + static_cast<uint32_t>(((np * 16 + kr) * kKStride + ks * 16 + kc) * 2), b);
+        mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
+        mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
+      }
     }
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -241,12 +276,19 @@ __global__ void __launch_bounds__(kVisThreads) vis_attn_kernel(const VisAttnPara
       a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
       a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
       a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      const uint32_t vrow = vb + static_cast<uint32_t>(((kk * 16 + vr) * kVStride + vc) * 2);
 #pragma unroll
-      for (int j = 0; j < 9; ++j) {
-        const __nv_bfloat16* vr = &vt_s[j * 8 + g][kk * 16 + 2 * t];
-        mma_bf16(o[j], a, *reinterpret_cast<const uint32_t*>(vr), *reinterpret_cast<const uint32_t*>(vr + 8));
+      for (int jp = 0; jp < 4; ++jp) {                  // dim blocks 2jp and 2jp + 1
+        uint32_t b[4];
+        vis_ldsm_x4_t(vrow + jp * 32, b);
+        mma_bf16(o[2 * jp], a, b[0], b[1]);
+        mma_bf16(o[2 * jp + 1], a, b[2], b[3]);
       }
+      uint32_t b2[2];                                   // dim block 8 (lanes 16-31 repeat the addresses of 0-15)
+      vis_ldsm_x2_t(vb + static_cast<uint32_t>(((kk * 16 + vr) * kVStride + 64) * 2), b2);
+      mma_bf16(o[8], a, b2[0], b2[1]);
     }
+    __syncthreads();                                    // this buffer is refilled by the next iteration's copies
   }
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -257,15 +299,15 @@ __global__ void __launch_bounds__(kVisThreads) vis_attn_kernel(const VisAttnPara
 #pragma unroll
   for (int j = 0; j < 9; ++j) {
     const int ch = h * 9 + j;                           // 16-byte chunk of the output row (72 = 9 chunks per head)
-    const int kb = ch >> 3, chunk = ch & 7;
+    const int kbk = ch >> 3, chunk = ch & 7;
     if (r0 < len) {
       const int mrow = seq0 + r0;
-      *reinterpret_cast<uint32_t*>(p.out_tiled + (static_cast<size_t>(kb) * p.M_pad + mrow) * 128 +
+      *reinterpret_cast<uint32_t*>(p.out_tiled + (static_cast<size_t>(kbk) * p.M_pad + mrow) * 128 +
                                    ((chunk ^ (mrow & 7)) << 4) + 4 * t) = pack_bf16(o[j][0] * i0, o[j][1] * i0);
     }
     if (r1 < len) {
       const int mrow = seq0 + r1;
-      *reinterpret_cast<uint32_t*>(p.out_tiled + (static_cast<size_t>(kb) * p.M_pad + mrow) * 128 +
+      *reinterpret_cast<uint32_t*>(p.out_tiled + (static_cast<size_t>(kbk) * p.M_pad + mrow) * 128 +
                                    ((chunk ^ (mrow & 7)) << 4) + 4 * t) = pack_bf16(o[j][2] * i1, o[j][3] * i1);
     }
   }
