@@ -751,12 +751,14 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   }
   // long row runs of 4-bit weights: two token tiles per CTA (pairs must be whole inside M_pad)
   q.mtiles = 1;
-  if (p->mtiles >= 0 && !p->group_tiles && p->splits == 1 && widen_l && p->nt == 128 && p->M > 128 &&
+  if (p->mtiles >= 0 && !p->group_tiles && p->splits == 1 && (widen_l || p->w4 == 3) && p->nt == 128 && p->M > 128 &&
       (p->M_pad / 128) % 2 == 0 && p->ag_flags == nullptr) {
-    const int wb = p->w4 == 2 ? 17408 : 16384;
+    // (bf16 weights pass through unwidened: no operand buffers, the 32 KiB stage feeds the MMA directly)
+    const int wb = p->w4 == 2 ? 17408 : (p->w4 == 3 ? 32768 : 16384);
+    const int ubytes = widen_l ? 2 * 32768 : 0;
     int st2 = 3;
-    while (st2 > 2 && st2 * (wb + 2 * 16384) + 2 * 32768 + 1024 > kSmemLimit) --st2;
-    const int smem2 = st2 * (wb + 2 * 16384) + 2 * 32768 + 1024;
+    while (st2 > 2 && st2 * (wb + 2 * 16384) + ubytes + 1024 > kSmemLimit) --st2;
+    const int smem2 = st2 * (wb + 2 * 16384) + ubytes + 1024;
     if (smem2 <= kSmemLimit) {
       q.mtiles = 2;
       dim3 grid2(p->N_pad / 256, (p->M + 255) / 256, 1);

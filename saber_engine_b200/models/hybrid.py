@@ -96,6 +96,8 @@ class Bucket:
     keep: list = field(default_factory=list)
     arenas: list = field(default_factory=list)     # pure activation buffers: written before read in every step
     digests: Optional[torch.Tensor] = None         # int64 [n_layers + 1] stage digests (race_check = "shadow")
+    seam_dev: Optional[torch.Tensor] = None        # int32 blob: ids [Mh*64] | values [Mh*64] fp32 bits | lse [Mh*2] (seam buckets)
+    seam_host: Optional[torch.Tensor] = None       # pinned mirror
 
 
 class HybridModel:
@@ -237,10 +239,13 @@ class HybridModel:
         return sorted({min(L_ - 1, max(1, round((k + 1) * L_ / (n + 1)))) for k in range(n)}) if n else []
 
     # ------------------------------------------------------------------------------ build
-    def build_bucket(self, kind: str, nseq: int, width: int, capture: bool = True) -> Bucket:
+    def build_bucket(self, kind: str, nseq: int, width: int, capture: bool = True, seam: bool = False) -> Bucket:
         """kind='decode': nseq sequences x width rows.  kind='prefill': up to nseq sequences packed in
         `width` rows in total (ragged through cu_rows), rows committed."""
-        key = (kind, nseq, width)
+        # seam = True: the program also leaves the 64 best logits of every head row (ids, values,
+        # log-sum-exp) for the host sampler; a bucket of its own so that greedy steps do not pay for it
+        key = (kind, nseq, width, "seam") if seam else (kind, nseq, width)
+        self._bucket_key, self._want_seam = key, seam
         if key in self.buckets:
             return self.buckets[key]
         cfg, sh, dev = self.cfg, self.sh, self.device
@@ -415,6 +420,15 @@ class HybridModel:
             pm = self.comm.pick_merge_params(o_picks, pick_val, Mh, ar_site)
             prog.pick_merge(pm, tag="pick_merge")
             ar_site += 1
+        seam_dev = None
+        if self._want_seam:
+            # one int32 blob so that the read-back is one copy: ids | values (fp32 bits) | lse pairs
+            seam_dev = torch.zeros(Mh * (2 * N.SEAM_K + 2), dtype=torch.int32, device=dev)
+            s_ids = seam_dev[:Mh * N.SEAM_K]
+            s_vals = seam_dev[Mh * N.SEAM_K: 2 * Mh * N.SEAM_K].view(torch.float32)
+            s_lse = seam_dev[2 * Mh * N.SEAM_K:].view(torch.float32)
+            prog.seam(logits, Mh, logits.stride(0), sh.vocab, sh.vocab_first, None, s_ids, s_vals, s_lse, tag="topk_seam")
+            keep += [seam_dev]
         if decode:
             vp = N.VerifyParams()
             vp.draft, vp.target, vp.cu_rows = at(lay.ids), o_picks.data_ptr(), at(lay.cu_rows)
@@ -427,7 +441,7 @@ class HybridModel:
         else:
             acc_ptr, bonus_ptr = at(lay.last_rows), o_picks.data_ptr()
         keep += [out, accept_row, bonus, pick_val, logits]
-        self._last_head = dict(out=out, logits=logits, W=W, block=block, Mh=Mh)
+        self._last_head = dict(out=out, logits=logits, W=W, block=block, Mh=Mh, seam=seam_dev)
         if self.use_drafter:
             self._build_drafter(prog, nseq, M, tap_buf, taps, acc_ptr, bonus_ptr, o_drafts, keep)
         if self.tp > 1:
@@ -478,6 +492,8 @@ class HybridModel:
         b = Bucket(kind, nseq, width, M, lay, prog, blob, blob_host, out, out_host,
                    n_launches=prog.declared_launches, logits=head["logits"], keep=keep)
         b.W, b.block, b.Mh = head["W"], head["block"], head["Mh"]
+        b.seam_dev = head.get("seam")
+        b.seam_host = torch.zeros(b.seam_dev.numel(), dtype=torch.int32).pin_memory() if b.seam_dev is not None else None
         if capture:
             # one eager walk first: sets function attributes and warms lazy module loading
             with torch.cuda.stream(self.stream):
@@ -487,7 +503,7 @@ class HybridModel:
                 prog.capture(self.stream)
             self.stream.synchronize()
             b.captured = True
-        self.buckets[(kind, nseq, width)] = b
+        self.buckets[self._bucket_key] = b
         return b
 
 
@@ -563,6 +579,8 @@ def run_bucket(model: "HybridModel", b: Bucket, seqs: list, eager: bool = False)
         else:
             b.program.run(st)
         b.out_host.copy_(b.out_dev, non_blocking=True)
+        if getattr(b, "seam_dev", None) is not None:
+            b.seam_host.copy_(b.seam_dev, non_blocking=True)
     st.synchronize()
     return parse_result(b, len(seqs))
 

@@ -16,6 +16,41 @@ from ..models.hybrid import HybridModel, SeqStep, run_bucket
 from ..sched.buckets import DEFAULT_DECODE_BATCHES, DEFAULT_PREFILL_RUNGS, select_batch, select_rung
 from ..sched.executor import SeqOut, SeqRun
 
+N_SEAM_K = 64
+
+
+def merge_rank_seams(ids, vals, lse):
+    """ids / vals [ranks, rows, K] (each rank's best K of its vocabulary shard, value desc), lse
+    [ranks, rows] -> the best K of the union (value desc, id asc) and the log-sum-exp of the whole row."""
+    import numpy as np
+    R, M, K = ids.shape
+    ai = np.transpose(ids, (1, 0, 2)).reshape(M, R * K)
+    av = np.transpose(vals, (1, 0, 2)).reshape(M, R * K)
+    order = np.lexsort((ai, -av), axis=1)[:, :K]
+    top = lse.max(axis=0)
+    return (np.take_along_axis(ai, order, 1), np.take_along_axis(av, order, 1),
+            top + np.log(np.exp(lse - top[None]).sum(axis=0)))
+
+
+def gather_rank_seams(ids, vals, lse, device):
+    """All-gather of the ranks' seams (a small NCCL collective outside the captured program: only steps
+    with a sampled request pay for it), merged identically on every rank."""
+    import numpy as np
+    import torch.distributed as dist
+    if not dist.is_initialized():
+        raise RuntimeError("sampled requests on vocabulary-sharded ranks need torch.distributed")
+    M, K = ids.shape
+    mine = torch.cat([torch.from_numpy(np.ascontiguousarray(ids)).view(torch.int32).reshape(-1),
+                      torch.from_numpy(np.ascontiguousarray(vals)).view(torch.int32).reshape(-1),
+                      torch.from_numpy(np.ascontiguousarray(lse)).view(torch.int32).reshape(-1)]).to(device)
+    world = dist.get_world_size()
+    allr = torch.empty(world * mine.numel(), dtype=torch.int32, device=device)
+    dist.all_gather_into_tensor(allr, mine)
+    a = allr.cpu().numpy().reshape(world, -1)
+    return merge_rank_seams(a[:, :M * K].reshape(world, M, K),
+                            a[:, M * K: 2 * M * K].view(np.float32).reshape(world, M, K),
+                            a[:, 2 * M * K:].view(np.float32).reshape(world, M))
+
 
 class HybridExecutor:
     def __init__(self, model: HybridModel, decode_batches=DEFAULT_DECODE_BATCHES, decode_widths=(1, 5, 8),
@@ -39,11 +74,25 @@ class HybridExecutor:
             for r in self.prefill_rungs:
                 self._bucket("prefill", self.prefill_pack, r)
 
-    def _bucket(self, kind: str, nseq: int, width: int):
-        key = (kind, nseq, width)
+    def _bucket(self, kind: str, nseq: int, width: int, seam: bool = False):
+        key = (kind, nseq, width, "seam") if seam else (kind, nseq, width)
         if key not in self.model.buckets:
             self.census["buckets_built"] += 1
-        return self.model.build_bucket(kind, nseq, width, capture=self.capture)
+        return self.model.build_bucket(kind, nseq, width, capture=self.capture, seam=seam)
+
+    def _seams(self, b, rows_of: list) -> list:
+        """Per run: {"ids", "vals", "lse"} over the run's head rows, from the bucket's read-back blob;
+        with vocabulary-sharded ranks the per-rank candidates are gathered and merged first."""
+        import numpy as np
+        K, Mh = N_SEAM_K, b.Mh
+        a = b.seam_host.numpy()
+        ids = a[:Mh * K].reshape(Mh, K)
+        vals = a[Mh * K: 2 * Mh * K].view(np.float32).reshape(Mh, K)
+        lse = a[2 * Mh * K:].view(np.float32).reshape(Mh, 2)[:, 0]
+        if self.model.tp > 1:
+            ids, vals, lse = gather_rank_seams(ids, vals, lse, self.model.device)
+        return [{"ids": ids[r0:r1].tolist(), "vals": vals[r0:r1].tolist(), "lse": lse[r0:r1].tolist()}
+                for r0, r1 in rows_of]
 
     def reset_slot(self, slot: int) -> None:
         self.model.reset_slot(slot)
@@ -59,17 +108,23 @@ class HybridExecutor:
 
     def prefill(self, runs: list) -> list:
         rows = sum(len(r.tokens) for r in runs)
-        b = self._bucket("prefill", max(self.prefill_pack, len(runs)), select_rung(rows, self.prefill_rungs))
+        want = any(r.want_seam and r.last_chunk for r in runs)
+        b = self._bucket("prefill", max(self.prefill_pack, len(runs)), select_rung(rows, self.prefill_rungs), seam=want)
         res = run_bucket(self.model, b, [self._step(r) for r in runs])
         self._count(b)
-        return [SeqOut([res.tokens[j][0]] if r.last_chunk else [], res.drafts[j] if r.last_chunk else [])
+        seams = self._seams(b, [(j, j + 1) for j in range(len(runs))]) if want else [None] * len(runs)
+        return [SeqOut([res.tokens[j][0]] if r.last_chunk else [], res.drafts[j] if r.last_chunk else [],
+                       seam=seams[j] if (r.want_seam and r.last_chunk) else None)
                 for j, r in enumerate(runs)]
 
     def decode(self, runs: list, width: int) -> list:
-        b = self._bucket("decode", select_batch(len(runs), self.decode_batches), width)
+        want = any(r.want_seam for r in runs)
+        b = self._bucket("decode", select_batch(len(runs), self.decode_batches), width, seam=want)
         res = run_bucket(self.model, b, [self._step(r) for r in runs])
         self._count(b)
-        return [SeqOut(res.tokens[j], res.drafts[j]) for j in range(len(runs))]
+        seams = self._seams(b, [(j * width, (j + 1) * width) for j in range(len(runs))]) if want else [None] * len(runs)
+        return [SeqOut(res.tokens[j], res.drafts[j], seam=seams[j] if runs[j].want_seam else None)
+                for j in range(len(runs))]
 
     # ---- prefix-cache snapshots (device resident)
     def snapshot_state(self, slot: int):

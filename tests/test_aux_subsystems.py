@@ -190,3 +190,21 @@ def test_prompt_store_survives_restart_and_obeys_the_crash_law(tmp_path):
     st = PromptStore(str(tmp_path), min_tokens=64)
     assert st.counters["dropped_at_boot"] >= 2 and files[0].stem not in st.records
     assert not any(p.name.startswith(".") for p in tmp_path.iterdir())      # no temporary files left behind
+
+
+def test_rank_seams_merge_to_the_seam_of_the_whole_vocabulary():
+    import numpy as np
+    from saber_engine_b200.runtime.hybrid_executor import merge_rank_seams
+    rng = np.random.default_rng(0)
+    full = rng.normal(size=(3, 400)).astype(np.float32)
+    ids, vals, lse = [], [], []
+    for r in range(4):
+        sh = full[:, r * 100:(r + 1) * 100]
+        o = np.argsort(-sh, axis=1)[:, :8]
+        ids.append(o + r * 100)
+        vals.append(np.take_along_axis(sh, o, 1))
+        lse.append(np.log(np.exp(sh).sum(1)))
+    i, v, l = merge_rank_seams(np.stack(ids), np.stack(vals), np.stack(lse))
+    want = np.argsort(-full, axis=1)[:, :8]
+    assert (i == want).all() and np.allclose(v, np.take_along_axis(full, want, 1))
+    assert np.allclose(l, np.log(np.exp(full).sum(1)), atol=1e-5)

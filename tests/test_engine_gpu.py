@@ -94,3 +94,34 @@ def test_park_and_restore_on_the_device_resumes_with_the_same_ids(executor, tmp_
     s.restore(key)
     s.run_until_idle()
     assert _collect(sub)[0] == want
+
+
+def test_sampled_requests_draw_from_the_device_seam(executor):
+    """Sampled requests on the real engine: the head leaves the 64 best logits per row, the host
+    sampler draws from them; top_k = 1 equals greedy, a seed fixes the ids, another seed moves them."""
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, executor.vocab, (90,), generator=g).tolist()
+    from saber_engine_b200.serve.sampler import HostSampler
+
+    def run(**kw):
+        s = Scheduler(executor, SchedulerConfig(max_seqs=4, max_ctx=2048, prefix_cache=False), sampler=HostSampler())
+        sub = s.submit(EngineRequest(prompt, SamplingParams(max_tokens=12, ignore_eos=True, **kw)))
+        s.run_until_idle()
+        return _collect(sub)[0]
+    greedy = run()
+    assert run(temperature=1.0, top_k=1, seed=3) == greedy
+    a, b, c = run(temperature=1.5, seed=11), run(temperature=1.5, seed=11), run(temperature=1.5, seed=12)
+    assert a == b and len(a) == 12
+    assert a != greedy or c != greedy          # flat random-init logits: a hot draw leaves the greedy path
+    # the seam itself against the logits the program left behind
+    bkt = executor._bucket("decode", 1, 5, seam=True)
+    import numpy as np
+    K, Mh = 64, bkt.Mh
+    arr = bkt.seam_host.numpy()
+    ids = torch.from_numpy(arr[:Mh * K].reshape(Mh, K).astype(np.int64))
+    vals = torch.from_numpy(arr[Mh * K:2 * Mh * K].view(np.float32).reshape(Mh, K).copy())
+    lse = torch.from_numpy(arr[2 * Mh * K:].view(np.float32).reshape(Mh, 2)[:, 0].copy())
+    logits = bkt.logits[:, :executor.vocab].float().cpu()
+    tv, _ = torch.topk(logits, K, dim=-1)
+    assert torch.equal(vals, tv) and torch.equal(logits.gather(1, ids), vals)
+    assert torch.allclose(lse, torch.logsumexp(logits, -1), atol=1e-3)

@@ -11,7 +11,8 @@ def _bf(x):
     return x.to(torch.bfloat16).float()
 
 
-@pytest.mark.parametrize("M,N,K,epi", [(40, 1152, 1536, 0), (300, 4304, 1152, 1), (352, 1152, 4304, 3), (96, 520, 4608, 2)])
+@pytest.mark.parametrize("M,N,K,epi", [(40, 1152, 1536, 0), (300, 4304, 1152, 1), (352, 1152, 4304, 3), (96, 520, 4608, 2),
+                                         (512, 1152, 1152, 3), (1000, 3456, 1152, 1)])
 def test_bf16_gemm_mode_bias_activation_residual(M, N, K, epi):
     from saber_engine_b200.ops import functional as F, layouts as L, native as N_
     from saber_engine_b200.vision.tower_gpu import VisionTowerGPU, _Lin
