@@ -65,7 +65,9 @@ __device__ __forceinline__ float gelu_f(float x, bool erf_form) {
 // two operand buffers instead of three, at most 102 registers -- so that TWO CTAs share an SM: an
 // expert tile is only 16 k-blocks long, and the second CTA's main loop hides the first one's
 // start-up latency (cold weights: 3-4 us to the first MMA) and epilogue.
-template <bool kLean>
+// kBf: the bf16 x bf16 instantiation (optional scales, bias, activation / residual epilogue); the
+// integer and MXFP4 instantiations compile none of it.
+template <bool kLean, bool kBf = false>
 __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int stages) {
   const int nub = (kLean || p.mtiles == 2) ? 2 : kUBufs;     // operand buffers in use
   extern __shared__ uint8_t smem_raw[];
@@ -74,7 +76,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
   __shared__ uint32_t is_last_s;
   __shared__ uint32_t abort_s;
   __shared__ float w_scale_s[256];
-  __shared__ float bias_s[256];
+  __shared__ float bias_s[kBf ? 256 : 1];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -116,9 +118,9 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
   const int n0 = tile_n * 256;
   // weight formats: 0 = int8 tiles, 1 = packed int4, 2 = MXFP4 (packed e2m1 + 1 KiB of block shifts)
   // 3 = bf16 x bf16: both operands pass through like int8 tiles (K counted in bytes), fp32 accumulators
-  const bool mx = p.w4 == 2;
-  const bool bf = p.w4 == 3;
-  const bool widen = p.w4 == 1 || mx;
+  const bool mx = !kBf && p.w4 == 2;
+  constexpr bool bf = kBf;
+  const bool widen = !kBf && p.w4 != 0;
   const uint32_t wbytes = mx ? 17408u : (widen ? 16384u : 32768u);
   const uint32_t abytes = static_cast<uint32_t>(p.nt) * 128u * static_cast<uint32_t>(mt2);
 
@@ -285,9 +287,13 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
     const int q4 = warp & 3;                     // TMEM lane quarter this warp may access
     bool ok = true;
     if (tgroup == 0) {  // epilogue warps stage the per-feature scales while the pipeline fills
-      for (int j = tid_t; j < 256; j += 128) {
-        w_scale_s[j] = (n0 + j < p.N) ? (p.w_scale ? w_scale_base[n0 + j] : 1.f) : 0.f;
-        bias_s[j] = (p.bias && n0 + j < p.N) ? p.bias[n0 + j] : 0.f;
+      if constexpr (kBf) {
+        for (int j = tid_t; j < 256; j += 128) {
+          w_scale_s[j] = (n0 + j < p.N) ? (p.w_scale ? w_scale_base[n0 + j] : 1.f) : 0.f;
+          bias_s[j] = (p.bias && n0 + j < p.N) ? p.bias[n0 + j] : 0.f;
+        }
+      } else {
+        for (int j = tid_t; j < 256; j += 128) w_scale_s[j] = (n0 + j < p.N) ? w_scale_base[n0 + j] : 0.f;
       }
     }
     if (widen) {
@@ -431,7 +437,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         if (!kLean && p.tp_rpr > 0) tp_owner = mb / p.tp_rpr;
         if (j2) named_bar_sync(1, 128);            // the staging buffer is free again
         if (warp_livej) {
-          const float asc = livej ? (p.a_scale ? p.a_scale[mb + row] : 1.f) : 0.f;
+          const float asc = livej ? ((!kBf || p.a_scale) ? p.a_scale[mb + row] : 1.f) : 0.f;
           for (int c = 0; c < ncols; c += 32) {
             uint32_t r[32];
             tmem_ld32(tl + c, r);
@@ -440,12 +446,15 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
               uint32_t pk[16];
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
-                const float lo = acc_f(r[2 * j]) * (asc * w_scale_s[c + 2 * j]) + bias_s[c + 2 * j];
-                const float hi = acc_f(r[2 * j + 1]) * (asc * w_scale_s[c + 2 * j + 1]) + bias_s[c + 2 * j + 1];
+                float lo = acc_f(r[2 * j]) * (asc * w_scale_s[c + 2 * j]);
+                float hi = acc_f(r[2 * j + 1]) * (asc * w_scale_s[c + 2 * j + 1]);
+                if constexpr (kBf) { lo += bias_s[c + 2 * j]; hi += bias_s[c + 2 * j + 1]; }
                 __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
-                if (p.epi == 1 || p.epi == 2) {   // the activation works on the rounded linear output
-                  const float2 y = __bfloat1622float2(b2);
-                  b2 = __floats2bfloat162_rn(gelu_f(y.x, p.epi == 2), gelu_f(y.y, p.epi == 2));
+                if constexpr (kBf) {
+                  if (p.epi == 1 || p.epi == 2) {   // the activation works on the rounded linear output
+                    const float2 y = __bfloat1622float2(b2);
+                    b2 = __floats2bfloat162_rn(gelu_f(y.x, p.epi == 2), gelu_f(y.y, p.epi == 2));
+                  }
                 }
                 pk[j] = *reinterpret_cast<const uint32_t*>(&b2);
               }
@@ -472,7 +481,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
                          : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                          : "r"(stage_s + rw * 512 + (chunk << 4)));
             if (!col_ok || col >= ncols) continue;
-            if (p.epi == 3 && p.res != nullptr) {     // residual add on the rounded linear output
+            if (kBf && p.epi == 3 && p.res != nullptr) {     // residual add on the rounded linear output
               const __nv_bfloat16* rp = p.res + static_cast<size_t>(mb + rw) * p.ldo + n0 + col;
               __nv_bfloat16* pv = reinterpret_cast<__nv_bfloat16*>(&v);
               if (full) {
@@ -672,6 +681,9 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
 __global__ void __launch_bounds__(kGemmThreads) gemm_i8_kernel(const GemmI8Params p, const int stages) {
   gemm_i8_body<false>(p, stages);
 }
+__global__ void __launch_bounds__(kGemmThreads) gemm_bf16_kernel(const GemmI8Params p, const int stages) {
+  gemm_i8_body<false, true>(p, stages);
+}
 __global__ void __launch_bounds__(kGemmThreads, 2) gemm_i8_lean_kernel(const GemmI8Params p, const int stages) {
   gemm_i8_body<true>(p, stages);
 }
@@ -716,7 +728,7 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   const int kSmemLimit = 224 * 1024;  // opt-in maximum minus the kernel's static shared memory
   const bool widen_l = p->w4 == 1 || p->w4 == 2;
   if (p->w4 < 0 || p->w4 > 3 || (p->w4 == 3 && (p->splits != 1 || p->group_tiles))) return static_cast<int>(cudaErrorInvalidValue);
-  if ((p->bias || p->epi) && p->splits != 1) return static_cast<int>(cudaErrorInvalidValue);
+  if ((p->bias || p->epi) && p->w4 != 3) return static_cast<int>(cudaErrorInvalidValue);   // bias / activation / residual: bf16 mode only
   if (stages <= 0) stages = widen_l ? 8 : 5;   // one CTA per SM, as deep a ring as fits
   if (stages < 2) stages = 2;
   if (stages > kMaxStages) stages = kMaxStages;
@@ -726,6 +738,7 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(gemm_i8_lean_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemLimit);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -762,10 +775,10 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
     if (smem2 <= kSmemLimit) {
       q.mtiles = 2;
       dim3 grid2(p->N_pad / 256, (p->M + 255) / 256, 1);
-      return static_cast<int>(saber::launch(gemm_i8_kernel, grid2, dim3(kGemmThreads), smem2, stream, 2, q, st2));
+      return static_cast<int>(saber::launch(p->w4 == 3 ? gemm_bf16_kernel : gemm_i8_kernel, grid2, dim3(kGemmThreads), smem2, stream, 2, q, st2));
     }
   }
-  return static_cast<int>(saber::launch(gemm_i8_kernel, grid, dim3(kGemmThreads), smem, stream, (q.coop != 0 ? 1 : 0) | 2, q, stages));
+  return static_cast<int>(saber::launch(p->w4 == 3 ? gemm_bf16_kernel : gemm_i8_kernel, grid, dim3(kGemmThreads), smem, stream, (q.coop != 0 ? 1 : 0) | 2, q, stages));
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -61,7 +61,7 @@ struct GemmI8Params {
   // k-block holds 64 values; K is the reduction length in BYTES), fp32 accumulation, scales optional
   // (null = 1).  y = bf16(acc + bias[n]); then epi 1: gelu_tanh(y), 2: gelu_erf(y), 3: y + res[m][n]
   // (res has out's row stride and may alias out), each rounded to bf16 once more.
-  const float* bias;           // [N] or null (any mode with splits == 1)
+  const float* bias;           // [N] or null
   const __nv_bfloat16* res;    // epi 3
   int epi;
 };
