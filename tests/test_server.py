@@ -130,3 +130,52 @@ def test_parsers_and_detok():
     ids = tok.encode("héllo")
     assert d.push(ids[:2]) == "h" and d.push(ids[2:]) == "éllo"       # never splits a UTF-8 sequence
     assert "<|im_start|>user\nhi<|im_end|>" in render_chat([{"role": "user", "content": "hi"}])
+
+
+def test_chat_request_with_an_image_part_reaches_the_engine_with_image_rows():
+    """An image_url part (data URL) goes through the processor and the request builder: placeholders
+    become rows of the image arena, three-axis positions ride with the request, the rows are freed
+    when the request ends; a server without a tower answers 400."""
+    import base64
+    import io
+    from types import SimpleNamespace
+
+    import numpy as np
+    import torch
+    from PIL import Image
+
+    from saber_engine_b200.vision import processor as VP
+    from saber_engine_b200.vision.engine import VisionFrontend
+    tok = ByteCodec(300)
+    ex = NullExecutor(seed=2, vocab=1000)
+    ex.model = SimpleNamespace(cfg=SimpleNamespace(vocab=300), image_rows=128, stream=None,
+                               embed_table=torch.zeros(428, 8, dtype=torch.bfloat16))
+    sched = Scheduler(ex, SchedulerConfig(max_seqs=4, max_ctx=4096, model_name="mock"))
+    sched.spawn_step_loop()
+    seen = []
+    sub0 = sched.submit
+    sched.submit = lambda req: (seen.append(req), sub0(req))[1]
+    vis = VisionFrontend(ex, SimpleNamespace(max_patches=512), tok.special_ids["<|image_pad|>"],
+                         VP.ProcessorConfig(min_pixels=0), encode=lambda px, grids, rows: rows.fill_(0.5))
+    img = (np.arange(64 * 64 * 3) % 255).astype(np.uint8).reshape(64, 64, 3)
+    buf = io.BytesIO()
+    Image.fromarray(img).save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    body = {"model": "mock", "max_tokens": 5, "messages": [{"role": "user", "content": [
+        {"type": "text", "text": "what is this?"}, {"type": "image_url", "image_url": {"url": url}}]}]}
+    try:
+        c = TestClient(create_app(ServerState(sched, tok, model_name="mock", vision=vis)))
+        r = c.post("/v1/chat/completions", json=body)
+        assert r.status_code == 200, r.text
+        req = seen[-1]
+        rows = [t for t in req.prompt_token_ids if t >= 300]
+        assert rows == list(range(300, 304)) and req.mm["grids"] == [(1, 4, 4)]      # 64 x 64 -> 16 patches -> 4 tokens
+        assert r.json()["usage"]["prompt_tokens"] == len(req.prompt_token_ids)
+        assert vis.arena.free_rows == 128 and vis.counters["images"] == 1
+        c2 = TestClient(create_app(ServerState(sched, tok, model_name="mock")))
+        r2 = c2.post("/v1/chat/completions", json=body)
+        assert r2.status_code == 400 and "vision" in r2.json()["error"]["message"]
+        body["messages"][0]["content"][1]["image_url"]["url"] = "https://example.com/cat.png"
+        assert c.post("/v1/chat/completions", json=body).status_code == 400
+    finally:
+        sched.shutdown()
