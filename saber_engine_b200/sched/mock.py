@@ -63,10 +63,19 @@ class NullExecutor:
             self._write_kv(run)
             if run.last_chunk:
                 tok = _next_token(d, self.vocab)
-                outs.append(SeqOut([tok], self._propose(d, tok, max(self.decode_widths) - 1)))
+                outs.append(SeqOut([tok], self._propose(d, tok, max(self.decode_widths) - 1),
+                                   seam=self._seam([tok]) if run.want_seam else None))
             else:
                 outs.append(SeqOut([]))
         return outs
+
+    def _seam(self, picks: list, k: int = 8) -> dict:
+        """A stand-in for the head's candidate rows: the pick at logit 0, its successors one unit apart."""
+        import math
+        vals = [-float(i) for i in range(k)]
+        lse = math.log(sum(math.exp(v) for v in vals))
+        return {"ids": [[(t + i) % self.vocab for i in range(k)] for t in picks],
+                "vals": [list(vals) for _ in picks], "lse": [lse for _ in picks]}
 
     def _propose(self, digest: bytes, first: int, k: int) -> list:
         """Drafts for the tokens AFTER `first`: right with probability draft_hit_rate each."""
@@ -112,7 +121,8 @@ class NullExecutor:
             while len(digests) < width:
                 digests.append(b"stale")
             self._stash[run.slot] = digests
-            outs.append(SeqOut(toks, self._propose(digests[len(toks) - 1], toks[-1], width - 1)))
+            outs.append(SeqOut(toks, self._propose(digests[len(toks) - 1], toks[-1], width - 1),
+                               seam=self._seam(toks) if run.want_seam else None))
         return outs
 
     # ---- prefix-cache hooks

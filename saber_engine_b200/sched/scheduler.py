@@ -231,7 +231,7 @@ class Scheduler:
                 if plan[0] == "prefill":
                     runs = [SeqRun(s.seq_id, s.prompt[pos:pos + n], pos, s.slot, 0, s.blocks, uid=s.seq_id,
                                    last_chunk=(pos + n == len(s.prompt)),
-                                   temperature=s.req.params.temperature, want_seam=not s.req.params.greedy,
+                                   temperature=s.req.params.temperature, want_seam=self._wants_seam(s),
                                    rope_pos=(None if s.req.mm is None else
                                              [list(ax[pos:pos + n]) for ax in s.req.mm["rope_pos"]]))
                             for s, pos, n in plan[1]]
@@ -243,7 +243,7 @@ class Scheduler:
                         drafts = (s.drafts + [0] * width)[: width - 1]
                         runs.append(SeqRun(s.seq_id, [s.output[-1]] + drafts, s.pos, s.slot, s.shift, s.blocks,
                                            uid=s.seq_id, step_no=s.step_no, temperature=s.req.params.temperature,
-                                           want_seam=not s.req.params.greedy,
+                                           want_seam=self._wants_seam(s),
                                            rope_delta=(0 if s.req.mm is None else int(s.req.mm.get("rope_delta", 0)))))
                     outs = self.ex.decode(runs, width)
         except Exception as exc:       # the executor failed: every request learns why (fatal law)
@@ -326,7 +326,7 @@ class Scheduler:
                 s.drafts = list(out.drafts)
                 s.shift = 0
                 s.t_first = time.monotonic()
-                self._append(s, [tok], dt, first=True)
+                self._append(s, [tok], dt, first=True, lps=self._logprobs(s, out, [tok], 0))
 
     def _commit_decode(self, dec, width, batch, outs, dt) -> None:
         self.counters["decode_steps"] += 1
@@ -347,7 +347,32 @@ class Scheduler:
             s.shift = n
             s.step_no += 1
             s.drafts = list(out.drafts)
-            self._append(s, toks, dt, drafted=width - 1, accepted=n - 1)
+            self._append(s, toks, dt, drafted=width - 1, accepted=n - 1, lps=self._logprobs(s, out, toks, 0))
+
+    @staticmethod
+    def _wants_seam(s: Sequence) -> bool:
+        return (not s.req.params.greedy) or s.req.params.logprobs is not None
+
+    @staticmethod
+    def _logprobs(s: Sequence, out: SeqOut, toks: list, row0: int) -> Optional[list]:
+        """Per committed token: its log-probability and the `logprobs` most likely alternatives, from
+        the seam row that produced it (log-softmax at temperature 1 over the whole vocabulary: value
+        minus the row's log-sum-exp).  A token outside the 64 candidates gets the floor of the seam."""
+        n = s.req.params.logprobs
+        if n is None or out.seam is None:
+            return None
+        res = []
+        for j, t in enumerate(toks):
+            r = row0 + j
+            if r >= len(out.seam["ids"]):
+                break
+            ids, vals = out.seam["ids"][r], out.seam["vals"][r]
+            lse = out.seam["lse"][r]
+            lse = lse[0] if isinstance(lse, (list, tuple)) else lse
+            lp = (vals[ids.index(t)] if t in ids else vals[-1]) - lse
+            res.append({"token_id": int(t), "logprob": float(lp),
+                        "top": [(int(i), float(v - lse)) for i, v in list(zip(ids, vals))[:n]]})
+        return res
 
     def _choose(self, s: Sequence, out: SeqOut, row: int, greedy_tok: int) -> int:
         if s.req.params.greedy or self.sampler is None or out.seam is None:
@@ -369,7 +394,7 @@ class Scheduler:
         return toks
 
     def _append(self, s: Sequence, toks: list, dt: float, first: bool = False, drafted: int = 0,
-                accepted: int = 0) -> None:
+                accepted: int = 0, lps: Optional[list] = None) -> None:
         p = s.req.params
         kept, reason = [], None
         for t in toks:
@@ -389,7 +414,8 @@ class Scheduler:
         self.counters["generation_tokens"] += len(kept)
         ev = StepEvent(s.seq_id, kept, reason is not None, reason, prompt_tokens=len(s.prompt),
                        cached_tokens=s.cached_tokens, n_drafted=drafted, n_accepted=accepted,
-                       step_time_s=dt, first_token=first)
+                       step_time_s=dt, first_token=first,
+                       logprobs=(lps[:len(kept)] if lps is not None else None))
         if reason:
             self._finish(s, reason, ev)
         else:

@@ -250,6 +250,20 @@ def create_app(state: ServerState) -> FastAPI:
                     state.metrics.inc("request_success_total" if ev.finish_reason in ("stop", "length") else "request_refused_total")
                     return
 
+        lp_items = []     # per generated token: {"token_id", "logprob", "top"} from the engine's candidate rows
+
+        def lp_chat(items):
+            def one(tid, lp):
+                bs = state.tok.token_bytes(tid)
+                return {"token": bs.decode("utf-8", errors="replace"), "logprob": lp, "bytes": list(bs)}
+            return {"content": [{**one(it["token_id"], it["logprob"]),
+                                 "top_logprobs": [one(i, v) for i, v in it["top"][: (params.logprobs or 0)]]} for it in items]}
+
+        def lp_text(items):
+            tk = lambda t: state.tok.token_bytes(t).decode("utf-8", errors="replace")   # noqa: E731
+            return {"tokens": [tk(it["token_id"]) for it in items], "token_logprobs": [it["logprob"] for it in items],
+                    "top_logprobs": [{tk(i): v for i, v in it["top"][: (params.logprobs or 0)]} for it in items]}
+
         def usage(ev):
             return {"prompt_tokens": len(prompt_ids), "completion_tokens": rec["completion_tokens"],
                     "total_tokens": len(prompt_ids) + rec["completion_tokens"],
@@ -281,6 +295,8 @@ def create_app(state: ServerState) -> FastAPI:
                         choice = {"index": 0, "delta": delta, "finish_reason": ev.finish_reason if ev.finished else None}
                     else:
                         choice = {"index": 0, "text": text, "finish_reason": ev.finish_reason if ev.finished else None}
+                    if ev.logprobs:
+                        choice["logprobs"] = lp_chat(ev.logprobs) if chat else lp_text(ev.logprobs)
                     first = False
                     yield "data: " + json.dumps({"id": rid, "object": obj + ".chunk" if chat else obj, "created": created,
                                                  "model": state.model_name, "choices": [choice]}) + "\n\n"
@@ -294,6 +310,8 @@ def create_app(state: ServerState) -> FastAPI:
         async for ev, text in events():
             full += text
             last = ev
+            if ev.logprobs:
+                lp_items.extend(ev.logprobs)
         if last is not None and last.finish_reason == "error":
             return _err(503, last.error or "engine error", "service_unavailable")
         if chat:
@@ -314,6 +332,8 @@ def create_app(state: ServerState) -> FastAPI:
             choice = {"index": 0, "message": msg, "finish_reason": finish}
         else:
             choice = {"index": 0, "text": full, "finish_reason": last.finish_reason}
+        if params.logprobs is not None:
+            choice["logprobs"] = lp_chat(lp_items) if chat else lp_text(lp_items)
         return {"id": rid, "object": obj, "created": created, "model": state.model_name,
                 "choices": [choice], "usage": usage(last)}
 

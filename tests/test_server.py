@@ -179,3 +179,28 @@ def test_chat_request_with_an_image_part_reaches_the_engine_with_image_rows():
         assert c.post("/v1/chat/completions", json=body).status_code == 400
     finally:
         sched.shutdown()
+
+
+def test_logprobs_come_from_the_engine_candidate_rows(client):
+    body = {"model": "mock", "prompt": "abc", "max_tokens": 6, "temperature": 0, "logprobs": 3}
+    r = client.post("/v1/completions", json=body).json()
+    lp = r["choices"][0]["logprobs"]
+    assert len(lp["tokens"]) == 6 and len(lp["token_logprobs"]) == 6 and all(1 <= len(t) <= 3 for t in lp["top_logprobs"])   # (byte tokens that are not text alone share one key)
+    import math
+    want = -math.log(sum(math.exp(-i) for i in range(8)))         # the mock's pick sits at logit 0
+    assert all(abs(x - want) < 1e-6 for x in lp["token_logprobs"])
+    chat = {"model": "mock", "max_tokens": 4, "temperature": 0, "logprobs": True, "top_logprobs": 2,
+            "messages": [{"role": "user", "content": "hi"}]}
+    c = client.post("/v1/chat/completions", json=chat).json()["choices"][0]["logprobs"]["content"]
+    assert len(c) == 4 and all(len(x["top_logprobs"]) == 2 and x["top_logprobs"][0]["logprob"] == x["logprob"] for x in c)
+    # streaming: every chunk carries the entries of its own tokens
+    n = 0
+    with client.stream("POST", "/v1/completions", json={**body, "stream": True}) as s:
+        for line in s.iter_lines():
+            if line.startswith("data: {"):
+                ch = json.loads(line[6:])["choices"]
+                if ch and ch[0].get("logprobs"):
+                    n += len(ch[0]["logprobs"]["tokens"])
+    assert n == 6
+    # without the field nothing is attached (and the engine is not asked for candidate rows)
+    assert "logprobs" not in client.post("/v1/completions", json={"model": "mock", "prompt": "abc", "max_tokens": 2}).json()["choices"][0]
