@@ -370,12 +370,17 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         if (++u == nub) { u = 0; ufree_ph ^= 1u; }
       }
     }
-    if (tgroup == 0) {
-      // the four epilogue warps decide TOGETHER whether to run the epilogue: the named barriers
+    // Two token tiles per CTA: BOTH transform groups run the epilogue, one accumulator each (either
+    // group's four warps cover the four TMEM lane quarters), with their own staging buffer and their
+    // own named barrier.  Otherwise only the first group does.
+    const bool pair = !kLean && mt2 == 2;
+    const int ebar = 1 + (pair ? tgroup : 0);
+    if (tgroup == 0 || pair) {
+      // the epilogue warps decide TOGETHER whether to run the epilogue: the named barriers
       // below have no time limit, so no warp may skip one that the others enter
       if (ok) ok = mbar_wait(bar_acc, 0, p.err, kErrWaitAcc);
       if (!ok) abort_s = 1u;
-      named_bar_sync(1, 128);  // also publishes w_scale_s
+      if (pair) named_bar_sync(3, 256); else named_bar_sync(1, 128);  // also publishes w_scale_s
       ok = abort_s == 0u;
     } else {
       ok = false;  // only the first group (TMEM lane quarters 2,3,0,1) is the epilogue
@@ -414,7 +419,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
           *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.tp_recv[peer]) + off) = v;
       };
       auto tp_signal = [&](int tile_id) {   // called by all 128 epilogue threads after their stores
-        named_bar_sync(1, 128);             // every thread's pushes precede the barrier ...
+        named_bar_sync(ebar, 128);          // every thread's pushes precede the barrier ...
         if (tp_owner >= 0 ? tid_t == tp_owner : tid_t < p.tp_nranks) {
           __threadfence_system();           // ... and this fence is cumulative over what the barrier ordered
           uint32_t* f = p.tp_flags[tid_t] + (static_cast<size_t>(tp_par) * p.tp_nranks + p.tp_rank) * kTpMaxTiles + tile_id;
@@ -427,15 +432,18 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         // So the bf16 tile is first staged in shared memory -- the operand buffers are idle by
         // now -- with its 16-byte chunks XOR-swizzled by the row, then every warp writes whole
         // rows: 512 contiguous bytes per store instruction, to local memory or to every rank.
-        const uint32_t stage_s = widen ? u_smem : w_smem;     // >= 64 KiB in either mode
-        for (int j2 = 0; j2 < mt2; ++j2) {
+        // (pair mode: the first group stages in the token ring -- at least two 32 KiB stages --, the second
+        // in the operand buffers / weight ring)
+        const uint32_t stage_s = (pair && tgroup == 0) ? a_smem : (widen ? u_smem : w_smem);     // >= 64 KiB in every mode
+        const int j2_lo = pair ? tgroup : 0, j2_hi = pair ? tgroup + 1 : mt2;
+        for (int j2 = j2_lo; j2 < j2_hi; ++j2) {
         const int mb = m0 + j2 * p.nt;             // first row of this accumulator's token tile
         const int mtj = rows_here >= 0 ? rows_here : min(p.nt, p.M - mb);
         if (mtj <= 0) break;                       // (uniform) the second tile of a ragged pair is empty
         const bool livej = row < mtj, warp_livej = q4 * 32 < mtj;
         const uint32_t tl = t_lane + static_cast<uint32_t>(j2) * 256u;
         if (!kLean && p.tp_rpr > 0) tp_owner = mb / p.tp_rpr;
-        if (j2) named_bar_sync(1, 128);            // the staging buffer is free again
+        if (j2 > j2_lo) named_bar_sync(ebar, 128);   // the staging buffer is free again
         if (warp_livej) {
           const float asc = livej ? ((!kBf || p.a_scale) ? p.a_scale[mb + row] : 1.f) : 0.f;
           for (int c = 0; c < ncols; c += 32) {
@@ -468,7 +476,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
             }
           }
         }
-        named_bar_sync(1, 128);
+        named_bar_sync(ebar, 128);
         {
           const int wq = tid_t >> 5;                  // 0..3: rows wq, wq + 4, ...
           const int col = lane * 8;                   // this lane's 8 output features of the row

@@ -270,6 +270,27 @@ extern "C" int saber_topk_seam_launch(const void* logits, int rows, int ld, int 
   return static_cast<int>(cudaGetLastError());
 }
 
+namespace saber {
+// out[m] = logits[m][ids[m] - id_offset] as fp32, or -inf when ids[m] lies outside [id_offset, id_offset + V)
+// (a row without a successor carries -1).  One thread per row.
+__global__ void logit_gather_kernel(const __nv_bfloat16* logits, int ld, int V, int id_offset,
+                                    const int32_t* ids, float* out, int rows) {
+  pdl_wait();
+  const int m = blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= rows) return;
+  const int id = ids[m] - id_offset;
+  out[m] = (id >= 0 && id < V) ? __bfloat162float(logits[static_cast<size_t>(m) * ld + id]) : -INFINITY;
+}
+}  // namespace saber
+
+extern "C" int saber_logit_gather_launch(const void* logits, int rows, int ld, int V, int id_offset,
+                                         const int32_t* ids, float* out, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  saber::launch(saber::logit_gather_kernel, dim3((rows + 127) / 128), dim3(128), 0, stream, 0,
+                static_cast<const __nv_bfloat16*>(logits), ld, V, id_offset, ids, out, rows);
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int saber_verify_launch(const saber::VerifyParams* p, cudaStream_t stream) {
   if (p->nseq <= 0) return 0;
   saber::launch(saber::verify_accept_kernel, dim3((p->nseq + 63) / 64), dim3(64), 0, stream, 0, *p);

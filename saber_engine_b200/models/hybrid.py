@@ -45,6 +45,7 @@ class BlobLayout:
     step_no: int = 0
     last_rows: int = 0
     temps: int = 0
+    next_ids: int = 0          # per row: the token that follows it in its prompt (-1: none), for prompt log-probabilities
     block_table: int = 0
     words: int = 0
 
@@ -68,6 +69,7 @@ class BlobLayout:
         b.step_no = take(nseq)
         b.last_rows = take(nseq)
         b.temps = take(M)
+        b.next_ids = take(M)
         b.block_table = take(nseq * max_blocks)
         b.words = off
         return b
@@ -98,6 +100,8 @@ class Bucket:
     digests: Optional[torch.Tensor] = None         # int64 [n_layers + 1] stage digests (race_check = "shadow")
     seam_dev: Optional[torch.Tensor] = None        # int32 blob: ids [Mh*64] | values [Mh*64] fp32 bits | lse [Mh*2] (seam buckets)
     seam_host: Optional[torch.Tensor] = None       # pinned mirror
+    plp_dev: Optional[torch.Tensor] = None         # int32 blob of a prompt-log-probability bucket (every row: candidates, lse, next-token logit)
+    plp_host: Optional[torch.Tensor] = None
 
 
 class HybridModel:
@@ -239,12 +243,19 @@ class HybridModel:
         return sorted({min(L_ - 1, max(1, round((k + 1) * L_ / (n + 1)))) for k in range(n)}) if n else []
 
     # ------------------------------------------------------------------------------ build
-    def build_bucket(self, kind: str, nseq: int, width: int, capture: bool = True, seam: bool = False) -> Bucket:
+    def build_bucket(self, kind: str, nseq: int, width: int, capture: bool = True, seam: bool = False,
+                     plp: bool = False) -> Bucket:
         """kind='decode': nseq sequences x width rows.  kind='prefill': up to nseq sequences packed in
         `width` rows in total (ragged through cu_rows), rows committed."""
         # seam = True: the program also leaves the 64 best logits of every head row (ids, values,
         # log-sum-exp) for the host sampler; a bucket of its own so that greedy steps do not pay for it
+        # plp = True (prefill only): the head also runs over EVERY row and leaves, per row, the candidate
+        # row and the logit of the token that follows it in the prompt (prompt log-probabilities)
         key = (kind, nseq, width, "seam") if seam else (kind, nseq, width)
+        if plp:
+            if kind != "prefill" or self.tp > 1:
+                raise ValueError("prompt log-probabilities: prefill buckets on one GPU only")
+            key = key + ("plp",)
         self._bucket_key, self._want_seam = key, seam
         if key in self.buckets:
             return self.buckets[key]
@@ -429,6 +440,21 @@ class HybridModel:
             s_lse = seam_dev[2 * Mh * N.SEAM_K:].view(torch.float32)
             prog.seam(logits, Mh, logits.stride(0), sh.vocab, sh.vocab_first, None, s_ids, s_vals, s_lse, tag="topk_seam")
             keep += [seam_dev]
+        plp_dev = None
+        if plp:
+            K = N.SEAM_K
+            qa_all = self._qa(M, H)
+            logits_all = torch.zeros(M, (sh.vocab + 7) // 8 * 8, dtype=torch.bfloat16, device=dev)
+            # ids [M*K] | values [M*K] | lse [M*2] | logit of the next prompt token [M]
+            plp_dev = torch.zeros(M * (2 * K + 3), dtype=torch.int32, device=dev)
+            prog.row(N.ROW_PLAIN, F.row_params(M, H, a=normed, qa=self._fmt(qa_all, self.w.lm_head)), tag="plp.head_quant")
+            self._gemm(prog, self.w.lm_head, qa_all, logits_all, "plp.lm_head")
+            prog.seam(logits_all, M, logits_all.stride(0), sh.vocab, sh.vocab_first, None, plp_dev[:M * K],
+                      plp_dev[M * K: 2 * M * K].view(torch.float32), plp_dev[2 * M * K: 2 * M * K + 2 * M].view(torch.float32),
+                      tag="plp.topk_seam")
+            prog.logit_gather(logits_all, M, logits_all.stride(0), sh.vocab, sh.vocab_first, at(lay.next_ids),
+                              plp_dev[2 * M * K + 2 * M:].view(torch.float32), tag="plp.logit_gather")
+            keep += [qa_all, logits_all, plp_dev]
         if decode:
             vp = N.VerifyParams()
             vp.draft, vp.target, vp.cu_rows = at(lay.ids), o_picks.data_ptr(), at(lay.cu_rows)
@@ -441,7 +467,7 @@ class HybridModel:
         else:
             acc_ptr, bonus_ptr = at(lay.last_rows), o_picks.data_ptr()
         keep += [out, accept_row, bonus, pick_val, logits]
-        self._last_head = dict(out=out, logits=logits, W=W, block=block, Mh=Mh, seam=seam_dev)
+        self._last_head = dict(out=out, logits=logits, W=W, block=block, Mh=Mh, seam=seam_dev, plp=plp_dev)
         if self.use_drafter:
             self._build_drafter(prog, nseq, M, tap_buf, taps, acc_ptr, bonus_ptr, o_drafts, keep)
         if self.tp > 1:
@@ -493,6 +519,8 @@ class HybridModel:
                    n_launches=prog.declared_launches, logits=head["logits"], keep=keep)
         b.W, b.block, b.Mh = head["W"], head["block"], head["Mh"]
         b.seam_dev = head.get("seam")
+        b.plp_dev = head.get("plp")
+        b.plp_host = torch.zeros(b.plp_dev.numel(), dtype=torch.int32).pin_memory() if b.plp_dev is not None else None
         b.seam_host = torch.zeros(b.seam_dev.numel(), dtype=torch.int32).pin_memory() if b.seam_dev is not None else None
         if capture:
             # one eager walk first: sets function attributes and warms lazy module loading
@@ -519,6 +547,7 @@ class SeqStep:
     step_no: int = 0
     rope_pos: Optional[object] = None   # int [3, rows]: three-axis rotary positions of the rows (prompts with images)
     rope_delta: int = 0       # added to the index of every row for the rotary position (after an image)
+    next_token: int = -1      # the prompt token after this chunk's last row (-1: none), for prompt log-probabilities
 
 
 @dataclass
@@ -538,12 +567,14 @@ def fill_blob(b: Bucket, seqs: list, page_tokens: int = 16) -> int:
     hdr = lay.header_words
     a[:hdr] = 0
     a[lay.slot_map:lay.slot_map + M] = -1
+    a[lay.next_ids:lay.next_ids + M] = -1
     a[lay.slots:lay.slots + nseq] = -1
     row = 0
     max_used = 0
     for j, s in enumerate(seqs):
         n = len(s.tokens)
         a[lay.ids + row: lay.ids + row + n] = s.tokens
+        a[lay.next_ids + row: lay.next_ids + row + n] = list(s.tokens[1:]) + [s.next_token]
         pos = np.arange(s.pos0, s.pos0 + n, dtype=np.int32)
         for ax in range(3):
             a[lay.pos + ax * M + row: lay.pos + ax * M + row + n] = \
@@ -581,6 +612,8 @@ def run_bucket(model: "HybridModel", b: Bucket, seqs: list, eager: bool = False)
         b.out_host.copy_(b.out_dev, non_blocking=True)
         if getattr(b, "seam_dev", None) is not None:
             b.seam_host.copy_(b.seam_dev, non_blocking=True)
+        if getattr(b, "plp_dev", None) is not None:
+            b.plp_host.copy_(b.plp_dev, non_blocking=True)
     st.synchronize()
     return parse_result(b, len(seqs))
 

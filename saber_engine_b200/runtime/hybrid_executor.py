@@ -74,11 +74,34 @@ class HybridExecutor:
             for r in self.prefill_rungs:
                 self._bucket("prefill", self.prefill_pack, r)
 
-    def _bucket(self, kind: str, nseq: int, width: int, seam: bool = False):
-        key = (kind, nseq, width, "seam") if seam else (kind, nseq, width)
+    def _bucket(self, kind: str, nseq: int, width: int, seam: bool = False, plp: bool = False):
+        key = ((kind, nseq, width, "seam") if seam else (kind, nseq, width)) + (("plp",) if plp else ())
         if key not in self.model.buckets:
             self.census["buckets_built"] += 1
-        return self.model.build_bucket(kind, nseq, width, capture=self.capture, seam=seam)
+        return self.model.build_bucket(kind, nseq, width, capture=self.capture, seam=seam, plp=plp)
+
+    @staticmethod
+    def _prompt_lps(b, runs: list) -> list:
+        """Per run: for every row of the chunk that has a successor in the prompt, the successor's
+        log-probability (its logit minus the row's log-sum-exp) and the best alternatives."""
+        import numpy as np
+        K, M = N_SEAM_K, b.M
+        a = b.plp_host.numpy()
+        ids = a[:M * K].reshape(M, K)
+        vals = a[M * K: 2 * M * K].view(np.float32).reshape(M, K)
+        lse = a[2 * M * K: 2 * M * K + 2 * M].view(np.float32).reshape(M, 2)[:, 0]
+        nxt = a[2 * M * K + 2 * M:].view(np.float32)
+        out, row = [], 0
+        for r in runs:
+            n, res = len(r.tokens), None
+            if r.prompt_lp is not None:
+                succ = list(r.tokens[1:]) + [r.next_token]
+                res = [{"token_id": int(succ[i]), "logprob": float(nxt[row + i] - lse[row + i]),
+                        "top": [(int(t), float(v - lse[row + i])) for t, v in zip(ids[row + i][:r.prompt_lp], vals[row + i][:r.prompt_lp])]}
+                       for i in range(n) if succ[i] >= 0]
+            out.append(res)
+            row += n
+        return out
 
     def _seams(self, b, rows_of: list) -> list:
         """Per run: {"ids", "vals", "lse"} over the run's head rows, from the bucket's read-back blob;
@@ -100,7 +123,7 @@ class HybridExecutor:
     @staticmethod
     def _step(r: SeqRun) -> SeqStep:
         return SeqStep(list(r.tokens), r.pos0, r.slot, r.shift, r.blocks, uid=r.uid, step_no=r.step_no,
-                       rope_pos=r.rope_pos, rope_delta=r.rope_delta)
+                       rope_pos=r.rope_pos, rope_delta=r.rope_delta, next_token=getattr(r, "next_token", -1))
 
     def _count(self, b) -> None:
         self.census["graph_replays" if b.captured else "eager_walks"] += 1
@@ -109,12 +132,14 @@ class HybridExecutor:
     def prefill(self, runs: list) -> list:
         rows = sum(len(r.tokens) for r in runs)
         want = any(r.want_seam and r.last_chunk for r in runs)
-        b = self._bucket("prefill", max(self.prefill_pack, len(runs)), select_rung(rows, self.prefill_rungs), seam=want)
+        plp = any(r.prompt_lp is not None for r in runs)
+        b = self._bucket("prefill", max(self.prefill_pack, len(runs)), select_rung(rows, self.prefill_rungs), seam=want, plp=plp)
         res = run_bucket(self.model, b, [self._step(r) for r in runs])
         self._count(b)
         seams = self._seams(b, [(j, j + 1) for j in range(len(runs))]) if want else [None] * len(runs)
+        plps = self._prompt_lps(b, runs) if plp else [None] * len(runs)
         return [SeqOut([res.tokens[j][0]] if r.last_chunk else [], res.drafts[j] if r.last_chunk else [],
-                       seam=seams[j] if (r.want_seam and r.last_chunk) else None)
+                       seam=seams[j] if (r.want_seam and r.last_chunk) else None, prompt_lps=plps[j])
                 for j, r in enumerate(runs)]
 
     def decode(self, runs: list, width: int) -> list:

@@ -27,6 +27,8 @@ class SeqRun:
     want_seam: bool = False
     rope_pos: Optional[object] = None   # int [3, rows]: rotary positions of a chunk of a prompt with images
     rope_delta: int = 0          # rotary position - index for rows after the prompt's images
+    prompt_lp: Optional[int] = None   # prefill: log-probability of every next prompt token with this many alternatives
+    next_token: int = -1         # the prompt token after this chunk (-1: the chunk ends the prompt)
 
 
 @dataclass
@@ -34,6 +36,7 @@ class SeqOut:
     tokens: list                 # committed tokens (decode: accepted drafts + bonus; prefill: 1 or 0)
     drafts: list = field(default_factory=list)   # proposal for the next step
     seam: Optional[dict] = None  # top-k candidates + log-sum-exps for sampled rows
+    prompt_lps: Optional[list] = None   # prefill: per row with a successor {token_id, logprob, top} of that successor
     logits_rows: Optional[object] = None
 
 

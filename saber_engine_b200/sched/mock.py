@@ -61,12 +61,18 @@ class NullExecutor:
             self._state[run.slot] = (d, n + len(run.tokens))
             self._stash.pop(run.slot, None)
             self._write_kv(run)
+            plps = None
+            if getattr(run, "prompt_lp", None) is not None:      # a stand-in law: the successor at a fixed distance below the best
+                succ = list(run.tokens[1:]) + [run.next_token]
+                plps = [{"token_id": int(t), "logprob": -1.0 - (t % 7) * 0.125,
+                         "top": [((t + i) % self.vocab, -1.0 - (t % 7) * 0.125 - i) for i in range(run.prompt_lp)]}
+                        for t in succ if t >= 0]
             if run.last_chunk:
                 tok = _next_token(d, self.vocab)
                 outs.append(SeqOut([tok], self._propose(d, tok, max(self.decode_widths) - 1),
-                                   seam=self._seam([tok]) if run.want_seam else None))
+                                   seam=self._seam([tok]) if run.want_seam else None, prompt_lps=plps))
             else:
-                outs.append(SeqOut([]))
+                outs.append(SeqOut([], prompt_lps=plps))
         return outs
 
     def _seam(self, picks: list, k: int = 8) -> dict:

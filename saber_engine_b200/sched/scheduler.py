@@ -61,6 +61,7 @@ class Sequence:
     t_admit: Optional[float] = None
     n_drafted: int = 0
     n_accepted: int = 0
+    prompt_lps: list = field(default_factory=list)   # log-probabilities of prompt tokens 1.., chunk by chunk
 
     @property
     def prefilling(self) -> bool:
@@ -156,7 +157,9 @@ class Scheduler:
             s = self.waiting[0]
             # speculative rows write KV past the last committed token: keep one step of head-room
             total = len(s.prompt) + s.req.params.max_tokens + max(self.ex.decode_widths)
-            mm = s.req.mm is not None         # image rows are arena addresses, not content: no prefix sharing
+            # image rows are arena addresses, not content: no prefix sharing; prompt log-probabilities
+            # need every prompt row to run
+            mm = s.req.mm is not None or s.req.params.prompt_logprobs is not None
             hit = None if mm else self.prefix.lookup(s.prompt)
             shared = list(hit.blocks) if hit else []
             need = self.arenas.kv.blocks_for(total) - len(shared)
@@ -233,7 +236,9 @@ class Scheduler:
                                    last_chunk=(pos + n == len(s.prompt)),
                                    temperature=s.req.params.temperature, want_seam=self._wants_seam(s),
                                    rope_pos=(None if s.req.mm is None else
-                                             [list(ax[pos:pos + n]) for ax in s.req.mm["rope_pos"]]))
+                                             [list(ax[pos:pos + n]) for ax in s.req.mm["rope_pos"]]),
+                                   prompt_lp=s.req.params.prompt_logprobs,
+                                   next_token=(s.prompt[pos + n] if pos + n < len(s.prompt) else -1))
                             for s, pos, n in plan[1]]
                     outs = self.ex.prefill(runs)
                 else:
@@ -311,6 +316,8 @@ class Scheduler:
         for (s, pos, n), out in zip(picks, outs):
             s.chunks.popleft()
             s.pos = pos + n
+            if out.prompt_lps is not None:
+                s.prompt_lps.extend(out.prompt_lps)
             self.counters["prompt_tokens"] += n
             if s.pos in s.cut_points:
                 snap = self.ex.snapshot_state(s.slot)
@@ -415,7 +422,8 @@ class Scheduler:
         ev = StepEvent(s.seq_id, kept, reason is not None, reason, prompt_tokens=len(s.prompt),
                        cached_tokens=s.cached_tokens, n_drafted=drafted, n_accepted=accepted,
                        step_time_s=dt, first_token=first,
-                       logprobs=(lps[:len(kept)] if lps is not None else None))
+                       logprobs=(lps[:len(kept)] if lps is not None else None),
+                       prompt_logprobs=(list(s.prompt_lps) if first and s.req.params.prompt_logprobs is not None else None))
         if reason:
             self._finish(s, reason, ev)
         else:

@@ -51,6 +51,8 @@ class SamplingParams:
             problems.append(f"prompt ({prompt_len}) + max_tokens ({self.max_tokens}) exceeds the context window ({max_ctx})")
         if self.logprobs is not None and not (0 <= self.logprobs <= 20):
             problems.append("logprobs must be in [0, 20]")
+        if self.prompt_logprobs is not None and not (isinstance(self.prompt_logprobs, int) and 0 <= self.prompt_logprobs <= 20):
+            problems.append("prompt_logprobs must be in [0, 20]")
         return problems
 
 
@@ -78,6 +80,7 @@ class StepEvent:
     n_drafted: int = 0
     n_accepted: int = 0
     logprobs: Optional[list] = None
+    prompt_logprobs: Optional[list] = None     # with the first token: {token_id, logprob, top} of prompt tokens 1..
     step_time_s: float = 0.0
     first_token: bool = False
 

@@ -250,6 +250,7 @@ def create_app(state: ServerState) -> FastAPI:
                     state.metrics.inc("request_success_total" if ev.finish_reason in ("stop", "length") else "request_refused_total")
                     return
 
+        plp_items = []
         lp_items = []     # per generated token: {"token_id", "logprob", "top"} from the engine's candidate rows
 
         def lp_chat(items):
@@ -263,6 +264,19 @@ def create_app(state: ServerState) -> FastAPI:
             tk = lambda t: state.tok.token_bytes(t).decode("utf-8", errors="replace")   # noqa: E731
             return {"tokens": [tk(it["token_id"]) for it in items], "token_logprobs": [it["logprob"] for it in items],
                     "top_logprobs": [{tk(i): v for i, v in it["top"][: (params.logprobs or 0)]} for it in items]}
+
+        def plp_vllm(items):
+            """vLLM's shape: one entry per prompt token, None for the first, else {token id: {logprob, rank, decoded_token}}."""
+            out = [None]
+            for it in items:
+                d = {}
+                for rank, (i, v) in enumerate(it["top"], 1):
+                    d[str(i)] = {"logprob": v, "rank": rank, "decoded_token": state.tok.token_bytes(i).decode("utf-8", errors="replace")}
+                if str(it["token_id"]) not in d:
+                    d[str(it["token_id"])] = {"logprob": it["logprob"], "rank": None,
+                                              "decoded_token": state.tok.token_bytes(it["token_id"]).decode("utf-8", errors="replace")}
+                out.append(d)
+            return out
 
         def usage(ev):
             return {"prompt_tokens": len(prompt_ids), "completion_tokens": rec["completion_tokens"],
@@ -297,6 +311,8 @@ def create_app(state: ServerState) -> FastAPI:
                         choice = {"index": 0, "text": text, "finish_reason": ev.finish_reason if ev.finished else None}
                     if ev.logprobs:
                         choice["logprobs"] = lp_chat(ev.logprobs) if chat else lp_text(ev.logprobs)
+                    if ev.prompt_logprobs is not None:
+                        choice["prompt_logprobs"] = plp_vllm(ev.prompt_logprobs)
                     first = False
                     yield "data: " + json.dumps({"id": rid, "object": obj + ".chunk" if chat else obj, "created": created,
                                                  "model": state.model_name, "choices": [choice]}) + "\n\n"
@@ -312,6 +328,8 @@ def create_app(state: ServerState) -> FastAPI:
             last = ev
             if ev.logprobs:
                 lp_items.extend(ev.logprobs)
+            if ev.prompt_logprobs is not None:
+                plp_items.extend(ev.prompt_logprobs)
         if last is not None and last.finish_reason == "error":
             return _err(503, last.error or "engine error", "service_unavailable")
         if chat:
@@ -334,6 +352,8 @@ def create_app(state: ServerState) -> FastAPI:
             choice = {"index": 0, "text": full, "finish_reason": last.finish_reason}
         if params.logprobs is not None:
             choice["logprobs"] = lp_chat(lp_items) if chat else lp_text(lp_items)
+        if params.prompt_logprobs is not None:
+            choice["prompt_logprobs"] = plp_vllm(plp_items)
         return {"id": rid, "object": obj, "created": created, "model": state.model_name,
                 "choices": [choice], "usage": usage(last)}
 

@@ -125,3 +125,53 @@ def test_sampled_requests_draw_from_the_device_seam(executor):
     tv, _ = torch.topk(logits, K, dim=-1)
     assert torch.equal(vals, tv) and torch.equal(logits.gather(1, ids), vals)
     assert torch.allclose(lse, torch.logsumexp(logits, -1), atol=1e-3)
+
+
+def test_greedy_request_with_logprobs_reads_the_seam(executor):
+    g = torch.Generator().manual_seed(6)
+    prompt = torch.randint(0, executor.vocab, (40,), generator=g).tolist()
+    s = _sched(executor, prefix_cache=False)
+    sub = s.submit(EngineRequest(prompt, SamplingParams(max_tokens=10, ignore_eos=True, logprobs=2)))
+    plain = s.submit(EngineRequest(prompt, SamplingParams(max_tokens=10, ignore_eos=True)))
+    s.run_until_idle()
+    toks, lps = [], []
+    while True:
+        ev = sub.events.get(timeout=60)
+        toks += ev.new_token_ids
+        lps += ev.logprobs or []
+        if ev.finished:
+            break
+    assert toks == _collect(plain)[0]                       # asking for log-probabilities does not move the ids
+    assert len(lps) == 10 and [x["token_id"] for x in lps] == toks
+    for x in lps:
+        assert x["logprob"] <= 0.0 and len(x["top"]) == 2
+        assert x["top"][0][0] == x["token_id"] and abs(x["top"][0][1] - x["logprob"]) < 1e-6   # greedy = best candidate
+        assert x["top"][1][1] <= x["top"][0][1]
+
+
+def test_prompt_logprobs_match_a_full_logits_pass(executor):
+    """Prompt log-probabilities from the prefill bucket variant (head over every row) against
+    log-softmax of the logits that variant leaves behind, over two chunks of a prompt."""
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, executor.vocab, (100,), generator=g).tolist()
+    s = _sched(executor, prefix_cache=False)
+    sub = s.submit(EngineRequest(prompt, SamplingParams(max_tokens=3, ignore_eos=True, prompt_logprobs=1)))
+    plain = s.submit(EngineRequest(prompt, SamplingParams(max_tokens=3, ignore_eos=True)))
+    s.run_until_idle()
+    ev = sub.events.get(timeout=60)
+    plp = ev.prompt_logprobs
+    assert ev.first_token and len(plp) == 99 and [x["token_id"] for x in plp] == prompt[1:]
+    toks = list(ev.new_token_ids)
+    while not ev.finished:
+        ev = sub.events.get(timeout=60)
+        toks += ev.new_token_ids
+    assert toks == _collect(plain)[0]
+    for x in plp:
+        assert x["logprob"] <= 1e-3 and x["top"][0][1] >= x["logprob"] - 1e-3 and x["top"][0][1] <= 1e-3
+    # the last chunk's rows against the logits buffer of its bucket (rung 64: rows 64..99 of the prompt)
+    b = [v for k, v in executor.model.buckets.items() if k[-1] == "plp" and k[2] == 64][0]
+    logits_all = [t for t in b.keep if isinstance(t, torch.Tensor) and t.dtype == torch.bfloat16 and t.shape[0] == 64 and t.shape[1] >= executor.vocab][-1]
+    ref = torch.log_softmax(logits_all[:35, :executor.vocab].float(), -1).cpu()
+    got = torch.tensor([x["logprob"] for x in plp[64:99]])
+    want = ref[torch.arange(35), torch.tensor(prompt[65:100])]
+    assert torch.allclose(got, want, atol=2e-3), (got - want).abs().max()

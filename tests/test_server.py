@@ -204,3 +204,16 @@ def test_logprobs_come_from_the_engine_candidate_rows(client):
     assert n == 6
     # without the field nothing is attached (and the engine is not asked for candidate rows)
     assert "logprobs" not in client.post("/v1/completions", json={"model": "mock", "prompt": "abc", "max_tokens": 2}).json()["choices"][0]
+
+
+def test_prompt_logprobs_cover_every_prompt_token_but_the_first(client):
+    body = {"model": "mock", "prompt": [5, 6, 7, 8, 9, 10, 11], "max_tokens": 2, "prompt_logprobs": 2}
+    ch = client.post("/v1/completions", json=body).json()["choices"][0]
+    plp = ch["prompt_logprobs"]
+    assert len(plp) == 7 and plp[0] is None
+    for tok, entry in zip(body["prompt"][1:], plp[1:]):
+        assert str(tok) in entry and entry[str(tok)]["logprob"] == -1.0 - (tok % 7) * 0.125 and len(entry) == 2
+    # a long prompt is prefilled in chunks: the entries of all chunks arrive together with the first token
+    long = {"model": "mock", "prompt": [(i * 7) % 250 for i in range(700)], "max_tokens": 1, "prompt_logprobs": 0}
+    plp = client.post("/v1/completions", json=long).json()["choices"][0]["prompt_logprobs"]
+    assert len(plp) == 700 and plp[0] is None and all(len(e) == 1 for e in plp[1:])
