@@ -256,7 +256,7 @@ class HybridModel:
             if kind != "prefill" or self.tp > 1:
                 raise ValueError("prompt log-probabilities: prefill buckets on one GPU only")
             key = key + ("plp",)
-        self._bucket_key, self._want_seam = key, seam
+        self._bucket_key, self._want_seam, self._want_plp = key, seam, plp
         if key in self.buckets:
             return self.buckets[key]
         cfg, sh, dev = self.cfg, self.sh, self.device
@@ -441,7 +441,7 @@ class HybridModel:
             prog.seam(logits, Mh, logits.stride(0), sh.vocab, sh.vocab_first, None, s_ids, s_vals, s_lse, tag="topk_seam")
             keep += [seam_dev]
         plp_dev = None
-        if plp:
+        if self._want_plp:
             K = N.SEAM_K
             qa_all = self._qa(M, H)
             logits_all = torch.zeros(M, (sh.vocab + 7) // 8 * 8, dtype=torch.bfloat16, device=dev)
@@ -455,6 +455,7 @@ class HybridModel:
             prog.logit_gather(logits_all, M, logits_all.stride(0), sh.vocab, sh.vocab_first, at(lay.next_ids),
                               plp_dev[2 * M * K + 2 * M:].view(torch.float32), tag="plp.logit_gather")
             keep += [qa_all, logits_all, plp_dev]
+            self._plp_logits = logits_all
         if decode:
             vp = N.VerifyParams()
             vp.draft, vp.target, vp.cu_rows = at(lay.ids), o_picks.data_ptr(), at(lay.cu_rows)
@@ -520,6 +521,7 @@ class HybridModel:
         b.W, b.block, b.Mh = head["W"], head["block"], head["Mh"]
         b.seam_dev = head.get("seam")
         b.plp_dev = head.get("plp")
+        b.plp_logits = getattr(self, "_plp_logits", None) if b.plp_dev is not None else None
         b.plp_host = torch.zeros(b.plp_dev.numel(), dtype=torch.int32).pin_memory() if b.plp_dev is not None else None
         b.seam_host = torch.zeros(b.seam_dev.numel(), dtype=torch.int32).pin_memory() if b.seam_dev is not None else None
         if capture:
