@@ -281,98 +281,165 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
 }
 
 // ---------------------------------------------------------------------------------- prefill rows
-// Committing (prefill) form of the recurrence for long row runs: the same row-by-row rule, but eight
-// threads per state row (16 values each) instead of two.  A prefill rung is one sequence walking
-// thousands of rows in order, so what counts is the latency of one row step, not throughput: the
-// dependent FMA chains are four times shorter, at the price of two more shuffle rounds per
-// reduction.  No stash and no replay (a prefill chunk starts from the committed state: shift is 0).
-// grid (HV * 4, nseq), block 256: thread = (v row of a 32-row slice, k part); the thread's values of
-// row v are k = 32 x + 4 kq + c (x, c < 4), so the eight parts read 128 contiguous bytes per x.
-__global__ void __launch_bounds__(256) gdn_prefill_rows_kernel(const GdnRecParams p) {
+// Committing (prefill) form of the recurrence for long row runs.  A prefill rung is one sequence
+// walking thousands of rows in order, so what counts is the latency of one row step.  A thread holds
+// VR state rows (16 values of each): one read of its k and q parts from shared memory serves VR
+// rows, and the rows give every dependent chain (decay, dot, reduction, update) VR independent
+// instances.  Batches of 16 rows arrive by 16-byte asynchronous copies into a double buffer while
+// the previous batch is computed; the reduction of a row's output rides with the next row's
+// dot-product reduction.  No stash and no replay (a prefill chunk starts from the committed state).
+// grid (HV * 4, nseq), block 256 / VR: thread = (group of VR v rows of a 32-row slice, k part); the
+// thread's values of a row are k = 32 x + 4 kq + c (x, c < 4): the eight parts read 128 contiguous
+// bytes per x.
+constexpr int kPfBatch = 16;
+
+__device__ __forceinline__ void gdn_cp_async16(void* dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst_smem))),
+               "l"(src) : "memory");
+}
+
+template <int VR>   // state rows per thread: 4 (block 64) or 2 (block 128)
+__global__ void __launch_bounds__(256 / VR) gdn_prefill_rows_kernel(const GdnRecParams p) {
+  constexpr int kThreads = 256 / VR;
   pdl_wait();
-  __shared__ __align__(16) float ks[kRecBatch][128];
-  __shared__ __align__(16) float qs[kRecBatch][128];
-  __shared__ float vsm[kRecBatch][32];
-  __shared__ float gsm[kRecBatch], bsm[kRecBatch];
+  __shared__ __align__(16) float ks[2][kPfBatch][128];
+  __shared__ __align__(16) float qs[2][kPfBatch][128];
+  __shared__ __align__(16) float vsm[2][kPfBatch][32];
+  __shared__ float dsm[2][kPfBatch], bsm[2][kPfBatch];     // decay = exp(g), beta
   const int b = blockIdx.y;
   const int slot = p.slots[b];
   if (slot < 0) return;
   const int h = blockIdx.x >> 2, vs = blockIdx.x & 3;
   const int hk = h / (p.HV / p.HK);
   const int tid = threadIdx.x;
-  const int vloc = tid >> 3, kq = tid & 7;
-  const int v = vs * 32 + vloc;
+  const int vg = tid >> 3, kq = tid & 7;
+  const int v0 = vs * 32 + vg * VR;
   const int row0 = p.cu_rows[b];
   const int n = p.cu_rows[b + 1] - row0;
   if (n <= 0) return;
-  float* sp = p.state + ((static_cast<size_t>(slot) * p.HV + h) * 128 + v) * 128 + kq * 4;
-  f32x2 S[8];
+  float* sp = p.state + ((static_cast<size_t>(slot) * p.HV + h) * 128 + v0) * 128 + kq * 4;
+  f32x2 S[VR][8];
 #pragma unroll
-  for (int x = 0; x < 4; ++x) {
-    const ulonglong2 t = *reinterpret_cast<const ulonglong2*>(sp + 32 * x);
-    S[2 * x] = t.x;
-    S[2 * x + 1] = t.y;
-  }
+  for (int j = 0; j < VR; ++j)
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const ulonglong2 t = *reinterpret_cast<const ulonglong2*>(sp + j * 128 + 32 * x);
+      S[j][2 * x] = t.x;
+      S[j][2 * x + 1] = t.y;
+    }
   const float neg_a = -__expf(p.A_log[h]);
   const float dtb = p.dt_bias[h];
-  for (int r0 = 0; r0 < n; r0 += kRecBatch) {
-    const int nb = min(kRecBatch, n - r0);
-    __syncthreads();                         // the previous batch is consumed
-    for (int idx = tid; idx < nb * 128; idx += 256) {
-      const int r = idx >> 7, i = idx & 127;
+  const int nbatch = (n + kPfBatch - 1) / kPfBatch;
+  float bb_n = 0.f, aa_n = 0.f;          // gate inputs of the batch in flight (threads tid < rows of the batch)
+  auto issue = [&](int bi, int buf) {
+    const int r0 = bi * kPfBatch, nb = min(kPfBatch, n - r0);
+    for (int idx = tid; idx < nb * 64; idx += kThreads) {
+      const int r = idx >> 6, c = idx & 63;
       const float* xr = p.qkv + static_cast<size_t>(row0 + r0 + r) * p.C;
-      qs[r][i] = xr[hk * 128 + i];
-      ks[r][i] = xr[p.n_q + hk * 128 + i];
+      if (c < 32) gdn_cp_async16(&qs[buf][r][4 * c], xr + hk * 128 + 4 * c);
+      else gdn_cp_async16(&ks[buf][r][4 * (c - 32)], xr + p.n_q + hk * 128 + 4 * (c - 32));
     }
-    for (int idx = tid; idx < nb * 32; idx += 256) {
-      const int r = idx >> 5, i = idx & 31;
-      vsm[r][i] = p.qkv[static_cast<size_t>(row0 + r0 + r) * p.C + p.n_q + p.n_k + h * 128 + vs * 32 + i];
+    for (int idx = tid; idx < nb * 8; idx += kThreads) {
+      const int r = idx >> 3, c = idx & 7;
+      gdn_cp_async16(&vsm[buf][r][4 * c],
+                     p.qkv + static_cast<size_t>(row0 + r0 + r) * p.C + p.n_q + p.n_k + h * 128 + vs * 32 + 4 * c);
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
     if (tid < nb) {
       const size_t m = static_cast<size_t>(row0 + r0 + tid);
-      const float bb = __bfloat162float(p.ba[m * p.ldba + h]);
-      const float aa = __bfloat162float(p.ba[m * p.ldba + p.HV + h]);
-      gsm[tid] = neg_a * gdn_softplus(aa + dtb);
-      bsm[tid] = 1.f / (1.f + __expf(-bb));
+      bb_n = __bfloat162float(p.ba[m * p.ldba + h]);
+      aa_n = __bfloat162float(p.ba[m * p.ldba + p.HV + h]);
+    }
+  };
+  issue(0, 0);
+  for (int bi = 0; bi < nbatch; ++bi) {
+    const int buf = bi & 1;
+    const int r0 = bi * kPfBatch, nb = min(kPfBatch, n - r0);
+    if (tid < nb) {
+      dsm[buf][tid] = __expf(neg_a * gdn_softplus(aa_n + dtb));
+      bsm[buf][tid] = 1.f / (1.f + __expf(-bb_n));
+    }
+    if (bi + 1 < nbatch) {
+      issue(bi + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    // The reduction of a row's OUTPUT partial sums is not needed by the next row: it rides with the
+    // next row's dot-product reduction (eight independent shuffles per stage instead of four) and
+    // the row is stored one step late; the last row of a batch is flushed after the loop.
+    float op[VR];
+#pragma unroll
+    for (int j = 0; j < VR; ++j) op[j] = 0.f;
     for (int r = 0; r < nb; ++r) {
-      const float decay = __expf(gsm[r]);
+      const float decay = dsm[buf][r], beta = bsm[buf][r];
       const f32x2 dec2 = pack2(decay, decay);
       ulonglong2 kk[4];
-      f32x2 a0 = 0ull, a1 = 0ull;
 #pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        kk[x] = *reinterpret_cast<const ulonglong2*>(&ks[r][32 * x + 4 * kq]);
-        S[2 * x] = mul2(S[2 * x], dec2);
-        S[2 * x + 1] = mul2(S[2 * x + 1], dec2);
-        a0 = fma2(S[2 * x], kk[x].x, a0);
-        a1 = fma2(S[2 * x + 1], kk[x].y, a1);
+      for (int x = 0; x < 4; ++x) kk[x] = *reinterpret_cast<const ulonglong2*>(&ks[buf][r][32 * x + 4 * kq]);
+      float dot[VR];
+#pragma unroll
+      for (int j = 0; j < VR; ++j) {
+        f32x2 a0 = 0ull, a1 = 0ull;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          S[j][2 * x] = mul2(S[j][2 * x], dec2);
+          S[j][2 * x + 1] = mul2(S[j][2 * x + 1], dec2);
+          a0 = fma2(S[j][2 * x], kk[x].x, a0);
+          a1 = fma2(S[j][2 * x + 1], kk[x].y, a1);
+        }
+        dot[j] = sum2(a0) + sum2(a1);
       }
-      float dot = sum2(a0) + sum2(a1);
 #pragma unroll
-      for (int o = 1; o < 8; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = (vsm[r][vloc] - dot) * bsm[r];
-      const f32x2 u2 = pack2(u, u);
-      f32x2 o0 = 0ull, o1 = 0ull;
+      for (int o = 1; o < 8; o <<= 1) {
 #pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const ulonglong2 qq = *reinterpret_cast<const ulonglong2*>(&qs[r][32 * x + 4 * kq]);
-        S[2 * x] = fma2(u2, kk[x].x, S[2 * x]);
-        S[2 * x + 1] = fma2(u2, kk[x].y, S[2 * x + 1]);
-        o0 = fma2(S[2 * x], qq.x, o0);
-        o1 = fma2(S[2 * x + 1], qq.y, o1);
+        for (int j = 0; j < VR; ++j) dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], o);
+#pragma unroll
+        for (int j = 0; j < VR; ++j) op[j] += __shfl_xor_sync(0xffffffffu, op[j], o);
       }
-      float o = sum2(o0) + sum2(o1);
+      if (r > 0 && kq == 0) {
+        float* po = p.out + static_cast<size_t>(row0 + r0 + r - 1) * (static_cast<size_t>(p.HV) * 128) + h * 128 + v0;
 #pragma unroll
-      for (int s2 = 1; s2 < 8; s2 <<= 1) o += __shfl_xor_sync(0xffffffffu, o, s2);
-      if (kq == 0)
-        p.out[static_cast<size_t>(row0 + r0 + r) * (static_cast<size_t>(p.HV) * 128) + h * 128 + v] = o;
+        for (int j = 0; j < VR; ++j) po[j] = op[j];
+      }
+      float vj[VR];
+#pragma unroll
+      for (int j = 0; j < VR; ++j) vj[j] = vsm[buf][r][vg * VR + j];
+      ulonglong2 qq[4];
+#pragma unroll
+      for (int x = 0; x < 4; ++x) qq[x] = *reinterpret_cast<const ulonglong2*>(&qs[buf][r][32 * x + 4 * kq]);
+#pragma unroll
+      for (int j = 0; j < VR; ++j) {
+        const float u = (vj[j] - dot[j]) * beta;
+        const f32x2 u2 = pack2(u, u);
+        f32x2 o0 = 0ull, o1 = 0ull;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          S[j][2 * x] = fma2(u2, kk[x].x, S[j][2 * x]);
+          S[j][2 * x + 1] = fma2(u2, kk[x].y, S[j][2 * x + 1]);
+          o0 = fma2(S[j][2 * x], qq[x].x, o0);
+          o1 = fma2(S[j][2 * x + 1], qq[x].y, o1);
+        }
+        op[j] = sum2(o0) + sum2(o1);
+      }
     }
+#pragma unroll
+    for (int s2 = 1; s2 < 8; s2 <<= 1)
+#pragma unroll
+      for (int j = 0; j < VR; ++j) op[j] += __shfl_xor_sync(0xffffffffu, op[j], s2);
+    if (kq == 0) {
+      float* po = p.out + static_cast<size_t>(row0 + r0 + nb - 1) * (static_cast<size_t>(p.HV) * 128) + h * 128 + v0;
+#pragma unroll
+      for (int j = 0; j < VR; ++j) po[j] = op[j];
+    }
+    __syncthreads();                       // this buffer is refilled by the copies of the next iteration
   }
 #pragma unroll
-  for (int x = 0; x < 4; ++x)
-    *reinterpret_cast<ulonglong2*>(sp + 32 * x) = make_ulonglong2(S[2 * x], S[2 * x + 1]);
+  for (int j = 0; j < VR; ++j)
+#pragma unroll
+    for (int x = 0; x < 4; ++x)
+      *reinterpret_cast<ulonglong2*>(sp + j * 128 + 32 * x) = make_ulonglong2(S[j][2 * x], S[j][2 * x + 1]);
 }
 
 }  // namespace saber
@@ -392,7 +459,9 @@ extern "C" int saber_gdn_recurrent_launch(const saber::GdnRecParams* p, int nseq
   using namespace saber;
   if (p->HV % p->HK) return static_cast<int>(cudaErrorInvalidValue);
   if (p->commit && p->prefill_rows) {      // long committing runs: the latency-oriented form
-    saber::launch(gdn_prefill_rows_kernel, dim3(p->HV * 4, nseq), dim3(256), 0, stream, 0, *p);
+    // two state rows per thread measured 863 us per 2048 rows, four 904 us, the first form (one row per
+    // eight threads, synchronous staging) 1071 us
+    saber::launch(gdn_prefill_rows_kernel<2>, dim3(p->HV * 4, nseq), dim3(128), 0, stream, 0, *p);
     return static_cast<int>(cudaGetLastError());
   }
   if (vs == 1) saber::launch(gdn_recurrent_kernel<1>, dim3(dim3(p->HV, nseq)), dim3(256), 0, stream, 0, *p);

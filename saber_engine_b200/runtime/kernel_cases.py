@@ -101,6 +101,28 @@ def _gdn(nseq, n, shift, vs=2, copies=3):
     return states, stashes, out
 
 
+def _gdn_prefill(n, copies=3):
+    """One sequence of n rows through the committing row-by-row form the prefill rungs use."""
+    HV, HK, d = 48, 16, 128
+    C_ = 2 * HK * d + HV * d
+    qkv = torch.randn(n, C_, device=DEV) * 0.1
+    ba = torch.randn(n, 2 * HV, device=DEV).to(torch.bfloat16)
+    A_log, dtb = torch.randn(HV, device=DEV) * 0.5, torch.randn(HV, device=DEV) * 0.5
+    states = [torch.randn(2, HV, d, d, device=DEV) * 0.01 for _ in range(copies)]
+    stash = torch.zeros(2, 9, HV, 2, F.gdn_stash_stride(2), device=DEV)
+    cu = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([1], dtype=torch.int32, device=DEV)
+    sh = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty(n, HV * d, device=DEV)
+    ps = [F.gdn_rec_params(qkv, ba, A_log, dtb, st, stash, cu, slots, sh, out, HK * d, HK * d, HV, HK, True,
+                           prefill_rows=True) for st in states]
+    torch.cuda.synchronize()
+    lib = N.lib()
+    fns = [lambda p=p: N.check(lib.saber_gdn_recurrent_launch(C.byref(p), 1, 2, N.stream_handle()), "gdn") for p in ps]
+    _time(fns, f"gdn prefill rows n={n}", n * (2 * HK * d + HV * d) * 4.0 + n * HV * d * 4.0)
+    return states, out
+
+
 def _row(M, K, copies=3):
     xs = [torch.randn(M, K, device=DEV).to(torch.bfloat16) for _ in range(copies)]
     res = torch.randn(M, K, device=DEV).to(torch.bfloat16)
@@ -163,6 +185,7 @@ CASES = {
     "attn_decode_b8_w1_ctx4096": lambda: _attn(8, 1, 4096, 9),
     "attn_decode_b8_w5_ctx4096": lambda: _attn(8, 5, 4096, 4),
     "gdn_rec_b8": lambda: _gdn(8, 9, 5),
+    "gdn_prefill_2048": lambda: _gdn_prefill(2048),
     "row_add_rms_m72": lambda: _row(72, 5120),
     "moe_block_m72": lambda: _moe(72),
     "vision_tower_512": lambda: _vision(512),
