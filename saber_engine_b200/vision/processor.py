@@ -122,7 +122,7 @@ def resize(img: np.ndarray, size: tuple) -> np.ndarray:
         return img
     import torch
     import torch.nn.functional as TF
-    x = torch.from_numpy(np.ascontiguousarray(img)).permute(2, 0, 1)[None]
+    x = torch.from_numpy(np.array(img, dtype=np.uint8, order="C")).permute(2, 0, 1)[None]   # (a copy: decoded images are read-only views)
     try:
         y = TF.interpolate(x, size=tuple(size), mode="bicubic", antialias=True, align_corners=False)
     except (RuntimeError, NotImplementedError):
