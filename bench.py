@@ -80,7 +80,7 @@ class ClockSampler:
 
 def reference_arm(args) -> int:
     """The reference is a Rust + HIP (gfx1201) project: it has no Python package to install
-    (`pip install /root/reference` answers: neither setup.py nor pyproject.toml), the image has no
+    (pip answers for its source tree: neither setup.py nor pyproject.toml), the image has no
     cargo/rustc/hipcc, and its kernels ship as AMD code objects only."""
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is Rust+HIP/gfx1201 only: not pip-installable, no cargo/hipcc in the image, cannot run on sm_100"}))

@@ -19,7 +19,7 @@
 // fp32 statement of the algorithm that version will be checked against.
 //
 // Parity: crates/saber-kernels/hip/sgdn_chunk.h / `chunk_scan` + `kkt` kernels of the reference's
-// prefill path (SURVEY: chunk_scan 2048 rows 159.9 us, kkt 43.1 us on gfx1201).
+// prefill path (its published timings on gfx1201: chunk_scan 2048 rows 159.9 us, kkt 43.1 us).
 #include "gdn.h"
 #include "launch.cuh"
 #include <cuda_bf16.h>
