@@ -189,7 +189,7 @@ int saber_program_add_pick_merge(void* h, const saber::PickMergeParams* p, const
   return add(h, OpPickMerge{*p}, p->nranks > 1 ? 1 : 0, tag);
 }
 int saber_program_add_moe_route(void* h, const saber::MoeRouteParams* p, const char* tag) {
-  return add(h, OpMoeRoute{*p}, 4, tag);
+  return add(h, OpMoeRoute{*p}, 3, tag);
 }
 int saber_program_add_moe_gather(void* h, const int8_t* q, const float* scale, int M_pad, const int32_t* src_row,
                                  const int32_t* ntiles, int8_t* q_out, float* scale_out, int rows_cap,

@@ -74,34 +74,54 @@ __global__ void __launch_bounds__(256) moe_topk_kernel(const MoeRouteParams p) {
   }
 }
 
-// one block of 1024 threads: padded exclusive scan of the counts, tile table, reset of the cursors.
+// One block of 1024 threads (one per local expert): exclusive scans of the padded row counts and of
+// the tile counts (warp shuffles, then the 32 warp totals), every thread writes its expert's tiles;
+// cursors and counts are cleared for the placement pass and for the next step's routing.
+__device__ __forceinline__ int block_excl_scan_1024(int v, int* warp_tot, int& total) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int n = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += n;
+  }
+  __syncthreads();                       // warp_tot may still be read by the previous scan
+  if (lane == 31) warp_tot[w] = inc;
+  __syncthreads();
+  int base = 0, tot = 0;
+#pragma unroll
+  for (int k = 0; k < 32; ++k) {
+    const int x = warp_tot[k];
+    if (k < w) base += x;
+    tot += x;
+  }
+  total = tot;
+  return base + inc - v;
+}
+
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const MoeRouteParams p) {
   pdl_wait();
-  __shared__ int padded[1024];
-  __shared__ int offs[1025];
+  __shared__ int warp_tot[32];
   const int t = threadIdx.x;
   int c = 0;
   if (t < p.e_n) {
     c = p.counts[t];
+    p.counts[t] = 0;                     // the next routing pass accumulates from zero
     p.cursors[t] = 0;
   }
-  padded[t] = t < p.e_n ? ((c + 15) & ~15) : 0;
-  __syncthreads();
-  if (t == 0) {
-    int acc = 0, nt_live = 0;
-    for (int e = 0; e < p.e_n; ++e) {
-      offs[e] = acc;
-      const int cnt = p.counts[e];
-      for (int r = 0; r < cnt; r += p.nt)
-        p.tiles[nt_live++] = make_int4(e, acc + r, min(p.nt, cnt - r), 0);
-      acc += padded[e];
-    }
-    offs[p.e_n] = acc;
-    p.ntiles[0] = nt_live;
-    p.ntiles[1] = acc;
+  int rows_total, tiles_total;
+  const int off = block_excl_scan_1024((c + 15) & ~15, warp_tot, rows_total);
+  const int toff = block_excl_scan_1024((c + p.nt - 1) / p.nt, warp_tot, tiles_total);
+  if (t < p.e_n) {
+    p.offsets[t] = off;
+    int i = toff;
+    for (int r = 0; r < c; r += p.nt) p.tiles[i++] = make_int4(t, off + r, min(p.nt, c - r), 0);
   }
-  __syncthreads();
-  if (t <= p.e_n) p.offsets[t] = offs[t];
+  if (t == 0) {
+    p.offsets[p.e_n] = rows_total;
+    p.ntiles[0] = tiles_total;
+    p.ntiles[1] = rows_total;
+  }
   for (int i = t; i < p.rows_cap; i += blockDim.x) p.src_row[i] = -1;
 }
 
@@ -132,13 +152,6 @@ __global__ void moe_gather_kernel(const int8_t* __restrict__ q, const float* __r
     v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(kb) * M_pad + m) * 128 + ((c ^ (m & 7)) << 4));
   *reinterpret_cast<uint4*>(q_out + (static_cast<size_t>(kb) * M_pad_out + r) * 128 + ((c ^ (r & 7)) << 4)) = v;
   if (threadIdx.x == 0) scale_out[r] = m >= 0 ? scale[m] : 0.f;
-}
-
-// clears the counts for the next step (after place has consumed them)
-__global__ void moe_reset_kernel(int32_t* counts, int n) {
-  pdl_wait();
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) counts[i] = 0;
 }
 
 // grid = (ceil(H / 256), ceil(M / nt)), block 256: lane -> 8 columns, warp -> rows w, w + 8, ...
@@ -217,7 +230,6 @@ extern "C" int saber_moe_route_launch(const saber::MoeRouteParams* p, cudaStream
   saber::launch(moe_topk_kernel, dim3((p->M + 7) / 8), dim3(256), 0, stream, 0, *p);
   saber::launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, 0, *p);
   saber::launch(moe_place_kernel, dim3((p->M * p->top_k + 255) / 256), dim3(256), 0, stream, 0, *p);
-  saber::launch(moe_reset_kernel, dim3((p->e_n + 255) / 256), dim3(256), 0, stream, 0, p->counts, p->e_n);
   return static_cast<int>(cudaGetLastError());
 }
 

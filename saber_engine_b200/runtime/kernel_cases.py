@@ -151,7 +151,7 @@ def _moe(M):
         add_moe_ops(prog, ws, cfg, moe, qa, out, F.scratch(DEV), "moe")
         progs.append(prog)
     torch.cuda.synchronize()
-    _time([p.run for p in progs] * 2, f"moe block (13 launches) M={M} experts={cfg.moe.n_experts} top_k={cfg.moe.top_k}")
+    _time([p.run for p in progs] * 2, f"moe block (12 launches) M={M} experts={cfg.moe.n_experts} top_k={cfg.moe.top_k}")
     return layers, ws, out, progs
 
 
