@@ -16,12 +16,12 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.mark.parametrize("nranks,M,splits", [(2, 9, 1), (4, 40, 2), (8, 72, 1)])
+@pytest.mark.parametrize("nranks,M,splits", [(2, 9, 1), (4, 40, 2), (8, 72, 1), (2, 256, 1)])   # the last: two token tiles per CTA
 def test_gemm_push_then_reduce_norm_quant(nranks, M, splits):
     torch.manual_seed(nranks)
     H, K = 512, 256 * nranks                      # hidden (GEMM N) and the full reduction dim
     Kr = K // nranks
-    group = SymmetricComm.local_group(nranks, DEV, max_elems=128 * H, rows_max=128, hidden=H)
+    group = SymmetricComm.local_group(nranks, DEV, max_elems=max(128, M) * H, rows_max=max(128, M), hidden=H)
     for g in group:
         g._local = True
     w = torch.randn(H, K) * 0.02
