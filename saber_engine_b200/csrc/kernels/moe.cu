@@ -137,21 +137,23 @@ __global__ void moe_place_kernel(const MoeRouteParams p) {
   p.src_row[pos] = i / p.top_k;
 }
 
-// grid = rows_cap, block = K / 16 threads (one 16-byte chunk each).
+// block = K / 16 threads (one 16-byte chunk each); the CTAs stride over the LIVE rows (a device-side
+// count): the grid is static (graph capture) but small, instead of one CTA per row of the worst case.
 __global__ void moe_gather_kernel(const int8_t* __restrict__ q, const float* __restrict__ scale, int M_pad,
                                   const int32_t* __restrict__ src_row, const int32_t* __restrict__ ntiles,
                                   int8_t* __restrict__ q_out, float* __restrict__ scale_out, int M_pad_out) {
   pdl_trigger();
   pdl_wait();
-  const int r = blockIdx.x;
-  if (r >= ntiles[1]) return;
-  const int m = src_row[r];
+  const int live = ntiles[1];
   const int kb = threadIdx.x >> 3, c = threadIdx.x & 7;       // k-block, logical 16-byte chunk
-  uint4 v = make_uint4(0u, 0u, 0u, 0u);
-  if (m >= 0)
-    v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(kb) * M_pad + m) * 128 + ((c ^ (m & 7)) << 4));
-  *reinterpret_cast<uint4*>(q_out + (static_cast<size_t>(kb) * M_pad_out + r) * 128 + ((c ^ (r & 7)) << 4)) = v;
-  if (threadIdx.x == 0) scale_out[r] = m >= 0 ? scale[m] : 0.f;
+  for (int r = blockIdx.x; r < live; r += gridDim.x) {
+    const int m = src_row[r];
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (m >= 0)
+      v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(kb) * M_pad + m) * 128 + ((c ^ (m & 7)) << 4));
+    *reinterpret_cast<uint4*>(q_out + (static_cast<size_t>(kb) * M_pad_out + r) * 128 + ((c ^ (r & 7)) << 4)) = v;
+    if (threadIdx.x == 0) scale_out[r] = m >= 0 ? scale[m] : 0.f;
+  }
 }
 
 // grid = (ceil(H / 256), ceil(M / nt)), block 256: lane -> 8 columns, warp -> rows w, w + 8, ...
@@ -237,7 +239,7 @@ extern "C" int saber_moe_gather_launch(const int8_t* q, const float* scale, int 
                                        const int32_t* ntiles, int8_t* q_out, float* scale_out, int rows_cap,
                                        int M_pad_out, int K, cudaStream_t stream) {
   if ((K & 127) || K / 16 > 1024 || rows_cap > M_pad_out) return static_cast<int>(cudaErrorInvalidValue);
-  saber::launch(saber::moe_gather_kernel, dim3(rows_cap), dim3(K / 16), 0, stream, 0, q, scale, M_pad, src_row, ntiles, q_out, scale_out, M_pad_out);
+  saber::launch(saber::moe_gather_kernel, dim3(rows_cap < 1184 ? rows_cap : 1184), dim3(K / 16), 0, stream, 0, q, scale, M_pad, src_row, ntiles, q_out, scale_out, M_pad_out);
   return static_cast<int>(cudaGetLastError());
 }
 
