@@ -195,7 +195,9 @@ class VisionTowerGPU:
             side = torch.cuda.Stream(device=d)
             side.wait_stream(cur)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
+            # thread-local capture mode: the engine's step loop keeps synchronising its own stream in
+            # another thread while an image of a new shape is captured here
+            with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
                 self._run(px, Lr, meta, ob, False)
             cur.wait_stream(side)
             if len(self._graphs) >= self.max_graphs:
