@@ -74,6 +74,7 @@ class VisionFrontend:
         cap_patches = min(self.arena.rows * merge2, getattr(tower, "max_patches", self.arena.rows * merge2))
         self.proc = proc.clamped_to_arena(cap_patches)
         self._encode = encode or self._encode_tower
+        self._tower_lock = threading.Lock()      # the tower's buffers serve one forward at a time
         self.counters = {"images": 0, "patch_rows": 0, "image_tokens": 0, "refused": 0}
 
     def _encode_tower(self, pixel_values: torch.Tensor, grids, out_rows: torch.Tensor) -> None:
@@ -101,7 +102,8 @@ class VisionFrontend:
             px = torch.from_numpy(np.concatenate([p.pixel_values for p in done], 0))
             if self.table.is_cuda:
                 px = px.pin_memory()
-            self._encode(px, grids, self.table[self.vocab + row0: self.vocab + row0 + total])
+            with self._tower_lock:
+                self._encode(px, grids, self.table[self.vocab + row0: self.vocab + row0 + total])
         except Exception:
             self.arena.free(row0, total)
             raise
