@@ -131,3 +131,48 @@ def test_image_prompt_through_scheduler_uses_tower_rows_and_three_axis_positions
     assert a[lay.pos + 1 * lay.M + 3] == 4 and a[lay.pos + 2 * lay.M + 16] == 18 and a[lay.slot_map + 16] == 2 * cfg.page_tokens + 0
     fill_blob(b, [SeqStep([5], 40, 1, 0, [1, 2, 3], rope_delta=-7)], cfg.page_tokens)
     assert a[lay.pos] == 33 and a[lay.kv_len] == 41
+
+
+def test_images_of_new_shapes_are_encoded_while_the_step_loop_decodes():
+    """The tower captures a CUDA graph per grid shape in the request thread while the scheduler's
+    own thread keeps replaying decode steps on the same stream: both must finish cleanly."""
+    import numpy as np
+    from saber_engine_b200.models import config as MC
+    from saber_engine_b200.models.hybrid import HybridModel
+    from saber_engine_b200.runtime.hybrid_executor import HybridExecutor
+    from saber_engine_b200.sched.scheduler import Scheduler, SchedulerConfig
+    from saber_engine_b200.serve.engine_api import EngineRequest, SamplingParams
+    from saber_engine_b200.vision import processor as VP
+    from saber_engine_b200.vision.engine import VisionFrontend
+    from saber_engine_b200.vision.tower import VisionConfig, VisionWeights
+    from saber_engine_b200.vision.tower_gpu import VisionTowerGPU
+    cfg = MC.scaled_hybrid()
+    model = HybridModel(cfg, device="cuda", max_seqs=4, max_ctx=1024, max_width=5, seed=2, image_rows=256)
+    ex = HybridExecutor(model, decode_batches=(1, 2, 4), decode_widths=(1, 5), prefill_rungs=(64, 256))
+    vcfg = VisionConfig.tiny(depth=1, out_hidden=cfg.hidden)
+    tower = VisionTowerGPU(vcfg, VisionWeights.random(vcfg, seed=7), "cuda", max_patches=1024)
+    PAD = 1999
+    vis = VisionFrontend(ex, tower, PAD, VP.ProcessorConfig(min_pixels=0))
+    s = Scheduler(ex, SchedulerConfig(max_seqs=4, max_ctx=1024, prefix_cache=False))
+    s.spawn_step_loop()
+    try:
+        long = s.submit(EngineRequest(list(range(10, 50)), SamplingParams(max_tokens=200, ignore_eos=True)))
+        rng = np.random.default_rng(5)
+        subs = []
+        for hw in [(64, 64), (96, 128), (64, 160)]:
+            img = rng.integers(0, 256, size=(*hw, 3), dtype=np.uint8)
+            subs.append(s.submit(vis.build_request([11, PAD, 12], [img], SamplingParams(max_tokens=6, ignore_eos=True))))
+        outs = []
+        for sub in subs + [long]:
+            toks = []
+            while True:
+                ev = sub.events.get(timeout=60)
+                assert ev.finish_reason != "error", ev.error
+                toks += ev.new_token_ids
+                if ev.finished:
+                    break
+            outs.append(toks)
+        assert [len(t) for t in outs] == [6, 6, 6, 200]
+        assert tower.graphs_captured == 3 and vis.arena.free_rows == 256 and s.fatal is None
+    finally:
+        s.shutdown()
