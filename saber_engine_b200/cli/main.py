@@ -95,12 +95,32 @@ def build_engine(a):
         from ..models.hybrid import HybridModel
         from ..runtime.hybrid_executor import HybridExecutor
         cfg = MC.by_name(a.engine_config)
+        widths = _ints(a.engine_decode_widths)
+        # several GPUs: one process per GPU (torchrun or the self-launch in cmd_engine); rank 0 plans
+        # and serves, the other ranks follow its executor calls (parallel/tp_serve.py)
+        rank, comm, dev = 0, None, "cuda"
+        if a.engine_tp > 1:
+            import os
+            import torch.distributed as dist
+            from ..parallel.symm import SymmetricComm
+            from ..parallel.tp_serve import init_control_group
+            rank, local = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", os.environ["RANK"]))
+            if int(os.environ["WORLD_SIZE"]) != a.engine_tp:
+                raise SystemExit(f"--engine-tp {a.engine_tp} needs {a.engine_tp} ranks, got {os.environ['WORLD_SIZE']}")
+            torch.cuda.set_device(local)
+            dev = torch.device("cuda", local)
+            dist.init_process_group("nccl", device_id=dev)
+            a._tp_group = init_control_group(timeout_s=7 * 86400.0)   # followers idle between requests
+            rows_max = max(max(_ints(a.engine_prefill_rows)), a.engine_max_seqs * max(widths), 128)
+            comm = SymmetricComm(rank, a.engine_tp, dev, max_elems=rows_max * cfg.hidden, rows_max=rows_max, hidden=cfg.hidden)
+            if getattr(a, "vision", False):
+                raise SystemExit("--vision serves from one GPU only")
+        a._tp_rank = rank
         weights = None
         if a.pack and not a.random_init:
             from ..pack.build import load_weights
-            weights = load_weights(a.pack, cfg, a.engine_tp, 0, "cuda")
-        widths = _ints(a.engine_decode_widths)
-        model = HybridModel(cfg, tp=a.engine_tp, rank=0, device="cuda", max_seqs=a.engine_max_seqs,
+            weights = load_weights(a.pack, cfg, a.engine_tp, rank, dev)
+        model = HybridModel(cfg, tp=a.engine_tp, rank=rank, device=dev, max_seqs=a.engine_max_seqs, comm=comm,
                             max_ctx=a.engine_max_ctx, kv_blocks=a.engine_kv_blocks or None, max_width=max(widths),
                             weights=weights, seed=a.seed, race_check=a.engine_race_check,
                             image_rows=(getattr(a, "vision_arena_patches", 0) // 4 if getattr(a, "vision", False) else 0))
@@ -109,6 +129,14 @@ def build_engine(a):
             model.tune_table = TuneTable.load(a.autotune)
         ex = HybridExecutor(model, _ints(a.engine_decode_batches), widths, _ints(a.engine_prefill_rows),
                             prebuild=a.prebuild)
+        if a.engine_tp > 1:
+            from ..parallel.tp_serve import TpLeaderExecutor, follower_loop
+            if rank != 0:                # a follower never returns from here until the leader stops it
+                follower_loop(ex, a._tp_group)
+                import torch.distributed as dist
+                dist.destroy_process_group()
+                raise SystemExit(0)
+            ex = TpLeaderExecutor(ex, a._tp_group)
     cfg_s = SchedulerConfig(max_seqs=a.engine_max_seqs, max_ctx=a.engine_max_ctx, prefix_cache=not a.no_prefix_cache,
                             prefix_cache_bytes=a.prefix_cache_host_mib << 20, model_name=a.served_model_name)
     sched = Scheduler(ex, cfg_s, sampler=HostSampler())
@@ -148,6 +176,13 @@ def build_engine(a):
 
 
 def cmd_engine(a) -> int:
+    import os
+    if getattr(a, "engine", "") == "real" and getattr(a, "engine_tp", 1) > 1 and "RANK" not in os.environ:
+        # self-launch: one process per GPU, rendezvous on the loopback address
+        port = 29400 + (os.getpid() % 500)
+        os.execvp(sys.executable, [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                                   f"--nproc-per-node={a.engine_tp}", "--master-addr", "127.0.0.1",
+                                   "--master-port", str(port), "-m", "saber_engine_b200", *sys.argv[1:]])
     import uvicorn
     from ..serve.server import ServerState, create_app
     from ..serve.tokenizer import ByteCodec, HfTokenizer
@@ -176,6 +211,8 @@ def cmd_engine(a) -> int:
         uvicorn.run(create_app(state), host=a.host, port=a.port, log_level="warning")
     finally:
         sched.shutdown()
+        if hasattr(ex, "stop_followers"):
+            ex.stop_followers()
     return 0
 
 

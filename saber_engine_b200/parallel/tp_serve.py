@@ -1,0 +1,121 @@
+"""Serving on several GPUs: rank 0 runs the scheduler and the HTTP plane, the other ranks follow.
+
+Every rank owns a shard of the model and runs the SAME step programs; the fused collectives inside
+the kernels keep the GPUs in step.  What the follower ranks lack is the scheduler's decisions, so
+rank 0 wraps its executor in `TpLeaderExecutor`: every executor call (prefill, decode, slot reset,
+state snapshot / restore) is first broadcast -- name and arguments, over a host-side (gloo) process
+group -- and then run locally; `follower_loop` on the other ranks receives the calls and runs them on
+its own executor, discarding the results (token picks are merged across ranks on the device and
+equal everywhere).
+
+    # one process per GPU, e.g. under torchrun
+    group = init_control_group()                      # gloo, beside the NCCL group used for bootstrap
+    if rank == 0:  scheduler = Scheduler(TpLeaderExecutor(executor, group), ...)
+    else:          follower_loop(executor, group)
+
+Parity: the reference's rank workers (`crates/saber-exec/src/peer.rs:140` `RankPeer::agree`, the
+2-rank command line of `crates/saber-engine/src/device.rs`): one planning rank, lock-step followers.
+"""
+from __future__ import annotations
+
+import itertools
+from typing import Optional
+
+FORWARDED = ("prefill", "decode", "reset_slot")
+
+
+def init_control_group(timeout_s: float = 1800.0):
+    """A gloo group over all ranks for the host-side command broadcast (the default group may be NCCL)."""
+    import datetime
+
+    import torch.distributed as dist
+    return dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=timeout_s))
+
+
+class TpLeaderExecutor:
+    """Rank 0's executor: broadcasts each call to the followers, then runs it on the local shard."""
+
+    def __init__(self, inner, group, src: int = 0):
+        self.inner, self.group, self.src = inner, group, src
+        self._snap_ids = itertools.count(1)
+        self.calls_cast = 0
+
+    def __getattr__(self, name):                     # geometry, census, model, ...: the local executor's
+        return getattr(self.inner, name)
+
+    def _cast(self, name: str, *args) -> None:
+        import torch.distributed as dist
+        dist.broadcast_object_list([(name, args)], src=self.src, group=self.group)
+        self.calls_cast += 1
+
+    def prefill(self, runs: list) -> list:
+        self._cast("prefill", runs)
+        return self.inner.prefill(runs)
+
+    def decode(self, runs: list, width: int) -> list:
+        self._cast("decode", runs, width)
+        return self.inner.decode(runs, width)
+
+    def reset_slot(self, slot: int) -> None:
+        self._cast("reset_slot", slot)
+        self.inner.reset_slot(slot)
+
+    # prefix-cache snapshots: every rank keeps its own shard of a snapshot under the leader's id
+    def snapshot_state(self, slot: int):
+        sid = next(self._snap_ids)
+        self._cast("snapshot_state", slot, sid)
+        return {"id": sid, "local": self.inner.snapshot_state(slot)}
+
+    def restore_state(self, slot: int, snap) -> None:
+        self._cast("restore_state", slot, snap["id"])
+        self.inner.restore_state(slot, snap["local"])
+
+    def free_snapshot(self, snap) -> None:
+        if isinstance(snap, dict) and "id" in snap:
+            self._cast("free_snapshot", snap["id"])
+            self.inner.free_snapshot(snap["local"])
+
+    def snapshot_bytes(self) -> int:
+        return self.inner.snapshot_bytes()
+
+    # session parking moves one rank's shard only: refused on several GPUs
+    def export_session(self, *a, **k):
+        raise NotImplementedError("session parking is not available on several GPUs")
+
+    import_session = export_session
+
+    def stop_followers(self) -> None:
+        self._cast("stop")
+
+
+def follower_loop(executor, group, src: int = 0, on_call=None) -> int:
+    """Runs the leader's calls on this rank's executor until the leader says stop.  Returns the number
+    of calls served."""
+    import torch.distributed as dist
+    snaps: dict = {}
+    served = 0
+    while True:
+        box = [None]
+        dist.broadcast_object_list(box, src=src, group=group)
+        name, args = box[0]
+        if name == "stop":
+            return served
+        if name == "prefill":
+            executor.prefill(args[0])
+        elif name == "decode":
+            executor.decode(args[0], args[1])
+        elif name == "reset_slot":
+            executor.reset_slot(args[0])
+        elif name == "snapshot_state":
+            snaps[args[1]] = executor.snapshot_state(args[0])
+        elif name == "restore_state":
+            executor.restore_state(args[0], snaps[args[1]])
+        elif name == "free_snapshot":
+            s = snaps.pop(args[0], None)
+            if s is not None:
+                executor.free_snapshot(s)
+        else:
+            raise RuntimeError(f"unknown call from the leader: {name!r}")
+        served += 1
+        if on_call is not None:
+            on_call(name, args)
