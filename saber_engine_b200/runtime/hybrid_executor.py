@@ -67,6 +67,8 @@ class HybridExecutor:
         self.vocab = model.cfg.vocab
         self.capture = capture
         self.census = {"graph_replays": 0, "eager_walks": 0, "launches": 0, "buckets_built": 0}
+        # the head over every prompt row needs the whole vocabulary on one GPU
+        self.supports_prompt_logprobs = model.tp == 1
         if prebuild:
             for b in self.decode_batches:
                 for w in self.decode_widths:

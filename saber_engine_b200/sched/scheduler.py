@@ -114,6 +114,8 @@ class Scheduler:
         if n == 0:
             raise EngineRefused("empty prompt", 400)
         problems = req.params.validate(self.ex.vocab, self.cfg.max_ctx, n)
+        if req.params.prompt_logprobs is not None and not getattr(self.ex, "supports_prompt_logprobs", True):
+            problems.append("prompt_logprobs is not available on this engine (vocabulary-sharded ranks)")
         if problems:
             raise EngineRefused("; ".join(problems), 400)
         with self._lock:

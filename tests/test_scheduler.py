@@ -163,3 +163,18 @@ def test_step_loop_thread_serves_requests():
             assert toks == reference_generation([i, i + 1, i + 2], 12, 1024)
     finally:
         sched.shutdown()
+
+
+def test_prompt_logprobs_refused_at_submit_when_the_engine_cannot_produce_them():
+    from saber_engine_b200.sched.mock import NullExecutor
+    from saber_engine_b200.sched.scheduler import Scheduler, SchedulerConfig
+    from saber_engine_b200.serve.engine_api import EngineRefused, EngineRequest, SamplingParams
+    ex = NullExecutor(vocab=300)
+    ex.supports_prompt_logprobs = False
+    s = Scheduler(ex, SchedulerConfig(max_seqs=2, max_ctx=512))
+    import pytest
+    with pytest.raises(EngineRefused) as e:
+        s.submit(EngineRequest([1, 2, 3], SamplingParams(max_tokens=2, prompt_logprobs=1)))
+    assert e.value.status == 400 and s.fatal is None
+    s.submit(EngineRequest([1, 2, 3], SamplingParams(max_tokens=2)))
+    s.run_until_idle()
