@@ -132,6 +132,11 @@ __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
 // together, so the per-row loop touches no global memory except its one output element).
 constexpr int kRecBatch = 16;
 
+__device__ __forceinline__ void gdn_cp16(void* dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst_smem))),
+               "l"(src) : "memory");
+}
+
 template <int VS>
 __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecParams p) {
   pdl_wait();
@@ -140,8 +145,13 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
   constexpr int KP = 64 + 4;           // padded half stride in shared memory (bank spread)
   __shared__ __align__(16) float ks[kRecBatch][2 * KP];
   __shared__ __align__(16) float qs[kRecBatch][2 * KP];
-  __shared__ float vsm[kRecBatch][VR];
+  __shared__ __align__(16) float vsm[kRecBatch][VR];
   __shared__ float gsm[kRecBatch], bsm[kRecBatch];
+  // the replayed rows of the previous step have buffers of their own: they are fetched together
+  // with this step's first batch and the state, so the kernel waits for global memory once
+  __shared__ __align__(16) float ksr[kRecBatch][2 * KP];
+  __shared__ __align__(16) float vsr[kRecBatch][VR];
+  __shared__ float gsr[kRecBatch], bsr[kRecBatch];
   const int b = blockIdx.y;
   const int slot = p.slots[b];
   if (slot < 0) return;
@@ -159,6 +169,37 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
                             static_cast<size_t>(h) * VS + vs) * stash_stride;
   const size_t stash_row = static_cast<size_t>(p.HV) * VS * stash_stride;
 
+  // ---- everything this CTA reads from global memory goes out now: replay rows, first batch, state
+  const int nb0 = min(kRecBatch, n);
+  for (int idx = tid; idx < shift * 32; idx += NT) {
+    const int r = idx >> 5, i = (idx & 31) * 4;
+    gdn_cp16(&ksr[r][(i >> 6) * KP + (i & 63)], stash + static_cast<size_t>(r) * stash_row + i);
+  }
+  for (int idx = tid; idx < shift * (VR / 4); idx += NT) {
+    const int r = idx / (VR / 4), i = (idx % (VR / 4)) * 4;
+    gdn_cp16(&vsr[r][i], stash + static_cast<size_t>(r) * stash_row + 128 + i);
+  }
+  for (int idx = tid; idx < nb0 * 64; idx += NT) {
+    const int r = idx >> 6, c = idx & 63, i = (c & 31) * 4;
+    const float* xr = p.qkv + static_cast<size_t>(row0 + r) * p.C;
+    if (c < 32) gdn_cp16(&qs[r][(i >> 6) * KP + (i & 63)], xr + hk * 128 + i);
+    else gdn_cp16(&ks[r][(i >> 6) * KP + (i & 63)], xr + p.n_q + hk * 128 + i);
+  }
+  for (int idx = tid; idx < nb0 * (VR / 4); idx += NT) {
+    const int r = idx / (VR / 4), i = (idx % (VR / 4)) * 4;
+    gdn_cp16(&vsm[r][i], p.qkv + static_cast<size_t>(row0 + r) * p.C + p.n_q + p.n_k + h * 128 + vs * VR + i);
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  float g_rep = 0.f, b_rep = 0.f, bb0 = 0.f, aa0 = 0.f;
+  if (tid < shift) {
+    g_rep = stash[static_cast<size_t>(tid) * stash_row + 128 + VR];
+    b_rep = stash[static_cast<size_t>(tid) * stash_row + 128 + VR + 1];
+  }
+  if (tid < nb0) {
+    const size_t m = static_cast<size_t>(row0 + tid);
+    bb0 = __bfloat162float(p.ba[m * p.ldba + h]);
+    aa0 = __bfloat162float(p.ba[m * p.ldba + p.HV + h]);
+  }
   f32x2 S[32];   // this thread's 64 state values as packed pairs
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
@@ -168,6 +209,13 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
   }
   const float neg_a = -__expf(p.A_log[h]);
   const float dtb = p.dt_bias[h];
+  if (tid < shift) { gsr[tid] = g_rep; bsr[tid] = b_rep; }
+  if (tid < nb0) {
+    gsm[tid] = neg_a * gdn_softplus(aa0 + dtb);
+    bsm[tid] = 1.f / (1.f + __expf(-bb0));
+  }
+  asm volatile("cp.async.wait_all;" ::: "memory");
+  __syncthreads();
 
   auto apply = [&](const float* kv, const float* qv, float vval, float g, float beta,
                    bool want_o) -> float {
@@ -210,47 +258,35 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
 
   // ---- replay the accepted rows of the previous step, then store the committed state
   if (shift > 0) {
-    for (int idx = tid; idx < shift * 128; idx += NT) {
-      const int r = idx >> 7, i = idx & 127;
-      ks[r][(i >> 6) * KP + (i & 63)] = stash[static_cast<size_t>(r) * stash_row + i];
-    }
-    for (int idx = tid; idx < shift * VR; idx += NT) {
-      const int r = idx / VR, i = idx % VR;
-      vsm[r][i] = stash[static_cast<size_t>(r) * stash_row + 128 + i];
-    }
-    if (tid < shift) {
-      gsm[tid] = stash[static_cast<size_t>(tid) * stash_row + 128 + VR];
-      bsm[tid] = stash[static_cast<size_t>(tid) * stash_row + 128 + VR + 1];
-    }
-    __syncthreads();
-    for (int r = 0; r < shift; ++r) apply(&ks[r][kh * KP], nullptr, vsm[r][vloc], gsm[r], bsm[r], false);
+    for (int r = 0; r < shift; ++r) apply(&ksr[r][kh * KP], nullptr, vsr[r][vloc], gsr[r], bsr[r], false);
 #pragma unroll
     for (int i = 0; i < 16; ++i)
       reinterpret_cast<ulonglong2*>(sp)[i] = make_ulonglong2(S[2 * i], S[2 * i + 1]);
-    __syncthreads();
   }
 
   // ---- this step's rows, a batch at a time
   for (int r0 = 0; r0 < n; r0 += kRecBatch) {
     const int nb = min(kRecBatch, n - r0);
-    for (int idx = tid; idx < nb * 128; idx += NT) {
-      const int r = idx >> 7, i = idx & 127;
-      const float* xr = p.qkv + static_cast<size_t>(row0 + r0 + r) * p.C;
-      qs[r][(i >> 6) * KP + (i & 63)] = xr[hk * 128 + i];
-      ks[r][(i >> 6) * KP + (i & 63)] = xr[p.n_q + hk * 128 + i];
+    if (r0 > 0) {      // (the first batch arrived with the state)
+      for (int idx = tid; idx < nb * 128; idx += NT) {
+        const int r = idx >> 7, i = idx & 127;
+        const float* xr = p.qkv + static_cast<size_t>(row0 + r0 + r) * p.C;
+        qs[r][(i >> 6) * KP + (i & 63)] = xr[hk * 128 + i];
+        ks[r][(i >> 6) * KP + (i & 63)] = xr[p.n_q + hk * 128 + i];
+      }
+      for (int idx = tid; idx < nb * VR; idx += NT) {
+        const int r = idx / VR, i = idx % VR;
+        vsm[r][i] = p.qkv[static_cast<size_t>(row0 + r0 + r) * p.C + p.n_q + p.n_k + h * 128 + vs * VR + i];
+      }
+      if (tid < nb) {
+        const size_t m = static_cast<size_t>(row0 + r0 + tid);
+        const float bb = __bfloat162float(p.ba[m * p.ldba + h]);
+        const float aa = __bfloat162float(p.ba[m * p.ldba + p.HV + h]);
+        gsm[tid] = neg_a * gdn_softplus(aa + dtb);
+        bsm[tid] = 1.f / (1.f + __expf(-bb));
+      }
+      __syncthreads();
     }
-    for (int idx = tid; idx < nb * VR; idx += NT) {
-      const int r = idx / VR, i = idx % VR;
-      vsm[r][i] = p.qkv[static_cast<size_t>(row0 + r0 + r) * p.C + p.n_q + p.n_k + h * 128 + vs * VR + i];
-    }
-    if (tid < nb) {
-      const size_t m = static_cast<size_t>(row0 + r0 + tid);
-      const float bb = __bfloat162float(p.ba[m * p.ldba + h]);
-      const float aa = __bfloat162float(p.ba[m * p.ldba + p.HV + h]);
-      gsm[tid] = neg_a * gdn_softplus(aa + dtb);
-      bsm[tid] = 1.f / (1.f + __expf(-bb));
-    }
-    __syncthreads();
     for (int r = 0; r < nb; ++r) {
       const float o = apply(&ks[r][kh * KP], &qs[r][kh * KP], vsm[r][vloc], gsm[r], bsm[r], true);
       if (kh == 0)
