@@ -5,6 +5,7 @@ import signal
 import subprocess
 import sys
 import time
+import urllib.error
 import urllib.request
 
 import pytest
@@ -42,8 +43,13 @@ def test_two_rank_engine_serves_greedy_and_sampled_requests():
         assert a == b and a
         s = _post(port, "/v1/completions", {**body, "temperature": 0.9, "seed": 4, "logprobs": 1})["choices"][0]
         assert len(s["logprobs"]["tokens"]) == 10
-        r = _post(port, "/v1/completions", {**body, "prompt_logprobs": 1}) if False else None      # refused on sharded ranks (400)
-        assert r is None
+        try:                                                    # prompt log-probabilities need the whole vocabulary on one GPU
+            _post(port, "/v1/completions", {**body, "prompt_logprobs": 1})
+            refused = False
+        except urllib.error.HTTPError as e:
+            refused = e.code == 400
+        assert refused
+        assert _post(port, "/v1/completions", body)["choices"][0]["text"] == a      # the engine is still up
     finally:
         os.killpg(p.pid, signal.SIGINT)
         try:
