@@ -54,12 +54,13 @@ struct OpMoeRoute { saber::MoeRouteParams p; };
 struct OpMoeCombine { saber::MoeCombineParams p; };
 struct OpDigest { const void* buf; size_t bytes; unsigned long long* out; };
 struct OpDigestClear { unsigned long long* out; int n; };
+struct OpSampleSeam { const int32_t* ids; const float* vals; const float* samp; const float* u; int32_t* picks; int rows; };
 struct OpLogitGather { const void* logits; int rows, ld, V, id_offset; const int32_t* ids; float* out; };
 struct OpMoeGather { const int8_t* q; const float* scale; int M_pad; const int32_t* src_row; const int32_t* ntiles;
                      int8_t* q_out; float* scale_out; int rows_cap, M_pad_out, K; };
 
 using Op = std::variant<OpGemm, OpRow, OpEmbed, OpGdnConv, OpGdnRec, OpRope, OpAttn, OpArgmax,
-                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather, OpDigest, OpDigestClear, OpGdnChunk, OpLogitGather>;
+                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather, OpDigest, OpDigestClear, OpGdnChunk, OpLogitGather, OpSampleSeam>;
 
 struct Entry {
   Op op;
@@ -106,6 +107,7 @@ int launch(const Op& op, cudaStream_t s) {
         else if constexpr (std::is_same_v<T, OpMoeCombine>) return saber_moe_combine_launch(&o.p, s);
         else if constexpr (std::is_same_v<T, OpDigest>) return saber_digest_launch(o.buf, o.bytes, o.out, s);
         else if constexpr (std::is_same_v<T, OpDigestClear>) return saber_digest_clear_launch(o.out, o.n, s);
+        else if constexpr (std::is_same_v<T, OpSampleSeam>) return saber_sample_seam_launch(o.ids, o.vals, o.samp, o.u, o.picks, o.rows, s);
         else if constexpr (std::is_same_v<T, OpLogitGather>) return saber_logit_gather_launch(o.logits, o.rows, o.ld, o.V, o.id_offset, o.ids, o.out, s);
         else if constexpr (std::is_same_v<T, OpMoeGather>)
           return saber_moe_gather_launch(o.q, o.scale, o.M_pad, o.src_row, o.ntiles, o.q_out, o.scale_out, o.rows_cap,
@@ -198,6 +200,10 @@ int saber_program_add_moe_gather(void* h, const int8_t* q, const float* scale, i
 }
 int saber_program_add_digest(void* h, const void* buf, size_t bytes, unsigned long long* out, const char* tag) {
   return add(h, OpDigest{buf, bytes, out}, 1, tag);
+}
+int saber_program_add_sample_seam(void* h, const int32_t* ids, const float* vals, const float* samp, const float* u,
+                                  int32_t* picks, int rows, const char* tag) {
+  return add(h, OpSampleSeam{ids, vals, samp, u, picks, rows}, 1, tag);
 }
 int saber_program_add_logit_gather(void* h, const void* logits, int rows, int ld, int V, int id_offset,
                                    const int32_t* ids, float* out, const char* tag) {

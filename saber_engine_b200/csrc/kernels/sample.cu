@@ -283,6 +283,64 @@ __global__ void logit_gather_kernel(const __nv_bfloat16* logits, int ld, int V, 
 }
 }  // namespace saber
 
+namespace saber {
+// Device draw for sampled rows.  The row's 64 candidates arrive sorted (value descending); with
+// temperature T the probabilities are softmax(v / T) over the candidates, cut by min-p, top-k and
+// top-p in that order (at least one stays), renormalised, and the uniform number u[m] (drawn on the
+// host as a function of seed and position) picks the token.  Rows with T <= 0 keep their greedy pick.
+// samp: [rows][4] = {T, top_k, top_p, min_p}.  One thread per row.
+__global__ void sample_seam_kernel(const int32_t* ids, const float* vals, const float* samp, const float* u,
+                                   int32_t* picks, int rows) {
+  pdl_wait();
+  const int m = blockIdx.x * blockDim.x + threadIdx.x;
+  if (m >= rows) return;
+  const float T = samp[4 * m];
+  if (!(T > 0.f)) return;
+  const int top_k = static_cast<int>(samp[4 * m + 1]);
+  const float top_p = samp[4 * m + 2], min_p = samp[4 * m + 3];
+  const float* v = vals + static_cast<size_t>(m) * kSeamK;
+  const int32_t* id = ids + static_cast<size_t>(m) * kSeamK;
+  const float inv_t = 1.f / fmaxf(T, 1e-6f), m0 = v[0] * inv_t;
+  float z = 0.f;
+  for (int j = 0; j < kSeamK; ++j) z += expf(v[j] * inv_t - m0);
+  int keep = kSeamK;
+  if (min_p > 0.f) {              // p_j >= min_p * p_0  <=>  e_j >= min_p  (e_0 = 1)
+    int c = 0;
+    for (int j = 0; j < kSeamK; ++j) c += expf(v[j] * inv_t - m0) >= min_p ? 1 : 0;
+    keep = min(keep, c);
+  }
+  if (top_k > 0) keep = min(keep, top_k);
+  if (top_p < 1.f) {
+    float acc = 0.f;
+    int k = 0;
+    for (int j = 0; j < keep; ++j) {
+      acc += expf(v[j] * inv_t - m0) / z;
+      ++k;
+      if (acc >= top_p) break;
+    }
+    keep = min(keep, k);
+  }
+  keep = max(1, keep);
+  float z2 = 0.f;
+  for (int j = 0; j < keep; ++j) z2 += expf(v[j] * inv_t - m0) / z;
+  const float x = u[m] * z2;
+  float acc = 0.f;
+  int pick = id[keep - 1];
+  for (int j = 0; j < keep; ++j) {
+    acc += expf(v[j] * inv_t - m0) / z;
+    if (x < acc) { pick = id[j]; break; }
+  }
+  picks[m] = pick;
+}
+}  // namespace saber
+
+extern "C" int saber_sample_seam_launch(const int32_t* ids, const float* vals, const float* samp, const float* u,
+                                        int32_t* picks, int rows, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  saber::launch(saber::sample_seam_kernel, dim3((rows + 63) / 64), dim3(64), 0, stream, 0, ids, vals, samp, u, picks, rows);
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int saber_logit_gather_launch(const void* logits, int rows, int ld, int V, int id_offset,
                                          const int32_t* ids, float* out, cudaStream_t stream) {
   if (rows <= 0) return 0;

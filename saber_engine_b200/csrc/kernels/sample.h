@@ -30,5 +30,7 @@ extern "C" int saber_topk_seam_launch(const void* logits, int rows, int ld, int 
                                       const float* temps, int32_t* ids, float* vals, float* lse,
                                       cudaStream_t stream);
 extern "C" int saber_verify_launch(const saber::VerifyParams* p, cudaStream_t stream);
+extern "C" int saber_sample_seam_launch(const int32_t* ids, const float* vals, const float* samp, const float* u,
+                                        int32_t* picks, int rows, cudaStream_t stream);
 extern "C" int saber_logit_gather_launch(const void* logits, int rows, int ld, int V, int id_offset,
                                          const int32_t* ids, float* out, cudaStream_t stream);

@@ -46,6 +46,8 @@ class BlobLayout:
     last_rows: int = 0
     temps: int = 0
     next_ids: int = 0          # per row: the token that follows it in its prompt (-1: none), for prompt log-probabilities
+    samp: int = 0              # per HEAD row: fp32 {temperature, top_k, top_p, min_p} (temperature 0: keep the greedy pick)
+    samp_u: int = 0            # per HEAD row: the uniform number of the draw (fp32)
     block_table: int = 0
     words: int = 0
 
@@ -70,6 +72,8 @@ class BlobLayout:
         b.last_rows = take(nseq)
         b.temps = take(M)
         b.next_ids = take(M)
+        b.samp = take(4 * M)
+        b.samp_u = take(M)
         b.block_table = take(nseq * max_blocks)
         b.words = off
         return b
@@ -439,6 +443,10 @@ class HybridModel:
             s_vals = seam_dev[Mh * N.SEAM_K: 2 * Mh * N.SEAM_K].view(torch.float32)
             s_lse = seam_dev[2 * Mh * N.SEAM_K:].view(torch.float32)
             prog.seam(logits, Mh, logits.stride(0), sh.vocab, sh.vocab_first, None, s_ids, s_vals, s_lse, tag="topk_seam")
+            if self.tp == 1:
+                # device draw for sampled rows: the picks that verify / accept and the drafter see are
+                # the sampled tokens (the host repeats the draw from the same candidates and uniforms)
+                prog.sample_seam(s_ids, s_vals, at(lay.samp), at(lay.samp_u), o_picks, Mh, tag="sample_seam")
             keep += [seam_dev]
         plp_dev = None
         if self._want_plp:
@@ -550,6 +558,8 @@ class SeqStep:
     rope_pos: Optional[object] = None   # int [3, rows]: three-axis rotary positions of the rows (prompts with images)
     rope_delta: int = 0       # added to the index of every row for the rotary position (after an image)
     next_token: int = -1      # the prompt token after this chunk's last row (-1: none), for prompt log-probabilities
+    sampling: Optional[tuple] = None   # (temperature, top_k, top_p, min_p) of a sampled sequence the device may draw for
+    uniforms: Optional[list] = None    # one uniform number per head row of this step (decode: every row; prefill: the last)
 
 
 @dataclass
@@ -577,6 +587,12 @@ def fill_blob(b: Bucket, seqs: list, page_tokens: int = 16) -> int:
         n = len(s.tokens)
         a[lay.ids + row: lay.ids + row + n] = s.tokens
         a[lay.next_ids + row: lay.next_ids + row + n] = list(s.tokens[1:]) + [s.next_token]
+        if s.sampling is not None and s.uniforms:
+            hr0, hn = (row, n) if b.kind == "decode" else (j, 1)      # head rows of this sequence
+            fa = a.view(np.float32)
+            for r in range(min(hn, len(s.uniforms))):
+                fa[lay.samp + 4 * (hr0 + r): lay.samp + 4 * (hr0 + r) + 4] = s.sampling
+                fa[lay.samp_u + hr0 + r] = s.uniforms[r]
         pos = np.arange(s.pos0, s.pos0 + n, dtype=np.int32)
         for ax in range(3):
             a[lay.pos + ax * M + row: lay.pos + ax * M + row + n] = \

@@ -204,6 +204,8 @@ def _declare(L: C.CDLL) -> None:
         "saber_program_add_argmax": (I, [P, P, I, I, I, I, P, P, C.c_char_p]),
         "saber_program_add_seam": (I, [P, P, I, I, I, I, P, P, P, P, C.c_char_p]),
         "saber_program_add_logit_gather": (I, [P, P, I, I, I, I, P, P, C.c_char_p]),
+        "saber_program_add_sample_seam": (I, [P, P, P, P, P, P, I, C.c_char_p]),
+        "saber_sample_seam_launch": (I, [P, P, P, P, P, I, S]),
         "saber_program_add_verify": (I, [P, C.POINTER(VerifyParams), C.c_char_p]),
         "saber_program_add_memset": (I, [P, P, I, C.c_size_t, C.c_char_p]),
         "saber_program_add_copy": (I, [P, P, P, C.c_size_t, C.c_char_p]),
@@ -314,6 +316,9 @@ class Program:
     def argmax(self, logits, rows, ld, V, id_offset, idx, val, tag="argmax") -> int:
         return self._L.saber_program_add_argmax(self._h, ptr(logits), rows, ld, V, id_offset,
                                                 ptr(idx), ptr(val), tag.encode())
+
+    def sample_seam(self, ids, vals, samp, u, picks, rows, tag="sample_seam") -> int:
+        return self._L.saber_program_add_sample_seam(self._h, ptr(ids), ptr(vals), ptr(samp), ptr(u), ptr(picks), rows, tag.encode())
 
     def logit_gather(self, logits, rows, ld, V, id_offset, ids, out, tag="logit_gather") -> int:
         return self._L.saber_program_add_logit_gather(self._h, ptr(logits), rows, ld, V, id_offset,

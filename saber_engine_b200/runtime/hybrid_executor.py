@@ -125,7 +125,8 @@ class HybridExecutor:
     @staticmethod
     def _step(r: SeqRun) -> SeqStep:
         return SeqStep(list(r.tokens), r.pos0, r.slot, r.shift, r.blocks, uid=r.uid, step_no=r.step_no,
-                       rope_pos=r.rope_pos, rope_delta=r.rope_delta, next_token=getattr(r, "next_token", -1))
+                       rope_pos=r.rope_pos, rope_delta=r.rope_delta, next_token=getattr(r, "next_token", -1),
+                       sampling=getattr(r, "sampling", None), uniforms=getattr(r, "uniforms", None))
 
     def _count(self, b) -> None:
         self.census["graph_replays" if b.captured else "eager_walks"] += 1

@@ -29,6 +29,8 @@ class SeqRun:
     rope_delta: int = 0          # rotary position - index for rows after the prompt's images
     prompt_lp: Optional[int] = None   # prefill: log-probability of every next prompt token with this many alternatives
     next_token: int = -1         # the prompt token after this chunk (-1: the chunk ends the prompt)
+    sampling: Optional[tuple] = None   # (temperature, top_k, top_p, min_p): the device may draw for this sequence
+    uniforms: Optional[list] = None    # the uniform numbers of this step's head rows
 
 
 @dataclass

@@ -95,7 +95,8 @@ class Scheduler:
         self.fatal: Optional[str] = None
         self.counters = dict(steps=0, prefill_steps=0, decode_steps=0, prompt_tokens=0, generation_tokens=0,
                              drafts=0, draft_tokens=0, accepted_tokens=0, requests_finished=0,
-                             requests_refused=0, requests_aborted=0, padding_slots=0)
+                             requests_refused=0, requests_aborted=0, padding_slots=0,
+                             sampled_steps=0, sampled_steps_device_agrees=0)
         self.accepted_per_pos = [0] * 16
         self.last_step_s = 0.0
         self.on_step = None                 # optional callback(timing dict) for metrics
@@ -240,7 +241,8 @@ class Scheduler:
                                    rope_pos=(None if s.req.mm is None else
                                              [list(ax[pos:pos + n]) for ax in s.req.mm["rope_pos"]]),
                                    prompt_lp=s.req.params.prompt_logprobs,
-                                   next_token=(s.prompt[pos + n] if pos + n < len(s.prompt) else -1))
+                                   next_token=(s.prompt[pos + n] if pos + n < len(s.prompt) else -1),
+                                   **(self._device_draw(s, 1) if pos + n == len(s.prompt) else {}))
                             for s, pos, n in plan[1]]
                     outs = self.ex.prefill(runs)
                 else:
@@ -251,7 +253,8 @@ class Scheduler:
                         runs.append(SeqRun(s.seq_id, [s.output[-1]] + drafts, s.pos, s.slot, s.shift, s.blocks,
                                            uid=s.seq_id, step_no=s.step_no, temperature=s.req.params.temperature,
                                            want_seam=self._wants_seam(s),
-                                           rope_delta=(0 if s.req.mm is None else int(s.req.mm.get("rope_delta", 0)))))
+                                           rope_delta=(0 if s.req.mm is None else int(s.req.mm.get("rope_delta", 0))),
+                                           **self._device_draw(s, width)))
                     outs = self.ex.decode(runs, width)
         except Exception as exc:       # the executor failed: every request learns why (fatal law)
             self.set_fatal(f"executor failed: {exc!r}")
@@ -344,6 +347,9 @@ class Scheduler:
             toks = list(out.tokens)
             if not s.req.params.greedy and self.sampler is not None and out.seam is not None:
                 toks = self._accept_sampled(s, out, width)
+                # census: did the device's own draw (same candidates, same uniform numbers) commit the same tokens?
+                self.counters["sampled_steps"] += 1
+                self.counters["sampled_steps_device_agrees"] += int(list(out.tokens) == toks)
             n = len(toks)
             self.counters["drafts"] += 1
             self.counters["draft_tokens"] += width - 1
@@ -357,6 +363,17 @@ class Scheduler:
             s.step_no += 1
             s.drafts = list(out.drafts)
             self._append(s, toks, dt, drafted=width - 1, accepted=n - 1, lps=self._logprobs(s, out, toks, 0))
+
+    def _device_draw(self, s: Sequence, n_rows: int) -> dict:
+        """Sampling parameters and the uniform numbers of this step's head rows, for executors that
+        draw on the device (the host repeats the draw and stays authoritative)."""
+        smp = self.sampler
+        if s.req.params.greedy or smp is None or not hasattr(smp, "device_params"):
+            return {}
+        dp = smp.device_params(s.req.params)
+        if dp is None:
+            return {}
+        return {"sampling": dp, "uniforms": smp.uniforms(s.req.params, s.seq_id, len(s.output), n_rows)}
 
     @staticmethod
     def _wants_seam(s: Sequence) -> bool:

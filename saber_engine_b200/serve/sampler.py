@@ -96,6 +96,20 @@ class HostSampler:
         tok, _ = sample_candidates(list(ids), list(vals), params, prompt, output, uniform01(seed, uid, position))
         return int(tok)
 
+    def uniforms(self, params: SamplingParams, seq_uid: int, position0: int, n: int) -> list:
+        """The uniform numbers `sample_row` will use at positions position0 .. position0 + n - 1 (the
+        device draws with the same numbers)."""
+        seed = params.seed if params.seed is not None else self.default_seed ^ (seq_uid * 0x9E3779B1)
+        uid = 0 if params.seed is not None else seq_uid
+        return [uniform01(seed, uid, position0 + r) for r in range(n)]
+
+    @staticmethod
+    def device_params(params: SamplingParams):
+        """(temperature, top_k, top_p, min_p) when the device can repeat the host's draw: no penalties."""
+        if params.greedy or params.repetition_penalty != 1.0 or params.frequency_penalty != 0.0 or params.presence_penalty != 0.0:
+            return None
+        return (float(params.temperature), float(params.top_k), float(params.top_p), float(params.min_p))
+
     @staticmethod
     def seam_from_logits(logits_rows, k: int = 64) -> dict:
         """Build a seam from full logits rows (CPU executors): top-k by (value desc, id asc)."""

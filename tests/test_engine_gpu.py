@@ -177,3 +177,16 @@ def test_prompt_logprobs_match_a_full_logits_pass(executor):
     plain = s2.submit(EngineRequest(prompt, SamplingParams(max_tokens=3, ignore_eos=True)))
     s2.run_until_idle()
     assert toks == _collect(plain)[0]
+
+
+def test_device_draws_agree_with_the_host_sampler_during_sampled_decoding(executor):
+    from saber_engine_b200.serve.sampler import HostSampler
+    g = torch.Generator().manual_seed(9)
+    prompt = torch.randint(0, executor.vocab, (50,), generator=g).tolist()
+    s = Scheduler(executor, SchedulerConfig(max_seqs=4, max_ctx=2048, prefix_cache=False), sampler=HostSampler())
+    sub = s.submit(EngineRequest(prompt, SamplingParams(max_tokens=24, ignore_eos=True, temperature=1.0, top_k=40, seed=7)))
+    s.run_until_idle()
+    toks = _collect(sub)[0]
+    assert len(toks) == 24
+    c = s.counters
+    assert c["sampled_steps"] > 0 and c["sampled_steps_device_agrees"] >= c["sampled_steps"] - 1
