@@ -208,3 +208,36 @@ def test_rank_seams_merge_to_the_seam_of_the_whole_vocabulary():
     want = np.argsort(-full, axis=1)[:, :8]
     assert (i == want).all() and np.allclose(v, np.take_along_axis(full, want, 1))
     assert np.allclose(l, np.log(np.exp(full).sum(1)), atol=1e-5)
+
+
+def test_index_blob_carries_positions_successors_and_sampling_rows():
+    """fill_blob on the CPU (a plain tensor stands in for the pinned blob): three-axis positions,
+    next-token table, and the per-head-row sampling tables of decode and prefill buckets."""
+    from types import SimpleNamespace
+
+    import numpy as np
+    import torch
+
+    from saber_engine_b200.models.hybrid import BlobLayout, SeqStep, fill_blob
+    lay = BlobLayout.make(M=16, nseq=2, max_blocks=4)
+    dec = SimpleNamespace(layout=lay, blob_host=torch.zeros(lay.words, dtype=torch.int32), kind="decode")
+    seqs = [SeqStep([5, 6, 7, 8], 40, 1, 0, [1, 2, 3], rope_delta=-3, sampling=(0.8, 20.0, 0.9, 0.0), uniforms=[0.1, 0.2, 0.3, 0.4]),
+            SeqStep([9, 10, 11, 12], 7, 2, 2, [4])]
+    fill_blob(dec, seqs, 16)
+    a = dec.blob_host.numpy()
+    f = a.view(np.float32)
+    assert a[lay.pos: lay.pos + 4].tolist() == [37, 38, 39, 40] and a[lay.pos + 4: lay.pos + 8].tolist() == [7, 8, 9, 10]
+    assert a[lay.next_ids: lay.next_ids + 8].tolist() == [6, 7, 8, -1, 10, 11, 12, -1]
+    assert np.allclose(f[lay.samp: lay.samp + 4], [0.8, 20.0, 0.9, 0.0]) and np.allclose(f[lay.samp + 12: lay.samp + 16], [0.8, 20.0, 0.9, 0.0])
+    assert np.allclose(f[lay.samp_u: lay.samp_u + 4], [0.1, 0.2, 0.3, 0.4])
+    assert f[lay.samp + 16] == 0.0                         # the greedy sequence's rows keep temperature 0
+    assert a[lay.slot_map + 1] == 3 * 16 + (41 % 16)       # KV slots follow the index, not the rotary position
+    pre = SimpleNamespace(layout=lay, blob_host=torch.zeros(lay.words, dtype=torch.int32), kind="prefill")
+    pos3 = [[0, 1, 2, 2, 2], [0, 1, 2, 2, 3], [0, 1, 2, 3, 2]]
+    fill_blob(pre, [SeqStep([1, 2, 3, 4, 5], 0, 1, 0, [1], rope_pos=pos3, next_token=77),
+                    SeqStep([6, 7], 0, 2, 0, [2], sampling=(1.0, 0.0, 1.0, 0.0), uniforms=[0.5])], 16)
+    a = pre.blob_host.numpy()
+    f = a.view(np.float32)
+    assert a[lay.pos + 16: lay.pos + 21].tolist() == [0, 1, 2, 2, 3] and a[lay.pos + 32 + 3] == 3
+    assert a[lay.next_ids: lay.next_ids + 7].tolist() == [2, 3, 4, 5, 77, 7, -1]
+    assert f[lay.samp] == 0.0 and np.allclose(f[lay.samp + 4: lay.samp + 8], [1.0, 0.0, 1.0, 0.0]) and f[lay.samp_u + 1] == 0.5
