@@ -52,7 +52,8 @@ struct GemmI8Params {
   // split-K reduction mode. Callers leave 0 (the launcher turns the cooperative form on when the
   // whole grid is resident) or set -1 to force the last-arriver form.
   int coop;
-  // token tiles per CTA, chosen by the launcher (callers leave 0): 2 for long row runs (prefill) of
+  // token tiles per CTA, chosen by the launcher (callers leave 0; 2 asks for pairs whenever the shape
+  // allows, -1 forbids them): 2 for long row runs (prefill) of
   // 4-bit weights -- one widened weight block then feeds two 128-row MMAs with their own TMEM
   // accumulators, which halves the widening work per output.
   int mtiles;

@@ -129,7 +129,7 @@ def pick_splits(n_tiles: int, m_tiles: int, kb: int, sms: int = 148) -> int:
 
 
 def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,
-                splits: Optional[int] = None, nt: Optional[int] = None, coop: int = 0) -> N.GemmI8Params:
+                splits: Optional[int] = None, nt: Optional[int] = None, coop: int = 0, mtiles: int = 0) -> N.GemmI8Params:
     assert a.K == w.K, (a.K, w.K)
     nt = nt or L.token_tile(a.M)
     assert a.M_pad % nt == 0
@@ -145,17 +145,18 @@ def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,
     assert bool(getattr(w, 'mx', False)) == bool(a.fp8), "MXFP4 weights take fp8 activations, integer weights int8"
     p.nt, p.splits, p.w4, p.ldo = nt, splits, w.fmt_code, out.stride(0)
     p.coop = coop
+    p.mtiles = mtiles      # 0: the launcher decides; 2: pair token tiles whenever the shape allows; -1: never
     assert out.stride(0) % 8 == 0, "GEMM output rows must be 16-byte aligned"
     return p
 
 
 def gemm_i8(w: QuantWeight, a: QuantAct, out: Optional[torch.Tensor] = None,
-            splits: Optional[int] = None, stages: int = 0, nt: Optional[int] = None, coop: int = 0) -> torch.Tensor:
+            splits: Optional[int] = None, stages: int = 0, nt: Optional[int] = None, coop: int = 0, mtiles: int = 0) -> torch.Tensor:
     """out[M, N] = bf16(int32 accumulate * a_scale[m] * w_scale[n])."""
     dev = a.q.device
     if out is None:
         out = torch.empty(a.M, w.N, dtype=torch.bfloat16, device=dev)
-    p = gemm_params(w, a, out, scratch(dev), splits, nt, coop)
+    p = gemm_params(w, a, out, scratch(dev), splits, nt, coop, mtiles)
     N.check(N.lib().saber_gemm_i8_launch(C.byref(p), stages, N.stream_handle()), "gemm_i8")
     return out
 

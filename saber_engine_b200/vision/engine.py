@@ -75,12 +75,19 @@ class VisionFrontend:
         self.proc = proc.clamped_to_arena(cap_patches)
         self._encode = encode or self._encode_tower
         self._tower_lock = threading.Lock()      # the tower's buffers serve one forward at a time
+        self._stream = None
         self.counters = {"images": 0, "patch_rows": 0, "image_tokens": 0, "refused": 0}
 
     def _encode_tower(self, pixel_values: torch.Tensor, grids, out_rows: torch.Tensor) -> None:
-        stream = self.ex.model.stream                # ordered before the prefill programs that read the rows
-        with torch.cuda.stream(stream):
+        # A stream of its own: the engine's step loop (another thread) may be capturing a new bucket
+        # on the model's stream at this very moment, and nothing else may touch a capturing stream.
+        # The rows are complete on the host's clock before the request is submitted, so the prefill
+        # that reads them needs no device-side dependency.
+        if self._stream is None:
+            self._stream = torch.cuda.Stream(device=self.table.device)
+        with torch.cuda.stream(self._stream):
             self.tower.forward(pixel_values, grids, out=out_rows, graph=True)
+        self._stream.synchronize()
 
     def build_request(self, token_ids: Sequence[int], images: Sequence[np.ndarray],
                       params: Optional[SamplingParams] = None, **kw) -> EngineRequest:

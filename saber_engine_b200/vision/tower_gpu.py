@@ -93,6 +93,7 @@ class VisionTowerGPU:
         p.out, p.ws, p.counters, p.err = out.data_ptr(), sc.ws.data_ptr(), sc.counters.data_ptr(), sc.err.data_ptr()
         p.M, p.M_pad, p.N, p.N_pad, p.K = M, m_pad, lin.N, lin.N_pad, (k_pad or lin.K_pad) * 2
         p.nt, p.splits, p.w4, p.ldo = L.token_tile(M), 1, 3, out.stride(0)
+        p.mtiles = getattr(self, "force_pairs", 0)     # tests set 2 to run the paired-tile path on small shapes
         p.bias, p.epi, p.res = lin.bias.data_ptr(), epi, (res.data_ptr() if res is not None else None)
         assert out.stride(0) % 8 == 0 and (res is None or res.stride(0) == out.stride(0))
         N.check(N.lib().saber_gemm_i8_launch(C.byref(p), 0, N.stream_handle()), "vision gemm")

@@ -9,7 +9,7 @@ from saber_engine_b200.ops import reference as R
 pytestmark = pytest.mark.gpu
 
 
-def _case(M, N, K, bits, splits=None, seed=0, coop=0):
+def _case(M, N, K, bits, splits=None, seed=0, coop=0, mtiles=0):
     g = torch.Generator().manual_seed(seed)
     w = torch.randn(N, K, generator=g) * 0.02
     x = torch.randn(M, K, generator=g)
@@ -20,7 +20,7 @@ def _case(M, N, K, bits, splits=None, seed=0, coop=0):
     qw = F.QuantWeight.from_int(wq, ws, bits, dev)
     m_pad = L.padded_rows(M)
     qa = F.QuantAct(L.tile_act_int8(aq, m_pad).to(dev), torch.cat([asc, torch.zeros(m_pad - M)]).to(dev), M, K)
-    out = F.gemm_i8(qw, qa, splits=splits, coop=coop)
+    out = F.gemm_i8(qw, qa, splits=splits, coop=coop, mtiles=mtiles)
     torch.cuda.synchronize()
     F.scratch(dev).check()
     got = out.float().cpu()
@@ -66,7 +66,9 @@ def test_gemm_prefill_tiles():
 
 def test_gemm_two_token_tiles_per_cta():
     """Long row runs of 4-bit weights: one widened weight block feeds two 128-row MMAs."""
-    _case(512, 512, 1024, 4, splits=1, seed=11)        # two pairs, whole
-    _case(400, 300 + 4, 2048, 4, splits=1, seed=12)    # last pair: second tile ragged (16 live rows), ragged N
-    _case(700, 256, 512, 4, splits=1, seed=13)         # M_pad = 768: three pairs, the last one half empty
-    _case(512, 512, 1024, 8, splits=1, seed=14)        # int8 weights keep one tile per CTA
+    # (the launcher pairs tiles by itself only when one tile per CTA needs more than a wave: forced here)
+    _case(512, 512, 1024, 4, splits=1, seed=11, mtiles=2)        # two pairs, whole
+    _case(400, 300 + 4, 2048, 4, splits=1, seed=12, mtiles=2)    # last pair: second tile ragged (16 live rows), ragged N
+    _case(700, 256, 512, 4, splits=1, seed=13, mtiles=2)         # M_pad = 768: three pairs, the last one half empty
+    _case(512, 512, 1024, 8, splits=1, seed=14, mtiles=2)        # int8 weights keep one tile per CTA
+    _case(2048, 40960, 256, 4, splits=1, seed=15)                # 160 x 16 single-tile CTAs: the launcher pairs by itself

@@ -42,7 +42,7 @@ def test_gemm_push_then_reduce_norm_quant(nranks, M, splits):
             m_pad = L.padded_rows(M)
             qa = F.QuantAct(L.tile_act_int8(aq, m_pad).to(DEV), torch.cat([asc, torch.zeros(m_pad - M)]).to(DEV), M, Kr)
             dummy = torch.zeros(M, H, dtype=torch.bfloat16, device=DEV)
-            p = F.gemm_params(qw, qa, dummy, sc, splits=splits)
+            p = F.gemm_params(qw, qa, dummy, sc, splits=splits, mtiles=2 if M > 128 else 0)
             g.gemm_tp(p, site)
             parts = N.lib().saber_gemm_i8_parts(C.byref(p))
             N.check(N.lib().saber_gemm_i8_launch(C.byref(p), 0, N.stream_handle()), "gemm")
@@ -118,7 +118,7 @@ def test_sequence_parallel_reduce_scatter_norm_allgather_gemm(nranks, M):
         m_pad = L.padded_rows(M)
         qa = F.QuantAct(L.tile_act_int8(aq, m_pad).to(DEV), torch.cat([asc, torch.zeros(m_pad - M)]).to(DEV), M, Kr)
         dummy = torch.zeros(M, H, dtype=torch.bfloat16, device=DEV)
-        p = F.gemm_params(qw, qa, dummy, sc, splits=1)
+        p = F.gemm_params(qw, qa, dummy, sc, splits=1, mtiles=2)     # owner-only push from paired token tiles
         g.gemm_rs(p, 0, rpr)
         N.check(N.lib().saber_gemm_i8_launch(C.byref(p), 0, N.stream_handle()), "gemm rs")
         keep.append((qw, qa, dummy))

@@ -26,6 +26,7 @@ def test_bf16_gemm_mode_bias_activation_residual(M, N, K, epi):
     lin = _Lin(w, b, dev)
     tw = VisionTowerGPU.__new__(VisionTowerGPU)                  # only the launch helpers are used
     tw.cfg, tw.dev, tw.launches = VisionConfig.tiny(), dev, 0
+    tw.force_pairs = 2 if M >= 512 else 0                       # the last two cases: two token tiles per CTA
     m_pad = L.padded_rows(M)
     tw.a_buf = torch.zeros(lin.K_pad * 2 * m_pad, dtype=torch.uint8, device=dev)
     tw._rows(x.to(dev), M, K, lin.K_pad, m_pad)
