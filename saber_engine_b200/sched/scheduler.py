@@ -89,6 +89,9 @@ class Scheduler:
         self.running: list = []
         self._ids = itertools.count(1)
         self._lock = threading.Lock()
+        # device work from outside the step loop (parking from a server thread) must not meet a step in
+        # flight on the executor's stream (a bucket may be under capture there): both take this lock
+        self._device_lock = threading.Lock()
         self._wake = threading.Condition(self._lock)
         self._stop = False
         self._thread: Optional[threading.Thread] = None
@@ -233,7 +236,7 @@ class Scheduler:
         if plan is None:
             return False
         try:
-          with self.trace.phase("Launch"):
+          with self.trace.phase("Launch"), self._device_lock:
                 if plan[0] == "prefill":
                     runs = [SeqRun(s.seq_id, s.prompt[pos:pos + n], pos, s.slot, 0, s.blocks, uid=s.seq_id,
                                    last_chunk=(pos + n == len(s.prompt)),
@@ -276,7 +279,7 @@ class Scheduler:
     def park(self, seq_id: int) -> str:
         """Moves a decoding sequence off the device: its KV pages and state slot become one verified
         image in the park tier, its blocks and slot are released.  Returns the key to restore with."""
-        with self._lock:
+        with self._device_lock, self._lock:
             s = next((x for x in self.running if x.seq_id == seq_id), None)
             if s is None or s.prefilling or s.finished:
                 raise EngineRefused(f"sequence {seq_id} is not a decoding sequence", 409)
@@ -293,7 +296,7 @@ class Scheduler:
 
     def restore(self, key: str) -> int:
         """Brings a parked sequence back (fresh blocks and slot, bytes verified first)."""
-        with self._lock:
+        with self._device_lock, self._lock:
             s = self.parked.get(key)
             if s is None:
                 raise EngineRefused(f"no parked session {key!r}", 404)
