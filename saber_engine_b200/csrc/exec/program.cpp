@@ -33,7 +33,7 @@ extern "C" int saber_digest_clear_launch(unsigned long long* out, int n, cudaStr
 
 namespace {
 
-struct OpGemm { saber::GemmI8Params p; int stages; };
+struct OpGemm { saber::GemmI8Params p; int stages; saber::RowOpParams tail; bool has_tail; };
 struct OpRow { int mode; saber::RowOpParams p; };
 struct OpEmbed { const void* table; const int32_t* ids; void* out; int M, H, vocab_lo, vocab_n, ldout; };
 struct OpExpand { const void* ctx; const void* tok; const void* pos; void* out; int nseq, block, H; };
@@ -80,7 +80,12 @@ int launch(const Op& op, cudaStream_t s) {
   return std::visit(
       [&](auto&& o) -> int {
         using T = std::decay_t<decltype(o)>;
-        if constexpr (std::is_same_v<T, OpGemm>) return saber_gemm_i8_launch(&o.p, o.stages, s);
+        if constexpr (std::is_same_v<T, OpGemm>) {
+          if (!o.has_tail) return saber_gemm_i8_launch(&o.p, o.stages, s);
+          saber::GemmI8Params q = o.p;      // the row tail's block lives in this op: point at it now
+          q.tail_row = &o.tail;             // (the op list may have moved since the op was added)
+          return saber_gemm_i8_launch(&q, o.stages, s);
+        }
         else if constexpr (std::is_same_v<T, OpRow>) return saber_row_producer_launch(o.mode, &o.p, s);
         else if constexpr (std::is_same_v<T, OpEmbed>)
           return saber_embed_gather_launch(o.table, o.ids, o.out, o.M, o.H, o.vocab_lo, o.vocab_n, o.ldout, s);
@@ -138,7 +143,43 @@ void saber_program_destroy(void* h) {
 }
 
 int saber_program_add_gemm(void* h, const saber::GemmI8Params* p, int stages, const char* tag) {
-  return add(h, OpGemm{*p, stages}, 1, tag);
+  OpGemm op{*p, stages, saber::RowOpParams{}, false};
+  if (p->tail_mode == 2 && p->tail_row != nullptr) {
+    op.tail = *p->tail_row;
+    op.has_tail = true;
+    op.p.tail_row = nullptr;
+  }
+  return add(h, std::move(op), 1, tag);
+}
+
+// Chains the GEMMs of the program for L2 prefetch: every (non-grouped) GEMM learns where the next
+// one's weight tiles start and how its grid walks them, so that its CTAs can ask L2 for the leading
+// k-blocks of every CTA of that next launch once their own copies are all issued.  Call once, after
+// the last op was added and before the program is run or captured.  Returns the number of links.
+int saber_program_link_prefetch(void* h, int pref_bytes) {
+  auto* pr = static_cast<Program*>(h);
+  OpGemm* prev = nullptr;
+  int links = 0;
+  for (auto& e : pr->ops) {
+    auto* g = std::get_if<OpGemm>(&e.op);
+    if (!g) continue;
+    if (g->p.group_tiles != nullptr) { prev = nullptr; continue; }   // expert tiles are only known on the device
+    if (prev != nullptr) {
+      const saber::GemmI8Params& n = g->p;
+      const int wbytes = n.w4 == 1 ? 16384 : (n.w4 == 2 ? 17408 : 32768);
+      const int KB = n.K >> 7;
+      prev->p.next_w = n.w;
+      prev->p.next_tiles = n.N_pad / 256;
+      prev->p.next_splits = n.splits;
+      prev->p.next_KB = KB;
+      prev->p.next_kb_per = (KB + n.splits - 1) / n.splits;
+      prev->p.next_wbytes = wbytes;
+      prev->p.next_pref = pref_bytes / wbytes > 0 ? pref_bytes / wbytes : 1;
+      ++links;
+    }
+    prev = g;
+  }
+  return links;
 }
 int saber_program_add_row(void* h, int mode, const saber::RowOpParams* p, const char* tag) {
   return add(h, OpRow{mode, *p}, 1, tag);

@@ -43,6 +43,7 @@
 #include "launch.cuh"
 #include "gemm_i8_noalloc.h"
 #include "ptx_sm100.cuh"
+#include "rowops_body.cuh"
 #include <cuda_bf16.h>
 #include <type_traits>
 
@@ -51,6 +52,7 @@ namespace saber {
 constexpr int kMaxStages = 12;
 constexpr int kGemmThreads = 320;
 constexpr uint32_t kTileBytes = 32768;   // int8 image of one weight tile (256 x 128)
+constexpr int kTailFlagsAt = 64 + 256 * 32;   // word offset of the per-tile "accumulator block is clean" flags in tail_sync
 constexpr int kUBufs = 3;                // W4: widened int8 operand buffers (transform, MMA and
                                          // the buffer-free round trip overlap with three)
 
@@ -61,6 +63,30 @@ __device__ __forceinline__ float gelu_f(float x, bool erf_form) {
   return 0.5f * x * (1.f + tanhf(u));
 }
 
+// Grid-wide barrier for grids that are resident as a whole (one CTA per SM, grid <= SM count).  ONE
+// thread per CTA calls, after a CTA-level barrier that ordered the other threads' writes before it.
+// `ctr` is zero when the kernel starts.  The wait is bounded like every other wait here: when it
+// runs out the status word is set and the caller goes on (its results are then garbage, the error
+// is what the host reads).  grid_depart is the second round of arrivals: it returns true in the
+// ONE caller that leaves last, which must put the counter back to zero.
+__device__ __forceinline__ bool grid_arrive_wait(uint32_t* ctr, uint32_t n_ctas, uint32_t* err) {
+  __threadfence();
+  atomicAdd(ctr, 1u);
+  const long long t0 = clock64();
+  for (uint32_t polls = 0;; ++polls) {
+    uint32_t seen;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(ctr) : "memory");
+    if (seen >= n_ctas) return true;
+    if ((polls & 1023u) == 1023u && clock64() - t0 > kWaitLimitCycles) {
+      if (err) atomicCAS(err, 0u, static_cast<uint32_t>(kErrWaitSplit));
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ bool grid_depart(uint32_t* ctr, uint32_t n_ctas) {
+  return atomicAdd(ctr, 1u) == 2u * n_ctas - 1u;
+}
+
 // kLean: the grouped (mixture-of-experts) instantiation -- no split-K and no tensor-parallel code,
 // two operand buffers instead of three, at most 102 registers -- so that TWO CTAs share an SM: an
 // expert tile is only 16 k-blocks long, and the second CTA's main loop hides the first one's
@@ -68,7 +94,7 @@ __device__ __forceinline__ float gelu_f(float x, bool erf_form) {
 // kBf: the bf16 x bf16 instantiation (optional scales, bias, activation / residual epilogue); the
 // integer and MXFP4 instantiations compile none of it.
 template <bool kLean, bool kBf = false>
-__device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int stages) {
+__device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int stages, const RowOpParams* tail) {
   const int nub = (kLean || p.mtiles == 2) ? 2 : kUBufs;     // operand buffers in use
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bars[2 * kMaxStages + 2 * kUBufs + 1];
@@ -80,17 +106,25 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // debug stamps: CTA (0,0,0) only, or (dbg_mma == 2) 16 slots for every CTA
+#ifdef SABER_STAMPS
+  // timing stamps (instrumented build only): CTA (0,0,0), or (dbg_mma == 2) 16 slots for every CTA
   const bool dbg_all = p.dbg != nullptr && p.dbg_mma == 2;
   const bool dbg_on = p.dbg != nullptr && (dbg_all || (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0));
   const size_t dbg_base = dbg_all ? 16u * ((static_cast<size_t>(blockIdx.z) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) : 0u;
 #define SABER_STAMP(i) do { if (dbg_on) p.dbg[dbg_base + (i)] = globaltimer_ns(); } while (0)
+#else
+#define SABER_STAMP(i) do { } while (0)
+#endif
   if (threadIdx.x == 0) SABER_STAMP(0);
   // Programmatic dependent launch: this kernel may be running ahead of its predecessor, so only
   // WEIGHTS (which no kernel writes) are touched before pdl_wait().  It never triggers its own
   // dependents early: CTAs of a successor placed while this grid holds the SMs would pile up on
   // the few SMs it leaves free.
-  const int tile_n = blockIdx.x;
+  // half tiles (p.halves == 2): two CTAs share a packed weight tile, each widens and multiplies only
+  // its 128 rows of it (the low or the high nibbles) -- twice the CTAs without split-K
+  const int halves = (!kLean && !kBf && p.halves == 2) ? 2 : 1;
+  const int tile_n = halves == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int half = halves == 2 ? static_cast<int>(blockIdx.x & 1u) : 0;
   const int tile_m = blockIdx.y;
   const int split = blockIdx.z;
 
@@ -115,7 +149,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
     w_base += static_cast<size_t>(t.x) * p.group_w_stride;
     w_scale_base += static_cast<size_t>(t.x) * p.N_pad;
   }
-  const int n0 = tile_n * 256;
+  const int n0 = tile_n * 256 + half * 128;
   // weight formats: 0 = int8 tiles, 1 = packed int4, 2 = MXFP4 (packed e2m1 + 1 KiB of block shifts)
   // 3 = bf16 x bf16: both operands pass through like int8 tiles (K counted in bytes), fp32 accumulators
   const bool mx = !kBf && p.w4 == 2;
@@ -216,6 +250,22 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         issued = it + 1;
         if (++s == stages) { s = 0; ph ^= 1u; }
       }
+      if (!kLean && ok && p.next_w != nullptr) {
+        // every copy of this CTA is issued: ask L2 for the leading weight tiles of the next GEMM's
+        // CTAs (weights are never written, so this is safe whatever runs in between)
+        const int g_ctas = gridDim.x * gridDim.y * gridDim.z;
+        const int me = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+        const int n_next = p.next_tiles * p.next_splits;
+        for (int j = me; j < n_next; j += g_ctas) {
+          const int tn = j / p.next_splits, sp = j - tn * p.next_splits;
+          const int kbeg = sp * p.next_kb_per;
+          const int cnt = min(p.next_pref, p.next_KB - kbeg);
+          const uint8_t* src = p.next_w + (static_cast<size_t>(tn) * p.next_KB + kbeg) * static_cast<size_t>(p.next_wbytes);
+          for (int t = 0; t < cnt; ++t)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src + static_cast<size_t>(t) * p.next_wbytes),
+                         "r"(static_cast<uint32_t>(p.next_wbytes)) : "memory");
+        }
+      }
       if (!ok) {
         // Unwinding: do not leave the CTA while one of its own copies is still in flight.
         for (int it = max(0, issued - stages); it < issued; ++it)
@@ -228,7 +278,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
       // M = 128 token rows (only the first nt are real), N = 256 output features
       const uint32_t idesc = mx ? make_idesc(kCFmtF32, kFmtE4M3, kFmtE4M3, 128, 256)
                            : bf ? make_idesc(kCFmtF32, kFmtBF16, kFmtBF16, 128, 256)
-                                : make_idesc(kCFmtS32, kFmtS8, kFmtS8, 128, 256);
+                                : make_idesc(kCFmtS32, kFmtS8, kFmtS8, 128, halves == 2 ? 128 : 256);
       const uint64_t desc_hi = make_desc_k128(0);  // everything but the start address
       uint32_t a_addr = a_smem;
       int s = 0, u = 0;
@@ -278,6 +328,21 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
       }
       if (ok) mma_commit(bar_acc);
       SABER_STAMP(6);
+    } else if (!kLean && !kBf && p.tail_mode == 3 && split == 0) {
+      // Row tail on the accumulator blocks: nobody re-zeroes a block after reading it (16-byte
+      // zero stores from one CTA per row share sectors across CTAs and are ruinously slow), so the
+      // first split of every tile cleans its block HERE, in whole lines, while the pipeline
+      // runs; the splits check the tile's "clean" flag before they add.  These 31 lanes are
+      // otherwise idle.
+      pdl_wait();                              // the previous launch may still be reading the blocks
+      const int tile_lin = tile_m * gridDim.x + tile_n;
+      int4* blk = reinterpret_cast<int4*>(p.acc + static_cast<size_t>(tile_lin) * p.nt * 256);
+      const int n16 = p.nt * 64;               // 16-byte pieces of the block
+      for (int i = lane - 1; i < n16; i += 31) __stcg(blk + i, make_int4(0, 0, 0, 0));
+      __threadfence();
+      __syncwarp(0xFFFFFFFEu);
+      if (lane == 1)
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.tail_sync + kTailFlagsAt + tile_lin), "r"(1u) : "memory");
     }
   } else {
     // ---------------------------------------------------------------- transform, then epilogue
@@ -349,6 +414,16 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + 16384u + off), "r"(ohi[0]), "r"(ohi[1]),
                          "r"(ohi[2]), "r"(ohi[3]) : "memory");
           }
+        } else if (halves == 2) {
+          const uint32_t sh = half ? 0u : 4u;      // this CTA's 128 rows: the high or the low nibbles
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t off = static_cast<uint32_t>(i * 256 + tid8) * 16u;
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + off),
+                         "r"((v[i][0] << sh) & 0xF0F0F0F0u), "r"((v[i][1] << sh) & 0xF0F0F0F0u),
+                         "r"((v[i][2] << sh) & 0xF0F0F0F0u), "r"((v[i][3] << sh) & 0xF0F0F0F0u)
+                         : "memory");
+          }
         } else
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -385,6 +460,120 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
     } else {
       ok = false;  // only the first group (TMEM lane quarters 2,3,0,1) is the epilogue
     }
+    if constexpr (!kLean && !kBf) {
+      if (p.tail_mode == 1) {
+        // silu(gate) * up and the per-token int8 quantisation inside the tile (paired weight tiles:
+        // columns c and 128 + c of the accumulator are the gate and up feature of the same index).
+        // The first group stages the bf16-rounded linear outputs in shared memory (one token row
+        // per thread, as the accumulator arrives); then ALL eight transform warps walk the rows, a
+        // warp per row and four products per lane, so the transcendental work is spread over 256
+        // threads whatever the number of live rows.  Row maxima meet in global memory (one cache
+        // line per row), ONE grid-wide barrier, and every CTA writes its 128 bytes of each row
+        // straight into the next GEMM's operand.  Rounding points are those of the separate
+        // kernels: linear output to bf16, product to bf16, absmax / 127, round-half-even.
+        const uint32_t stage_s = widen ? u_smem : w_smem;
+        const int mt = min(p.nt, p.M - m0);
+        pdl_wait();
+        if (tgroup == 0 && ok) {
+          tc_fence_after_sync();
+          const int row = q4 * 32 + lane;
+          if (q4 * 32 < mt) {
+            const bool live = row < mt;
+            const float asc = live ? p.a_scale[m0 + row] : 0.f;
+            const uint32_t t_lane = tmem_d + (static_cast<uint32_t>(q4 * 32) << 16);
+            for (int c = 0; c < 256; c += 32) {
+              uint32_t r[32];
+              tmem_ld32(t_lane + c, r);
+              tmem_ld_wait();
+              if (live) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const float lo = static_cast<float>(static_cast<int32_t>(r[2 * j])) * (asc * w_scale_s[c + 2 * j]);
+                  const float hi = static_cast<float>(static_cast<int32_t>(r[2 * j + 1])) * (asc * w_scale_s[c + 2 * j + 1]);
+                  const __nv_bfloat162 b2 = __floats2bfloat162_rn(lo, hi);
+                  pk[j] = *reinterpret_cast<const uint32_t*>(&b2);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint32_t chunk = static_cast<uint32_t>((c >> 3) + j) ^ (static_cast<uint32_t>(row) & 31u);
+                  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(stage_s + row * 512 + (chunk << 4)),
+                               "r"(pk[4 * j]), "r"(pk[4 * j + 1]), "r"(pk[4 * j + 2]), "r"(pk[4 * j + 3]) : "memory");
+                }
+              }
+            }
+          }
+        }
+        named_bar_sync(2, 256);
+        const bool go = abort_s == 0u;
+        const int w8 = warp - 2;                       // 0..7
+        constexpr int kRowsPerWarp = 16;               // nt <= 128
+        uint32_t act[kRowsPerWarp][2];                 // four products per row as bf16 pairs
+        uint32_t* rowmax = p.tail_sync + 64;           // one 128-byte line per row
+        if (go) {
+#pragma unroll
+          for (int i = 0; i < kRowsPerWarp; ++i) {
+            const int rw = w8 + 8 * i;
+            if (rw >= mt) break;
+            // lane l: products 4l .. 4l+3 = gate columns 4l.. and up columns 128 + 4l..
+            const uint32_t cg = (static_cast<uint32_t>(lane) >> 1) ^ (static_cast<uint32_t>(rw) & 31u);
+            const uint32_t cu = (16u + (static_cast<uint32_t>(lane) >> 1)) ^ (static_cast<uint32_t>(rw) & 31u);
+            const uint32_t sub = (static_cast<uint32_t>(lane) & 1u) << 3;
+            uint32_t g0, g1, u0, u1;
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(g0), "=r"(g1) : "r"(stage_s + rw * 512 + (cg << 4) + sub));
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(u0), "=r"(u1) : "r"(stage_s + rw * 512 + (cu << 4) + sub));
+            const float2 ga = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g0));
+            const float2 gb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g1));
+            const float2 ua = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u0));
+            const float2 ub = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u1));
+            const __nv_bfloat162 x0 = __floats2bfloat162_rn(silu_f(ga.x) * ua.x, silu_f(ga.y) * ua.y);
+            const __nv_bfloat162 x1 = __floats2bfloat162_rn(silu_f(gb.x) * ub.x, silu_f(gb.y) * ub.y);
+            const float2 y0 = __bfloat1622float2(x0), y1 = __bfloat1622float2(x1);
+            float amax = fmaxf(fmaxf(fabsf(y0.x), fabsf(y0.y)), fmaxf(fabsf(y1.x), fabsf(y1.y)));
+            amax = warp_max(amax);
+            if (lane == 0) atomicMax(rowmax + static_cast<size_t>(m0 + rw) * 32, __float_as_uint(amax));   // non-negative floats order like their bits
+            act[i][0] = *reinterpret_cast<const uint32_t*>(&x0);
+            act[i][1] = *reinterpret_cast<const uint32_t*>(&x1);
+          }
+        }
+        named_bar_sync(2, 256);
+        if (tid8 == 0) SABER_STAMP(10);
+        const uint32_t n_ctas = gridDim.x * gridDim.y * gridDim.z;
+        if (tid8 == 0) grid_arrive_wait(p.tail_sync, n_ctas, p.err);
+        named_bar_sync(2, 256);
+        if (tid8 == 0) SABER_STAMP(13);
+        const int rows_pad = min(p.nt, p.tail_M_pad - m0);     // live rows, then padding rows (zeros)
+#pragma unroll
+        for (int i = 0; i < kRowsPerWarp; ++i) {
+          const int rw = w8 + 8 * i;
+          if (rw >= rows_pad) break;
+          const int mm = m0 + rw;
+          const bool lv = go && rw < mt;
+          const float am = lv ? __uint_as_float(__ldcg(rowmax + static_cast<size_t>(mm) * 32)) : 0.f;
+          const float inv = am > 0.f ? 127.f / am : 0.f;
+          uint32_t word = 0u;
+          if (lv) {
+            const float2 y0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&act[i][0]));
+            const float2 y1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&act[i][1]));
+            word = quant4(y0.x, y0.y, y1.x, y1.y, inv, 0);
+          }
+          int8_t* dst = p.tail_q + (static_cast<size_t>(tile_n) * p.tail_M_pad + mm) * 128;
+          *reinterpret_cast<uint32_t*>(dst + ((((lane >> 2) ^ (mm & 7)) & 7) << 4) + ((lane & 3) << 2)) = word;
+          if (tile_n == 0 && lane == 0) p.tail_scale[mm] = am / 127.f;
+        }
+        // second round of arrivals, off the critical path: the CTA that leaves last re-arms the words
+        named_bar_sync(2, 256);
+        if (tid8 == 0) is_last_s = grid_depart(p.tail_sync, n_ctas) ? 1u : 0u;
+        named_bar_sync(2, 256);
+        if (is_last_s) {
+          for (int i = tid8; i < p.tail_M_pad; i += 256) rowmax[static_cast<size_t>(i) * 32] = 0u;
+          __threadfence();
+          named_bar_sync(2, 256);
+          if (tid8 == 0) p.tail_sync[0] = 0u;
+        }
+        ok = false;        // the generic epilogue below is not for this launch
+      }
+    }
     if (ok) {
       tc_fence_after_sync();
       pdl_wait();   // already satisfied (the token tiles have landed); orders this thread's reads and writes
@@ -395,7 +584,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
       const bool live = row < mt;
       const bool warp_live = q4 * 32 < mt;  // warp-uniform: this lane quarter holds live rows
       const uint32_t t_lane = tmem_d + (static_cast<uint32_t>(q4 * 32) << 16);
-      const int ncols = min(256, p.N_pad - n0);
+      const int ncols = halves == 2 ? 128 : min(256, p.N_pad - n0);
       // accumulator words are int32 (integer formats) or fp32 bits (MXFP4)
       auto acc_f = [&](uint32_t raw) -> float {
         return (mx || bf) ? __uint_as_float(raw) : static_cast<float>(static_cast<int32_t>(raw));
@@ -522,8 +711,59 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         // (32 consecutive rows) store -- and later load -- 512 contiguous bytes
         const int tile_lin = tile_m * gridDim.x + tile_n;
         const size_t blk_stride = 128u * 256u;   // ints per (split, tile) block
+        // Integer partial sums can be added in any order, so the splits of a tile do not keep private
+        // copies: each stages its live rows in shared memory and hands them to ONE asynchronous bulk
+        // reduction (TMA add.s32) into the tile's accumulator block in L2 -- zero when the kernel
+        // starts, re-zeroed by whoever reads it out.  The block is [c4][nt rows][4 ints].  MXFP4
+        // partials are fp32 and keep the private copies (their sum must not depend on the arrival order).
+        const bool bulk = !mx && !bf && p.acc != nullptr;
+        const int rstride = bulk ? p.nt : 128;   // rows per four-column group of a block
         int32_t* wblk = p.ws + (static_cast<size_t>(split) * (gridDim.x * gridDim.y) + tile_lin) * blk_stride;
-        if (warp_live) {
+        int32_t* ablk = bulk ? p.acc + static_cast<size_t>(tile_lin) * p.nt * 256u : nullptr;
+        if (bulk) {
+          const uint32_t stage_s = widen ? u_smem : w_smem;     // idle by now, at least 128 KiB in a row
+          if (q4 * 32 < p.nt) {
+            for (int c = 0; c < 256; c += 32) {
+              uint32_t r[32];
+              tmem_ld32(t_lane + c, r);
+              tmem_ld_wait();
+              if (row < p.nt) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const uint32_t a = stage_s + (static_cast<uint32_t>((c >> 2) + j) * p.nt + row) * 16u;
+                  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(live ? r[4 * j] : 0u),
+                               "r"(live ? r[4 * j + 1] : 0u), "r"(live ? r[4 * j + 2] : 0u), "r"(live ? r[4 * j + 3] : 0u)
+                               : "memory");
+                }
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (tid_t == 0) {
+            if (p.tail_mode == 3) {            // the block must have been cleaned by this launch's first split
+              const uint32_t* flag = p.tail_sync + kTailFlagsAt + tile_lin;
+              const long long t0 = clock64();
+              for (uint32_t polls = 0;; ++polls) {
+                uint32_t v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+                if (v != 0u) break;
+                if ((polls & 1023u) == 1023u && clock64() - t0 > kWaitLimitCycles) {
+                  atomicCAS(p.err, 0u, static_cast<uint32_t>(kErrWaitSplit));
+                  break;
+                }
+              }
+            }
+            const uint32_t total = static_cast<uint32_t>(p.nt) * 1024u;
+            for (uint32_t off = 0; off < total; off += 16384u)
+              asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.s32 [%0], [%1], %2;" ::"l"(
+                               reinterpret_cast<uint8_t*>(ablk) + off), "r"(stage_s + off), "r"(min(16384u, total - off))
+                           : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+          }
+        } else if (warp_live) {
           for (int c = 0; c < ncols; c += 32) {
             uint32_t r[32];
             tmem_ld32(t_lane + c, r);
@@ -539,6 +779,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         __threadfence();
         named_bar_sync(1, 128);
         if (tid_t == 0) SABER_STAMP(10);
+        if (!(bulk && p.tail_mode == 3)) {     // (tail mode 3: the row tail reads the accumulator blocks itself)
         const int tile_id = tile_lin;
         // Two ways to add the splits.  Cooperative (every CTA of the grid is resident, the launcher
         // guarantees it): all splits of a tile wait for one another and each reduces the rows
@@ -582,7 +823,8 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
           const int rows_part = mt > part ? (mt - part + nparts - 1) / nparts : 0;
           const int n_items = tp ? rows_part * n_c4 : c4_part * mt;
           const size_t tiles_all = static_cast<size_t>(gridDim.x) * gridDim.y;
-          const int32_t* rblk = p.ws + static_cast<size_t>(tile_lin) * blk_stride;
+          int32_t* rblk = bulk ? ablk : p.ws + static_cast<size_t>(tile_lin) * blk_stride;
+          const int nsp = bulk ? 1 : p.splits;     // blocks to add per item
           auto reduce_items = [&](auto ilp_c, auto maxs_c) {
           constexpr int kIlp = decltype(ilp_c)::value;
           constexpr int kMaxS = decltype(maxs_c)::value;
@@ -603,19 +845,21 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
               }
 #pragma unroll
               for (int sp = 0; sp < kMaxS; ++sp)
-                if (sp < p.splits)
+                if (sp < nsp)
                   y[u][sp] = __ldcg(reinterpret_cast<const int4*>(
-                      rblk + static_cast<size_t>(sp) * tiles_all * blk_stride + (static_cast<size_t>(c4[u]) * 128 + rr[u]) * 4));
+                      rblk + static_cast<size_t>(sp) * tiles_all * blk_stride + (static_cast<size_t>(c4[u]) * rstride + rr[u]) * 4));
             }
 #pragma unroll
             for (int u = 0; u < kIlp; ++u) {
               if (base + u * 128 >= n_items) continue;
+              if (bulk)   // the accumulator block goes back to zero for the next launch
+                __stcg(reinterpret_cast<int4*>(rblk + (static_cast<size_t>(c4[u]) * rstride + rr[u]) * 4), make_int4(0, 0, 0, 0));
               float f[4];
               if (mx) {   // fp32 partials: added in split order, the same on every launch
                 f[0] = f[1] = f[2] = f[3] = 0.f;
 #pragma unroll
                 for (int sp = 0; sp < kMaxS; ++sp)
-                  if (sp < p.splits) {
+                  if (sp < nsp) {
                     f[0] += __int_as_float(y[u][sp].x); f[1] += __int_as_float(y[u][sp].y);
                     f[2] += __int_as_float(y[u][sp].z); f[3] += __int_as_float(y[u][sp].w);
                   }
@@ -623,7 +867,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
                 int4 x = make_int4(0, 0, 0, 0);
 #pragma unroll
                 for (int sp = 0; sp < kMaxS; ++sp)
-                  if (sp < p.splits) { x.x += y[u][sp].x; x.y += y[u][sp].y; x.z += y[u][sp].z; x.w += y[u][sp].w; }
+                  if (sp < nsp) { x.x += y[u][sp].x; x.y += y[u][sp].y; x.z += y[u][sp].z; x.w += y[u][sp].w; }
                 f[0] = static_cast<float>(x.x); f[1] = static_cast<float>(x.y);
                 f[2] = static_cast<float>(x.z); f[3] = static_cast<float>(x.w);
               }
@@ -655,7 +899,8 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
           }
           };
           // the budget is ~16 loads in flight per thread: more items per round when there are few splits
-          if (p.splits <= 2) reduce_items(std::integral_constant<int, 8>{}, std::integral_constant<int, 2>{});
+          if (bulk) reduce_items(std::integral_constant<int, 8>{}, std::integral_constant<int, 1>{});
+          else if (p.splits <= 2) reduce_items(std::integral_constant<int, 8>{}, std::integral_constant<int, 2>{});
           else if (p.splits <= 4) reduce_items(std::integral_constant<int, 4>{}, std::integral_constant<int, 4>{});
           else reduce_items(std::integral_constant<int, 2>{}, std::integral_constant<int, 8>{});
           if (!p.coop) {
@@ -674,6 +919,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
             if (old == static_cast<uint32_t>(2 * p.splits - 1)) p.counters[tile_id] = 0u;
           }
         }
+        }
       }
     }
   }
@@ -683,19 +929,96 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_d, kTmemCols);
   if (threadIdx.x == 32) SABER_STAMP(9);
+  if constexpr (!kLean && !kBf) {
+    if ((p.tail_mode == 2 || p.tail_mode == 3) && tail != nullptr) {
+      // Row tail.  Every CTA arrives here whatever happened above (an aborted pipeline has set the
+      // status word; the barrier still completes), then the rows are dealt round-robin to the CTAs.
+      const uint32_t n_ctas = gridDim.x * gridDim.y * gridDim.z;
+      const uint32_t me = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+      {
+        // while the barrier forms: pull what the first row of this CTA reads besides the GEMM's
+        // output (its residual row, the norm weights) into L1 -- neither is written by this launch
+        const int rows0 = tail->q ? tail->M_pad : tail->M;
+        if (static_cast<int>(me) < rows0 && static_cast<int>(me) < tail->M) {
+          for (int ch = threadIdx.x; ch < (tail->K >> 4); ch += kGemmThreads) {
+            if (tail->res) {
+              const __nv_bfloat16* r = tail->res + static_cast<size_t>(me) * tail->ldres + (ch << 4);
+              asm volatile("prefetch.global.L1 [%0];" ::"l"(r));
+            }
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(tail->w + (ch << 4)));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(tail->w + (ch << 4) + 8));
+            if (p.tail_mode == 3) {
+              asm volatile("prefetch.global.L1 [%0];" ::"l"(tail->acc_w_scale + (ch << 4)));
+              asm volatile("prefetch.global.L1 [%0];" ::"l"(tail->acc_w_scale + (ch << 4) + 8));
+            }
+          }
+        }
+      }
+      if (threadIdx.x == 0) grid_arrive_wait(p.tail_sync, n_ctas, p.err);
+      __syncthreads();
+      if (threadIdx.x == 0) SABER_STAMP(13);
+      if (p.tail_mode == 3 && me == n_ctas - 1)      // every split has added: the "clean" flags go down for the next launch
+        for (int i = threadIdx.x; i < static_cast<int>(gridDim.x * gridDim.y); i += kGemmThreads) p.tail_sync[kTailFlagsAt + i] = 0u;
+      float* red = w_scale_s;     // the per-feature scales are no longer needed
+      const int rows = tail->q ? tail->M_pad : tail->M;
+      for (int r = static_cast<int>(me); r < rows; r += static_cast<int>(n_ctas)) {
+        if (p.tail_mode == 3) {
+          if (tail->K <= 16 * kGemmThreads) row_reg_body<kRowAddRms, 1, true, true>(*tail, r, red);
+          else row_reg_body<kRowAddRms, 2, true, true>(*tail, r, red);
+        } else {
+          if (tail->K <= 16 * kGemmThreads) row_reg_body<kRowAddRms, 1, true>(*tail, r, red);
+          else row_reg_body<kRowAddRms, 2, true>(*tail, r, red);
+        }
+      }
+      if (threadIdx.x == 0) SABER_STAMP(14);
+      if (threadIdx.x == 0 && grid_depart(p.tail_sync, n_ctas)) p.tail_sync[0] = 0u;
+    }
+  }
 #undef SABER_STAMP
 }
 
 __global__ void __launch_bounds__(kGemmThreads) gemm_i8_kernel(const GemmI8Params p, const int stages) {
-  gemm_i8_body<false>(p, stages);
+  gemm_i8_body<false>(p, stages, nullptr);
+}
+// the same body with a row tail: the row producer's parameter block rides as a second argument
+__global__ void __launch_bounds__(kGemmThreads) gemm_i8_tail_kernel(const GemmI8Params p, const int stages,
+                                                                    const __grid_constant__ RowOpParams tail) {
+  gemm_i8_body<false>(p, stages, &tail);
 }
 __global__ void __launch_bounds__(kGemmThreads) gemm_bf16_kernel(const GemmI8Params p, const int stages) {
-  gemm_i8_body<false, true>(p, stages);
+  gemm_i8_body<false, true>(p, stages, nullptr);
 }
 __global__ void __launch_bounds__(kGemmThreads, 2) gemm_i8_lean_kernel(const GemmI8Params p, const int stages) {
-  gemm_i8_body<true>(p, stages);
+  gemm_i8_body<true>(p, stages, nullptr);
 }
 
+}  // namespace saber
+
+namespace saber {
+static int g_coop_launch = 0;
+constexpr int kMaxDevices = 64;
+// Per-device set-up (function attributes are per device): returns 0 and the SM count of the current device.
+static int device_setup(int* sm_count) {
+  static int sms[kMaxDevices];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
+  if (sms[dev] == 0) {
+    const int kSmemLimit = 224 * 1024;
+    cudaFuncSetAttribute(gemm_i8_lean_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
+    cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    cudaFuncSetAttribute(gemm_i8_tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    e = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    int n = 0;
+    e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    sms[dev] = n;
+  }
+  *sm_count = sms[dev];
+  return 0;
+}
 }  // namespace saber
 
 // Number of flags per output tile a tensor-parallel launch of `p` raises (the consumer must wait
@@ -743,27 +1066,35 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   while (stages > 2 && saber_gemm_i8_smem_bytes_w(p->nt, stages, p->w4) > kSmemLimit) --stages;
   const int smem = saber_gemm_i8_smem_bytes_w(p->nt, stages, p->w4);
   if (smem > kSmemLimit) return static_cast<int>(cudaErrorInvalidValue);
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(gemm_i8_lean_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
-    cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
-    cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kSmemLimit);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  int sm_count = 0;
+  const int cfg_err = device_setup(&sm_count);
+  if (cfg_err != 0) return cfg_err;
   // grouped mode: every tile holds at least 16 rows of the padded expert-major row space
   const int grid_y = p->group_tiles ? p->M_pad / 16 : (p->M + p->nt - 1) / p->nt;
-  dim3 grid(p->N_pad / 256, grid_y, p->splits);
-  static int sm_count = 0;
-  if (sm_count == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-  }
+  const int halves = p->halves == 2 ? 2 : 1;
+  if (halves == 2 && (p->w4 != 1 || p->splits != 1 || p->group_tiles || p->tail_mode != 0 || p->tp_nranks > 1 ||
+                      p->ag_flags != nullptr || p->mtiles == 2))
+    return static_cast<int>(cudaErrorInvalidValue);
+  dim3 grid(p->N_pad / 256 * halves, grid_y, p->splits);
+  const bool resident = static_cast<int>(grid.x * grid.y * grid.z) <= sm_count;
   GemmI8Params q = *p;
   // one CTA per SM (shared memory): the whole grid is resident iff it has no more CTAs than SMs
-  q.coop = (p->splits > 1 && p->coop >= 0 && static_cast<int>(grid.x * grid.y * grid.z) <= sm_count) ? 1 : 0;
+  q.coop = (p->splits > 1 && p->coop >= 0 && resident) ? 1 : 0;
+  if (p->tail_mode != 0) {
+    // the tails wait for the whole grid: every CTA must be resident, one token-tile form only
+    if (!resident || p->group_tiles || p->w4 == 3 || p->tail_sync == nullptr || p->mtiles == 2 ||
+        false)
+      return static_cast<int>(cudaErrorInvalidValue);
+    if (p->tail_mode == 1 &&
+        (p->splits != 1 || p->w4 == 2 || p->tp_nranks > 1 || p->N != p->N_pad || p->tail_q == nullptr ||
+         p->tail_scale == nullptr || p->tail_M_pad < p->M || p->tail_M_pad > 256 || (p->tail_M_pad % p->nt) != 0))
+      return static_cast<int>(cudaErrorInvalidValue);
+    if (p->tail_mode == 2 &&
+        (p->tail_row == nullptr || p->tail_row_mode != kRowAddRms || (p->tail_row->K & 127) ||
+         p->tail_row->K > 2 * 16 * kGemmThreads))
+      return static_cast<int>(cudaErrorInvalidValue);
+    if (p->tail_mode != 1 && p->tail_mode != 2) return static_cast<int>(cudaErrorInvalidValue);
+  }
   // grouped tiles: the lean instantiation, two CTAs per SM, when two ring stages fit its budget
   if (p->group_tiles && p->w4 == 1 && p->splits == 1) {
     const int lean_smem = 2 * (16384 + p->nt * 128) + 2 * 32768 + 1024;
@@ -773,7 +1104,7 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   // long row runs of 4-bit weights: two token tiles per CTA (pairs must be whole inside M_pad)
   q.mtiles = 1;
   if (p->mtiles >= 0 && !p->group_tiles && p->splits == 1 && (widen_l || p->w4 == 3) && p->nt == 128 && p->M > 128 &&
-      (p->M_pad / 128) % 2 == 0 && p->ag_flags == nullptr &&
+      (p->M_pad / 128) % 2 == 0 && p->ag_flags == nullptr && p->tail_mode == 0 && halves == 1 &&
       (p->mtiles == 2 || static_cast<int>(grid.x * grid.y) > sm_count)) {
     // (only when one tile per CTA needs more than one wave of CTAs: a grid that is resident as a whole
     // gains nothing from pairing tiles, its CTAs would just run twice as long)
@@ -789,8 +1120,41 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
       return static_cast<int>(saber::launch(p->w4 == 3 ? gemm_bf16_kernel : gemm_i8_kernel, grid2, dim3(kGemmThreads), smem2, stream, 2, q, st2));
     }
   }
-  return static_cast<int>(saber::launch(p->w4 == 3 ? gemm_bf16_kernel : gemm_i8_kernel, grid, dim3(kGemmThreads), smem, stream, (q.coop != 0 ? 1 : 0) | 2, q, stages));
+  // CTAs that wait for one another (split-K parts, tails) need the grid resident as a whole: it has
+  // at most one CTA per SM and no kernel of this library waits on a LATER launch, so a plain
+  // (programmatic) launch gets there; the cooperative attribute, which serialises the launch, is a switch.
+  const int lflags = ((q.coop != 0 && g_coop_launch) ? 1 : 0) | 2;
+  if (p->tail_mode == 2) {
+    q.tail_row = nullptr;
+    RowOpParams tail = *p->tail_row;
+    // One GPU, integer partial sums meeting in the accumulator blocks: the row tail reads the blocks
+    // itself (scales, rounds to bf16 exactly as the GEMM's own read-out would), so the splits neither
+    // wait for one another nor write and re-read the bf16 tile.  These launches use blocks of their
+    // own (acc_tail) which they clean themselves: the shared blocks stay zero between launches.
+    if (p->splits > 1 && p->acc_tail != nullptr && p->w4 != 2 && p->tp_nranks <= 1 && tail.tp_nranks <= 1 &&
+        tail.a == p->out && tail.K == p->N && tail.lda == p->ldo && p->N == p->N_pad) {
+      q.tail_mode = 3;
+      q.acc = p->acc_tail;
+      tail.acc = p->acc_tail;
+      tail.acc_a_scale = p->a_scale;
+      tail.acc_w_scale = p->w_scale;
+      tail.acc_nt = p->nt;
+      tail.acc_tiles_n = p->N_pad / 256;
+    }
+    return static_cast<int>(saber::launch(gemm_i8_tail_kernel, grid, dim3(kGemmThreads), smem, stream, lflags, q, stages, tail));
+  }
+  return static_cast<int>(saber::launch(p->w4 == 3 ? gemm_bf16_kernel : gemm_i8_kernel, grid, dim3(kGemmThreads), smem, stream, lflags, q, stages));
 }
+
+extern "C" int saber_gemm_i8_tail_ok(const saber::GemmI8Params* p) {
+  int sm_count = 0;
+  if (saber::device_setup(&sm_count) != 0) return 0;
+  if (p->group_tiles || p->w4 == 3 || p->nt <= 0) return 0;
+  const int grid_y = (p->M + p->nt - 1) / p->nt;
+  return (p->N_pad / 256) * (p->halves == 2 ? 2 : 1) * grid_y * p->splits <= sm_count ? 1 : 0;
+}
+
+extern "C" void saber_set_coop_launch(int on) { saber::g_coop_launch = on; }
 
 // ------------------------------------------------------------------------------------------------
 // Entry point that allocates nothing (declared in gemm_i8_noalloc.h).
@@ -832,8 +1196,9 @@ extern "C" int saber_gemm_i8_noalloc(const uint8_t* w, const float* w_scale, con
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess) return static_cast<int>(e);
-    e = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
-    if (e != cudaSuccess) return static_cast<int>(e);
+    int sms = 0;
+    const int se = device_setup(&sms);      // shared-memory opt-in of every GEMM kernel, on THIS device
+    if (se != 0) return se;
     g_noalloc_ptr[dev] = p;
   }
   unsigned char* base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
@@ -849,4 +1214,20 @@ extern "C" int saber_gemm_i8_noalloc(const uint8_t* w, const float* w_scale, con
   p.M = M; p.M_pad = M_pad; p.N = N; p.N_pad = N_pad; p.K = K;
   p.nt = nt; p.splits = splits; p.w4 = w4; p.ldo = ldo;
   return saber_gemm_i8_launch(&p, 0, stream);
+}
+
+// Reads back the library's own status word of the current device (what a call with status == null
+// used): 0, or the code of the first bounded wait that ran out since the last call cleared it.
+// Synchronises with `stream` first.  Returns a negative value when the entry point has not been
+// used on this device yet.
+extern "C" int saber_gemm_i8_noalloc_status(cudaStream_t stream) {
+  using namespace saber;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices || g_noalloc_ptr[dev] == nullptr)
+    return kNoAllocBadArgs;
+  uint32_t word = 0;
+  if (cudaMemcpyAsync(&word, g_noalloc_ptr[dev], sizeof(word), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess)
+    return kNoAllocBadArgs;
+  return static_cast<int>(word);
 }

@@ -7,6 +7,8 @@
 
 namespace saber {
 
+struct RowOpParams;
+
 constexpr int kTpMaxTiles = 512;   // flag words per (parity, source rank): one per (m tile, n tile)
 
 struct GemmI8Params {
@@ -65,6 +67,43 @@ struct GemmI8Params {
   const float* bias;           // [N] or null
   const __nv_bfloat16* res;    // epi 3
   int epi;
+  // ---- Fused tails (integer / MXFP4 instantiation only).  Both forms need every CTA of the grid
+  // resident at the same time (one CTA per SM: grid <= SM count); the launcher refuses other shapes.
+  //   1  silu(gate) * up + per-token int8 quantisation INSIDE the tile: the weight tiles are paired
+  //      (rows 0-127 of tile t = gate features [128 t, 128 t + 128), rows 128-255 = the up features
+  //      of the same indices), so a CTA owns whole (gate, up) pairs; the row maxima meet in
+  //      tail_sync, one grid-wide barrier, then every CTA writes its 128 bytes of each row straight
+  //      into the next GEMM's operand (tail_q / tail_scale).  splits must be 1; `out` is not written.
+  //   2  row tail: after the output is complete (all tiles, all split-K parts) and a grid-wide
+  //      barrier, the CTAs walk the rows with the row producer `tail_row_mode` on *tail_row
+  //      (add + RMSNorm + quantise of the NEXT op's input, the consumer side of the tensor-parallel
+  //      push included), so the row op costs no launch.
+  int tail_mode;
+  int tail_row_mode;
+  const RowOpParams* tail_row;   // HOST pointer, copied into the launch
+  int8_t* tail_q;                // mode 1: tiled int8 [N / 256][tail_M_pad][128]
+  float* tail_scale;             // mode 1: [tail_M_pad]
+  int tail_M_pad;
+  uint32_t* tail_sync;           // device words, zero between launches: [0] barrier counter, [64 + 32 r] maximum of row r (256 rows)
+  // ---- L2 prefetch of the NEXT GEMM's leading weight tiles (filled in by the step program): when
+  // this CTA has issued its last copy, it asks for the first next_pref k-blocks of the CTAs
+  // (tile, split) of the next launch, so that launch starts from L2 instead of cold HBM.
+  const uint8_t* next_w;
+  int next_tiles, next_splits, next_KB, next_kb_per, next_wbytes, next_pref;
+  // ---- split-K accumulator blocks (integer formats): one block of nt x 256 int32 per (m tile, n tile),
+  // ZERO between launches.  Non-null: the splits add their partial tiles into it with asynchronous
+  // bulk reductions in L2 (order-free, exact) instead of keeping private copies in `ws`; the CTAs
+  // that read a tile out put its block back to zero.  Null: private copies.
+  int32_t* acc;
+  // Blocks for launches whose row tail reads the accumulators itself (split-K + row tail on one
+  // GPU): same shape, NOT zero between launches -- such a launch cleans its blocks itself.  Null:
+  // the row tail reads the bf16 tile the GEMM's own read-out wrote.
+  int32_t* acc_tail;
+  // Half tiles (packed int4 weights, splits == 1, no tail, one GPU): halves == 2 launches two CTAs
+  // per 256-row weight tile; each copies the whole packed tile but widens and multiplies only its
+  // 128 rows (the low or the high nibbles).  For shapes whose tile count fills less than half of
+  // the SMs this doubles the CTAs without any split-K round trip.  0 / 1 = whole tiles.
+  int halves;
 };
 
 }  // namespace saber
@@ -73,3 +112,5 @@ extern "C" int saber_gemm_i8_smem_bytes(int nt, int stages);
 extern "C" int saber_gemm_i8_smem_bytes_w(int nt, int stages, int w4);
 extern "C" int saber_gemm_i8_parts(const saber::GemmI8Params* p);
 extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cudaStream_t stream);
+// 1 when the launch of `p` keeps its whole grid resident (what the fused tails need), else 0.
+extern "C" int saber_gemm_i8_tail_ok(const saber::GemmI8Params* p);

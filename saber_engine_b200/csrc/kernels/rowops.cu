@@ -15,76 +15,13 @@
 #include "rowops.h"
 #include "gemm_i8.h"
 #include "ptx_sm100.cuh"
+#include "rowops_body.cuh"
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
 namespace saber {
 
 constexpr int kRowThreads = 256;
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-template <bool kMax>
-__device__ __forceinline__ float block_reduce(float v, float* red) {
-  v = kMax ? warp_max(v) : warp_sum(v);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __syncthreads();  // protect `red` against the previous use
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  const int nw = blockDim.x >> 5;
-  float r = (lane < nw) ? red[lane] : (kMax ? 0.f : 0.f);
-  r = kMax ? warp_max(r) : warp_sum(r);
-  return r;
-}
-
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
-__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
-
-// four values -> four quantised bytes (int8 round-to-nearest with clamp, or fp8 e4m3 saturating)
-__device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, float inv, int qfmt) {
-  if (qfmt == 1) {
-    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a * inv, b * inv), __NV_SATFINITE, __NV_E4M3);
-    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c * inv, d * inv), __NV_SATFINITE, __NV_E4M3);
-    return lo | (hi << 16);
-  }
-  const float x[4] = {a, b, c, d};
-  uint32_t word = 0;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    int qi = __float2int_rn(x[j] * inv);
-    qi = max(-127, min(127, qi));
-    word |= (static_cast<uint32_t>(qi) & 0xFFu) << (8 * j);
-  }
-  return word;
-}
-
-struct alignas(16) Bf16x8 {
-  __nv_bfloat162 v[4];
-};
-
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
-  const Bf16x8 raw = *reinterpret_cast<const Bf16x8*>(p);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 t = __bfloat1622float2(raw.v[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
-  Bf16x8 raw;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) raw.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-  *reinterpret_cast<Bf16x8*>(p) = raw;
-}
 
 // Quantise the row held in shared memory (bf16, K values) and store it tiled. All threads call.
 __device__ __forceinline__ void quant_store_row(const __nv_bfloat16* h, int K, int m, int M_pad,
@@ -239,8 +176,11 @@ __global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpPa
       float x[8];
       if (MODE == kRowSiluMul) {
         float g[8], u[8];
-        load8(p.a + static_cast<size_t>(m) * p.lda + v * 8, g);
-        load8(p.a + static_cast<size_t>(m) * p.lda + K + v * 8, u);
+        const int k = v * 8;
+        const int kg = p.silu_pair ? ((k >> 7) << 8) + (k & 127) : k;
+        const int ku = p.silu_pair ? kg + 128 : K + k;
+        load8(p.a + static_cast<size_t>(m) * p.lda + kg, g);
+        load8(p.a + static_cast<size_t>(m) * p.lda + ku, u);
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = silu_f(g[i]) * u[i];
       } else if (MODE == kRowGateSig) {
@@ -265,226 +205,20 @@ __global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpPa
   if (p.q) quant_store_row(h, K, m, p.M_pad, amax, p.q, p.scale, p.qfmt);
 }
 
-// Register-resident form of ADD_RMS / SILU_MUL / GATE_SIG / PLAIN: a thread owns whole 16-value
-// chunks (the unit of the tiled int8 store) and keeps them in registers between the passes, so the
-// kernel needs no dynamic shared memory and its CTAs fit beside a resident GEMM CTA: the GEMM that
-// follows a row kernel is launched programmatically, gets resident while the row kernel runs and
-// streams its first weight tiles meanwhile.  MAXC bounds the chunks per thread: K <= MAXC * 4096.
+// Register-resident form of ADD_RMS / SILU_MUL / GATE_SIG / PLAIN (body in rowops_body.cuh): a
+// thread owns whole 16-value chunks (the unit of the tiled int8 store) and keeps them in registers
+// between the passes, so the kernel needs no dynamic shared memory and its CTAs fit beside a
+// resident GEMM CTA: the GEMM that follows a row kernel is launched programmatically, gets resident
+// while the row kernel runs and streams its first weight tiles meanwhile.  MAXC bounds the chunks
+// per thread: K <= MAXC * 4096.
 template <int MODE, int MAXC>
 __global__ void __launch_bounds__(kRowThreads) row_reg_kernel(const RowOpParams p) {
   pdl_trigger();
   pdl_wait();
   __shared__ float red[32];
   const int m = blockIdx.x;
-  const int K = p.K;
   if (p.m_live != nullptr && m >= *p.m_live) return;
-  const int nchunk = K >> 4;
-  const bool sp = MODE == kRowAddRms && p.sp_rpr > 0 && p.tp_nranks > 1;
-  if (sp && (m >= p.M || m / p.sp_rpr != p.sp_rank)) return;   // sequence parallel: not this rank's row
-  if (m >= p.M) {  // padding row: zeros
-    if (p.q) {
-      for (int ch = threadIdx.x; ch < nchunk; ch += kRowThreads) {
-        const int kb = ch >> 3, c = ch & 7;
-        int8_t* dst = p.q + (static_cast<size_t>(kb) * p.M_pad + m) * 128 + (((c ^ (m & 7)) & 7) << 4);
-        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
-      }
-      if (threadIdx.x == 0) p.scale[m] = 0.f;
-    }
-    return;
-  }
-  uint32_t tp_par = 0;
-  if (MODE == kRowAddRms && p.tp_nranks > 1) {
-    const uint32_t seq = *p.tp_seq_base + static_cast<uint32_t>(p.tp_site) + 1u;
-    tp_par = seq & 1u;
-    const int nflags = p.tp_nranks * p.tp_tiles_n;
-    for (int f = threadIdx.x; f < nflags; f += kRowThreads) {
-      const int src = f / p.tp_tiles_n, tn = f - src * p.tp_tiles_n;
-      const int tile_id = (m / p.tp_nt) * p.tp_tiles_n + tn;
-      const uint32_t* flag = p.tp_flags + (static_cast<size_t>(tp_par) * p.tp_nranks + src) * kTpMaxTiles + tile_id;
-      const long long t0 = clock64();
-      uint32_t spins = 0;
-      while (true) {
-        uint32_t v;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-        if (static_cast<int32_t>(v - seq) >= 0) break;
-        if ((++spins & 1023u) == 0u && clock64() - t0 > kWaitLimitCycles) {
-          if (p.err) atomicCAS(p.err, 0u, static_cast<uint32_t>(kErrWaitPeer));
-          break;
-        }
-      }
-    }
-    __syncthreads();
-  }
-  float hv[MAXC][16];   // the row's values of this thread (ADD_RMS: first the sums, then the normed row)
-  float amax = 0.f;
-  float ss = 0.f;
-#pragma unroll
-  for (int c = 0; c < MAXC; ++c) {
-    const int ch = threadIdx.x + c * kRowThreads;
-    if (ch >= nchunk) continue;
-    const int k0 = ch << 4;
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int k = k0 + half * 8;
-      float x[8];
-      if (MODE == kRowAddRms) {
-        if (p.tp_nranks > 1) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) x[i] = 0.f;
-          for (int src = 0; src < p.tp_nranks; ++src) {   // fixed order: identical sums on every rank
-            const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(
-                p.tp_recv + ((static_cast<size_t>(tp_par) * p.tp_nranks + src) * p.tp_rows + m) * p.tp_ld + k));
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 f = __bfloat1622float2(h2[i]);
-              x[2 * i] += f.x;
-              x[2 * i + 1] += f.y;
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i) x[i] = __bfloat162float(__float2bfloat16(x[i]));
-        } else if (p.a) {
-          load8(p.a + static_cast<size_t>(m) * p.lda + k, x);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) x[i] = 0.f;
-        }
-        if (p.res) {
-          float r[8];
-          load8(p.res + static_cast<size_t>(m) * p.ldres + k, r);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) x[i] += r[i];
-          store8(p.res + static_cast<size_t>(m) * p.ldres + k, x);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
-      } else {
-        if (MODE == kRowSiluMul) {
-          float g[8], u[8];
-          load8(p.a + static_cast<size_t>(m) * p.lda + k, g);
-          load8(p.a + static_cast<size_t>(m) * p.lda + K + k, u);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) x[i] = silu_f(g[i]) * u[i];
-        } else if (MODE == kRowGateSig) {
-          float a[8], b[8];
-          load8(p.a + static_cast<size_t>(m) * p.lda + k, a);
-          load8(p.b + static_cast<size_t>(m) * p.ldb + k, b);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) x[i] = a[i] * sigmoid_f(b[i]);
-        } else {
-          load8(p.a + static_cast<size_t>(m) * p.lda + k, x);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          x[i] = __bfloat162float(__float2bfloat16(x[i]));
-          amax = fmaxf(amax, fabsf(x[i]));
-        }
-        if (p.out) store8(p.out + static_cast<size_t>(m) * p.ldout + k, x);
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) hv[c][half * 8 + i] = x[i];
-    }
-  }
-  if (MODE == kRowAddRms) {
-    ss = block_reduce<false>(ss, red);
-    const float rstd = rsqrtf(ss / static_cast<float>(K) + p.eps);
-#pragma unroll
-    for (int c = 0; c < MAXC; ++c) {
-      const int ch = threadIdx.x + c * kRowThreads;
-      if (ch >= nchunk) continue;
-      const int k0 = ch << 4;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float x[8];
-        const float4 w0 = *reinterpret_cast<const float4*>(p.w + k0 + half * 8);
-        const float4 w1 = *reinterpret_cast<const float4*>(p.w + k0 + half * 8 + 4);
-        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          x[i] = __bfloat162float(__float2bfloat16(hv[c][half * 8 + i] * rstd * (wv[i] + p.w_offset)));
-          amax = fmaxf(amax, fabsf(x[i]));
-          hv[c][half * 8 + i] = x[i];
-        }
-        if (p.out) store8(p.out + static_cast<size_t>(m) * p.ldout + k0 + half * 8, x);
-      }
-    }
-  }
-  if (p.had_sign != nullptr && p.q) {
-    // 32-point Hadamard per block = this thread's 16 values (one chunk) and its lane neighbour's
-    // (chunks 2j and 2j + 1 belong to lanes 2i and 2i + 1): four butterfly stages in registers,
-    // the fifth across the lane pair.  The quantisation scale is taken AFTER the rotation.
-    amax = 0.f;
-    const bool odd = threadIdx.x & 1;
-#pragma unroll
-    for (int c = 0; c < MAXC; ++c) {
-      const int ch = threadIdx.x + c * kRowThreads;
-      const bool on = ch < nchunk;               // (nchunk is even: K is a multiple of 128)
-      if (on) {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) hv[c][i] *= p.had_sign[(ch << 4) + i];
-#pragma unroll
-        for (int st = 1; st < 16; st <<= 1)
-#pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if ((i & st) == 0) {
-              const float a = hv[c][i], b2 = hv[c][i | st];
-              hv[c][i] = a + b2;
-              hv[c][i | st] = a - b2;
-            }
-      }
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float other = __shfl_xor_sync(0xffffffffu, hv[c][i], 1);
-        const float r = (odd ? other - hv[c][i] : hv[c][i] + other) * 0.17677669529663687f;   // 1 / sqrt(32)
-        hv[c][i] = __bfloat162float(__float2bfloat16(r));
-        if (on) amax = fmaxf(amax, fabsf(hv[c][i]));
-      }
-    }
-  }
-  amax = block_reduce<true>(amax, red);
-  if (p.q) {
-    const float qmax = p.qfmt == 1 ? 448.f : 127.f;
-    const float inv = amax > 0.f ? qmax / amax : 0.f;
-    if (threadIdx.x == 0 && !sp) p.scale[m] = amax / qmax;
-#pragma unroll
-    for (int c = 0; c < MAXC; ++c) {
-      const int ch = threadIdx.x + c * kRowThreads;
-      if (ch >= nchunk) continue;
-      uint32_t w[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        w[i] = quant4(hv[c][i * 4], hv[c][i * 4 + 1], hv[c][i * 4 + 2], hv[c][i * 4 + 3], inv, p.qfmt);
-      const int kb = ch >> 3, cc = ch & 7;
-      const size_t off = (static_cast<size_t>(kb) * p.M_pad + m) * 128 + (((cc ^ (m & 7)) & 7) << 4);
-      if (sp) {
-        for (int peer = 0; peer < p.tp_nranks; ++peer)
-          *reinterpret_cast<uint4*>(p.sp_q[peer] + off) = make_uint4(w[0], w[1], w[2], w[3]);
-      } else {
-        *reinterpret_cast<uint4*>(p.q + off) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    }
-    if (sp) {
-      if (threadIdx.x == 0)
-        for (int peer = 0; peer < p.tp_nranks; ++peer) p.sp_scale[peer][m] = amax / qmax;
-      // the row is on every rank once these stores are visible; the CTA that completes the 128-row
-      // tile raises its arrival flag everywhere
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        __threadfence_system();
-        const int tile = m >> 7;
-        const int rows_in_tile = min(128, p.M - (tile << 7));
-        const uint32_t old = atomicAdd(p.sp_counter + tile, 1u);
-        if (old == static_cast<uint32_t>(rows_in_tile - 1)) {
-          p.sp_counter[tile] = 0u;
-          __threadfence_system();
-          const uint32_t seq = *p.tp_seq_base + static_cast<uint32_t>(p.tp_site) + 1u;
-          for (int peer = 0; peer < p.tp_nranks; ++peer)
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.sp_flags[peer] + (seq & 1u) * 64u + tile), "r"(seq) : "memory");
-        }
-      }
-    }
-  }
+  row_reg_body<MODE, MAXC, false>(p, m, red);
 }
 
 // out[m, :] = table[ids[m], :]   (bf16 rows, 16-byte vectors); ids outside [0, vocab) give zeros.

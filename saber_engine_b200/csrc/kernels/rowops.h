@@ -54,6 +54,21 @@ struct RowOpParams {
   uint32_t* sp_flags[8];        // each rank's arrival flags [2 parity][64 row tiles]
   uint32_t* sp_counter;         // this rank's rows-done counters [64 row tiles] (zero between uses)
   int sp_rpr, sp_rank;
+  // ADD_RMS: optional second copy of the updated residual row (same row stride as `res`): the
+  // drafter's tap of this layer, written here instead of by a copy launch.  Null = off.
+  __nv_bfloat16* res_copy;
+  // SILU_MUL on the output of a PAIRED gate | up linear: gate and up of feature 128 t + c sit at
+  // columns 256 t + c and 256 t + 128 + c (instead of c and K + c).
+  int silu_pair;
+  // ADD_RMS as the row tail of a split-K GEMM on one GPU (filled in by the GEMM launcher): the
+  // primary input is not `a` but the GEMM's int32 accumulator blocks ([tile][c4][acc_nt rows][4]);
+  // the row op scales and rounds them exactly as the GEMM's own read-out would
+  // (bf16(acc * (a_scale[m] * w_scale[n]))).  The blocks are left as they are: a GEMM launch in
+  // this mode cleans them itself before its splits add.
+  int32_t* acc;
+  const float* acc_a_scale;
+  const float* acc_w_scale;
+  int acc_nt, acc_tiles_n;
 };
 
 }  // namespace saber

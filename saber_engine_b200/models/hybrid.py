@@ -114,7 +114,7 @@ class HybridModel:
                  max_width: int = 8, weights: Optional[ModelWeights] = None, seed: int = 0,
                  comm=None, oracle_p: float = 0.0, oracle_seed: int = 0, gdn_vs: int = 2,
                  use_drafter: bool = True, race_check: str = "off", gdn_prefill: str = "rows",
-                 image_rows: int = 0):
+                 image_rows: int = 0, fuse: bool = True):
         self.cfg, self.tp, self.rank = cfg, tp, rank
         if race_check not in ("off", "shadow"):
             raise ValueError("race_check must be 'off' or 'shadow'")
@@ -132,6 +132,18 @@ class HybridModel:
         self.use_drafter = use_drafter and cfg.drafter is not None
         self.w = weights if weights is not None else random_init(cfg, tp, rank, self.device, seed)
         self.scratch = F.scratch(self.device)
+        # Fused forms of the decode chain (launches that stay resident as a whole grid): the row op
+        # after a row-parallel linear rides as that GEMM's row tail, silu * mul + quant runs in the
+        # epilogue of the (paired) gate | up linear.  fuse=False keeps one launch per op.
+        self.fuse = bool(fuse)
+        self._held = None
+        if self.fuse and cfg.moe is None:
+            for lw in self.w.layers:
+                if lw.gate_up is not None:
+                    lw.gate_up = F.pair_gate_up(lw.gate_up)
+            if self.w.drafter is not None:
+                for d in self.w.drafter.layers:
+                    d["gate_up"] = F.pair_gate_up(d["gate_up"])
         self.k_scale = self.v_scale = 1.0
         # Image rows: the token table is extended by `image_rows` rows that the vision tower writes; a
         # prompt names them as token ids vocab + r, so the embedding gather of every (captured) prefill
@@ -193,25 +205,73 @@ class HybridModel:
             return None
         return F.QuantAct(a.q, a.scale, a.M, a.K, fp8=bool(getattr(w, "mx", False)), had_sign=getattr(w, "had_sign", None))
 
+    def _flush(self, prog: N.Program) -> None:
+        """Add the GEMM that was held back for a row tail as a plain launch."""
+        if self._held is not None:
+            p, stages, tag = self._held
+            self._held = None
+            prog.gemm(p, stages, tag=tag)
+
     def _gemm(self, prog: N.Program, w: F.QuantWeight, a: F.QuantAct, out: torch.Tensor, tag: str,
-              tp_site: int = -1) -> None:
-        """tp_site >= 0: a row-parallel GEMM whose epilogue pushes its partial sums to every rank."""
+              tp_site: int = -1, hold: bool = False) -> None:
+        """tp_site >= 0: a row-parallel GEMM whose epilogue pushes its partial sums to every rank.
+        hold: the launch is kept back until the next op is known -- an add + RMSNorm + quantise that
+        consumes this GEMM's output becomes its row tail (`_add_rms`), anything else adds it as it is."""
+        self._flush(prog)
         a = self._fmt(a, w)
-        splits = self.pick_splits(w, a)
-        p = F.gemm_params(w, a, out, self.scratch, splits=splits)
+        nt = L.token_tile(a.M)
+        halves = 2 if (self.fuse and tp_site < 0 and not hold and
+                       F.pick_halves(w, w.N_pad // L.TILE_N, (a.M + nt - 1) // nt)) else 1
+        splits = 1 if halves == 2 else self.pick_splits(w, a)
+        p = F.gemm_params(w, a, out, self.scratch, splits=splits, halves=halves)
         if tp_site >= 0 and self.tp > 1:
             self.comm.gemm_tp(p, tp_site)
             self._site_parts[tp_site] = N.lib().saber_gemm_i8_parts(C.byref(p))
-        prog.gemm(p, self.gemm_stages(w, a), tag=tag)
+        if hold and self.fuse:
+            self._held = (p, self.gemm_stages(w, a), tag)
+        else:
+            prog.gemm(p, self.gemm_stages(w, a), tag=tag)
 
-    def _add_rms(self, prog: N.Program, M: int, tag: str, w, res, qa, delta, tp_site: int = -1, out=None) -> None:
-        """residual += (delta | the all-reduced GEMM output of `tp_site`); norm; int8 quant."""
+    def _mlp_in(self, prog: N.Program, w: F.QuantWeight, a: F.QuantAct, gu: torch.Tensor, qa_i: F.QuantAct,
+                w_down, K_inter: int, M: int, tag: str) -> None:
+        """gate | up linear, silu(gate) * up, per-token quantisation into `qa_i`: one launch when the
+        weight is paired and the grid stays resident, else GEMM + row kernel."""
+        self._flush(prog)
+        a = self._fmt(a, w)
+        splits = self.pick_splits(w, a)
+        p = F.gemm_params(w, a, gu, self.scratch, splits=splits)
+        qi = self._fmt(qa_i, w_down)
+        if self.fuse and w.paired and splits == 1 and not qi.fp8 and qi.had_sign is None and F.gemm_tail_ok(p) \
+                and qi.M_pad % p.nt == 0 and qi.M_pad <= 256:
+            F.gemm_tail_silu_quant(p, qi, self.scratch)
+            prog.gemm(p, self.gemm_stages(w, a), tag=f"{tag}.gate_up+silu_mul_quant")
+            return
+        prog.gemm(p, self.gemm_stages(w, a), tag=f"{tag}.gate_up")
+        rp = F.row_params(M, K_inter, a=gu, qa=qi)
+        rp.silu_pair = int(w.paired)
+        prog.row(N.ROW_SILU_MUL, rp, tag=f"{tag}.silu_mul_quant")
+
+    def _add_rms(self, prog: N.Program, M: int, tag: str, w, res, qa, delta, tp_site: int = -1, out=None,
+                 res_copy=None) -> None:
+        """residual += (delta | the all-reduced GEMM output of `tp_site`); norm; int8 quant.  When the
+        GEMM that produced `delta` is being held (`_gemm(hold=True)`) and its grid stays resident, the
+        op becomes that GEMM's row tail instead of a launch of its own."""
         cfg = self.cfg
         p = F.row_params(M, cfg.hidden, a=delta, res=res, w=w, w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa, out=out)
+        if res_copy is not None:
+            p.res_copy = res_copy.data_ptr()
         if tp_site >= 0 and self.tp > 1:
             nt = self._site_nt.get(tp_site, L.token_tile(M))
             # a producer that signals per split-K part shows up as that many flags per feature tile
             self.comm.row_tp(p, tp_site, nt, L.round_up(cfg.hidden, L.TILE_N) // L.TILE_N * self._site_parts.get(tp_site, 1))
+        if self._held is not None:
+            gp, stages, gtag = self._held
+            if cfg.hidden <= 2 * 16 * 320 and (qa is None or qa.had_sign is None) and F.gemm_tail_ok(gp):
+                self._held = None
+                F.gemm_tail_row(gp, p, self.scratch)
+                prog.gemm(gp, stages, tag=f"{gtag}+{tag}")
+                return
+            self._flush(prog)
         prog.row(N.ROW_ADD_RMS, p, tag=tag)
 
     def pick_splits(self, w: F.QuantWeight, a: F.QuantAct) -> int:
@@ -300,6 +360,7 @@ class HybridModel:
                 tap_buf, part_o, part_ml]
 
         def row(mode, Mr, K, tag, **kw):
+            self._flush(prog)
             prog.row(mode, F.row_params(Mr, K, **kw), tag=tag)
 
         digests = None
@@ -313,10 +374,12 @@ class HybridModel:
         pending = -1          # site of the TP GEMM whose pushed output the next add-norm consumes
         for i, lw in enumerate(self.w.layers):
             t = f"L{i}"
-            self._add_rms(prog, M, f"{t}.in_norm", lw.in_norm, h, self._fmt(qa_h, lw.mixer_in), None if first else delta, pending)
-            first = False
-            if i in taps:
+            # (the drafter's tap of this layer = the residual stream after this add: a second store of the row op)
+            self._add_rms(prog, M, f"{t}.in_norm", lw.in_norm, h, self._fmt(qa_h, lw.mixer_in), None if first else delta, pending,
+                          res_copy=tap_buf[taps.index(i)] if (i in taps and not first) else None)
+            if i in taps and first:
                 prog.copy(tap_buf[taps.index(i)], h, tag=f"{t}.tap")
+            first = False
             if lw.kind == "gdn":
                 n_q = n_k = sh.gdn_k_heads * d
                 C_ = sh.gdn_conv_c
@@ -341,7 +404,7 @@ class HybridModel:
                     prog.gdn_rec(rp, nseq, self.gdn_vs, tag=f"{t}.gdn.rec")
                 row(N.ROW_GDN_NORM, M, sh.gdn_out_k, f"{t}.gdn.norm_quant", a_f32=gdn_o,
                     b=buf_in[:, C_:], w=lw.gdn_norm, eps=cfg.eps, qa=self._fmt(qa_gdn, lw.mixer_out), ldb=ld_in)
-                self._gemm(prog, lw.mixer_out, qa_gdn, delta, f"{t}.gdn.out_proj", tp_site=ar_site)
+                self._gemm(prog, lw.mixer_out, qa_gdn, delta, f"{t}.gdn.out_proj", tp_site=ar_site, hold=True)
             else:
                 nq, nkv = sh.n_q_heads, sh.n_kv_heads
                 gate = 2 if cfg.attn_out_gate else 1
@@ -367,18 +430,19 @@ class HybridModel:
                         qa=self._fmt(qa_attn, lw.mixer_out), ldb=ld_in)
                 else:
                     row(N.ROW_PLAIN, M, nq * D, f"{t}.attn.quant", a=ao, qa=self._fmt(qa_attn, lw.mixer_out))
-                self._gemm(prog, lw.mixer_out, qa_attn, delta, f"{t}.attn.o_proj", tp_site=ar_site)
+                self._gemm(prog, lw.mixer_out, qa_attn, delta, f"{t}.attn.o_proj", tp_site=ar_site, hold=True)
             pending, ar_site = (ar_site, ar_site + 1) if self.tp > 1 else (-1, ar_site)
             self._add_rms(prog, M, f"{t}.post_norm", lw.post_norm, h, self._fmt(qa_h, lw.gate_up), delta, pending)
             if cfg.moe is None:
-                self._gemm(prog, lw.gate_up, qa_h, gu, f"{t}.mlp.gate_up")
-                row(N.ROW_SILU_MUL, M, sh.ffn_inter, f"{t}.mlp.silu_mul_quant", a=gu, qa=self._fmt(qa_i, lw.down))
-                self._gemm(prog, lw.down, qa_i, delta, f"{t}.mlp.down", tp_site=ar_site)
+                self._mlp_in(prog, lw.gate_up, qa_h, gu, qa_i, lw.down, sh.ffn_inter, M, f"{t}.mlp")
+                self._gemm(prog, lw.down, qa_i, delta, f"{t}.mlp.down", tp_site=ar_site, hold=True)
             else:
                 from .moe_block import add_moe_block
+                self._flush(prog)
                 self._site_nt[ar_site] = add_moe_block(self, prog, lw, qa_h, h, delta, M, t, keep, tp_site=ar_site)
             pending, ar_site = (ar_site, ar_site + 1) if self.tp > 1 else (-1, ar_site)
             if digests is not None:     # what the layer left in the residual stream and in its MLP output
+                self._flush(prog)
                 prog.digest(h, M * H * 2, digests.data_ptr() + 8 * i, tag=f"{t}.digest")
         self._build_head(prog, kind, nseq, width, M, Mh, lay, at, h, delta, qa_h, tap_buf, taps, keep,
                          ar_site, pending)
@@ -425,6 +489,7 @@ class HybridModel:
             normed = torch.zeros(M, H, dtype=torch.bfloat16, device=dev)
             last = torch.zeros(nseq, H, dtype=torch.bfloat16, device=dev)
             self._add_rms(prog, M, "final_norm", self.w.final_norm, h, None, delta, pending, out=normed)
+            self._flush(prog)
             prog.embed(normed, at(lay.last_rows), last, nseq, H, 0, M, H, tag="gather_last_rows")
             qa_head = self._qa(nseq, H)
             prog.row(N.ROW_PLAIN, F.row_params(nseq, H, a=last, qa=self._fmt(qa_head, self.w.lm_head)), tag="head_quant")
@@ -504,22 +569,21 @@ class HybridModel:
         prog.expand(ctx, tok, dw.pos_emb, x, nseq, B, Hd, tag="draft.expand")
         qa_x, qa_di = self._qa(R, Hd), self._qa(R, dc.inter)
         gu = torch.zeros(R, 2 * dc.inter, dtype=torch.bfloat16, device=dev)
+        assert Hd == cfg.hidden
         for li, lw in enumerate(dw.layers):
-            prog.row(N.ROW_ADD_RMS, F.row_params(R, Hd, a=None if li == 0 else dd, res=x, w=lw["norm"],
-                                                 w_offset=cfg.norm_offset, eps=cfg.eps, qa=self._fmt(qa_x, lw["gate_up"])),
-                     tag=f"draft.L{li}.norm")
-            self._gemm(prog, lw["gate_up"], qa_x, gu, f"draft.L{li}.gate_up")
-            prog.row(N.ROW_SILU_MUL, F.row_params(R, dc.inter, a=gu, qa=self._fmt(qa_di, lw["down"])), tag=f"draft.L{li}.silu_mul")
-            self._gemm(prog, lw["down"], qa_di, dd, f"draft.L{li}.down")
-        prog.row(N.ROW_ADD_RMS, F.row_params(R, Hd, a=dd if dw.layers else None, res=x, w=dw.final_norm,
-                                             w_offset=cfg.norm_offset, eps=cfg.eps, qa=self._fmt(qa_x, dw.head)),
-                 tag="draft.final_norm")
+            self._add_rms(prog, R, f"draft.L{li}.norm", lw["norm"], x, self._fmt(qa_x, lw["gate_up"]), None if li == 0 else dd)
+            self._mlp_in(prog, lw["gate_up"], qa_x, gu, qa_di, lw["down"], dc.inter, R, f"draft.L{li}")
+            self._gemm(prog, lw["down"], qa_di, dd, f"draft.L{li}.down", hold=True)
+        self._add_rms(prog, R, "draft.final_norm", dw.final_norm, x, self._fmt(qa_x, dw.head), dd if dw.layers else None)
         dlogits = torch.zeros(R, (cfg.vocab + 7) // 8 * 8, dtype=torch.bfloat16, device=dev)
         self._gemm(prog, dw.head, qa_x, dlogits, "draft.head")
         prog.argmax(dlogits, R, dlogits.stride(0), cfg.vocab, 0, o_drafts, None, tag="draft.argmax")
         keep += [cat, qa_cat, ctx, tok, x, dd, qa_x, qa_di, gu, dlogits]
 
     def _finish_bucket(self, prog, kind, nseq, width, M, lay, blob, blob_host, keep, capture) -> Bucket:
+        self._flush(prog)
+        if self.fuse:
+            prog.link_prefetch()
         head = self._last_head
         out = head["out"]
         out_host = torch.zeros(out.numel(), dtype=torch.int32).pin_memory()

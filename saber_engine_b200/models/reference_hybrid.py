@@ -14,7 +14,10 @@ from .weights import ModelWeights
 
 
 def dequant_linear(w: QuantWeight):
-    """(int8 true values [N, K], fp32 row scale [N]) on the CPU."""
+    """(int8 true values [N, K], fp32 row scale [N]) on the CPU, rows in the canonical order."""
+    if getattr(w, "paired", False):
+        from ..ops.functional import unpair_gate_up
+        w = unpair_gate_up(w)
     tiles = w.tiles.cpu()
     if w.w4:
         q = L.unpack_weight_int4(tiles, w.N, w.K)

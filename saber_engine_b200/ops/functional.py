@@ -27,6 +27,7 @@ class QuantWeight:
     w4: bool
     mx: bool = False         # MXFP4 tiles (e2m1 codes + block shifts): fp8 activations, fp32 accumulate
     had_sign: Optional[torch.Tensor] = None   # fp32 [K] +-1: the input must be rotated (sign, 32-point Hadamard) before quantisation
+    paired: bool = False     # merged gate | up linear regrouped so that tile t holds gate and up features [128 t, 128 t + 128)
 
     @property
     def N_pad(self) -> int:
@@ -65,6 +66,23 @@ class QuantWeight:
         return QuantWeight(tiles.to(dev).contiguous(), sc.to(dev), Nn, K, bits == 4)
 
 
+def pair_gate_up(w: QuantWeight) -> QuantWeight:
+    """The merged gate | up linear with its tiles regrouped for the fused silu * mul epilogue (see
+    `layouts.pair_gate_up_int4`); weights that cannot be paired (int8, MXFP4, ragged) come back unchanged."""
+    if w.paired or not w.w4 or w.mx or w.N % 256 or (w.N // 2) % 128:
+        return w
+    tiles, scale = L.pair_gate_up_int4(w.tiles, w.scale, w.N // 2)
+    return QuantWeight(tiles, scale, w.N, w.K, True, had_sign=w.had_sign, paired=True)
+
+
+def unpair_gate_up(w: QuantWeight) -> QuantWeight:
+    """The canonical (gate rows, then up rows) form of a paired weight."""
+    if not w.paired:
+        return w
+    tiles, scale = L.unpair_gate_up_int4(w.tiles, w.scale, w.N // 2)
+    return QuantWeight(tiles, scale, w.N, w.K, True, had_sign=w.had_sign, paired=False)
+
+
 @dataclass
 class QuantAct:
     """Quantised activations in the tiled layout."""
@@ -96,12 +114,21 @@ class GemmScratch:
         self.ws = torch.zeros(max_rows * max_cols, dtype=torch.int32, device=device)
         self.counters = torch.zeros(8192, dtype=torch.int32, device=device)
         self.err = torch.zeros(1, dtype=torch.int32, device=device)
+        # words of the fused tails (zero between launches): [0] grid-barrier counter, then one 128-byte line per row for the row maxima
+        self.tail_sync = torch.zeros(64 + 256 * 32 + 256, dtype=torch.int32, device=device)
+        # split-K accumulator blocks (nt x 256 int32 per tile), zero between launches
+        self.acc = torch.zeros(80 * 32768, dtype=torch.int32, device=device)
+        # blocks of the GEMMs whose row tail reads the accumulators itself: cleaned by each launch, not between launches
+        self.acc_tail = torch.zeros(40 * 32768, dtype=torch.int32, device=device)
         self.capacity = max_rows * max_cols
 
     def check(self) -> None:
         code = int(self.err.item())
         if code != 0:
             self.err.zero_()
+            self.counters.zero_()       # a kernel that gave up half-way leaves its arrival words behind
+            self.tail_sync.zero_()
+            self.acc.zero_()
             raise N.NativeError(f"kernel wait timed out: {N.ERR_NAMES.get(code, code)}")
 
 
@@ -129,7 +156,8 @@ def pick_splits(n_tiles: int, m_tiles: int, kb: int, sms: int = 148) -> int:
 
 
 def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,
-                splits: Optional[int] = None, nt: Optional[int] = None, coop: int = 0, mtiles: int = 0) -> N.GemmI8Params:
+                splits: Optional[int] = None, nt: Optional[int] = None, coop: int = 0, mtiles: int = 0,
+                halves: int = 1) -> N.GemmI8Params:
     assert a.K == w.K, (a.K, w.K)
     nt = nt or L.token_tile(a.M)
     assert a.M_pad % nt == 0
@@ -145,20 +173,57 @@ def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,
     assert bool(getattr(w, 'mx', False)) == bool(a.fp8), "MXFP4 weights take fp8 activations, integer weights int8"
     p.nt, p.splits, p.w4, p.ldo = nt, splits, w.fmt_code, out.stride(0)
     p.coop = coop
+    if splits > 1 and not getattr(w, "mx", False) and m_tiles * (w.N_pad // L.TILE_N) * nt * 256 <= sc.acc.numel():
+        p.acc = sc.acc.data_ptr()       # integer partial sums meet in L2 (bulk reduction) instead of private copies
+        if m_tiles * (w.N_pad // L.TILE_N) * nt * 256 <= sc.acc_tail.numel():
+            p.acc_tail = sc.acc_tail.data_ptr()
+    p.halves = halves      # 2: two CTAs per weight tile, each on 128 of its rows (packed int4, splits == 1)
     p.mtiles = mtiles      # 0: the launcher decides; 2: pair token tiles whenever the shape allows; -1: never
     assert out.stride(0) % 8 == 0, "GEMM output rows must be 16-byte aligned"
     return p
 
 
+def gemm_tail_silu_quant(p: N.GemmI8Params, qa_out: QuantAct, sc: GemmScratch) -> N.GemmI8Params:
+    """Turn `p` (a paired gate | up linear, splits == 1) into the fused form: silu(gate) * up and the
+    per-token int8 quantisation run in the epilogue and land in `qa_out` (K = N / 2)."""
+    p.tail_mode = 1
+    p.tail_q, p.tail_scale, p.tail_M_pad = qa_out.q.data_ptr(), qa_out.scale.data_ptr(), qa_out.M_pad
+    p.tail_sync = sc.tail_sync.data_ptr()
+    return p
+
+
+def gemm_tail_row(p: N.GemmI8Params, row_p: N.RowOpParams, sc: GemmScratch) -> N.GemmI8Params:
+    """Attach the add + RMSNorm + quantise row op `row_p` (which reads this GEMM's output) as the
+    GEMM's row tail: it runs inside the same launch, after a grid-wide barrier."""
+    p.tail_mode, p.tail_row_mode = 2, N.ROW_ADD_RMS
+    p.tail_row = C.addressof(row_p)
+    p._tail_keep = row_p                 # the block must outlive the launch / the add to a program
+    p.tail_sync = sc.tail_sync.data_ptr()
+    return p
+
+
+def gemm_tail_ok(p: N.GemmI8Params) -> bool:
+    """True when the launch of `p` keeps its whole grid resident (the condition of both fused tails)."""
+    return bool(N.lib().saber_gemm_i8_tail_ok(C.byref(p)))
+
+
 def gemm_i8(w: QuantWeight, a: QuantAct, out: Optional[torch.Tensor] = None,
-            splits: Optional[int] = None, stages: int = 0, nt: Optional[int] = None, coop: int = 0, mtiles: int = 0) -> torch.Tensor:
+            splits: Optional[int] = None, stages: int = 0, nt: Optional[int] = None, coop: int = 0, mtiles: int = 0,
+            halves: int = 1) -> torch.Tensor:
     """out[M, N] = bf16(int32 accumulate * a_scale[m] * w_scale[n])."""
     dev = a.q.device
     if out is None:
         out = torch.empty(a.M, w.N, dtype=torch.bfloat16, device=dev)
-    p = gemm_params(w, a, out, scratch(dev), splits, nt, coop, mtiles)
+    p = gemm_params(w, a, out, scratch(dev), splits, nt, coop, mtiles, halves)
     N.check(N.lib().saber_gemm_i8_launch(C.byref(p), stages, N.stream_handle()), "gemm_i8")
     return out
+
+
+def pick_halves(w: QuantWeight, n_tiles: int, m_tiles: int, sms: int = 148) -> bool:
+    """Half tiles instead of split-K: packed int4 weights whose whole-tile grid fills between a
+    quarter and a half of the SMs."""
+    ctas = n_tiles * m_tiles
+    return bool(w.w4 and not w.mx and sms // 4 < ctas <= sms // 2)
 
 
 def row_params(M: int, K: int, *, a=None, a_f32=None, b=None, res=None, w=None, w_offset=0.0,
@@ -196,12 +261,16 @@ def add_rms_quant(x: Optional[torch.Tensor], res: Optional[torch.Tensor], w: tor
     return qa, out
 
 
-def silu_mul_quant(gu: torch.Tensor, want_out: bool = False):
+def silu_mul_quant(gu: torch.Tensor, want_out: bool = False, paired: bool = False):
+    """paired: `gu` is the output of a paired gate | up linear (gate and up of feature 128 t + c sit at
+    columns 256 t + c and 256 t + 128 + c)."""
     M, K2 = gu.shape
     K = K2 // 2
     qa = QuantAct.alloc(M, K, gu.device)
     out = torch.empty(M, K, dtype=torch.bfloat16, device=gu.device) if want_out else None
-    _row(N.ROW_SILU_MUL, row_params(M, K, a=gu, out=out, qa=qa))
+    p = row_params(M, K, a=gu, out=out, qa=qa)
+    p.silu_pair = int(paired)
+    _row(N.ROW_SILU_MUL, p)
     return qa, out
 
 

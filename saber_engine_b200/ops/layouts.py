@@ -190,3 +190,30 @@ def hadamard32_rows(x: torch.Tensor, sign: torch.Tensor) -> torch.Tensor:
     M, K = x.shape
     h = hadamard32_matrix(x.device)
     return ((x.float() * sign.float()).reshape(M, K // 32, 32) @ h).reshape(M, K)
+
+
+# ------------------------------------------------------------------------------- paired gate | up tiles
+def pair_gate_up_int4(tiles: torch.Tensor, scale: torch.Tensor, inter: int):
+    """Packed W4 tiles of a merged [gate rows; up rows] linear (2 * inter rows, inter a multiple of
+    128) -> tiles whose rows 0-127 are gate features [128 t, 128 t + 128) and rows 128-255 the up
+    features of the same indices, so that one CTA of the GEMM owns whole (gate, up) pairs.  A packed
+    tile keeps rows r and r + 128 in the two nibbles of one byte and the swizzle only looks at
+    r & 7, so the regrouping is a nibble shuffle between tiles.  Returns (tiles, scale)."""
+    assert inter % 128 == 0 and tiles.shape[0] * TILE_N == 2 * inter, (tiles.shape, inter)
+    nb = inter // 128
+    blocks = torch.stack([tiles & 0x0F, tiles >> 4], dim=1).reshape(2 * nb, *tiles.shape[1:])   # block b = rows [128 b, 128 b + 128)
+    out = blocks[:nb] | (blocks[nb:] << 4)
+    sc = torch.cat([scale[:inter].reshape(nb, 128), scale[inter:2 * inter].reshape(nb, 128)], dim=1).reshape(-1)
+    return out.contiguous(), sc.contiguous()
+
+
+def unpair_gate_up_int4(tiles: torch.Tensor, scale: torch.Tensor, inter: int):
+    """Inverse of pair_gate_up_int4."""
+    nb = inter // 128
+    assert tiles.shape[0] == nb
+    blocks = torch.cat([tiles & 0x0F, tiles >> 4], dim=0)            # [gate blocks; up blocks] = canonical block order
+    pairs = blocks.reshape(nb, 2, *tiles.shape[1:])
+    out = pairs[:, 0] | (pairs[:, 1] << 4)
+    s2 = scale.reshape(nb, 2, 128)
+    sc = torch.cat([s2[:, 0].reshape(-1), s2[:, 1].reshape(-1)])
+    return out.contiguous(), sc.contiguous()

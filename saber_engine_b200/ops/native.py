@@ -43,7 +43,10 @@ class GemmI8Params(C.Structure):
                 ("counters", P), ("err", P), ("M", I), ("M_pad", I), ("N", I), ("N_pad", I),
                 ("K", I), ("nt", I), ("splits", I), ("w4", I), ("ldo", I), ("dbg_mma", I), ("tp_recv", P * 8), ("tp_flags", P * 8), ("tp_seq_base", P),
                 ("tp_nranks", I), ("tp_rank", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I), ("tp_rpr", I), ("ag_flags", P), ("ag_seq_base", P), ("ag_site", I),
-                ("group_tiles", P), ("group_ntiles", P), ("group_w_stride", U64), ("coop", I), ("mtiles", I), ("dbg", P), ("bias", P), ("res", P), ("epi", I)]
+                ("group_tiles", P), ("group_ntiles", P), ("group_w_stride", U64), ("coop", I), ("mtiles", I), ("dbg", P), ("bias", P), ("res", P), ("epi", I),
+                ("tail_mode", I), ("tail_row_mode", I), ("tail_row", P), ("tail_q", P), ("tail_scale", P), ("tail_M_pad", I),
+                ("tail_sync", P), ("next_w", P), ("next_tiles", I), ("next_splits", I), ("next_KB", I), ("next_kb_per", I),
+                ("next_wbytes", I), ("next_pref", I), ("acc", P), ("acc_tail", P), ("halves", I)]
 
 
 class RowOpParams(C.Structure):
@@ -53,7 +56,8 @@ class RowOpParams(C.Structure):
                 ("tp_seq_base", P), ("err", P), ("tp_nranks", I), ("tp_site", I), ("tp_rows", I), ("tp_ld", I),
                 ("tp_nt", I), ("tp_tiles_n", I), ("m_live", P), ("qfmt", I), ("had_sign", P),
                 ("sp_q", P * MAX_RANKS), ("sp_scale", P * MAX_RANKS), ("sp_flags", P * MAX_RANKS), ("sp_counter", P),
-                ("sp_rpr", I), ("sp_rank", I)]
+                ("sp_rpr", I), ("sp_rank", I), ("res_copy", P), ("silu_pair", I),
+                ("acc", P), ("acc_a_scale", P), ("acc_w_scale", P), ("acc_nt", I), ("acc_tiles_n", I)]
 
 
 class GdnConvParams(C.Structure):
@@ -194,6 +198,10 @@ def _declare(L: C.CDLL) -> None:
         "saber_program_destroy": (None, [P]),
         "saber_program_add_gemm": (I, [P, C.POINTER(GemmI8Params), I, C.c_char_p]),
         "saber_program_add_row": (I, [P, I, C.POINTER(RowOpParams), C.c_char_p]),
+        "saber_program_link_prefetch": (I, [P, I]),
+        "saber_gemm_i8_tail_ok": (I, [C.POINTER(GemmI8Params)]),
+        "saber_set_coop_launch": (None, [I]),
+        "saber_gemm_i8_noalloc_status": (I, [S]),
         "saber_program_add_embed": (I, [P, P, P, P, I, I, I, I, I, C.c_char_p]),
         "saber_program_add_expand": (I, [P, P, P, P, P, I, I, I, C.c_char_p]),
         "saber_program_add_advance": (I, [P, P, U32, C.c_char_p]),
@@ -286,6 +294,10 @@ class Program:
     # ---- op builders -------------------------------------------------------------------------
     def gemm(self, p: GemmI8Params, stages: int = 0, tag: str = "gemm") -> int:
         return self._L.saber_program_add_gemm(self._h, C.byref(p), stages, tag.encode())
+
+    def link_prefetch(self, pref_bytes: int = 96 * 1024) -> int:
+        """Chain the program's GEMMs so that each asks L2 for the next one's leading weight tiles."""
+        return self._L.saber_program_link_prefetch(self._h, int(pref_bytes))
 
     def row(self, mode: int, p: RowOpParams, tag: str = "row") -> int:
         return self._L.saber_program_add_row(self._h, mode, C.byref(p), tag.encode())

@@ -36,6 +36,9 @@ def _np(t: torch.Tensor) -> np.ndarray:
 def _qw_records(name: str, w: Optional[QuantWeight], shard: int):
     if w is None:
         return
+    if getattr(w, "paired", False):      # records keep the canonical row order (gate rows, then up rows)
+        from ..ops.functional import unpair_gate_up
+        w = unpair_gate_up(w)
     if getattr(w, "mx", False):
         # MXFP4: e2m1 codes + block shifts in the GEMM's tile order, and the per-row 2^wref scale
         yield (f"{name}.weight_mxfp4", _np(w.tiles), "u8", (w.N, w.K), PF.LAYOUT_MXFP4_TILE, shard)

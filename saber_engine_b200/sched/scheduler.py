@@ -21,7 +21,7 @@ from . import buckets as B
 from .alloc import Arenas, GdnStateAllocator, OutOfBlocks, PagedKvAllocator
 from .executor import SeqOut, SeqRun
 from .prefix_cache import PrefixCache
-from .width import WidthByBatch
+from .width import WidthByBatch, WidthEma
 
 
 @dataclass
@@ -36,6 +36,15 @@ class SchedulerConfig:
     prefill_pack_seqs: int = 1           # sequences packed in one prefill step
     width_table: Optional[WidthByBatch] = None
     model_name: str = "saber"
+    # mixed steps: while a prompt prefills, the decoding sequences still get a decode launch in the
+    # same step, and the prompt's chunks are capped so that no stream waits for a whole prompt
+    mixed_steps: bool = True
+    mixed_chunk_rows: int = 512
+    width_policy: str = "table"          # "table" (batch -> width) | "ema" (widest recent acceptance of the live sequences)
+    lookup_drafts: bool = False          # sequences without model drafts propose by prompt lookup (n-gram continuation)
+    park_victims: bool = False           # a waiting request that does not fit parks the decoding sequence with most tokens to go
+    mem_valve: Optional[object] = None   # sched.mem_valve.MemValve: demote (drop cached prefixes) -> park -> refuse
+    mem_valve_every: int = 64            # steps between polls
 
 
 @dataclass
@@ -61,6 +70,7 @@ class Sequence:
     t_admit: Optional[float] = None
     n_drafted: int = 0
     n_accepted: int = 0
+    ema: Optional[object] = None          # WidthEma of this sequence (width_policy = "ema")
     prompt_lps: list = field(default_factory=list)   # log-probabilities of prompt tokens 1.., chunk by chunk
 
     @property
@@ -109,6 +119,9 @@ class Scheduler:
         self.park_tier = ParkTier()
         self.parked: dict = {}              # key -> Sequence whose device state lives in the park tier
         self.prompt_store = None            # optional sched.prompt_store.PromptStore (prefixes that survive restarts)
+        self.valve_level = "ok"
+        self.auto_parked: list = []         # keys parked by the scheduler itself (victims), restored when room appears
+        self.counters.update(mixed_steps=0, victims_parked=0, victims_restored=0, lookup_drafts=0, valve_demotions=0)
 
     # ------------------------------------------------------------------------------ Engine trait
     def submit(self, req: EngineRequest) -> Submission:
@@ -120,8 +133,17 @@ class Scheduler:
         problems = req.params.validate(self.ex.vocab, self.cfg.max_ctx, n)
         if req.params.prompt_logprobs is not None and not getattr(self.ex, "supports_prompt_logprobs", True):
             problems.append("prompt_logprobs is not available on this engine (vocabulary-sharded ranks)")
+        vocab = self.ex.vocab
+        top = vocab + (int(getattr(self.ex, "image_rows", 0)) if req.mm is not None else 0)
+        bad = next((t for t in req.prompt_token_ids if not isinstance(t, int) or isinstance(t, bool) or t < 0 or t >= top), None)
+        if bad is not None:
+            problems.append(f"prompt token id {bad!r} is outside the vocabulary [0, {vocab})")
         if problems:
             raise EngineRefused("; ".join(problems), 400)
+        if self.valve_level == "refuse":
+            with self._lock:
+                self.counters["requests_refused"] += 1
+            raise EngineRefused("host memory is exhausted: no new requests for now", 503)
         with self._lock:
             if len(self.waiting) >= self.cfg.max_waiting:
                 self.counters["requests_refused"] += 1
@@ -173,6 +195,8 @@ class Scheduler:
                 self.prefix.evict_for_blocks(need)          # cached pages yield to live requests
                 hit = None if mm else self.prefix.lookup(s.prompt)   # the entry itself may have been evicted
                 shared = list(hit.blocks) if hit else []
+                if not self.arenas.can_admit(total, len(shared)) and self.cfg.park_victims and self._park_victim():
+                    continue                                # a victim left the device: try this request again
                 if not self.arenas.can_admit(total, len(shared)):
                     if not self.running:                    # can never fit
                         self.waiting.popleft()
@@ -186,7 +210,7 @@ class Scheduler:
             s.t_admit = time.monotonic()
             start = 0
             stored = None
-            if not hit and not mm and self.prompt_store is not None and hasattr(self.ex, "import_session"):
+            if not hit and not mm and self.prompt_store is not None and self._can_park():
                 stored = self.prompt_store.get(s.prompt)     # verified before anything reaches the device
             if hit:
                 self.ex.restore_state(s.slot, hit.snapshot)
@@ -205,94 +229,181 @@ class Scheduler:
             s.chunks = deque(B.cut_prompt(len(s.prompt), start, self.ex.prefill_rungs, cuts))
             self.running.append(s)
 
-    def _plan(self):
-        """Returns ("prefill", [(seq, pos, n)]) | ("decode", seqs, width, batch) | None."""
+    def _can_park(self) -> bool:
+        return bool(getattr(self.ex, "supports_parking", hasattr(self.ex, "export_session")))
+
+    def _park_victim(self) -> bool:
+        """Parks the decoding sequence with the most tokens still to generate (called under both locks)."""
+        if not self._can_park():
+            return False
+        cands = [x for x in self.running if not x.prefilling and not x.finished and x.output]
+        if not cands:
+            return False
+        v = max(cands, key=lambda x: x.req.params.max_tokens - len(x.output))
+        try:
+            key = self._park_locked(v)
+        except Exception:
+            return False
+        self.auto_parked.append(key)
+        self.counters["victims_parked"] += 1
+        return True
+
+    def _restore_victims(self) -> None:
+        """Brings scheduler-parked sequences back when nobody waits and there is room again."""
+        while self.auto_parked and not self.waiting and len(self.running) < self.cfg.max_seqs:
+            key = self.auto_parked[0]
+            s = self.parked.get(key)
+            if s is None:
+                self.auto_parked.pop(0)
+                continue
+            total = len(s.prompt) + s.req.params.max_tokens + max(self.ex.decode_widths)
+            if not self.arenas.can_admit(total, 0):
+                return
+            self.auto_parked.pop(0)
+            self._restore_locked(key)
+            self.counters["victims_restored"] += 1
+
+    def _poll_valve(self) -> None:
+        v = self.cfg.mem_valve
+        if v is None or self.counters["steps"] % max(1, self.cfg.mem_valve_every):
+            return
+        level = v.poll()
+        self.valve_level = level
+        if level in ("demote", "park", "refuse"):
+            dropped = self.prefix.evict_for_blocks(1 << 30)      # cached prefixes (pages + host snapshots) go first
+            self.counters["valve_demotions"] += int(bool(dropped) or 0)
+        if level in ("park", "refuse") and len(self.running) > 1:
+            self._park_victim()
+
+    def _plan(self) -> list:
+        """The step's phases, in launch order: ("prefill", [(seq, pos, n)]) and / or
+        ("decode", seqs, width, batch).  With mixed steps a prefill chunk (capped) and the decode
+        launch of the other sequences share the step; without, prefill goes first and alone."""
+        phases = []
         pre = [s for s in self.running if s.prefilling]
+        dec = [s for s in self.running if not s.finished and not s.prefilling]
+        mixed = bool(pre and dec and self.cfg.mixed_steps)
         if pre:
             picks, rows = [], 0
             top = max(self.ex.prefill_rungs)
+            cap = min(top, self.cfg.mixed_chunk_rows) if mixed else top
             for s in pre[: max(1, self.cfg.prefill_pack_seqs)]:
                 pos, n = s.chunks[0]
-                if picks and rows + n > top:
+                if n > cap:                       # a capped chunk: the rest stays at the head of the queue
+                    s.chunks[0] = (pos + cap, n - cap)
+                    s.chunks.appendleft((pos, cap))
+                    n = cap
+                if picks and rows + n > cap:
                     break
                 picks.append((s, pos, n))
                 rows += n
-            return ("prefill", picks)
-        dec = [s for s in self.running if not s.finished]
-        if not dec:
-            return None
-        batch = B.select_batch(len(dec), self.ex.decode_batches)
-        width = self.width_table.width_for(len(dec))
-        return ("decode", dec, width, batch)
+            phases.append(("prefill", picks))
+            if not mixed:
+                return phases
+        if dec:
+            batch = B.select_batch(len(dec), self.ex.decode_batches)
+            if self.cfg.width_policy == "ema":
+                captured = self.width_table.captured
+                width = max(s.ema.width(captured) if s.ema is not None else max(captured) for s in dec)
+            else:
+                width = self.width_table.width_for(len(dec))
+            phases.append(("decode", dec, width, batch))
+        return phases
+
+    def _launch(self, phase):
+        if phase[0] == "prefill":
+            runs = [SeqRun(s.seq_id, s.prompt[pos:pos + n], pos, s.slot, 0, s.blocks, uid=s.seq_id,
+                           last_chunk=(pos + n == len(s.prompt)),
+                           temperature=s.req.params.temperature, want_seam=self._wants_seam(s),
+                           rope_pos=(None if s.req.mm is None else
+                                     [list(ax[pos:pos + n]) for ax in s.req.mm["rope_pos"]]),
+                           prompt_lp=s.req.params.prompt_logprobs,
+                           next_token=(s.prompt[pos + n] if pos + n < len(s.prompt) else -1),
+                           **(self._device_draw(s, 1) if pos + n == len(s.prompt) else {}))
+                    for s, pos, n in phase[1]]
+            return self.ex.prefill(runs)
+        _, dec, width, batch = phase
+        runs = []
+        for s in dec:
+            drafts = s.drafts
+            if self.cfg.lookup_drafts and width > 1 and not any(drafts):
+                from ..runtime.lookup import lookup_draft
+                drafts = lookup_draft(s.prompt + s.output, width - 1)
+                self.counters["lookup_drafts"] += 1
+            s.drafts = (list(drafts) + [0] * width)[: width - 1]
+            runs.append(SeqRun(s.seq_id, [s.output[-1]] + s.drafts, s.pos, s.slot, s.shift, s.blocks,
+                               uid=s.seq_id, step_no=s.step_no, temperature=s.req.params.temperature,
+                               want_seam=self._wants_seam(s),
+                               rope_delta=(0 if s.req.mm is None else int(s.req.mm.get("rope_delta", 0))),
+                               **self._device_draw(s, width)))
+        return self.ex.decode(runs, width)
 
     # ------------------------------------------------------------------------------ the step
     def step(self) -> bool:
-        """One engine step. Returns False when there was nothing to do."""
+        """One engine step. Returns False when there was nothing to do.
+
+        Plan, Launch and Accept all run under the device lock: parking and restoring from another
+        thread (which take the same lock) can therefore never slip between a plan and its launch.
+        Whatever goes wrong in any phase ends in the fatal law: every request learns the reason."""
         t0 = time.monotonic()
-        with self.trace.phase("Plan"), self._lock:
-            self._drain_aborted()
-            self._admit_waiting()
-            plan = self._plan()
-        if plan is None:
-            return False
         try:
-          with self.trace.phase("Launch"), self._device_lock:
-                if plan[0] == "prefill":
-                    runs = [SeqRun(s.seq_id, s.prompt[pos:pos + n], pos, s.slot, 0, s.blocks, uid=s.seq_id,
-                                   last_chunk=(pos + n == len(s.prompt)),
-                                   temperature=s.req.params.temperature, want_seam=self._wants_seam(s),
-                                   rope_pos=(None if s.req.mm is None else
-                                             [list(ax[pos:pos + n]) for ax in s.req.mm["rope_pos"]]),
-                                   prompt_lp=s.req.params.prompt_logprobs,
-                                   next_token=(s.prompt[pos + n] if pos + n < len(s.prompt) else -1),
-                                   **(self._device_draw(s, 1) if pos + n == len(s.prompt) else {}))
-                            for s, pos, n in plan[1]]
-                    outs = self.ex.prefill(runs)
-                else:
-                    _, dec, width, batch = plan
-                    runs = []
-                    for s in dec:
-                        drafts = (s.drafts + [0] * width)[: width - 1]
-                        runs.append(SeqRun(s.seq_id, [s.output[-1]] + drafts, s.pos, s.slot, s.shift, s.blocks,
-                                           uid=s.seq_id, step_no=s.step_no, temperature=s.req.params.temperature,
-                                           want_seam=self._wants_seam(s),
-                                           rope_delta=(0 if s.req.mm is None else int(s.req.mm.get("rope_delta", 0))),
-                                           **self._device_draw(s, width)))
-                    outs = self.ex.decode(runs, width)
-        except Exception as exc:       # the executor failed: every request learns why (fatal law)
-            self.set_fatal(f"executor failed: {exc!r}")
+            with self._device_lock:
+                with self.trace.phase("Plan"), self._lock:
+                    self._drain_aborted()
+                    self._poll_valve()
+                    self._restore_victims()
+                    self._admit_waiting()
+                    phases = self._plan()
+                if not phases:
+                    return False
+                for phase in phases:
+                    with self.trace.phase("Launch"):
+                        outs = self._launch(phase)
+                    dt = time.monotonic() - t0
+                    with self.trace.phase("Accept"), self._lock:
+                        if phase[0] == "prefill":
+                            self._commit_prefill(phase[1], outs, dt)
+                        else:
+                            self._commit_decode(phase[1], phase[2], phase[3], outs, dt)
+                with self._lock:
+                    self.counters["steps"] += 1
+                    self.counters["mixed_steps"] += int(len(phases) > 1)
+                    self.last_step_s = dt
+        except Exception as exc:       # every request learns why (fatal law); the loop ends
+            self.set_fatal(f"step failed: {exc!r}")
             raise
-        dt = time.monotonic() - t0
-        with self.trace.phase("Accept"), self._lock:
-            if plan[0] == "prefill":
-                self._commit_prefill(plan[1], outs, dt)
-            else:
-                self._commit_decode(plan[1], plan[2], plan[3], outs, dt)
-            self.counters["steps"] += 1
-            self.last_step_s = dt
         self.trace.end_step()
         if self.on_step:
-            self.on_step({"kind": plan[0], "seconds": dt, "live": len(plan[1])})
+            for phase in phases:
+                self.on_step({"kind": phase[0], "seconds": dt, "live": len(phase[1])})
         return True
 
     # ------------------------------------------------------------------------------ parking / warm prompts
     def park(self, seq_id: int) -> str:
         """Moves a decoding sequence off the device: its KV pages and state slot become one verified
         image in the park tier, its blocks and slot are released.  Returns the key to restore with."""
+        if not self._can_park():
+            raise EngineRefused("session parking is not available on this engine", 501)
         with self._device_lock, self._lock:
             s = next((x for x in self.running if x.seq_id == seq_id), None)
             if s is None or s.prefilling or s.finished:
                 raise EngineRefused(f"sequence {seq_id} is not a decoding sequence", 409)
-            from .park import ParkImage
-            header, payload = self.ex.export_session(s.slot, s.blocks, s.pos)
-            key = f"seq{seq_id}"
-            header.update(seq_id=seq_id, pos=s.pos, shift=s.shift, step_no=s.step_no)
-            self.park_tier.put(key, ParkImage.build(header, payload))
-            self.running.remove(s)
-            self.arenas.release(s.blocks, s.slot)
-            s.blocks, s.slot = [], 0
-            self.parked[key] = s
-            return key
+            try:
+                return self._park_locked(s)
+            except NotImplementedError as exc:
+                raise EngineRefused(f"session parking is not available on this engine: {exc}", 501)
+
+    def _park_locked(self, s: Sequence) -> str:
+        from .park import ParkImage
+        header, payload = self.ex.export_session(s.slot, s.blocks, s.pos)
+        key = f"seq{s.seq_id}"
+        header.update(seq_id=s.seq_id, pos=s.pos, shift=s.shift, step_no=s.step_no)
+        self.park_tier.put(key, ParkImage.build(header, payload))
+        self.running.remove(s)
+        self.arenas.release(s.blocks, s.slot)
+        s.blocks, s.slot = [], 0
+        self.parked[key] = s
+        return key
 
     def restore(self, key: str) -> int:
         """Brings a parked sequence back (fresh blocks and slot, bytes verified first)."""
@@ -303,13 +414,31 @@ class Scheduler:
             total = len(s.prompt) + s.req.params.max_tokens + max(self.ex.decode_widths)
             if len(self.running) >= self.cfg.max_seqs or not self.arenas.can_admit(total, 0):
                 raise EngineRefused("no room to restore the session now", 503)
-            img = self.park_tier.take(key)            # raises ParkError on a corrupt image: nothing reached the device
-            s.blocks, s.slot = self.arenas.admit(total, [])
-            self.ex.import_session(s.slot, s.blocks, img.header, img.payload)
-            del self.parked[key]
-            self.running.append(s)
-            self._wake.notify_all()
-            return s.seq_id
+            from .park import ParkError
+            try:
+                sid = self._restore_locked(key)
+            except ParkError as exc:       # the image is gone or corrupt: the session is lost, say so once
+                self.parked.pop(key, None)
+                s.finished = True
+                self._emit(s, StepEvent(s.seq_id, [], True, "error", error=f"parked session lost: {exc}",
+                                        prompt_tokens=len(s.prompt)))
+                raise EngineRefused(f"parked session {key!r} cannot be restored: {exc}", 410)
+            except NotImplementedError as exc:
+                raise EngineRefused(f"session parking is not available on this engine: {exc}", 501)
+            if key in self.auto_parked:
+                self.auto_parked.remove(key)
+            return sid
+
+    def _restore_locked(self, key: str) -> int:
+        s = self.parked[key]
+        total = len(s.prompt) + s.req.params.max_tokens + max(self.ex.decode_widths)
+        img = self.park_tier.take(key)            # raises ParkError on a corrupt image: nothing reached the device
+        s.blocks, s.slot = self.arenas.admit(total, [])
+        self.ex.import_session(s.slot, s.blocks, img.header, img.payload)
+        del self.parked[key]
+        self.running.append(s)
+        self._wake.notify_all()
+        return s.seq_id
 
     def warm(self, prompts: list) -> int:
         """Warm prompts: run each prompt once (one generated token) so that its pages and state
@@ -331,7 +460,7 @@ class Scheduler:
                 snap = self.ex.snapshot_state(s.slot)
                 self.prefix.insert(s.prompt, s.pos, s.blocks, snap, self.ex.snapshot_bytes())
                 st = self.prompt_store
-                if st is not None and hasattr(self.ex, "export_session") and not st.has(s.prompt, s.pos):
+                if st is not None and self._can_park() and not st.has(s.prompt, s.pos):
                     from .park import ParkImage
                     header, payload = self.ex.export_session(s.slot, s.blocks, s.pos)
                     header["n_tokens"] = s.pos
@@ -361,6 +490,10 @@ class Scheduler:
                 self.accepted_per_pos[k] += 1
             s.n_drafted += width - 1
             s.n_accepted += n - 1
+            if self.cfg.width_policy == "ema":
+                if s.ema is None:
+                    s.ema = WidthEma()
+                s.ema.update(n - 1)
             s.pos += n
             s.shift = n
             s.step_no += 1
@@ -494,7 +627,9 @@ class Scheduler:
                         return
                 try:
                     self.step()
-                except Exception:
+                except Exception as exc:        # step() has already told every request (fatal law)
+                    if not self.fatal:
+                        self.set_fatal(f"step loop failed: {exc!r}")
                     return
         self._thread = threading.Thread(target=loop, name="saber-step-loop", daemon=True)
         self._thread.start()

@@ -104,3 +104,23 @@ def test_batched_equals_solo(model):
             shift[j] = 1
     assert outs == solo
     assert b.captured and b.program.declared_launches == b.n_launches
+
+
+def test_fused_launches_equal_one_launch_per_op(model):
+    """The fused decode chain (row tails, silu * mul + quant in the gate | up epilogue, weight
+    prefetch) commits the same tokens and leaves the same logits as one launch per op, with fewer launches."""
+    from saber_engine_b200.models.weights import random_init
+    plain = HybridModel(model.cfg, device="cuda", max_seqs=4, max_ctx=512, max_width=5, seed=1, fuse=False)
+    assert model.fuse and not plain.fuse
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, model.cfg.vocab, (41,), generator=g).tolist()
+    outs = []
+    for mdl in (model, plain):
+        r = _prefill(mdl, prompt, 1, _blocks(0))
+        toks, _ = _decode(mdl, prompt, r.tokens[0][0], r.drafts[0], 1, _blocks(0), 16, 5)
+        outs.append((r.tokens, toks, mdl.buckets[("decode", 1, 5)].logits.clone()))
+    assert outs[0][0] == outs[1][0] and outs[0][1] == outs[1][1]
+    assert torch.equal(outs[0][2], outs[1][2])
+    fused_n = model.buckets[("decode", 1, 5)].n_launches
+    plain_n = plain.buckets[("decode", 1, 5)].n_launches
+    assert fused_n < plain_n, (fused_n, plain_n)
