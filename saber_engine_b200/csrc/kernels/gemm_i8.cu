@@ -67,11 +67,11 @@ __device__ __forceinline__ float gelu_f(float x, bool erf_form) {
 // thread per CTA calls, after a CTA-level barrier that ordered the other threads' writes before it.
 // `ctr` is zero when the kernel starts.  The wait is bounded like every other wait here: when it
 // runs out the status word is set and the caller goes on (its results are then garbage, the error
-// is what the host reads).  grid_depart is the second round of arrivals: it returns true in the
-// ONE caller that leaves last, which must put the counter back to zero.
+// is what the host reads).  grid_depart is the second round of arrivals.
 __device__ __forceinline__ bool grid_arrive_wait(uint32_t* ctr, uint32_t n_ctas, uint32_t* err) {
   __threadfence();
-  atomicAdd(ctr, 1u);
+  // (inc wraps to zero on the 2 n-th increment: n arrivals, then n departures, re-arm the word)
+  asm volatile("red.global.inc.u32 [%0], %1;" ::"l"(ctr), "r"(2u * n_ctas - 1u) : "memory");
   const long long t0 = clock64();
   for (uint32_t polls = 0;; ++polls) {
     uint32_t seen;
@@ -83,8 +83,9 @@ __device__ __forceinline__ bool grid_arrive_wait(uint32_t* ctr, uint32_t n_ctas,
     }
   }
 }
-__device__ __forceinline__ bool grid_depart(uint32_t* ctr, uint32_t n_ctas) {
-  return atomicAdd(ctr, 1u) == 2u * n_ctas - 1u;
+// Second round of arrivals: fire and forget, the last one wraps the counter back to zero.
+__device__ __forceinline__ void grid_depart(uint32_t* ctr, uint32_t n_ctas) {
+  asm volatile("red.global.inc.u32 [%0], %1;" ::"l"(ctr), "r"(2u * n_ctas - 1u) : "memory");
 }
 
 // kLean: the grouped (mixture-of-experts) instantiation -- no split-K and no tensor-parallel code,
@@ -177,7 +178,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int u = 0; u < nub; ++u) {
-      mbar_init(bar_ready + 8 * u, 8);  // one arrival per transform warp
+      mbar_init(bar_ready + 8 * u, 4);  // one arrival per warp of the transform group that owns the block
       mbar_init(bar_ufree + 8 * u, 1);
     }
     mbar_init(bar_acc, 1);
@@ -326,8 +327,20 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         a_addr += abytes;
         if (++s == stages) { s = 0; ph ^= 1u; a_addr = a_smem; }
       }
-      if (ok) mma_commit(bar_acc);
+      mma_commit(bar_acc);
+      // Unwinding after a wait that ran out: the MMAs issued so far must have retired before the
+      // CTA gives its tensor memory back (the status word already tells the host the result is void).
+      if (!ok) mbar_wait(bar_acc, 0, nullptr, 0);
       SABER_STAMP(6);
+    } else if (!kLean && !kBf && p.tail_mode == 1 && blockIdx.x == 0 && blockIdx.y == 0) {
+      // in-tile silu * mul + quant: the row maxima start from zero; this launch's first CTA cleans
+      // them here (the previous user finished with its whole grid) and raises the "clean" flag
+      pdl_wait();
+      for (int i = lane - 1; i < p.tail_M_pad; i += 31) p.tail_sync[64 + static_cast<size_t>(i) * 32] = 0u;
+      __threadfence();
+      __syncwarp(0xFFFFFFFEu);
+      if (lane == 1)
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.tail_sync + kTailFlagsAt + 255), "r"(1u) : "memory");
     } else if (!kLean && !kBf && p.tail_mode == 3 && split == 0) {
       // Row tail on the accumulator blocks: nobody re-zeroes a block after reading it (16-byte
       // zero stores from one CTA per row share sectors across CTAs and are ruinously slow), so the
@@ -362,30 +375,44 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
       }
     }
     if (widen) {
+      // The two groups of four warps take the k-blocks in turn (group g: blocks g, g + 2, ...).  A
+      // warp's chain for one block -- read the packed stage, wait for a free operand buffer, write,
+      // proxy fence, arrive -- is long and mostly latency; with the groups alternating, one
+      // group's fence and arrival overlap the other group's reads and writes.
+      // Phase bookkeeping: a parity wait is only unambiguous for a waiter that has seen the phase
+      // before it, so BOTH groups pass through every stage's "full" barrier in block order (the
+      // wait for the other group's block returns at once in steady state); the operand-buffer
+      // barriers are only waited on by the block's owner, which is safe because the MMAs retire in
+      // order (the owner's previous wait already implies the phase in between).
       int s = 0, u = 0;
       uint32_t ph = 0, ufree_ph = 1;
       for (int it = 0; it < nkb; ++it) {
-        if (!mbar_wait(bar_full + 8 * s, ph, p.err, kErrWaitFull)) { ok = false; break; }
+        const int s_now = s, u_now = u;
+        const uint32_t ph_now = ph, ufree_now = ufree_ph;
+        if (++s == stages) { s = 0; ph ^= 1u; }
+        if (++u == nub) { u = 0; ufree_ph ^= 1u; }
+        if (!mbar_wait(bar_full + 8 * s_now, ph_now, p.err, kErrWaitFull)) { ok = false; break; }
+        if ((it & 1) != tgroup) continue;
         if (it == 0 && tid8 == 0) SABER_STAMP(3);
-        const uint32_t src = w_smem + s * wbytes;
-        const uint32_t dst = u_smem + u * kTileBytes;
-        uint32_t v[4][4];
+        const uint32_t src = w_smem + s_now * wbytes;
+        const uint32_t dst = u_smem + u_now * kTileBytes;
+        uint32_t v[8][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t off = static_cast<uint32_t>(i * 256 + tid8) * 16u;
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t off = static_cast<uint32_t>(i * 128 + tid_t) * 16u;
           asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                        : "=r"(v[i][0]), "=r"(v[i][1]), "=r"(v[i][2]), "=r"(v[i][3])
                        : "r"(src + off));
         }
-        if (!mbar_wait(bar_ufree + 8 * u, ufree_ph, p.err, kErrWaitEmpty)) { ok = false; break; }
+        if (!mbar_wait(bar_ufree + 8 * u_now, ufree_now, p.err, kErrWaitEmpty)) { ok = false; break; }
         if (mx) {
           // MXFP4: a 16-bit half of a packed word = four e2m1 codes of one row = the selector of a
           // byte permute over the eight e4m3 magnitudes, shifted down by the block's exponent
           // distance k to the row's largest block (entries whose exponent field would reach 0
           // are flushed); the sign bits come from a second permute over {0x00, 0x80}.
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint32_t ci = static_cast<uint32_t>(i * 256 + tid8);
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t ci = static_cast<uint32_t>(i * 128 + tid_t);
             const uint32_t r = ci >> 3, lc = (ci & 7u) ^ (r & 7u);
             uint32_t klo, khi;
             asm volatile("ld.shared.u8 %0, [%1];" : "=r"(klo) : "r"(src + 16384u + r * 4u + (lc >> 1)));
@@ -417,8 +444,8 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         } else if (halves == 2) {
           const uint32_t sh = half ? 0u : 4u;      // this CTA's 128 rows: the high or the low nibbles
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint32_t off = static_cast<uint32_t>(i * 256 + tid8) * 16u;
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t off = static_cast<uint32_t>(i * 128 + tid_t) * 16u;
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + off),
                          "r"((v[i][0] << sh) & 0xF0F0F0F0u), "r"((v[i][1] << sh) & 0xF0F0F0F0u),
                          "r"((v[i][2] << sh) & 0xF0F0F0F0u), "r"((v[i][3] << sh) & 0xF0F0F0F0u)
@@ -426,8 +453,8 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
           }
         } else
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint32_t off = static_cast<uint32_t>(i * 256 + tid8) * 16u;
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t off = static_cast<uint32_t>(i * 128 + tid_t) * 16u;
           asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst + off),
                        "r"((v[i][0] << 4) & 0xF0F0F0F0u), "r"((v[i][1] << 4) & 0xF0F0F0F0u),
                        "r"((v[i][2] << 4) & 0xF0F0F0F0u), "r"((v[i][3] << 4) & 0xF0F0F0F0u)
@@ -439,10 +466,8 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_ready + 8 * u);
+        if (lane == 0) mbar_arrive(bar_ready + 8 * u_now);
         if (it == 0 && tid8 == 0) SABER_STAMP(4);
-        if (++s == stages) { s = 0; ph ^= 1u; }
-        if (++u == nub) { u = 0; ufree_ph ^= 1u; }
       }
     }
     // Two token tiles per CTA: BOTH transform groups run the epilogue, one accumulator each (either
@@ -450,17 +475,54 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
     // own named barrier.  Otherwise only the first group does.
     const bool pair = !kLean && mt2 == 2;
     const int ebar = 1 + (pair ? tgroup : 0);
-    if (tgroup == 0 || pair) {
+    // wide forms: both groups read the accumulator out (half of the columns each: either group's
+    // four warps cover the four TMEM lane quarters) -- the in-tile silu * mul + quant and the
+    // staging of split-K partial sums for the bulk reduction
+    const bool bulk = !kLean && !kBf && !mx && p.splits > 1 && p.acc != nullptr;
+    const bool smq = !kLean && !kBf && p.tail_mode == 1;
+    const bool wide = bulk || smq;
+    if (tgroup == 0 || pair || wide) {
       // the epilogue warps decide TOGETHER whether to run the epilogue: the named barriers
       // below have no time limit, so no warp may skip one that the others enter
       if (ok) ok = mbar_wait(bar_acc, 0, p.err, kErrWaitAcc);
       if (!ok) abort_s = 1u;
-      if (pair) named_bar_sync(3, 256); else named_bar_sync(1, 128);  // also publishes w_scale_s
+      if (pair || wide) named_bar_sync(3, 256); else named_bar_sync(1, 128);  // also publishes w_scale_s
       ok = abort_s == 0u;
     } else {
       ok = false;  // only the first group (TMEM lane quarters 2,3,0,1) is the epilogue
     }
     if constexpr (!kLean && !kBf) {
+      if (bulk) {
+        // split-K partial sums: the live rows go to shared memory as [c4][nt rows][4 ints] (a warp's
+        // 32 rows store 512 contiguous bytes), rows between the live count and nt as zeros
+        if (ok) {
+          tc_fence_after_sync();
+          const int mt = min(p.nt, p.M - m0);
+          const int row = q4 * 32 + lane;
+          const uint32_t stage_s = widen ? u_smem : w_smem;     // idle by now, at least 128 KiB in a row
+          const uint32_t t_lane = tmem_d + (static_cast<uint32_t>(q4 * 32) << 16);
+          if (q4 * 32 < p.nt) {
+            const bool live = row < mt;
+            for (int c = tgroup * 128; c < tgroup * 128 + 128; c += 32) {
+              uint32_t r[32];
+              tmem_ld32(t_lane + c, r);
+              tmem_ld_wait();
+              if (row < p.nt) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const uint32_t a = stage_s + (static_cast<uint32_t>((c >> 2) + j) * p.nt + row) * 16u;
+                  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(live ? r[4 * j] : 0u),
+                               "r"(live ? r[4 * j + 1] : 0u), "r"(live ? r[4 * j + 2] : 0u), "r"(live ? r[4 * j + 3] : 0u)
+                               : "memory");
+                }
+              }
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(3, 256);
+        if (tgroup == 1) ok = false;       // the first group goes on alone
+      }
       if (p.tail_mode == 1) {
         // silu(gate) * up and the per-token int8 quantisation inside the tile (paired weight tiles:
         // columns c and 128 + c of the accumulator are the gate and up feature of the same index).
@@ -474,14 +536,14 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         const uint32_t stage_s = widen ? u_smem : w_smem;
         const int mt = min(p.nt, p.M - m0);
         pdl_wait();
-        if (tgroup == 0 && ok) {
+        if (ok) {
           tc_fence_after_sync();
           const int row = q4 * 32 + lane;
           if (q4 * 32 < mt) {
             const bool live = row < mt;
             const float asc = live ? p.a_scale[m0 + row] : 0.f;
             const uint32_t t_lane = tmem_d + (static_cast<uint32_t>(q4 * 32) << 16);
-            for (int c = 0; c < 256; c += 32) {
+            for (int c = tgroup * 128; c < tgroup * 128 + 128; c += 32) {
               uint32_t r[32];
               tmem_ld32(t_lane + c, r);
               tmem_ld_wait();
@@ -504,12 +566,25 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
             }
           }
         }
+        uint32_t* rowmax = p.tail_sync + 64;           // one 128-byte line per row
+        if (tid8 == 0) {       // the row maxima were put back to zero by this launch's first CTA (see the MMA warp)
+          const uint32_t* flag = p.tail_sync + kTailFlagsAt + 255;
+          const long long t0 = clock64();
+          for (uint32_t polls = 0;; ++polls) {
+            uint32_t v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (v != 0u) break;
+            if ((polls & 1023u) == 1023u && clock64() - t0 > kWaitLimitCycles) {
+              atomicCAS(p.err, 0u, static_cast<uint32_t>(kErrWaitSplit));
+              break;
+            }
+          }
+        }
         named_bar_sync(2, 256);
         const bool go = abort_s == 0u;
         const int w8 = warp - 2;                       // 0..7
         constexpr int kRowsPerWarp = 16;               // nt <= 128
         uint32_t act[kRowsPerWarp][2];                 // four products per row as bf16 pairs
-        uint32_t* rowmax = p.tail_sync + 64;           // one 128-byte line per row
         if (go) {
 #pragma unroll
           for (int i = 0; i < kRowsPerWarp; ++i) {
@@ -561,15 +636,10 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
           *reinterpret_cast<uint32_t*>(dst + ((((lane >> 2) ^ (mm & 7)) & 7) << 4) + ((lane & 3) << 2)) = word;
           if (tile_n == 0 && lane == 0) p.tail_scale[mm] = am / 127.f;
         }
-        // second round of arrivals, off the critical path: the CTA that leaves last re-arms the words
-        named_bar_sync(2, 256);
-        if (tid8 == 0) is_last_s = grid_depart(p.tail_sync, n_ctas) ? 1u : 0u;
-        named_bar_sync(2, 256);
-        if (is_last_s) {
-          for (int i = tid8; i < p.tail_M_pad; i += 256) rowmax[static_cast<size_t>(i) * 32] = 0u;
-          __threadfence();
-          named_bar_sync(2, 256);
-          if (tid8 == 0) p.tail_sync[0] = 0u;
+        // second round of arrivals (fire and forget); the last CTA of the grid lowers the flag
+        if (tid8 == 0) {
+          if (blockIdx.x == gridDim.x - 1 && blockIdx.y == gridDim.y - 1) p.tail_sync[kTailFlagsAt + 255] = 0u;
+          grid_depart(p.tail_sync, n_ctas);
         }
         ok = false;        // the generic epilogue below is not for this launch
       }
@@ -716,30 +786,11 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         // reduction (TMA add.s32) into the tile's accumulator block in L2 -- zero when the kernel
         // starts, re-zeroed by whoever reads it out.  The block is [c4][nt rows][4 ints].  MXFP4
         // partials are fp32 and keep the private copies (their sum must not depend on the arrival order).
-        const bool bulk = !mx && !bf && p.acc != nullptr;
         const int rstride = bulk ? p.nt : 128;   // rows per four-column group of a block
         int32_t* wblk = p.ws + (static_cast<size_t>(split) * (gridDim.x * gridDim.y) + tile_lin) * blk_stride;
         int32_t* ablk = bulk ? p.acc + static_cast<size_t>(tile_lin) * p.nt * 256u : nullptr;
         if (bulk) {
-          const uint32_t stage_s = widen ? u_smem : w_smem;     // idle by now, at least 128 KiB in a row
-          if (q4 * 32 < p.nt) {
-            for (int c = 0; c < 256; c += 32) {
-              uint32_t r[32];
-              tmem_ld32(t_lane + c, r);
-              tmem_ld_wait();
-              if (row < p.nt) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  const uint32_t a = stage_s + (static_cast<uint32_t>((c >> 2) + j) * p.nt + row) * 16u;
-                  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(live ? r[4 * j] : 0u),
-                               "r"(live ? r[4 * j + 1] : 0u), "r"(live ? r[4 * j + 2] : 0u), "r"(live ? r[4 * j + 3] : 0u)
-                               : "memory");
-                }
-              }
-            }
-          }
-          fence_proxy_async_smem();
-          named_bar_sync(1, 128);
+          const uint32_t stage_s = widen ? u_smem : w_smem;     // staged by both groups above
           if (tid_t == 0) {
             if (p.tail_mode == 3) {            // the block must have been cleaned by this launch's first split
               const uint32_t* flag = p.tail_sync + kTailFlagsAt + tile_lin;
@@ -971,7 +1022,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         }
       }
       if (threadIdx.x == 0) SABER_STAMP(14);
-      if (threadIdx.x == 0 && grid_depart(p.tail_sync, n_ctas)) p.tail_sync[0] = 0u;
+      if (threadIdx.x == 0) grid_depart(p.tail_sync, n_ctas);
     }
   }
 #undef SABER_STAMP

@@ -72,3 +72,26 @@ def test_gemm_two_token_tiles_per_cta():
     _case(700, 256, 512, 4, splits=1, seed=13, mtiles=2)         # M_pad = 768: three pairs, the last one half empty
     _case(512, 512, 1024, 8, splits=1, seed=14, mtiles=2)        # int8 weights keep one tile per CTA
     _case(2048, 40960, 256, 4, splits=1, seed=15)                # 160 x 16 single-tile CTAs: the launcher pairs by itself
+
+
+def test_gemm_back_to_back_launches_keep_their_pipeline_phases():
+    """Deep K loops in every ring configuration (odd and even stage counts, two and three operand
+    buffers), launched back to back: the two transform groups take the k-blocks in turn and must
+    never read a stage before its copy has landed."""
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(21)
+    for (M, Nn, K, mt) in [(512, 512, 17408, 2), (128, 768, 8192, 0), (64, 512, 17408, 0), (80, 256, 5120, 0)]:
+        w = torch.randn(Nn, K, generator=g) * 0.02
+        x = torch.randn(M, K, generator=g)
+        wq, ws = L.quantize_weight_rows(w, 4)
+        aq, asc = L.quantize_act_rows(x)
+        ref = R.gemm_i8(wq, ws, aq, asc).float()
+        qw = F.QuantWeight.from_int(wq, ws, 4, dev)
+        m_pad = L.padded_rows(M)
+        qa = F.QuantAct(L.tile_act_int8(aq, m_pad).to(dev), torch.cat([asc, torch.zeros(m_pad - M)]).to(dev), M, K)
+        outs = [F.gemm_i8(qw, qa, splits=1, mtiles=mt) for _ in range(20)]
+        torch.cuda.synchronize()
+        F.scratch(dev).check()
+        tol = 1e-2 * ref.abs().max().item() + 1e-6
+        for o in outs:
+            assert (o.float().cpu() - ref).abs().max().item() <= tol
