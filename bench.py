@@ -100,6 +100,7 @@ def main() -> int:
     ap.add_argument("--width", type=int, default=8)
     ap.add_argument("--accept-p", type=float, default=0.75)
     ap.add_argument("--rung", type=int, default=2048)
+    ap.add_argument("--max-ctx", type=int, default=0, help="context the KV pool and block tables are sized for (0: the model's 262,144)")
     ap.add_argument("--pdl", type=int, default=-1, help="programmatic dependent launch: 0 off, 1 all kernels, 2 GEMMs only (A/B)")
     ap.add_argument("--no-single", action="store_true", help="skip the single-stream side measurement")
     args = ap.parse_args()

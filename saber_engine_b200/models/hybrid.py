@@ -100,6 +100,8 @@ class Bucket:
     n_launches: int = 0
     logits: Optional[torch.Tensor] = None
     keep: list = field(default_factory=list)
+    bt_rows: dict = field(default_factory=dict)    # row j -> (blocks_key, n blocks) of the block-table row the device holds
+    last_h2d_bytes: int = 0                        # index-table bytes the last step copied to the device
     arenas: list = field(default_factory=list)     # pure activation buffers: written before read in every step
     digests: Optional[torch.Tensor] = None         # int64 [n_layers + 1] stage digests (race_check = "shadow")
     seam_dev: Optional[torch.Tensor] = None        # int32 blob: ids [Mh*64] | values [Mh*64] fp32 bits | lse [Mh*2] (seam buckets)
@@ -624,6 +626,7 @@ class SeqStep:
     next_token: int = -1      # the prompt token after this chunk's last row (-1: none), for prompt log-probabilities
     sampling: Optional[tuple] = None   # (temperature, top_k, top_p, min_p) of a sampled sequence the device may draw for
     uniforms: Optional[list] = None    # one uniform number per head row of this step (decode: every row; prefill: the last)
+    blocks_key: Optional[object] = None   # identity of `blocks` (same key = same list contents): the block table row is then uploaded once
 
 
 @dataclass
@@ -634,8 +637,13 @@ class StepResult:
     picks: list
 
 
-def fill_blob(b: Bucket, seqs: list, page_tokens: int = 16) -> int:
-    """Write the index tables of one step into the bucket's pinned blob. Returns the words to copy."""
+def fill_blob(b: Bucket, seqs: list, page_tokens: int = 16) -> list:
+    """Write the index tables of one step into the bucket's pinned blob.  Returns the word ranges
+    [(first, count), ...] that have to reach the device: the header (every per-row and per-sequence
+    table) and the block-table rows that changed.  A sequence's KV blocks are allocated up front
+    and never change, so a row whose `blocks_key` is the one the device already holds is skipped:
+    in steady-state decode no block-table byte crosses the bus (the reference sends the table only
+    on page-crossing steps, `crates/saber-engine/src/tp2.rs:1897`)."""
     import numpy as np
     lay = b.layout
     a = b.blob_host.numpy()
@@ -645,8 +653,8 @@ def fill_blob(b: Bucket, seqs: list, page_tokens: int = 16) -> int:
     a[lay.slot_map:lay.slot_map + M] = -1
     a[lay.next_ids:lay.next_ids + M] = -1
     a[lay.slots:lay.slots + nseq] = -1
+    ranges = [(0, hdr)]
     row = 0
-    max_used = 0
     for j, s in enumerate(seqs):
         n = len(s.tokens)
         a[lay.ids + row: lay.ids + row + n] = s.tokens
@@ -661,8 +669,10 @@ def fill_blob(b: Bucket, seqs: list, page_tokens: int = 16) -> int:
         for ax in range(3):
             a[lay.pos + ax * M + row: lay.pos + ax * M + row + n] = \
                 pos + s.rope_delta if s.rope_pos is None else np.asarray(s.rope_pos[ax], dtype=np.int32)[:n]
-        blk = np.asarray(s.blocks, dtype=np.int32)
-        a[lay.slot_map + row: lay.slot_map + row + n] = blk[pos // page_tokens] * page_tokens + pos % page_tokens
+        nblk = len(s.blocks)
+        first_page, last_page = s.pos0 // page_tokens, (s.pos0 + n - 1) // page_tokens
+        touched = np.asarray(s.blocks[first_page:last_page + 1], dtype=np.int32)     # pages this step's rows write
+        a[lay.slot_map + row: lay.slot_map + row + n] = touched[pos // page_tokens - first_page] * page_tokens + pos % page_tokens
         a[lay.cu_rows + j] = row
         a[lay.slots + j] = s.slot
         a[lay.shift + j] = s.shift
@@ -671,22 +681,32 @@ def fill_blob(b: Bucket, seqs: list, page_tokens: int = 16) -> int:
         a[lay.step_no + j] = s.step_no
         a[lay.last_rows + j] = row + n - 1
         bt = lay.block_table + j * lay.max_blocks
-        a[bt: bt + len(blk)] = blk
-        max_used = max(max_used, len(blk))
+        sig = (s.blocks_key, nblk) if s.blocks_key is not None else None
+        held = getattr(b, "bt_rows", None)
+        if sig is None or held is None or held.get(j) != sig:
+            a[bt: bt + nblk] = np.asarray(s.blocks, dtype=np.int32)
+            ranges.append((bt, nblk))
+            if held is not None:
+                held[j] = sig
         row += n
     for j in range(len(seqs), nseq + 1):
         a[lay.cu_rows + j] = row
     assert row <= M, (row, M)
-    return lay.words
+    return ranges
 
 
 def run_bucket(model: "HybridModel", b: Bucket, seqs: list, eager: bool = False) -> StepResult:
-    """One step: index tables host->device (pinned), the program (graph replay or eager walk),
-    results device->host, then parse."""
-    fill_blob(b, seqs, model.cfg.page_tokens)
+    """One step: index tables host->device (pinned; only what changed), the program (graph replay
+    or eager walk), results device->host, then parse."""
+    ranges = fill_blob(b, seqs, model.cfg.page_tokens)
     st = model.stream
     with torch.cuda.stream(st):
-        b.blob_dev.copy_(b.blob_host, non_blocking=True)
+        nbytes = 0
+        for first, count in ranges:
+            if count > 0:
+                b.blob_dev[first:first + count].copy_(b.blob_host[first:first + count], non_blocking=True)
+                nbytes += 4 * count
+        b.last_h2d_bytes = nbytes
         if b.captured and not eager:
             b.program.replay(st)
         else:

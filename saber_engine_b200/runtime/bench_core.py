@@ -51,7 +51,7 @@ def timed_decode(model: HybridModel, bucket, seqs_state: list, steps: int, warmu
     """Runs warmup + steps decode steps over the given live sequences; returns (ms, tokens)."""
     def one_step():
         seqs = [SeqStep([s["last"]] + s["drafts"][: bucket.width - 1], s["pos"], s["slot"], s["shift"],
-                        s["blocks"], uid=s["uid"], step_no=s["step"]) for s in seqs_state]
+                        s["blocks"], uid=s["uid"], step_no=s["step"], blocks_key=("bench", s["uid"])) for s in seqs_state]
         res = run_bucket(model, bucket, seqs)
         n = 0
         for j, s in enumerate(seqs_state):
@@ -117,8 +117,9 @@ def e2e_through_engine(model: HybridModel, prompts: list, steps: int, warmup: in
     for sub in subs:
         sched.abort(sub.seq_id)
     sched.step()
-    return {"tokens": tokens, "wall_ms": wall * 1e3, "h2d": b.layout.words * 4, "d2h": b.out_host.numel() * 4,
-            "prefill_s": prefill_s, "prefix_cache": hits, "live": n}
+    return {"tokens": tokens, "wall_ms": wall * 1e3, "h2d": b.last_h2d_bytes, "d2h": b.out_host.numel() * 4,
+            "prefill_s": prefill_s, "prefix_cache": hits, "live": n,
+            "mixed_steps": sched.counters["mixed_steps"], "deferred_for_prefix": sched.counters["deferred_for_prefix"]}
 
 
 def run_benchmark(args, ClockSampler):
@@ -130,7 +131,9 @@ def run_benchmark(args, ClockSampler):
     cfg = C.by_name(args.model)
     streams, W = args.streams, args.width
     decode_budget = (args.warmup + args.steps + 8) * W * 2 + 64
-    max_ctx = args.prompt + decode_budget
+    # the pool and every block table are sized for the model's full context (262,144 tokens per
+    # sequence) unless --max-ctx says otherwise; the workload itself uses prompt + decode budget
+    max_ctx = max(int(getattr(args, "max_ctx", 0) or cfg.max_ctx), args.prompt + decode_budget)
     comm = None
     if world > 1:
         from ..parallel.symm import SymmetricComm
@@ -224,6 +227,7 @@ def run_benchmark(args, ClockSampler):
                       launches_per_step=sb.n_launches)
     # ---- end to end through the public engine API (fresh KV / state, same model and buckets)
     e2e = e2e_through_engine(model, prompts, args.steps, args.warmup, world, W, rung, max_ctx)
+    kv_tokens = (model.kv_blocks - 1) * page
     e2e_wall = _max_over_ranks(e2e["wall_ms"], world)
     model.scratch.check()
     if rank != 0:
@@ -242,13 +246,14 @@ def run_benchmark(args, ClockSampler):
         "config": {"model": cfg.name, "global_batch": streams, "seq_len": args.prompt,
                    "parallelism": f"tp{world}", "verify_width": W, "accept_p": args.accept_p,
                    "decode_tokens_timed": tokens, "l2": "inputs larger than L2 (weights re-streamed every step)",
-                   "shared_prefix": args.shared_prefix},
+                   "shared_prefix": args.shared_prefix, "max_ctx": max_ctx, "kv_pool_tokens": kv_tokens},
         "clocks": clocks,
         "e2e": {"value": e2e["tokens"] / (e2e_wall / 1e3), "unit": "tok/s",
                 "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                 "ms_per_step": e2e_wall / args.steps, "tokens": e2e["tokens"],
                 "api": "sched.Scheduler.submit/step over runtime.HybridExecutor (prefix cache on)",
                 "prefill_s_all_streams": e2e["prefill_s"], "prefix_cache": e2e["prefix_cache"],
+                "mixed_steps": e2e["mixed_steps"], "deferred_for_prefix": e2e["deferred_for_prefix"],
                 "bucket_loop_tok_s": tokens / (wall_ms / 1e3)},
         "gpu_launches": db.n_launches * args.steps,
         "extra": {"single_stream": single, "ttft_p50_ms": ttft_p50, "ttft_512_tokens_ms": short_ms,

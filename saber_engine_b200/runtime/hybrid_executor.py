@@ -65,6 +65,8 @@ class HybridExecutor:
         self.page_tokens = model.cfg.page_tokens
         self.n_kv_blocks = model.kv_blocks
         self.vocab = model.cfg.vocab
+        self.image_rows = int(getattr(model, "image_rows", 0))     # token ids [vocab, vocab + image_rows) name rows of the image arena
+        self.supports_parking = model.tp == 1
         self.capture = capture
         self.census = {"graph_replays": 0, "eager_walks": 0, "launches": 0, "buckets_built": 0}
         # the head over every prompt row needs the whole vocabulary on one GPU
@@ -126,7 +128,8 @@ class HybridExecutor:
     def _step(r: SeqRun) -> SeqStep:
         return SeqStep(list(r.tokens), r.pos0, r.slot, r.shift, r.blocks, uid=r.uid, step_no=r.step_no,
                        rope_pos=r.rope_pos, rope_delta=r.rope_delta, next_token=getattr(r, "next_token", -1),
-                       sampling=getattr(r, "sampling", None), uniforms=getattr(r, "uniforms", None))
+                       sampling=getattr(r, "sampling", None), uniforms=getattr(r, "uniforms", None),
+                       blocks_key=getattr(r, "blocks_key", None))
 
     def _count(self, b) -> None:
         self.census["graph_replays" if b.captured else "eager_walks"] += 1

@@ -31,6 +31,7 @@ class SeqRun:
     next_token: int = -1         # the prompt token after this chunk (-1: the chunk ends the prompt)
     sampling: Optional[tuple] = None   # (temperature, top_k, top_p, min_p): the device may draw for this sequence
     uniforms: Optional[list] = None    # the uniform numbers of this step's head rows
+    blocks_key: Optional[object] = None   # identity of `blocks`: an executor may keep the block table of an unchanged key on the device
 
 
 @dataclass

@@ -72,8 +72,18 @@ class PrefixCache:
         return sorted(c for c in cuts if c > start)
 
     # ---- lookup ----------------------------------------------------------------------------
-    def lookup(self, tokens) -> Optional[PrefixEntry]:
-        """Longest cached prefix of `tokens` that ends strictly before the last token."""
+    def lookup(self, tokens, count: bool = True) -> Optional[PrefixEntry]:
+        """Longest cached prefix of `tokens` that ends strictly before the last token.  count=False
+        is a peek: neither the statistics nor the LRU order change."""
+        if not count:
+            if not self.enabled or len(tokens) < self.min_tokens or not self._entries:
+                return None
+            hashes = chain_hashes(tokens[: len(tokens) - 1], self.page)
+            for i in range(len(hashes) - 1, -1, -1):
+                e = self._entries.get(hashes[i])
+                if e is not None and e.tokens == tuple(tokens[: e.n_tokens]):
+                    return e
+            return None
         self.stats.lookups += 1
         if not self.enabled or len(tokens) < self.min_tokens or not self._entries:
             return None

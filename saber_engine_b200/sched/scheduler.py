@@ -38,6 +38,7 @@ class SchedulerConfig:
     model_name: str = "saber"
     # mixed steps: while a prompt prefills, the decoding sequences still get a decode launch in the
     # same step, and the prompt's chunks are capped so that no stream waits for a whole prompt
+    prefix_aware_admission: bool = True  # a request waits while a prefilling prompt is about to cache a prefix they share
     mixed_steps: bool = True
     mixed_chunk_rows: int = 512
     width_policy: str = "table"          # "table" (batch -> width) | "ema" (widest recent acceptance of the live sequences)
@@ -71,6 +72,8 @@ class Sequence:
     n_drafted: int = 0
     n_accepted: int = 0
     ema: Optional[object] = None          # WidthEma of this sequence (width_policy = "ema")
+    blocks_key: Optional[tuple] = None    # changes whenever `blocks` is reassigned (admission, restore)
+    hashes: Optional[list] = None         # block-chained hashes of the prompt (prefix-aware admission)
     prompt_lps: list = field(default_factory=list)   # log-probabilities of prompt tokens 1.., chunk by chunk
 
     @property
@@ -98,6 +101,7 @@ class Scheduler:
         self.waiting: deque = deque()
         self.running: list = []
         self._ids = itertools.count(1)
+        self._bkeys = itertools.count(1)
         self._lock = threading.Lock()
         # device work from outside the step loop (parking from a server thread) must not meet a step in
         # flight on the executor's stream (a bucket may be under capture there): both take this lock
@@ -121,7 +125,7 @@ class Scheduler:
         self.prompt_store = None            # optional sched.prompt_store.PromptStore (prefixes that survive restarts)
         self.valve_level = "ok"
         self.auto_parked: list = []         # keys parked by the scheduler itself (victims), restored when room appears
-        self.counters.update(mixed_steps=0, victims_parked=0, victims_restored=0, lookup_drafts=0, valve_demotions=0)
+        self.counters.update(mixed_steps=0, deferred_for_prefix=0, victims_parked=0, victims_restored=0, lookup_drafts=0, valve_demotions=0)
 
     # ------------------------------------------------------------------------------ Engine trait
     def submit(self, req: EngineRequest) -> Submission:
@@ -188,6 +192,15 @@ class Scheduler:
             # image rows are arena addresses, not content: no prefix sharing; prompt log-probabilities
             # need every prompt row to run
             mm = s.req.mm is not None or s.req.params.prompt_logprobs is not None
+            if not mm and self.cfg.prefix_aware_admission and self.prefix.enabled:
+                coming = self._coming_prefix(s)
+                if coming > 0:
+                    have = self.prefix.lookup(s.prompt, count=False)
+                    if coming > (have.n_tokens if have else 0):
+                        # a prompt that is prefilling right now shares a longer prefix with this one and
+                        # will put it in the cache at a cut point ahead: admitting now would compute it twice
+                        self.counters["deferred_for_prefix"] += 1
+                        break
             hit = None if mm else self.prefix.lookup(s.prompt)
             shared = list(hit.blocks) if hit else []
             need = self.arenas.kv.blocks_for(total) - len(shared)
@@ -207,6 +220,7 @@ class Scheduler:
                     break
             self.waiting.popleft()
             s.blocks, s.slot = self.arenas.admit(total, shared)
+            s.blocks_key = (s.seq_id, next(self._bkeys))
             s.t_admit = time.monotonic()
             start = 0
             stored = None
@@ -228,6 +242,29 @@ class Scheduler:
             s.cut_points = set(cuts)
             s.chunks = deque(B.cut_prompt(len(s.prompt), start, self.ex.prefill_rungs, cuts))
             self.running.append(s)
+
+    def _coming_prefix(self, s: Sequence) -> int:
+        """Tokens of `s`'s prompt that a currently prefilling sequence will have inserted into the
+        prefix cache at one of its cut points still ahead of it (0: none)."""
+        from .prefix_cache import chain_hashes
+        if len(s.prompt) < self.prefix.min_tokens:
+            return 0
+        if s.hashes is None:
+            s.hashes = chain_hashes(s.prompt[: len(s.prompt) - 1], self.page)
+        best = 0
+        for r in self.running:
+            if not r.prefilling or r.req.mm is not None or not r.cut_points:
+                continue
+            if r.hashes is None:
+                r.hashes = chain_hashes(r.prompt[: len(r.prompt) - 1], self.page)
+            n, limit = 0, min(len(s.hashes), len(r.hashes))
+            while n < limit and s.hashes[n] == r.hashes[n]:
+                n += 1
+            shared = n * self.page
+            ahead = [c for c in r.cut_points if r.pos < c <= shared]
+            if ahead:
+                best = max(best, max(ahead))
+        return best
 
     def _can_park(self) -> bool:
         return bool(getattr(self.ex, "supports_parking", hasattr(self.ex, "export_session")))
@@ -319,6 +356,7 @@ class Scheduler:
                                      [list(ax[pos:pos + n]) for ax in s.req.mm["rope_pos"]]),
                            prompt_lp=s.req.params.prompt_logprobs,
                            next_token=(s.prompt[pos + n] if pos + n < len(s.prompt) else -1),
+                           blocks_key=s.blocks_key,
                            **(self._device_draw(s, 1) if pos + n == len(s.prompt) else {}))
                     for s, pos, n in phase[1]]
             return self.ex.prefill(runs)
@@ -335,6 +373,7 @@ class Scheduler:
                                uid=s.seq_id, step_no=s.step_no, temperature=s.req.params.temperature,
                                want_seam=self._wants_seam(s),
                                rope_delta=(0 if s.req.mm is None else int(s.req.mm.get("rope_delta", 0))),
+                               blocks_key=s.blocks_key,
                                **self._device_draw(s, width)))
         return self.ex.decode(runs, width)
 
@@ -434,6 +473,7 @@ class Scheduler:
         total = len(s.prompt) + s.req.params.max_tokens + max(self.ex.decode_widths)
         img = self.park_tier.take(key)            # raises ParkError on a corrupt image: nothing reached the device
         s.blocks, s.slot = self.arenas.admit(total, [])
+        s.blocks_key = (s.seq_id, next(self._bkeys))
         self.ex.import_session(s.slot, s.blocks, img.header, img.payload)
         del self.parked[key]
         self.running.append(s)

@@ -200,3 +200,27 @@ def test_memory_valve_demotes_parks_and_refuses():
     sched.run_until_idle()
     assert _collect(a)[0] == reference_generation(_prompt(30, 13), 400, 1024)
     assert _collect(b)[0] == reference_generation(_prompt(30, 14), 400, 1024)
+
+
+def test_requests_sharing_a_prefix_wait_for_the_prompt_that_is_caching_it():
+    """Eight prompts with a common 2048-token prefix arrive together: the first prefills, the others
+    are admitted once its cut point is in the cache, and each of them hits it."""
+    shared = _prompt(2048, 20)
+    prompts = [shared + _prompt(1000, 30 + j) for j in range(4)]
+    ex = NullExecutor(seed=4)
+    sched = Scheduler(ex, SchedulerConfig(max_seqs=4, max_ctx=8192, prefix_cache=True))
+    subs = [sched.submit(EngineRequest(p, SamplingParams(max_tokens=6))) for p in prompts]
+    sched.run_until_idle()
+    for p, sub in zip(prompts, subs):
+        toks, last = _collect(sub)
+        assert toks == reference_generation(p, 6, 1024)
+    st = sched.prefix.stats
+    assert st.hits == 3 and st.hit_tokens == 3 * 2048
+    assert sched.counters["deferred_for_prefix"] > 0
+    # negative control: the same arrival without the law computes the prefix four times
+    ex2 = NullExecutor(seed=4)
+    s2 = Scheduler(ex2, SchedulerConfig(max_seqs=4, max_ctx=8192, prefix_cache=True, prefix_aware_admission=False))
+    subs2 = [s2.submit(EngineRequest(p, SamplingParams(max_tokens=6))) for p in prompts]
+    s2.run_until_idle()
+    assert s2.prefix.stats.hits == 0
+    assert sum(r for k, _, r in ex2.launch_log if k == "prefill") > sum(r for k, _, r in ex.launch_log if k == "prefill")
