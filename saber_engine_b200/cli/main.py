@@ -116,19 +116,49 @@ def build_engine(a):
             if getattr(a, "vision", False):
                 raise SystemExit("--vision serves from one GPU only")
         a._tp_rank = rank
+        # ---- one resolved plan drives the engine: buckets, the KV pool (budget - billed), tuned routes
+        from ..plan import launch_plan as LP
+        from ..utils.host_trace import StartupLedger
+        boot = StartupLedger()
+        with boot.phase("plan"):
+            if getattr(a, "manifest", None):
+                man = LP.Manifest.from_toml(Path(a.manifest).read_text())
+                if man.tp != a.engine_tp:
+                    raise SystemExit(f"saber: the manifest is for tp {man.tp} but the engine runs tp {a.engine_tp}")
+            else:
+                man = LP.Manifest(model=a.engine_config, pack=a.pack, tp=a.engine_tp, max_ctx=a.engine_max_ctx,
+                                  max_seqs=a.engine_max_seqs, decode_batches=tuple(_ints(a.engine_decode_batches)),
+                                  decode_widths=tuple(widths), prefill_rows=tuple(_ints(a.engine_prefill_rows)),
+                                  draft_block=a.engine_draft_block, budget_mib=a.engine_budget_mib,
+                                  prefix_cache_mib=a.prefix_cache_host_mib, autotune=a.autotune,
+                                  allow_untuned=not getattr(a, "require_tuned", False))
+            try:
+                plan = LP.bind(LP.resolve(man, LP.DeviceProfile.measured()))
+            except LP.PlanError as exc:
+                for prob in exc.problems:
+                    print(f"saber: {prob}", file=sys.stderr)
+                raise SystemExit(2)
+            a._plan = plan
+            cfg = MC.by_name(man.model)
+            widths = list(man.decode_widths)
         weights = None
-        if a.pack and not a.random_init:
-            from ..pack.build import load_weights
-            weights = load_weights(a.pack, cfg, a.engine_tp, rank, dev)
-        model = HybridModel(cfg, tp=a.engine_tp, rank=rank, device=dev, max_seqs=a.engine_max_seqs, comm=comm,
-                            max_ctx=a.engine_max_ctx, kv_blocks=a.engine_kv_blocks or None, max_width=max(widths),
-                            weights=weights, seed=a.seed, race_check=a.engine_race_check,
-                            image_rows=(getattr(a, "vision_arena_patches", 0) // 4 if getattr(a, "vision", False) else 0))
-        if a.autotune:
-            from ..plan.autotune import TuneTable
-            model.tune_table = TuneTable.load(a.autotune)
-        ex = HybridExecutor(model, _ints(a.engine_decode_batches), widths, _ints(a.engine_prefill_rows),
-                            prebuild=a.prebuild)
+        with boot.phase("weights"):
+            if a.pack and not a.random_init:
+                from ..pack.build import load_weights
+                weights = load_weights(a.pack, cfg, a.engine_tp, rank, dev)
+        with boot.phase("model"):
+            kv_blocks = a.engine_kv_blocks or plan.kv_blocks            # the ledger's pool unless a count is forced
+            model = HybridModel(cfg, tp=a.engine_tp, rank=rank, device=dev, max_seqs=man.max_seqs, comm=comm,
+                                max_ctx=man.max_ctx, kv_blocks=kv_blocks, max_width=max(widths),
+                                weights=weights, seed=a.seed, race_check=a.engine_race_check,
+                                image_rows=(getattr(a, "vision_arena_patches", 0) // 4 if getattr(a, "vision", False) else 0))
+            if man.autotune:
+                from ..plan.autotune import TuneTable
+                model.tune_table = TuneTable.load(man.autotune)
+        with boot.phase("buckets"):
+            ex = HybridExecutor(model, list(man.decode_batches), widths, list(man.prefill_rows), prebuild=a.prebuild)
+        ex.startup = boot
+        ex.plan_hash = plan.plan_hash
         if a.engine_tp > 1:
             from ..parallel.tp_serve import TpLeaderExecutor, follower_loop
             if rank != 0:                # a follower never returns from here until the leader stops it
@@ -137,8 +167,20 @@ def build_engine(a):
                 dist.destroy_process_group()
                 raise SystemExit(0)
             ex = TpLeaderExecutor(ex, a._tp_group)
+    if a.engine_tp > 1 and (getattr(a, "prompt_cache_dir", None) or getattr(a, "park_dir", None)):
+        raise SystemExit("saber: --prompt-cache-dir / --park-dir move one rank's shard only: not available with --engine-tp > 1")
+    from ..sched.width import WidthByBatch
+    wt = WidthByBatch.parse(a.engine_width_table, captured=tuple(_ints(a.engine_decode_widths))) if getattr(a, "engine_width_table", "") else None
     cfg_s = SchedulerConfig(max_seqs=a.engine_max_seqs, max_ctx=a.engine_max_ctx, prefix_cache=not a.no_prefix_cache,
-                            prefix_cache_bytes=a.prefix_cache_host_mib << 20, model_name=a.served_model_name)
+                            prefix_cache_bytes=a.prefix_cache_host_mib << 20, model_name=a.served_model_name,
+                            width_table=wt, width_policy=getattr(a, "engine_width_policy", "table"),
+                            lookup_drafts=bool(getattr(a, "engine_lookup_drafts", False)),
+                            park_victims=bool(getattr(a, "engine_park_victims", False)),
+                            mixed_steps=not getattr(a, "no_mixed_steps", False),
+                            mixed_chunk_rows=getattr(a, "engine_mixed_chunk_rows", 512))
+    if getattr(a, "engine_mem_valve", False):
+        from ..sched.mem_valve import MemValve
+        cfg_s.mem_valve = MemValve()
     sched = Scheduler(ex, cfg_s, sampler=HostSampler())
     from ..sched.park import ParkTier
     from ..utils.host_trace import HostTrace, StepLedger
@@ -206,6 +248,9 @@ def cmd_engine(a) -> int:
     for path in getattr(a, "warm_prompt", []):
         ids = tok.encode(Path(path).read_text())
         sched.warm([ids])
+    if getattr(ex, "startup", None) is not None or getattr(getattr(ex, "inner", None), "startup", None) is not None:
+        boot = getattr(ex, "startup", None) or ex.inner.startup
+        print("saber: ready; startup phases\n" + boot.render(), file=sys.stderr)
     sched.spawn_step_loop()
     try:
         uvicorn.run(create_app(state), host=a.host, port=a.port, log_level="warning")
@@ -302,7 +347,16 @@ def make_parser() -> argparse.ArgumentParser:
     e.add_argument("--engine-decode-widths", default="1,5,8")
     e.add_argument("--engine-draft-block", type=int, default=8)
     e.add_argument("--engine-budget-mib", type=int, default=160000)
-    e.add_argument("--engine-kv-blocks", type=int, default=0)
+    e.add_argument("--engine-kv-blocks", type=int, default=0, help="force the KV block count (0: what the plan's ledger derives from the budget)")
+    e.add_argument("--manifest", help="typed TOML manifest: replaces the bucket / limit flags (see examples/)")
+    e.add_argument("--require-tuned", action="store_true", help="refuse to boot when a route has no measurement in the autotune table")
+    e.add_argument("--engine-width-table", default="", help="verify width by batch, e.g. 1:8,4:5")
+    e.add_argument("--engine-width-policy", default="table", choices=["table", "ema"])
+    e.add_argument("--engine-lookup-drafts", action="store_true", help="prompt-lookup drafts for sequences without model drafts")
+    e.add_argument("--engine-park-victims", action="store_true", help="park a decoding sequence when a waiting request does not fit")
+    e.add_argument("--engine-mem-valve", action="store_true", help="host-memory pressure valve: demote, park, refuse")
+    e.add_argument("--no-mixed-steps", action="store_true")
+    e.add_argument("--engine-mixed-chunk-rows", type=int, default=512)
     e.add_argument("--served-model-name", default="saber")
     e.add_argument("--host", default="127.0.0.1")
     e.add_argument("--port", type=int, default=8000)

@@ -222,8 +222,12 @@ class HybridModel:
         self._flush(prog)
         a = self._fmt(a, w)
         nt = L.token_tile(a.M)
-        halves = 2 if (self.fuse and tp_site < 0 and not hold and
-                       F.pick_halves(w, w.N_pad // L.TILE_N, (a.M + nt - 1) // nt)) else 1
+        hit = self._tuned(w, a)
+        if hit is not None and tp_site < 0 and not hold:
+            halves = int(hit.get("halves", 1))
+        else:
+            halves = 2 if (self.fuse and tp_site < 0 and not hold and
+                           F.pick_halves(w, w.N_pad // L.TILE_N, (a.M + nt - 1) // nt)) else 1
         splits = 1 if halves == 2 else self.pick_splits(w, a)
         p = F.gemm_params(w, a, out, self.scratch, splits=splits, halves=halves)
         if tp_site >= 0 and self.tp > 1:
@@ -276,11 +280,16 @@ class HybridModel:
             self._flush(prog)
         prog.row(N.ROW_ADD_RMS, p, tag=tag)
 
+    def _tuned(self, w: F.QuantWeight, a: F.QuantAct):
+        """The measured variant of this (linear, rows) route from the plan's tune table, or None."""
+        table = getattr(self, "tune_table", None)
+        return table.lookup("gemm_i8", N=w.N_pad, K=w.K, M=a.M, w4=int(w.w4)) if table is not None else None
+
     def pick_splits(self, w: F.QuantWeight, a: F.QuantAct) -> int:
         table = getattr(self, "tune_table", None)
         if table is not None:
             hit = table.lookup("gemm_i8", N=w.N_pad, K=w.K, M=a.M, w4=int(w.w4))
-            if hit is not None:
+            if hit is not None and int(hit.get("halves", 1)) != 2:
                 return int(hit.get("splits", 1))
         nt = L.token_tile(a.M)
         return F.pick_splits(w.N_pad // L.TILE_N, (a.M + nt - 1) // nt, w.K // 128)

@@ -79,6 +79,8 @@ class TpLeaderExecutor:
         return self.inner.snapshot_bytes()
 
     # session parking moves one rank's shard only: refused on several GPUs
+    supports_parking = False
+
     def export_session(self, *a, **k):
         raise NotImplementedError("session parking is not available on several GPUs")
 

@@ -110,8 +110,8 @@ class Manifest:
             p.append("decode_widths must contain 1")
         if max(self.decode_widths) > self.draft_block + 1:
             p.append("a decode width exceeds draft_block + 1")
-        if self.gdn_state_dtype not in ("f32", "f16"):
-            p.append("gdn_state_dtype must be f32 or f16")
+        if self.gdn_state_dtype != "f32":
+            p.append("gdn_state_dtype must be f32 (the recurrent state of this build is fp32 only)")
         return p
 
 
@@ -205,7 +205,7 @@ def resolve(manifest: Manifest, device: Optional[DeviceProfile] = None, table: O
             key = make_key("gemm_i8", N=n_pad, K=K, M=M, w4=w4)
             hit = table.records.get(key) if table else None
             if hit is not None:
-                routes[f"{name} M={M}"] = {"key": key, "variant": {k: hit.variant[k] for k in ("splits", "stages")}, "source": "autotune"}
+                routes[f"{name} M={M}"] = {"key": key, "variant": {k: hit.variant.get(k, 1) for k in ("splits", "stages", "halves")}, "source": "autotune"}
             else:
                 nt = L.token_tile(M)
                 routes[f"{name} M={M}"] = {"key": key, "variant": {"splits": pick_splits(n_pad // L.TILE_N, (M + nt - 1) // nt, K // 128), "stages": 0},

@@ -38,15 +38,17 @@ def model_gemm_shapes(cfg, tp: int) -> list:
 
 def candidates(n_tiles: int, m_tiles: int, kb: int, nt: int, w4: int = 1) -> dict:
     out = {}
-    for s in (1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 16):
+    for s in (1, 2, 3, 4, 5, 6, 7, 8):          # the kernel's split-K ceiling is 8
         if s > kb or (s - 1) * math.ceil(kb / s) >= kb:
             continue
-        if n_tiles * m_tiles * s > 148 * 24:
+        if n_tiles * m_tiles * s > 148 * 24 or (s > 1 and n_tiles * m_tiles * s > 148):
             continue
-        for st in ((4, 6, 8, 10) if w4 else (3, 4, 5, 6)):
+        for st in ((4, 8) if w4 else (3, 5)):
             if N.lib().saber_gemm_i8_smem_bytes_w(nt, st, w4) > 224 * 1024:
                 continue
-            out[f"s{s}_st{st}"] = {"splits": s, "stages": st}
+            out[f"s{s}_st{st}"] = {"splits": s, "stages": st, "halves": 1}
+    if w4 == 1 and 148 // 4 < n_tiles * m_tiles <= 148 // 2:
+        out["halves_st8"] = {"splits": 1, "stages": 8, "halves": 2}     # two CTAs per weight tile instead of split-K
     return out
 
 
@@ -74,7 +76,7 @@ def tune_shape(Nn: int, K: int, M: int, w4: int, sweeper: Sweeper, dev) -> "Tune
         back to back without any host gap inside the measured interval."""
         prog = N.Program(f"tune-s{v['splits']}-st{v['stages']}")
         for w in ws:
-            prog.gemm(F.gemm_params(w, qa, out, sc, splits=v["splits"]), v["stages"], tag="gemm")
+            prog.gemm(F.gemm_params(w, qa, out, sc, splits=v["splits"], halves=v.get("halves", 1)), v["stages"], tag="gemm")
         prog.keep(ws, qa, out)
         with torch.cuda.stream(stream):
             prog.capture(stream)
@@ -141,7 +143,7 @@ def main(argv=None) -> int:
             rec = tune_shape(Nn, K, M, w4, sw, dev)
             table.put(rec)
             print(f"{name:14s} N={Nn:6d} K={K:5d} M={M:4d} w4={w4}: {rec.variant['name']:10s} "
-                  f"{rec.measured_us:8.1f} us  {rec.variant['gbps']:7.0f} GB/s  runner-up {rec.runner_up_us:.1f} us"
+                  f"{rec.measured_us:8.1f} us  {rec.variant['gbps']:7.0f} GB/s  runner-up {(rec.runner_up_us if rec.runner_up_us is not None else float('nan')):.1f} us"
                   f"{'' if rec.stable else '  UNSTABLE'}", flush=True)
     table.save(args.out)
     return 0

@@ -142,6 +142,13 @@ def run_benchmark(args, ClockSampler):
     t_build = time.perf_counter()
     model = HybridModel(cfg, tp=world, rank=rank, device=dev, max_seqs=streams, max_ctx=max_ctx,
                         max_width=W, seed=1234, comm=comm, oracle_p=args.accept_p, oracle_seed=99)
+    tuned = None
+    table_path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                              "examples", f"autotune-b200-{cfg.name}-tp{world}.json")
+    if os.path.exists(table_path) and not getattr(args, "no_tune_table", False):
+        from ..plan.autotune import TuneTable
+        model.tune_table = TuneTable.load(table_path)        # the committed device table of this model and degree
+        tuned = os.path.basename(table_path)
     torch.cuda.synchronize()
     build_s = time.perf_counter() - t_build
     page = cfg.page_tokens
@@ -246,7 +253,8 @@ def run_benchmark(args, ClockSampler):
         "config": {"model": cfg.name, "global_batch": streams, "seq_len": args.prompt,
                    "parallelism": f"tp{world}", "verify_width": W, "accept_p": args.accept_p,
                    "decode_tokens_timed": tokens, "l2": "inputs larger than L2 (weights re-streamed every step)",
-                   "shared_prefix": args.shared_prefix, "max_ctx": max_ctx, "kv_pool_tokens": kv_tokens},
+                   "shared_prefix": args.shared_prefix, "max_ctx": max_ctx, "kv_pool_tokens": kv_tokens,
+                   "autotune_table": tuned},
         "clocks": clocks,
         "e2e": {"value": e2e["tokens"] / (e2e_wall / 1e3), "unit": "tok/s",
                 "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
