@@ -72,15 +72,27 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeKvParams p) {
     const int slot = p.slot_map[m];
     if (slot >= 0) {
       const int blk = slot / kPageTokens, off = slot % kPageTokens;
-      uint8_t* kdst = p.kv_cache +
-                      ((static_cast<size_t>(blk) * p.nkv + kh) * 2 * kPageTokens + off) * kHeadDim;
-      uint8_t* vdst = kdst + kPageTokens * kHeadDim;
       const float2 vv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(
           p.qkv + static_cast<size_t>(m) * p.ld + p.v_off + kh * kHeadDim + 2 * t));
-      *reinterpret_cast<__nv_fp8x2_storage_t*>(kdst + 2 * t) = __nv_cvt_float2_to_fp8x2(
+      const __nv_fp8x2_storage_t k2 = __nv_cvt_float2_to_fp8x2(
           make_float2(o2[0] * p.k_inv_scale, o2[1] * p.k_inv_scale), __NV_SATFINITE, __NV_E4M3);
-      *reinterpret_cast<__nv_fp8x2_storage_t*>(vdst + 2 * t) = __nv_cvt_float2_to_fp8x2(
+      const __nv_fp8x2_storage_t v2 = __nv_cvt_float2_to_fp8x2(
           make_float2(vv.x * p.v_inv_scale, vv.y * p.v_inv_scale), __NV_SATFINITE, __NV_E4M3);
+      uint8_t* page = p.kv_cache + (static_cast<size_t>(blk) * p.nkv + kh) * (2 * kPageTokens * kHeadDim);
+      if (p.page_layout == 1) {
+        // core-matrix order: K [key group][dim chunk][8 keys][16 dims], V [dim group][8 dims][16 keys]
+        const int d = 2 * t;
+        uint8_t* kdst = page + (off >> 3) * 2048 + (d >> 4) * 128 + (off & 7) * 16 + (d & 15);
+        *reinterpret_cast<__nv_fp8x2_storage_t*>(kdst) = k2;
+        uint8_t* vdst = page + kPageTokens * kHeadDim + (d >> 3) * 128 + (d & 7) * 16 + off;
+        vdst[0] = static_cast<uint8_t>(v2 & 0xFFu);
+        vdst[16] = static_cast<uint8_t>(v2 >> 8);
+      } else {
+        uint8_t* kdst = page + off * kHeadDim;
+        uint8_t* vdst = kdst + kPageTokens * kHeadDim;
+        *reinterpret_cast<__nv_fp8x2_storage_t*>(kdst + 2 * t) = k2;
+        *reinterpret_cast<__nv_fp8x2_storage_t*>(vdst + 2 * t) = v2;
+      }
     }
   }
 }
@@ -444,6 +456,13 @@ extern "C" int saber_rope_kv_launch(const saber::RopeKvParams* p, cudaStream_t s
 extern "C" int saber_attn_launch(const saber::AttnParams* p, cudaStream_t stream) {
   using namespace saber;
   if (p->nq % p->nkv || p->splits < 1) return static_cast<int>(cudaErrorInvalidValue);
+  if (p->impl == 1) {      // tcgen05 kernel (core-matrix pages); the split partials share the combine kernel
+    const int e = saber_attn_tc_launch(p, stream);
+    if (e != 0) return e;
+    if (p->splits > 1)
+      saber::launch(attn_combine_kernel, dim3(dim3(p->nseq * p->nq, 16)), dim3(256), 0, stream, 0, *p);
+    return static_cast<int>(cudaGetLastError());
+  }
   if (p->splits > 1 && p->q_tiles != 1) return static_cast<int>(cudaErrorInvalidValue);
   const int group = p->nq / p->nkv;
   // decode (one query tile): pack several heads of the group into one 16-row tile

@@ -22,6 +22,10 @@ struct RopeKvParams {
   int sec_h, sec_w;            // interleaved M-RoPE section sizes of the h and w axes
   float theta, eps, w_offset;  // w_offset = 1 for (1 + w)
   float k_inv_scale, v_inv_scale;  // stored = value * inv_scale
+  // Byte order inside a 4 KiB page.  0: [16 tokens][256 dims].  1: the order the tcgen05 attention
+  // multiplies in place (core matrices of 8 rows x 16 bytes): K [2 key groups][16 dim chunks][8 keys][16 dims],
+  // V [32 dim groups][8 dims][16 keys].
+  int page_layout;
 };
 
 struct AttnParams {
@@ -39,9 +43,11 @@ struct AttnParams {
   int pack_rows;               // decode: upper bound of the rows of one sequence (1..8 packs heads into a tile; 0 = off)
   int n_blocks;                // blocks in kv_cache (0 = unknown): a table entry outside [0, n_blocks) is
                                // recorded in the status word and its page is treated as empty
+  int impl;                    // 0: warp-level MMA kernel on [16][256] pages; 1: tcgen05 kernel on core-matrix pages
 };
 
 }  // namespace saber
 
 extern "C" int saber_rope_kv_launch(const saber::RopeKvParams* p, cudaStream_t stream);
 extern "C" int saber_attn_launch(const saber::AttnParams* p, cudaStream_t stream);
+extern "C" int saber_attn_tc_launch(const saber::AttnParams* p, cudaStream_t stream);

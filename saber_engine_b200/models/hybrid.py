@@ -116,7 +116,7 @@ class HybridModel:
                  max_width: int = 8, weights: Optional[ModelWeights] = None, seed: int = 0,
                  comm=None, oracle_p: float = 0.0, oracle_seed: int = 0, gdn_vs: int = 2,
                  use_drafter: bool = True, race_check: str = "off", gdn_prefill: str = "rows",
-                 image_rows: int = 0, fuse: bool = True):
+                 image_rows: int = 0, fuse: bool = True, attn_impl: str = "tc"):
         self.cfg, self.tp, self.rank = cfg, tp, rank
         if race_check not in ("off", "shadow"):
             raise ValueError("race_check must be 'off' or 'shadow'")
@@ -138,6 +138,10 @@ class HybridModel:
         # after a row-parallel linear rides as that GEMM's row tail, silu * mul + quant runs in the
         # epilogue of the (paired) gate | up linear.  fuse=False keeps one launch per op.
         self.fuse = bool(fuse)
+        # "tc": tcgen05 attention, KV pages in the order it multiplies in place; "mma": warp-level MMA kernel, [token][dim] pages
+        if attn_impl not in ("tc", "mma"):
+            raise ValueError("attn_impl must be 'tc' or 'mma'")
+        self.attn_impl = attn_impl
         self._held = None
         if self.fuse and cfg.moe is None:
             for lw in self.w.layers:
@@ -306,6 +310,10 @@ class HybridModel:
         """KV splits of the decode attention: fill the GPU once.  The kernel runs two CTAs per SM;
         a CTA holds up to four 16-row tiles and a tile holds floor(16 / width) heads of a GQA group."""
         group = self.sh.n_q_heads // self.sh.n_kv_heads
+        if self.attn_impl == "tc":        # one CTA per SM, a CTA = (sequence, KV head, key segment): fill the GPU once
+            if width > 16 or width * group > 128:
+                return 1
+            return max(1, min(32, 148 // max(1, nseq * self.sh.n_kv_heads)))
         hpt = min(group, 16 // width) if 1 <= width <= 8 else 1
         tiles = -(-group // hpt)
         hgroups = -(-tiles // 4)
@@ -424,7 +432,8 @@ class HybridModel:
                 rk = F.rope_kv_params(buf_in, q_rot, lw.q_norm, lw.k_norm, blob, blob, self.kv[i], nq, nkv,
                                       0, k_off, k_off + nkv * D, rot_dim=cfg.rot_dim,
                                       sections=cfg.mrope_sections, theta=cfg.rope_theta, eps=cfg.eps,
-                                      w_offset=cfg.norm_offset, k_scale=self.k_scale, v_scale=self.v_scale)
+                                      w_offset=cfg.norm_offset, k_scale=self.k_scale, v_scale=self.v_scale,
+                                      page_layout=int(self.attn_impl == "tc"))
                 rk.pos, rk.slot_map, rk.ld = at(lay.pos), at(lay.slot_map), ld_in
                 prog.rope(rk, tag=f"{t}.attn.rope_kv")
                 q_tiles = (width + 15) // 16
@@ -434,6 +443,7 @@ class HybridModel:
                 ap.max_blocks, ap.nseq = self.max_blocks, nseq
                 ap.err = self.scratch.err.data_ptr()
                 ap.pack_rows = width if (decode and q_tiles == 1) else 0
+                ap.impl = int(self.attn_impl == "tc")
                 prog.attn(ap, tag=f"{t}.attn.core")
                 ao = attn_out.view(M, nq * D)
                 if cfg.attn_out_gate:

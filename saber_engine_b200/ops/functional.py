@@ -409,7 +409,7 @@ def gdn_chunked(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, n_
 # ----------------------------------------------------------------------------------- attention
 def rope_kv_params(qkv, q_out, q_norm_w, k_norm_w, pos, slot_map, kv_cache, nq, nkv, q_off, k_off,
                    v_off, rot_dim=64, sections=(11, 11, 10), theta=1e7, eps=1e-6, w_offset=1.0,
-                   k_scale=1.0, v_scale=1.0):
+                   k_scale=1.0, v_scale=1.0, page_layout: int = 0):
     p = N.RopeKvParams()
     p.qkv, p.q_out = qkv.data_ptr(), q_out.data_ptr()
     p.q_norm_w, p.k_norm_w = q_norm_w.data_ptr(), k_norm_w.data_ptr()
@@ -419,6 +419,7 @@ def rope_kv_params(qkv, q_out, q_norm_w, k_norm_w, pos, slot_map, kv_cache, nq, 
     p.rot_dim, p.sec_h, p.sec_w = rot_dim, sections[1], sections[2]
     p.theta, p.eps, p.w_offset = theta, eps, w_offset
     p.k_inv_scale, p.v_inv_scale = 1.0 / k_scale, 1.0 / v_scale
+    p.page_layout = page_layout      # 1: the tcgen05 attention's core-matrix page order
     return p
 
 
@@ -431,7 +432,7 @@ def rope_kv(qkv, q_norm_w, k_norm_w, pos, slot_map, kv_cache, nq, nkv, q_off, k_
 
 
 def attn_params(q, kv_cache, block_table, cu_q, kv_len, out, part_o, part_ml, nkv, splits, q_tiles,
-                k_scale=1.0, v_scale=1.0, sm_scale=None, pack_rows: int = 0):
+                k_scale=1.0, v_scale=1.0, sm_scale=None, pack_rows: int = 0, impl: int = 0):
     p = N.AttnParams()
     p.q, p.kv_cache, p.block_table = q.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr()
     p.cu_q, p.kv_len, p.out = cu_q.data_ptr(), kv_len.data_ptr(), out.data_ptr()
@@ -443,11 +444,12 @@ def attn_params(q, kv_cache, block_table, cu_q, kv_len, out, part_o, part_ml, nk
     p.err = scratch(q.device).err.data_ptr()
     p.n_blocks = kv_cache.shape[0]
     p.pack_rows = pack_rows if q_tiles == 1 else 0
+    p.impl = impl                    # 1: tcgen05 kernel (pages in core-matrix order)
     return p
 
 
 def attention(q, kv_cache, block_table, cu_q, kv_len, nkv, max_rows_per_seq: int, splits: int = 1,
-              k_scale=1.0, v_scale=1.0):
+              k_scale=1.0, v_scale=1.0, impl: int = 0):
     """q bf16 [M, nq, 256]; returns bf16 [M, nq, 256]."""
     out = torch.empty_like(q)
     nseq, nq = kv_len.numel(), q.shape[1]
@@ -457,6 +459,6 @@ def attention(q, kv_cache, block_table, cu_q, kv_len, nkv, max_rows_per_seq: int
         part_o = torch.empty(nseq, nq, splits, 16, 256, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(nseq, nq, splits, 16, 2, dtype=torch.float32, device=q.device)
     p = attn_params(q, kv_cache, block_table, cu_q, kv_len, out, part_o, part_ml, nkv, splits,
-                    q_tiles, k_scale, v_scale, pack_rows=max_rows_per_seq)
+                    q_tiles, k_scale, v_scale, pack_rows=max_rows_per_seq, impl=impl)
     N.check(N.lib().saber_attn_launch(C.byref(p), N.stream_handle()), "attn")
     return out

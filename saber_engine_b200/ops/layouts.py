@@ -217,3 +217,22 @@ def unpair_gate_up_int4(tiles: torch.Tensor, scale: torch.Tensor, inter: int):
     s2 = scale.reshape(nb, 2, 128)
     sc = torch.cat([s2[:, 0].reshape(-1), s2[:, 1].reshape(-1)])
     return out.contiguous(), sc.contiguous()
+
+
+# ------------------------------------------------------------------------------- KV pages in core-matrix order
+def kv_pages_to_core(cache: torch.Tensor) -> torch.Tensor:
+    """Paged KV pool uint8 [blocks, kv heads, 2, 16, 256] in the plain [token][dim] page order -> the
+    page order the tcgen05 attention multiplies in place (same shape and bytes per page):
+    K [2 key groups][16 dim chunks][8 keys][16 dims], V [32 dim groups][8 dims][16 keys]."""
+    nb, nkv = cache.shape[:2]
+    k = cache[:, :, 0].reshape(nb, nkv, 2, 8, 16, 16).permute(0, 1, 2, 4, 3, 5).reshape(nb, nkv, 4096)
+    v = cache[:, :, 1].reshape(nb, nkv, 16, 32, 8).permute(0, 1, 3, 4, 2).reshape(nb, nkv, 4096)
+    return torch.stack([k, v], dim=2).reshape(nb, nkv, 2, 16, 256).contiguous()
+
+
+def kv_pages_from_core(cache: torch.Tensor) -> torch.Tensor:
+    """Inverse of kv_pages_to_core."""
+    nb, nkv = cache.shape[:2]
+    k = cache[:, :, 0].reshape(nb, nkv, 2, 16, 8, 16).permute(0, 1, 2, 4, 3, 5).reshape(nb, nkv, 16, 256)
+    v = cache[:, :, 1].reshape(nb, nkv, 32, 8, 16).permute(0, 1, 4, 2, 3).reshape(nb, nkv, 16, 256)
+    return torch.stack([k, v], dim=2).contiguous()

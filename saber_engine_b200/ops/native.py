@@ -77,14 +77,14 @@ class RopeKvParams(C.Structure):
                 ("slot_map", P), ("kv_cache", P), ("M", I), ("ld", I), ("nq", I), ("nkv", I),
                 ("q_off", I), ("k_off", I), ("v_off", I), ("rot_dim", I), ("sec_h", I),
                 ("sec_w", I), ("theta", F), ("eps", F), ("w_offset", F), ("k_inv_scale", F),
-                ("v_inv_scale", F)]
+                ("v_inv_scale", F), ("page_layout", I)]
 
 
 class AttnParams(C.Structure):
     _fields_ = [("q", P), ("kv_cache", P), ("block_table", P), ("cu_q", P), ("kv_len", P),
                 ("out", P), ("part_o", P), ("part_ml", P), ("nseq", I), ("nq", I), ("nkv", I),
                 ("max_blocks", I), ("splits", I), ("q_tiles", I), ("sm_scale", F), ("k_scale", F),
-                ("v_scale", F), ("err", P), ("pack_rows", I), ("n_blocks", I)]
+                ("v_scale", F), ("err", P), ("pack_rows", I), ("n_blocks", I), ("impl", I)]
 
 
 class VerifyParams(C.Structure):

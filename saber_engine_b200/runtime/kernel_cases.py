@@ -57,7 +57,7 @@ def _gemm(Nn, K, M, w4, splits, copies=3):
     return ws, qa, out
 
 
-def _attn(nseq, n, ctx, splits, copies=3):
+def _attn(nseq, n, ctx, splits, copies=3, impl=0):
     nq, nkv, D = 24, 4, 256
     M = nseq * n
     pages = (ctx + n + 15) // 16
@@ -71,11 +71,12 @@ def _attn(nseq, n, ctx, splits, copies=3):
     out = torch.empty_like(q)
     po = torch.empty(nseq, nq, splits, 16, D, device=DEV) if splits > 1 else None
     pm = torch.empty(nseq, nq, splits, 16, 2, device=DEV) if splits > 1 else None
-    ps = [F.attn_params(q, kv, bt, cu, kvl, out, po, pm, nkv, splits, 1, pack_rows=n) for kv in kvs]
+    q_tiles = (n + 15) // 16
+    ps = [F.attn_params(q, kv, bt, cu, kvl, out, po, pm, nkv, splits, q_tiles, pack_rows=n, impl=impl) for kv in kvs]
     torch.cuda.synchronize()
     lib = N.lib()
     fns = [lambda p=p: N.check(lib.saber_attn_launch(C.byref(p), N.stream_handle()), "attn") for p in ps]
-    _time(fns, f"attn_paged nseq={nseq} rows={n} ctx={ctx} splits={splits}", nseq * (ctx + n) * nkv * 2 * D)
+    _time(fns, f"attn_{'tc' if impl else 'paged'} nseq={nseq} rows={n} ctx={ctx} splits={splits}", nseq * (ctx + n) * nkv * 2 * D)
     return kvs, q, out, po, pm
 
 
@@ -184,6 +185,12 @@ CASES = {
     "attn_decode_b8_w8_ctx4096": lambda: _attn(8, 8, 4096, 9),
     "attn_decode_b8_w1_ctx4096": lambda: _attn(8, 1, 4096, 9),
     "attn_decode_b8_w5_ctx4096": lambda: _attn(8, 5, 4096, 4),
+    "attn_tc_decode_b8_w8_ctx4096": lambda: _attn(8, 8, 4096, 4, impl=1),
+    "attn_tc_decode_b8_w8_ctx4096_s2": lambda: _attn(8, 8, 4096, 2, impl=1),
+    "attn_tc_decode_b8_w8_ctx4096_s1": lambda: _attn(8, 8, 4096, 1, impl=1),
+    "attn_tc_decode_b1_w8_ctx32768": lambda: _attn(1, 8, 32768, 32, copies=2, impl=1),
+    "attn_tc_decode_b1_w8_ctx131072": lambda: _attn(1, 8, 131072, 32, copies=2, impl=1),
+    "attn_tc_prefill_2048_ctx4096": lambda: _attn(1, 2048, 2048, 1, impl=1),
     "gdn_rec_b8": lambda: _gdn(8, 9, 5),
     "gdn_prefill_2048": lambda: _gdn_prefill(2048),
     "row_add_rms_m72": lambda: _row(72, 5120),

@@ -208,7 +208,10 @@ def test_gdn_prefill_commit_then_decode():
     assert torch.equal(dev["hist"][1, :3].cpu().float(), allx[-3:])
 
 
-def _attn_case(ctx_lens, rows, splits, nq=12, nkv=2, seed=0):
+_LAST_GOT = []
+
+
+def _attn_case(ctx_lens, rows, splits, nq=12, nkv=2, seed=0, impl=0, tol=3e-2):
     torch.manual_seed(seed)
     nseq = len(ctx_lens)
     M = sum(rows)
@@ -240,12 +243,14 @@ def _attn_case(ctx_lens, rows, splits, nq=12, nkv=2, seed=0):
         cu.append(cu[-1] + rows[b])
     cu_t = torch.tensor(cu, dtype=torch.int32)
     kv_len = torch.tensor([c + r for c, r in zip(ctx_lens, rows)], dtype=torch.int32)
-    cache_d = cache.to(DEV)
+    from saber_engine_b200.ops import layouts as L
+    cache_d = (L.kv_pages_to_core(cache) if impl == 1 else cache).to(DEV)     # the tcgen05 kernel's page order
     q_out = F.rope_kv(qkv.to(DEV), qw.to(DEV), kw.to(DEV), pos.to(DEV), slot_map.to(DEV), cache_d,
-                      nq, nkv, q_off, k_off, v_off)
+                      nq, nkv, q_off, k_off, v_off, page_layout=impl)
     out = F.attention(q_out, cache_d, perm.to(DEV), cu_t.to(DEV), kv_len.to(DEV), nkv,
-                      max(rows), splits=splits)
+                      max(rows), splits=splits, impl=impl)
     torch.cuda.synchronize()
+    F.scratch(DEV).check()
     # reference
     qf = qkv.float()
     q_ref = R.qk_norm_rope(qf[:, :nq * 256].reshape(M, nq, 256), qw, pos)
@@ -259,13 +264,27 @@ def _attn_case(ctx_lens, rows, splits, nq=12, nkv=2, seed=0):
         ref = R.attention_rows(R.bf16_round(q_ref[sl]), kk, vv, int(kv_len[b]))
         got = out[sl].float().cpu()
         err = (got - ref).abs().max().item()
-        assert err < 3e-2, f"seq {b}: max err {err}"
+        _LAST_GOT.append((got, ref))
+        assert err < tol * max(1.0, ref.abs().max().item()), f"seq {b}: max err {err}"
 
 
 def test_attention_decode_single_and_split():
     _attn_case([100, 37, 513], [5, 5, 5], splits=1)
     _attn_case([100, 37, 513], [5, 5, 5], splits=4, seed=1)
     _attn_case([0], [9], splits=1, seed=2)           # no history: only this step's rows
+
+
+def test_attention_tcgen05_decode_prefill_and_splits():
+    """The tcgen05 kernel (fp8 operand legs: Q and the probabilities are e4m3 like the pages) against
+    the fp32 restatement."""
+    tol = 5e-2          # of the largest output value: the probabilities carry three mantissa bits (half an ulp = 6%)
+    _attn_case([100, 37, 513], [5, 5, 5], splits=1, impl=1, tol=tol)
+    _attn_case([100, 37, 513], [5, 5, 5], splits=4, seed=1, impl=1, tol=tol)
+    _attn_case([0], [9], splits=1, seed=2, impl=1, tol=tol)
+    _attn_case([64, 300], [8, 8], splits=2, nq=24, nkv=4, seed=3, impl=1, tol=tol)
+    _attn_case([0, 50], [40, 33], splits=1, nq=12, nkv=2, seed=4, impl=1, tol=tol)       # prefill: several query tiles
+    _attn_case([700], [1], splits=3, nq=16, nkv=2, seed=5, impl=1, tol=tol)             # GQA 8, one row
+    _attn_case([1500, 20], [16, 3], splits=1, nq=6, nkv=2, seed=6, impl=1, tol=tol)     # GQA 3
 
 
 def test_attention_27b_geometry_and_prefill_rows():

@@ -111,7 +111,14 @@ def test_image_prompt_through_scheduler_uses_tower_rows_and_three_axis_positions
     # the same ids WITHOUT the three-axis positions give another continuation: the positions reach the rope kernel
     s = Scheduler(ex, SchedulerConfig(max_seqs=2, max_ctx=1024, prefix_cache=False))
     req = vis.build_request(text, [img_a], SamplingParams(max_tokens=8, ignore_eos=True))
-    plain = EngineRequest(list(req.prompt_token_ids), SamplingParams(max_tokens=8, ignore_eos=True))
+    # (ids of image rows without the image's metadata are refused: they would read another request's rows)
+    import pytest as _pt
+    from saber_engine_b200.serve.engine_api import EngineRefused
+    with _pt.raises(EngineRefused):
+        s.submit(EngineRequest(list(req.prompt_token_ids), SamplingParams(max_tokens=8, ignore_eos=True)))
+    n_ids = len(req.prompt_token_ids)
+    flat = {"rope_pos": [list(range(n_ids))] * 3, "rope_delta": 0, "grids": req.mm["grids"], "release": None}
+    plain = EngineRequest(list(req.prompt_token_ids), SamplingParams(max_tokens=8, ignore_eos=True), mm=flat)
     sub = s.submit(plain)
     s.run_until_idle()
     toks = []
