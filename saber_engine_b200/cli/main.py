@@ -316,6 +316,33 @@ def cmd_gate(a) -> int:
     return pytest.main(["-q", "-m", "gpu", str(Path(__file__).resolve().parents[2] / "tests")] + (["-k", a.k] if a.k else []))
 
 
+def cmd_console(a) -> int:
+    """The console: supervises `saber engine ...` as a child, proxies /v1 to it, keeps usage, audit and config history."""
+    import urllib.request
+    import uvicorn
+    from ..console.app import Console
+    from ..console.supervisor import Supervisor
+    Path(a.data_dir).mkdir(parents=True, exist_ok=True)
+
+    def ready() -> bool:
+        try:
+            with urllib.request.urlopen(f"{a.engine_url}/health", timeout=1) as r:
+                return r.status == 200
+        except OSError:
+            return False
+    sup = Supervisor(ready_probe=ready, ready_timeout_s=a.ready_timeout, history_path=str(Path(a.data_dir) / "history.json"))
+    con = Console(sup, a.data_dir, a.engine_url, admin_token=a.admin_token, engine_bearer=a.engine_key)
+    if a.engine_argv:
+        if not sup.apply(a.engine_argv, note="boot"):
+            print("saber console: the engine never reached ready", file=sys.stderr)
+    try:
+        uvicorn.run(con.app(), host=a.host, port=a.port, log_level="warning")
+    finally:
+        sup.stop()
+        con.usage.close()
+    return 0
+
+
 def make_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="saber")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -404,6 +431,15 @@ def make_parser() -> argparse.ArgumentParser:
     p.add_argument("--dir")
     p.add_argument("--device", default="cpu")
     sub.add_parser("probe")
+    c = sub.add_parser("console", help="supervisor + /v1 proxy + usage, audit and config history (then `--` and the engine's argv)")
+    c.add_argument("--data-dir", required=True)
+    c.add_argument("--engine-url", default="http://127.0.0.1:8090")
+    c.add_argument("--host", default="127.0.0.1")
+    c.add_argument("--port", type=int, default=8080)
+    c.add_argument("--admin-token", default=None)
+    c.add_argument("--engine-key", default=None)
+    c.add_argument("--ready-timeout", type=float, default=600.0)
+    c.add_argument("engine_argv", nargs=argparse.REMAINDER)
     g = sub.add_parser("gate")
     g.add_argument("-k")
     return ap
@@ -420,12 +456,15 @@ def main(argv=None) -> int:
         sys.argv = ["bench.py"] + argv[1:]
         runpy.run_path(str(Path(__file__).resolve().parents[2] / "bench.py"), run_name="__main__")
         return 0
+    if argv and argv[0] == "shadow":
+        from ..shadow.__main__ import main as shadow_main
+        return shadow_main(argv[1:])
     if argv and argv[0] == "tp-gate":
         from ..parallel import tp_gate
         return tp_gate.main(argv[1:])
     a = ap.parse_args(argv)
     return {"models": cmd_models, "engine": cmd_engine, "explain": cmd_explain, "tune": cmd_tune,
-            "pack": cmd_pack, "probe": cmd_probe, "gate": cmd_gate}[a.cmd](a)
+            "pack": cmd_pack, "probe": cmd_probe, "gate": cmd_gate, "console": cmd_console}[a.cmd](a)
 
 
 if __name__ == "__main__":

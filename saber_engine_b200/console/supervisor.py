@@ -8,8 +8,8 @@ supervisor's recovery).  Readiness is a probe the caller supplies (the served en
 `/health`; tests use a file).
 
 Parity: `crates/saber-console/src/supervisor.rs:1-40` (state machine, auto-rollback of a config that
-never reaches ready), `docs/CONSOLE.md:28-31,165-177` (config history + rollback).  The web console,
-usage database and `/v1` proxy of the reference's console are not part of this build.
+never reaches ready), `docs/CONSOLE.md:28-31,165-177` (config history + rollback).  The HTTP application, the `/v1` proxy, the usage
+store and the audit log are in `app.py`, `proxy.py`, `usage.py` and `audit.py` of this package.
 """
 from __future__ import annotations
 

@@ -40,6 +40,7 @@ struct OpExpand { const void* ctx; const void* tok; const void* pos; void* out; 
 struct OpAdvance { uint32_t* seq_base; uint32_t by; };
 struct OpGdnConv { saber::GdnConvParams p; int nseq; };
 struct OpGdnRec { saber::GdnRecParams p; int nseq, vs; };
+struct OpGdnStep { saber::GdnStepParams p; int nseq; };
 struct OpGdnChunk { saber::GdnRecParams p; int nseq, max_rows; float* scratch; };
 struct OpRope { saber::RopeKvParams p; };
 struct OpAttn { saber::AttnParams p; };
@@ -60,7 +61,7 @@ struct OpMoeGather { const int8_t* q; const float* scale; int M_pad; const int32
                      int8_t* q_out; float* scale_out; int rows_cap, M_pad_out, K; };
 
 using Op = std::variant<OpGemm, OpRow, OpEmbed, OpGdnConv, OpGdnRec, OpRope, OpAttn, OpArgmax,
-                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather, OpDigest, OpDigestClear, OpGdnChunk, OpLogitGather, OpSampleSeam>;
+                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather, OpDigest, OpDigestClear, OpGdnChunk, OpLogitGather, OpSampleSeam, OpGdnStep>;
 
 struct Entry {
   Op op;
@@ -93,6 +94,7 @@ int launch(const Op& op, cudaStream_t s) {
           return saber_block_expand_launch(o.ctx, o.tok, o.pos, o.out, o.nseq, o.block, o.H, s);
         else if constexpr (std::is_same_v<T, OpAdvance>) return saber_comm_advance_launch(o.seq_base, o.by, s);
         else if constexpr (std::is_same_v<T, OpGdnConv>) return saber_gdn_conv_launch(&o.p, o.nseq, s);
+        else if constexpr (std::is_same_v<T, OpGdnStep>) return saber_gdn_step_launch(&o.p, o.nseq, s);
         else if constexpr (std::is_same_v<T, OpGdnRec>) return saber_gdn_recurrent_launch(&o.p, o.nseq, o.vs, s);
         else if constexpr (std::is_same_v<T, OpGdnChunk>) return saber_gdn_chunk_launch(&o.p, o.nseq, o.max_rows, o.scratch, s);
         else if constexpr (std::is_same_v<T, OpRope>) return saber_rope_kv_launch(&o.p, s);
@@ -197,6 +199,9 @@ int saber_program_add_advance(void* h, uint32_t* seq_base, uint32_t by, const ch
 }
 int saber_program_add_gdn_conv(void* h, const saber::GdnConvParams* p, int nseq, const char* tag) {
   return add(h, OpGdnConv{*p, nseq}, p->commit ? 2 : 1, tag);
+}
+int saber_program_add_gdn_step(void* h, const saber::GdnStepParams* p, int nseq, const char* tag) {
+  return add(h, OpGdnStep{*p, nseq}, 1, tag);
 }
 int saber_program_add_gdn_rec(void* h, const saber::GdnRecParams* p, int nseq, int vs, const char* tag) {
   return add(h, OpGdnRec{*p, nseq, vs}, 1, tag);

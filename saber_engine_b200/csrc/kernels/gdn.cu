@@ -23,6 +23,15 @@ namespace saber {
 __device__ __forceinline__ float gdn_silu(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float gdn_softplus(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
 
+// First row of the slot's current conv window (a slot with two windows names the current one in the
+// first word of its last row).
+__device__ __forceinline__ __nv_bfloat16* gdn_hist_current(const GdnConvParams& p, int slot) {
+  if (!p.dual) return p.hist + static_cast<size_t>(slot) * p.hist_rows * p.C;
+  __nv_bfloat16* base = p.hist + static_cast<size_t>(slot) * (2 * p.hist_rows + 1) * p.C;
+  const int cur = *reinterpret_cast<const int*>(base + static_cast<size_t>(2 * p.hist_rows) * p.C) & 1;
+  return base + static_cast<size_t>(cur) * p.hist_rows * p.C;
+}
+
 // ---------------------------------------------------------------------------------- conv update
 // grid (C / 128, nseq, row chunks), block 128.  The conv is causal with a 4-tap window, so chunks of
 // kConvChunk rows are independent: a chunk reads the three inputs before its first row from x (or,
@@ -41,7 +50,7 @@ __global__ void __launch_bounds__(128) gdn_conv_update_kernel(const GdnConvParam
   if (r_first >= n) return;
   const int r_last = min(n, r_first + kConvChunk);
   const int shift = p.shift[b];
-  __nv_bfloat16* hp = p.hist + static_cast<size_t>(slot) * p.hist_rows * p.C + ch;
+  __nv_bfloat16* hp = gdn_hist_current(p, slot) + ch;
   // window = the three inputs that precede this chunk's first row: input j < 0 of the step is row
   // shift + 3 + j of the history (the committed window shifted by the accepted rows)
   auto input_at = [&](int j) -> float {
@@ -90,13 +99,22 @@ __global__ void __launch_bounds__(128) gdn_conv_commit_kernel(const GdnConvParam
   const int n = p.cu_rows[b + 1] - row0;
   if (n <= 0) return;
   const int shift = p.shift[b];
-  __nv_bfloat16* hp = p.hist + static_cast<size_t>(slot) * p.hist_rows * p.C + ch;
+  __nv_bfloat16* hp = gdn_hist_current(p, slot) + ch;
   __nv_bfloat16 win[3];
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
     const int j = n + i;  // index into (old window(3) ++ rows(n)), last three are j = n..n+2
     win[i] = j < 3 ? hp[static_cast<size_t>(shift + j) * p.C]
                    : p.x[static_cast<size_t>(row0 + j - 3) * p.ldx + ch];
+  }
+  if (p.dual) {   // both windows get the committed inputs: whichever the slot's word names is right
+    __nv_bfloat16* h0 = p.hist + static_cast<size_t>(slot) * (2 * p.hist_rows + 1) * p.C + ch;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      h0[static_cast<size_t>(i) * p.C] = win[i];
+      h0[static_cast<size_t>(p.hist_rows + i) * p.C] = win[i];
+    }
+    return;
   }
 #pragma unroll
   for (int i = 0; i < 3; ++i) hp[static_cast<size_t>(i) * p.C] = win[i];
@@ -139,6 +157,7 @@ __device__ __forceinline__ void gdn_cp16(void* dst_smem, const void* src) {
 
 template <int VS>
 __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecParams p) {
+  pdl_trigger();   // successors (the norm rows, then a GEMM) get resident on the SMs the last round leaves idle
   pdl_wait();
   constexpr int VR = 128 / VS;         // v rows per CTA
   constexpr int NT = 2 * VR;           // threads

@@ -347,22 +347,24 @@ def gdn_stash_stride(vs: int) -> int:
     return 128 + 128 // vs + 4
 
 
-def gdn_conv_params(x, conv_w, hist, cu_rows, slots, shift, out, n_q, n_k, commit, ldx=None):
+def gdn_conv_params(x, conv_w, hist, cu_rows, slots, shift, out, n_q, n_k, commit, ldx=None, dual: bool = False):
+    """dual: a slot of `hist` holds two windows and the word naming the current one ([2 R + 1][C])."""
     p = N.GdnConvParams()
     p.x, p.conv_w, p.hist = x.data_ptr(), conv_w.data_ptr(), hist.data_ptr()
     p.cu_rows, p.slots, p.shift, p.out = cu_rows.data_ptr(), slots.data_ptr(), shift.data_ptr(), out.data_ptr()
     p.C, p.n_q, p.n_k = conv_w.shape[0], n_q, n_k
     p.ldx = ldx if ldx is not None else x.stride(0)
-    p.hist_rows, p.commit, p.q_scale = hist.shape[1], int(commit), 1.0 / math.sqrt(128.0)
+    p.hist_rows, p.commit, p.q_scale = ((hist.shape[1] - 1) // 2 if dual else hist.shape[1]), int(commit), 1.0 / math.sqrt(128.0)
     p.max_rows = x.shape[0]
+    p.dual = int(dual)
     return p
 
 
-def gdn_conv(x, conv_w, hist, cu_rows, slots, shift, n_q, n_k, commit=False):
+def gdn_conv(x, conv_w, hist, cu_rows, slots, shift, n_q, n_k, commit=False, dual=False):
     """x bf16 [M, >=C] (first C columns are q|k|v); returns fp32 [M, C]."""
     M = x.shape[0]
     out = torch.empty(M, conv_w.shape[0], dtype=torch.float32, device=x.device)
-    p = gdn_conv_params(x, conv_w, hist, cu_rows, slots, shift, out, n_q, n_k, commit)
+    p = gdn_conv_params(x, conv_w, hist, cu_rows, slots, shift, out, n_q, n_k, commit, dual=dual)
     N.check(N.lib().saber_gdn_conv_launch(C.byref(p), slots.numel(), N.stream_handle()), "gdn_conv")
     return out
 
@@ -388,6 +390,54 @@ def gdn_recurrent(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, 
                        HV, HK, commit, prefill_rows=prefill_rows)
     N.check(N.lib().saber_gdn_recurrent_launch(C.byref(p), slots.numel(), vs, N.stream_handle()), "gdn_rec")
     return out
+
+
+class GdnStepScratch:
+    """Buffers between the phases of the fused decode step of one DeltaNet layer (shared by the layers
+    of a program: launches are ordered): normed head outputs, row maxima per head, sequence tickets."""
+
+    def __init__(self, M: int, HV: int, nseq: int, device):
+        self.hout = torch.empty(M, HV * 128, dtype=torch.bfloat16, device=device)
+        self.amax = torch.zeros(M, HV, dtype=torch.float32, device=device)
+        self.tickets = torch.zeros(max(nseq, 1), dtype=torch.int32, device=device)
+
+
+def gdn_hist_alloc(n_slots: int, rows: int, C_: int, device) -> torch.Tensor:
+    """Conv windows of the fused decode step: two windows of `rows` rows per slot and a last row whose
+    first word names the current one (zero = window 0)."""
+    return torch.zeros(n_slots, 2 * rows + 1, C_, dtype=torch.bfloat16, device=device)
+
+
+def gdn_step_params(x, z, ba, conv_w, A_log, dt_bias, norm_w, hist, state, stash, cu_rows, slots, shift,
+                    scratch: GdnStepScratch, qa: QuantAct, n_q, n_k, HV, HK, max_rows, *, eps=1e-6,
+                    w_offset=0.0, ldx=None, ldz=None, ldba=None) -> N.GdnStepParams:
+    """Fused conv + recurrence + gated norm + quantisation of one decode step (`stash` is laid out
+    for one value slice per head: [slots][rows][HV][1][260])."""
+    p = N.GdnStepParams()
+    p.x, p.z, p.ba = x.data_ptr(), z.data_ptr(), ba.data_ptr()
+    p.conv_w, p.A_log, p.dt_bias, p.norm_w = conv_w.data_ptr(), A_log.data_ptr(), dt_bias.data_ptr(), norm_w.data_ptr()
+    p.hist, p.state, p.stash = hist.data_ptr(), state.data_ptr(), stash.data_ptr()
+    p.cu_rows, p.slots, p.shift = cu_rows.data_ptr(), slots.data_ptr(), shift.data_ptr()
+    p.hout, p.amax_part, p.tickets = scratch.hout.data_ptr(), scratch.amax.data_ptr(), scratch.tickets.data_ptr()
+    p.q, p.scale = qa.q.data_ptr(), qa.scale.data_ptr()
+    p.C, p.n_q, p.n_k, p.HV, p.HK = conv_w.shape[0], n_q, n_k, HV, HK
+    p.ldx = ldx if ldx is not None else x.stride(0)
+    p.ldz = ldz if ldz is not None else z.stride(0)
+    p.ldba = ldba if ldba is not None else ba.stride(0)
+    assert stash.shape[3] == 1 and stash.shape[4] == 260, "the fused step wants one value slice per head"
+    p.hist_rows, p.stash_rows, p.M_pad = (hist.shape[1] - 1) // 2, stash.shape[1], qa.M_pad
+    p.qfmt, p.max_rows = int(qa.fp8), max_rows
+    p.q_scale, p.eps, p.w_offset = 1.0 / math.sqrt(128.0), eps, w_offset
+    return p
+
+
+def gdn_step(x, z, ba, conv_w, A_log, dt_bias, norm_w, hist, state, stash, cu_rows, slots, shift,
+             qa: QuantAct, n_q, n_k, HV, HK, max_rows, eps=1e-6, w_offset=0.0, scratch=None):
+    scratch = scratch or GdnStepScratch(x.shape[0], HV, slots.numel(), x.device)
+    p = gdn_step_params(x, z, ba, conv_w, A_log, dt_bias, norm_w, hist, state, stash, cu_rows, slots, shift,
+                        scratch, qa, n_q, n_k, HV, HK, max_rows, eps=eps, w_offset=w_offset)
+    N.check(N.lib().saber_gdn_step_launch(C.byref(p), slots.numel(), N.stream_handle()), "gdn_step")
+    return scratch
 
 
 def gdn_chunk_scratch(total_rows: int, nseq: int, HV: int, device) -> torch.Tensor:

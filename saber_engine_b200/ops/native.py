@@ -63,7 +63,16 @@ class RowOpParams(C.Structure):
 class GdnConvParams(C.Structure):
     _fields_ = [("x", P), ("conv_w", P), ("hist", P), ("cu_rows", P), ("slots", P), ("shift", P),
                 ("out", P), ("C", I), ("n_q", I), ("n_k", I), ("ldx", I), ("hist_rows", I),
-                ("commit", I), ("q_scale", F), ("max_rows", I)]
+                ("commit", I), ("q_scale", F), ("max_rows", I), ("dual", I)]
+
+
+class GdnStepParams(C.Structure):
+    _fields_ = [("x", P), ("z", P), ("ba", P), ("conv_w", P), ("A_log", P), ("dt_bias", P), ("norm_w", P),
+                ("hist", P), ("state", P), ("stash", P), ("cu_rows", P), ("slots", P), ("shift", P),
+                ("hout", P), ("amax_part", P), ("tickets", P), ("q", P), ("scale", P),
+                ("C", I), ("n_q", I), ("n_k", I), ("HV", I), ("HK", I), ("ldx", I), ("ldz", I), ("ldba", I),
+                ("hist_rows", I), ("stash_rows", I), ("M_pad", I), ("qfmt", I), ("max_rows", I),
+                ("q_scale", F), ("eps", F), ("w_offset", F)]
 
 
 class GdnRecParams(C.Structure):
@@ -175,6 +184,8 @@ def _declare(L: C.CDLL) -> None:
         "saber_block_expand_launch": (I, [P, P, P, P, I, I, I, S]),
         "saber_gdn_conv_launch": (I, [C.POINTER(GdnConvParams), I, S]),
         "saber_gdn_recurrent_launch": (I, [C.POINTER(GdnRecParams), I, I, S]),
+        "saber_gdn_step_launch": (I, [C.POINTER(GdnStepParams), I, S]),
+        "saber_program_add_gdn_step": (I, [P, C.POINTER(GdnStepParams), I, C.c_char_p]),
         "saber_gdn_chunk_scratch_bytes": (C.c_size_t, [I, I, I]),
         "saber_gdn_chunk_launch": (I, [C.POINTER(GdnRecParams), I, I, P, S]),
         "saber_program_add_gdn_chunk": (I, [P, C.POINTER(GdnRecParams), I, I, P, C.c_char_p]),
@@ -315,6 +326,9 @@ class Program:
 
     def gdn_conv(self, p: GdnConvParams, nseq: int, tag="gdn_conv") -> int:
         return self._L.saber_program_add_gdn_conv(self._h, C.byref(p), nseq, tag.encode())
+
+    def gdn_step(self, p: GdnStepParams, nseq: int, tag="gdn_step") -> int:
+        return self._L.saber_program_add_gdn_step(self._h, C.byref(p), nseq, tag.encode())
 
     def gdn_rec(self, p: GdnRecParams, nseq: int, vs: int, tag="gdn_rec") -> int:
         return self._L.saber_program_add_gdn_rec(self._h, C.byref(p), nseq, vs, tag.encode())

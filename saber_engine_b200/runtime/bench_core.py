@@ -141,7 +141,8 @@ def run_benchmark(args, ClockSampler):
         comm = SymmetricComm(rank, world, dev, max_elems=rows_max * cfg.hidden, rows_max=rows_max, hidden=cfg.hidden)
     t_build = time.perf_counter()
     model = HybridModel(cfg, tp=world, rank=rank, device=dev, max_seqs=streams, max_ctx=max_ctx,
-                        max_width=W, seed=1234, comm=comm, oracle_p=args.accept_p, oracle_seed=99)
+                        max_width=W, seed=1234, comm=comm, oracle_p=args.accept_p, oracle_seed=99,
+                        gdn_fused=(None if getattr(args, "gdn_fused", -1) < 0 else bool(args.gdn_fused)))
     tuned = None
     table_path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
                               "examples", f"autotune-b200-{cfg.name}-tp{world}.json")

@@ -102,6 +102,47 @@ def _gdn(nseq, n, shift, vs=2, copies=3):
     return states, stashes, out
 
 
+def _gdn_step(nseq, n, shift, copies=3):
+    """One DeltaNet layer of a decode step: the fused launch, and the three launches it replaces."""
+    HV, HK, d = 48, 16, 128
+    M = nseq * n
+    K = HV * d
+    C_ = 2 * HK * d + K
+    ld = C_ + K + 2 * HV
+    x = (torch.randn(M, ld, device=DEV) * 0.5).to(torch.bfloat16)
+    conv_w = torch.randn(C_, 4, device=DEV) * 0.5
+    A_log, dtb = torch.randn(HV, device=DEV) * 0.5, torch.randn(HV, device=DEV) * 0.5
+    norm_w = torch.ones(d, device=DEV)
+    states = [torch.randn(nseq + 1, HV, d, d, device=DEV) * 0.01 for _ in range(copies)]
+    stashes = [torch.randn(nseq + 1, 9, HV, 1, 260, device=DEV) * 0.1 for _ in range(copies)]
+    hists = [F.gdn_hist_alloc(nseq + 1, 3 + 9, C_, DEV) for _ in range(copies)]
+    cu = torch.arange(0, M + 1, n, dtype=torch.int32, device=DEV)
+    slots = torch.arange(1, nseq + 1, dtype=torch.int32, device=DEV)
+    sh = torch.full((nseq,), shift, dtype=torch.int32, device=DEV)
+    qa = F.QuantAct.alloc(M, K, DEV)
+    scr = F.GdnStepScratch(M, HV, nseq, DEV)
+    lib = N.lib()
+    ps = [F.gdn_step_params(x, x[:, C_:], x[:, C_ + K:], conv_w, A_log, dtb, norm_w, hists[i], states[i], stashes[i],
+                            cu, slots, sh, scr, qa, HK * d, HK * d, HV, HK, n) for i in range(copies)]
+    fns = [lambda p=p: N.check(lib.saber_gdn_step_launch(C.byref(p), nseq, N.stream_handle()), "gdn_step") for p in ps]
+    nbytes = 2.0 * nseq * HV * d * d * 4
+    _time(fns, f"gdn fused step nseq={nseq} rows={n} replay={shift}", nbytes)
+    conv_out = torch.empty(M, C_, device=DEV)
+    o = torch.empty(M, K, device=DEV)
+    trio = []
+    for i in range(copies):
+        cp = F.gdn_conv_params(x, conv_w, hists[i], cu, slots, sh, conv_out, HK * d, HK * d, False, dual=True)
+        rp = F.gdn_rec_params(conv_out, x[:, C_ + K:], A_log, dtb, states[i], stashes[i], cu, slots, sh, o, HK * d, HK * d, HV, HK, False)
+        np_ = F.row_params(M, K, a_f32=o, b=x[:, C_:], w=norm_w, qa=qa, ldb=ld)
+        def f(cp=cp, rp=rp, np_=np_):
+            N.check(lib.saber_gdn_conv_launch(C.byref(cp), nseq, N.stream_handle()), "conv")
+            N.check(lib.saber_gdn_recurrent_launch(C.byref(rp), nseq, 1, N.stream_handle()), "rec")
+            N.check(lib.saber_row_producer_launch(N.ROW_GDN_NORM, C.byref(np_), N.stream_handle()), "norm")
+        trio.append(f)
+    _time(trio, f"gdn conv + recurrence (one slice per head) + norm_quant, three launches nseq={nseq} rows={n} replay={shift}", nbytes)
+    return states, stashes, hists, x, qa, scr, conv_out, o
+
+
 def _gdn_prefill(n, copies=3):
     """One sequence of n rows through the committing row-by-row form the prefill rungs use."""
     HV, HK, d = 48, 16, 128
@@ -192,6 +233,8 @@ CASES = {
     "attn_tc_decode_b1_w8_ctx131072": lambda: _attn(1, 8, 131072, 32, copies=2, impl=1),
     "attn_tc_prefill_2048_ctx4096": lambda: _attn(1, 2048, 2048, 1, impl=1),
     "gdn_rec_b8": lambda: _gdn(8, 9, 5),
+    "gdn_step_b8_w8": lambda: _gdn_step(8, 8, 4),
+    "gdn_step_b1_w8": lambda: _gdn_step(1, 8, 4),
     "gdn_prefill_2048": lambda: _gdn_prefill(2048),
     "row_add_rms_m72": lambda: _row(72, 5120),
     "moe_block_m72": lambda: _moe(72),

@@ -207,6 +207,8 @@ def create_app(state: ServerState) -> FastAPI:
         created = int(time.time())
         rec = {"id": rid, "created": created, "prompt_tokens": len(prompt_ids), "completion_tokens": 0,
                "stream": bool(body.get("stream")), "status": "running", "kind": "chat" if chat else "completion"}
+        if request.headers.get("x-saber-console-ref"):     # the console proxy's row id: its usage poll merges on it
+            rec["client_ref"] = request.headers["x-saber-console-ref"][:64]
         state.requests.append(rec)
         detok = IncrementalDetok(state.tok, skip_ids=[getattr(state.tok, "eos_token_id", -1)])
         stopper = StopStrings(stops)

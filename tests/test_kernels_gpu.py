@@ -208,6 +208,69 @@ def test_gdn_prefill_commit_then_decode():
     assert torch.equal(dev["hist"][1, :3].cpu().float(), allx[-3:])
 
 
+def test_gdn_fused_step_equals_the_three_launches_byte_for_byte():
+    """conv + recurrence + gated norm + quantisation in one launch, against the separate kernels, over
+    four steps with different accepted counts, a padding sequence, and a committing (prefill) step in
+    the middle that has to find the current conv window."""
+    nseq, W, HV, HK = 3, 5, 6, 2
+    s = _gdn_setup(nseq, W, HV=HV, HK=HK, seed=11)
+    n_q, n_k, Cc = s["n_q"], s["n_k"], s["C"]
+    K = HV * 128
+    conv_w, A_log, dt_bias = s["conv_w"].to(DEV), s["A_log"].to(DEV), s["dt_bias"].to(DEV)
+    norm_w = (torch.randn(128) * 0.2 + 1.0).to(DEV)
+    # reference arm: one window per slot, stash of one slice; fused arm: two windows + word
+    hist_a = s["hist"].to(DEV).clone()
+    hist_b = F.gdn_hist_alloc(s["nslots"], 3 + W, Cc, DEV)
+    hist_b[:, :3 + W] = hist_a
+    state_a, state_b = s["state"].to(DEV).clone(), s["state"].to(DEV).clone()
+    stash_a = torch.zeros(s["nslots"], W, HV, 1, 260, device=DEV)
+    stash_b = torch.zeros_like(stash_a)
+    slots = torch.tensor([2, -1, 1], dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0, W, 2 * W, 3 * W], dtype=torch.int32, device=DEV)
+    M = nseq * W
+    ld = Cc + K + 2 * HV
+    ld = (ld + 7) // 8 * 8
+
+    def both(x, shift):
+        sh = torch.tensor(shift, dtype=torch.int32, device=DEV)
+        ba = x[:, Cc + K:]
+        qkv = F.gdn_conv(x, conv_w, hist_a, cu, slots, sh, n_q, n_k)
+        o = F.gdn_recurrent(qkv, ba, A_log, dt_bias, state_a, stash_a, cu, slots, sh, n_q, n_k, HV, HK, vs=1)
+        qa_a = F.QuantAct.alloc(M, K, DEV)
+        qa_a.q.zero_(); qa_a.scale.zero_()
+        F._row(N.ROW_GDN_NORM, F.row_params(M, K, a_f32=o, b=x[:, Cc:], w=norm_w, eps=1e-6, qa=qa_a, ldb=ld))
+        qa_b = F.QuantAct.alloc(M, K, DEV)
+        qa_b.q.zero_(); qa_b.scale.zero_()
+        F.gdn_step(x, x[:, Cc:], ba, conv_w, A_log, dt_bias, norm_w, hist_b, state_b, stash_b, cu, slots, sh,
+                   qa_b, n_q, n_k, HV, HK, W)
+        torch.cuda.synchronize()
+        live = [m for m in range(M) if int(slots[m // W]) >= 0]
+        assert torch.equal(qa_a.q[:, live], qa_b.q[:, live])
+        assert torch.equal(qa_a.scale[live], qa_b.scale[live])
+        assert torch.equal(state_a, state_b) and torch.equal(stash_a, stash_b)
+
+    torch.manual_seed(3)
+    for shift in ([0, 0, 0], [3, 0, 1], [5, 0, 2]):
+        both(torch.randn(M, ld, device=DEV).to(torch.bfloat16), shift)
+    # the fused arm's current window is now window 1 of both live slots
+    words = hist_b[:, -1, :2].view(torch.int32).flatten().tolist()
+    assert words[1] == 1 and words[2] == 1 and words[0] == 0
+    # a committing step (the rows of a prompt chunk) reads the current window and leaves the new one in both
+    T = 7
+    xp = torch.randn(nseq * T, ld, device=DEV).to(torch.bfloat16)
+    cup = torch.tensor([0, T, 2 * T, 3 * T], dtype=torch.int32, device=DEV)
+    zero = torch.zeros(nseq, dtype=torch.int32, device=DEV)
+    # (bring the reference arm's committed state up to date first: its replay happens in the next launch)
+    qa_ = F.gdn_conv(xp, conv_w, hist_a, cup, slots, torch.tensor([1, 0, 4], dtype=torch.int32, device=DEV), n_q, n_k, commit=True)
+    qb_ = F.gdn_conv(xp, conv_w, hist_b, cup, slots, torch.tensor([1, 0, 4], dtype=torch.int32, device=DEV), n_q, n_k, commit=True, dual=True)
+    torch.cuda.synchronize()
+    livep = [m for m in range(nseq * T) if int(slots[m // T]) >= 0]
+    assert torch.equal(qa_[livep], qb_[livep])
+    for slot in (1, 2):
+        assert torch.equal(hist_a[slot, :3], hist_b[slot, :3]) and torch.equal(hist_a[slot, :3], hist_b[slot, 3 + W:6 + W])
+    both(torch.randn(M, ld, device=DEV).to(torch.bfloat16), [0, 0, 0])
+
+
 _LAST_GOT = []
 
 
