@@ -162,11 +162,17 @@ def build_engine(a):
         if a.engine_tp > 1:
             from ..parallel.tp_serve import TpLeaderExecutor, follower_loop
             if rank != 0:                # a follower never returns from here until the leader stops it
-                follower_loop(ex, a._tp_group)
+                import os
+                channel = alive = None
+                if getattr(a, "ctrl_line", None):
+                    from ..parallel.control_frames import ShmChannel
+                    from ..parallel.launcher import parent_alive
+                    channel, alive = ShmChannel(a.ctrl_line, a.engine_tp, rank, create=False), parent_alive(os.getppid())
+                follower_loop(ex, a._tp_group, channel=channel, alive=alive)
                 import torch.distributed as dist
                 dist.destroy_process_group()
                 raise SystemExit(0)
-            ex = TpLeaderExecutor(ex, a._tp_group)
+            ex = TpLeaderExecutor(ex, a._tp_group, channel=getattr(a, "_ctrl_channel", None))
     if a.engine_tp > 1 and (getattr(a, "prompt_cache_dir", None) or getattr(a, "park_dir", None)):
         raise SystemExit("saber: --prompt-cache-dir / --park-dir move one rank's shard only: not available with --engine-tp > 1")
     from ..sched.width import WidthByBatch
@@ -219,16 +225,28 @@ def build_engine(a):
 
 def cmd_engine(a) -> int:
     import os
+    holder = {"sched": None}
     if getattr(a, "engine", "") == "real" and getattr(a, "engine_tp", 1) > 1 and "RANK" not in os.environ:
-        # self-launch: one process per GPU, rendezvous on the loopback address
+        # self-launch: this process is rank 0, one watched child per further GPU, rendezvous on the
+        # loopback address; the control frames go over one shared-memory line per follower
+        from ..parallel.control_frames import ShmChannel
+        from ..parallel.launcher import launch_followers
+        from ..serve import fatal
         port = 29400 + (os.getpid() % 500)
-        os.execvp(sys.executable, [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
-                                   f"--nproc-per-node={a.engine_tp}", "--master-addr", "127.0.0.1",
-                                   "--master-port", str(port), "-m", "saber_engine_b200", *sys.argv[1:]])
+        a.ctrl_line = f"/saber-ctl-{os.getpid()}"
+        a._ctrl_channel = ShmChannel(a.ctrl_line, a.engine_tp, 0, create=True)
+
+        def follower_died(rank: int, why: str) -> None:
+            if holder["sched"] is not None:
+                holder["sched"].set_fatal(why)
+            fatal.set_fatal(rank, why, exit_process=True, watchdog_s=getattr(a, "fatal_watchdog_s", 10.0))
+        a._ranks = launch_followers([sys.executable, "-m", "saber_engine_b200", *sys.argv[1:], "--ctrl-line", a.ctrl_line],
+                                    a.engine_tp, port, follower_died)
     import uvicorn
     from ..serve.server import ServerState, create_app
     from ..serve.tokenizer import ByteCodec, HfTokenizer
     ex, sched = build_engine(a)
+    holder["sched"] = sched
     tok = HfTokenizer(str(Path(a.tokenizer).parent)) if a.tokenizer and Path(a.tokenizer).exists() else ByteCodec(ex.vocab)
     template = Path(a.chat_template).read_text() if a.chat_template and Path(a.chat_template).exists() else None
     vision = None
@@ -256,8 +274,13 @@ def cmd_engine(a) -> int:
         uvicorn.run(create_app(state), host=a.host, port=a.port, log_level="warning")
     finally:
         sched.shutdown()
+        if getattr(a, "_ranks", None) is not None:
+            a._ranks.expect_exit()
         if hasattr(ex, "stop_followers"):
             ex.stop_followers()
+        if getattr(a, "_ranks", None) is not None:
+            a._ranks.wait()
+            a._ctrl_channel.close()
     return 0
 
 
@@ -410,6 +433,7 @@ def make_parser() -> argparse.ArgumentParser:
     e.add_argument("--prompt-cache-dir", help="keep prefilled prefixes on this drive across restarts")
     e.add_argument("--park-ram-mib", type=int, default=8192)
     e.add_argument("--fatal-watchdog-s", type=float, default=10.0)
+    e.add_argument("--ctrl-line", default=None, help=argparse.SUPPRESS)      # set by the self-launch for its followers
     e.add_argument("--fail-rank-after-steps", default=None, metavar="R:N", help=argparse.SUPPRESS)
     x = sub.add_parser("explain")
     x.add_argument("--manifest")

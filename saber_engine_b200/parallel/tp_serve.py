@@ -35,17 +35,28 @@ def init_control_group(timeout_s: float = 1800.0):
 class TpLeaderExecutor:
     """Rank 0's executor: broadcasts each call to the followers, then runs it on the local shard."""
 
-    def __init__(self, inner, group, src: int = 0):
-        self.inner, self.group, self.src = inner, group, src
+    def __init__(self, inner, group, src: int = 0, channel=None):
+        """channel: a `control_frames.ShmChannel` (fixed-layout frames over shared memory, block tables
+        as deltas); without one every call is pickled through the gloo group."""
+        self.inner, self.group, self.src, self.channel = inner, group, src, channel
         self._snap_ids = itertools.count(1)
         self.calls_cast = 0
+        self.bytes_cast = 0
+        if channel is not None:
+            from .control_frames import FrameEncoder
+            self._enc = FrameEncoder()
 
     def __getattr__(self, name):                     # geometry, census, model, ...: the local executor's
         return getattr(self.inner, name)
 
     def _cast(self, name: str, *args) -> None:
-        import torch.distributed as dist
-        dist.broadcast_object_list([(name, args)], src=self.src, group=self.group)
+        if self.channel is not None:
+            parts = self._enc.encode(name, *args)
+            self.channel.send(parts)
+            self.bytes_cast += sum(len(p) for p in parts)
+        else:
+            import torch.distributed as dist
+            dist.broadcast_object_list([(name, args)], src=self.src, group=self.group)
         self.calls_cast += 1
 
     def prefill(self, runs: list) -> list:
@@ -90,16 +101,27 @@ class TpLeaderExecutor:
         self._cast("stop")
 
 
-def follower_loop(executor, group, src: int = 0, on_call=None) -> int:
+def follower_loop(executor, group, src: int = 0, on_call=None, channel=None, alive=None) -> int:
     """Runs the leader's calls on this rank's executor until the leader says stop.  Returns the number
-    of calls served."""
-    import torch.distributed as dist
+    of calls served.  With a channel the calls arrive as fixed-layout frames; `alive()` is asked while
+    the line is idle, and a follower whose leader is gone leaves with ConnectionError."""
     snaps: dict = {}
     served = 0
+    dec = None
+    if channel is not None:
+        from .control_frames import FrameDecoder
+        dec = FrameDecoder()
     while True:
-        box = [None]
-        dist.broadcast_object_list(box, src=src, group=group)
-        name, args = box[0]
+        if dec is not None:
+            call = None
+            while call is None:
+                call = dec.feed(channel.recv(alive=alive))
+            name, args = call
+        else:
+            import torch.distributed as dist
+            box = [None]
+            dist.broadcast_object_list(box, src=src, group=group)
+            name, args = box[0]
         if name == "stop":
             return served
         if name == "prefill":

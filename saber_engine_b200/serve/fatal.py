@@ -63,8 +63,9 @@ def reset_for_tests() -> None:
 class RankWatch:
     """Watches a child rank process: its exit (any code) or a FATAL line on stderr is fatal here."""
 
-    def __init__(self, proc: subprocess.Popen, rank: int, on_death: Callable):
-        self.proc, self.rank, self.on_death = proc, rank, on_death
+    def __init__(self, proc: subprocess.Popen, rank: int, on_death: Callable, tee=None):
+        """tee: a text stream that gets every stderr line of the child (its log is not swallowed)."""
+        self.proc, self.rank, self.on_death, self.tee = proc, rank, on_death, tee
         self.thread = threading.Thread(target=self._run, daemon=True)
         self.thread.start()
 
@@ -73,8 +74,15 @@ class RankWatch:
         if self.proc.stderr is not None:
             for line in self.proc.stderr:
                 line = line.decode(errors="replace") if isinstance(line, bytes) else line
-                if "saber: FATAL" in line:
+                if self.tee is not None:
+                    try:
+                        self.tee.write(line)
+                        self.tee.flush()
+                    except (OSError, ValueError):
+                        pass
+                if "saber: FATAL" in line and reason is None:
                     reason = line.strip()
-                    break
+                    if self.tee is None:
+                        break
         code = self.proc.wait()
         self.on_death(self.rank, reason or f"rank {self.rank} exited with code {code}")
