@@ -22,9 +22,34 @@ __device__ __forceinline__ unsigned long long ar_now_ns() {
   return t;
 }
 
-__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const AllReduceParams p) {
-  pdl_wait();
-  const int b = blockIdx.x, tid = threadIdx.x;
+// ---- race-check helpers (checked twin only)
+__device__ __forceinline__ uint32_t chk_mix(uint32_t h) {
+  h ^= h >> 15; h *= 0x2c1b3c6du; h ^= h >> 12; h *= 0x297a2d39u; h ^= h >> 15;
+  return h;
+}
+// hash of one pushed 16-byte word, keyed by its position in the message and the call's sequence
+__device__ __forceinline__ uint32_t chk_word16(const uint4& w, uint32_t pos, uint32_t seq) {
+  uint32_t h = chk_mix(pos * 0x9e3779b9u + seq);
+  h = chk_mix(h ^ w.x); h = chk_mix(h ^ w.y); h = chk_mix(h ^ w.z); h = chk_mix(h ^ w.w);
+  return h;
+}
+__device__ __forceinline__ uint32_t block_xor(uint32_t v, uint32_t* sh) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v ^= __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  uint32_t r = 0;
+  for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) r ^= sh[i];
+  return r;
+}
+
+// One block's share of the all-reduce.  kCheck = the checked twin: the pushes, the handshake, the
+// reduce and the stores are the served code; the check words and counters ride beside them.
+template <bool kCheck>
+__device__ __forceinline__ void ar_body(const AllReduceParams& p, const int b) {
+  __shared__ uint32_t xsh[17];   // 16 warp words of the block XOR + one decision word
+  const int tid = threadIdx.x;
   const uint32_t seq = *p.seq_base + static_cast<uint32_t>(p.site) + 1u;
   const uint32_t par = seq & 1u;
   const int nvec = p.n_elems >> 3;
@@ -32,12 +57,22 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const AllReduceP
   const int v0 = b * per, v1 = min(nvec, v0 + per);
   const uint4* src = reinterpret_cast<const uint4*>(p.in);
   const size_t slot_vecs = static_cast<size_t>(p.max_elems) >> 3;
+  // check word of (slot, block): the slot's last kArBlocks words
+  auto chk_at = [&](void* recv, int from_rank) -> uint32_t* {
+    return reinterpret_cast<uint32_t*>(reinterpret_cast<uint4*>(recv) + (par * p.nranks + from_rank + 1) * slot_vecs) - kArBlocks + b;
+  };
 
   // push
+  uint32_t hx = 0;
   for (int peer = 0; peer < p.nranks; ++peer) {
     if (peer == p.rank) continue;
     uint4* dst = reinterpret_cast<uint4*>(p.peer_recv[peer]) + (par * p.nranks + p.rank) * slot_vecs;
     for (int v = v0 + tid; v < v1; v += blockDim.x) dst[v] = src[v];
+  }
+  if constexpr (kCheck) {
+    for (int v = v0 + tid; v < v1; v += blockDim.x) hx ^= chk_word16(src[v], static_cast<uint32_t>(v), seq);
+    hx = block_xor(hx, xsh);
+    if (tid < p.nranks && tid != p.rank && !p.chk_fault) *chk_at(p.peer_recv[tid], p.rank) = hx;
   }
   __threadfence_system();
   __syncthreads();
@@ -50,10 +85,20 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const AllReduceP
     const unsigned long long limit =
         (p.spin_limit_us ? static_cast<unsigned long long>(p.spin_limit_us) : 1000000ull) * 1000ull;
     const unsigned long long t0 = ar_now_ns();
+    bool timed_out = false;
     while (static_cast<int32_t>(ld_acquire_sys(f) - seq) < 0) {
       if (ar_now_ns() - t0 > limit) {
         atomicCAS(p.err, 0u, 5u);
+        timed_out = true;
         break;
+      }
+    }
+    if constexpr (kCheck) {
+      if (timed_out) {
+        atomicAdd(p.diag + kArDTimeout, 1u);
+      } else {
+        const uint32_t now = ld_acquire_sys(f);      // lockstep: == seq; the peer already in the next call of this parity: ahead
+        if (now != seq) atomicAdd(p.diag + (static_cast<int32_t>(now - seq) > 0 ? kArDAhead : kArDDrift), 1u);
       }
     }
   }
@@ -62,10 +107,18 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const AllReduceP
   // reduce in rank order
   const uint4* own_recv = reinterpret_cast<const uint4*>(p.peer_recv[p.rank]);
   uint4* dst = reinterpret_cast<uint4*>(p.out);
+  uint32_t hr[kMaxRanks];
+#pragma unroll
+  for (int s = 0; s < kMaxRanks; ++s) hr[s] = 0;
   for (int v = v0 + tid; v < v1; v += blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int s = 0; s < p.nranks; ++s) {
+#pragma unroll
+    for (int s = 0; s < kMaxRanks; ++s) {
+      if (s >= p.nranks) break;
       const uint4 raw = (s == p.rank) ? src[v] : __ldcg(own_recv + (par * p.nranks + s) * slot_vecs + v);
+      if constexpr (kCheck) {
+        if (s != p.rank) hr[s] ^= chk_word16(raw, static_cast<uint32_t>(v), seq);
+      }
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -80,6 +133,71 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const AllReduceP
     for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
     dst[v] = o;
   }
+  if constexpr (kCheck) {
+    if (tid == 0) {
+      atomicAdd(p.diag + kArDBlocks, 1u);
+      if (b == 0) p.diag[kArDLastSeq] = seq;
+    }
+#pragma unroll
+    for (int s = 0; s < kMaxRanks; ++s) {
+      if (s >= p.nranks) break;
+      if (s == p.rank) continue;
+      const uint32_t got = block_xor(hr[s], xsh);
+      const uint32_t* cw = chk_at(p.peer_recv[p.rank], s);
+      // ONE thread reads the check word and decides for the block (the word may still be changing:
+      // every thread reading it for itself could split the block across the barriers below)
+      __syncthreads();
+      if (tid == 0) xsh[16] = (got == ld_acquire_sys(cw)) ? 1u : 0u;
+      __syncthreads();
+      if (xsh[16]) continue;
+      if (tid == 0) {
+        if (atomicAdd(p.diag + kArDMismatch, 1u) == 0u) {
+          p.diag[kArDFirstSeq] = seq; p.diag[kArDFirstBlock] = b; p.diag[kArDFirstSrc] = s;
+        }
+      }
+      // diagnostic re-read at system scope: the reduce already used the first read
+      uint32_t conv = 0;
+      int polls = 0;
+      for (; polls < kArProbeMax && !conv; ++polls) {
+        __nanosleep(200);
+        uint32_t h2 = 0;
+        for (int v = v0 + tid; v < v1; v += blockDim.x) {
+          uint4 w;
+          const uint4* a = own_recv + (par * p.nranks + s) * slot_vecs + v;
+          asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w) : "l"(a) : "memory");
+          h2 ^= chk_word16(w, static_cast<uint32_t>(v), seq);
+        }
+        h2 = block_xor(h2, xsh);
+        __syncthreads();
+        if (tid == 0) xsh[16] = (h2 == ld_acquire_sys(cw)) ? 1u : 0u;
+        __syncthreads();
+        conv = xsh[16];
+      }
+      if (tid == 0) {
+        atomicAdd(p.diag + (conv ? kArDConverged : kArDNever), 1u);
+        atomicMax(p.diag + kArDPolls, static_cast<uint32_t>(polls));
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const AllReduceParams p) {
+  pdl_wait();
+  ar_body<false>(p, blockIdx.x);
+}
+
+// the checked twin: the served body with the race checks around it
+__global__ void __launch_bounds__(512) allreduce_oneshot_chk_kernel(const AllReduceParams p) {
+  pdl_wait();
+  ar_body<true>(p, blockIdx.x);
+}
+
+// Test form for a one-device group: block (rank, b) runs rank's share, all ranks in ONE cooperative
+// launch (blocks that wait on one another must be resident together).
+__global__ void __launch_bounds__(512) allreduce_emul_kernel(const __grid_constant__ ArEmulParams e) {
+  const int r = blockIdx.x / kArBlocks, b = blockIdx.x % kArBlocks;
+  if (e.checked) ar_body<true>(e.r[r], b);
+  else ar_body<false>(e.r[r], b);
 }
 
 __global__ void __launch_bounds__(1024) pick_merge_kernel(const PickMergeParams p) {
@@ -139,6 +257,33 @@ extern "C" int saber_allreduce_launch(const saber::AllReduceParams* p, cudaStrea
     return 0;
   }
   saber::launch(allreduce_oneshot_kernel, dim3(kArBlocks), dim3(512), 0, stream, 0, *p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int saber_allreduce_chk_launch(const saber::AllReduceParams* p, cudaStream_t stream) {
+  using namespace saber;
+  // a checked message leaves the slot's last kArBlocks words (16 bf16 each pair of words) to the check words
+  if (p->nranks < 2 || p->nranks > kMaxRanks || (p->n_elems & 7) || p->n_elems > p->max_elems - 2 * kArBlocks || !p->diag)
+    return static_cast<int>(cudaErrorInvalidValue);
+  saber::launch(allreduce_oneshot_chk_kernel, dim3(kArBlocks), dim3(512), 0, stream, 0, *p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int saber_allreduce_emul_launch(const saber::ArEmulParams* e, cudaStream_t stream) {
+  using namespace saber;
+  if (e->nranks < 2 || e->nranks > kMaxRanks) return static_cast<int>(cudaErrorInvalidValue);
+  for (int r = 0; r < e->nranks; ++r) {
+    const AllReduceParams& p = e->r[r];
+    if ((p.n_elems & 7) || p.n_elems > p.max_elems - (e->checked ? 2 * kArBlocks : 0) || (e->checked && !p.diag))
+      return static_cast<int>(cudaErrorInvalidValue);
+  }
+  // every block of every rank must be resident: refuse a device that cannot hold the grid at once
+  int dev = 0, sms = 0, per_sm = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, allreduce_emul_kernel, 512, 0);
+  if (sms * per_sm < e->nranks * kArBlocks) return static_cast<int>(cudaErrorCooperativeLaunchTooLarge);
+  saber::launch(allreduce_emul_kernel, dim3(e->nranks * kArBlocks), dim3(512), 0, stream, 1, *e);
   return static_cast<int>(cudaGetLastError());
 }
 

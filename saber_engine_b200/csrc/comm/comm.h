@@ -30,6 +30,26 @@ struct AllReduceParams {
   uint32_t* err;
   int n_elems, max_elems, site, nranks, rank;
   uint32_t spin_limit_us;       // 0 = default bound
+  // checked twin only (the served kernel reads none of these):
+  uint32_t* diag;               // [kArDiagWords] LOCAL words the peers never write (see kArD* below)
+  int chk_fault;                // test control: 1 = this rank pushes its payload but no check word
+};
+
+// Race check of the all-reduce (the checked twin computes the served bytes and, beside them, these
+// counters).  The sender XORs a position- and sequence-keyed hash of every 16-byte word it pushes into
+// one check word per block at the TAIL of the peer's slot (the last kArBlocks words of a slot: a
+// checked message must leave them free); the receiver hashes what it READ after the flag and
+// compares.  A mismatch is a read of data the peer had not landed: it is counted, its first (sequence,
+// block, source) is kept, and the piece is re-read at system scope for at most kArProbeMax polls to
+// tell "landed late" (converges) from "another call's data" (never).  The re-read is a diagnostic only.
+constexpr int kArDiagWords = 16;
+constexpr int kArProbeMax = 256;
+constexpr int kArDBlocks = 0, kArDMismatch = 1, kArDConverged = 2, kArDNever = 3, kArDAhead = 4, kArDDrift = 5,
+              kArDTimeout = 6, kArDFirstSeq = 8, kArDFirstBlock = 9, kArDFirstSrc = 10, kArDPolls = 11, kArDLastSeq = 12;
+
+struct ArEmulParams {           // test form: every rank of a one-device group in ONE cooperative launch
+  AllReduceParams r[kMaxRanks];
+  int nranks, checked;
 };
 
 // Vocab-parallel head: every rank holds (value, id) of its shard's best token per row; the ranks
@@ -48,6 +68,8 @@ struct PickMergeParams {
 
 extern "C" int saber_pick_merge_launch(const saber::PickMergeParams* p, cudaStream_t stream);
 extern "C" int saber_allreduce_launch(const saber::AllReduceParams* p, cudaStream_t stream);
+extern "C" int saber_allreduce_chk_launch(const saber::AllReduceParams* p, cudaStream_t stream);
+extern "C" int saber_allreduce_emul_launch(const saber::ArEmulParams* p, cudaStream_t stream);
 extern "C" int saber_comm_advance_launch(uint32_t* seq_base, uint32_t by, cudaStream_t stream);
 extern "C" int saber_ipc_get_handle(void* dev_ptr, void* out_handle_64);
 extern "C" int saber_ipc_open_handle(const void* handle_64, void** out_ptr);

@@ -138,6 +138,7 @@ class HybridModel:
         if self.gdn_fused:
             gdn_vs = 1
         self.gdn_vs = gdn_vs
+        self.step_timeout_s = 120.0         # host-side deadline of one step (graph capture and first launches included)
         self.use_drafter = use_drafter and cfg.drafter is not None
         self.w = weights if weights is not None else random_init(cfg, tp, rank, self.device, seed)
         self.scratch = F.scratch(self.device)
@@ -314,18 +315,11 @@ class HybridModel:
         return 0
 
     def attn_splits(self, nseq: int, width: int = 16) -> int:
-        """KV splits of the decode attention: fill the GPU once.  The kernel runs two CTAs per SM;
-        a CTA holds up to four 16-row tiles and a tile holds floor(16 / width) heads of a GQA group."""
-        group = self.sh.n_q_heads // self.sh.n_kv_heads
-        if self.attn_impl == "tc":        # one CTA per SM, a CTA = (sequence, KV head, key segment): fill the GPU once
-            if width > 16 or width * group > 128:
-                return 1
-            return max(1, min(32, 148 // max(1, nseq * self.sh.n_kv_heads)))
-        hpt = min(group, 16 // width) if 1 <= width <= 8 else 1
-        tiles = -(-group // hpt)
-        hgroups = -(-tiles // 4)
-        ctas = nseq * self.sh.n_kv_heads * hgroups
-        return max(1, min(32, (2 * 148) // ctas))
+        """KV splits of the decode attention: fill the GPU once (the `decode_splits` law of the launch
+        rules, per attention kernel)."""
+        from ..rules import default_rules
+        return default_rules().attn_decode_splits(self.attn_impl, nseq, self.sh.n_kv_heads,
+                                                  self.sh.n_q_heads // self.sh.n_kv_heads, width)
 
     def tap_layers(self) -> list:
         n = self.cfg.drafter.n_taps if self.cfg.drafter else 0
@@ -759,7 +753,10 @@ def run_bucket(model: "HybridModel", b: Bucket, seqs: list, eager: bool = False)
             b.seam_host.copy_(b.seam_dev, non_blocking=True)
         if getattr(b, "plp_dev", None) is not None:
             b.plp_host.copy_(b.plp_dev, non_blocking=True)
-    st.synchronize()
+    # bounded: a step that never completes (a kernel wait that did not run out, a lost peer) raises,
+    # and the scheduler's fatal law ends the engine instead of leaving this thread blocked
+    from ..runtime.device_rt import bounded_wait
+    bounded_wait(st, model.step_timeout_s, f"the {b.kind} step")
     return parse_result(b, len(seqs))
 
 

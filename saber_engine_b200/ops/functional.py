@@ -142,17 +142,11 @@ def scratch(device) -> GemmScratch:
     return _SCRATCH[key]
 
 
-def pick_splits(n_tiles: int, m_tiles: int, kb: int, sms: int = 148) -> int:
-    """Split-K factor that fills the SMs when the tile grid alone does not.  The GEMM runs one CTA
-    per SM, so the target is ONE wave: tiles x splits <= SMs (a second, partial wave costs more
-    than the parallelism gains)."""
-    ctas = n_tiles * m_tiles
-    if ctas * 2 > sms or kb < 8:
-        return 1
-    s = min(sms // ctas, max(1, kb // 4), 8)
-    while s > 1 and (s - 1) * math.ceil(kb / s) >= kb:
-        s -= 1
-    return max(1, s)
+def pick_splits(n_tiles: int, m_tiles: int, kb: int, sms: Optional[int] = None) -> int:
+    """Split-K factor that fills the SMs when the tile grid alone does not: the law and its numbers
+    are the `[gemm.splits]` table of the launch rules (one wave, at most 8 parts, no empty part)."""
+    from ..rules import default_rules
+    return default_rules().gemm_splits(n_tiles, m_tiles, kb)
 
 
 def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,
@@ -219,11 +213,12 @@ def gemm_i8(w: QuantWeight, a: QuantAct, out: Optional[torch.Tensor] = None,
     return out
 
 
-def pick_halves(w: QuantWeight, n_tiles: int, m_tiles: int, sms: int = 148) -> bool:
-    """Half tiles instead of split-K: packed int4 weights whose whole-tile grid fills between a
-    quarter and a half of the SMs."""
-    ctas = n_tiles * m_tiles
-    return bool(w.w4 and not w.mx and sms // 4 < ctas <= sms // 2)
+def pick_halves(w: QuantWeight, n_tiles: int, m_tiles: int, sms: Optional[int] = None) -> bool:
+    """Half tiles instead of split-K (`[gemm.halves]` of the launch rules): packed int4 weights whose
+    whole-tile grid fills between a quarter and a half of the SMs."""
+    from ..rules import default_rules
+    fmt = "mxfp4" if getattr(w, "mx", False) else ("int4" if w.w4 else "int8")
+    return default_rules().gemm_halves(fmt, n_tiles, m_tiles)
 
 
 def row_params(M: int, K: int, *, a=None, a_f32=None, b=None, res=None, w=None, w_offset=0.0,

@@ -105,7 +105,15 @@ class VerifyParams(C.Structure):
 class AllReduceParams(C.Structure):
     _fields_ = [("inp", P), ("out", P), ("peer_recv", P * MAX_RANKS), ("peer_flags", P * MAX_RANKS),
                 ("seq_base", P), ("err", P), ("n_elems", I), ("max_elems", I), ("site", I),
-                ("nranks", I), ("rank", I), ("spin_limit_us", U32)]
+                ("nranks", I), ("rank", I), ("spin_limit_us", U32), ("diag", P), ("chk_fault", I)]
+
+
+class ArEmulParams(C.Structure):
+    _fields_ = [("r", AllReduceParams * MAX_RANKS), ("nranks", I), ("checked", I)]
+
+
+AR_DIAG = {"blocks": 0, "mismatch": 1, "converged": 2, "never": 3, "ahead": 4, "drift": 5, "timeout": 6,
+           "first_seq": 8, "first_block": 9, "first_src": 10, "polls": 11, "last_seq": 12}
 
 
 class PickMergeParams(C.Structure):
@@ -195,6 +203,8 @@ def _declare(L: C.CDLL) -> None:
         "saber_topk_seam_launch": (I, [P, I, I, I, I, P, P, P, P, S]),
         "saber_verify_launch": (I, [C.POINTER(VerifyParams), S]),
         "saber_allreduce_launch": (I, [C.POINTER(AllReduceParams), S]),
+        "saber_allreduce_chk_launch": (I, [C.POINTER(AllReduceParams), S]),
+        "saber_allreduce_emul_launch": (I, [C.POINTER(ArEmulParams), S]),
         "saber_pick_merge_launch": (I, [C.POINTER(PickMergeParams), S]),
         "saber_program_add_pick_merge": (I, [P, C.POINTER(PickMergeParams), C.c_char_p]),
         "saber_comm_advance_launch": (I, [P, U32, S]),

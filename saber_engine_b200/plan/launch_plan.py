@@ -168,7 +168,9 @@ class LaunchPlan:
 
     def explain(self) -> str:
         m = self.manifest
-        out = [f"plan {self.plan_hash[:16]}  model={m.model} tp={m.tp} device={self.device.name}",
+        from ..rules import default_rules
+        out = [f"plan {self.plan_hash[:16]}  model={m.model} tp={m.tp} device={self.device.name}  "
+               f"rules={default_rules().doc['name']}@{default_rules().policy_digest()[:12]}",
                f"  context {m.max_ctx} tokens x {m.max_seqs} sequences; decode batches {list(m.decode_batches)} x widths {list(m.decode_widths)}; prefill rungs {list(m.prefill_rows)}",
                "  ledger (bytes per rank):"]
         for name, b in self.ledger.table():
@@ -232,8 +234,10 @@ def resolve(manifest: Manifest, device: Optional[DeviceProfile] = None, table: O
                          f"raise budget_mib or lower max_ctx"])
     cap = manifest.max_seqs * need + 1        # never larger than every sequence at full context
     kv_blocks = min(kv_blocks, cap) if block_bytes else 0
+    from ..rules import default_rules
     desc = {"manifest": {k: (list(v) if isinstance(v, tuple) else v) for k, v in asdict(manifest).items()},
-            "routes": {k: v["variant"] for k, v in routes.items()}, "kv_blocks": kv_blocks}
+            "routes": {k: v["variant"] for k, v in routes.items()}, "kv_blocks": kv_blocks,
+            "rules": default_rules().policy_digest()}
     plan = LaunchPlan(manifest, device, routes, led, kv_blocks, kv_blocks * cfg.page_tokens, missing,
                       hashlib.sha256(json.dumps(desc, sort_keys=True).encode()).hexdigest())
     plan._block_bytes = block_bytes

@@ -179,6 +179,12 @@ class HybridExecutor:
         if isinstance(snap, dict):
             snap.clear()
 
+    def copy_lane(self):
+        if getattr(self, "_lane", None) is None:
+            from .device_rt import CopyLane
+            self._lane = CopyLane(self.model.device)
+        return self._lane
+
     # ---- session parking: KV pages + the slot's recurrent state and conv window as one image
     def export_session(self, slot: int, blocks: list, n_tokens: int):
         """(header, payload): every tensor of the sequence, in a declared order, read back over a
@@ -187,22 +193,21 @@ class HybridExecutor:
         npages = (n_tokens + self.page_tokens - 1) // self.page_tokens
         idx = torch.tensor(blocks[:npages], dtype=torch.long, device=m.device)
         parts, layout, off = [], [], 0
-        with torch.cuda.stream(m.stream):
-            def add(name, t):
-                nonlocal off
-                raw = t.contiguous().view(torch.uint8).reshape(-1)
-                host = torch.empty(raw.numel(), dtype=torch.uint8).pin_memory()
-                host.copy_(raw, non_blocking=True)
-                layout.append((name, str(t.dtype), list(t.shape), off, raw.numel()))
-                parts.append(host)
-                off += raw.numel()
-            for i, kv in m.kv.items():
-                add(f"kv.{i}", kv[idx])
+        lane = self.copy_lane()
+        with torch.cuda.stream(m.stream):          # the gathers run on the step stream (ordered after the last step) ...
+            staged = [(f"kv.{i}", kv[idx]) for i, kv in m.kv.items()]
             for i in m.gdn_state:
-                add(f"gdn_state.{i}", m.gdn_state[i][slot])
-                add(f"gdn_stash.{i}", m.gdn_stash[i][slot])
-                add(f"gdn_hist.{i}", m.gdn_hist[i][slot])
-            m.stream.synchronize()
+                staged += [(f"gdn_state.{i}", m.gdn_state[i][slot].clone()), (f"gdn_stash.{i}", m.gdn_stash[i][slot].clone()),
+                           (f"gdn_hist.{i}", m.gdn_hist[i][slot].clone())]
+        lane.after(m.stream)                       # ... and the bytes leave on the copy lane: later steps do not wait for them
+        for name, t in staged:
+            raw = t.contiguous().view(torch.uint8).reshape(-1)
+            host = lane.pinned(raw.numel(), tag=f"export.{name}")
+            lane.d2h(host, raw)
+            layout.append((name, str(t.dtype), list(t.shape), off, raw.numel()))
+            parts.append(host)
+            off += raw.numel()
+        lane.wait(self.model.step_timeout_s)
         payload = b"".join(p.numpy().tobytes() for p in parts)
         return {"kind": "hybrid", "n_tokens": n_tokens, "npages": npages, "tensors": layout}, payload
 

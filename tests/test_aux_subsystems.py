@@ -241,3 +241,22 @@ def test_index_blob_carries_positions_successors_and_sampling_rows():
     assert a[lay.pos + 16: lay.pos + 21].tolist() == [0, 1, 2, 2, 3] and a[lay.pos + 32 + 3] == 3
     assert a[lay.next_ids: lay.next_ids + 7].tolist() == [2, 3, 4, 5, 77, 7, -1]
     assert f[lay.samp] == 0.0 and np.allclose(f[lay.samp + 4: lay.samp + 8], [1.0, 0.0, 1.0, 0.0]) and f[lay.samp_u + 1] == 0.5
+
+
+def test_bounded_host_wait_returns_or_raises_by_its_deadline():
+    """A fake of the failing call: an event that completes after a few polls, and one that never does."""
+    import time
+    from saber_engine_b200.runtime.device_rt import DeviceWaitTimeout, bounded_wait
+
+    class Ev:
+        def __init__(self, after):
+            self.n, self.after = 0, after
+
+        def query(self):
+            self.n += 1
+            return self.n > self.after
+    assert bounded_wait(Ev(5), 1.0, "a step") < 0.5
+    t0 = time.perf_counter()
+    with pytest.raises(DeviceWaitTimeout) as ei:
+        bounded_wait(Ev(10 ** 12), 0.15, "the decode step", spin_s=0.02)
+    assert 0.15 <= time.perf_counter() - t0 < 1.0 and "decode step" in str(ei.value)

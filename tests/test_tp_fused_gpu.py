@@ -180,3 +180,59 @@ def test_allgather_wait_runs_out_cleanly_when_no_owner_pushes():
         g.check()
     assert float((torch.ones(4, device=DEV) * 2).sum()) == 8.0
     group[0].close()
+
+
+def _ar_emul(group, xs, checked, fault_rank=None, advance=True):
+    """All emulated ranks of a one-device group through ONE cooperative launch."""
+    n = len(group)
+    outs = [torch.empty_like(x) for x in xs]
+    diags = [torch.zeros(16, dtype=torch.int32, device=DEV) for _ in range(n)]
+    e = N.ArEmulParams()
+    e.nranks, e.checked = n, int(checked)
+    for r, g in enumerate(group):
+        p = g.allreduce_params(xs[r], outs[r], xs[r].numel(), site=0)
+        p.diag, p.chk_fault = diags[r].data_ptr(), int(fault_rank == r)
+        e.r[r] = p
+    N.check(N.lib().saber_allreduce_emul_launch(C.byref(e), N.stream_handle()), "allreduce (emulated ranks)")
+    if advance:
+        for g in group:
+            g.seq_base += 1              # one call site per "program run"
+    torch.cuda.synchronize()
+    return outs, [{k: int(d[i]) for k, i in N.AR_DIAG.items()} for d in diags]
+
+
+@pytest.mark.parametrize("nranks", [2, 4, 8])
+def test_allreduce_checked_twin_computes_the_served_bytes_and_counts_a_missing_check_word(nranks):
+    """The one-shot all-reduce with every rank in one cooperative launch: the checked twin gives the
+    served bytes and clean counters; a rank that pushes its payload but no check word (the control)
+    is found by every other rank -- first source recorded, the re-read never converges within its
+    bound -- and the reduced bytes are still the served ones."""
+    n_elems = 32 * 512 * 8 - 64           # a checked message leaves the slot's last 32 words free
+    group = SymmetricComm.local_group(nranks, DEV, max_elems=32 * 512 * 8, rows_max=128, hidden=256)
+    torch.manual_seed(nranks)
+    xs = [(torch.randn(n_elems, device=DEV) * 0.5).to(torch.bfloat16) for _ in range(nranks)]
+    want = torch.zeros(n_elems, device=DEV)
+    for x in xs:
+        want += x.float()
+    want = want.to(torch.bfloat16)
+    served, _ = _ar_emul(group, xs, checked=False)
+    for o in served:
+        assert torch.equal(o, want)                       # fp32 sum in rank order, the same on every rank
+    for call in range(3):                                 # both parities of the slots
+        outs, diag = _ar_emul(group, xs, checked=True)
+        for r in range(nranks):
+            assert torch.equal(outs[r], want)
+            d = diag[r]
+            assert d["blocks"] == 32 and d["mismatch"] == d["never"] == d["drift"] == d["timeout"] == 0, d
+    bad = 1
+    outs, diag = _ar_emul(group, xs, checked=True, fault_rank=bad)
+    for r in range(nranks):
+        assert torch.equal(outs[r], want)
+        d = diag[r]
+        if r == bad:
+            assert d["mismatch"] == 0
+        else:
+            assert d["mismatch"] == 32 and d["never"] == 32 and d["converged"] == 0 and d["first_src"] == bad and d["polls"] == 256, d
+    for g in group:
+        g.check()
+    group[0].close()
