@@ -94,7 +94,11 @@ __device__ __forceinline__ void grid_depart(uint32_t* ctr, uint32_t n_ctas) {
 // start-up latency (cold weights: 3-4 us to the first MMA) and epilogue.
 // kBf: the bf16 x bf16 instantiation (optional scales, bias, activation / residual epilogue); the
 // integer and MXFP4 instantiations compile none of it.
-template <bool kLean, bool kBf = false>
+// kFp4: native block-scaled FP4 x FP4 (tcgen05.mma kind::mxf4nvf4 / kind::mxf4): both operands stay
+// packed e2m1 in shared memory (a 32 KiB stage is 256 features x 256 k), their block scales ride
+// behind the tiles, are copied into tensor memory by tcgen05.cp and applied by the tensor core; no
+// transform warps, fp32 accumulators, the per-token and per-tensor scales in the epilogue.
+template <bool kLean, bool kBf = false, bool kFp4 = false>
 __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int stages, const RowOpParams* tail) {
   const int nub = (kLean || p.mtiles == 2) ? 2 : kUBufs;     // operand buffers in use
   extern __shared__ uint8_t smem_raw[];
@@ -153,10 +157,16 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
   const int n0 = tile_n * 256 + half * 128;
   // weight formats: 0 = int8 tiles, 1 = packed int4, 2 = MXFP4 (packed e2m1 + 1 KiB of block shifts)
   // 3 = bf16 x bf16: both operands pass through like int8 tiles (K counted in bytes), fp32 accumulators
-  const bool mx = !kBf && p.w4 == 2;
+  const bool mx = !kBf && !kFp4 && p.w4 == 2;
   constexpr bool bf = kBf;
-  const bool widen = !kBf && p.w4 != 0;
-  const uint32_t wbytes = mx ? 17408u : (widen ? 16384u : 32768u);
+  const bool widen = !kBf && !kFp4 && p.w4 != 0;
+  // FP4: w4 = 4 is NVFP4 (e4m3 scale per 16 values: 16 scales per row and k-block), 5 is MXFP4 (e8m0 per 32: 8).
+  // Scales are stored as 512-byte atoms (128 rows x 4 scales, byte (r % 32) * 16 + (r / 32) * 4 + s):
+  // the shape tcgen05.cp moves into four tensor-memory columns.
+  const bool nv = kFp4 && p.w4 == 4;
+  const uint32_t sf_atoms = nv ? 4u : 2u;                   // atoms along K per k-block and 128 rows
+  const uint32_t sfa_bytes = kFp4 ? sf_atoms * 512u : 0u;   // tokens: one 128-row chunk
+  const uint32_t wbytes = kFp4 ? 32768u + 2u * sf_atoms * 512u : (mx ? 17408u : (widen ? 16384u : 32768u));
   const uint32_t abytes = static_cast<uint32_t>(p.nt) * 128u * static_cast<uint32_t>(mt2);
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -164,12 +174,13 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
   const uint32_t a_smem = smem_base;
   const uint32_t u_smem = smem_base + static_cast<uint32_t>(stages) * abytes;
   const uint32_t w_smem = u_smem + (widen ? nub * kTileBytes : 0u);
+  const uint32_t sfa_smem = w_smem + static_cast<uint32_t>(stages) * wbytes;     // FP4: token scales, one 128-row chunk per stage
   const uint32_t bar_full = smem_u32(&bars[0]);
   const uint32_t bar_empty = smem_u32(&bars[kMaxStages]);
   const uint32_t bar_ready = smem_u32(&bars[2 * kMaxStages]);           // kUBufs
   const uint32_t bar_ufree = smem_u32(&bars[2 * kMaxStages + kUBufs]);  // kUBufs
   const uint32_t bar_acc = smem_u32(&bars[2 * kMaxStages + 2 * kUBufs]);
-  const uint32_t kTmemCols = (!kLean && p.mtiles == 2) ? 512u : 256u;
+  const uint32_t kTmemCols = (kFp4 || (!kLean && p.mtiles == 2)) ? 512u : 256u;     // FP4: 256 accumulator + 2 x 48 scale columns
   constexpr int kMaxSplits = 8;   // split-K factor the reduction is unrolled for
 
   if (threadIdx.x == 0) {
@@ -202,6 +213,9 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
       const uint8_t* wp = w_base + (static_cast<size_t>(tile_n) * KB + kb0) * wbytes;
       const int8_t* ap = p.a + (static_cast<size_t>(kb0) * p.M_pad + m0) * 128;
       const size_t a_kb_stride = static_cast<size_t>(p.M_pad) * 128;
+      // FP4: the token scales of this CTA's 128-row chunk, one run of atoms per k-block
+      const size_t sf_kb_stride = static_cast<size_t>((p.M_pad + 127) >> 7) * sfa_bytes;
+      const uint8_t* sfp = kFp4 ? p.a_sf + static_cast<size_t>(kb0) * sf_kb_stride + static_cast<size_t>(m0 >> 7) * sfa_bytes : nullptr;
       int issued = 0, s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -209,7 +223,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
       // predecessor kernel (which produced them) has completed
       const int pre = min(stages, nkb);
       for (int it = 0; it < pre; ++it) {
-        mbar_arrive_expect_tx(bar_full + 8 * it, wbytes + abytes);
+        mbar_arrive_expect_tx(bar_full + 8 * it, wbytes + abytes + sfa_bytes);
         bulk_g2s_hint(w_smem + it * wbytes, wp, wbytes, bar_full + 8 * it, pol);
         wp += wbytes;
         if (it == 0) SABER_STAMP(2);
@@ -238,14 +252,22 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
       for (int it = 0; it < pre; ++it) {
         bulk_g2s(a_smem + it * abytes, ap, abytes, bar_full + 8 * it);
         ap += a_kb_stride;
+        if constexpr (kFp4) {
+          bulk_g2s(sfa_smem + it * sfa_bytes, sfp, sfa_bytes, bar_full + 8 * it);
+          sfp += sf_kb_stride;
+        }
       }
       issued = pre;
       if (pre == stages) { s = 0; ph = 1u; } else { s = pre; }
       for (int it = pre; it < nkb; ++it) {
         if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, p.err, kErrWaitEmpty)) { ok = false; break; }
-        mbar_arrive_expect_tx(bar_full + 8 * s, wbytes + abytes);
+        mbar_arrive_expect_tx(bar_full + 8 * s, wbytes + abytes + sfa_bytes);
         bulk_g2s_hint(w_smem + s * wbytes, wp, wbytes, bar_full + 8 * s, pol);
         bulk_g2s(a_smem + s * abytes, ap, abytes, bar_full + 8 * s);
+        if constexpr (kFp4) {
+          bulk_g2s(sfa_smem + s * sfa_bytes, sfp, sfa_bytes, bar_full + 8 * s);
+          sfp += sf_kb_stride;
+        }
         wp += wbytes;
         ap += a_kb_stride;
         issued = it + 1;
@@ -292,7 +314,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
           w_addr = u_smem + u * kTileBytes;
         } else {
           if (!mbar_wait(bar_full + 8 * s, ph, p.err, kErrWaitReady)) { ok = false; break; }
-          w_addr = w_smem + s * kTileBytes;
+          w_addr = w_smem + s * wbytes;
         }
         tc_fence_after_sync();
         if (it == 0) SABER_STAMP(5);
@@ -302,7 +324,26 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
         for (int j2 = 0; j2 < mt2; ++j2) {
           const uint32_t dj = tmem_d + static_cast<uint32_t>(j2) * 256u;             // accumulator of token tile j2
           const uint64_t aj = a_desc + static_cast<uint64_t>(j2) * (static_cast<uint64_t>(p.nt) * 128u >> 4);
-          if (mx) {   // fp8 x fp8 -> fp32 (the weights were folded to e4m3 by the transform warps)
+          if constexpr (kFp4) {
+            // the block's scales go to tensor memory first (copies and MMAs of one thread run in
+            // order), into the column set of the block's parity: per 64-value MMA step four columns
+            // of token scales and eight of feature scales (two 128-row chunks)
+            const uint32_t sf_t = tmem_d + 256u + static_cast<uint32_t>(it & 1) * 48u;
+            const uint32_t sfa_s = sfa_smem + static_cast<uint32_t>(s) * sfa_bytes;
+            const uint32_t sfb_s = w_addr + 32768u;
+            for (uint32_t g = 0; g < sf_atoms; ++g) {
+              tmem_cp_sf(sf_t + g * 12u, sf_desc(sfa_s + g * 512u));
+              tmem_cp_sf(sf_t + g * 12u + 4u, sf_desc(sfb_s + (g * 2u) * 512u));
+              tmem_cp_sf(sf_t + g * 12u + 8u, sf_desc(sfb_s + (g * 2u + 1u) * 512u));
+            }
+            for (uint32_t j = 0; j < 4; ++j) {
+              // NVFP4: step j has its own atom (four scales per row); MXFP4: an atom serves two steps, bytes 0-1 then 2-3
+              const uint32_t g = nv ? j : (j >> 1);
+              const uint32_t sid = nv ? 0u : ((j & 1u) << 1);
+              const uint32_t id = make_idesc_bs(kFmtE2M1Packed, kFmtE2M1Packed, 128, 256, nv ? 0u : 1u, sid, sid);
+              mma_fp4_bs(nv, dj, aj + 2 * j, b_desc + 2 * j, id, sf_t + g * 12u, sf_t + g * 12u + 4u, (it != 0 || j != 0) ? 1u : 0u);
+            }
+          } else if (mx) {   // fp8 x fp8 -> fp32 (the weights were folded to e4m3 by the transform warps)
             mma_f8_ss(dj, aj, b_desc, idesc, it != 0 ? 1u : 0u);
             mma_f8_ss(dj, aj + 2, b_desc + 2, idesc, 1u);
             mma_f8_ss(dj, aj + 4, b_desc + 4, idesc, 1u);
@@ -478,7 +519,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
     // wide forms: both groups read the accumulator out (half of the columns each: either group's
     // four warps cover the four TMEM lane quarters) -- the in-tile silu * mul + quant and the
     // staging of split-K partial sums for the bulk reduction
-    const bool bulk = !kLean && !kBf && !mx && p.splits > 1 && p.acc != nullptr;
+    const bool bulk = !kLean && !kBf && !kFp4 && !mx && p.splits > 1 && p.acc != nullptr;
     const bool smq = !kLean && !kBf && p.tail_mode == 1;
     const bool wide = bulk || smq;
     if (tgroup == 0 || pair || wide) {
@@ -657,7 +698,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
       const int ncols = halves == 2 ? 128 : min(256, p.N_pad - n0);
       // accumulator words are int32 (integer formats) or fp32 bits (MXFP4)
       auto acc_f = [&](uint32_t raw) -> float {
-        return (mx || bf) ? __uint_as_float(raw) : static_cast<float>(static_cast<int32_t>(raw));
+        return (mx || bf || kFp4) ? __uint_as_float(raw) : static_cast<float>(static_cast<int32_t>(raw));
       };
       // tensor-parallel mode: a finished 16-byte group of outputs goes to every rank's receive
       // region (slot = parity of the call's sequence number, source = this rank)
@@ -906,7 +947,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
               if (bulk)   // the accumulator block goes back to zero for the next launch
                 __stcg(reinterpret_cast<int4*>(rblk + (static_cast<size_t>(c4[u]) * rstride + rr[u]) * 4), make_int4(0, 0, 0, 0));
               float f[4];
-              if (mx) {   // fp32 partials: added in split order, the same on every launch
+              if (mx || kFp4) {   // fp32 partials: added in split order, the same on every launch
                 f[0] = f[1] = f[2] = f[3] = 0.f;
 #pragma unroll
                 for (int sp = 0; sp < kMaxS; ++sp)
@@ -1039,6 +1080,9 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_i8_tail_kernel(const GemmI8
 __global__ void __launch_bounds__(kGemmThreads) gemm_bf16_kernel(const GemmI8Params p, const int stages) {
   gemm_i8_body<false, true>(p, stages, nullptr);
 }
+__global__ void __launch_bounds__(kGemmThreads) gemm_fp4_kernel(const GemmI8Params p, const int stages) {
+  gemm_i8_body<false, false, true>(p, stages, nullptr);
+}
 __global__ void __launch_bounds__(kGemmThreads, 2) gemm_i8_lean_kernel(const GemmI8Params p, const int stages) {
   gemm_i8_body<true>(p, stages, nullptr);
 }
@@ -1059,6 +1103,7 @@ static int device_setup(int* sm_count) {
     const int kSmemLimit = 224 * 1024;
     cudaFuncSetAttribute(gemm_i8_lean_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
     cudaFuncSetAttribute(gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    cudaFuncSetAttribute(gemm_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     cudaFuncSetAttribute(gemm_i8_tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     e = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -1089,6 +1134,8 @@ extern "C" int saber_gemm_i8_smem_bytes(int nt, int stages) {
 // The token-side descriptor spans 128 rows although only nt are loaded: its reads run on into the
 // operand buffers / weight ring, which lie behind the token ring inside the same allocation.
 extern "C" int saber_gemm_i8_smem_bytes_w(int nt, int stages, int w4) {
+  if (w4 == 4) return stages * (32768 + 4096 + nt * 128 + 2048) + 1024;
+  if (w4 == 5) return stages * (32768 + 2048 + nt * 128 + 1024) + 1024;
   if (w4 == 2) return stages * (17408 + nt * 128) + 3 * 32768 + 1024;
   return w4 == 1 ? stages * (16384 + nt * 128) + 3 * 32768 + 1024 : stages * (32768 + nt * 128) + 1024;
 }
@@ -1099,6 +1146,29 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   if (p->nt < 16 || p->nt > 128 || (p->nt & 15) || (p->K & 127) || p->K <= 0 || p->M <= 0 ||
       (p->N_pad & 255) || p->splits < 1 || p->splits > 8 || (p->M_pad % p->nt) != 0 || (p->ldo & 7))
     return static_cast<int>(cudaErrorInvalidValue);
+  if (p->w4 == 4 || p->w4 == 5) {
+    // native FP4: K counts values (256 per k-block); inside the kernel K counts the 128-byte rows of a block
+    if ((p->K & 255) || p->a_sf == nullptr || p->group_tiles || p->tail_mode != 0 || p->tp_nranks > 1 || p->ag_flags != nullptr ||
+        p->halves == 2 || p->bias || p->epi || (p->M > 128 && p->nt != 128))
+      return static_cast<int>(cudaErrorInvalidValue);
+    GemmI8Params q = *p;
+    q.K = p->K >> 1;
+    q.mtiles = 1;
+    const int KBf = q.K >> 7;
+    const int kb_per_f = (KBf + p->splits - 1) / p->splits;
+    if ((p->splits - 1) * kb_per_f >= KBf) return static_cast<int>(cudaErrorInvalidValue);
+    if (stages <= 0) stages = 5;
+    if (stages > kMaxStages) stages = kMaxStages;
+    while (stages > 2 && saber_gemm_i8_smem_bytes_w(p->nt, stages, p->w4) > 224 * 1024) --stages;
+    const int smem_f = saber_gemm_i8_smem_bytes_w(p->nt, stages, p->w4);
+    int sms = 0;
+    const int e = device_setup(&sms);
+    if (e != 0) return e;
+    dim3 grid_f(p->N_pad / 256, (p->M + p->nt - 1) / p->nt, p->splits);
+    q.coop = (p->splits > 1 && p->coop >= 0 && static_cast<int>(grid_f.x * grid_f.y * grid_f.z) <= sms) ? 1 : 0;
+    return static_cast<int>(saber::launch(gemm_fp4_kernel, grid_f, dim3(kGemmThreads), smem_f, stream,
+                                          ((q.coop != 0 && g_coop_launch) ? 1 : 0) | 2, q, stages));
+  }
   const int KB = p->K >> 7;
   const int kb_per = (KB + p->splits - 1) / p->splits;
   if ((p->splits - 1) * kb_per >= KB) return static_cast<int>(cudaErrorInvalidValue);

@@ -104,6 +104,11 @@ struct GemmI8Params {
   // 128 rows (the low or the high nibbles).  For shapes whose tile count fills less than half of
   // the SMs this doubles the CTAs without any split-K round trip.  0 / 1 = whole tiles.
   int halves;
+  // Native FP4 (w4 = 4: NVFP4, one ue4m3 scale per 16 values; w4 = 5: MXFP4, one ue8m0 per 32): `w` tiles are
+  // [N_pad/256][K/256][32768 packed e2m1 bytes + scale atoms], `a` is [K/256][M_pad][128 packed bytes] and
+  // `a_sf` the token scales [K/256][ceil(M_pad/128)][atoms x 512].  K counts VALUES; w_scale / a_scale carry
+  // the per-tensor and per-token fp32 scales.  No tails, no tensor-parallel push, no grouped mode.
+  const uint8_t* a_sf;
 };
 
 }  // namespace saber

@@ -173,7 +173,55 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t c_fmt, uint32_t a_fmt
   return (c_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 constexpr uint32_t kFmtS8 = 1, kFmtBF16 = 1, kFmtE4M3 = 0, kFmtE2M1 = 5;
+constexpr uint32_t kFmtE2M1Packed = 1;   // the 4-bit kinds (mxf4, mxf4nvf4): packed e2m1 has a format code of its own
 constexpr uint32_t kCFmtF32 = 1, kCFmtS32 = 2;
+
+// Block-scaled kinds (mxf4, mxf4nvf4, mxf8f6f4): no accumulator-format field (fp32 always); the id of
+// the scale byte inside its tensor-memory column at bits [4,6) (B) and [29,31) (A); bit 23 is the
+// scale format (0 = ue4m3, 1 = ue8m0).
+__host__ __device__ constexpr uint32_t make_idesc_bs(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n,
+                                                     uint32_t sf_e8m0, uint32_t a_sf_id, uint32_t b_sf_id) {
+  return (b_sf_id << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | (sf_e8m0 << 23) | ((m >> 4) << 24) | (a_sf_id << 29);
+}
+// Descriptor of one 512-byte scale atom in shared memory: 32 rows of 16 bytes, no swizzle (8-row
+// core matrices 128 bytes apart).
+__device__ __forceinline__ uint64_t sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 16;
+  d |= static_cast<uint64_t>(128 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  return d;
+}
+// shared memory -> tensor memory, 32 lanes x 128 bits, replicated to the four lane quarters (the
+// layout the block-scaled MMAs read their scales from); issued by ONE thread, ordered with its MMAs
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// D[tmem] (+)= (A[smem] * SFA[tmem]) * (B[smem] * SFB[tmem]), e2m1 operands, 64 values along K.
+// nv: scales per 16 values (ue4m3 or ue8m0, kind::mxf4nvf4), else per 32 (ue8m0, kind::mxf4).
+__device__ __forceinline__ void mma_fp4_bs(bool nv, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  if (nv) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+  }
+}
 
 // ------------------------------------------------------------------ MMA
 // D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.

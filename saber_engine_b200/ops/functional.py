@@ -28,6 +28,7 @@ class QuantWeight:
     mx: bool = False         # MXFP4 tiles (e2m1 codes + block shifts): fp8 activations, fp32 accumulate
     had_sign: Optional[torch.Tensor] = None   # fp32 [K] +-1: the input must be rotated (sign, 32-point Hadamard) before quantisation
     paired: bool = False     # merged gate | up linear regrouped so that tile t holds gate and up features [128 t, 128 t + 128)
+    fp4: int = 0             # native block-scaled FP4 tiles: 4 = NVFP4 (ue4m3 per 16), 5 = MXFP4 (ue8m0 per 32); FP4 activations
 
     @property
     def N_pad(self) -> int:
@@ -35,8 +36,28 @@ class QuantWeight:
 
     @property
     def fmt_code(self) -> int:
-        """The kernel's weight-format selector: 0 int8, 1 int4, 2 MXFP4."""
+        """The kernel's weight-format selector: 0 int8, 1 int4, 2 MXFP4 (widened to fp8), 4 / 5 native FP4."""
+        if self.fp4:
+            return self.fp4
         return 2 if self.mx else int(self.w4)
+
+    @staticmethod
+    def from_nvfp4(codes: torch.Tensor, block_scale: torch.Tensor, g, device=None) -> "QuantWeight":
+        """e2m1 codes uint8 [N, K] + e4m3-valued block scales fp32 [N, K/16] + the tensor's fp32 scale:
+        tiles for the native block-scaled MMA (nothing is requantised)."""
+        Nn, K = codes.shape
+        sf = block_scale.to(torch.float8_e4m3fn).view(torch.uint8)
+        tiles = L.tile_weight_fp4(codes, sf, 16)
+        dev = device if device is not None else codes.device
+        sc = torch.full((tiles.shape[0] * L.TILE_N,), float(g), dtype=torch.float32)
+        return QuantWeight(tiles.to(dev), sc.to(dev), Nn, K, True, fp4=4)
+
+    @staticmethod
+    def from_mxfp4_native(codes: torch.Tensor, e8m0: torch.Tensor, device=None) -> "QuantWeight":
+        Nn, K = codes.shape
+        tiles = L.tile_weight_fp4(codes, e8m0, 32)
+        dev = device if device is not None else codes.device
+        return QuantWeight(tiles.to(dev), torch.ones(tiles.shape[0] * L.TILE_N, dtype=torch.float32, device=dev), Nn, K, True, fp4=5)
 
     @staticmethod
     def from_mxfp4(codes: torch.Tensor, e8m0: torch.Tensor, device=None) -> "QuantWeight":
@@ -91,6 +112,8 @@ class QuantAct:
     M: int
     K: int
     fp8: bool = False        # bytes are fp8 e4m3 (scale = amax / 448) instead of int8 (amax / 127)
+    fp4: int = 0             # 4 / 5: packed e2m1 rows [K/256, M_pad, 128] with block scales in `sf` (NVFP4 / MXFP4)
+    sf: Optional[torch.Tensor] = None         # uint8 scale atoms [K/256, ceil(M_pad/128), atoms * 512]
     had_sign: Optional[torch.Tensor] = None   # rotation the producer applies before it quantises into this buffer
 
     @property
@@ -157,7 +180,7 @@ def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,
     assert a.M_pad % nt == 0
     m_tiles = (a.M + nt - 1) // nt
     if splits is None:
-        splits = pick_splits(w.N_pad // L.TILE_N, m_tiles, w.K // 128)
+        splits = pick_splits(w.N_pad // L.TILE_N, m_tiles, w.K // (256 if w.fp4 else 128))
     if splits > 1:   # one 128 x 256 int32 block per (split, tile)
         assert splits * m_tiles * (w.N_pad // L.TILE_N) * 32768 <= sc.capacity, "split-K scratch too small"
     p = N.GemmI8Params()
@@ -165,9 +188,12 @@ def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,
     p.out, p.ws, p.counters, p.err = out.data_ptr(), sc.ws.data_ptr(), sc.counters.data_ptr(), sc.err.data_ptr()
     p.M, p.M_pad, p.N, p.N_pad, p.K = a.M, a.M_pad, w.N, w.N_pad, w.K
     assert bool(getattr(w, 'mx', False)) == bool(a.fp8), "MXFP4 weights take fp8 activations, integer weights int8"
+    assert w.fp4 == a.fp4, "native FP4 weights take FP4 activations of the same block format"
+    if w.fp4:
+        p.a_sf = a.sf.data_ptr()
     p.nt, p.splits, p.w4, p.ldo = nt, splits, w.fmt_code, out.stride(0)
     p.coop = coop
-    if splits > 1 and not getattr(w, "mx", False) and m_tiles * (w.N_pad // L.TILE_N) * nt * 256 <= sc.acc.numel():
+    if splits > 1 and not getattr(w, "mx", False) and not w.fp4 and m_tiles * (w.N_pad // L.TILE_N) * nt * 256 <= sc.acc.numel():
         p.acc = sc.acc.data_ptr()       # integer partial sums meet in L2 (bulk reduction) instead of private copies
         if m_tiles * (w.N_pad // L.TILE_N) * nt * 256 <= sc.acc_tail.numel():
             p.acc_tail = sc.acc_tail.data_ptr()
@@ -175,6 +201,34 @@ def gemm_params(w: QuantWeight, a: QuantAct, out: torch.Tensor, sc: GemmScratch,
     p.mtiles = mtiles      # 0: the launcher decides; 2: pair token tiles whenever the shape allows; -1: never
     assert out.stride(0) % 8 == 0, "GEMM output rows must be 16-byte aligned"
     return p
+
+
+def quant_act_fp4(x: torch.Tensor, fmt: int, device=None) -> QuantAct:
+    """Host-side (torch) FP4 quantiser of activation rows, the arithmetic the device producer follows.
+    fmt 4 = NVFP4: per-token fp32 scale g = amax / (6 * 448), one e4m3 scale per 16 values, e2m1 codes;
+    fmt 5 = MXFP4: one power-of-two scale per 32 values (token scale 1)."""
+    from ..pack import quant_fp4 as Q
+    x = x.to(torch.bfloat16).float().cpu()
+    M, K = x.shape
+    m_pad = L.padded_rows(M)
+    if fmt == 4:
+        g = (x.abs().amax(dim=1) / (6.0 * 448.0)).clamp_min(1e-30)
+        b = x.reshape(M, K // 16, 16)
+        bs = Q._e4m3_round((b.abs().amax(dim=-1) / 6.0 / g[:, None]).clamp(max=448.0))
+        denom = (bs * g[:, None]).clamp_min(1e-30)
+        codes = Q.e2m1_encode(b / denom[..., None]).reshape(M, K)
+        sf = bs.to(torch.float8_e4m3fn).view(torch.uint8)
+        q, at = L.tile_act_fp4(codes, sf, 16, m_pad)
+    else:
+        codes, e = Q.quantize_mxfp4(x)
+        g = torch.ones(M)
+        q, at = L.tile_act_fp4(codes, e, 32, m_pad)
+    scale = torch.zeros(m_pad, dtype=torch.float32)
+    scale[:M] = g
+    dev = device if device is not None else x.device
+    qa = QuantAct(q.to(dev), scale.to(dev), M, K, fp4=fmt, sf=at.to(dev))
+    qa._codes, qa._g = codes, g             # (kept for tests: the exact dequantisation)
+    return qa
 
 
 def gemm_tail_silu_quant(p: N.GemmI8Params, qa_out: QuantAct, sc: GemmScratch) -> N.GemmI8Params:

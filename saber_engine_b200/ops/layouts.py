@@ -236,3 +236,60 @@ def kv_pages_from_core(cache: torch.Tensor) -> torch.Tensor:
     k = cache[:, :, 0].reshape(nb, nkv, 2, 16, 8, 16).permute(0, 1, 2, 4, 3, 5).reshape(nb, nkv, 16, 256)
     v = cache[:, :, 1].reshape(nb, nkv, 32, 8, 16).permute(0, 1, 4, 2, 3).reshape(nb, nkv, 16, 256)
     return torch.stack([k, v], dim=2).contiguous()
+
+
+# ------------------------------------------------------------------------------- native FP4 (block-scaled MMA)
+FP4_KB = 256          # values per k-block: a 128-byte row of packed e2m1 pairs
+
+
+def pack_e2m1(codes: torch.Tensor) -> torch.Tensor:
+    """uint8 codes [.., K] (one per byte) -> packed bytes [.., K/2]: the even value in the low nibble."""
+    return (codes[..., 0::2] & 0x0F) | ((codes[..., 1::2] & 0x0F) << 4)
+
+
+def unpack_e2m1(packed: torch.Tensor) -> torch.Tensor:
+    out = torch.empty(*packed.shape[:-1], packed.shape[-1] * 2, dtype=torch.uint8, device=packed.device)
+    out[..., 0::2] = packed & 0x0F
+    out[..., 1::2] = packed >> 4
+    return out
+
+
+def scale_atoms(sf: torch.Tensor, per_kb: int) -> torch.Tensor:
+    """Block scales as the 512-byte atoms the tensor core's scale copy moves: sf uint8 [R, n_sf] with R
+    a multiple of 128 and n_sf a multiple of `per_kb` (scales per row and k-block, itself a multiple of
+    4) -> uint8 [n_sf / per_kb, R / 128, per_kb / 4, 512]; inside an atom (128 rows x 4 scales) the byte
+    of (row r, scale s) sits at (r % 32) * 16 + (r // 32) * 4 + s."""
+    R, n_sf = sf.shape
+    assert R % 128 == 0 and n_sf % per_kb == 0 and per_kb % 4 == 0
+    x = sf.reshape(R // 128, 4, 32, n_sf // per_kb, per_kb // 4, 4)      # [chunk, r // 32, r % 32, kb, atom, s]
+    return x.permute(3, 0, 4, 2, 1, 5).contiguous().reshape(n_sf // per_kb, R // 128, per_kb // 4, 512)
+
+
+def tile_weight_fp4(codes: torch.Tensor, sf: torch.Tensor, vs: int) -> torch.Tensor:
+    """e2m1 codes uint8 [N, K] + block scales uint8 [N, K / vs] (vs = 16: ue4m3, 32: ue8m0) -> tiles uint8
+    [N_pad/256, K/256, 32768 + SF]: the swizzled image of the packed 256 x 128-byte tile, then its scale
+    atoms in the order the kernel copies them: [atom along K][128-row chunk][512]."""
+    N, K = codes.shape
+    assert K % FP4_KB == 0
+    n_pad = round_up(N, TILE_N)
+    if n_pad != N:
+        codes = torch.cat([codes, torch.zeros(n_pad - N, K, dtype=codes.dtype, device=codes.device)], 0)
+        sf = torch.cat([sf, torch.zeros(n_pad - N, sf.shape[1], dtype=sf.dtype, device=sf.device)], 0)
+    img = tile_weight_int8(pack_e2m1(codes).view(torch.int8))                  # [n_tiles, K/256, 32768]
+    per_kb = FP4_KB // vs
+    at = scale_atoms(sf, per_kb)                                                # [K/256, n_pad/128, per_kb/4, 512]
+    at = at.reshape(K // FP4_KB, n_pad // TILE_N, 2, per_kb // 4, 512).permute(1, 0, 3, 2, 4)   # [tile, kb, atom, chunk, 512]
+    return torch.cat([img, at.reshape(n_pad // TILE_N, K // FP4_KB, -1)], dim=-1).contiguous()
+
+
+def tile_act_fp4(codes: torch.Tensor, sf: torch.Tensor, vs: int, m_pad: int):
+    """e2m1 codes uint8 [M, K] + block scales uint8 [M, K / vs] -> (packed rows uint8 [K/256, M_pad, 128] in
+    the activation swizzle, scale atoms uint8 [K/256, ceil(M_pad/128), (256/vs)/4 * 512]); rows past M are zero."""
+    M, K = codes.shape
+    q = tile_act_int8(pack_e2m1(codes).view(torch.int8), m_pad).view(torch.uint8)
+    r_pad = round_up(m_pad, 128)
+    full = torch.zeros(r_pad, sf.shape[1], dtype=torch.uint8, device=sf.device)
+    full[:M] = sf
+    per_kb = FP4_KB // vs
+    at = scale_atoms(full, per_kb)
+    return q, at.reshape(K // FP4_KB, r_pad // 128, -1).contiguous()

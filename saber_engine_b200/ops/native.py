@@ -46,7 +46,7 @@ class GemmI8Params(C.Structure):
                 ("group_tiles", P), ("group_ntiles", P), ("group_w_stride", U64), ("coop", I), ("mtiles", I), ("dbg", P), ("bias", P), ("res", P), ("epi", I),
                 ("tail_mode", I), ("tail_row_mode", I), ("tail_row", P), ("tail_q", P), ("tail_scale", P), ("tail_M_pad", I),
                 ("tail_sync", P), ("next_w", P), ("next_tiles", I), ("next_splits", I), ("next_KB", I), ("next_kb_per", I),
-                ("next_wbytes", I), ("next_pref", I), ("acc", P), ("acc_tail", P), ("halves", I)]
+                ("next_wbytes", I), ("next_pref", I), ("acc", P), ("acc_tail", P), ("halves", I), ("a_sf", P)]
 
 
 class RowOpParams(C.Structure):
