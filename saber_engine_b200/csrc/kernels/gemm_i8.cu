@@ -1270,7 +1270,7 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
 extern "C" int saber_gemm_i8_tail_ok(const saber::GemmI8Params* p) {
   int sm_count = 0;
   if (saber::device_setup(&sm_count) != 0) return 0;
-  if (p->group_tiles || p->w4 == 3 || p->nt <= 0) return 0;
+  if (p->group_tiles || p->w4 >= 3 || p->nt <= 0) return 0;
   const int grid_y = (p->M + p->nt - 1) / p->nt;
   return (p->N_pad / 256) * (p->halves == 2 ? 2 : 1) * grid_y * p->splits <= sm_count ? 1 : 0;
 }

@@ -25,7 +25,19 @@ constexpr int kRowThreads = 256;
 
 // Quantise the row held in shared memory (bf16, K values) and store it tiled. All threads call.
 __device__ __forceinline__ void quant_store_row(const __nv_bfloat16* h, int K, int m, int M_pad,
-                                                float amax, int8_t* q, float* scale, int qfmt) {
+                                                float amax, int8_t* q, float* scale, int qfmt,
+                                                uint8_t* q_sf = nullptr, int sf_m_tiles = 0) {
+  if (qfmt == 2) {   // NVFP4: a 16-value chunk is one block
+    const float g = amax / (6.f * 448.f);
+    if (threadIdx.x == 0) scale[m] = g;
+    for (int ch = threadIdx.x; ch < (K >> 4); ch += blockDim.x) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = __bfloat162float(h[(ch << 4) + i]);
+      fp4_store_chunk(v, g, ch, m, M_pad, q, q_sf, sf_m_tiles);
+    }
+    return;
+  }
   const float qmax = qfmt == 1 ? 448.f : 127.f;
   const float inv = amax > 0.f ? qmax / amax : 0.f;
   if (threadIdx.x == 0) scale[m] = amax / qmax;
@@ -56,7 +68,7 @@ __global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpPa
   if (p.m_live != nullptr && m >= *p.m_live) return;   // whole block: rows past the live count
   if (m >= p.M) {  // padding row: zeros
     if (p.q) {
-      const int nchunk = K >> 4;
+      const int nchunk = p.qfmt == 2 ? (K >> 5) : (K >> 4);    // 16-byte pieces of the row (packed FP4: half as many)
       for (int ch = threadIdx.x; ch < nchunk; ch += blockDim.x) {
         const int k0 = ch << 4;
         const int kb = k0 >> 7, c = (k0 & 127) >> 4;
@@ -202,7 +214,7 @@ __global__ void __launch_bounds__(kRowThreads) row_producer_kernel(const RowOpPa
     }
   }
   amax = block_reduce<true>(amax, red);  // its barriers also publish h to the whole block
-  if (p.q) quant_store_row(h, K, m, p.M_pad, amax, p.q, p.scale, p.qfmt);
+  if (p.q) quant_store_row(h, K, m, p.M_pad, amax, p.q, p.scale, p.qfmt, p.q_sf, p.sf_m_tiles);
 }
 
 // Register-resident form of ADD_RMS / SILU_MUL / GATE_SIG / PLAIN (body in rowops_body.cuh): a

@@ -69,6 +69,10 @@ struct RowOpParams {
   const float* acc_a_scale;
   const float* acc_w_scale;
   int acc_nt, acc_tiles_n;
+  // qfmt == 2: NVFP4 rows -- packed e2m1 [K/256][M_pad][128 bytes] in `q`, one ue4m3 scale per 16 values as
+  // 512-byte atoms [K/256][sf_m_tiles][4][512] in `q_sf`, the per-token fp32 scale amax / (6 * 448) in `scale`
+  uint8_t* q_sf;
+  int sf_m_tiles;
 };
 
 }  // namespace saber

@@ -10,6 +10,7 @@
 #include "ptx_sm100.cuh"
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
+#include <cuda_fp4.h>
 
 namespace saber {
 
@@ -58,6 +59,32 @@ __device__ __forceinline__ uint32_t quant4(float a, float b, float c, float d, f
   return word;
 }
 
+// One NVFP4 block: 16 values of row m, chunk `ch` (values [16 ch, 16 ch + 16)), token scale g = amax / (6 * 448).
+// Block scale = e4m3(block amax / (6 g)) (round to nearest, saturating), codes = e2m1(v / (scale * g)) to
+// nearest even; eight packed bytes go to the row's 128-byte line of k-block ch / 16 (16-byte chunks
+// XOR-swizzled by the row like every activation tile), the scale byte to its atom.
+__device__ __forceinline__ void fp4_store_chunk(const float (&v)[16], float g, int ch, int m, int M_pad,
+                                                int8_t* q, uint8_t* q_sf, int sf_m_tiles) {
+  float bmax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(v[i]));
+  const float want = g > 0.f ? fminf(bmax / 6.f / g, 448.f) : 0.f;
+  const __nv_fp8_storage_t sfb = __nv_cvt_float_to_fp8(want, __NV_SATFINITE, __NV_E4M3);
+  const float sf = __half2float(__half(__nv_cvt_fp8_to_halfraw(sfb, __NV_E4M3)));
+  const float denom = fmaxf(sf * g, 1e-30f);
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const __nv_fp4x2_storage_t b = __nv_cvt_float2_to_fp4x2(make_float2(v[2 * i] / denom, v[2 * i + 1] / denom), __NV_E2M1, cudaRoundNearest);
+    w[i >> 2] |= static_cast<uint32_t>(b) << (8 * (i & 3));
+  }
+  const int kb = ch >> 4, c8 = ch & 15;
+  const size_t off = (static_cast<size_t>(kb) * M_pad + m) * 128 + ((((c8 >> 1) ^ (m & 7)) & 7) << 4) + ((c8 & 1) << 3);
+  *reinterpret_cast<uint2*>(q + off) = make_uint2(w[0], w[1]);
+  const size_t so = ((static_cast<size_t>(kb) * sf_m_tiles + (m >> 7)) * 4 + (c8 >> 2)) * 512 + ((m & 31) << 4) + (((m >> 5) & 3) << 2) + (c8 & 3);
+  q_sf[so] = sfb;
+}
+
 struct alignas(16) Bf16x8 {
   __nv_bfloat162 v[4];
 };
@@ -100,7 +127,8 @@ __device__ __forceinline__ void row_reg_body(const RowOpParams& p, const int m, 
   if (sp && (m >= p.M || m / p.sp_rpr != p.sp_rank)) return;   // sequence parallel: not this rank's row
   if (m >= p.M) {  // padding row: zeros
     if (p.q) {
-      for (int ch = threadIdx.x; ch < nchunk; ch += nthr) {
+      const int npiece = p.qfmt == 2 ? (K >> 5) : nchunk;      // 16-byte pieces of the row (packed FP4: half as many)
+      for (int ch = threadIdx.x; ch < npiece; ch += nthr) {
         const int kb = ch >> 3, c = ch & 7;
         int8_t* dst = p.q + (static_cast<size_t>(kb) * p.M_pad + m) * 128 + (((c ^ (m & 7)) & 7) << 4);
         *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
@@ -279,7 +307,16 @@ __device__ __forceinline__ void row_reg_body(const RowOpParams& p, const int m, 
     }
   }
   amax = block_reduce<true>(amax, red);
-  if (p.q) {
+  if (p.q && p.qfmt == 2) {
+    const float g = amax / (6.f * 448.f);
+    if (threadIdx.x == 0) p.scale[m] = g;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int ch = threadIdx.x + c * nthr;
+      if (ch >= nchunk) continue;
+      fp4_store_chunk(hv[c], g, ch, m, p.M_pad, p.q, p.q_sf, p.sf_m_tiles);
+    }
+  } else if (p.q) {
     const float qmax = p.qfmt == 1 ? 448.f : 127.f;
     const float inv = amax > 0.f ? qmax / amax : 0.f;
     if (threadIdx.x == 0 && !sp) p.scale[m] = amax / qmax;

@@ -59,7 +59,7 @@ class HybridConfig:
     attn_out_gate: bool = True
     tie_embeddings: bool = False
     act_hadamard: bool = False          # rotate activations (sign + 32-point Hadamard) before int8/fp8 quant; weights pre-rotated
-    weight_format: str = "iu8"         # 4-bit linears: "iu8" (int4 x int8 acts) | "mxfp4" (e2m1/e8m0 x fp8 acts)
+    weight_format: str = "iu8"         # 4-bit linears: "iu8" (int4 x int8 acts) | "mxfp4" (e2m1/e8m0 x fp8 acts) | "nvfp4" (native block-scaled FP4 x FP4)
     max_ctx: int = 262144
     page_tokens: int = 16
     moe: Optional[MoEConfig] = None
@@ -220,6 +220,7 @@ def by_name(name: str):
     table = {"qwen38-27b": qwen38_27b, "flashnext-moe": flashnext_moe,
              "flashnext-ref": lambda: flashnext_moe(True), "hybrid-mini": scaled_hybrid,
              "qwen38-27b-mxfp4": lambda: dataclasses.replace(qwen38_27b(), name="qwen38-27b-mxfp4", weight_format="mxfp4"),
+             "qwen38-27b-nvfp4": lambda: dataclasses.replace(qwen38_27b(), name="qwen38-27b-nvfp4", weight_format="nvfp4"),
              "tiny-qwen3": TinyQwen3Config}
     if name not in table:
         raise KeyError(f"unknown model {name!r}; known: {sorted(table)}")

@@ -217,6 +217,10 @@ class HybridModel:
         (int8 for integer weights, fp8 e4m3 for MXFP4): same storage, different law."""
         if a is None:
             return None
+        if getattr(w, "fp4", 0):          # native FP4 linear: NVFP4 rows + scale atoms in the same storage
+            v = a.as_fp4(w.fp4)
+            v.had_sign = getattr(w, "had_sign", None)
+            return v
         return F.QuantAct(a.q, a.scale, a.M, a.K, fp8=bool(getattr(w, "mx", False)), had_sign=getattr(w, "had_sign", None))
 
     def _flush(self, prog: N.Program) -> None:
@@ -259,7 +263,7 @@ class HybridModel:
         splits = self.pick_splits(w, a)
         p = F.gemm_params(w, a, gu, self.scratch, splits=splits)
         qi = self._fmt(qa_i, w_down)
-        if self.fuse and w.paired and splits == 1 and not qi.fp8 and qi.had_sign is None and F.gemm_tail_ok(p) \
+        if self.fuse and w.paired and splits == 1 and not qi.fp8 and not qi.fp4 and qi.had_sign is None and F.gemm_tail_ok(p) \
                 and qi.M_pad % p.nt == 0 and qi.M_pad <= 256:
             F.gemm_tail_silu_quant(p, qi, self.scratch)
             prog.gemm(p, self.gemm_stages(w, a), tag=f"{tag}.gate_up+silu_mul_quant")
@@ -295,21 +299,21 @@ class HybridModel:
     def _tuned(self, w: F.QuantWeight, a: F.QuantAct):
         """The measured variant of this (linear, rows) route from the plan's tune table, or None."""
         table = getattr(self, "tune_table", None)
-        return table.lookup("gemm_i8", N=w.N_pad, K=w.K, M=a.M, w4=int(w.w4)) if table is not None else None
+        return table.lookup("gemm_i8", N=w.N_pad, K=w.K, M=a.M, w4=w.fmt_code) if table is not None else None
 
     def pick_splits(self, w: F.QuantWeight, a: F.QuantAct) -> int:
         table = getattr(self, "tune_table", None)
         if table is not None:
-            hit = table.lookup("gemm_i8", N=w.N_pad, K=w.K, M=a.M, w4=int(w.w4))
+            hit = table.lookup("gemm_i8", N=w.N_pad, K=w.K, M=a.M, w4=w.fmt_code)
             if hit is not None and int(hit.get("halves", 1)) != 2:
                 return int(hit.get("splits", 1))
         nt = L.token_tile(a.M)
-        return F.pick_splits(w.N_pad // L.TILE_N, (a.M + nt - 1) // nt, w.K // 128)
+        return F.pick_splits(w.N_pad // L.TILE_N, (a.M + nt - 1) // nt, w.K // (256 if w.fp4 else 128))
 
     def gemm_stages(self, w: F.QuantWeight, a: F.QuantAct) -> int:
         table = getattr(self, "tune_table", None)
         if table is not None:
-            hit = table.lookup("gemm_i8", N=w.N_pad, K=w.K, M=a.M, w4=int(w.w4))
+            hit = table.lookup("gemm_i8", N=w.N_pad, K=w.K, M=a.M, w4=w.fmt_code)
             if hit is not None:
                 return int(hit.get("stages", 0))
         return 0

@@ -41,10 +41,35 @@ def _mx_linear(x: torch.Tensor, wq: torch.Tensor) -> torch.Tensor:
     return ((aq.float().double() @ wq.double().t()).float() * asc[:, None]).to(torch.bfloat16)
 
 
+def _fp4_dense(w: QuantWeight) -> torch.Tensor:
+    """The fp32 matrix a native FP4 linear multiplies with (exact dequantisation of its tiles)."""
+    from ..pack import quant_fp4 as Q
+    vs = 16 if w.fp4 == 4 else 32
+    codes, sf = L.untile_weight_fp4(w.tiles.cpu(), w.N, w.K, vs)
+    if w.fp4 == 4:
+        return Q.dequant_nvfp4(codes, sf.view(torch.float8_e4m3fn).float(), w.scale.cpu()[0])
+    return Q.dequant_mxfp4(codes, sf)
+
+
+def _fp4_linear(x: torch.Tensor, w: QuantWeight) -> torch.Tensor:
+    """NVFP4 rows (per-token fp32 scale, e4m3 scale per 16, e2m1 codes) times the dequantised weight."""
+    from ..pack import quant_fp4 as Q
+    x = x.to(torch.bfloat16).float()
+    M, K = x.shape
+    g = (x.abs().amax(dim=1) / (6.0 * 448.0))
+    b = x.reshape(M, K // 16, 16)
+    bs = Q._e4m3_round((b.abs().amax(dim=-1) / 6.0 / g[:, None].clamp_min(1e-38)).clamp(max=448.0))
+    denom = (bs * g[:, None]).clamp_min(1e-30)
+    xd = (Q.e2m1_decode(Q.e2m1_encode(b / denom[..., None])) * denom[..., None]).reshape(M, K)
+    return (xd.double() @ _fp4_dense(w).double().t()).float().to(torch.bfloat16)
+
+
 def qlinear(x_bf16_rounded: torch.Tensor, w: QuantWeight) -> torch.Tensor:
     """Quantise rows per token, exact integer GEMM, scale, round to bf16 (as fp32 values)."""
     if getattr(w, "had_sign", None) is not None:      # the producer rotates before it quantises
         x_bf16_rounded = R.bf16_round(L.hadamard32_rows(x_bf16_rounded, w.had_sign.cpu()))
+    if getattr(w, "fp4", 0):
+        return _fp4_linear(x_bf16_rounded, w).float()
     if getattr(w, "mx", False):
         return _mx_linear(x_bf16_rounded, _mx_dense(w)).float()
     q, s = dequant_linear(w)

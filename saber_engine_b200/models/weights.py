@@ -102,6 +102,10 @@ def _quant_on(dev, w: torch.Tensor, bits: int, rotate: bool = False) -> QuantWei
         from ..pack import quant_fp4 as Q
         codes, e = Q.quantize_mxfp4(w)
         return QuantWeight.from_mxfp4(codes, e, dev)
+    if bits == 4 and _FORMAT["fmt"] == "nvfp4" and w.shape[1] % 256 == 0:
+        from ..pack import quant_fp4 as Q
+        codes, bs, g = Q.quantize_nvfp4(w)
+        return QuantWeight.from_nvfp4(codes, bs, g, dev)
     q, s = L.quantize_weight_rows(w, bits)
     return QuantWeight.from_int(q, s, bits, dev)
 
@@ -127,6 +131,10 @@ def _quant_cols_plain(dev, w_full: torch.Tensor, bits: int, c0: int, c1: int) ->
         sc = torch.zeros(tiles.shape[0] * L.TILE_N, dtype=torch.float32, device=w_full.device)
         sc[:w_full.shape[0]] = row_scale
         return QuantWeight(tiles.to(dev).contiguous(), sc.to(dev), w_full.shape[0], c1 - c0, True, mx=True)
+    if bits == 4 and _FORMAT["fmt"] == "nvfp4" and (c1 - c0) % 256 == 0 and c0 % 256 == 0:
+        from ..pack import quant_fp4 as Q
+        codes, bs, g = Q.quantize_nvfp4(w_full)            # block and tensor scales of the FULL matrix
+        return QuantWeight.from_nvfp4(codes[:, c0:c1].contiguous(), bs[:, c0 // 16:c1 // 16].contiguous(), g, dev)
     q, s = L.quantize_weight_rows(w_full, bits)
     return QuantWeight.from_int(q[:, c0:c1].contiguous(), s, bits, dev)
 

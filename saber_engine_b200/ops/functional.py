@@ -90,7 +90,7 @@ class QuantWeight:
 def pair_gate_up(w: QuantWeight) -> QuantWeight:
     """The merged gate | up linear with its tiles regrouped for the fused silu * mul epilogue (see
     `layouts.pair_gate_up_int4`); weights that cannot be paired (int8, MXFP4, ragged) come back unchanged."""
-    if w.paired or not w.w4 or w.mx or w.N % 256 or (w.N // 2) % 128:
+    if w.paired or not w.w4 or w.mx or w.fp4 or w.N % 256 or (w.N // 2) % 128:
         return w
     tiles, scale = L.pair_gate_up_int4(w.tiles, w.scale, w.N // 2)
     return QuantWeight(tiles, scale, w.N, w.K, True, had_sign=w.had_sign, paired=True)
@@ -125,6 +125,15 @@ class QuantAct:
         m_pad = L.padded_rows(M)
         return QuantAct(torch.empty(K // 128, m_pad, 128, dtype=torch.int8, device=device),
                         torch.empty(m_pad, dtype=torch.float32, device=device), M, K, fp8)
+
+    def as_fp4(self, fmt: int = 4) -> "QuantAct":
+        """The same storage seen as NVFP4 rows (half the bytes of the int8 rows) with scale atoms beside
+        them (allocated on first use, zero: padding rows keep zero scales)."""
+        assert self.K % 256 == 0, "FP4 rows come in k-blocks of 256 values"
+        if getattr(self, "_sf", None) is None:
+            self._sf = torch.zeros(self.K // 256, (self.M_pad + 127) // 128, 2048, dtype=torch.uint8, device=self.q.device)
+        q = self.q.view(-1)[: self.K // 256 * self.M_pad * 128].view(self.K // 256, self.M_pad, 128)
+        return QuantAct(q, self.scale, self.M, self.K, fp4=fmt, sf=self._sf, had_sign=self.had_sign)
 
 
 class GemmScratch:
@@ -271,7 +280,7 @@ def pick_halves(w: QuantWeight, n_tiles: int, m_tiles: int, sms: Optional[int] =
     """Half tiles instead of split-K (`[gemm.halves]` of the launch rules): packed int4 weights whose
     whole-tile grid fills between a quarter and a half of the SMs."""
     from ..rules import default_rules
-    fmt = "mxfp4" if getattr(w, "mx", False) else ("int4" if w.w4 else "int8")
+    fmt = "fp4" if w.fp4 else ("mxfp4" if getattr(w, "mx", False) else ("int4" if w.w4 else "int8"))
     return default_rules().gemm_halves(fmt, n_tiles, m_tiles)
 
 
@@ -289,7 +298,10 @@ def row_params(M: int, K: int, *, a=None, a_f32=None, b=None, res=None, w=None, 
     p.ldb = ldb if ldb is not None else (b.stride(0) if b is not None else 0)
     p.ldres = res.stride(0) if res is not None else 0
     p.ldout = out.stride(0) if out is not None else 0
-    p.qfmt = int(qa.fp8) if qa is not None else 0
+    p.qfmt = (2 if qa.fp4 else int(qa.fp8)) if qa is not None else 0
+    if qa is not None and qa.fp4:
+        assert qa.fp4 == 4, "the device producers write NVFP4 rows"
+        p.q_sf, p.sf_m_tiles = qa.sf.data_ptr(), qa.sf.shape[1]
     p.had_sign = N.ptr(qa.had_sign) if qa is not None else None
     return p
 

@@ -293,3 +293,30 @@ def tile_act_fp4(codes: torch.Tensor, sf: torch.Tensor, vs: int, m_pad: int):
     per_kb = FP4_KB // vs
     at = scale_atoms(full, per_kb)
     return q, at.reshape(K // FP4_KB, r_pad // 128, -1).contiguous()
+
+
+def untile_scale_atoms(at: torch.Tensor) -> torch.Tensor:
+    """Inverse of scale_atoms: uint8 [n_kb, R/128, per_kb/4, 512] -> [R, n_kb * per_kb]."""
+    n_kb, chunks, atoms, _ = at.shape
+    x = at.reshape(n_kb, chunks, atoms, 32, 4, 4).permute(1, 4, 3, 0, 2, 5)       # [chunk, r // 32, r % 32, kb, atom, s]
+    return x.reshape(chunks * 128, n_kb * atoms * 4).contiguous()
+
+
+def untile_weight_fp4(tiles: torch.Tensor, N: int, K: int, vs: int):
+    """Inverse of tile_weight_fp4 (tests, the CPU oracle): -> (codes uint8 [N, K], block scales uint8 [N, K / vs])."""
+    n_tiles, n_kb, _ = tiles.shape
+    img = tiles[..., :32768].contiguous()
+    codes = unpack_e2m1(untile_weight_int8(img, n_tiles * TILE_N, K // 2).view(torch.uint8))[:N]
+    per_kb = FP4_KB // vs
+    at = tiles[..., 32768:].reshape(n_tiles, n_kb, per_kb // 4, 2, 512).permute(1, 0, 3, 2, 4)    # [kb, tile, chunk, atom, 512]
+    sf = untile_scale_atoms(at.reshape(n_kb, n_tiles * 2, per_kb // 4, 512).contiguous())
+    return codes.contiguous(), sf[:N].contiguous()
+
+
+def untile_act_fp4(q: torch.Tensor, sf_atoms: torch.Tensor, M: int, vs: int):
+    """Inverse of tile_act_fp4: -> (codes uint8 [M, K], block scales uint8 [M, K / vs])."""
+    codes = unpack_e2m1(untile_act_int8(q.view(torch.int8), M).view(torch.uint8))
+    n_kb, chunks, _ = sf_atoms.shape
+    per_kb = FP4_KB // vs
+    sf = untile_scale_atoms(sf_atoms.reshape(n_kb, chunks, per_kb // 4, 512))
+    return codes, sf[:M].contiguous()

@@ -57,7 +57,8 @@ class RowOpParams(C.Structure):
                 ("tp_nt", I), ("tp_tiles_n", I), ("m_live", P), ("qfmt", I), ("had_sign", P),
                 ("sp_q", P * MAX_RANKS), ("sp_scale", P * MAX_RANKS), ("sp_flags", P * MAX_RANKS), ("sp_counter", P),
                 ("sp_rpr", I), ("sp_rank", I), ("res_copy", P), ("silu_pair", I),
-                ("acc", P), ("acc_a_scale", P), ("acc_w_scale", P), ("acc_nt", I), ("acc_tiles_n", I)]
+                ("acc", P), ("acc_a_scale", P), ("acc_w_scale", P), ("acc_nt", I), ("acc_tiles_n", I),
+                ("q_sf", P), ("sf_m_tiles", I)]
 
 
 class GdnConvParams(C.Structure):

@@ -57,6 +57,28 @@ def _gemm(Nn, K, M, w4, splits, copies=3):
     return ws, qa, out
 
 
+def _gemm_fp4(Nn, K, M, fmt, splits, copies=3):
+    """Native block-scaled FP4 GEMM (4 = NVFP4, 5 = MXFP4): random packed operands and scales."""
+    n_pad = L.round_up(Nn, 256)
+    sfb = 4096 if fmt == 4 else 2048
+    ws = []
+    for _ in range(copies):
+        t = torch.randint(0, 255, (n_pad // 256, K // 256, 32768 + sfb), dtype=torch.uint8, device=DEV)
+        t[..., 32768:] = torch.randint(0x30, 0x40, t[..., 32768:].shape, dtype=torch.uint8, device=DEV) if fmt == 4 else 127
+        ws.append(F.QuantWeight(t, torch.full((n_pad,), 1e-3, device=DEV), Nn, K, True, fp4=fmt))
+    m_pad = L.padded_rows(M)
+    q = torch.randint(0, 255, (K // 256, m_pad, 128), dtype=torch.uint8, device=DEV)
+    sf = torch.full((K // 256, (m_pad + 127) // 128, sfb // 2), 0x38 if fmt == 4 else 127, dtype=torch.uint8, device=DEV)
+    qa = F.QuantAct(q, torch.ones(m_pad, device=DEV), M, K, fp4=fmt, sf=sf)
+    out = torch.empty(M, Nn, dtype=torch.bfloat16, device=DEV)
+    sc = F.scratch(DEV)
+    ps = [F.gemm_params(w, qa, out, sc, splits=splits) for w in ws]
+    lib = N.lib()
+    fns = [lambda p=p: N.check(lib.saber_gemm_i8_launch(C.byref(p), 0, N.stream_handle()), "gemm") for p in ps]
+    _time(fns, f"gemm_fp4 ({'nvfp4' if fmt == 4 else 'mxfp4'}) N={Nn} K={K} M={M} splits={ps[0].splits}", n_pad * K * 0.5 + n_pad * K // (16 if fmt == 4 else 32))
+    return ws, qa, out
+
+
 def _attn(nseq, n, ctx, splits, copies=3, impl=0):
     nq, nkv, D = 24, 4, 256
     M = nseq * n
@@ -220,6 +242,12 @@ CASES = {
     "gemm_w4_down_m72_split": lambda: _gemm(5120, 17408, 72, 1, 7, copies=4),
     "gemm_w4_in_proj_m9_split": lambda: _gemm(10496, 5120, 9, 1, 3, copies=6),
     "gemm_w8_lm_head_m72": lambda: _gemm(248320, 5120, 72, 0, 1, copies=2),
+    "gemm_nvfp4_gate_up_m64": lambda: _gemm_fp4(34816, 5120, 64, 4, 1),
+    "gemm_nvfp4_down_m64_split": lambda: _gemm_fp4(5120, 17408, 64, 4, 7, copies=4),
+    "gemm_nvfp4_in_proj_m64_split": lambda: _gemm_fp4(16640, 5120, 64, 4, 2, copies=4),
+    "gemm_mxfp4_gate_up_m64": lambda: _gemm_fp4(34816, 5120, 64, 5, 1),
+    "gemm_nvfp4_gate_up_m2048": lambda: _gemm_fp4(34816, 5120, 2048, 4, 1, copies=2),
+    "gemm_w4_gate_up_m64": lambda: _gemm(34816, 5120, 64, 1, 1),
     "gemm_w4_gate_up_m2048": lambda: _gemm(34816, 5120, 2048, 1, 1, copies=2),
     "attn_decode_b8_ctx4096": lambda: _attn(8, 9, 4096, 4),
     "attn_decode_b1_ctx32768": lambda: _attn(1, 9, 32768, 32, copies=2),
