@@ -104,6 +104,7 @@ def main() -> int:
     ap.add_argument("--pdl", type=int, default=-1, help="programmatic dependent launch: 0 off, 1 all kernels, 2 GEMMs only (A/B)")
     ap.add_argument("--gdn-fused", type=int, default=-1, help="DeltaNet decode step as one launch (1) or three (0); -1: the model's default (A/B)")
     ap.add_argument("--no-tune-table", action="store_true", help="ignore the committed autotune table (A/B)")
+    ap.add_argument("--no-extra-arms", action="store_true", help="skip the NVFP4 side arm of the 27B run")
     ap.add_argument("--no-single", action="store_true", help="skip the single-stream side measurement")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -113,6 +114,25 @@ def main() -> int:
     import torch
     from saber_engine_b200.runtime.bench_core import run_benchmark
     res = run_benchmark(args, ClockSampler)
+    if res is not None and args.gpus == 1 and args.model == "qwen38-27b" and not args.no_extra_arms:
+        # side arm (one GPU only, after the headline has been measured): the same 27B architecture with native
+        # NVFP4 linears, weights and online-quantised activations both 4-bit, on the block-scaled tensor-core
+        # GEMM; a shorter run with a small KV pool.  A failure here never touches the headline line.
+        import copy
+        import gc
+        try:
+            gc.collect()
+            torch.cuda.empty_cache()
+            a2 = copy.copy(args)
+            a2.model, a2.steps, a2.warmup, a2.no_single, a2.max_ctx = "qwen38-27b-nvfp4", min(args.steps, 12), 3, True, 16384
+            r2 = run_benchmark(a2, ClockSampler)
+            res["extra"]["nvfp4_27b"] = {
+                "value": r2["value"], "unit": "tok/s", "ms_per_step": r2["ms_per_step"], "steps": a2.steps, "dtype": r2["dtype"],
+                "e2e_value": r2["e2e"]["value"], "prefill_tok_s": r2["extra"]["prefill_tok_s"],
+                "ttft_512_tokens_ms": r2["extra"]["ttft_512_tokens_ms"], "launches_per_step": r2["extra"]["launches_per_step"],
+                "clocks": r2["clocks"], "max_ctx": 16384}
+        except Exception as exc:       # noqa: BLE001  (reported, not raised)
+            res["extra"]["nvfp4_27b"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     if res is not None:
         print(json.dumps(res))
     return 0

@@ -249,7 +249,9 @@ def run_benchmark(args, ClockSampler):
         "metric": metric, "value": value, "unit": "tok/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": (value / base8) if base8 and streams == 8 else None, "dtype": "w4a8-int8 (bf16 activations)", "data": "synthetic",
+        "vs_baseline": (value / base8) if base8 and streams == 8 else None, "dtype": {"iu8": "w4a8-int8 (bf16 activations)", "mxfp4": "mxfp4 weights x fp8 activations (bf16 residual stream)",
+                  "nvfp4": "nvfp4 weights x nvfp4 activations, block-scaled tensor-core MMA (bf16 residual stream)"}.get(
+                      getattr(cfg, "weight_format", "iu8"), "w4a8-int8 (bf16 activations)"), "data": "synthetic",
         "impl": "ours",
         "config": {"model": cfg.name, "global_batch": streams, "seq_len": args.prompt,
                    "parallelism": f"tp{world}", "verify_width": W, "accept_p": args.accept_p,
