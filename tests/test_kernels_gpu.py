@@ -290,10 +290,11 @@ def _attn_case(ctx_lens, rows, splits, nq=12, nkv=2, seed=0, impl=0, tol=3e-2):
     cache = torch.zeros(nblocks, nkv, 2, 16, 256, dtype=torch.uint8)
     cache_f8 = cache.view(torch.float8_e4m3fn)
     for b in range(nseq):
-        for t in range(ctx_lens[b]):
-            blk = int(perm[b, t // 16])
-            cache_f8[blk, :, 0, t % 16] = k_hist[b][t].to(torch.float8_e4m3fn)
-            cache_f8[blk, :, 1, t % 16] = v_hist[b][t].to(torch.float8_e4m3fn)
+        if ctx_lens[b]:
+            t = torch.arange(ctx_lens[b])
+            blk = perm[b, t // 16].long()
+            cache[blk, :, 0, t % 16] = k_hist[b].to(torch.float8_e4m3fn).view(torch.uint8)
+            cache[blk, :, 1, t % 16] = v_hist[b].to(torch.float8_e4m3fn).view(torch.uint8)
     pos = torch.zeros(3, M, dtype=torch.int32)
     slot_map = torch.zeros(M, dtype=torch.int32)
     cu = [0]
@@ -335,6 +336,12 @@ def test_attention_decode_single_and_split():
     _attn_case([100, 37, 513], [5, 5, 5], splits=1)
     _attn_case([100, 37, 513], [5, 5, 5], splits=4, seed=1)
     _attn_case([0], [9], splits=1, seed=2)           # no history: only this step's rows
+
+
+def test_attention_tcgen05_decode_at_131072_tokens_of_context():
+    """One sequence, 131,072 tokens of history in 8,192 scattered pages, a width-8 decode step over 32 key
+    segments, against the fp32 restatement."""
+    _attn_case([131072], [8], splits=32, impl=1, tol=5e-2, seed=3)
 
 
 def test_attention_tcgen05_decode_prefill_and_splits():

@@ -124,3 +124,52 @@ def test_fused_launches_equal_one_launch_per_op(model):
     fused_n = model.buckets[("decode", 1, 5)].n_launches
     plain_n = plain.buckets[("decode", 1, 5)].n_launches
     assert fused_n < plain_n, (fused_n, plain_n)
+
+
+def test_context_of_131072_tokens_prefill_decode_and_prefix_reuse():
+    """One sequence of 131,072 tokens through the model in 2048-row chunks (8,192 KV pages per attention
+    layer, 32 key segments per decode launch), then decode: speculative == greedy at that depth, and a
+    second sequence that re-uses the first 126,976 tokens' pages and a snapshot of the recurrent state,
+    prefills the rest in other chunk sizes and must produce the same tokens."""
+    cfg = C.scaled_hybrid()
+    T, cut = 131072, 131072 - 4096
+    model = HybridModel(cfg, device="cuda", max_seqs=2, max_ctx=T + 512, max_width=5, seed=1)
+    g = torch.Generator().manual_seed(9)
+    prompt = torch.randint(0, cfg.vocab, (T,), generator=g).tolist()
+    nblk = (T + 512) // cfg.page_tokens
+    blocks_a = list(range(1, 1 + nblk))
+    shared = cut // cfg.page_tokens
+    blocks_b = blocks_a[:shared] + list(range(1 + nblk, 1 + nblk + (nblk - shared)))
+    model.reset_slot(1)
+    b2048 = model.build_bucket("prefill", 1, 2048)
+    snap, res = None, None
+    for pos in range(0, T, 2048):
+        if pos == cut:
+            torch.cuda.synchronize()
+            snap = {i: (model.gdn_state[i][1].clone(), model.gdn_hist[i][1].clone()) for i in model.gdn_state}
+        res = run_bucket(model, b2048, [SeqStep(prompt[pos:pos + 2048], pos, 1, 0, blocks_a, blocks_key=("a", 0))])
+    first = res.tokens[0][0]
+
+    def decode(slot, blocks, first, drafts, width, steps=8):
+        out, shift, pos, n = [first], 0, T, 0
+        b = model.build_bucket("decode", 1, width)
+        while len(out) < steps:
+            rows = [out[-1]] + list(drafts[:width - 1])
+            r = run_bucket(model, b, [SeqStep(rows, pos, slot, shift, blocks, uid=3, step_no=n)])
+            k = r.n_commit[0]
+            out += r.tokens[0]
+            pos, shift, drafts, n = pos + k, k, r.drafts[0], n + 1
+        return out[:steps]
+    # the second sequence first (slot 2): shared pages + restored state, the tail in 512-row chunks
+    model.reset_slot(2)
+    for i, (st, hist) in snap.items():
+        model.gdn_state[i][2].copy_(st)
+        model.gdn_hist[i][2].copy_(hist)
+    b512 = model.build_bucket("prefill", 1, 512)
+    for pos in range(cut, T, 512):
+        res_b = run_bucket(model, b512, [SeqStep(prompt[pos:pos + 512], pos, 2, 0, blocks_b, blocks_key=("b", 0))])
+    assert res_b.tokens[0][0] == first
+    spec_b = decode(2, blocks_b, first, res_b.drafts[0], 5)
+    plain_a = decode(1, blocks_a, first, [], 1)
+    assert spec_b == plain_a
+    model.scratch.check()
