@@ -239,6 +239,100 @@ __global__ void __launch_bounds__(1024) pick_merge_kernel(const PickMergeParams 
   }
 }
 
+// One CTA of 1024 threads per rank.  Push this rank's rows to every peer, raise a flag per peer, wait
+// (bounded) for every peer's flag, then merge: 64 x nranks candidates per row, rank by counting (a
+// candidate's place = how many beat it: larger value, or equal value and smaller id).
+__device__ __forceinline__ void seam_merge_body(const SeamMergeParams& p) {
+  __shared__ float cv[kMaxRanks * 64];
+  __shared__ int ci[kMaxRanks * 64];
+  const int tid = threadIdx.x;
+  const uint32_t seq = *p.seq_base + static_cast<uint32_t>(p.site) + 1u;
+  const uint32_t par = seq & 1u;
+  const size_t slot_words = static_cast<size_t>(p.rows_max) * kSeamWords;
+  for (int peer = 0; peer < p.nranks; ++peer) {
+    if (peer == p.rank) continue;
+    uint32_t* dst = static_cast<uint32_t*>(p.peer_win[peer]) + (par * p.nranks + p.rank) * slot_words;
+    for (int i = tid; i < p.rows * kSeamWords; i += blockDim.x) {
+      const int r = i / kSeamWords, w = i - r * kSeamWords;
+      uint32_t v;
+      if (w < 64) v = static_cast<uint32_t>(p.ids[r * 64 + w]);
+      else if (w < 128) v = __float_as_uint(p.vals[r * 64 + (w - 64)]);
+      else v = __float_as_uint(p.lse[r * 2 + (w - 128)]);
+      dst[i] = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (tid < p.nranks && tid != p.rank) {
+    st_release_sys(p.peer_flags[tid] + par * p.nranks + p.rank, seq);
+    const uint32_t* f = p.peer_flags[p.rank] + par * p.nranks + tid;
+    const unsigned long long t0 = ar_now_ns();
+    while (static_cast<int32_t>(ld_acquire_sys(f) - seq) < 0) {
+      if (ar_now_ns() - t0 > 1000000000ull) { atomicCAS(p.err, 0u, 5u); break; }
+    }
+  }
+  __syncthreads();
+  const uint32_t* win = static_cast<const uint32_t*>(p.peer_win[p.rank]) + par * p.nranks * slot_words;
+  const int ncand = p.nranks * 64;
+  for (int r = 0; r < p.rows; ++r) {
+    for (int c = tid; c < ncand; c += blockDim.x) {
+      const int src = c >> 6, j = c & 63;
+      if (src == p.rank) {
+        cv[c] = p.vals[r * 64 + j];
+        ci[c] = p.ids[r * 64 + j];
+      } else {
+        const uint32_t* w = win + src * slot_words + static_cast<size_t>(r) * kSeamWords;
+        ci[c] = static_cast<int>(__ldcg(w + j));
+        cv[c] = __uint_as_float(__ldcg(w + 64 + j));
+      }
+    }
+    float l1 = 0.f, lT = 0.f;
+    if (tid == 0) {                  // the two log-sum-exps of the whole row, ranks in order
+      float m1 = -INFINITY, mT = -INFINITY;
+      for (int s2 = 0; s2 < p.nranks; ++s2) {
+        const float a = s2 == p.rank ? p.lse[r * 2] : __uint_as_float(__ldcg(win + s2 * slot_words + static_cast<size_t>(r) * kSeamWords + 128));
+        const float b = s2 == p.rank ? p.lse[r * 2 + 1] : __uint_as_float(__ldcg(win + s2 * slot_words + static_cast<size_t>(r) * kSeamWords + 129));
+        m1 = fmaxf(m1, a);
+        mT = fmaxf(mT, b);
+      }
+      float a1 = 0.f, aT = 0.f;
+      for (int s2 = 0; s2 < p.nranks; ++s2) {
+        const float a = s2 == p.rank ? p.lse[r * 2] : __uint_as_float(__ldcg(win + s2 * slot_words + static_cast<size_t>(r) * kSeamWords + 128));
+        const float b = s2 == p.rank ? p.lse[r * 2 + 1] : __uint_as_float(__ldcg(win + s2 * slot_words + static_cast<size_t>(r) * kSeamWords + 129));
+        a1 += expf(a - m1);
+        aT += expf(b - mT);
+      }
+      l1 = m1 + logf(a1);
+      lT = mT + logf(aT);
+    }
+    __syncthreads();                 // candidates staged; every thread has read this row's local values
+    for (int c = tid; c < ncand; c += blockDim.x) {
+      const float v = cv[c];
+      const int id = ci[c];
+      int place = 0;
+      for (int o = 0; o < ncand; ++o) {
+        const float ov = cv[o];
+        const int oi = ci[o];
+        place += (ov > v || (ov == v && oi < id)) ? 1 : 0;
+      }
+      if (place < 64) {
+        p.vals[r * 64 + place] = v;
+        p.ids[r * 64 + place] = id;
+      }
+    }
+    if (tid == 0) { p.lse[r * 2] = l1; p.lse[r * 2 + 1] = lT; }
+    __syncthreads();                 // before the next row overwrites the staging arrays
+  }
+}
+
+__global__ void __launch_bounds__(1024) seam_merge_kernel(const SeamMergeParams p) {
+  pdl_wait();
+  seam_merge_body(p);
+}
+__global__ void __launch_bounds__(1024) seam_merge_emul_kernel(const __grid_constant__ SeamEmulParams e) {
+  seam_merge_body(e.r[blockIdx.x]);
+}
+
 __global__ void comm_advance_kernel(uint32_t* seq_base, uint32_t by) {
   pdl_wait();
   *seq_base += by;
@@ -292,6 +386,23 @@ extern "C" int saber_pick_merge_launch(const saber::PickMergeParams* p, cudaStre
   if (p->nranks < 1 || p->nranks > kMaxRanks || p->rows > p->rows_max) return static_cast<int>(cudaErrorInvalidValue);
   if (p->nranks == 1) return 0;
   saber::launch(pick_merge_kernel, dim3(1), dim3(1024), 0, stream, 0, *p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int saber_seam_merge_launch(const saber::SeamMergeParams* p, cudaStream_t stream) {
+  using namespace saber;
+  if (p->nranks < 1 || p->nranks > kMaxRanks || p->rows > p->rows_max) return static_cast<int>(cudaErrorInvalidValue);
+  if (p->nranks == 1) return 0;
+  saber::launch(seam_merge_kernel, dim3(1), dim3(1024), 0, stream, 0, *p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int saber_seam_merge_emul_launch(const saber::SeamEmulParams* e, cudaStream_t stream) {
+  using namespace saber;
+  if (e->nranks < 2 || e->nranks > kMaxRanks) return static_cast<int>(cudaErrorInvalidValue);
+  for (int r = 0; r < e->nranks; ++r)
+    if (e->r[r].rows > e->r[r].rows_max) return static_cast<int>(cudaErrorInvalidValue);
+  saber::launch(seam_merge_emul_kernel, dim3(e->nranks), dim3(1024), 0, stream, 1, *e);   // cooperative: the blocks wait on one another
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -47,6 +47,26 @@ constexpr int kArProbeMax = 256;
 constexpr int kArDBlocks = 0, kArDMismatch = 1, kArDConverged = 2, kArDNever = 3, kArDAhead = 4, kArDDrift = 5,
               kArDTimeout = 6, kArDFirstSeq = 8, kArDFirstBlock = 9, kArDFirstSrc = 10, kArDPolls = 11, kArDLastSeq = 12;
 
+// Sampling on vocabulary-sharded ranks: every rank holds the 64 best (value, id) of its shard per head
+// row and the row's two log-sum-exps; the ranks swap them through peer windows and each merges the
+// union to the global best 64 (value desc, id asc) and the global log-sum-exps, in place.  The device
+// draw then runs on identical candidates on every rank.
+constexpr int kSeamWords = 64 * 2 + 2;            // ids | value bits | two lse words, per row
+struct SeamMergeParams {
+  int32_t* ids;                 // [rows][64] in: this shard's candidates (global ids), out: the merged ones
+  float* vals;                  // [rows][64]
+  float* lse;                   // [rows][2]
+  void* peer_win[kMaxRanks];    // each rank's window: [2][nranks][rows_max][kSeamWords] words
+  uint32_t* peer_flags[kMaxRanks];  // each rank's flags: [2][nranks]
+  const uint32_t* seq_base;
+  uint32_t* err;
+  int rows, rows_max, site, nranks, rank;
+};
+struct SeamEmulParams {         // test form: all ranks of a one-device group in ONE cooperative launch
+  SeamMergeParams r[kMaxRanks];
+  int nranks;
+};
+
 struct ArEmulParams {           // test form: every rank of a one-device group in ONE cooperative launch
   AllReduceParams r[kMaxRanks];
   int nranks, checked;
@@ -68,6 +88,8 @@ struct PickMergeParams {
 
 extern "C" int saber_pick_merge_launch(const saber::PickMergeParams* p, cudaStream_t stream);
 extern "C" int saber_allreduce_launch(const saber::AllReduceParams* p, cudaStream_t stream);
+extern "C" int saber_seam_merge_launch(const saber::SeamMergeParams* p, cudaStream_t stream);
+extern "C" int saber_seam_merge_emul_launch(const saber::SeamEmulParams* p, cudaStream_t stream);
 extern "C" int saber_allreduce_chk_launch(const saber::AllReduceParams* p, cudaStream_t stream);
 extern "C" int saber_allreduce_emul_launch(const saber::ArEmulParams* p, cudaStream_t stream);
 extern "C" int saber_comm_advance_launch(uint32_t* seq_base, uint32_t by, cudaStream_t stream);

@@ -40,6 +40,7 @@ struct OpExpand { const void* ctx; const void* tok; const void* pos; void* out; 
 struct OpAdvance { uint32_t* seq_base; uint32_t by; };
 struct OpGdnConv { saber::GdnConvParams p; int nseq; };
 struct OpGdnRec { saber::GdnRecParams p; int nseq, vs; };
+struct OpSeamMerge { saber::SeamMergeParams p; };
 struct OpGdnStep { saber::GdnStepParams p; int nseq; };
 struct OpGdnChunk { saber::GdnRecParams p; int nseq, max_rows; float* scratch; };
 struct OpRope { saber::RopeKvParams p; };
@@ -61,7 +62,7 @@ struct OpMoeGather { const int8_t* q; const float* scale; int M_pad; const int32
                      int8_t* q_out; float* scale_out; int rows_cap, M_pad_out, K; };
 
 using Op = std::variant<OpGemm, OpRow, OpEmbed, OpGdnConv, OpGdnRec, OpRope, OpAttn, OpArgmax,
-                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather, OpDigest, OpDigestClear, OpGdnChunk, OpLogitGather, OpSampleSeam, OpGdnStep>;
+                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather, OpDigest, OpDigestClear, OpGdnChunk, OpLogitGather, OpSampleSeam, OpGdnStep, OpSeamMerge>;
 
 struct Entry {
   Op op;
@@ -109,6 +110,7 @@ int launch(const Op& op, cudaStream_t s) {
         else if constexpr (std::is_same_v<T, OpCopy>)
           return static_cast<int>(cudaMemcpyAsync(o.dst, o.src, o.bytes, cudaMemcpyDeviceToDevice, s));
         else if constexpr (std::is_same_v<T, OpAllReduce>) return saber_allreduce_launch(&o.p, s);
+        else if constexpr (std::is_same_v<T, OpSeamMerge>) return saber_seam_merge_launch(&o.p, s);
         else if constexpr (std::is_same_v<T, OpPickMerge>) return saber_pick_merge_launch(&o.p, s);
         else if constexpr (std::is_same_v<T, OpMoeRoute>) return saber_moe_route_launch(&o.p, s);
         else if constexpr (std::is_same_v<T, OpMoeCombine>) return saber_moe_combine_launch(&o.p, s);
@@ -232,6 +234,9 @@ int saber_program_add_memset(void* h, void* dst, int value, size_t bytes, const 
 }
 int saber_program_add_copy(void* h, void* dst, const void* src, size_t bytes, const char* tag) {
   return add(h, OpCopy{dst, src, bytes}, 1, tag);
+}
+int saber_program_add_seam_merge(void* h, const saber::SeamMergeParams* p, const char* tag) {
+  return add(h, OpSeamMerge{*p}, 1, tag);
 }
 int saber_program_add_pick_merge(void* h, const saber::PickMergeParams* p, const char* tag) {
   return add(h, OpPickMerge{*p}, p->nranks > 1 ? 1 : 0, tag);

@@ -551,10 +551,14 @@ class HybridModel:
             s_vals = seam_dev[Mh * N.SEAM_K: 2 * Mh * N.SEAM_K].view(torch.float32)
             s_lse = seam_dev[2 * Mh * N.SEAM_K:].view(torch.float32)
             prog.seam(logits, Mh, logits.stride(0), sh.vocab, sh.vocab_first, None, s_ids, s_vals, s_lse, tag="topk_seam")
-            if self.tp == 1:
-                # device draw for sampled rows: the picks that verify / accept and the drafter see are
-                # the sampled tokens (the host repeats the draw from the same candidates and uniforms)
-                prog.sample_seam(s_ids, s_vals, at(lay.samp), at(lay.samp_u), o_picks, Mh, tag="sample_seam")
+            if self.tp > 1:
+                # vocabulary-sharded ranks swap their candidates through the symmetric heap and merge them
+                # on the device: every rank then holds the same global best 64 and log-sum-exps
+                prog.seam_merge(self.comm.seam_merge_params(s_ids, s_vals, s_lse, Mh, ar_site), tag="seam_merge")
+                ar_site += 1
+            # device draw for sampled rows: the picks that verify / accept and the drafter see are the
+            # sampled tokens (the host repeats the draw from the same candidates and uniforms)
+            prog.sample_seam(s_ids, s_vals, at(lay.samp), at(lay.samp_u), o_picks, Mh, tag="sample_seam")
             keep += [seam_dev]
         plp_dev = None
         if self._want_plp:

@@ -117,6 +117,15 @@ AR_DIAG = {"blocks": 0, "mismatch": 1, "converged": 2, "never": 3, "ahead": 4, "
            "first_seq": 8, "first_block": 9, "first_src": 10, "polls": 11, "last_seq": 12}
 
 
+class SeamMergeParams(C.Structure):
+    _fields_ = [("ids", P), ("vals", P), ("lse", P), ("peer_win", P * MAX_RANKS), ("peer_flags", P * MAX_RANKS),
+                ("seq_base", P), ("err", P), ("rows", I), ("rows_max", I), ("site", I), ("nranks", I), ("rank", I)]
+
+
+class SeamEmulParams(C.Structure):
+    _fields_ = [("r", SeamMergeParams * MAX_RANKS), ("nranks", I)]
+
+
 class PickMergeParams(C.Structure):
     _fields_ = [("idx", P), ("val", P), ("peer_win", P * MAX_RANKS), ("peer_flags", P * MAX_RANKS),
                 ("seq_base", P), ("err", P), ("rows", I), ("rows_max", I), ("site", I), ("nranks", I), ("rank", I)]
@@ -207,6 +216,9 @@ def _declare(L: C.CDLL) -> None:
         "saber_allreduce_chk_launch": (I, [C.POINTER(AllReduceParams), S]),
         "saber_allreduce_emul_launch": (I, [C.POINTER(ArEmulParams), S]),
         "saber_pick_merge_launch": (I, [C.POINTER(PickMergeParams), S]),
+        "saber_seam_merge_launch": (I, [C.POINTER(SeamMergeParams), S]),
+        "saber_seam_merge_emul_launch": (I, [C.POINTER(SeamEmulParams), S]),
+        "saber_program_add_seam_merge": (I, [P, C.POINTER(SeamMergeParams), C.c_char_p]),
         "saber_program_add_pick_merge": (I, [P, C.POINTER(PickMergeParams), C.c_char_p]),
         "saber_comm_advance_launch": (I, [P, U32, S]),
         "saber_ipc_get_handle": (I, [P, P]),
@@ -375,6 +387,9 @@ class Program:
     def copy(self, dst: torch.Tensor, src: torch.Tensor, tag="copy") -> int:
         nbytes = src.numel() * src.element_size()
         return self._L.saber_program_add_copy(self._h, ptr(dst), ptr(src), nbytes, tag.encode())
+
+    def seam_merge(self, p: "SeamMergeParams", tag="seam_merge") -> int:
+        return self._L.saber_program_add_seam_merge(self._h, C.byref(p), tag.encode())
 
     def pick_merge(self, p: "PickMergeParams", tag="pick_merge") -> int:
         return self._L.saber_program_add_pick_merge(self._h, C.byref(p), tag.encode())

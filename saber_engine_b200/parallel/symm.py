@@ -49,6 +49,8 @@ class HeapLayout:
     ar_flags: int = 0
     pick_win: int = 0
     pick_flags: int = 0
+    seam_win: int = 0      # [2 parity][nranks][rows_max][130 words] sampling candidates of the other ranks
+    seam_flags: int = 0
     ag_q: int = 0          # all-gathered quantised activations [hidden / 128][rows_pad][128] bytes
     ag_scale: int = 0      # [rows_pad] fp32
     ag_flags: int = 0      # [2 parity][64 row tiles] arrival flags
@@ -71,6 +73,8 @@ class HeapLayout:
         L.ar_flags = take(2 * nranks * N.AR_BLOCKS * 4)
         L.pick_win = take(2 * nranks * rows_max * 8)
         L.pick_flags = take(2 * nranks * 4)
+        L.seam_win = take(2 * nranks * rows_max * 130 * 4)
+        L.seam_flags = take(2 * nranks * 4)
         L.rows_pad = (rows_max + 127) // 128 * 128
         L.ag_q = take(L.rows_pad * max(128, (hidden + 127) // 128 * 128))
         L.ag_scale = take(L.rows_pad * 4)
@@ -82,9 +86,9 @@ class HeapLayout:
 
     def digest(self) -> str:
         d = {k: getattr(self, k) for k in ("nranks", "rows_max", "hidden", "gemm_recv", "gemm_flags", "ar_recv",
-                                            "ar_flags", "pick_win", "pick_flags", "ag_q", "ag_scale", "ag_flags",
+                                            "ar_flags", "pick_win", "pick_flags", "seam_win", "seam_flags", "ag_q", "ag_scale", "ag_flags",
                                             "ag_counter", "total")}
-        d["protocol"] = "saber-b200-symm/2"
+        d["protocol"] = "saber-b200-symm/3"
         return hashlib.sha256(json.dumps(d, sort_keys=True).encode()).hexdigest()
 
 
@@ -222,6 +226,18 @@ class SymmetricComm:
         p.seq_base, p.err = self.seq_base.data_ptr(), self.err.data_ptr()
         p.n_elems, p.max_elems, p.site, p.nranks, p.rank = n_elems, lay.ar_max_elems, site, self.nranks, self.rank
         p.spin_limit_us = 0
+        return p
+
+    def seam_merge_params(self, ids: torch.Tensor, vals: torch.Tensor, lse: torch.Tensor, rows: int, site: int) -> N.SeamMergeParams:
+        """Swap and merge the ranks' sampling candidates (64 per head row and shard) on the device."""
+        lay = self.layout
+        p = N.SeamMergeParams()
+        p.ids, p.vals, p.lse = ids.data_ptr(), vals.data_ptr(), lse.data_ptr()
+        for r in range(self.nranks):
+            p.peer_win[r] = self.bases[r] + lay.seam_win
+            p.peer_flags[r] = self.bases[r] + lay.seam_flags
+        p.seq_base, p.err = self.seq_base.data_ptr(), self.err.data_ptr()
+        p.rows, p.rows_max, p.site, p.nranks, p.rank = rows, lay.rows_max, site, self.nranks, self.rank
         return p
 
     def pick_merge_params(self, idx: torch.Tensor, val: torch.Tensor, rows: int, site: int) -> N.PickMergeParams:

@@ -108,16 +108,14 @@ class HybridExecutor:
         return out
 
     def _seams(self, b, rows_of: list) -> list:
-        """Per run: {"ids", "vals", "lse"} over the run's head rows, from the bucket's read-back blob;
-        with vocabulary-sharded ranks the per-rank candidates are gathered and merged first."""
+        """Per run: {"ids", "vals", "lse"} over the run's head rows, from the bucket's read-back blob (on
+        vocabulary-sharded ranks the program has already merged the ranks' candidates on the device)."""
         import numpy as np
         K, Mh = N_SEAM_K, b.Mh
         a = b.seam_host.numpy()
         ids = a[:Mh * K].reshape(Mh, K)
         vals = a[Mh * K: 2 * Mh * K].view(np.float32).reshape(Mh, K)
         lse = a[2 * Mh * K:].view(np.float32).reshape(Mh, 2)[:, 0]
-        if self.model.tp > 1:
-            ids, vals, lse = gather_rank_seams(ids, vals, lse, self.model.device)
         return [{"ids": ids[r0:r1].tolist(), "vals": vals[r0:r1].tolist(), "lse": lse[r0:r1].tolist()}
                 for r0, r1 in rows_of]
 

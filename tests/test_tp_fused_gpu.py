@@ -236,3 +236,44 @@ def test_allreduce_checked_twin_computes_the_served_bytes_and_counts_a_missing_c
     for g in group:
         g.check()
     group[0].close()
+
+
+@pytest.mark.parametrize("nranks", [2, 4, 8])
+def test_sampling_candidates_merge_on_the_device_across_vocabulary_shards(nranks):
+    """Every rank takes the 64 best logits of its vocabulary shard; the ranks swap them through the
+    heap and merge on the device (all ranks in one cooperative launch here).  Each rank must end with
+    the global best 64 (value desc, id asc) and the whole row's log-sum-exps, identical everywhere, so
+    the device draw picks the same token on every rank."""
+    rows, V = 9, 8192
+    group = SymmetricComm.local_group(nranks, DEV, max_elems=128 * 256, rows_max=128, hidden=256)
+    torch.manual_seed(nranks)
+    logits = (torch.randn(rows, V, device=DEV) * 3).to(torch.bfloat16)
+    logits[:, 100] = logits[:, 7000]                     # ties across shards: the lower id wins
+    temps = torch.full((rows,), 0.7, device=DEV)
+    vs = V // nranks
+    shards = [F.topk_seam(logits[:, r * vs:(r + 1) * vs].contiguous(), temps, id_offset=r * vs) for r in range(nranks)]
+    want_ids, want_vals, want_lse = F.topk_seam(logits, temps)
+    e = N.SeamEmulParams()
+    e.nranks = nranks
+    for r, g in enumerate(group):
+        e.r[r] = g.seam_merge_params(shards[r][0], shards[r][1], shards[r][2], rows, site=0)
+    N.check(N.lib().saber_seam_merge_emul_launch(C.byref(e), N.stream_handle()), "seam merge (emulated ranks)")
+    torch.cuda.synchronize()
+    for r in range(nranks):
+        ids, vals, lse = shards[r]
+        assert torch.equal(ids, want_ids) and torch.equal(vals, want_vals), r
+        assert torch.allclose(lse, want_lse, atol=2e-3, rtol=1e-4)
+    # the device draw on two different ranks' merged rows: same candidates, same uniforms, same tokens
+    samp = torch.tensor([[0.7, 40, 0.9, 0.0]] * rows, device=DEV)
+    u = torch.rand(rows, device=DEV)
+    picks = []
+    for r in (0, nranks - 1):
+        pk = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+        N.check(N.lib().saber_sample_seam_launch(shards[r][0].data_ptr(), shards[r][1].data_ptr(), samp.data_ptr(), u.data_ptr(),
+                                                 pk.data_ptr(), rows, N.stream_handle()), "sample_seam")
+        picks.append(pk)
+    torch.cuda.synchronize()
+    assert torch.equal(picks[0], picks[1]) and int(picks[0].min()) >= 0
+    for g in group:
+        g.check()
+    group[0].close()
