@@ -102,6 +102,7 @@ def main() -> int:
     ap.add_argument("--rung", type=int, default=2048)
     ap.add_argument("--max-ctx", type=int, default=0, help="context the KV pool and block tables are sized for (0: the model's 262,144)")
     ap.add_argument("--pdl", type=int, default=-1, help="programmatic dependent launch: 0 off, 1 all kernels, 2 GEMMs only (A/B)")
+    ap.add_argument("--fuse", type=int, default=1, help="fused GEMM tails (silu-quant epilogue, add-norm-quant row tail): 1 on, 0 off (A/B)")
     ap.add_argument("--gdn-fused", type=int, default=-1, help="DeltaNet decode step as one launch (1) or three (0); -1: the model's default (A/B)")
     ap.add_argument("--no-tune-table", action="store_true", help="ignore the committed autotune table (A/B)")
     ap.add_argument("--no-extra-arms", action="store_true", help="skip the NVFP4 side arm of the 27B run")

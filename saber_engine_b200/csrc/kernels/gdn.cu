@@ -7,7 +7,7 @@
 // 1/sqrt(128).  Parity: crates/saber-kernels/hip/sgdn_rec.h:1-30 (recurrence), sgdn_conv.h:1-10
 // (conv), and the base + stash + replay form of sgdn_replay.h:1-12: the state in memory is always
 // the COMMITTED state; a speculative step's rows run on a register copy and leave only a small
-// stash (k, v, g, beta per row); the next step first replays the `shift` rows that were accepted,
+// stash (k, u, g per row: u = beta (v - S k) as the row computed it); the next step first replays the `shift` rows that were accepted,
 // stores the new committed state, and then answers its own rows.  No per-row state snapshots.
 //
 // Two launches per layer: conv_update (thread = channel, block = one 128-wide head so the q/k L2
@@ -165,6 +165,7 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
   __shared__ __align__(16) float ks[kRecBatch][2 * KP];
   __shared__ __align__(16) float qs[kRecBatch][2 * KP];
   __shared__ __align__(16) float vsm[kRecBatch][VR];
+  __shared__ __align__(16) float usm[kRecBatch][VR];     // u of this step's rows (what the stash keeps instead of v)
   __shared__ float gsm[kRecBatch], bsm[kRecBatch];
   // the replayed rows of the previous step have buffers of their own: they are fetched together
   // with this step's first batch and the state, so the kernel waits for global memory once
@@ -236,8 +237,21 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
   asm volatile("cp.async.wait_all;" ::: "memory");
   __syncthreads();
 
+  // replay of a row whose u is known: S <- S e^g + u (x) k (the same two operations, in the same
+  // order, that the row itself applied: the state comes out bit-identical, without its dot product)
+  auto replay = [&](const float* kv, float u, float g) {
+    const ulonglong2* kv2 = reinterpret_cast<const ulonglong2*>(kv);
+    const float decay = __expf(g);
+    const f32x2 dec2 = pack2(decay, decay), u2 = pack2(u, u);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const ulonglong2 kk = kv2[i];
+      S[2 * i] = fma2(u2, kk.x, mul2(S[2 * i], dec2));
+      S[2 * i + 1] = fma2(u2, kk.y, mul2(S[2 * i + 1], dec2));
+    }
+  };
   auto apply = [&](const float* kv, const float* qv, float vval, float g, float beta,
-                   bool want_o) -> float {
+                   bool want_o, float& u_out) -> float {
     const ulonglong2* kv2 = reinterpret_cast<const ulonglong2*>(kv);   // 16-byte aligned rows
     const ulonglong2* qv2 = reinterpret_cast<const ulonglong2*>(qv);
     const float decay = __expf(g);
@@ -254,6 +268,7 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
     float dot = (sum2(acc[0]) + sum2(acc[1])) + (sum2(acc[2]) + sum2(acc[3]));
     dot += __shfl_xor_sync(0xffffffffu, dot, 1);
     const float u = (vval - dot) * beta;
+    u_out = u;
     const f32x2 u2 = pack2(u, u);
     f32x2 oac[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
@@ -277,7 +292,7 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
 
   // ---- replay the accepted rows of the previous step, then store the committed state
   if (shift > 0) {
-    for (int r = 0; r < shift; ++r) apply(&ksr[r][kh * KP], nullptr, vsr[r][vloc], gsr[r], bsr[r], false);
+    for (int r = 0; r < shift; ++r) replay(&ksr[r][kh * KP], vsr[r][vloc], gsr[r]);      // (vsr holds the stashed u)
 #pragma unroll
     for (int i = 0; i < 16; ++i)
       reinterpret_cast<ulonglong2*>(sp)[i] = make_ulonglong2(S[2 * i], S[2 * i + 1]);
@@ -307,11 +322,15 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
       __syncthreads();
     }
     for (int r = 0; r < nb; ++r) {
-      const float o = apply(&ks[r][kh * KP], &qs[r][kh * KP], vsm[r][vloc], gsm[r], bsm[r], true);
-      if (kh == 0)
+      float u;
+      const float o = apply(&ks[r][kh * KP], &qs[r][kh * KP], vsm[r][vloc], gsm[r], bsm[r], true, u);
+      if (kh == 0) {
         p.out[static_cast<size_t>(row0 + r0 + r) * (static_cast<size_t>(p.HV) * 128) + h * 128 + v] = o;
+        usm[r][vloc] = u;
+      }
     }
     if (!p.commit) {
+      __syncthreads();      // u of every row is in shared memory
       for (int idx = tid; idx < nb * 128; idx += NT) {
         const int r = idx >> 7, i = idx & 127;
         if (r0 + r < p.stash_rows)
@@ -319,7 +338,7 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
       }
       for (int idx = tid; idx < nb * VR; idx += NT) {
         const int r = idx / VR, i = idx % VR;
-        if (r0 + r < p.stash_rows) stash[static_cast<size_t>(r0 + r) * stash_row + 128 + i] = vsm[r][i];
+        if (r0 + r < p.stash_rows) stash[static_cast<size_t>(r0 + r) * stash_row + 128 + i] = usm[r][i];
       }
       if (tid < nb && r0 + tid < p.stash_rows) {
         stash[static_cast<size_t>(r0 + tid) * stash_row + 128 + VR] = gsm[tid];

@@ -183,7 +183,18 @@ __global__ void __launch_bounds__(kStepThreads, 2) gdn_step_kernel(const GdnStep
   __syncthreads();
 
   // ---- phase 1: the recurrence (the arithmetic of gdn_recurrent_kernel, one v slice)
-  auto apply = [&](const float* kv, const float* qv, float vval, float g, float beta, bool want_o) -> float {
+  auto replay = [&](const float* kv, float u, float g) {     // a row whose u is known (the stash keeps u, not v)
+    const ulonglong2* kv2 = reinterpret_cast<const ulonglong2*>(kv);
+    const float decay = __expf(g);
+    const gs_f32x2 dec2 = gs_pack2(decay, decay), u2 = gs_pack2(u, u);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const ulonglong2 kk = kv2[i];
+      S[2 * i] = gs_fma2(u2, kk.x, gs_mul2(S[2 * i], dec2));
+      S[2 * i + 1] = gs_fma2(u2, kk.y, gs_mul2(S[2 * i + 1], dec2));
+    }
+  };
+  auto apply = [&](const float* kv, const float* qv, float vval, float g, float beta, bool want_o, float& u_out) -> float {
     const ulonglong2* kv2 = reinterpret_cast<const ulonglong2*>(kv);
     const ulonglong2* qv2 = reinterpret_cast<const ulonglong2*>(qv);
     const float decay = __expf(g);
@@ -200,6 +211,7 @@ __global__ void __launch_bounds__(kStepThreads, 2) gdn_step_kernel(const GdnStep
     float dot = (gs_sum2(acc[0]) + gs_sum2(acc[1])) + (gs_sum2(acc[2]) + gs_sum2(acc[3]));
     dot += __shfl_xor_sync(0xffffffffu, dot, 1);
     const float u = (vval - dot) * beta;
+    u_out = u;
     const gs_f32x2 u2 = gs_pack2(u, u);
     gs_f32x2 oac[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
@@ -221,16 +233,21 @@ __global__ void __launch_bounds__(kStepThreads, 2) gdn_step_kernel(const GdnStep
     return o;
   };
   if (shift > 0) {
-    for (int r = 0; r < shift; ++r) apply(&ksr[r][kh * KP], nullptr, vsr[r][vloc], gsr[r], bsr[r], false);
+    for (int r = 0; r < shift; ++r) replay(&ksr[r][kh * KP], vsr[r][vloc], gsr[r]);
 #pragma unroll
     for (int i = 0; i < 16; ++i)
       reinterpret_cast<ulonglong2*>(sp)[i] = make_ulonglong2(S[2 * i], S[2 * i + 1]);
   }
   __syncthreads();                         // every thread is done with the replayed v rows: the buffer becomes the output rows
   for (int r = 0; r < n; ++r) {
-    const float o = apply(&ks[r][kh * KP], &qs[r][kh * KP], vsm[r][vloc], gsm[r], bsm[r], true);
-    if (kh == 0) vsr[r][vloc] = o;
+    float u;
+    const float o = apply(&ks[r][kh * KP], &qs[r][kh * KP], vsm[r][vloc], gsm[r], bsm[r], true, u);
+    if (kh == 0) {
+      vsr[r][vloc] = o;
+      vsm[r][vloc] = u;          // (this thread pair is the only reader of vsm[r][vloc]: the stash takes u)
+    }
   }
+  __syncthreads();
   // stash of this step's rows: k [128] | v [128] | g, beta
   for (int idx = tid; idx < n * 128; idx += kStepThreads) {
     const int r = idx >> 7, i = idx & 127;
