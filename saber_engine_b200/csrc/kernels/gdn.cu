@@ -165,7 +165,6 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
   __shared__ __align__(16) float ks[kRecBatch][2 * KP];
   __shared__ __align__(16) float qs[kRecBatch][2 * KP];
   __shared__ __align__(16) float vsm[kRecBatch][VR];
-  __shared__ __align__(16) float usm[kRecBatch][VR];     // u of this step's rows (what the stash keeps instead of v)
   __shared__ float gsm[kRecBatch], bsm[kRecBatch];
   // the replayed rows of the previous step have buffers of their own: they are fetched together
   // with this step's first batch and the state, so the kernel waits for global memory once
@@ -326,7 +325,8 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
       const float o = apply(&ks[r][kh * KP], &qs[r][kh * KP], vsm[r][vloc], gsm[r], bsm[r], true, u);
       if (kh == 0) {
         p.out[static_cast<size_t>(row0 + r0 + r) * (static_cast<size_t>(p.HV) * 128) + h * 128 + v] = o;
-        usm[r][vloc] = u;
+        vsm[r][vloc] = u;        // (the thread pair of this state row is the only reader of vsm[r][vloc], and both of
+                                 //  its lanes took the value before the shuffles inside apply: the stash takes u from here)
       }
     }
     if (!p.commit) {
@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
       }
       for (int idx = tid; idx < nb * VR; idx += NT) {
         const int r = idx / VR, i = idx % VR;
-        if (r0 + r < p.stash_rows) stash[static_cast<size_t>(r0 + r) * stash_row + 128 + i] = usm[r][i];
+        if (r0 + r < p.stash_rows) stash[static_cast<size_t>(r0 + r) * stash_row + 128 + i] = vsm[r][i];
       }
       if (tid < nb && r0 + tid < p.stash_rows) {
         stash[static_cast<size_t>(r0 + tid) * stash_row + 128 + VR] = gsm[tid];
@@ -535,7 +535,10 @@ extern "C" int saber_gdn_recurrent_launch(const saber::GdnRecParams* p, int nseq
   if (p->commit && p->prefill_rows) {      // long committing runs: the latency-oriented form
     // two state rows per thread measured 863 us per 2048 rows, four 904 us, the first form (one row per
     // eight threads, synchronous staging) 1071 us
-    saber::launch(gdn_prefill_rows_kernel<2>, dim3(p->HV * 4, nseq), dim3(128), 0, stream, 0, *p);
+    // (prefill_rows selects the form: 1 = two state rows per thread, 2 = one, 3 = four)
+    if (p->prefill_rows == 2) saber::launch(gdn_prefill_rows_kernel<1>, dim3(p->HV * 4, nseq), dim3(256), 0, stream, 0, *p);
+    else if (p->prefill_rows == 3) saber::launch(gdn_prefill_rows_kernel<4>, dim3(p->HV * 4, nseq), dim3(64), 0, stream, 0, *p);
+    else saber::launch(gdn_prefill_rows_kernel<2>, dim3(p->HV * 4, nseq), dim3(128), 0, stream, 0, *p);
     return static_cast<int>(cudaGetLastError());
   }
   if (vs == 1) saber::launch(gdn_recurrent_kernel<1>, dim3(dim3(p->HV, nseq)), dim3(256), 0, stream, 0, *p);

@@ -439,7 +439,7 @@ def gdn_rec_params(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift,
     p.C, p.n_q, p.n_k, p.HV, p.HK = qkv.shape[1], n_q, n_k, HV, HK
     p.ldba = ldba if ldba is not None else ba.stride(0)
     p.stash_rows, p.commit = stash.shape[1], int(commit)
-    p.prefill_rows = int(bool(prefill_rows and commit))
+    p.prefill_rows = int(prefill_rows) if commit else 0      # 1: two state rows per thread (default), 2: one, 3: four
     return p
 
 

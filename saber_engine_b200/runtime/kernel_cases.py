@@ -165,7 +165,7 @@ def _gdn_step(nseq, n, shift, copies=3):
     return states, stashes, hists, x, qa, scr, conv_out, o
 
 
-def _gdn_prefill(n, copies=3):
+def _gdn_prefill(n, copies=3, form=1):
     """One sequence of n rows through the committing row-by-row form the prefill rungs use."""
     HV, HK, d = 48, 16, 128
     C_ = 2 * HK * d + HV * d
@@ -179,11 +179,11 @@ def _gdn_prefill(n, copies=3):
     sh = torch.zeros(1, dtype=torch.int32, device=DEV)
     out = torch.empty(n, HV * d, device=DEV)
     ps = [F.gdn_rec_params(qkv, ba, A_log, dtb, st, stash, cu, slots, sh, out, HK * d, HK * d, HV, HK, True,
-                           prefill_rows=True) for st in states]
+                           prefill_rows=form) for st in states]
     torch.cuda.synchronize()
     lib = N.lib()
     fns = [lambda p=p: N.check(lib.saber_gdn_recurrent_launch(C.byref(p), 1, 2, N.stream_handle()), "gdn") for p in ps]
-    _time(fns, f"gdn prefill rows n={n}", n * (2 * HK * d + HV * d) * 4.0 + n * HV * d * 4.0)
+    _time(fns, f"gdn prefill rows n={n} form={form}", n * (2 * HK * d + HV * d) * 4.0 + n * HV * d * 4.0)
     return states, out
 
 
@@ -264,6 +264,9 @@ CASES = {
     "gdn_step_b8_w8": lambda: _gdn_step(8, 8, 4),
     "gdn_step_b1_w8": lambda: _gdn_step(1, 8, 4),
     "gdn_prefill_2048": lambda: _gdn_prefill(2048),
+    "gdn_prefill_2048_one_row": lambda: _gdn_prefill(2048, form=2),
+    "gdn_prefill_512": lambda: _gdn_prefill(512),
+    "gdn_prefill_512_one_row": lambda: _gdn_prefill(512, form=2),
     "row_add_rms_m72": lambda: _row(72, 5120),
     "moe_block_m72": lambda: _moe(72),
     "vision_tower_512": lambda: _vision(512),
