@@ -18,7 +18,8 @@ from typing import Optional
 SCHEMA = {
     "": {"schema_version", "name", "device", "gemm", "attn_tc", "attn_paged", "gdn"},
     "device": {"sms", "smem_per_cta", "tmem_columns"},
-    "gemm": {"symbol", "tile_n", "tile_k", "threads", "token_tiles", "splits", "halves", "stages"},
+    "gemm": {"symbol", "tile_n", "tile_k", "threads", "token_tiles", "splits", "halves", "stages", "tails"},
+    "gemm.tails": {"row_tail_max_ranks"},
     "gemm.splits": {"waves", "max_parts", "min_kb_per_split", "min_kb", "skip_when_fill_above"},
     "gemm.halves": {"formats", "fill_above", "fill_up_to"},
     "gemm.stages": {"int4", "int8", "mxfp4", "pair"},
