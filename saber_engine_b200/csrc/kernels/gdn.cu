@@ -38,6 +38,7 @@ __device__ __forceinline__ __nv_bfloat16* gdn_hist_current(const GdnConvParams& 
 // for the first rows of the step, from the committed window in `hist`).
 constexpr int kConvChunk = 32;
 __global__ void __launch_bounds__(128) gdn_conv_update_kernel(const GdnConvParams p) {
+  pdl_trigger();   // the recurrence that follows loads its state (which no kernel of this step writes before it) meanwhile
   pdl_wait();
   __shared__ float red[4];
   const int b = blockIdx.y;
@@ -158,7 +159,6 @@ __device__ __forceinline__ void gdn_cp16(void* dst_smem, const void* src) {
 template <int VS>
 __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecParams p) {
   pdl_trigger();   // successors (the norm rows, then a GEMM) get resident on the SMs the last round leaves idle
-  pdl_wait();
   constexpr int VR = 128 / VS;         // v rows per CTA
   constexpr int NT = 2 * VR;           // threads
   constexpr int KP = 64 + 4;           // padded half stride in shared memory (bank spread)
@@ -187,8 +187,18 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
   float* stash = p.stash + ((static_cast<size_t>(slot) * p.stash_rows) * p.HV * VS +
                             static_cast<size_t>(h) * VS + vs) * stash_stride;
   const size_t stash_row = static_cast<size_t>(p.HV) * VS * stash_stride;
+  // The state goes out FIRST, before the wait for the predecessor (the conv kernel): the index tables were
+  // uploaded before the program started and the state was last written by the previous step.
+  f32x2 S[32];   // this thread's 64 state values as packed pairs
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const ulonglong2 t = reinterpret_cast<const ulonglong2*>(sp)[i];
+    S[2 * i] = t.x;
+    S[2 * i + 1] = t.y;
+  }
+  pdl_wait();
 
-  // ---- everything this CTA reads from global memory goes out now: replay rows, first batch, state
+  // ---- everything else this CTA reads from global memory goes out now: replay rows, first batch
   const int nb0 = min(kRecBatch, n);
   for (int idx = tid; idx < shift * 32; idx += NT) {
     const int r = idx >> 5, i = (idx & 31) * 4;
@@ -218,13 +228,6 @@ __global__ void __launch_bounds__(256 / VS) gdn_recurrent_kernel(const GdnRecPar
     const size_t m = static_cast<size_t>(row0 + tid);
     bb0 = __bfloat162float(p.ba[m * p.ldba + h]);
     aa0 = __bfloat162float(p.ba[m * p.ldba + p.HV + h]);
-  }
-  f32x2 S[32];   // this thread's 64 state values as packed pairs
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const ulonglong2 t = reinterpret_cast<const ulonglong2*>(sp)[i];
-    S[2 * i] = t.x;
-    S[2 * i + 1] = t.y;
   }
   const float neg_a = -__expf(p.A_log[h]);
   const float dtb = p.dt_bias[h];
