@@ -62,7 +62,7 @@ def tune_shape(Nn: int, K: int, M: int, w4: int, sweeper: Sweeper, dev) -> "Tune
     ws = [F.QuantWeight(t, scale, Nn, K, bool(w4)) for t in tiles]
     x = torch.randn(M, K, device=dev).to(torch.bfloat16)
     qa = F.plain_quant(x)
-    out = torch.empty(M, Nn, dtype=torch.bfloat16, device=dev)
+    out = torch.empty(M, (Nn + 7) // 8 * 8, dtype=torch.bfloat16, device=dev)[:, :Nn]      # rows 16-byte aligned, as the model's buffers are
     nt = L.token_tile(M)
     m_tiles = (M + nt - 1) // nt
     cands = candidates(n_pad // L.TILE_N, m_tiles, K // 128, nt, w4)
@@ -127,7 +127,7 @@ def main(argv=None) -> int:
                                           dtype=torch.uint8, device=dev),
                             torch.rand(n_pad, device=dev) * 1e-3, Nn, K, bool(w4)) for _ in range(4)]
         qa = F.plain_quant(torch.randn(M, K, device=dev).to(torch.bfloat16))
-        out = torch.empty(M, Nn, dtype=torch.bfloat16, device=dev)
+        out = torch.empty(M, (Nn + 7) // 8 * 8, dtype=torch.bfloat16, device=dev)[:, :Nn]      # rows 16-byte aligned, as the model's buffers are
         for i in range(6):
             pr = F.gemm_params(ws[i % 4], qa, out, F.scratch(dev), splits=splits)
             N.check(N.lib().saber_gemm_i8_launch(C.byref(pr), stages, N.stream_handle()), "gemm")
