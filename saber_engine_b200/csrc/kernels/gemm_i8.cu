@@ -909,7 +909,13 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
           // read consecutive 16-byte groups.  All splits of an item are loaded before any is
           // used, two items per round: one memory round trip per round.
           const int n_c4 = ncols >> 2;
-          const int c4_part = n_c4 > part ? (n_c4 - part + nparts - 1) / nparts : 0;
+          // one GPU: a part owns a CONTIGUOUS span of four-column groups, so that its share of every row is one
+          // run of bytes: the rounded outputs are staged in shared memory (8-byte pieces, 16-byte chunks
+          // XOR-swizzled by the row) and leave as whole spans, a warp per row (stored one piece per row and
+          // lane they were 32 partial sectors per instruction: 7.8 us of a 27 us launch)
+          const int c4_lo = (n_c4 * part) / nparts, c4_hi = (n_c4 * (part + 1)) / nparts;
+          const int c4_part = c4_hi - c4_lo;
+          const uint32_t stage_o = widen ? u_smem : w_smem;     // idle by now (the bulk reduction has read it)
           // tensor-parallel: the parts split the ROWS and lanes run over the column groups, so
           // that a warp's pushes to a peer are contiguous bytes of one row
           const int rows_part = mt > part ? (mt - part + nparts - 1) / nparts : 0;
@@ -933,7 +939,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
               } else {
                 const int ci = idx / mt;
                 rr[u] = idx - ci * mt;
-                c4[u] = part + ci * nparts;
+                c4[u] = c4_lo + ci;
               }
 #pragma unroll
               for (int sp = 0; sp < kMaxS; ++sp)
@@ -978,7 +984,28 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
                       *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.tp_recv[peer]) + off) = pk;
                 }
               } else {
-                __nv_bfloat16* o = p.out + static_cast<size_t>(m0 + rr[u]) * p.ldo + n0 + c;
+                const uint32_t sa = stage_o + static_cast<uint32_t>(rr[u]) * 512u +
+                                    (((static_cast<uint32_t>(c4[u]) >> 1) ^ (static_cast<uint32_t>(rr[u]) & 31u)) << 4) + ((static_cast<uint32_t>(c4[u]) & 1u) << 3);
+                asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(sa), "r"(pk.x), "r"(pk.y) : "memory");
+              }
+            }
+          }
+          };
+          // the budget is ~16 loads in flight per thread: more items per round when there are few splits
+          if (bulk) reduce_items(std::integral_constant<int, 8>{}, std::integral_constant<int, 1>{});
+          else if (p.splits <= 2) reduce_items(std::integral_constant<int, 8>{}, std::integral_constant<int, 2>{});
+          else if (p.splits <= 4) reduce_items(std::integral_constant<int, 4>{}, std::integral_constant<int, 4>{});
+          else reduce_items(std::integral_constant<int, 2>{}, std::integral_constant<int, 8>{});
+          if (!tp) {
+            named_bar_sync(1, 128);             // every piece of this part is staged
+            for (int rw = tid_t >> 5; rw < mt; rw += 4) {
+              for (int g = c4_lo + lane; g < c4_hi; g += 32) {
+                const uint32_t sa = stage_o + static_cast<uint32_t>(rw) * 512u +
+                                    (((static_cast<uint32_t>(g) >> 1) ^ (static_cast<uint32_t>(rw) & 31u)) << 4) + ((static_cast<uint32_t>(g) & 1u) << 3);
+                uint2 pk;
+                asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(pk.x), "=r"(pk.y) : "r"(sa));
+                const int c = g << 2;
+                __nv_bfloat16* o = p.out + static_cast<size_t>(m0 + rw) * p.ldo + n0 + c;
                 if (n0 + c + 4 <= p.N) {
                   *reinterpret_cast<uint2*>(o) = pk;
                 } else {
@@ -989,12 +1016,6 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
               }
             }
           }
-          };
-          // the budget is ~16 loads in flight per thread: more items per round when there are few splits
-          if (bulk) reduce_items(std::integral_constant<int, 8>{}, std::integral_constant<int, 1>{});
-          else if (p.splits <= 2) reduce_items(std::integral_constant<int, 8>{}, std::integral_constant<int, 2>{});
-          else if (p.splits <= 4) reduce_items(std::integral_constant<int, 4>{}, std::integral_constant<int, 4>{});
-          else reduce_items(std::integral_constant<int, 2>{}, std::integral_constant<int, 8>{});
           if (!p.coop) {
             if (tid_t == 0) p.counters[tile_id] = 0u;
             if (tp) tp_signal(tile_id);
