@@ -59,7 +59,7 @@ struct OpDigestClear { unsigned long long* out; int n; };
 struct OpSampleSeam { const int32_t* ids; const float* vals; const float* samp; const float* u; int32_t* picks; int rows; };
 struct OpLogitGather { const void* logits; int rows, ld, V, id_offset; const int32_t* ids; float* out; };
 struct OpMoeGather { const int8_t* q; const float* scale; int M_pad; const int32_t* src_row; const int32_t* ntiles;
-                     int8_t* q_out; float* scale_out; int rows_cap, M_pad_out, K; };
+                     int8_t* q_out; float* scale_out; int rows_cap, M_pad_out, K, to_fp8; };
 
 using Op = std::variant<OpGemm, OpRow, OpEmbed, OpGdnConv, OpGdnRec, OpRope, OpAttn, OpArgmax,
                         OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather, OpDigest, OpDigestClear, OpGdnChunk, OpLogitGather, OpSampleSeam, OpGdnStep, OpSeamMerge>;
@@ -120,7 +120,7 @@ int launch(const Op& op, cudaStream_t s) {
         else if constexpr (std::is_same_v<T, OpLogitGather>) return saber_logit_gather_launch(o.logits, o.rows, o.ld, o.V, o.id_offset, o.ids, o.out, s);
         else if constexpr (std::is_same_v<T, OpMoeGather>)
           return saber_moe_gather_launch(o.q, o.scale, o.M_pad, o.src_row, o.ntiles, o.q_out, o.scale_out, o.rows_cap,
-                                         o.M_pad_out, o.K, s);
+                                         o.M_pad_out, o.K, o.to_fp8, s);
         else return static_cast<int>(cudaErrorInvalidValue);
       },
       op);
@@ -246,8 +246,8 @@ int saber_program_add_moe_route(void* h, const saber::MoeRouteParams* p, const c
 }
 int saber_program_add_moe_gather(void* h, const int8_t* q, const float* scale, int M_pad, const int32_t* src_row,
                                  const int32_t* ntiles, int8_t* q_out, float* scale_out, int rows_cap,
-                                 int M_pad_out, int K, const char* tag) {
-  return add(h, OpMoeGather{q, scale, M_pad, src_row, ntiles, q_out, scale_out, rows_cap, M_pad_out, K}, 1, tag);
+                                 int M_pad_out, int K, int to_fp8, const char* tag) {
+  return add(h, OpMoeGather{q, scale, M_pad, src_row, ntiles, q_out, scale_out, rows_cap, M_pad_out, K, to_fp8}, 1, tag);
 }
 int saber_program_add_digest(void* h, const void* buf, size_t bytes, unsigned long long* out, const char* tag) {
   return add(h, OpDigest{buf, bytes, out}, 1, tag);

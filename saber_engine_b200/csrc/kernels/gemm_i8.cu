@@ -1238,8 +1238,8 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
     if (p->tail_mode != 1 && p->tail_mode != 2) return static_cast<int>(cudaErrorInvalidValue);
   }
   // grouped tiles: the lean instantiation, two CTAs per SM, when two ring stages fit its budget
-  if (p->group_tiles && p->w4 == 1 && p->splits == 1) {
-    const int lean_smem = 2 * (16384 + p->nt * 128) + 2 * 32768 + 1024;
+  if (p->group_tiles && widen_l && p->splits == 1) {
+    const int lean_smem = 2 * ((p->w4 == 2 ? 17408 : 16384) + p->nt * 128) + 2 * 32768 + 1024;
     if (lean_smem <= 112 * 1024)
       return static_cast<int>(saber::launch(gemm_i8_lean_kernel, grid, dim3(kGemmThreads), lean_smem, stream, 2, q, 2));
   }

@@ -10,6 +10,7 @@
 #include "moe.h"
 #include "gemm_i8.h"
 #include <math.h>
+#include <cuda_fp8.h>
 
 namespace saber {
 
@@ -139,9 +140,11 @@ __global__ void moe_place_kernel(const MoeRouteParams p) {
 
 // block = K / 16 threads (one 16-byte chunk each); the CTAs stride over the LIVE rows (a device-side
 // count): the grid is static (graph capture) but small, instead of one CTA per row of the worst case.
+// to_fp8: the sorted rows feed MXFP4 experts, whose GEMM multiplies fp8 x fp8: an int8 value q (row scale s)
+// leaves as e4m3(q * 448 / 127) with row scale s * 127 / 448 (round to nearest even, saturating).
 __global__ void moe_gather_kernel(const int8_t* __restrict__ q, const float* __restrict__ scale, int M_pad,
                                   const int32_t* __restrict__ src_row, const int32_t* __restrict__ ntiles,
-                                  int8_t* __restrict__ q_out, float* __restrict__ scale_out, int M_pad_out) {
+                                  int8_t* __restrict__ q_out, float* __restrict__ scale_out, int M_pad_out, int to_fp8) {
   pdl_trigger();
   pdl_wait();
   const int live = ntiles[1];
@@ -151,8 +154,21 @@ __global__ void moe_gather_kernel(const int8_t* __restrict__ q, const float* __r
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (m >= 0)
       v = *reinterpret_cast<const uint4*>(q + (static_cast<size_t>(kb) * M_pad + m) * 128 + ((c ^ (m & 7)) << 4));
+    if (to_fp8) {
+      uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float f0 = static_cast<float>(static_cast<int8_t>(w[i] & 0xFFu)) * (448.f / 127.f);
+        const float f1 = static_cast<float>(static_cast<int8_t>((w[i] >> 8) & 0xFFu)) * (448.f / 127.f);
+        const float f2 = static_cast<float>(static_cast<int8_t>((w[i] >> 16) & 0xFFu)) * (448.f / 127.f);
+        const float f3 = static_cast<float>(static_cast<int8_t>(w[i] >> 24)) * (448.f / 127.f);
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f0, f1), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f2, f3), __NV_SATFINITE, __NV_E4M3);
+        w[i] = lo | (hi << 16);
+      }
+    }
     *reinterpret_cast<uint4*>(q_out + (static_cast<size_t>(kb) * M_pad_out + r) * 128 + ((c ^ (r & 7)) << 4)) = v;
-    if (threadIdx.x == 0) scale_out[r] = m >= 0 ? scale[m] : 0.f;
+    if (threadIdx.x == 0) scale_out[r] = m >= 0 ? scale[m] * (to_fp8 ? 127.f / 448.f : 1.f) : 0.f;
   }
 }
 
@@ -237,9 +253,9 @@ extern "C" int saber_moe_route_launch(const saber::MoeRouteParams* p, cudaStream
 
 extern "C" int saber_moe_gather_launch(const int8_t* q, const float* scale, int M_pad, const int32_t* src_row,
                                        const int32_t* ntiles, int8_t* q_out, float* scale_out, int rows_cap,
-                                       int M_pad_out, int K, cudaStream_t stream) {
+                                       int M_pad_out, int K, int to_fp8, cudaStream_t stream) {
   if ((K & 127) || K / 16 > 1024 || rows_cap > M_pad_out) return static_cast<int>(cudaErrorInvalidValue);
-  saber::launch(saber::moe_gather_kernel, dim3(rows_cap < 1184 ? rows_cap : 1184), dim3(K / 16), 0, stream, 0, q, scale, M_pad, src_row, ntiles, q_out, scale_out, M_pad_out);
+  saber::launch(saber::moe_gather_kernel, dim3(rows_cap < 1184 ? rows_cap : 1184), dim3(K / 16), 0, stream, 0, q, scale, M_pad, src_row, ntiles, q_out, scale_out, M_pad_out, to_fp8);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -46,6 +46,6 @@ struct MoeCombineParams {
 // expert-major order: sorted row r takes token row src_row[r]; padding rows become zeros.
 extern "C" int saber_moe_gather_launch(const int8_t* q, const float* scale, int M_pad, const int32_t* src_row,
                                        const int32_t* ntiles, int8_t* q_out, float* scale_out, int rows_cap,
-                                       int M_pad_out, int K, cudaStream_t stream);
+                                       int M_pad_out, int K, int to_fp8, cudaStream_t stream);
 extern "C" int saber_moe_route_launch(const saber::MoeRouteParams* p, cudaStream_t stream);
 extern "C" int saber_moe_combine_launch(const saber::MoeCombineParams* p, cudaStream_t stream);

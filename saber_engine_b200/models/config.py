@@ -23,6 +23,7 @@ class MoEConfig:
     expert_inter: int = 512
     shared_inter: int = 512
     norm_topk_prob: bool = True
+    expert_format: str = "iu8"         # routed experts: "iu8" (int4 x int8 rows) | "mxfp4" (e2m1 / e8m0 per 32, fp8 rows)
 
 
 @dataclass(frozen=True)
@@ -221,6 +222,8 @@ def by_name(name: str):
              "flashnext-ref": lambda: flashnext_moe(True), "hybrid-mini": scaled_hybrid,
              "qwen38-27b-mxfp4": lambda: dataclasses.replace(qwen38_27b(), name="qwen38-27b-mxfp4", weight_format="mxfp4"),
              "qwen38-27b-nvfp4": lambda: dataclasses.replace(qwen38_27b(), name="qwen38-27b-nvfp4", weight_format="nvfp4"),
+             "flashnext-moe-mxfp4": lambda: dataclasses.replace(flashnext_moe(), name="flashnext-moe-mxfp4",
+                                                                moe=MoEConfig(512, 10, 512, 512, True, "mxfp4")),
              "tiny-qwen3": TinyQwen3Config}
     if name not in table:
         raise KeyError(f"unknown model {name!r}; known: {sorted(table)}")

@@ -45,6 +45,7 @@ class MoeWorkspace:
 
     def __init__(self, cfg, e_n: int, M: int, device, shared_inter: int):
         m = cfg.moe
+        self.mx = getattr(m, "expert_format", "iu8") == "mxfp4"     # the experts' rows are fp8 e4m3
         dev = device
         H, I, K = cfg.hidden, m.expert_inter, m.top_k
         self.M, self.e_n = M, e_n
@@ -61,10 +62,10 @@ class MoeWorkspace:
         self.ntiles = i32(2)
         self.src_row, self.slot_of = i32(m_pad), i32(M, K)
         self.qa_sorted = F.QuantAct(torch.zeros(H // 128, m_pad, 128, dtype=torch.int8, device=dev),
-                                    torch.zeros(m_pad, dtype=torch.float32, device=dev), self.rows_cap, H)
+                                    torch.zeros(m_pad, dtype=torch.float32, device=dev), self.rows_cap, H, fp8=self.mx)
         self.gu = bf(m_pad, 2 * I)
         self.qa_inter = F.QuantAct(torch.zeros(I // 128, m_pad, 128, dtype=torch.int8, device=dev),
-                                   torch.zeros(m_pad, dtype=torch.float32, device=dev), self.rows_cap, I)
+                                   torch.zeros(m_pad, dtype=torch.float32, device=dev), self.rows_cap, I, fp8=self.mx)
         self.y = bf(m_pad, H)
         self.shared_inter = shared_inter
         if shared_inter:
@@ -91,7 +92,7 @@ def grouped_gemm_params(stack, a: F.QuantAct, out: torch.Tensor, ws: MoeWorkspac
     p.w, p.w_scale, p.a, p.a_scale = stack.tiles.data_ptr(), stack.scale.data_ptr(), a.q.data_ptr(), a.scale.data_ptr()
     p.out, p.ws, p.counters, p.err = out.data_ptr(), sc.ws.data_ptr(), sc.counters.data_ptr(), sc.err.data_ptr()
     p.M, p.M_pad, p.N, p.N_pad, p.K = a.M_pad, a.M_pad, stack.N, stack.N_pad, stack.K
-    p.nt, p.splits, p.w4, p.ldo = ws.nt, 1, 1, out.stride(0)
+    p.nt, p.splits, p.w4, p.ldo = ws.nt, 1, (2 if getattr(stack, "mx", False) else 1), out.stride(0)
     p.group_tiles, p.group_ntiles, p.group_w_stride = ws.tiles.data_ptr(), ws.ntiles.data_ptr(), stack.stride_bytes
     return p
 
@@ -131,7 +132,7 @@ def add_moe_ops(prog: N.Program, ws: MoeWorkspace, cfg, moe: dict, qa_h: F.Quant
 
     dense(moe["router"], qa_h, ws.logits, "router")
     prog.add_moe_route(route_params(ws, cfg, moe["e_lo"]), tag=f"{tag}.route")
-    prog.add_moe_gather(qa_h, ws.src_row, ws.ntiles, ws.qa_sorted, ws.rows_cap, tag=f"{tag}.gather")
+    prog.add_moe_gather(qa_h, ws.src_row, ws.ntiles, ws.qa_sorted, ws.rows_cap, tag=f"{tag}.gather", to_fp8=ws.mx)
     prog.gemm(grouped_gemm_params(moe["gate_up"], ws.qa_sorted, ws.gu, ws, sc), 0, tag=f"{tag}.experts.gate_up")
     rp = F.row_params(ws.rows_cap, cfg.moe.expert_inter, a=ws.gu, qa=ws.qa_inter)
     rp.m_live = ws.ntiles.data_ptr() + 4

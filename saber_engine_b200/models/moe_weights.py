@@ -30,6 +30,7 @@ class ExpertStack:
     scale: torch.Tensor      # fp32 [E_local, N_pad] (already / 16)
     N: int
     K: int
+    mx: bool = False         # MXFP4 experts: tiles uint8 [E_local, N_pad/256, K/128, 17408] (codes + block shifts), scale = row scale of the fold
 
     @property
     def n_experts(self) -> int:
@@ -44,7 +45,19 @@ class ExpertStack:
         return self.tiles.stride(0)
 
     def expert(self, e: int) -> QuantWeight:
-        return QuantWeight(self.tiles[e], self.scale[e], self.N, self.K, True)
+        return QuantWeight(self.tiles[e], self.scale[e], self.N, self.K, True, mx=self.mx)
+
+    @staticmethod
+    def from_mxfp4(codes: torch.Tensor, e8m0: torch.Tensor, device=None) -> "ExpertStack":
+        """e2m1 codes uint8 [E, N, K] + e8m0 block scales uint8 [E, N, K/32]: the fold of every output row
+        (block scales as shifts against the row's largest, the row scale in `scale`)."""
+        from ..pack import quant_fp4 as Q
+        E, Nn, K = codes.shape
+        assert Nn % L.TILE_N == 0 and K % 128 == 0, "expert linears must be whole tiles"
+        shift, row_scale = Q.fold_mxfp4(codes.reshape(E * Nn, K), e8m0.reshape(E * Nn, K // 32))
+        tiles = L.tile_weight_mxfp4(codes.reshape(E * Nn, K), shift).reshape(E, Nn // L.TILE_N, K // 128, -1)
+        dev = device if device is not None else codes.device
+        return ExpertStack(tiles.to(dev).contiguous(), row_scale.reshape(E, Nn).float().to(dev).contiguous(), Nn, K, mx=True)
 
     @staticmethod
     def from_int(q: torch.Tensor, s: torch.Tensor, device=None) -> "ExpertStack":
@@ -86,6 +99,15 @@ def random_moe_layer(cfg: HybridConfig, tp: int, rank: int, dev, g: torch.Genera
     router_w = rand(m.n_experts, H) * 4.0          # wider logits: a sharper, more realistic router
     q, s = L.quantize_weight_rows(router_w, 8)
     router = QuantWeight.from_int(q, s, 8, dev)
+    mxe = getattr(m, "expert_format", "iu8") == "mxfp4"
+
+    def quant_e(w):
+        if not mxe:
+            return quantize_experts(w)
+        from ..pack import quant_fp4 as Q
+        E_, N_, K_ = w.shape
+        codes, e = Q.quantize_mxfp4(w.reshape(E_ * N_, K_))
+        return codes.reshape(E_, N_, K_), e.reshape(E_, N_, K_ // 32)
     gu_parts, dn_parts = [], []
     for c0 in range(0, m.n_experts, chunk):
         n = min(chunk, m.n_experts - c0)
@@ -93,11 +115,12 @@ def random_moe_layer(cfg: HybridConfig, tp: int, rank: int, dev, g: torch.Genera
         wdn = rand(n, H, I)
         lo, hi = max(c0, e_lo), min(c0 + n, e_lo + e_n)
         if lo < hi:
-            gu_parts.append(quantize_experts(wgu[lo - c0:hi - c0]))
-            dn_parts.append(quantize_experts(wdn[lo - c0:hi - c0]))
+            gu_parts.append(quant_e(wgu[lo - c0:hi - c0]))
+            dn_parts.append(quant_e(wdn[lo - c0:hi - c0]))
         del wgu, wdn
-    gu = ExpertStack.from_int(torch.cat([p[0] for p in gu_parts]), torch.cat([p[1] for p in gu_parts]), dev)
-    dn = ExpertStack.from_int(torch.cat([p[0] for p in dn_parts]), torch.cat([p[1] for p in dn_parts]), dev)
+    make = ExpertStack.from_mxfp4 if mxe else ExpertStack.from_int
+    gu = make(torch.cat([p[0] for p in gu_parts]), torch.cat([p[1] for p in gu_parts]), dev)
+    dn = make(torch.cat([p[0] for p in dn_parts]), torch.cat([p[1] for p in dn_parts]), dev)
     # shared expert: gate | up | one sigmoid-gate row, then down
     wsg, wsu, wgate = rand(Is, H), rand(Is, H), rand(1, H) * 4.0
     wsd = rand(H, Is)

@@ -127,6 +127,13 @@ def moe_mlp_ref(cfg: HybridConfig, moe: dict, n: torch.Tensor, tp: int = 1) -> t
     for e in ids.unique().tolist():
         tok, kk = (ids == e).nonzero(as_tuple=True)
         x = n[tok]
+        if getattr(moe["gate_up"], "mx", False):
+            # MXFP4 experts: the sorted rows are the layer's int8 rows turned into e4m3 (q * 448 / 127, row scale * 127 / 448)
+            aq, asc = L.quantize_act_rows(x)
+            f8 = (aq.float() * (448.0 / 127.0)).to(torch.float8_e4m3fn).float()
+            gu = ((f8.double() @ _mx_dense(moe["gate_up"].expert(e)).double().t()).float() * (asc * (127.0 / 448.0))[:, None]).to(torch.bfloat16).float()
+            y[tok, kk] = qlinear(R.silu_mul(gu), moe["down"].expert(e))
+            continue
         gu = qlinear(x, moe["gate_up"].expert(e))
         y[tok, kk] = qlinear(R.silu_mul(gu), moe["down"].expert(e))
     # shared expert

@@ -260,8 +260,8 @@ def _declare(L: C.CDLL) -> None:
         "saber_get_pdl": (I, []),
         "saber_moe_route_launch": (I, [C.POINTER(MoeRouteParams), S]),
         "saber_moe_combine_launch": (I, [C.POINTER(MoeCombineParams), S]),
-        "saber_moe_gather_launch": (I, [P, P, I, P, P, P, P, I, I, I, S]),
-        "saber_program_add_moe_gather": (I, [P, P, P, I, P, P, P, P, I, I, I, C.c_char_p]),
+        "saber_moe_gather_launch": (I, [P, P, I, P, P, P, P, I, I, I, I, S]),
+        "saber_program_add_moe_gather": (I, [P, P, P, I, P, P, P, P, I, I, I, I, C.c_char_p]),
         "saber_program_add_moe_route": (I, [P, C.POINTER(MoeRouteParams), C.c_char_p]),
         "saber_program_add_moe_combine": (I, [P, C.POINTER(MoeCombineParams), C.c_char_p]),
         "saber_vis_rows_launch": (I, [C.POINTER(VisRowsParams), S]),
@@ -410,11 +410,12 @@ class Program:
     def add_moe_route(self, p: "MoeRouteParams", tag: str = "moe_route") -> int:
         return self._L.saber_program_add_moe_route(self._h, C.byref(p), tag.encode())
 
-    def add_moe_gather(self, src, src_row, ntiles, dst, rows_cap: int, tag: str = "moe_gather") -> int:
-        """src / dst: objects with .q (tiled int8), .scale, .M_pad, .K (QuantAct)."""
+    def add_moe_gather(self, src, src_row, ntiles, dst, rows_cap: int, tag: str = "moe_gather", to_fp8: bool = False) -> int:
+        """src / dst: objects with .q (tiled int8), .scale, .M_pad, .K (QuantAct); to_fp8: the sorted rows
+        leave as e4m3 (MXFP4 experts multiply fp8 x fp8)."""
         return self._L.saber_program_add_moe_gather(self._h, ptr(src.q), ptr(src.scale), src.M_pad, ptr(src_row),
                                                     ptr(ntiles), ptr(dst.q), ptr(dst.scale), rows_cap, dst.M_pad,
-                                                    src.K, tag.encode())
+                                                    src.K, int(to_fp8), tag.encode())
 
     def add_moe_combine(self, p: "MoeCombineParams", tag: str = "moe_combine") -> int:
         return self._L.saber_program_add_moe_combine(self._h, C.byref(p), tag.encode())

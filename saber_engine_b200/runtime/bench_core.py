@@ -244,15 +244,19 @@ def run_benchmark(args, ClockSampler):
     lay = db.layout
     names = {"qwen38-27b": ("decode_tok_s_8streams_27b_w4a8", 642.0, 230.0, 5200.0),
              "flashnext-moe": ("decode_tok_s_8streams_flashnext_moe_w4a8", 420.2, 166.9, None),
+             "flashnext-moe-mxfp4": ("decode_tok_s_8streams_flashnext_moe_mxfp4_experts", 420.2, 166.9, None),
              "flashnext-ref": ("decode_tok_s_8streams_flashnext_moe_w4a8", 420.2, 166.9, None)}
+    dtype = {"iu8": "w4a8-int8 (bf16 activations)", "mxfp4": "mxfp4 weights x fp8 activations (bf16 residual stream)",
+             "nvfp4": "nvfp4 weights x nvfp4 activations, block-scaled tensor-core MMA (bf16 residual stream)"}.get(
+                 getattr(cfg, "weight_format", "iu8"), "w4a8-int8 (bf16 activations)")
+    if cfg.moe is not None and getattr(cfg.moe, "expert_format", "iu8") == "mxfp4":
+        dtype = "routed experts mxfp4 x fp8 rows; " + dtype + " elsewhere"
     metric, base8, base1, base_pre = names.get(cfg.name, (f"decode_tok_s_{streams}streams_{cfg.name}", None, None, None))
     return {
         "metric": metric, "value": value, "unit": "tok/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": (value / base8) if base8 and streams == 8 else None, "dtype": {"iu8": "w4a8-int8 (bf16 activations)", "mxfp4": "mxfp4 weights x fp8 activations (bf16 residual stream)",
-                  "nvfp4": "nvfp4 weights x nvfp4 activations, block-scaled tensor-core MMA (bf16 residual stream)"}.get(
-                      getattr(cfg, "weight_format", "iu8"), "w4a8-int8 (bf16 activations)"), "data": "synthetic",
+        "vs_baseline": (value / base8) if base8 and streams == 8 else None, "dtype": dtype, "data": "synthetic",
         "impl": "ours",
         "config": {"model": cfg.name, "global_batch": streams, "seq_len": args.prompt,
                    "parallelism": f"tp{world}", "verify_width": W, "accept_p": args.accept_p,

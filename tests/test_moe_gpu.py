@@ -69,11 +69,14 @@ def test_route_placement(M):
     assert int(ws.counts.abs().sum()) == 0
 
 
-@pytest.mark.parametrize("M", [5, 72, 200])
-def test_moe_block_matches_oracle(M):
+@pytest.mark.parametrize("M,fmt", [(5, "iu8"), (72, "iu8"), (200, "iu8"), (5, "mxfp4"), (200, "mxfp4")])
+def test_moe_block_matches_oracle(M, fmt):
+    """fmt = mxfp4: the routed experts are MXFP4 (e2m1 / e8m0 per 32) and their rows fp8 e4m3, made from the
+    layer's int8 rows by the gather; router and shared expert stay integer."""
+    import dataclasses
     from saber_engine_b200.models.moe_block import MoeWorkspace, add_moe_ops
     from saber_engine_b200.models.reference_hybrid import moe_mlp_ref
-    cfg = _cfg()
+    cfg = _cfg() if fmt == "iu8" else C.scaled_hybrid(name="hybrid-mini-moe-mx", moe=dataclasses.replace(MOE, expert_format="mxfp4"))
     moe = _moe_layer(cfg)
     H = cfg.hidden
     g = torch.Generator().manual_seed(100 + M)
@@ -86,10 +89,12 @@ def test_moe_block_matches_oracle(M):
     prog.run()
     torch.cuda.synchronize()
     F.scratch("cuda").check()
+    assert moe["gate_up"].mx == (fmt == "mxfp4")
     ref = moe_mlp_ref(cfg, moe, x.float())
     got = out.float().cpu()
     err = (got - ref).abs().max()
-    assert err <= 0.02 * ref.abs().max() + 1e-4, (float(err), float(ref.abs().max()))
+    # (fp8 rows: a silu output that sits on a rounding edge moves one e4m3 step, 6 %, in one of the 128 terms)
+    assert err <= (0.02 if fmt == "iu8" else 0.04) * ref.abs().max() + 1e-4, (float(err), float(ref.abs().max()))
     # graph replay gives the same bytes as the eager walk
     st = torch.cuda.Stream()
     st.wait_stream(torch.cuda.current_stream())
