@@ -1246,7 +1246,7 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
   // long row runs of 4-bit weights: two token tiles per CTA (pairs must be whole inside M_pad)
   q.mtiles = 1;
   if (p->mtiles >= 0 && !p->group_tiles && p->splits == 1 && (widen_l || p->w4 == 3) && p->nt == 128 && p->M > 128 &&
-      (p->M_pad / 128) % 2 == 0 && p->ag_flags == nullptr && p->tail_mode == 0 && halves == 1 &&
+      (p->M_pad / 128) % 2 == 0 && p->tail_mode == 0 && halves == 1 &&
       (p->mtiles == 2 || static_cast<int>(grid.x * grid.y) > sm_count)) {
     // (only when one tile per CTA needs more than one wave of CTAs: a grid that is resident as a whole
     // gains nothing from pairing tiles, its CTAs would just run twice as long)

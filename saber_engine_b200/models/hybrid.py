@@ -104,6 +104,7 @@ class Bucket:
     last_h2d_bytes: int = 0                        # index-table bytes the last step copied to the device
     arenas: list = field(default_factory=list)     # pure activation buffers: written before read in every step
     digests: Optional[torch.Tensor] = None         # int64 [n_layers + 1] stage digests (race_check = "shadow")
+    sp: bool = False                               # prefill on several ranks: the sequence-parallel chain (rows owned by ranks)
     seam_dev: Optional[torch.Tensor] = None        # int32 blob: ids [Mh*64] | values [Mh*64] fp32 bits | lse [Mh*2] (seam buckets)
     seam_host: Optional[torch.Tensor] = None       # pinned mirror
     plp_dev: Optional[torch.Tensor] = None         # int32 blob of a prompt-log-probability bucket (every row: candidates, lse, next-token logit)
@@ -116,7 +117,7 @@ class HybridModel:
                  max_width: int = 8, weights: Optional[ModelWeights] = None, seed: int = 0,
                  comm=None, oracle_p: float = 0.0, oracle_seed: int = 0, gdn_vs: int = 2,
                  use_drafter: bool = True, race_check: str = "off", gdn_prefill: str = "rows", gdn_fused: Optional[bool] = None,
-                 image_rows: int = 0, fuse: bool = True, attn_impl: str = "tc"):
+                 image_rows: int = 0, fuse: bool = True, attn_impl: str = "tc", sp_prefill: Optional[bool] = None):
         self.cfg, self.tp, self.rank = cfg, tp, rank
         if race_check not in ("off", "shadow"):
             raise ValueError("race_check must be 'off' or 'shadow'")
@@ -151,6 +152,14 @@ class HybridModel:
             raise ValueError("attn_impl must be 'tc' or 'mma'")
         self.attn_impl = attn_impl
         self._held = None
+        # sequence-parallel prefill on several ranks: a row-parallel GEMM sends a row's partial sums to the
+        # row's owner only (reduce-scatter), the owner adds, normalises and quantises it and stores the
+        # quantised row into every rank's buffer (all-gather), and the next GEMM waits per 128-row tile.
+        # Parity: the reference's fused GEMM + all-reduce + add-norm-quant (`crates/saber-kernels/hip/macaq_iu8f.hip:1-12`)
+        # is the two-rank, all-reduce form of this chain.
+        from ..rules import default_rules
+        self.sp_prefill = (tp >= default_rules().doc["prefill"]["sequence_parallel_min_ranks"]) if sp_prefill is None else bool(sp_prefill)
+        self._sp, self._sp_rpr, self._ag_site, self._qa_ag, self._qa_src_ptr = False, 0, -1, None, 0
         if self.fuse and cfg.moe is None:
             for lw in self.w.layers:
                 if lw.gate_up is not None:
@@ -237,6 +246,7 @@ class HybridModel:
         consumes this GEMM's output becomes its row tail (`_add_rms`), anything else adds it as it is."""
         self._flush(prog)
         a = self._fmt(a, w)
+        a, ag_site = self._ag_input(a)
         nt = L.token_tile(a.M)
         hit = self._tuned(w, a)
         if hit is not None and tp_site < 0 and not hold:
@@ -245,9 +255,16 @@ class HybridModel:
             halves = 2 if (self.fuse and tp_site < 0 and not hold and
                            F.pick_halves(w, w.N_pad // L.TILE_N, (a.M + nt - 1) // nt)) else 1
         splits = 1 if halves == 2 else self.pick_splits(w, a)
+        if self._sp and tp_site >= 0:
+            splits, halves = 1, 1           # one arrival per feature tile at the row's owner
         p = F.gemm_params(w, a, out, self.scratch, splits=splits, halves=halves)
+        if ag_site >= 0:
+            self.comm.gemm_ag(p, ag_site)
         if tp_site >= 0 and self.tp > 1:
-            self.comm.gemm_tp(p, tp_site)
+            if self._sp:
+                self.comm.gemm_rs(p, tp_site, self._sp_rpr)
+            else:
+                self.comm.gemm_tp(p, tp_site)
             self._site_parts[tp_site] = N.lib().saber_gemm_i8_parts(C.byref(p))
         # (a row-parallel GEMM on several ranks keeps its consumer as a launch of its own: as a row tail the
         # consumer's cross-rank waits sit inside the GEMM's grid, measured 9.63 against 8.63 ms per step at 8 ranks)
@@ -263,8 +280,11 @@ class HybridModel:
         weight is paired and the grid stays resident, else GEMM + row kernel."""
         self._flush(prog)
         a = self._fmt(a, w)
+        a, ag_site = self._ag_input(a)
         splits = self.pick_splits(w, a)
         p = F.gemm_params(w, a, gu, self.scratch, splits=splits)
+        if ag_site >= 0:
+            self.comm.gemm_ag(p, ag_site)
         qi = self._fmt(qa_i, w_down)
         if self.fuse and w.paired and splits == 1 and not qi.fp8 and not qi.fp4 and qi.had_sign is None and F.gemm_tail_ok(p) \
                 and qi.M_pad % p.nt == 0 and qi.M_pad <= 256:
@@ -282,13 +302,23 @@ class HybridModel:
         GEMM that produced `delta` is being held (`_gemm(hold=True)`) and its grid stays resident, the
         op becomes that GEMM's row tail instead of a launch of its own."""
         cfg = self.cfg
+        sp = self._sp and tp_site >= 0 and self.tp > 1
+        if sp and qa is not None:
+            # the quantised rows of the owned rows go to every rank's copy of the all-gather buffer
+            g = self._qa_ag
+            qa = F.QuantAct(g.q, g.scale, M, cfg.hidden, fp8=qa.fp8, had_sign=qa.had_sign)
         p = F.row_params(M, cfg.hidden, a=delta, res=res, w=w, w_offset=cfg.norm_offset, eps=cfg.eps, qa=qa, out=out)
         if res_copy is not None:
             p.res_copy = res_copy.data_ptr()
         if tp_site >= 0 and self.tp > 1:
             nt = self._site_nt.get(tp_site, L.token_tile(M))
             # a producer that signals per split-K part shows up as that many flags per feature tile
-            self.comm.row_tp(p, tp_site, nt, L.round_up(cfg.hidden, L.TILE_N) // L.TILE_N * self._site_parts.get(tp_site, 1))
+            tiles = L.round_up(cfg.hidden, L.TILE_N) // L.TILE_N * self._site_parts.get(tp_site, 1)
+            if sp:
+                self.comm.row_sp(p, tp_site, nt, tiles, self._sp_rpr)
+                self._ag_site = tp_site if qa is not None else -1
+            else:
+                self.comm.row_tp(p, tp_site, nt, tiles)
         if self._held is not None:
             gp, stages, gtag = self._held
             if cfg.hidden <= 2 * 16 * 320 and (qa is None or qa.had_sign is None) and F.gemm_tail_ok(gp):
@@ -298,6 +328,14 @@ class HybridModel:
                 return
             self._flush(prog)
         prog.row(N.ROW_ADD_RMS, p, tag=tag)
+
+    def _ag_input(self, a: F.QuantAct):
+        """Sequence-parallel prefill: the rows the last add-norm quantised live in the all-gather buffer
+        (every rank's owners stored theirs); a GEMM that reads them waits for their arrival flags."""
+        if self._sp and self._ag_site >= 0 and a.q.data_ptr() == self._qa_src_ptr:
+            g = self._qa_ag
+            return F.QuantAct(g.q, g.scale, a.M, a.K, fp8=a.fp8, had_sign=a.had_sign), self._ag_site
+        return a, -1
 
     def _tuned(self, w: F.QuantWeight, a: F.QuantAct):
         """The measured variant of this (linear, rows) route from the plan's tune table, or None."""
@@ -369,6 +407,13 @@ class HybridModel:
 
         h, delta = bf(M, H), bf(M, H)
         qa_h = self._qa(M, H)
+        self._sp = bool(not decode and self.tp > 1 and self.sp_prefill and cfg.moe is None and not plp
+                        and M % (128 * self.tp) == 0 and M <= min(self.comm.layout.rows_max, 64 * 128)
+                        and getattr(cfg, "weight_format", "iu8") == "iu8"
+                        and getattr(self.w.layers[0].mixer_in, "had_sign", None) is None)
+        self._sp_rpr, self._ag_site, self._qa_src_ptr = M // self.tp, -1, qa_h.q.data_ptr()
+        self._qa_ag = self.comm.heap_qact(M, H) if self._sp else None
+        sp_used = self._sp
         ld_in = (max(sh.qkv_n, sh.gdn_in_n) + 7) // 8 * 8
         buf_in = bf(M, ld_in)
         conv_out, gdn_o = f32(M, sh.gdn_conv_c), f32(M, sh.gdn_out_k)
@@ -501,6 +546,7 @@ class HybridModel:
         b = self._finish_bucket(prog, kind, nseq, width, M, lay, blob, blob_host, keep, capture)
         b.arenas = [a for a in arenas if a is not None]
         b.digests = digests
+        b.sp = sp_used
         return b
 
     def _allreduce(self, prog: N.Program, buf: torch.Tensor, n_elems: int, site: int, tag: str) -> int:
@@ -536,7 +582,14 @@ class HybridModel:
             last = torch.zeros(nseq, H, dtype=torch.bfloat16, device=dev)
             self._add_rms(prog, M, "final_norm", self.w.final_norm, h, None, delta, pending, out=normed)
             self._flush(prog)
-            prog.embed(normed, at(lay.last_rows), last, nseq, H, 0, M, H, tag="gather_last_rows")
+            if self._sp:
+                # a row's owner holds its normed values: every rank gathers the last rows it owns (zeros for the
+                # others) and the sum over ranks puts every last row on every rank
+                r0 = self.rank * self._sp_rpr
+                prog.embed(normed[r0:], at(lay.last_rows), last, nseq, H, r0, self._sp_rpr, H, tag="gather_last_rows")
+                ar_site = self._allreduce(prog, last, nseq * H, ar_site, "last_rows.allgather")
+            else:
+                prog.embed(normed, at(lay.last_rows), last, nseq, H, 0, M, H, tag="gather_last_rows")
             qa_head = self._qa(nseq, H)
             prog.row(N.ROW_PLAIN, F.row_params(nseq, H, a=last, qa=self._fmt(qa_head, self.w.lm_head)), tag="head_quant")
             keep += [normed, last, qa_head]
@@ -593,11 +646,12 @@ class HybridModel:
         keep += [out, accept_row, bonus, pick_val, logits]
         self._last_head = dict(out=out, logits=logits, W=W, block=block, Mh=Mh, seam=seam_dev, plp=plp_dev)
         if self.use_drafter:
-            self._build_drafter(prog, nseq, M, tap_buf, taps, acc_ptr, bonus_ptr, o_drafts, keep)
+            ar_site = self._build_drafter(prog, nseq, M, tap_buf, taps, acc_ptr, bonus_ptr, o_drafts, keep, ar_site)
+        self._sp = False
         if self.tp > 1:
             prog.advance(self.comm.seq_base, ar_site, tag="comm_advance")
 
-    def _build_drafter(self, prog, nseq, M, tap_buf, taps, acc_ptr, bonus_ptr, o_drafts, keep) -> None:
+    def _build_drafter(self, prog, nseq, M, tap_buf, taps, acc_ptr, bonus_ptr, o_drafts, keep, ar_site: int = 0) -> int:
         """Block drafter: taps of the last committed row -> aux projection -> + token and position
         embeddings -> MLP layers over the block rows -> head -> `block` draft tokens per sequence."""
         cfg, dc, dw, dev = self.cfg, self.cfg.drafter, self.w.drafter, self.device
@@ -606,7 +660,13 @@ class HybridModel:
         nt = len(taps)
         cat = torch.zeros(nseq, dc.n_taps * H, dtype=torch.bfloat16, device=dev)
         for j in range(nt):
-            prog.embed(tap_buf[j], acc_ptr, cat[:, j * H:], nseq, H, 0, M, dc.n_taps * H, tag=f"draft.tap{j}")
+            if self._sp:      # tap rows live on their owners: owned rows or zeros, summed over the ranks below
+                r0 = self.rank * self._sp_rpr
+                prog.embed(tap_buf[j][r0:], acc_ptr, cat[:, j * H:], nseq, H, r0, self._sp_rpr, dc.n_taps * H, tag=f"draft.tap{j}")
+            else:
+                prog.embed(tap_buf[j], acc_ptr, cat[:, j * H:], nseq, H, 0, M, dc.n_taps * H, tag=f"draft.tap{j}")
+        if self._sp and nt:
+            ar_site = self._allreduce(prog, cat, nseq * dc.n_taps * H, ar_site, "draft.taps.allgather")
         qa_cat = self._qa(nseq, dc.n_taps * H)
         prog.row(N.ROW_PLAIN, F.row_params(nseq, dc.n_taps * H, a=cat, qa=self._fmt(qa_cat, dw.aux_fc)), tag="draft.tap_quant")
         ctx = torch.zeros(nseq, Hd, dtype=torch.bfloat16, device=dev)
@@ -629,6 +689,7 @@ class HybridModel:
         self._gemm(prog, dw.head, qa_x, dlogits, "draft.head")
         prog.argmax(dlogits, R, dlogits.stride(0), cfg.vocab, 0, o_drafts, None, tag="draft.argmax")
         keep += [cat, qa_cat, ctx, tok, x, dd, qa_x, qa_di, gu, dlogits]
+        return ar_site
 
     def _finish_bucket(self, prog, kind, nseq, width, M, lay, blob, blob_host, keep, capture) -> Bucket:
         self._flush(prog)

@@ -46,6 +46,28 @@ def generate(model, prompt, n_new: int, width: int, slot: int = 1):
     return out[:n_new], first_logits, steps
 
 
+def sp_prefill_check(model, cfg, world: int) -> dict:
+    """A prompt of 128 rows per rank through the sequence-parallel prefill chain (reduce-scatter epilogue,
+    add-norm on the owned rows, all-gather into the next GEMM) and through the push-to-all-ranks chain:
+    same rows, same arithmetic, so tokens, drafts and logits have to be the same bytes."""
+    M = 128 * world
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, cfg.vocab, (M,), generator=g).tolist()
+    blocks = list(range(1, 2 + (M + 15) // 16))
+    outs, used = [], []
+    for sp in (True, False):
+        model.sp_prefill = sp
+        model.buckets.pop(("prefill", 1, M), None)
+        model.reset_slot(1)
+        pb = model.build_bucket("prefill", 1, M)
+        used.append(bool(pb.sp))
+        res = run_bucket(model, pb, [SeqStep(prompt, 0, 1, 0, blocks)])
+        outs.append((list(res.tokens[0]), list(res.drafts[0]), pb.logits[0].float().cpu().clone()))
+    model.sp_prefill = True
+    return {"sp_used": used, "sp_equals_push_all": outs[0][0] == outs[1][0] and outs[0][1] == outs[1][1]
+            and bool(torch.equal(outs[0][2], outs[1][2]))}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=24)
@@ -60,8 +82,9 @@ def main(argv=None) -> int:
     moe = C.MoEConfig(n_experts=32, top_k=4, expert_inter=128, shared_inter=256) if args.moe else None
     cfg = C.scaled_hybrid(q_heads=8, kv_heads=2, k_heads=8, v_heads=8, ffn=1024 * max(1, world // 2), hidden=512,
                           moe=moe)
-    comm = SymmetricComm(rank, world, dev, max_elems=128 * cfg.hidden, rows_max=128, hidden=cfg.hidden)
-    model = HybridModel(cfg, tp=world, rank=rank, device=dev, max_seqs=2, max_ctx=512, max_width=args.width,
+    rows_max = 128 * world
+    comm = SymmetricComm(rank, world, dev, max_elems=rows_max * cfg.hidden, rows_max=rows_max, hidden=cfg.hidden)
+    model = HybridModel(cfg, tp=world, rank=rank, device=dev, max_seqs=2, max_ctx=max(512, rows_max + 64), max_width=args.width,
                         seed=5, comm=comm)
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab, (args.prompt,), generator=g).tolist()
@@ -72,6 +95,14 @@ def main(argv=None) -> int:
     dist.all_gather_object(gathered, toks)
     ok = all(t == gathered[0] for t in gathered)
     report = {"world": world, "ranks_agree": ok, "steps": steps}
+    if not args.moe:
+        spc = sp_prefill_check(model, cfg, world)
+        model.scratch.check()
+        comm.check()
+        sp_all = [None] * world
+        dist.all_gather_object(sp_all, spc)
+        report["sp_prefill"] = spc
+        ok = ok and all(c["sp_equals_push_all"] and c["sp_used"] == [True, False] for c in sp_all)
     if rank == 0:
         ref_model = HybridModel(cfg, tp=1, rank=0, device=dev, max_seqs=2, max_ctx=512, max_width=args.width, seed=5)
         ref, ref_logits, _ = generate(ref_model, prompt, args.tokens, args.width)

@@ -16,7 +16,8 @@ from pathlib import Path
 from typing import Optional
 
 SCHEMA = {
-    "": {"schema_version", "name", "device", "gemm", "attn_tc", "attn_paged", "gdn"},
+    "": {"schema_version", "name", "device", "gemm", "prefill", "attn_tc", "attn_paged", "gdn"},
+    "prefill": {"sequence_parallel_min_ranks"},
     "device": {"sms", "smem_per_cta", "tmem_columns"},
     "gemm": {"symbol", "tile_n", "tile_k", "threads", "token_tiles", "splits", "halves", "stages", "tails"},
     "gemm.tails": {"row_tail_max_ranks"},
