@@ -34,6 +34,8 @@ struct GdnRecParams {
   float* out;               // [M][HV * 128]
   int C, n_q, n_k, HV, HK, ldba, stash_rows, commit;
   int prefill_rows;         // commit mode only: 1 = use the eight-threads-per-row kernel (every shift must be 0)
+  int chunk_impl;           // chunked prefill: 0 = fp32 on the CUDA cores, 1 = tensor cores (tf32 prep, tcgen05 scan)
+  uint32_t* err;            // status word for waits that ran out (tensor-core scan); may be null
 };
 
 // One launch per layer and decode step: conv + recurrence + gated RMSNorm + per-token quantisation.
@@ -70,6 +72,9 @@ extern "C" int saber_gdn_conv_launch(const saber::GdnConvParams* p, int nseq, cu
 extern "C" size_t saber_gdn_chunk_scratch_bytes(int max_rows, int nseq, int HV);
 extern "C" int saber_gdn_chunk_launch(const saber::GdnRecParams* p, int nseq, int max_rows, float* scratch,
                                       cudaStream_t stream);
+extern "C" size_t saber_gdn_chunk_tc_scratch_bytes(int max_rows, int nseq, int HV);
+extern "C" int saber_gdn_chunk_tc_launch(const saber::GdnRecParams* p, int nseq, int max_rows, float* scratch,
+                                         cudaStream_t stream);
 extern "C" int saber_gdn_step_launch(const saber::GdnStepParams* p, int nseq, cudaStream_t stream);
 extern "C" int saber_gdn_recurrent_launch(const saber::GdnRecParams* p, int nseq, int vs,
                                           cudaStream_t stream);

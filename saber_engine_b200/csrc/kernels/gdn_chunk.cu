@@ -245,7 +245,10 @@ __global__ void __launch_bounds__(256) gdn_chunk_scan_kernel(const GdnRecParams 
 }  // namespace saber
 
 extern "C" size_t saber_gdn_chunk_scratch_bytes(int max_rows, int nseq, int HV) {
-  return (static_cast<size_t>(max_rows / saber::kChunk + nseq + 1)) * HV * saber::kChunkScratchFloats * sizeof(float);
+  // (one scratch serves either form: the tensor-core form's operand images are the larger)
+  const size_t a = (static_cast<size_t>(max_rows / saber::kChunk + nseq + 1)) * HV * saber::kChunkScratchFloats * sizeof(float);
+  const size_t b = saber_gdn_chunk_tc_scratch_bytes(max_rows, nseq, HV);
+  return a > b ? a : b;
 }
 
 // Committing (prefill) recurrence over all rows of every sequence.  `max_rows` bounds the rows of one
@@ -253,6 +256,7 @@ extern "C" size_t saber_gdn_chunk_scratch_bytes(int max_rows, int nseq, int HV) 
 extern "C" int saber_gdn_chunk_launch(const saber::GdnRecParams* p, int nseq, int max_rows, float* scratch,
                                       cudaStream_t stream) {
   using namespace saber;
+  if (p->chunk_impl == 1) return saber_gdn_chunk_tc_launch(p, nseq, max_rows, scratch, stream);
   if (p->HV % p->HK || !p->commit || scratch == nullptr || max_rows <= 0) return static_cast<int>(cudaErrorInvalidValue);
   const int prep_smem = (2 * kChunk * kKPad + kChunk * kChunk) * sizeof(float);
   const int scan_smem = (3 * 64 * 128 + 2 * 64 * 33 + 64 * 64) * sizeof(float);

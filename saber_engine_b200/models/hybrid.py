@@ -121,7 +121,7 @@ class HybridModel:
         self.cfg, self.tp, self.rank = cfg, tp, rank
         if race_check not in ("off", "shadow"):
             raise ValueError("race_check must be 'off' or 'shadow'")
-        self.gdn_prefill = gdn_prefill      # "rows" (row-by-row recurrence) | "chunked" (64-row chunks, fp32)
+        self.gdn_prefill = gdn_prefill      # "rows" (row-by-row recurrence) | "chunked" (64-row chunks, fp32) | "tc" (chunks on the tensor cores)
         self.race_check = race_check        # "shadow": a digest of the residual stream after every layer rides with the result
         self.sh = shard(cfg, tp, rank)
         self.device = torch.device(device)
@@ -481,9 +481,10 @@ class HybridModel:
                     rp = F.gdn_rec_params(conv_out, ba, lw.A_log, lw.dt_bias, self.gdn_state[i],
                                           self.gdn_stash[i], blob, blob, blob, gdn_o, n_q, n_k,
                                           sh.gdn_v_heads, sh.gdn_k_heads, commit=not decode, ldba=ld_in,
-                                          prefill_rows=(not decode and width >= 32))
+                                          prefill_rows=(not decode and width >= 32),
+                                          chunk_impl=int(self.gdn_prefill == "tc"))
                     rp.cu_rows, rp.slots, rp.shift = at(lay.cu_rows), at(lay.slots), at(lay.shift)
-                    if not decode and width >= 64 and self.gdn_prefill == "chunked":
+                    if not decode and width >= 64 and self.gdn_prefill in ("chunked", "tc"):
                         # prefill: the chunked (64-row) form; one scratch shared by every layer of the bucket
                         if chunk_scratch is None:
                             chunk_scratch = F.gdn_chunk_scratch(M, nseq, sh.gdn_v_heads, dev)

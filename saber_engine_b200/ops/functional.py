@@ -431,7 +431,7 @@ def gdn_conv(x, conv_w, hist, cu_rows, slots, shift, n_q, n_k, commit=False, dua
 
 
 def gdn_rec_params(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, out, n_q, n_k,
-                   HV, HK, commit, ldba=None, prefill_rows: bool = False):
+                   HV, HK, commit, ldba=None, prefill_rows: bool = False, chunk_impl: int = 0):
     p = N.GdnRecParams()
     p.qkv, p.ba, p.A_log, p.dt_bias = qkv.data_ptr(), ba.data_ptr(), A_log.data_ptr(), dt_bias.data_ptr()
     p.state, p.stash = state.data_ptr(), stash.data_ptr()
@@ -440,6 +440,8 @@ def gdn_rec_params(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift,
     p.ldba = ldba if ldba is not None else ba.stride(0)
     p.stash_rows, p.commit = stash.shape[1], int(commit)
     p.prefill_rows = int(prefill_rows) if commit else 0      # 1: two state rows per thread (default), 2: one, 3: four
+    p.chunk_impl = int(chunk_impl)                           # chunked prefill: 1 = tensor cores
+    p.err = scratch(qkv.device).err.data_ptr() if qkv.is_cuda else 0
     return p
 
 
@@ -506,11 +508,14 @@ def gdn_chunk_scratch(total_rows: int, nseq: int, HV: int, device) -> torch.Tens
     return torch.empty(n // 4, dtype=torch.float32, device=device)
 
 
-def gdn_chunked(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, n_q, n_k, HV, HK, max_rows: int):
-    """Committing (prefill) recurrence by 64-row chunks; same contract as gdn_recurrent(commit=True)."""
+def gdn_chunked(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, n_q, n_k, HV, HK, max_rows: int,
+                impl: int = 0):
+    """Committing (prefill) recurrence by 64-row chunks; same contract as gdn_recurrent(commit=True).
+    impl = 1: pair products on tf32 tiles, the chunk scan on tcgen05 with the state in tensor memory."""
     M = qkv.shape[0]
     out = torch.empty(M, HV * 128, dtype=torch.float32, device=qkv.device)
-    p = gdn_rec_params(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, out, n_q, n_k, HV, HK, True)
+    p = gdn_rec_params(qkv, ba, A_log, dt_bias, state, stash, cu_rows, slots, shift, out, n_q, n_k, HV, HK, True,
+                       chunk_impl=impl)
     scratch_t = gdn_chunk_scratch(M, slots.numel(), HV, qkv.device)
     N.check(N.lib().saber_gdn_chunk_launch(C.byref(p), slots.numel(), max_rows, scratch_t.data_ptr(), N.stream_handle()),
             "gdn_chunk")

@@ -79,7 +79,8 @@ class GdnStepParams(C.Structure):
 class GdnRecParams(C.Structure):
     _fields_ = [("qkv", P), ("ba", P), ("A_log", P), ("dt_bias", P), ("state", P), ("stash", P),
                 ("cu_rows", P), ("slots", P), ("shift", P), ("out", P), ("C", I), ("n_q", I),
-                ("n_k", I), ("HV", I), ("HK", I), ("ldba", I), ("stash_rows", I), ("commit", I), ("prefill_rows", I)]
+                ("n_k", I), ("HV", I), ("HK", I), ("ldba", I), ("stash_rows", I), ("commit", I), ("prefill_rows", I),
+                ("chunk_impl", I), ("err", P)]
 
 
 class RopeKvParams(C.Structure):

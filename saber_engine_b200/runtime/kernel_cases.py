@@ -165,8 +165,9 @@ def _gdn_step(nseq, n, shift, copies=3):
     return states, stashes, hists, x, qa, scr, conv_out, o
 
 
-def _gdn_prefill(n, copies=3, form=1):
-    """One sequence of n rows through the committing row-by-row form the prefill rungs use."""
+def _gdn_prefill(n, copies=3, form=1, chunk_impl=-1):
+    """One sequence of n rows through the committing row-by-row form the prefill rungs use
+    (chunk_impl >= 0: the 64-row chunked form instead, 0 = fp32, 1 = tensor cores)."""
     HV, HK, d = 48, 16, 128
     C_ = 2 * HK * d + HV * d
     qkv = torch.randn(n, C_, device=DEV) * 0.1
@@ -179,9 +180,15 @@ def _gdn_prefill(n, copies=3, form=1):
     sh = torch.zeros(1, dtype=torch.int32, device=DEV)
     out = torch.empty(n, HV * d, device=DEV)
     ps = [F.gdn_rec_params(qkv, ba, A_log, dtb, st, stash, cu, slots, sh, out, HK * d, HK * d, HV, HK, True,
-                           prefill_rows=form) for st in states]
+                           prefill_rows=form, chunk_impl=max(chunk_impl, 0)) for st in states]
     torch.cuda.synchronize()
     lib = N.lib()
+    if chunk_impl >= 0:
+        scr = F.gdn_chunk_scratch(n, 1, HV, DEV)
+        fns = [lambda p=p: N.check(lib.saber_gdn_chunk_launch(C.byref(p), 1, n, scr.data_ptr(), N.stream_handle()), "gdn") for p in ps]
+        _time(fns, f"gdn prefill chunked n={n} impl={chunk_impl}", n * (2 * HK * d + HV * d) * 4.0 + n * HV * d * 4.0)
+        F.scratch(DEV).check()
+        return states, out, scr
     fns = [lambda p=p: N.check(lib.saber_gdn_recurrent_launch(C.byref(p), 1, 2, N.stream_handle()), "gdn") for p in ps]
     _time(fns, f"gdn prefill rows n={n} form={form}", n * (2 * HK * d + HV * d) * 4.0 + n * HV * d * 4.0)
     return states, out
@@ -265,6 +272,8 @@ CASES = {
     "gdn_step_b1_w8": lambda: _gdn_step(1, 8, 4),
     "gdn_prefill_2048": lambda: _gdn_prefill(2048),
     "gdn_prefill_2048_one_row": lambda: _gdn_prefill(2048, form=2),
+    "gdn_prefill_2048_chunk_tc": lambda: _gdn_prefill(2048, chunk_impl=1),
+    "gdn_prefill_512_chunk_tc": lambda: _gdn_prefill(512, chunk_impl=1),
     "gdn_prefill_512": lambda: _gdn_prefill(512),
     "gdn_prefill_512_one_row": lambda: _gdn_prefill(512, form=2),
     "row_add_rms_m72": lambda: _row(72, 5120),

@@ -423,6 +423,19 @@ def test_gdn_chunked_prefill_equals_row_by_row_kernel():
     assert (got - want).abs().max().item() <= 2e-4 * scale + 1e-5, ((got - want).abs().max().item(), scale)
     assert (st_a[1:] - st_b[1:]).abs().max().item() <= 2e-4 * st_a.abs().max().item() + 1e-5
     assert torch.equal(st_a[0], st_b[0])            # the padding slot is untouched
+    # the tensor-core form (tf32 pair products, tcgen05 scan with the state in tensor memory): bf16 operands,
+    # fp32 accumulation -- the state copy that feeds a chunk's products is rounded once per chunk
+    st_d = s["state"].to(DEV).clone()
+    got_tc = F.gdn_chunked(qkv, ba, A_log, dtb, st_d, stash, cu, slots, sh, n_q, n_k, HV, HK, max_rows=max(lens), impl=1)
+    torch.cuda.synchronize()
+    F.scratch(DEV).check()
+    err_o = (got_tc - want).abs().max().item()
+    err_s = (st_a[1:] - st_d[1:]).abs().max().item()
+    assert err_o <= 1.5e-2 * scale + 1e-4, (err_o, scale)
+    assert err_s <= 1.5e-2 * st_a.abs().max().item() + 1e-4, (err_s, st_a.abs().max().item())
+    assert torch.equal(st_a[0], st_d[0])
+    rms = (got_tc - want).pow(2).mean().sqrt().item() / want.pow(2).mean().sqrt().item()
+    assert rms <= 5e-3, rms
 
 
 def test_attention_packs_several_heads_into_one_tile():
