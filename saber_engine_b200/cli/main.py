@@ -151,6 +151,7 @@ def build_engine(a):
             model = HybridModel(cfg, tp=a.engine_tp, rank=rank, device=dev, max_seqs=man.max_seqs, comm=comm,
                                 max_ctx=man.max_ctx, kv_blocks=kv_blocks, max_width=max(widths),
                                 weights=weights, seed=a.seed, race_check=a.engine_race_check,
+                                gdn_prefill=getattr(a, "engine_gdn_prefill", "tc"),
                                 image_rows=(getattr(a, "vision_arena_patches", 0) // 4 if getattr(a, "vision", False) else 0))
             if man.autotune:
                 from ..plan.autotune import TuneTable
@@ -424,6 +425,9 @@ def make_parser() -> argparse.ArgumentParser:
     e.add_argument("--vision-arena-patches", type=int, default=16384, help="patch rows the tower arena holds (larger images are downscaled)")
     e.add_argument("--engine-host-trace", action="store_true", help="named host phases per step (an attribution, not a published time)")
     e.add_argument("--engine-race-check", default="off", choices=["off", "shadow"])
+    e.add_argument("--engine-gdn-prefill", default="tc", choices=["tc", "rows", "chunked"],
+                   help="DeltaNet prefill: 64-row chunks on the tensor cores (default), the exact fp32 row-by-row "
+                        "recurrence, or the fp32 chunked form")
     e.add_argument("--poison-boot", type=lambda v: int(v, 0), default=None, metavar="BYTE",
                    help="fill every activation arena with this byte when a bucket is built (write-before-read proof)")
     e.add_argument("--warm-prompt", action="append", default=[], metavar="FILE",

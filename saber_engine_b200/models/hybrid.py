@@ -116,7 +116,7 @@ class HybridModel:
                  max_seqs: int = 8, max_ctx: Optional[int] = None, kv_blocks: Optional[int] = None,
                  max_width: int = 8, weights: Optional[ModelWeights] = None, seed: int = 0,
                  comm=None, oracle_p: float = 0.0, oracle_seed: int = 0, gdn_vs: int = 2,
-                 use_drafter: bool = True, race_check: str = "off", gdn_prefill: str = "rows", gdn_fused: Optional[bool] = None,
+                 use_drafter: bool = True, race_check: str = "off", gdn_prefill: str = "tc", gdn_fused: Optional[bool] = None,
                  image_rows: int = 0, fuse: bool = True, attn_impl: str = "tc", sp_prefill: Optional[bool] = None):
         self.cfg, self.tp, self.rank = cfg, tp, rank
         if race_check not in ("off", "shadow"):

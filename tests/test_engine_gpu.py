@@ -25,7 +25,12 @@ def _collect(sub):
 @pytest.fixture(scope="module")
 def executor():
     cfg = C.scaled_hybrid()
-    model = HybridModel(cfg, device="cuda", max_seqs=4, max_ctx=2048, max_width=5, seed=1)
+    # gdn_prefill="rows": the laws below compare token ids of the same prompt prefilled in different pieces
+    # (cold, resumed from a cached prefix, restored from a park).  The row-by-row recurrence is the same fp32
+    # arithmetic however the rows are cut; the tensor-core chunked default rounds the state copy that feeds a
+    # chunk's products to bf16, so a cut inside a 64-row chunk moves the last bits (cuts at chunk boundaries do
+    # not: tests/test_kernels_gpu.py), and a random-init model turns last bits into other tokens.
+    model = HybridModel(cfg, device="cuda", max_seqs=4, max_ctx=2048, max_width=5, seed=1, gdn_prefill="rows")
     return HybridExecutor(model, decode_batches=(1, 2, 4), decode_widths=(1, 5), prefill_rungs=(64, 256))
 
 

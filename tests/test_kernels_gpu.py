@@ -438,6 +438,42 @@ def test_gdn_chunked_prefill_equals_row_by_row_kernel():
     assert rms <= 5e-3, rms
 
 
+def test_gdn_tensor_core_prefill_split_at_a_chunk_boundary_gives_the_same_bytes():
+    """The tensor-core chunked form carries the state in tensor memory between chunks and in fp32 memory
+    between launches: 256 rows in one launch and as 128 + 128 rows are the same arithmetic, bit for bit
+    (what the prefix cache relies on when it resumes at a multiple of 64 rows), and so is a second run."""
+    HV, HK = 6, 2
+    s = _gdn_setup(2, 4, HV=HV, HK=HK, seed=19)
+    n_q, n_k = s["n_q"], s["n_k"]
+    M = 256
+    torch.manual_seed(20)
+    qk = torch.nn.functional.normalize(torch.randn(M, 2 * HK, 128), dim=-1).reshape(M, n_q + n_k)
+    qk[:, :n_q] /= 128 ** 0.5
+    qkv = torch.cat([qk, torch.randn(M, HV * 128)], 1).to(DEV)
+    ba = torch.randn(M, 2 * HV).to(torch.bfloat16).to(DEV)
+    slots = torch.tensor([1], dtype=torch.int32, device=DEV)
+    sh = torch.zeros(1, dtype=torch.int32, device=DEV)
+    A_log, dtb = s["A_log"].to(DEV), s["dt_bias"].to(DEV)
+    stash = torch.zeros(3, 4, HV, 2, F.gdn_stash_stride(2), device=DEV)
+
+    def run(pieces):
+        st = s["state"].to(DEV).clone()
+        outs = []
+        for lo, hi in pieces:
+            cu = torch.tensor([0, hi - lo], dtype=torch.int32, device=DEV)
+            outs.append(F.gdn_chunked(qkv[lo:hi].contiguous(), ba[lo:hi].contiguous(), A_log, dtb, st, stash, cu, slots, sh,
+                                      n_q, n_k, HV, HK, max_rows=hi - lo, impl=1))
+        torch.cuda.synchronize()
+        return torch.cat(outs), st
+
+    o1, s1 = run([(0, 256)])
+    o2, s2 = run([(0, 256)])
+    o3, s3 = run([(0, 128), (128, 256)])
+    F.scratch(DEV).check()
+    assert torch.equal(o1, o2) and torch.equal(s1, s2)
+    assert torch.equal(o1, o3) and torch.equal(s1, s3)
+
+
 def test_attention_packs_several_heads_into_one_tile():
     """Few rows per sequence: 2 heads per 16-row tile at 8 rows, 3 at 5, all 6 at 1 or 2 rows."""
     _attn_case([200, 31], [8, 8], splits=2, nq=24, nkv=4, seed=5)
