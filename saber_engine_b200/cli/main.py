@@ -174,8 +174,10 @@ def build_engine(a):
                 dist.destroy_process_group()
                 raise SystemExit(0)
             ex = TpLeaderExecutor(ex, a._tp_group, channel=getattr(a, "_ctrl_channel", None))
-    if a.engine_tp > 1 and (getattr(a, "prompt_cache_dir", None) or getattr(a, "park_dir", None)):
-        raise SystemExit("saber: --prompt-cache-dir / --park-dir move one rank's shard only: not available with --engine-tp > 1")
+    if a.engine_tp > 1 and getattr(a, "prompt_cache_dir", None):
+        # (parked sessions work on several ranks: every rank keeps its shard under the leader's park id, in the
+        # memory of the running process group; a prompt cache on a drive would outlive that group)
+        raise SystemExit("saber: --prompt-cache-dir holds one rank's shard only: not available with --engine-tp > 1")
     from ..sched.width import WidthByBatch
     wt = WidthByBatch.parse(a.engine_width_table, captured=tuple(_ints(a.engine_decode_widths))) if getattr(a, "engine_width_table", "") else None
     cfg_s = SchedulerConfig(max_seqs=a.engine_max_seqs, max_ctx=a.engine_max_ctx, prefix_cache=not a.no_prefix_cache,

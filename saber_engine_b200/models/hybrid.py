@@ -382,8 +382,8 @@ class HybridModel:
         # row and the logit of the token that follows it in the prompt (prompt log-probabilities)
         key = (kind, nseq, width, "seam") if seam else (kind, nseq, width)
         if plp:
-            if kind != "prefill" or self.tp > 1:
-                raise ValueError("prompt log-probabilities: prefill buckets on one GPU only")
+            if kind != "prefill":
+                raise ValueError("prompt log-probabilities: prefill buckets only")
             key = key + ("plp",)
         self._bucket_key, self._want_seam, self._want_plp = key, seam, plp
         if key in self.buckets:
@@ -629,8 +629,20 @@ class HybridModel:
             prog.seam(logits_all, M, logits_all.stride(0), sh.vocab, sh.vocab_first, None, plp_dev[:M * K],
                       plp_dev[M * K: 2 * M * K].view(torch.float32), plp_dev[2 * M * K: 2 * M * K + 2 * M].view(torch.float32),
                       tag="plp.topk_seam")
-            prog.logit_gather(logits_all, M, logits_all.stride(0), sh.vocab, sh.vocab_first, at(lay.next_ids),
-                              plp_dev[2 * M * K + 2 * M:].view(torch.float32), tag="plp.logit_gather")
+            nxt = plp_dev[2 * M * K + 2 * M:].view(torch.float32)
+            prog.logit_gather(logits_all, M, logits_all.stride(0), sh.vocab, sh.vocab_first, at(lay.next_ids), nxt,
+                              tag="plp.logit_gather")
+            if self.tp > 1:
+                # vocabulary shards: the candidates of every row are merged across the ranks on the device, and the
+                # successor's logit (minus infinity on the ranks that do not hold its column) by the pick merge
+                prog.seam_merge(self.comm.seam_merge_params(plp_dev[:M * K], plp_dev[M * K: 2 * M * K].view(torch.float32),
+                                                            plp_dev[2 * M * K: 2 * M * K + 2 * M].view(torch.float32), M, ar_site),
+                                tag="plp.seam_merge")
+                ar_site += 1
+                nxt_ids = torch.zeros(M, dtype=torch.int32, device=dev)
+                prog.pick_merge(self.comm.pick_merge_params(nxt_ids, nxt, M, ar_site), tag="plp.next_logit_merge")
+                ar_site += 1
+                keep.append(nxt_ids)
             keep += [qa_all, logits_all, plp_dev]
             self._plp_logits = logits_all
         if decode:

@@ -22,7 +22,8 @@ from typing import Optional
 from ..sched.executor import SeqRun
 
 MAGIC = 0x53424346                    # "SBCF"
-OPS = {"prefill": 1, "decode": 2, "reset_slot": 3, "snapshot_state": 4, "restore_state": 5, "free_snapshot": 6, "stop": 7}
+OPS = {"prefill": 1, "decode": 2, "reset_slot": 3, "snapshot_state": 4, "restore_state": 5, "free_snapshot": 6, "stop": 7,
+       "export_session": 8, "import_session": 9}
 OP_NAMES = {v: k for k, v in OPS.items()}
 HEADER = struct.Struct("<IHHHHQIII")  # magic, op, part, parts, reserved, call number, nseq, width, payload bytes (whole call)
 SEQ = struct.Struct("<qqqiiiiiiiifiiiiffff")

@@ -68,6 +68,32 @@ def sp_prefill_check(model, cfg, world: int) -> dict:
             and bool(torch.equal(outs[0][2], outs[1][2]))}
 
 
+def prompt_logprob_check(model, ref_model, cfg, world: int) -> dict:
+    """Prompt log-probabilities on vocabulary shards: every row's candidates and the successor's logit are
+    merged across the ranks on the device, so every rank reads the same numbers; rank 0 compares them with the
+    unsharded model (same weights, tensor-parallel rounding apart)."""
+    from ..runtime.hybrid_executor import HybridExecutor
+    from ..sched.executor import SeqRun
+    g = torch.Generator().manual_seed(21)
+    prompt = torch.randint(0, cfg.vocab, (50,), generator=g).tolist()
+    blocks = list(range(1, 6))
+
+    def run(m):
+        ex = HybridExecutor(m, decode_batches=(1,), decode_widths=(1,), prefill_rungs=(64,))
+        m.reset_slot(1)
+        out = ex.prefill([SeqRun(1, prompt, 0, 1, 0, blocks, uid=1, step_no=0, last_chunk=True, prompt_lp=3, next_token=-1)])
+        return out[0].prompt_lps
+
+    got = run(model)
+    res = {"rows": len(got), "ids_ok": [x["token_id"] for x in got] == prompt[1:]}
+    if ref_model is not None:
+        want = run(ref_model)
+        res["max_abs_diff_vs_tp1"] = max(abs(a["logprob"] - b["logprob"]) for a, b in zip(got, want))
+        res["top1_agree"] = sum(a["top"][0][0] == b["top"][0][0] for a, b in zip(got, want)) / len(got)
+    res["digest"] = [round(x["logprob"], 4) for x in got[:8]]
+    return res
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=24)
@@ -103,8 +129,20 @@ def main(argv=None) -> int:
         dist.all_gather_object(sp_all, spc)
         report["sp_prefill"] = spc
         ok = ok and all(c["sp_equals_push_all"] and c["sp_used"] == [True, False] for c in sp_all)
+    ref_model = None
     if rank == 0:
         ref_model = HybridModel(cfg, tp=1, rank=0, device=dev, max_seqs=2, max_ctx=512, max_width=args.width, seed=5)
+    if not args.moe:
+        plc = prompt_logprob_check(model, ref_model, cfg, world)
+        model.scratch.check()
+        comm.check()
+        pl_all = [None] * world
+        dist.all_gather_object(pl_all, plc["digest"])
+        report["prompt_logprobs"] = plc
+        ok = ok and plc["ids_ok"] and plc["rows"] == 49 and all(d == pl_all[0] for d in pl_all)
+        if rank == 0:
+            ok = ok and plc["max_abs_diff_vs_tp1"] < 0.25 and plc["top1_agree"] > 0.8
+    if rank == 0:
         ref, ref_logits, _ = generate(ref_model, prompt, args.tokens, args.width)
         same = sum(a == b for a, b in zip(ref, toks))
         # the sharded head holds vocab / world columns: compare against the matching slice.  The

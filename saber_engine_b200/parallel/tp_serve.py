@@ -22,6 +22,7 @@ import itertools
 from typing import Optional
 
 FORWARDED = ("prefill", "decode", "reset_slot")
+FOLLOWER_PARKS = 64          # parked images a follower keeps (host memory, newest first out last)
 
 
 def init_control_group(timeout_s: float = 1800.0):
@@ -40,6 +41,11 @@ class TpLeaderExecutor:
         as deltas); without one every call is pickled through the gloo group."""
         self.inner, self.group, self.src, self.channel = inner, group, src, channel
         self._snap_ids = itertools.count(1)
+        import collections
+        import os
+        self.epoch = int.from_bytes(os.urandom(6), "little")
+        self.world = int(getattr(getattr(inner, "model", None), "tp", 0)) or 0
+        self._parks_made = collections.deque(maxlen=FOLLOWER_PARKS)
         self.calls_cast = 0
         self.bytes_cast = 0
         if channel is not None:
@@ -89,13 +95,35 @@ class TpLeaderExecutor:
     def snapshot_bytes(self) -> int:
         return self.inner.snapshot_bytes()
 
-    # session parking moves one rank's shard only: refused on several GPUs
-    supports_parking = False
+    # session parking: every rank exports its own shard (its KV heads, its DeltaNet heads) under the leader's
+    # park id.  The leader's image travels through the park tiers as on one GPU; a follower keeps its shard
+    # in host memory (the newest `FOLLOWER_PARKS` images), so an image can only come back into the process
+    # group that made it: the header carries the group's epoch and an image of another epoch is refused
+    # before any rank is asked to import.
+    supports_parking = True
 
-    def export_session(self, *a, **k):
-        raise NotImplementedError("session parking is not available on several GPUs")
+    def export_session(self, slot: int, blocks: list, n_tokens: int):
+        pid = next(self._snap_ids)
+        self._parks_made.append(pid)
+        self._cast("export_session", slot, n_tokens, pid, *blocks)
+        header, payload = self.inner.export_session(slot, blocks, n_tokens)
+        header["tp_park"] = {"id": pid, "epoch": self.epoch, "ranks": self.world}
+        return header, payload
 
-    import_session = export_session
+    def import_session(self, slot: int, blocks: list, header: dict, payload: bytes) -> None:
+        from ..sched.park import ParkError
+        tag = header.get("tp_park")
+        if not tag or tag.get("epoch") != self.epoch:
+            raise ParkError("this image was parked by another process group: the follower ranks do not hold their shards of it")
+        if tag["id"] < self._park_floor():
+            raise ParkError("the follower ranks have dropped their shards of this image")
+        self._cast("import_session", slot, tag["id"], *blocks)
+        self.inner.import_session(slot, blocks, header, payload)
+
+    def _park_floor(self) -> int:
+        """Oldest park id the followers still hold (they keep the newest FOLLOWER_PARKS images; ids are shared
+        with the snapshot counter, so this bound is conservative)."""
+        return self._parks_made[0] if len(self._parks_made) == FOLLOWER_PARKS else 0
 
     def stop_followers(self) -> None:
         self._cast("stop")
@@ -106,6 +134,7 @@ def follower_loop(executor, group, src: int = 0, on_call=None, channel=None, ali
     of calls served.  With a channel the calls arrive as fixed-layout frames; `alive()` is asked while
     the line is idle, and a follower whose leader is gone leaves with ConnectionError."""
     snaps: dict = {}
+    parks: dict = {}
     served = 0
     dec = None
     if channel is not None:
@@ -138,6 +167,15 @@ def follower_loop(executor, group, src: int = 0, on_call=None, channel=None, ali
             s = snaps.pop(args[0], None)
             if s is not None:
                 executor.free_snapshot(s)
+        elif name == "export_session":
+            slot, n_tokens, pid = int(args[0]), int(args[1]), int(args[2])
+            parks[pid] = executor.export_session(slot, [int(b) for b in args[3:]], n_tokens)
+            while len(parks) > FOLLOWER_PARKS:
+                parks.pop(next(iter(parks)))
+        elif name == "import_session":
+            slot, pid = int(args[0]), int(args[1])
+            header, payload = parks[pid]
+            executor.import_session(slot, [int(b) for b in args[2:]], header, payload)
         else:
             raise RuntimeError(f"unknown call from the leader: {name!r}")
         served += 1

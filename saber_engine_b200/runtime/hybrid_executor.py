@@ -70,7 +70,7 @@ class HybridExecutor:
         self.capture = capture
         self.census = {"graph_replays": 0, "eager_walks": 0, "launches": 0, "buckets_built": 0}
         # the head over every prompt row needs the whole vocabulary on one GPU
-        self.supports_prompt_logprobs = model.tp == 1
+        self.supports_prompt_logprobs = True      # on vocabulary shards the rows' candidates and successor logits are merged on the device
         if prebuild:
             for b in self.decode_batches:
                 for w in self.decode_widths:

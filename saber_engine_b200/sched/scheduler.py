@@ -232,9 +232,13 @@ class Scheduler:
                 s.cached_tokens = start
             elif stored is not None:
                 self.ex.reset_slot(s.slot)
-                self.ex.import_session(s.slot, s.blocks, stored.header, stored.payload)
-                start = stored.header["n_tokens"]
-                s.cached_tokens = start
+                from .park import ParkError
+                try:
+                    self.ex.import_session(s.slot, s.blocks, stored.header, stored.payload)
+                    start = stored.header["n_tokens"]
+                    s.cached_tokens = start
+                except ParkError:            # e.g. an image other ranks no longer hold their shards of: a cold prefill
+                    pass
             else:
                 self.ex.reset_slot(s.slot)
             s.pos = start
@@ -279,7 +283,10 @@ class Scheduler:
         v = max(cands, key=lambda x: x.req.params.max_tokens - len(x.output))
         try:
             key = self._park_locked(v)
-        except Exception:
+        except Exception as exc:           # the victim stays where it is; the waiting request keeps waiting
+            import sys
+            print(f"saber: parking a victim failed: {type(exc).__name__}: {exc}", file=sys.stderr, flush=True)
+            self.counters["victim_park_failures"] = self.counters.get("victim_park_failures", 0) + 1
             return False
         self.auto_parked.append(key)
         self.counters["victims_parked"] += 1
@@ -661,7 +668,8 @@ class Scheduler:
         def loop():
             while True:
                 with self._lock:
-                    while not self._stop and not self.fatal and not self.waiting and not self.running:
+                    # (a victim the scheduler parked is work too: it comes back as soon as nobody waits)
+                    while not self._stop and not self.fatal and not self.waiting and not self.running and not self.auto_parked:
                         self._wake.wait(timeout=0.5)
                     if self._stop or self.fatal:
                         return

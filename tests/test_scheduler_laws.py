@@ -177,6 +177,29 @@ def test_victim_parking_admits_a_waiting_request_and_restores_the_victim():
     assert tb == reference_generation(_prompt(100, 11), 200, 1024)
 
 
+def test_the_step_loop_brings_a_parked_victim_back_when_everything_else_is_done():
+    """Served mode: once the request that displaced the victim has finished nothing runs and nothing waits,
+    but the parked victim is still work -- the loop must not go to sleep on it."""
+    class Slow(NullExecutor):
+        def decode(self, runs, width):
+            time.sleep(0.002)                              # the second request arrives while the first still decodes
+            return super().decode(runs, width)
+
+    ex = Slow(seed=9, n_kv_blocks=40)
+    sched = Scheduler(ex, SchedulerConfig(max_seqs=4, max_ctx=4096, park_victims=True, prefix_cache=False))
+    sched.spawn_step_loop()
+    a = sched.submit(EngineRequest(_prompt(100, 10), SamplingParams(max_tokens=300)))
+    while not sched.counters["decode_steps"]:
+        time.sleep(0.001)
+    b = sched.submit(EngineRequest(_prompt(100, 11), SamplingParams(max_tokens=200)))
+    tb, _ = _collect(b)
+    ta, _ = _collect(a)                                     # would time out with the victim left in the park tier
+    assert ta == reference_generation(_prompt(100, 10), 300, 1024)
+    assert tb == reference_generation(_prompt(100, 11), 200, 1024)
+    assert sched.counters["victims_restored"] == sched.counters["victims_parked"] >= 1
+    sched.shutdown()
+
+
 def test_memory_valve_demotes_parks_and_refuses():
     avail = {"v": 64 << 30}
     valve = MemValve(reader=lambda: avail["v"])

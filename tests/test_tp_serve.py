@@ -24,6 +24,31 @@ if rank == 0:
     s.run_until_idle()
     late = s.submit(EngineRequest(shared + [1, 2, 3], SamplingParams(max_tokens=5)))     # a prefix-cache hit: restore on both ranks
     s.run_until_idle()
+    # park a decoding sequence and bring it back: every rank exports and imports its own shard
+    from saber_engine_b200.sched.mock import reference_generation
+    pp = list(range(300, 340))
+    psub = s.submit(EngineRequest(pp, SamplingParams(max_tokens=20)))
+    for _ in range(4):
+        s.step()
+    key = s.park(psub.seq_id)
+    other = s.submit(EngineRequest(list(range(50, 90)), SamplingParams(max_tokens=6)))    # the slot is used meanwhile
+    s.run_until_idle()
+    s.restore(key)
+    s.run_until_idle()
+    pt = []
+    while True:
+        ev = psub.events.get(timeout=10)
+        pt += ev.new_token_ids
+        if ev.finished:
+            break
+    park_ok = pt == reference_generation(pp, 20, 500)
+    # an image of another process group is refused before any rank is asked to import it
+    from saber_engine_b200.sched.park import ParkError
+    try:
+        lead.import_session(1, [1, 2], {"tp_park": {"id": 1, "epoch": lead.epoch + 1}}, b"")
+        foreign = "imported"
+    except ParkError:
+        foreign = "refused"
     toks = []
     for sub in subs + [late]:
         t = []
@@ -34,8 +59,8 @@ if rank == 0:
                 break
         toks.append(t)
     lead.stop_followers()
-    print(json.dumps({"rank": 0, "log": ex.launch_log, "tokens": toks, "cast": lead.calls_cast,
-                      "hits": s.prefix.stats.hits, "state": sorted((k, v[1]) for k, v in ex._state.items())}))
+    print(json.dumps({"rank": 0, "log": ex.launch_log, "tokens": toks, "cast": lead.calls_cast, "park_ok": park_ok,
+                      "foreign": foreign, "hits": s.prefix.stats.hits, "state": sorted((k, v[1]) for k, v in ex._state.items())}))
 else:
     n = follower_loop(ex, group)
     print(json.dumps({"rank": 1, "log": ex.launch_log, "served": n,
@@ -66,6 +91,7 @@ def test_follower_rank_runs_the_leaders_calls(tmp_path):
     assert fol["served"] == lead["cast"] - 1                           # every call but the stop
     assert lead["state"] == fol["state"]                               # slots hold the same committed lengths
     assert lead["hits"] >= 1 and all(len(t) > 0 for t in lead["tokens"])
+    assert lead["park_ok"] and lead["foreign"] == "refused"            # parked and restored on both ranks, same ids as unparked
 
 
 _CHILD_SHM = r'''
