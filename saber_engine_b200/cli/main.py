@@ -152,6 +152,7 @@ def build_engine(a):
                                 max_ctx=man.max_ctx, kv_blocks=kv_blocks, max_width=max(widths),
                                 weights=weights, seed=a.seed, race_check=a.engine_race_check,
                                 gdn_prefill=getattr(a, "engine_gdn_prefill", "tc"),
+                                prefill_w8=bool(getattr(man, "prefill_w8", True)),
                                 image_rows=(getattr(a, "vision_arena_patches", 0) // 4 if getattr(a, "vision", False) else 0))
             if man.autotune:
                 from ..plan.autotune import TuneTable

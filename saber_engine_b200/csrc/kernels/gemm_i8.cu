@@ -1243,15 +1243,16 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
     if (lean_smem <= 112 * 1024)
       return static_cast<int>(saber::launch(gemm_i8_lean_kernel, grid, dim3(kGemmThreads), lean_smem, stream, 2, q, 2));
   }
-  // long row runs of 4-bit weights: two token tiles per CTA (pairs must be whole inside M_pad)
+  // long row runs: two token tiles per CTA (pairs must be whole inside M_pad).  4-bit weights are widened once
+  // for both tiles; int8 and bf16 weights pass through unwidened and are read from shared memory once for both.
   q.mtiles = 1;
-  if (p->mtiles >= 0 && !p->group_tiles && p->splits == 1 && (widen_l || p->w4 == 3) && p->nt == 128 && p->M > 128 &&
+  if (p->mtiles >= 0 && !p->group_tiles && p->splits == 1 && p->nt == 128 && p->M > 128 &&
       (p->M_pad / 128) % 2 == 0 && p->tail_mode == 0 && halves == 1 &&
       (p->mtiles == 2 || static_cast<int>(grid.x * grid.y) > sm_count)) {
     // (only when one tile per CTA needs more than one wave of CTAs: a grid that is resident as a whole
     // gains nothing from pairing tiles, its CTAs would just run twice as long)
     // (bf16 weights pass through unwidened: no operand buffers, the 32 KiB stage feeds the MMA directly)
-    const int wb = p->w4 == 2 ? 17408 : (p->w4 == 3 ? 32768 : 16384);
+    const int wb = p->w4 == 2 ? 17408 : (p->w4 == 1 ? 16384 : 32768);
     const int ubytes = widen_l ? 2 * 32768 : 0;
     int st2 = 3;
     while (st2 > 2 && st2 * (wb + 2 * 16384) + ubytes + 1024 > kSmemLimit) --st2;

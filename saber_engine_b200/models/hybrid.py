@@ -117,7 +117,8 @@ class HybridModel:
                  max_width: int = 8, weights: Optional[ModelWeights] = None, seed: int = 0,
                  comm=None, oracle_p: float = 0.0, oracle_seed: int = 0, gdn_vs: int = 2,
                  use_drafter: bool = True, race_check: str = "off", gdn_prefill: str = "tc", gdn_fused: Optional[bool] = None,
-                 image_rows: int = 0, fuse: bool = True, attn_impl: str = "tc", sp_prefill: Optional[bool] = None):
+                 image_rows: int = 0, fuse: bool = True, attn_impl: str = "tc", sp_prefill: Optional[bool] = None,
+                 prefill_w8: Optional[bool] = None):
         self.cfg, self.tp, self.rank = cfg, tp, rank
         if race_check not in ("off", "shadow"):
             raise ValueError("race_check must be 'off' or 'shadow'")
@@ -160,6 +161,14 @@ class HybridModel:
         from ..rules import default_rules
         self.sp_prefill = (tp >= default_rules().doc["prefill"]["sequence_parallel_min_ranks"]) if sp_prefill is None else bool(sp_prefill)
         self._sp, self._sp_rpr, self._ag_site, self._qa_ag, self._qa_src_ptr = False, 0, -1, None, 0
+        # Prefill rungs of 256 rows and more multiply with an int8 twin of every 4-bit linear (the tile image
+        # the decode kernel widens to, made once): at that many rows a GEMM is bound by the tensor pipe and by
+        # shared-memory bandwidth, not by the weight stream, and the widening pass takes a third of the latter.
+        # Same integers, same scales, so the outputs are the same bytes; the price is memory (twice the 4-bit
+        # weights again), which is what a 180 GB part has.  None: on while free memory covers it.
+        self.prefill_w8 = prefill_w8
+        self._big_prefill = False
+        self.twin_bytes = 0
         if self.fuse and cfg.moe is None:
             for lw in self.w.layers:
                 if lw.gate_up is not None:
@@ -214,7 +223,7 @@ class HybridModel:
         gdn = sum(t.numel() * 4 for t in self.gdn_state.values()) + \
             sum(t.numel() * 2 for t in self.gdn_hist.values()) + \
             sum(t.numel() * 4 for t in self.gdn_stash.values())
-        return {"weights": self.w.nbytes(), "kv_pool": kv, "gdn": gdn}
+        return {"weights": self.w.nbytes(), "weights_prefill_int8_twin": self.twin_bytes, "kv_pool": kv, "gdn": gdn}
 
     # ------------------------------------------------------------------------------ helpers
     def _qa(self, M: int, K: int) -> F.QuantAct:
@@ -245,9 +254,26 @@ class HybridModel:
         hold: the launch is kept back until the next op is known -- an add + RMSNorm + quantise that
         consumes this GEMM's output becomes its row tail (`_add_rms`), anything else adds it as it is."""
         self._flush(prog)
+        w = self._twin8(w, a.M)
         a = self._fmt(a, w)
         a, ag_site = self._ag_input(a)
         nt = L.token_tile(a.M)
+        # A feature-tile count just over a multiple of the SMs (the vocabulary heads: 594 tiles = 4 x 148 + 2)
+        # costs a whole extra round of CTAs for a handful of tiles: those tiles run as a GEMM of their own,
+        # split along K over the SMs, while the rest fills whole rounds.
+        from ..rules import default_rules
+        sms = int(default_rules().doc["device"]["sms"])
+        n_tiles = w.N_pad // L.TILE_N
+        rem = n_tiles % sms
+        if (self.fuse and tp_site < 0 and not hold and ag_site < 0 and not w.fp4 and not w.paired and a.M <= 128
+                and n_tiles > sms and 0 < rem <= sms // 16 and out.stride(0) % 8 == 0):
+            cut = n_tiles - rem
+            head = F.QuantWeight(w.tiles[:cut], w.scale[:cut * L.TILE_N], cut * L.TILE_N, w.K, w.w4, mx=w.mx, had_sign=w.had_sign)
+            tail = F.QuantWeight(w.tiles[cut:], w.scale[cut * L.TILE_N:], w.N - cut * L.TILE_N, w.K, w.w4, mx=w.mx, had_sign=w.had_sign)
+            prog.gemm(F.gemm_params(head, a, out, self.scratch, splits=1), 0, tag=f"{tag}.whole_rounds")
+            ksplit = F.pick_splits(rem, 1, w.K // 128)
+            prog.gemm(F.gemm_params(tail, a, out[:, cut * L.TILE_N:], self.scratch, splits=ksplit), 0, tag=f"{tag}.last_tiles")
+            return
         hit = self._tuned(w, a)
         if hit is not None and tp_site < 0 and not hold:
             halves = int(hit.get("halves", 1))
@@ -279,6 +305,7 @@ class HybridModel:
         """gate | up linear, silu(gate) * up, per-token quantisation into `qa_i`: one launch when the
         weight is paired and the grid stays resident, else GEMM + row kernel."""
         self._flush(prog)
+        w = self._twin8(w, a.M)
         a = self._fmt(a, w)
         a, ag_site = self._ag_input(a)
         splits = self.pick_splits(w, a)
@@ -328,6 +355,28 @@ class HybridModel:
                 return
             self._flush(prog)
         prog.row(N.ROW_ADD_RMS, p, tag=tag)
+
+    def _twin8(self, w: F.QuantWeight, rows: int) -> F.QuantWeight:
+        """The int8 twin of a packed 4-bit weight for the big prefill rungs (or the weight itself)."""
+        if not self._big_prefill or rows < 256 or self.prefill_w8 is False or not w.w4 or w.mx or w.fp4:
+            return w
+        tw = getattr(w, "_twin8", None)
+        if tw is None:
+            need = w.tiles.numel() * 2
+            if self.prefill_w8 is None:
+                free, _ = torch.cuda.mem_get_info(self.device)
+                if free < need + (12 << 30):          # keep room for the buckets' buffers and the graphs
+                    self.prefill_w8 = False
+                    return w
+            t = w.tiles
+            img = torch.empty(*t.shape[:-1], 2 * t.shape[-1], dtype=torch.uint8, device=t.device)
+            half = t.shape[-1]
+            torch.bitwise_and(t << 4, 0xF0, out=img[..., :half])       # low nibbles: the first half of the int8 image (16 w)
+            torch.bitwise_and(t, 0xF0, out=img[..., half:])            # high nibbles: the second half
+            tw = F.QuantWeight(img, w.scale, w.N, w.K, False, had_sign=w.had_sign, paired=w.paired)
+            w._twin8 = tw
+            self.twin_bytes += img.numel()
+        return tw
 
     def _ag_input(self, a: F.QuantAct):
         """Sequence-parallel prefill: the rows the last add-norm quantised live in the all-gather buffer
@@ -414,6 +463,7 @@ class HybridModel:
         self._sp_rpr, self._ag_site, self._qa_src_ptr = M // self.tp, -1, qa_h.q.data_ptr()
         self._qa_ag = self.comm.heap_qact(M, H) if self._sp else None
         sp_used = self._sp
+        self._big_prefill = bool(not decode and M >= 256 and cfg.moe is None)
         ld_in = (max(sh.qkv_n, sh.gdn_in_n) + 7) // 8 * 8
         buf_in = bf(M, ld_in)
         conv_out, gdn_o = f32(M, sh.gdn_conv_c), f32(M, sh.gdn_out_k)
@@ -661,6 +711,7 @@ class HybridModel:
         if self.use_drafter:
             ar_site = self._build_drafter(prog, nseq, M, tap_buf, taps, acc_ptr, bonus_ptr, o_drafts, keep, ar_site)
         self._sp = False
+        self._big_prefill = False
         if self.tp > 1:
             prog.advance(self.comm.seq_base, ar_site, tag="comm_advance")
 

@@ -67,10 +67,11 @@ class Manifest:
     autotune: Optional[str] = None
     allow_untuned: bool = False
     width_table: str = ""
+    prefill_w8: bool = True             # big prefill rungs multiply with an int8 twin of the 4-bit linears (billed below)
 
     SECTIONS = {"model": ("model", "pack", "tp"), "limits": ("max_ctx", "max_seqs", "budget_mib", "headroom_mib", "prefix_cache_mib"),
                 "buckets": ("decode_batches", "decode_widths", "prefill_rows", "draft_block", "width_table"),
-                "plan": ("autotune", "allow_untuned", "gdn_state_dtype", "kv_dtype")}
+                "plan": ("autotune", "allow_untuned", "gdn_state_dtype", "kv_dtype", "prefill_w8")}
 
     @staticmethod
     def from_toml(text: str) -> "Manifest":
@@ -218,6 +219,9 @@ def resolve(manifest: Manifest, device: Optional[DeviceProfile] = None, table: O
     # ---- ledger
     led = Ledger(manifest.budget_mib << 20)
     led.bill("weights", model_weight_bytes(cfg, tp))
+    if manifest.prefill_w8 and cfg.moe is None and getattr(cfg, "weight_format", "iu8") == "iu8" and max(rows) >= 256:
+        # (twice the packed linears; the embedding table and the int8 head have no twin: an upper bound)
+        led.bill("weights_prefill_int8_twin", 2 * model_weight_bytes(cfg, tp))
     state_b = 4 if manifest.gdn_state_dtype == "f32" else 2
     led.bill("gdn_state_slots", (manifest.max_seqs + 1) * cfg.gdn_state_bytes_per_seq(tp, state_b))
     led.bill("prefix_cache_snapshots", manifest.prefix_cache_mib << 20)

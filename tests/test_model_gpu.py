@@ -173,3 +173,43 @@ def test_context_of_131072_tokens_prefill_decode_and_prefix_reuse():
     plain_a = decode(1, blocks_a, first, [], 1)
     assert spec_b == plain_a
     model.scratch.check()
+
+
+def test_a_vocabulary_head_just_over_whole_rounds_of_ctas_runs_its_last_tiles_as_a_split_gemm():
+    """150 feature tiles on 148 SMs: 148 tiles fill one round, the two left over run as a GEMM of their own
+    split along K -- same logits as the oracle, and the spec-decode invariant holds through both heads."""
+    from saber_engine_b200.models.reference_hybrid import forward_full
+    cfg = C.scaled_hybrid(name="hybrid-mini-v38400", vocab=150 * 256)
+    m = HybridModel(cfg, device="cuda", max_seqs=2, max_ctx=512, max_width=5, seed=4)
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
+    res = _prefill(m, prompt, 1, _blocks(0))
+    b = m.buckets[("prefill", 1, 48)]
+    tags = b.program.tags()
+    assert "lm_head.whole_rounds" in tags and "lm_head.last_tiles" in tags and "draft.head.last_tiles" in tags
+    got = b.logits[0, : cfg.vocab].float().cpu()
+    ref = forward_full(cfg, m.w, torch.tensor(prompt))["logits"][-1]
+    assert (got - ref).abs().max() < 0.05 * ref.abs().max() + 1e-3
+    plain, _ = _decode(m, prompt, res.tokens[0][0], [], 1, _blocks(0), 12, 1)
+    res2 = _prefill(m, prompt, 2, _blocks(1))
+    spec, _ = _decode(m, prompt, res2.tokens[0][0], res2.drafts[0], 2, _blocks(1), 12, 5)
+    assert spec == plain
+    m.scratch.check()
+
+
+def test_big_prefill_rungs_on_int8_weight_twins_give_the_same_bytes():
+    """Rungs of 256 rows and more multiply with the int8 image of the 4-bit tiles (no widening pass, two token
+    tiles per CTA): the same integers and scales, so logits, tokens and drafts are the same bytes."""
+    cfg = C.scaled_hybrid()
+    g = torch.Generator().manual_seed(8)
+    prompt = torch.randint(0, cfg.vocab, (300,), generator=g).tolist()
+    outs = []
+    for w8 in (True, False):
+        m = HybridModel(cfg, device="cuda", max_seqs=2, max_ctx=1024, max_width=5, seed=1, prefill_w8=w8)
+        m.reset_slot(1)
+        b = m.build_bucket("prefill", 1, 512)
+        res = run_bucket(m, b, [SeqStep(prompt, 0, 1, 0, list(range(1, 40)))])
+        assert (m.twin_bytes > 0) == w8
+        outs.append((res.tokens[0], res.drafts[0], b.logits[0].float().cpu().clone()))
+        m.scratch.check()
+    assert outs[0][0] == outs[1][0] and outs[0][1] == outs[1][1] and torch.equal(outs[0][2], outs[1][2])
