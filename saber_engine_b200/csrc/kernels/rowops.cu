@@ -233,6 +233,18 @@ __global__ void __launch_bounds__(kRowThreads) row_reg_kernel(const RowOpParams 
   row_reg_body<MODE, MAXC, false>(p, m, red);
 }
 
+// The same body for many rows (prefill rungs): as many threads as the row has 16-value chunks (over MAXC),
+// so that every thread carries the same load and more bytes per SM are in flight.
+template <int MODE, int MAXC>
+__global__ void __launch_bounds__(1024) row_reg_wide_kernel(const RowOpParams p) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[32];
+  const int m = blockIdx.x;
+  if (p.m_live != nullptr && m >= *p.m_live) return;
+  row_reg_body<MODE, MAXC, false>(p, m, red);
+}
+
 // out[m, :] = table[ids[m], :]   (bf16 rows, 16-byte vectors); ids outside [0, vocab) give zeros.
 __global__ void embed_gather_kernel(const __nv_bfloat16* table, const int32_t* ids,
                                     __nv_bfloat16* out, int M, int H, int vocab_lo, int vocab_n,
@@ -281,6 +293,19 @@ extern "C" int saber_row_producer_launch(int mode, const saber::RowOpParams* p, 
   using namespace saber;
   if ((p->K & 127) || p->M_pad < p->M) return static_cast<int>(cudaErrorInvalidValue);
   const int rows = p->q ? p->M_pad : p->M;
+  // many rows (prefill): one thread per chunk (or per two), up to 1024 threads per row
+#define SABER_ROW_WIDE(MODE, MAXC)                                                                       \
+  if (mode == MODE && rows >= 256 && (p->K >> 4) <= MAXC * 1024 && (MAXC == 1 || (p->K >> 4) > 1024)) {   \
+    const int threads = ((((p->K >> 4) + MAXC - 1) / MAXC) + 31) / 32 * 32;                              \
+    saber::launch(row_reg_wide_kernel<MODE, MAXC>, dim3(rows), dim3(threads), 0, stream, 0, *p);         \
+    return static_cast<int>(cudaGetLastError());                                                         \
+  }
+  SABER_ROW_WIDE(kRowAddRms, 1)
+  SABER_ROW_WIDE(kRowSiluMul, 1)
+  SABER_ROW_WIDE(kRowSiluMul, 2)
+  SABER_ROW_WIDE(kRowGateSig, 1)
+  SABER_ROW_WIDE(kRowPlain, 1)
+#undef SABER_ROW_WIDE
   // register-resident forms (no dynamic shared memory) wherever the row fits the chunk budget
 #define SABER_ROW_REG(MODE, MAXC)                                                                \
   if (mode == MODE && p->K <= MAXC * 4096) {                                                     \

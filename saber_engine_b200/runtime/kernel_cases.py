@@ -277,6 +277,7 @@ CASES = {
     "gdn_prefill_512": lambda: _gdn_prefill(512),
     "gdn_prefill_512_one_row": lambda: _gdn_prefill(512, form=2),
     "row_add_rms_m72": lambda: _row(72, 5120),
+    "row_add_rms_m2048": lambda: _row(2048, 5120),
     "moe_block_m72": lambda: _moe(72),
     "vision_tower_512": lambda: _vision(512),
     "vision_tower_1024": lambda: _vision(1024),
