@@ -105,6 +105,7 @@ def main() -> int:
     ap.add_argument("--fuse", type=int, default=1, help="fused GEMM tails (silu-quant epilogue, add-norm-quant row tail): 1 on, 0 off (A/B)")
     ap.add_argument("--gdn-fused", type=int, default=-1, help="DeltaNet decode step as one launch (1) or three (0); -1: the model's default (A/B)")
     ap.add_argument("--gdn-prefill", default="tc", choices=["tc", "rows", "chunked"], help="DeltaNet prefill form (A/B)")
+    ap.add_argument("--prefill-w8", type=int, default=-1, help="int8 twins of the 4-bit linears for big prefill rungs: 1 on, 0 off, -1 while memory allows (A/B)")
     ap.add_argument("--sp-prefill", type=int, default=-1, help="sequence-parallel prefill chain on several ranks: 1 on, 0 off, -1 the launch rules' default (A/B)")
     ap.add_argument("--no-tune-table", action="store_true", help="ignore the committed autotune table (A/B)")
     ap.add_argument("--no-extra-arms", action="store_true", help="skip the NVFP4 side arm of the 27B run")

@@ -128,9 +128,15 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
   // half tiles (p.halves == 2): two CTAs share a packed weight tile, each widens and multiplies only
   // its 128 rows of it (the low or the high nibbles) -- twice the CTAs without split-K
   const int halves = (!kLean && !kBf && p.halves == 2) ? 2 : 1;
-  const int tile_n = halves == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  // Two token tiles per CTA (long row runs): the grid is (token tile pairs, feature tiles), so CTAs that are
+  // scheduled together share a weight tile -- it comes from memory once and from L2 for the other row tiles
+  // (with the feature tile running fastest every row-tile wave would stream the whole weight again).
+  const bool raster_m = !kLean && p.mtiles == 2;
+  const int grid_n = raster_m ? static_cast<int>(gridDim.y) : static_cast<int>(gridDim.x);
+  const int tile_n = raster_m ? static_cast<int>(blockIdx.y)
+                              : (halves == 2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x));
   const int half = halves == 2 ? static_cast<int>(blockIdx.x & 1u) : 0;
-  const int tile_m = blockIdx.y;
+  const int tile_m = raster_m ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.y);
   const int split = blockIdx.z;
 
   const int KB = p.K >> 7;
@@ -209,7 +215,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
-      const uint64_t pol = l2_policy_evict_first();
+      const uint64_t pol = raster_m ? l2_policy_evict_normal() : l2_policy_evict_first();   // pairs: the tile is re-read by the other row tiles
       const uint8_t* wp = w_base + (static_cast<size_t>(tile_n) * KB + kb0) * wbytes;
       const int8_t* ap = p.a + (static_cast<size_t>(kb0) * p.M_pad + m0) * 128;
       const size_t a_kb_stride = static_cast<size_t>(p.M_pad) * 128;
@@ -389,7 +395,7 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
       // runs; the splits check the tile's "clean" flag before they add.  These 31 lanes are
       // otherwise idle.
       pdl_wait();                              // the previous launch may still be reading the blocks
-      const int tile_lin = tile_m * gridDim.x + tile_n;
+      const int tile_lin = tile_m * grid_n + tile_n;
       int4* blk = reinterpret_cast<int4*>(p.acc + static_cast<size_t>(tile_lin) * p.nt * 256);
       const int n16 = p.nt * 64;               // 16-byte pieces of the block
       for (int i = lane - 1; i < n16; i += 31) __stcg(blk + i, make_int4(0, 0, 0, 0));
@@ -814,13 +820,13 @@ __device__ __forceinline__ void gemm_i8_body(const GemmI8Params& p, const int st
             }
           }
         }
-        if (tp) tp_signal((tile_m * mt2 + j2) * gridDim.x + tile_n);
+        if (tp) tp_signal((tile_m * mt2 + j2) * grid_n + tile_n);
         }
       } else if constexpr (!kLean) {
         // each split writes its own partial tile; inside a (split, tile) block the 16-byte group of
         // four columns c4 of row r sits at (c4 * 128 + r) * 16 bytes, so the 32 lanes of a warp
         // (32 consecutive rows) store -- and later load -- 512 contiguous bytes
-        const int tile_lin = tile_m * gridDim.x + tile_n;
+        const int tile_lin = tile_m * grid_n + tile_n;
         const size_t blk_stride = 128u * 256u;   // ints per (split, tile) block
         // Integer partial sums can be added in any order, so the splits of a tile do not keep private
         // copies: each stages its live rows in shared memory and hands them to ONE asynchronous bulk
@@ -1112,6 +1118,7 @@ __global__ void __launch_bounds__(kGemmThreads, 2) gemm_i8_lean_kernel(const Gem
 
 namespace saber {
 static int g_coop_launch = 0;
+static int g_gemm_2sm = 0;     // int8 weights, long row runs: CTA pairs (gemm_w8_2sm.cu) instead of two token tiles per CTA
 constexpr int kMaxDevices = 64;
 // Per-device set-up (function attributes are per device): returns 0 and the SM count of the current device.
 static int device_setup(int* sm_count) {
@@ -1243,6 +1250,9 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
     if (lean_smem <= 112 * 1024)
       return static_cast<int>(saber::launch(gemm_i8_lean_kernel, grid, dim3(kGemmThreads), lean_smem, stream, 2, q, 2));
   }
+  if (g_gemm_2sm && p->mtiles >= 0 && p->nt == 128 && saber_gemm_w8_2sm_ok(p) &&
+      static_cast<int>(grid.x * grid.y) > sm_count)
+    return saber_gemm_w8_2sm_launch(p, 0, stream);
   // long row runs: two token tiles per CTA (pairs must be whole inside M_pad).  4-bit weights are widened once
   // for both tiles; int8 and bf16 weights pass through unwidened and are read from shared memory once for both.
   q.mtiles = 1;
@@ -1259,7 +1269,7 @@ extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cu
     const int smem2 = st2 * (wb + 2 * 16384) + ubytes + 1024;
     if (smem2 <= kSmemLimit) {
       q.mtiles = 2;
-      dim3 grid2(p->N_pad / 256, (p->M + 255) / 256, 1);
+      dim3 grid2((p->M + 255) / 256, p->N_pad / 256, 1);      // token tile pairs run fastest (see raster_m in the kernel)
       return static_cast<int>(saber::launch(p->w4 == 3 ? gemm_bf16_kernel : gemm_i8_kernel, grid2, dim3(kGemmThreads), smem2, stream, 2, q, st2));
     }
   }
@@ -1298,6 +1308,8 @@ extern "C" int saber_gemm_i8_tail_ok(const saber::GemmI8Params* p) {
 }
 
 extern "C" void saber_set_coop_launch(int on) { saber::g_coop_launch = on; }
+extern "C" void saber_set_gemm_2sm(int on) { saber::g_gemm_2sm = on; }
+extern "C" int saber_get_gemm_2sm() { return saber::g_gemm_2sm; }
 
 // ------------------------------------------------------------------------------------------------
 // Entry point that allocates nothing (declared in gemm_i8_noalloc.h).

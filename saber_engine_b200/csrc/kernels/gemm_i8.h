@@ -119,3 +119,9 @@ extern "C" int saber_gemm_i8_parts(const saber::GemmI8Params* p);
 extern "C" int saber_gemm_i8_launch(const saber::GemmI8Params* p, int stages, cudaStream_t stream);
 // 1 when the launch of `p` keeps its whole grid resident (what the fused tails need), else 0.
 extern "C" int saber_gemm_i8_tail_ok(const saber::GemmI8Params* p);
+
+// int8 weights on CTA pairs (tcgen05 cta_group::2) for long row runs: gemm_w8_2sm.cu
+extern "C" int saber_gemm_w8_2sm_ok(const saber::GemmI8Params* p);
+extern "C" int saber_gemm_w8_2sm_launch(const saber::GemmI8Params* p, int stages, cudaStream_t stream);
+extern "C" void saber_set_gemm_2sm(int on);
+extern "C" int saber_get_gemm_2sm();

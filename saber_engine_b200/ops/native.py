@@ -11,6 +11,7 @@ mirrors the parameter blocks as `ctypes.Structure`s, loads the library once, and
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 from typing import Optional
 
@@ -174,7 +175,14 @@ def lib() -> C.CDLL:
                 "Run `python -m saber_engine_b200.build`.") from exc
     _LIB = C.CDLL(str(path))
     _declare(_LIB)
+    if os.environ.get("SABER_GEMM_2SM", "") != "":       # A/B switch: int8 prefill GEMMs on CTA pairs (1) or not (0)
+        _LIB.saber_set_gemm_2sm(int(os.environ["SABER_GEMM_2SM"]))
     return _LIB
+
+
+def set_gemm_2sm(on: bool) -> None:
+    """int8-weight GEMMs over long row runs on CTA pairs (`tcgen05.mma.cta_group::2`) from now on."""
+    lib().saber_set_gemm_2sm(int(bool(on)))
 
 
 def set_pdl(mode: int) -> None:
@@ -259,6 +267,10 @@ def _declare(L: C.CDLL) -> None:
         "saber_program_add_digest_clear": (I, [P, P, I, C.c_char_p]),
         "saber_set_pdl": (None, [I]),
         "saber_get_pdl": (I, []),
+        "saber_set_gemm_2sm": (None, [I]),
+        "saber_get_gemm_2sm": (I, []),
+        "saber_gemm_w8_2sm_ok": (I, [C.POINTER(GemmI8Params)]),
+        "saber_gemm_w8_2sm_launch": (I, [C.POINTER(GemmI8Params), I, S]),
         "saber_moe_route_launch": (I, [C.POINTER(MoeRouteParams), S]),
         "saber_moe_combine_launch": (I, [C.POINTER(MoeCombineParams), S]),
         "saber_moe_gather_launch": (I, [P, P, I, P, P, P, P, I, I, I, I, S]),

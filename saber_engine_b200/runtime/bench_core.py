@@ -144,6 +144,7 @@ def run_benchmark(args, ClockSampler):
                         max_width=W, seed=1234, comm=comm, oracle_p=args.accept_p, oracle_seed=99,
                         gdn_fused=(None if getattr(args, "gdn_fused", -1) < 0 else bool(args.gdn_fused)),
                         fuse=bool(getattr(args, "fuse", 1)), gdn_prefill=getattr(args, "gdn_prefill", "tc"),
+                        prefill_w8=(None if getattr(args, "prefill_w8", -1) < 0 else bool(args.prefill_w8)),
                         sp_prefill=(None if getattr(args, "sp_prefill", -1) < 0 else bool(args.sp_prefill)))
     tuned = None
     table_path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),

@@ -57,6 +57,28 @@ def _gemm(Nn, K, M, w4, splits, copies=3):
     return ws, qa, out
 
 
+def _gemm_2sm(Nn, K, M, copies=3):
+    """int8 weights over a long row run on CTA pairs (cta_group::2), beside the one-CTA kernel on the same operands."""
+    n_pad = L.round_up(Nn, 256)
+    ws = [F.QuantWeight(torch.randint(0, 255, (n_pad // 256, K // 128, 32768), dtype=torch.uint8, device=DEV),
+                        torch.rand(n_pad, device=DEV) * 1e-3, Nn, K, False) for _ in range(copies)]
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    q0 = F.plain_quant(x)
+    m_pad = L.round_up(M, 512)
+    qa = F.QuantAct(torch.zeros(K // 128, m_pad, 128, dtype=torch.int8, device=DEV), torch.zeros(m_pad, device=DEV), M, K)
+    qa.q[:, : q0.M_pad] = q0.q[:, : min(q0.M_pad, m_pad)]
+    qa.scale[: q0.M_pad] = q0.scale[: min(q0.M_pad, m_pad)]
+    out = torch.empty(M, Nn, dtype=torch.bfloat16, device=DEV)
+    sc = F.scratch(DEV)
+    ps = [F.gemm_params(w, qa, out, sc, splits=1) for w in ws]
+    lib = N.lib()
+    fns = [lambda p=p: N.check(lib.saber_gemm_w8_2sm_launch(C.byref(p), 0, N.stream_handle()), "gemm 2sm") for p in ps]
+    _time(fns, f"gemm_w8_2sm N={Nn} K={K} M={M}", n_pad * K * 1.0)
+    fns = [lambda p=p: N.check(lib.saber_gemm_i8_launch(C.byref(p), 0, N.stream_handle()), "gemm") for p in ps]
+    _time(fns, f"gemm_i8 (one CTA, two token tiles) N={Nn} K={K} M={M} w8", n_pad * K * 1.0)
+    return ws, qa, out
+
+
 def _gemm_fp4(Nn, K, M, fmt, splits, copies=3):
     """Native block-scaled FP4 GEMM (4 = NVFP4, 5 = MXFP4): random packed operands and scales."""
     n_pad = L.round_up(Nn, 256)
@@ -276,6 +298,8 @@ CASES = {
     "gdn_prefill_512_chunk_tc": lambda: _gdn_prefill(512, chunk_impl=1),
     "gdn_prefill_512": lambda: _gdn_prefill(512),
     "gdn_prefill_512_one_row": lambda: _gdn_prefill(512, form=2),
+    "gemm_w8_2sm_gate_up_m2048": lambda: _gemm_2sm(34816, 5120, 2048),
+    "gemm_w8_2sm_down_m2048": lambda: _gemm_2sm(5120, 17408, 2048),
     "row_add_rms_m72": lambda: _row(72, 5120),
     "row_add_rms_m2048": lambda: _row(2048, 5120),
     "moe_block_m72": lambda: _moe(72),

@@ -95,3 +95,34 @@ def test_gemm_back_to_back_launches_keep_their_pipeline_phases():
         tol = 1e-2 * ref.abs().max().item() + 1e-6
         for o in outs:
             assert (o.float().cpu() - ref).abs().max().item() <= tol
+
+
+def test_gemm_int8_weights_on_cta_pairs_gives_the_bytes_of_the_one_cta_kernel():
+    """`tcgen05.mma.cta_group::2`: a cluster of two CTAs per 512 x 256 output tile, each loading its token
+    rows and its half of the weight tile.  Same integers, same scales, same rounding as the one-CTA kernel."""
+    import ctypes as C
+    from saber_engine_b200.ops import native as N
+    dev = torch.device("cuda")
+    lib = N.lib()
+    for (M, Nn, K, seed) in [(512, 256, 256, 21), (1024, 512, 1024, 22), (700, 304, 2048, 23), (1300, 256, 512, 25), (2048, 1024, 5120, 24)]:
+        g = torch.Generator().manual_seed(seed)
+        w = torch.randn(Nn, K, generator=g) * 0.02
+        x = torch.randn(M, K, generator=g)
+        wq, ws = L.quantize_weight_rows(w, 8)
+        aq, asc = L.quantize_act_rows(x)
+        qw = F.QuantWeight.from_int(wq, ws, 8, dev)
+        m_pad = L.round_up(M, 512)
+        qa = F.QuantAct(L.tile_act_int8(aq, m_pad).to(dev), torch.cat([asc, torch.zeros(m_pad - M)]).to(dev), M, K)
+        ldo = L.round_up(Nn, 8)
+        one = torch.zeros(M, ldo, dtype=torch.bfloat16, device=dev)
+        two = torch.zeros(M, ldo, dtype=torch.bfloat16, device=dev)
+        p1 = F.gemm_params(qw, qa, one, F.scratch(dev), splits=1)
+        N.check(lib.saber_gemm_i8_launch(C.byref(p1), 0, N.stream_handle()), "one-CTA gemm")
+        p2 = F.gemm_params(qw, qa, two, F.scratch(dev), splits=1)
+        assert lib.saber_gemm_w8_2sm_ok(C.byref(p2)) == 1
+        N.check(lib.saber_gemm_w8_2sm_launch(C.byref(p2), 0, N.stream_handle()), "CTA-pair gemm")
+        torch.cuda.synchronize()
+        F.scratch(dev).check()
+        ref = R.gemm_i8(wq, ws, aq, asc).float()
+        assert (one[:, :Nn].float().cpu() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-6
+        assert torch.equal(one, two), (M, Nn, K, (one.float() - two.float()).abs().max().item())
