@@ -48,6 +48,7 @@ struct OpAttn { saber::AttnParams p; };
 struct OpArgmax { const void* logits; int rows, ld, V, id_offset; int32_t* idx; float* val; };
 struct OpSeam { const void* logits; int rows, ld, V, id_offset; const float* temps; int32_t* ids; float* vals; float* lse; };
 struct OpVerify { saber::VerifyParams p; };
+struct OpDraftIndex { saber::DraftIndexParams p; };
 struct OpMemset { void* dst; int value; size_t bytes; };
 struct OpCopy { void* dst; const void* src; size_t bytes; };
 struct OpAllReduce { saber::AllReduceParams p; };
@@ -62,7 +63,7 @@ struct OpMoeGather { const int8_t* q; const float* scale; int M_pad; const int32
                      int8_t* q_out; float* scale_out; int rows_cap, M_pad_out, K, to_fp8; };
 
 using Op = std::variant<OpGemm, OpRow, OpEmbed, OpGdnConv, OpGdnRec, OpRope, OpAttn, OpArgmax,
-                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather, OpDigest, OpDigestClear, OpGdnChunk, OpLogitGather, OpSampleSeam, OpGdnStep, OpSeamMerge>;
+                        OpSeam, OpVerify, OpMemset, OpCopy, OpAllReduce, OpExpand, OpAdvance, OpPickMerge, OpMoeRoute, OpMoeCombine, OpMoeGather, OpDigest, OpDigestClear, OpGdnChunk, OpLogitGather, OpSampleSeam, OpGdnStep, OpSeamMerge, OpDraftIndex>;
 
 struct Entry {
   Op op;
@@ -105,6 +106,7 @@ int launch(const Op& op, cudaStream_t s) {
         else if constexpr (std::is_same_v<T, OpSeam>)
           return saber_topk_seam_launch(o.logits, o.rows, o.ld, o.V, o.id_offset, o.temps, o.ids, o.vals, o.lse, s);
         else if constexpr (std::is_same_v<T, OpVerify>) return saber_verify_launch(&o.p, s);
+        else if constexpr (std::is_same_v<T, OpDraftIndex>) return saber_draft_index_launch(&o.p, s);
         else if constexpr (std::is_same_v<T, OpMemset>)
           return static_cast<int>(cudaMemsetAsync(o.dst, o.value, o.bytes, s));
         else if constexpr (std::is_same_v<T, OpCopy>)
@@ -228,6 +230,9 @@ int saber_program_add_seam(void* h, const void* logits, int rows, int ld, int V,
 }
 int saber_program_add_verify(void* h, const saber::VerifyParams* p, const char* tag) {
   return add(h, OpVerify{*p}, 1, tag);
+}
+int saber_program_add_draft_index(void* h, const saber::DraftIndexParams* p, const char* tag) {
+  return add(h, OpDraftIndex{*p}, 1, tag);
 }
 int saber_program_add_memset(void* h, void* dst, int value, size_t bytes, const char* tag) {
   return add(h, OpMemset{dst, value, bytes}, 1, tag);

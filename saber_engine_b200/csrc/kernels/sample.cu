@@ -349,6 +349,39 @@ extern "C" int saber_logit_gather_launch(const void* logits, int rows, int ld, i
   return static_cast<int>(cudaGetLastError());
 }
 
+namespace saber {
+// one thread per block row
+__global__ void draft_index_kernel(const DraftIndexParams p) {
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int R = p.nseq * p.block;
+  if (i >= R) return;
+  const int b = i / p.block, j = i - b * p.block;
+  const int rows = p.cu_rows[b + 1] - p.cu_rows[b];
+  const int r = p.acc_row[b];
+  const bool live = rows > 0 && r >= p.cu_rows[b] && r < p.cu_rows[b + 1];
+  // sequence index of the committed row: the step's rows end at kv_len - 1
+  const int at = live ? p.kv_len[b] - (p.cu_rows[b + 1] - r) : 0;
+  const int t = at + 1 + j;
+#pragma unroll
+  for (int ax = 0; ax < 3; ++ax) p.pos_out[ax * R + i] = live ? p.pos[ax * p.M + r] + 1 + j : 0;
+  int slot = -1;
+  if (live && t / p.page_tokens < p.max_blocks) {
+    const int blk = p.block_table[static_cast<size_t>(b) * p.max_blocks + t / p.page_tokens];
+    if (blk > 0) slot = blk * p.page_tokens + t % p.page_tokens;      // block 0 is the null page
+  }
+  p.slot_out[i] = slot;
+  if (j == 0) p.kv_len_out[b] = live ? at + 1 + p.block : 0;
+}
+}  // namespace saber
+
+extern "C" int saber_draft_index_launch(const saber::DraftIndexParams* p, cudaStream_t stream) {
+  const int R = p->nseq * p->block;
+  if (R <= 0) return 0;
+  saber::launch(saber::draft_index_kernel, dim3((R + 127) / 128), dim3(128), 0, stream, 0, *p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int saber_verify_launch(const saber::VerifyParams* p, cudaStream_t stream) {
   if (p->nseq <= 0) return 0;
   saber::launch(saber::verify_accept_kernel, dim3((p->nseq + 63) / 64), dim3(64), 0, stream, 0, *p);

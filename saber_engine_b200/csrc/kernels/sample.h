@@ -22,7 +22,23 @@ struct VerifyParams {
   uint64_t seed;
 };
 
+// Index tables of the drafter's block rows (the drafter's attention layers): block row j of sequence b sits at the
+// position that follows the last committed row of the step by j + 1 tokens.
+struct DraftIndexParams {
+  const int32_t* pos;          // [3][M] rope positions of the step's rows
+  const int32_t* cu_rows;      // [nseq + 1]
+  const int32_t* kv_len;       // [nseq] tokens of the sequence after this step's rows
+  const int32_t* acc_row;      // [nseq] global row index of the last committed row
+  const int32_t* block_table;  // [nseq][max_blocks]
+  int32_t* pos_out;            // [3][nseq * block]
+  int32_t* slot_out;           // [nseq * block] KV slot of the block row (-1: none)
+  int32_t* kv_len_out;         // [nseq] context + block rows, what the block's attention sees
+  int M, nseq, block, max_blocks, page_tokens;
+};
+
 }  // namespace saber
+
+extern "C" int saber_draft_index_launch(const saber::DraftIndexParams* p, cudaStream_t stream);
 
 extern "C" int saber_argmax_launch(const void* logits, int rows, int ld, int V, int id_offset,
                                    int32_t* out_idx, float* out_val, cudaStream_t stream);

@@ -35,6 +35,11 @@ class DrafterConfig:
     block: int = 8
     n_taps: int = 5            # target layers whose residual stream conditions the drafter
     head_bits: int = 4
+    # attention in the first `attn_layers` drafter layers: the block rows attend (causally) over a context-KV
+    # store written from the target's last tap row of every context position, and over the block's own rows
+    attn_layers: int = 0
+    attn_q_heads: int = 4
+    attn_kv_heads: int = 1
 
 
 @dataclass(frozen=True)

@@ -196,6 +196,12 @@ class HybridModel:
             if cfg.is_attention_layer(i):
                 self.kv[i] = torch.zeros(kv_blocks, self.sh.n_kv_heads, 2, cfg.page_tokens, cfg.head_dim,
                                          dtype=torch.uint8, device=dev)
+        # the drafter's context-KV store: one page pool per drafter attention layer, addressed by the target's block tables
+        self.draft_kv = {}
+        if cfg.drafter is not None and use_drafter:
+            for li in range(getattr(cfg.drafter, "attn_layers", 0)):
+                self.draft_kv[li] = torch.zeros(kv_blocks, cfg.drafter.attn_kv_heads, 2, cfg.page_tokens, cfg.head_dim,
+                                                dtype=torch.uint8, device=dev)
         # ---- GDN state slots (slot 0 = null slot)
         self.n_slots = max_seqs + 1
         hv, hk, d = self.sh.gdn_v_heads, self.sh.gdn_k_heads, cfg.gdn_head_dim
@@ -448,6 +454,7 @@ class HybridModel:
         base = blob.data_ptr()
         at = lambda off: base + 4 * off                 # noqa: E731  device address of a table
         prog = N.Program(f"{kind}-b{nseq}-w{width}")
+        self._lay_at = (lay, at, blob)                  # the bucket's index tables, for builders further down
         self._site_nt = {}                              # TP site -> row-tile height its producer signals with
         self._site_parts = {}                           # TP site -> flags per feature tile (split-K parts)
         bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)   # noqa: E731
@@ -459,7 +466,8 @@ class HybridModel:
         self._sp = bool(not decode and self.tp > 1 and self.sp_prefill and cfg.moe is None and not plp
                         and M % (128 * self.tp) == 0 and M <= min(self.comm.layout.rows_max, 64 * 128)
                         and getattr(cfg, "weight_format", "iu8") == "iu8"
-                        and getattr(self.w.layers[0].mixer_in, "had_sign", None) is None)
+                        and getattr(self.w.layers[0].mixer_in, "had_sign", None) is None
+                        and not self.draft_kv)      # (the context-KV store wants the tap rows of every position on every rank)
         self._sp_rpr, self._ag_site, self._qa_src_ptr = M // self.tp, -1, qa_h.q.data_ptr()
         self._qa_ag = self.comm.heap_qact(M, H) if self._sp else None
         sp_used = self._sp
@@ -744,8 +752,62 @@ class HybridModel:
         qa_x, qa_di = self._qa(R, Hd), self._qa(R, dc.inter)
         gu = torch.zeros(R, 2 * dc.inter, dtype=torch.bfloat16, device=dev)
         assert Hd == cfg.hidden
+        # ---- attention layers: context K | V of this step's rows (from the last tap), then the block rows
+        n_attn = len(self.draft_kv)
+        if n_attn:
+            D, nqd, nkvd = cfg.head_dim, dc.attn_q_heads, dc.attn_kv_heads
+            lay_, at_, blob_ = self._lay_at
+            tc = int(self.attn_impl == "tc")
+            qa_tap = self._qa(M, H)
+            kvbuf = torch.zeros(M, 2 * nkvd * D, dtype=torch.bfloat16, device=dev)
+            dummy_q = torch.zeros(1, dtype=torch.bfloat16, device=dev)
+            prog.row(N.ROW_PLAIN, F.row_params(M, H, a=tap_buf[nt - 1], qa=self._fmt(qa_tap, dw.layers[0]["attn"]["kv_ctx"])), tag="draft.ctx.tap_quant")
+            # index tables of the block rows: positions, KV slots, and the length their attention sees
+            idx = torch.zeros(3 * R + R + nseq, dtype=torch.int32, device=dev)
+            pos_d, slot_d, kvlen_d = idx[:3 * R], idx[3 * R: 4 * R], idx[4 * R:]
+            cu_d = torch.arange(0, R + 1, B, dtype=torch.int32, device=dev)
+            ip = N.DraftIndexParams()
+            ip.pos, ip.cu_rows, ip.kv_len, ip.acc_row = at_(lay_.pos), at_(lay_.cu_rows), at_(lay_.kv_len), acc_ptr
+            ip.block_table, ip.pos_out, ip.slot_out, ip.kv_len_out = at_(lay_.block_table), pos_d.data_ptr(), slot_d.data_ptr(), kvlen_d.data_ptr()
+            ip.M, ip.nseq, ip.block, ip.max_blocks, ip.page_tokens = M, nseq, B, self.max_blocks, cfg.page_tokens
+            prog.draft_index(ip, tag="draft.block_index")
+            qkvbuf = torch.zeros(R, (nqd + 2 * nkvd) * D, dtype=torch.bfloat16, device=dev)
+            q_rot_d = torch.zeros(R, nqd, D, dtype=torch.bfloat16, device=dev)
+            attn_d = torch.zeros(R, nqd, D, dtype=torch.bfloat16, device=dev)
+            qa_ad = self._qa(R, nqd * D)
+            da = torch.zeros(R, Hd, dtype=torch.bfloat16, device=dev)
+            keep += [qa_tap, kvbuf, dummy_q, idx, cu_d, qkvbuf, q_rot_d, attn_d, qa_ad, da]
         for li, lw in enumerate(dw.layers):
-            self._add_rms(prog, R, f"draft.L{li}.norm", lw["norm"], x, self._fmt(qa_x, lw["gate_up"]), None if li == 0 else dd)
+            prev = None if li == 0 else dd
+            if li < n_attn:
+                aw = lw["attn"]
+                # context K | V of the step's rows: projected from the target's tap row, normed, rotated, appended
+                self._gemm(prog, aw["kv_ctx"], qa_tap, kvbuf, f"draft.L{li}.attn.kv_ctx")
+                rk = F.rope_kv_params(kvbuf, dummy_q, aw["q_norm"], aw["k_norm"], blob_, blob_, self.draft_kv[li], 0, nkvd,
+                                      0, 0, nkvd * D, rot_dim=cfg.rot_dim, sections=cfg.mrope_sections, theta=cfg.rope_theta,
+                                      eps=cfg.eps, w_offset=cfg.norm_offset, k_scale=self.k_scale, v_scale=self.v_scale, page_layout=tc)
+                rk.pos, rk.slot_map, rk.ld = at_(lay_.pos), at_(lay_.slot_map), kvbuf.stride(0)
+                prog.rope(rk, tag=f"draft.L{li}.attn.ctx_kv_append")
+                # the block rows: q | k | v from the drafter's own stream, appended behind the context, causal attention
+                self._add_rms(prog, R, f"draft.L{li}.attn.norm", aw["norm"], x, self._fmt(qa_x, aw["qkv"]), prev)
+                self._gemm(prog, aw["qkv"], qa_x, qkvbuf, f"draft.L{li}.attn.qkv")
+                rb = F.rope_kv_params(qkvbuf, q_rot_d, aw["q_norm"], aw["k_norm"], pos_d, slot_d, self.draft_kv[li], nqd, nkvd,
+                                      0, nqd * D, (nqd + nkvd) * D, rot_dim=cfg.rot_dim, sections=cfg.mrope_sections,
+                                      theta=cfg.rope_theta, eps=cfg.eps, w_offset=cfg.norm_offset, k_scale=self.k_scale,
+                                      v_scale=self.v_scale, page_layout=tc)
+                prog.rope(rb, tag=f"draft.L{li}.attn.rope_kv")
+                ap = F.attn_params(q_rot_d, self.draft_kv[li], blob_.view(1, -1), cu_d, kvlen_d, attn_d, None, None, nkvd, 1, 1,
+                                   self.k_scale, self.v_scale)
+                ap.block_table, ap.max_blocks, ap.nseq = at_(lay_.block_table), self.max_blocks, nseq
+                ap.err = self.scratch.err.data_ptr()
+                ap.pack_rows, ap.impl = B, tc
+                prog.attn(ap, tag=f"draft.L{li}.attn.core")
+                self._flush(prog)
+                prog.row(N.ROW_PLAIN, F.row_params(R, nqd * D, a=attn_d.view(R, nqd * D), qa=self._fmt(qa_ad, aw["o_proj"])),
+                         tag=f"draft.L{li}.attn.quant")
+                self._gemm(prog, aw["o_proj"], qa_ad, da, f"draft.L{li}.attn.o_proj", hold=True)
+                prev = da
+            self._add_rms(prog, R, f"draft.L{li}.norm", lw["norm"], x, self._fmt(qa_x, lw["gate_up"]), prev)
             self._mlp_in(prog, lw["gate_up"], qa_x, gu, qa_di, lw["down"], dc.inter, R, f"draft.L{li}")
             self._gemm(prog, lw["down"], qa_di, dd, f"draft.L{li}.down", hold=True)
         self._add_rms(prog, R, "draft.final_norm", dw.final_norm, x, self._fmt(qa_x, dw.head), dd if dw.layers else None)

@@ -72,6 +72,8 @@ class ModelWeights:
             tot += qw(self.drafter.aux_fc) + qw(self.drafter.head)
             for d in self.drafter.layers:
                 tot += qw(d["gate_up"]) + qw(d["down"])
+                if "attn" in d:
+                    tot += qw(d["attn"]["kv_ctx"]) + qw(d["attn"]["qkv"]) + qw(d["attn"]["o_proj"])
         return tot
 
 
@@ -230,10 +232,17 @@ def random_init(cfg: HybridConfig, tp: int, rank: int, device, seed: int = 0,
         Hd = dc.hidden
         dw = DrafterWeights(aux_fc=_quant_on(dev, rand(Hd, dc.n_taps * H), 4),
                             pos_emb=(torch.randn(dc.block, Hd, generator=g, device=dev) * std).to(torch.bfloat16))
-        for _ in range(dc.n_layers):
-            dw.layers.append(dict(norm=vec(Hd),
-                                  gate_up=_quant_on(dev, rand(2 * dc.inter, Hd), 4),
-                                  down=_quant_on(dev, rand(Hd, dc.inter), 4)))
+        for li in range(dc.n_layers):
+            lw = dict(norm=vec(Hd),
+                      gate_up=_quant_on(dev, rand(2 * dc.inter, Hd), 4),
+                      down=_quant_on(dev, rand(Hd, dc.inter), 4))
+            if li < getattr(dc, "attn_layers", 0):
+                nq, nkv, D = dc.attn_q_heads, dc.attn_kv_heads, cfg.head_dim
+                lw["attn"] = dict(norm=vec(Hd), q_norm=vec(D), k_norm=vec(D),
+                                  kv_ctx=_quant_on(dev, rand(2 * nkv * D, H), 4),          # context K | V from the target's tap row
+                                  qkv=_quant_on(dev, rand((nq + 2 * nkv) * D, Hd), 4),      # the block rows' q | k | v
+                                  o_proj=_quant_on(dev, rand(Hd, nq * D), 4))
+            dw.layers.append(lw)
         dw.final_norm = vec(Hd)
         dw.head = _quant_on(dev, rand(cfg.vocab, Hd), dc.head_bits)
         mw.drafter = dw

@@ -99,6 +99,11 @@ class AttnParams(C.Structure):
                 ("v_scale", F), ("err", P), ("pack_rows", I), ("n_blocks", I), ("impl", I)]
 
 
+class DraftIndexParams(C.Structure):
+    _fields_ = [("pos", P), ("cu_rows", P), ("kv_len", P), ("acc_row", P), ("block_table", P), ("pos_out", P),
+                ("slot_out", P), ("kv_len_out", P), ("M", I), ("nseq", I), ("block", I), ("max_blocks", I), ("page_tokens", I)]
+
+
 class VerifyParams(C.Structure):
     _fields_ = [("draft", P), ("target", P), ("cu_rows", P), ("seq_uid", P), ("step_no", P),
                 ("n_commit", P), ("out_tokens", P), ("accept_row", P), ("bonus", P), ("nseq", I), ("max_w", I), ("oracle_p", F),
@@ -267,6 +272,8 @@ def _declare(L: C.CDLL) -> None:
         "saber_program_add_digest_clear": (I, [P, P, I, C.c_char_p]),
         "saber_set_pdl": (None, [I]),
         "saber_get_pdl": (I, []),
+        "saber_draft_index_launch": (I, [C.POINTER(DraftIndexParams), S]),
+        "saber_program_add_draft_index": (I, [P, C.POINTER(DraftIndexParams), C.c_char_p]),
         "saber_set_gemm_2sm": (None, [I]),
         "saber_get_gemm_2sm": (I, []),
         "saber_gemm_w8_2sm_ok": (I, [C.POINTER(GemmI8Params)]),
@@ -389,6 +396,9 @@ class Program:
     def seam(self, logits, rows, ld, V, id_offset, temps, ids, vals, lse, tag="seam") -> int:
         return self._L.saber_program_add_seam(self._h, ptr(logits), rows, ld, V, id_offset,
                                               ptr(temps), ptr(ids), ptr(vals), ptr(lse), tag.encode())
+
+    def draft_index(self, p: "DraftIndexParams", tag="draft_index") -> int:
+        return self._L.saber_program_add_draft_index(self._h, C.byref(p), tag.encode())
 
     def verify(self, p: VerifyParams, tag="verify") -> int:
         return self._L.saber_program_add_verify(self._h, C.byref(p), tag.encode())

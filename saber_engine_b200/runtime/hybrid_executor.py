@@ -194,6 +194,7 @@ class HybridExecutor:
         lane = self.copy_lane()
         with torch.cuda.stream(m.stream):          # the gathers run on the step stream (ordered after the last step) ...
             staged = [(f"kv.{i}", kv[idx]) for i, kv in m.kv.items()]
+            staged += [(f"draft_kv.{i}", kv[idx]) for i, kv in getattr(m, "draft_kv", {}).items()]   # the drafter's context-KV store
             for i in m.gdn_state:
                 staged += [(f"gdn_state.{i}", m.gdn_state[i][slot].clone()), (f"gdn_stash.{i}", m.gdn_stash[i][slot].clone()),
                            (f"gdn_hist.{i}", m.gdn_hist[i][slot].clone())]
@@ -218,9 +219,10 @@ class HybridExecutor:
             for name, dtype, shape, off, nbytes in header["tensors"]:
                 kind, i = name.rsplit(".", 1)
                 i = int(i)
-                dst = {"kv": m.kv, "gdn_state": m.gdn_state, "gdn_stash": m.gdn_stash, "gdn_hist": m.gdn_hist}[kind][i]
+                dst = {"kv": m.kv, "draft_kv": getattr(m, "draft_kv", {}), "gdn_state": m.gdn_state, "gdn_stash": m.gdn_stash,
+                       "gdn_hist": m.gdn_hist}[kind][i]
                 src = buf[off:off + nbytes].to(m.device).view(dst.dtype).reshape(shape)
-                if kind == "kv":
+                if kind in ("kv", "draft_kv"):
                     dst[idx] = src
                 else:
                     dst[slot].copy_(src)

@@ -510,3 +510,44 @@ def test_device_draw_equals_the_host_sampler_on_the_same_candidates():
                                     [], [], float(u[r]))
         agree += int(want == got[r])
     assert agree >= 78            # fp32 on the device, double on the host: a draw at a boundary may differ
+
+
+def test_draft_block_index_tables():
+    """Positions, KV slots and attention lengths of the drafter's block rows, against the plain statement."""
+    import ctypes as C
+    import numpy as np
+    from saber_engine_b200.ops import native as N
+    nseq, B, max_blocks, page, M = 3, 4, 8, 16, 20
+    cu = np.array([0, 5, 5, 20], dtype=np.int32)               # the middle sequence is a padding slot (no rows)
+    kv_len = np.array([37, 0, 110], dtype=np.int32)             # sequence 2: block rows 110 .. 113 cross into the page that is not there
+    acc = np.array([2, 0, 19], dtype=np.int32)                 # last committed rows: row 2 of sequence 0, the last row of sequence 2
+    pos = np.arange(3 * M, dtype=np.int32).reshape(3, M) * 3 + 7
+    bt = np.zeros((nseq, max_blocks), dtype=np.int32)
+    bt[0, :4] = [5, 9, 2, 11]
+    bt[2, :8] = [20, 21, 22, 23, 24, 25, 26, 0]                # the eighth page is not allocated
+    dev = lambda a: torch.from_numpy(a).to(DEV)
+    t = dict(pos=dev(pos.reshape(-1)), cu=dev(cu), kv=dev(kv_len), acc=dev(acc), bt=dev(bt.reshape(-1)))
+    R = nseq * B
+    pos_o = torch.full((3 * R,), -7, dtype=torch.int32, device=DEV)
+    slot_o = torch.full((R,), -7, dtype=torch.int32, device=DEV)
+    len_o = torch.full((nseq,), -7, dtype=torch.int32, device=DEV)
+    p = N.DraftIndexParams()
+    p.pos, p.cu_rows, p.kv_len, p.acc_row, p.block_table = (t[k].data_ptr() for k in ("pos", "cu", "kv", "acc", "bt"))
+    p.pos_out, p.slot_out, p.kv_len_out = pos_o.data_ptr(), slot_o.data_ptr(), len_o.data_ptr()
+    p.M, p.nseq, p.block, p.max_blocks, p.page_tokens = M, nseq, B, max_blocks, page
+    N.check(N.lib().saber_draft_index_launch(C.byref(p), N.stream_handle()), "draft_index")
+    torch.cuda.synchronize()
+    want_pos, want_slot, want_len = np.zeros((3, R), np.int32), np.full(R, -1, np.int32), np.zeros(nseq, np.int32)
+    for b in range(nseq):
+        if cu[b + 1] == cu[b]:
+            continue
+        at = kv_len[b] - (cu[b + 1] - acc[b])                   # sequence index of the committed row
+        want_len[b] = at + 1 + B
+        for j in range(B):
+            tpos = at + 1 + j
+            want_pos[:, b * B + j] = pos[:, acc[b]] + 1 + j
+            blk = bt[b, tpos // page] if tpos // page < max_blocks else 0
+            want_slot[b * B + j] = blk * page + tpos % page if blk > 0 else -1
+    assert np.array_equal(pos_o.cpu().numpy().reshape(3, R), want_pos)
+    assert np.array_equal(slot_o.cpu().numpy(), want_slot)
+    assert np.array_equal(len_o.cpu().numpy(), want_len)

@@ -213,3 +213,30 @@ def test_big_prefill_rungs_on_int8_weight_twins_give_the_same_bytes():
         outs.append((res.tokens[0], res.drafts[0], b.logits[0].float().cpu().clone()))
         m.scratch.check()
     assert outs[0][0] == outs[1][0] and outs[0][1] == outs[1][1] and torch.equal(outs[0][2], outs[1][2])
+
+
+def test_drafter_attention_layers_over_the_context_kv_store_keep_the_invariants():
+    """A drafter whose first layer attends over a context-KV store (written from the target's tap row of every
+    context position, addressed by the target's block tables) and over its own block rows: drafts change, the
+    committed tokens do not (speculative == plain greedy), and graph replay == eager walk."""
+    import dataclasses
+    base = C.scaled_hybrid()
+    cfg = dataclasses.replace(base, name="hybrid-mini-dattn", drafter=dataclasses.replace(base.drafter, attn_layers=1))
+    m = HybridModel(cfg, device="cuda", max_seqs=4, max_ctx=512, max_width=5, seed=1)
+    ref = HybridModel(base, device="cuda", max_seqs=4, max_ctx=512, max_width=5, seed=1)
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, cfg.vocab, (40,), generator=g).tolist()
+    res = _prefill(m, prompt, 1, _blocks(0))
+    tags = m.buckets[("prefill", 1, 48)].program.tags()
+    assert "draft.L0.attn.core" in tags and "draft.L0.attn.ctx_kv_append" in tags and "draft.block_index" in tags
+    res_ref = _prefill(ref, prompt, 1, _blocks(0))
+    assert res.tokens[0] == res_ref.tokens[0]                       # the target is the same model
+    plain, _ = _decode(m, prompt, res.tokens[0][0], [], 1, _blocks(0), 14, 1)
+    res2 = _prefill(m, prompt, 2, _blocks(1))
+    spec, n_spec = _decode(m, prompt, res2.tokens[0][0], res2.drafts[0], 2, _blocks(1), 14, 5)
+    assert spec == plain
+    res3 = _prefill(m, prompt, 3, _blocks(2))
+    eager, _ = _decode(m, prompt, res3.tokens[0][0], res3.drafts[0], 3, _blocks(2), 14, 5, eager=True)
+    assert eager == plain
+    assert int(m.draft_kv[0].abs().sum()) > 0                        # the store has been written
+    m.scratch.check()
