@@ -229,6 +229,8 @@ def by_name(name: str):
              "qwen38-27b-nvfp4": lambda: dataclasses.replace(qwen38_27b(), name="qwen38-27b-nvfp4", weight_format="nvfp4"),
              "flashnext-moe-mxfp4": lambda: dataclasses.replace(flashnext_moe(), name="flashnext-moe-mxfp4",
                                                                 moe=MoEConfig(512, 10, 512, 512, True, "mxfp4")),
+             "qwen38-27b-dattn": lambda: dataclasses.replace(qwen38_27b(), name="qwen38-27b-dattn",
+                                                             drafter=dataclasses.replace(qwen38_27b().drafter, attn_layers=1)),
              "tiny-qwen3": TinyQwen3Config}
     if name not in table:
         raise KeyError(f"unknown model {name!r}; known: {sorted(table)}")
