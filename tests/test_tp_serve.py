@@ -114,6 +114,14 @@ if rank == 0:
     subs = [s.submit(EngineRequest(shared + [7, 8, 9 + i], SamplingParams(max_tokens=12))) for i in range(3)]
     subs.append(s.submit(EngineRequest([j % 400 for j in range(3000)], SamplingParams(max_tokens=40))))   # multi-part frames, many pages
     s.run_until_idle()
+    # a session parked and restored through the frames: its page list rides in one export / import frame
+    ps = s.submit(EngineRequest(list(range(20, 420)), SamplingParams(max_tokens=400)))
+    while not any(x.seq_id == ps.seq_id and not x.prefilling and x.output for x in s.running):
+        s.step()                             # (the prompt is prefilled in pieces, one per prefix-cache cut point)
+    key = s.park(ps.seq_id)
+    s.run_until_idle()
+    s.restore(key)
+    s.run_until_idle()
     lead.stop_followers()
     print(json.dumps({"rank": 0, "log": ex.launch_log, "cast": lead.calls_cast, "bytes": lead.bytes_cast,
                       "state": sorted((k, v[1]) for k, v in ex._state.items())}))
