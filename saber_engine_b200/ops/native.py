@@ -275,6 +275,7 @@ def _declare(L: C.CDLL) -> None:
         "saber_draft_index_launch": (I, [C.POINTER(DraftIndexParams), S]),
         "saber_program_add_draft_index": (I, [P, C.POINTER(DraftIndexParams), C.c_char_p]),
         "saber_set_gemm_2sm": (None, [I]),
+        "saber_set_gemm_2sm_persistent": (None, [I]),
         "saber_get_gemm_2sm": (I, []),
         "saber_gemm_w8_2sm_ok": (I, [C.POINTER(GemmI8Params)]),
         "saber_gemm_w8_2sm_launch": (I, [C.POINTER(GemmI8Params), I, S]),

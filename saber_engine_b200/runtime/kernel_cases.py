@@ -73,7 +73,11 @@ def _gemm_2sm(Nn, K, M, copies=3):
     ps = [F.gemm_params(w, qa, out, sc, splits=1) for w in ws]
     lib = N.lib()
     fns = [lambda p=p: N.check(lib.saber_gemm_w8_2sm_launch(C.byref(p), 0, N.stream_handle()), "gemm 2sm") for p in ps]
-    _time(fns, f"gemm_w8_2sm N={Nn} K={K} M={M}", n_pad * K * 1.0)
+    lib.saber_set_gemm_2sm_persistent(1)
+    _time(fns, f"gemm_w8_2sm persistent N={Nn} K={K} M={M}", n_pad * K * 1.0)
+    lib.saber_set_gemm_2sm_persistent(0)
+    _time(fns, f"gemm_w8_2sm one tile per cluster N={Nn} K={K} M={M}", n_pad * K * 1.0)
+    lib.saber_set_gemm_2sm_persistent(1)
     fns = [lambda p=p: N.check(lib.saber_gemm_i8_launch(C.byref(p), 0, N.stream_handle()), "gemm") for p in ps]
     _time(fns, f"gemm_i8 (one CTA, two token tiles) N={Nn} K={K} M={M} w8", n_pad * K * 1.0)
     return ws, qa, out

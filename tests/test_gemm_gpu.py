@@ -104,7 +104,7 @@ def test_gemm_int8_weights_on_cta_pairs_gives_the_bytes_of_the_one_cta_kernel():
     from saber_engine_b200.ops import native as N
     dev = torch.device("cuda")
     lib = N.lib()
-    for (M, Nn, K, seed) in [(512, 256, 256, 21), (1024, 512, 1024, 22), (700, 304, 2048, 23), (1300, 256, 512, 25), (2048, 1024, 5120, 24)]:
+    for (M, Nn, K, seed) in [(512, 256, 256, 21), (1024, 512, 1024, 22), (700, 304, 2048, 23), (1300, 256, 512, 25), (2048, 1024, 5120, 24), (2048, 20480, 256, 26)]:
         g = torch.Generator().manual_seed(seed)
         w = torch.randn(Nn, K, generator=g) * 0.02
         x = torch.randn(M, K, generator=g)
@@ -120,9 +120,15 @@ def test_gemm_int8_weights_on_cta_pairs_gives_the_bytes_of_the_one_cta_kernel():
         N.check(lib.saber_gemm_i8_launch(C.byref(p1), 0, N.stream_handle()), "one-CTA gemm")
         p2 = F.gemm_params(qw, qa, two, F.scratch(dev), splits=1)
         assert lib.saber_gemm_w8_2sm_ok(C.byref(p2)) == 1
-        N.check(lib.saber_gemm_w8_2sm_launch(C.byref(p2), 0, N.stream_handle()), "CTA-pair gemm")
+        N.check(lib.saber_gemm_w8_2sm_launch(C.byref(p2), 0, N.stream_handle()), "CTA-pair gemm")       # persistent pairs (default)
+        three = torch.zeros(M, ldo, dtype=torch.bfloat16, device=dev)
+        p3 = F.gemm_params(qw, qa, three, F.scratch(dev), splits=1)
+        lib.saber_set_gemm_2sm_persistent(0)
+        N.check(lib.saber_gemm_w8_2sm_launch(C.byref(p3), 0, N.stream_handle()), "CTA-pair gemm, one tile per cluster")
+        lib.saber_set_gemm_2sm_persistent(1)
         torch.cuda.synchronize()
         F.scratch(dev).check()
+        assert torch.equal(one, three)
         ref = R.gemm_i8(wq, ws, aq, asc).float()
         assert (one[:, :Nn].float().cpu() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-6
         assert torch.equal(one, two), (M, Nn, K, (one.float() - two.float()).abs().max().item())
