@@ -78,14 +78,19 @@ def test_follower_rank_runs_the_leaders_calls(tmp_path):
         env = dict(os.environ, RANK=str(r), INIT=init, PYTHONPATH=os.pathsep.join([os.getcwd()] + sys.path))
         procs.append(subprocess.Popen([sys.executable, "-c", _CHILD], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
     outs = []
-    for p in procs:
-        try:
-            so, se = p.communicate(timeout=120)
-        except subprocess.TimeoutExpired:
-            p.kill()
-            pytest.fail("rank process did not finish")
-        assert p.returncode == 0, se[-2000:]
-        outs.append(json.loads(so.strip().splitlines()[-1]))
+    try:
+        for p in procs:
+            try:
+                so, se = p.communicate(timeout=120)
+            except subprocess.TimeoutExpired:
+                p.kill()
+                pytest.fail("rank process did not finish")
+            assert p.returncode == 0, se[-2000:]
+            outs.append(json.loads(so.strip().splitlines()[-1]))
+    finally:
+        for p in procs:               # no rank may outlive the test
+            if p.poll() is None:
+                p.kill()
     lead, fol = (outs[0], outs[1]) if outs[0]["rank"] == 0 else (outs[1], outs[0])
     assert lead["log"] == fol["log"] and len(lead["log"]) > 5          # the same launches, in the same order
     assert fol["served"] == lead["cast"] - 1                           # every call but the stop
@@ -128,7 +133,8 @@ if rank == 0:
     ch.close()
 else:
     ch = ShmChannel(line, 3, rank, create=False)
-    n = follower_loop(ex, None, channel=ch)
+    from saber_engine_b200.parallel.launcher import parent_alive
+    n = follower_loop(ex, None, channel=ch, alive=parent_alive(os.getppid()))
     print(json.dumps({"rank": rank, "log": ex.launch_log, "served": n,
                       "state": sorted((k, v[1]) for k, v in ex._state.items())}))
     ch.close()
@@ -154,14 +160,19 @@ def test_followers_run_the_leaders_calls_from_fixed_layout_frames_over_shared_me
     lead.stdin.write("go\n")
     lead.stdin.flush()
     outs = []
-    for p in [lead] + fols:
-        try:
-            so, se = p.communicate(timeout=120)
-        except subprocess.TimeoutExpired:
-            p.kill()
-            pytest.fail("rank process did not finish")
-        assert p.returncode == 0, se[-2000:]
-        outs.append(json.loads(so.strip().splitlines()[-1]))
+    try:
+        for p in [lead] + fols:
+            try:
+                so, se = p.communicate(timeout=120)
+            except subprocess.TimeoutExpired:
+                p.kill()
+                pytest.fail("rank process did not finish")
+            assert p.returncode == 0, se[-2000:]
+            outs.append(json.loads(so.strip().splitlines()[-1]))
+    finally:
+        for p in [lead] + fols:       # a leader that failed leaves followers polling their lines: none may outlive the test
+            if p.poll() is None:
+                p.kill()
     l, f1, f2 = outs
     assert l["log"] == f1["log"] == f2["log"] and len(l["log"]) > 8
     assert f1["served"] == f2["served"] == l["cast"] - 1
