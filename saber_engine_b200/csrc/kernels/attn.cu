@@ -464,6 +464,7 @@ extern "C" int saber_attn_launch(const saber::AttnParams* p, cudaStream_t stream
     return static_cast<int>(cudaGetLastError());
   }
   if (p->splits > 1 && p->q_tiles != 1) return static_cast<int>(cudaErrorInvalidValue);
+  if (p->window > 0) return static_cast<int>(cudaErrorInvalidValue);      // sliding windows: the tcgen05 kernel only
   const int group = p->nq / p->nkv;
   // decode (one query tile): pack several heads of the group into one 16-row tile
   int hpt = 1, pack = 16;

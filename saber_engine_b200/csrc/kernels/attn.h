@@ -44,6 +44,7 @@ struct AttnParams {
   int n_blocks;                // blocks in kv_cache (0 = unknown): a table entry outside [0, n_blocks) is
                                // recorded in the status word and its page is treated as empty
   int impl;                    // 0: warp-level MMA kernel on [16][256] pages; 1: tcgen05 kernel on core-matrix pages
+  int window;                  // > 0: sliding window -- a row sees its last `window` keys only (tcgen05 kernel); 0: all
 };
 
 }  // namespace saber

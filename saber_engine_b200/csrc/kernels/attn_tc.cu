@@ -93,8 +93,10 @@ __global__ void __launch_bounds__(kTcThreads) attn_tc_kernel(const AttnParams p,
   const int kbase = kvlen - (n - 1) + t0;              // keys visible to token 0 of the tile (exclusive bound)
   const int kmax = kbase + ntok - 1;
   const int pages = (kmax + kPageTokens - 1) / kPageTokens;
-  const int per = (pages + p.splits - 1) / p.splits;
-  const int pg0 = sp * per, pg1 = min(pages, pg0 + per);
+  // sliding window: pages wholly below the first row's window are never touched
+  const int pg_first = p.window > 0 ? min(max(0, kbase - p.window) / kPageTokens, pages) : 0;
+  const int per = (pages - pg_first + p.splits - 1) / p.splits;
+  const int pg0 = pg_first + sp * per, pg1 = min(pages, pg0 + per);
   const int npages = max(0, pg1 - pg0);
   const int ntiles = (npages + kTcPages - 1) / kTcPages;
   const int key_end = pg1 * kPageTokens;
@@ -262,10 +264,11 @@ __global__ void __launch_bounds__(kTcThreads) attn_tc_kernel(const AttnParams p,
       if (warp == 4 && lane == 0 && j < 20) { ATTN_STAMP(8 + 4 * j); }
       const int key0 = (pg0 + j * kTcPages) * kPageTokens;
       const int kcap = min(klim, key_end) - key0;        // columns below this bound are live for the row
+      const int kfloor = p.window > 0 ? klim - p.window - key0 : 0;     // ... and, with a window, columns from this one on
       float alpha = 1.f;
       if (warp_live) {
         const uint32_t prow = p_s + (j & 1) * kTcPBytes + (r >> 3) * 1024 + (r & 7) * 16;
-        const bool full_tile = kcap >= kTcKeys;          // no masking needed for this row
+        const bool full_tile = kcap >= kTcKeys && kfloor <= 0;   // no masking needed for this row
         // (every decision that steers a TMEM load below is made for the WHOLE warp: the loads are
         // warp-collective)
         // Rows without a reference maximum yet (first tile with live keys) take a maximum pass first.
@@ -278,7 +281,7 @@ __global__ void __launch_bounds__(kTcThreads) attn_tc_kernel(const AttnParams p,
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if (full_tile || c0 + i < kcap) tmax = fmaxf(tmax, __uint_as_float(sv[i]));
+              if (full_tile || (c0 + i < kcap && c0 + i >= kfloor)) tmax = fmaxf(tmax, __uint_as_float(sv[i]));
           }
           if (row_live && m_ref == -INFINITY) m_ref = tmax * scale_log2;     // (nothing accumulated yet: no rescale)
         }
@@ -303,7 +306,7 @@ __global__ void __launch_bounds__(kTcThreads) attn_tc_kernel(const AttnParams p,
               for (int e = 0; e < 4; ++e) {
                 const int c = c0 + 4 * i + e;
                 const float sc = __uint_as_float(sv[4 * i + e]);
-                const bool on = row_live && (full_tile || c < kcap);
+                const bool on = row_live && (full_tile || (c < kcap && c >= kfloor));
                 tmax = on ? fmaxf(tmax, sc) : tmax;
                 pv[e] = on ? exp2f(sc * scale_log2 - msafe) : 0.f;
                 l_tile += pv[e];

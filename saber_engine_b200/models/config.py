@@ -40,6 +40,7 @@ class DrafterConfig:
     attn_layers: int = 0
     attn_q_heads: int = 4
     attn_kv_heads: int = 1
+    attn_window: int = 2048      # sliding window of the drafter's attention (keys a block row sees); 0: the whole context
 
 
 @dataclass(frozen=True)

@@ -797,7 +797,7 @@ class HybridModel:
                                       v_scale=self.v_scale, page_layout=tc)
                 prog.rope(rb, tag=f"draft.L{li}.attn.rope_kv")
                 ap = F.attn_params(q_rot_d, self.draft_kv[li], blob_.view(1, -1), cu_d, kvlen_d, attn_d, None, None, nkvd, 1, 1,
-                                   self.k_scale, self.v_scale)
+                                   self.k_scale, self.v_scale, window=(dc.attn_window if tc else 0))
                 ap.block_table, ap.max_blocks, ap.nseq = at_(lay_.block_table), self.max_blocks, nseq
                 ap.err = self.scratch.err.data_ptr()
                 ap.pack_rows, ap.impl = B, tc

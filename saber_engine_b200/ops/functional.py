@@ -548,7 +548,7 @@ def rope_kv(qkv, q_norm_w, k_norm_w, pos, slot_map, kv_cache, nq, nkv, q_off, k_
 
 
 def attn_params(q, kv_cache, block_table, cu_q, kv_len, out, part_o, part_ml, nkv, splits, q_tiles,
-                k_scale=1.0, v_scale=1.0, sm_scale=None, pack_rows: int = 0, impl: int = 0):
+                k_scale=1.0, v_scale=1.0, sm_scale=None, pack_rows: int = 0, impl: int = 0, window: int = 0):
     p = N.AttnParams()
     p.q, p.kv_cache, p.block_table = q.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr()
     p.cu_q, p.kv_len, p.out = cu_q.data_ptr(), kv_len.data_ptr(), out.data_ptr()
@@ -561,11 +561,12 @@ def attn_params(q, kv_cache, block_table, cu_q, kv_len, out, part_o, part_ml, nk
     p.n_blocks = kv_cache.shape[0]
     p.pack_rows = pack_rows if q_tiles == 1 else 0
     p.impl = impl                    # 1: tcgen05 kernel (pages in core-matrix order)
+    p.window = window                # > 0: a row sees its last `window` keys only (tcgen05 kernel)
     return p
 
 
 def attention(q, kv_cache, block_table, cu_q, kv_len, nkv, max_rows_per_seq: int, splits: int = 1,
-              k_scale=1.0, v_scale=1.0, impl: int = 0):
+              k_scale=1.0, v_scale=1.0, impl: int = 0, window: int = 0):
     """q bf16 [M, nq, 256]; returns bf16 [M, nq, 256]."""
     out = torch.empty_like(q)
     nseq, nq = kv_len.numel(), q.shape[1]
@@ -575,6 +576,6 @@ def attention(q, kv_cache, block_table, cu_q, kv_len, nkv, max_rows_per_seq: int
         part_o = torch.empty(nseq, nq, splits, 16, 256, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(nseq, nq, splits, 16, 2, dtype=torch.float32, device=q.device)
     p = attn_params(q, kv_cache, block_table, cu_q, kv_len, out, part_o, part_ml, nkv, splits,
-                    q_tiles, k_scale, v_scale, pack_rows=max_rows_per_seq, impl=impl)
+                    q_tiles, k_scale, v_scale, pack_rows=max_rows_per_seq, impl=impl, window=window)
     N.check(N.lib().saber_attn_launch(C.byref(p), N.stream_handle()), "attn")
     return out

@@ -96,7 +96,7 @@ class AttnParams(C.Structure):
     _fields_ = [("q", P), ("kv_cache", P), ("block_table", P), ("cu_q", P), ("kv_len", P),
                 ("out", P), ("part_o", P), ("part_ml", P), ("nseq", I), ("nq", I), ("nkv", I),
                 ("max_blocks", I), ("splits", I), ("q_tiles", I), ("sm_scale", F), ("k_scale", F),
-                ("v_scale", F), ("err", P), ("pack_rows", I), ("n_blocks", I), ("impl", I)]
+                ("v_scale", F), ("err", P), ("pack_rows", I), ("n_blocks", I), ("impl", I), ("window", I)]
 
 
 class DraftIndexParams(C.Structure):

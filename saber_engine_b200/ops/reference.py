@@ -127,8 +127,9 @@ def fp8_round(x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
     return (x.float() / scale).to(torch.float8_e4m3fn).float() * scale
 
 
-def attention_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_len: int) -> torch.Tensor:
-    """One sequence. q fp32 [n, nq, 256]; k, v fp32 [kv_len, nkv, 256]; right-aligned causal mask."""
+def attention_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_len: int, window: int = 0) -> torch.Tensor:
+    """One sequence. q fp32 [n, nq, 256]; k, v fp32 [kv_len, nkv, 256]; right-aligned causal mask
+    (window > 0: a row sees its last `window` keys only)."""
     n, nq, _ = q.shape
     nkv = k.shape[1]
     g = nq // nkv
@@ -138,6 +139,8 @@ def attention_rows(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_len: in
     rows = torch.arange(n)[:, None]
     keys = torch.arange(kv_len)[None, :]
     mask = keys < (kv_len - (n - 1) + rows)
+    if window > 0:
+        mask = mask & (keys >= (kv_len - (n - 1) + rows - window))
     s = s.masked_fill(~mask[None], float("-inf"))
     p = torch.softmax(s, -1)
     return torch.einsum("hnk,khd->nhd", p, vv)

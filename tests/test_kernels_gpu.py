@@ -274,7 +274,7 @@ def test_gdn_fused_step_equals_the_three_launches_byte_for_byte():
 _LAST_GOT = []
 
 
-def _attn_case(ctx_lens, rows, splits, nq=12, nkv=2, seed=0, impl=0, tol=3e-2):
+def _attn_case(ctx_lens, rows, splits, nq=12, nkv=2, seed=0, impl=0, tol=3e-2, window=0):
     torch.manual_seed(seed)
     nseq = len(ctx_lens)
     M = sum(rows)
@@ -312,7 +312,7 @@ def _attn_case(ctx_lens, rows, splits, nq=12, nkv=2, seed=0, impl=0, tol=3e-2):
     q_out = F.rope_kv(qkv.to(DEV), qw.to(DEV), kw.to(DEV), pos.to(DEV), slot_map.to(DEV), cache_d,
                       nq, nkv, q_off, k_off, v_off, page_layout=impl)
     out = F.attention(q_out, cache_d, perm.to(DEV), cu_t.to(DEV), kv_len.to(DEV), nkv,
-                      max(rows), splits=splits, impl=impl)
+                      max(rows), splits=splits, impl=impl, window=window)
     torch.cuda.synchronize()
     F.scratch(DEV).check()
     # reference
@@ -325,7 +325,7 @@ def _attn_case(ctx_lens, rows, splits, nq=12, nkv=2, seed=0, impl=0, tol=3e-2):
         sl = slice(cu[b], cu[b + 1])
         kk = torch.cat([R.fp8_round(k_hist[b]), R.fp8_round(k_new[sl])], 0)
         vv = torch.cat([R.fp8_round(v_hist[b]), R.fp8_round(v_new[sl])], 0)
-        ref = R.attention_rows(R.bf16_round(q_ref[sl]), kk, vv, int(kv_len[b]))
+        ref = R.attention_rows(R.bf16_round(q_ref[sl]), kk, vv, int(kv_len[b]), window=window)
         got = out[sl].float().cpu()
         err = (got - ref).abs().max().item()
         _LAST_GOT.append((got, ref))
@@ -472,6 +472,16 @@ def test_gdn_tensor_core_prefill_split_at_a_chunk_boundary_gives_the_same_bytes(
     F.scratch(DEV).check()
     assert torch.equal(o1, o2) and torch.equal(s1, s2)
     assert torch.equal(o1, o3) and torch.equal(s1, s3)
+
+
+def test_attention_sliding_window_on_the_tensor_core_kernel():
+    """A row sees its last `window` keys only: pages below the first row's window are skipped, the rows' own
+    lower bounds are masked inside the first tile; decode (with and without splits) and a prefill tile."""
+    _attn_case([700, 37, 1500], [5, 5, 5], splits=1, impl=1, window=256, seed=31)
+    _attn_case([700, 37, 1500], [4, 4, 4], splits=3, impl=1, window=100, seed=32)      # a window that is no page multiple
+    # prefill rows: the window slides inside the tile (128 keys per row: the e4m3 probabilities average over fewer terms)
+    _attn_case([900], [200], splits=1, impl=1, window=128, seed=33, nq=6, nkv=1, tol=5e-2)
+    _attn_case([50], [6], splits=1, impl=1, window=2048, seed=34)                      # a window longer than the context is no window
 
 
 def test_attention_packs_several_heads_into_one_tile():
