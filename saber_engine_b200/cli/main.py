@@ -306,8 +306,16 @@ def cmd_explain(a) -> int:
 
 
 def cmd_tune(a) -> int:
-    from ..plan import tune_gemm
-    return tune_gemm.main(["--model", a.model, "--tp", str(a.tp), "--rows", a.rows, "--out", a.out])
+    """GEMM records first (a new table), then the decode attention's split counts into the same file."""
+    from ..plan import tune_attn, tune_gemm
+    ops = set((getattr(a, "ops", "") or "gemm,attn").split(","))
+    rc = 0
+    if "gemm" in ops:
+        rc = tune_gemm.main(["--model", a.model, "--tp", str(a.tp), "--rows", a.rows, "--out", a.out])
+    if rc == 0 and "attn" in ops:
+        import os
+        rc = tune_attn.main(["--model", a.model, "--tp", str(a.tp)] + (["--into", a.out] if os.path.exists(a.out) else ["--out", a.out]))
+    return rc
 
 
 def cmd_pack(a) -> int:
@@ -453,6 +461,7 @@ def make_parser() -> argparse.ArgumentParser:
     t.add_argument("--tp", type=int, default=1)
     t.add_argument("--rows", default="9,72")
     t.add_argument("--out", default="autotune.json")
+    t.add_argument("--ops", default="gemm,attn", help="what to measure: gemm (a new table), attn (decode attention splits, added to the table)")
     p = sub.add_parser("pack")
     p.add_argument("action", choices=["build", "check"])
     p.add_argument("--model", default="hybrid-mini")

@@ -418,6 +418,12 @@ class HybridModel:
         """KV splits of the decode attention: fill the GPU once (the `decode_splits` law of the launch
         rules, per attention kernel)."""
         from ..rules import default_rules
+        if self.attn_impl == "tc" and getattr(self, "tune_table", None) is not None:
+            from ..plan.tune_attn import lookup
+            hit = lookup(self.tune_table, nseq, width, min(self.max_ctx, getattr(self, "attn_ctx_hint", 4096)),
+                         self.sh.n_q_heads, self.sh.n_kv_heads)
+            if hit is not None:
+                return hit
         return default_rules().attn_decode_splits(self.attn_impl, nseq, self.sh.n_kv_heads,
                                                   self.sh.n_q_heads // self.sh.n_kv_heads, width)
 

@@ -105,3 +105,20 @@ def test_cli_front_door(tmp_path, capsys):
     assert "tp=8" in capsys.readouterr().out
     r = subprocess.run([sys.executable, "-m", "saber_engine_b200", "probe"], capture_output=True, text=True)
     assert r.returncode == 0 and "native_library" in r.stdout
+
+
+def test_attention_split_records_are_looked_up_by_shape_and_nearest_context():
+    """`attn_tc_decode` records sit beside the GEMM records; a lookup takes the record of the largest tuned
+    context not above the asked one, and none when the shape was never measured."""
+    from saber_engine_b200.plan.autotune import TuneRecord, TuneTable, make_key
+    from saber_engine_b200.plan.tune_attn import OP, lookup
+    t = TuneTable("test-device", "build")
+    t.put(TuneRecord(make_key(OP, nseq=8, width=8, ctx=4096, nq=24, nkv=4), {"splits": 4, "name": "s4"}, 40.0, 41.0, 7, True))
+    t.put(TuneRecord(make_key(OP, nseq=8, width=8, ctx=65536, nq=24, nkv=4), {"splits": 16, "name": "s16"}, 300.0, 320.0, 7, True))
+    assert lookup(t, 8, 8, 4096, 24, 4) == 4
+    assert lookup(t, 8, 8, 20000, 24, 4) == 4            # between the tuned contexts: the one below
+    assert lookup(t, 8, 8, 262144, 24, 4) == 16
+    assert lookup(t, 8, 8, 512, 24, 4) is None           # below the smallest tuned context: the rules decide
+    assert lookup(t, 4, 8, 4096, 24, 4) is None and lookup(None, 8, 8, 4096, 24, 4) is None
+    t2 = TuneTable.load_json(t.to_json()) if hasattr(TuneTable, "load_json") else None
+    assert t2 is None or lookup(t2, 8, 8, 4096, 24, 4) == 4
