@@ -52,3 +52,19 @@ def test_the_launchers_read_the_table_and_the_digest_follows_it():
     finally:
         set_default_rules(None)
     assert pick_splits(20, 1, 136) == 7
+
+
+def test_prefill_and_tail_thresholds_are_table_entries_and_the_ledger_bills_the_int8_twins():
+    from saber_engine_b200.plan import launch_plan as LP
+    r = default_rules()
+    assert r.doc["prefill"]["sequence_parallel_min_ranks"] == 2 and r.doc["gemm"]["tails"]["row_tail_max_ranks"] == 1
+    doc = copy.deepcopy(r.doc)
+    del doc["prefill"]["sequence_parallel_min_ranks"]
+    with pytest.raises(RulesError) as ei:
+        Rules(doc)
+    assert "sequence_parallel_min_ranks" in str(ei.value)
+    # big prefill rungs multiply with int8 twins of the 4-bit linears: the plan bills them before it sizes the KV pool
+    on = LP.resolve(LP.Manifest(allow_untuned=True))
+    off = LP.resolve(LP.Manifest(allow_untuned=True, prefill_w8=False))
+    assert "weights_prefill_int8_twin" in on.ledger.items and "weights_prefill_int8_twin" not in off.ledger.items
+    assert on.plan_hash != off.plan_hash
