@@ -216,3 +216,18 @@ def test_a_follower_that_dies_ends_in_the_fatal_law(tmp_path):
             else:
                 os.environ[k] = v
     assert parent_alive(os.getppid())() and not parent_alive(1 if os.getppid() != 1 else 2)()
+
+
+def test_export_and_import_frames_carry_the_page_list():
+    """Parking across ranks rides on two small-integer frames: slot, token count, park id and the session's pages."""
+    from saber_engine_b200.parallel.control_frames import FrameDecoder, FrameEncoder
+    enc, dec = FrameEncoder(), FrameDecoder()
+    blocks = list(range(7, 7 + 700))                       # more than one 4 KiB part
+    parts = enc.encode("export_session", 3, 11000, 42, *blocks)
+    assert len(parts) == 2
+    got = None
+    for p in parts:
+        got = dec.feed(p)
+    assert got == ("export_session", (3, 11000, 42, *blocks))
+    (part,) = enc.encode("import_session", 1, 42, *blocks[:5])
+    assert dec.feed(part) == ("import_session", (1, 42, 7, 8, 9, 10, 11))
